@@ -1,0 +1,195 @@
+/*
+ * krk_cuda.h -- C ABI of the B200 (sm_100a) backend for Kraken's quantized-weight
+ * matmul path: GGUF Q8_0 / Q4_0 / Q4_K / Q6_K weights that stay quantized in device
+ * memory and are decoded inside the GEMV (decode) and GEMM (prefill) kernels.
+ *
+ * Conventions (they mirror krk::Backend, include/krk/backend.hpp:337):
+ *  - every data pointer is a DEVICE pointer unless the parameter is named host_*;
+ *  - weights are the unmodified GGUF bytes, row-major [n_out][krk_cuda_row_bytes()],
+ *    16-byte aligned at the base, resident and not written while a call is in flight;
+ *  - activations and outputs are f32 (the CPU backend's activation type,
+ *    src/backend_cpu.cpp:584), except the f16 X of the prefill entry;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the default stream, which is
+ *    the reference's only stream, include/krk/backend.hpp:775-779); work is enqueued,
+ *    ordered, asynchronous;
+ *  - every entry returns 0 or a negative KRK_CUDA_E* code, never aborts or throws,
+ *    and has launched nothing when it returns an error (the reference's "false =
+ *    nothing launched" rule for optional fused ops, include/krk/backend.hpp:876-881).
+ * There is no CPU fallback behind any entry.
+ */
+#ifndef KRK_CUDA_H
+#define KRK_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* GGUF on-disk type ids, identical to krk::DType (include/krk/quant.hpp:16-30). */
+#define KRK_CUDA_Q4_0 2
+#define KRK_CUDA_Q8_0 8
+#define KRK_CUDA_Q4_K 12
+#define KRK_CUDA_Q6_K 14
+
+/* Activation types accepted by krk_cuda_gemm. */
+#define KRK_CUDA_X_F32 0
+#define KRK_CUDA_X_F16 1
+
+#define KRK_CUDA_OK 0
+#define KRK_CUDA_EDTYPE (-1)    /* weight type is not one of the four above */
+#define KRK_CUDA_ESHAPE (-2)    /* n_in not a whole number of blocks, negative size, rows out of range */
+#define KRK_CUDA_ENULL (-3)     /* a required pointer is NULL */
+#define KRK_CUDA_EALIGN (-4)    /* weight base or x not 16-byte aligned, or y not 4-byte aligned */
+#define KRK_CUDA_ELAUNCH (-5)   /* the CUDA runtime refused the launch; see krk_cuda_last_cuda_error() */
+#define KRK_CUDA_EWORKSPACE (-6)/* workspace missing or smaller than the _workspace_bytes() answer */
+#define KRK_CUDA_EDEVICE (-7)   /* no sm_100 device is current */
+#define KRK_CUDA_EARG (-8)      /* any other bad argument (n_mat, k, flags) */
+#define KRK_CUDA_ETIMEOUT (-9)  /* a bounded device-side wait gave up; see krk_cuda_device_status() */
+
+#define KRK_CUDA_MAX_GROUP 16   /* matrices per grouped launch */
+#define KRK_CUDA_MAX_ROWS 8     /* activation rows per GEMV launch */
+
+const char *krk_cuda_strerror(int rc);
+
+/* Text of the last CUDA runtime error seen by this library on this thread ("" if none). */
+const char *krk_cuda_last_cuda_error(void);
+
+/* 1 if `wt` is Q8_0, Q4_0, Q4_K or Q6_K. Replaces krk::dtype_supported for this path
+ * (include/krk/quant.hpp:180-186). */
+int krk_cuda_dtype_ok(int wt);
+
+/* Geometry: replaces dtype_block_size / dtype_block_bytes / dtype_row_bytes
+ * (src/quant.cpp:1805-1900). 0 for an unsupported type. */
+int krk_cuda_block_size(int wt);
+int krk_cuda_block_bytes(int wt);
+size_t krk_cuda_row_bytes(int wt, int64_t n_in);
+
+/* Can the GEMV/GEMM address a contraction of k columns of type wt? Replaces
+ * Backend::gemm_k_ok (include/krk/backend.hpp:862-869): k > 0 and a whole number of
+ * blocks. */
+int krk_cuda_gemm_k_ok(int wt, int64_t k);
+
+/* out_f32[n_rows][n_in] = decode(w). Bit-exact with the host decoders deq_q8_0 /
+ * deq_q4_0 / deq_q4_k / deq_q6_k (src/quant.cpp:331-339, 381-387, 437-460, 491-512)
+ * behind krk::dequant_row (src/quant.cpp:1911-1960). */
+int krk_cuda_dequant_rows(void *out_f32, const void *w, int wt, int64_t n_rows, int64_t n_in,
+                          void *stream);
+
+/* Decode GEMV: y[rows][n_out] (+)= x[rows][n_in] . W^T for rows in 1..8. Replaces
+ * Backend::gemm at rows <= 8 (include/krk/backend.hpp:858-860; HIP ladder
+ * src/hip/backend_hip.hip:3203-3237) and, with accumulate != 0, Backend::gemm_accumulate
+ * with a null rexp (include/krk/backend.hpp:894-900). y must not alias x. */
+int krk_cuda_gemv(void *y_f32, const void *x_f32, const void *w, int wt, int64_t n_out,
+                  int64_t n_in, int64_t rows, int accumulate, void *stream);
+
+/* Up to KRK_CUDA_MAX_GROUP independent GEMVs of one activation row each, in one launch.
+ * Replaces Backend::gemm_group at rows == 1 (include/krk/backend.hpp:1040-1056;
+ * src/hip/kernels/fused.hpp:71-126). x[m] is matrix m's activation (the same pointer
+ * may repeat: the `x` form; distinct pointers: the `xs` form). All matrices share n_in.
+ * With fuse_silu_pair != 0 matrices (0,1), (2,3), ... are gate/up pairs of equal n_out:
+ * y[2i] receives silu(gate) * up; y[2i+1] must still be a valid buffer of n_out floats,
+ * whose contents are unspecified afterwards (the `silu` fold,
+ * src/hip/kernels/fused.hpp:142-169; silu as in src/backend_cpu.cpp:2394-2400).
+ * The pointer arrays are HOST arrays, read before the call returns. */
+int krk_cuda_gemv_group(void *const host_y[], const void *const host_x[],
+                        const void *const host_w[], const int host_wt[],
+                        const int64_t host_n_out[], int64_t n_in, int n_mat,
+                        int fuse_silu_pair, void *stream);
+
+/* Prefill GEMM on the tensor cores: y[rows][n_out] = x[rows][n_in] . W^T, W decoded to
+ * f16 tiles in shared memory, f32 accumulation. Replaces Backend::gemm at rows > 8
+ * (src/hip/backend_hip.hip:3284-3325 -> src/hip/kernels/gemm.hpp:621-970). x is f16
+ * (KRK_CUDA_X_F16) or f32 (KRK_CUDA_X_F32, converted to f16 into the workspace first).
+ * n_in must be a multiple of 256. */
+size_t krk_cuda_gemm_workspace_bytes(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows);
+int krk_cuda_gemm(void *y_f32, const void *x, int x_dtype, const void *w, int wt, int64_t n_out,
+                  int64_t n_in, int64_t rows, void *workspace, size_t ws_bytes, void *stream);
+
+/* Router on the device: softmax over n_expert logits per token, k picks of the largest
+ * probability (ties to the lower id), weights renormalised over the picks. Replaces the
+ * host routing of Engine::moe_ffn (src/engine.cpp:11704-11713, 11853-11920) and
+ * Backend::router_softmax / router_topk (include/krk/backend.hpp:934-975).
+ * ids_i32 and wts_f32 are [n_tok][k]. */
+int krk_cuda_route(void *ids_i32, void *wts_f32, const void *logits_f32, int64_t n_tok,
+                   int n_expert, int k, void *stream);
+
+/* One bank of routed experts held by this device: expert e (global id) is held when
+ * expert_base <= e < expert_base + n_local; its matrices are the e-expert_base'th
+ * [n_ff][row_bytes(n_embd)] / [n_embd][row_bytes(n_ff)] slices of gate/up/down. */
+struct krk_cuda_expert_bank {
+    const void *gate;   /* [n_local][n_ff][row_bytes(wt_gate_up, n_embd)] */
+    const void *up;     /* same shape as gate */
+    const void *down;   /* [n_local][n_embd][row_bytes(wt_down, n_ff)] */
+    int wt_gate_up;
+    int wt_down;
+    int n_local;
+    int expert_base;
+    int64_t n_embd;
+    int64_t n_ff;
+};
+
+/* Routed-expert FFN: y[t] = sum over the picks of token t that this bank holds, in
+ * ascending expert id, of wts * Wdown_e . (silu(Wgate_e x_t) * (Wup_e x_t)); picks held
+ * elsewhere contribute nothing (a shard's partial sum). Replaces the per-expert loop /
+ * moe_decode_batch / Backend::moe_dispatch (src/engine.cpp:12353-, 10896-11060;
+ * include/krk/backend.hpp:1001-1009). ids/wts come from krk_cuda_route. n_tok in 1..8.
+ * workspace: krk_cuda_moe_workspace_bytes() bytes of device memory. */
+size_t krk_cuda_moe_workspace_bytes(const struct krk_cuda_expert_bank *bank, int k, int64_t n_tok);
+int krk_cuda_moe_ffn(void *y_f32, const void *x_f32, const void *ids_i32, const void *wts_f32,
+                     const struct krk_cuda_expert_bank *bank, int k, int64_t n_tok,
+                     void *workspace, size_t ws_bytes, void *stream);
+
+/* out = silu(gate) * up elementwise (Backend::silu_mul, include/krk/backend.hpp:1309;
+ * src/backend_cpu.cpp:2394-2400). */
+int krk_cuda_silu_mul(void *out_f32, const void *gate_f32, const void *up_f32, int64_t n,
+                      void *stream);
+
+/* dst[rows[i]] += alpha[i] * src[i] over rows of n floats (Backend::scatter_axpy_rows,
+ * include/krk/backend.hpp:1473; src/backend_cpu.cpp:3193-3220). Row indices must be
+ * distinct within one call. */
+int krk_cuda_scatter_axpy_rows(void *dst_f32, const void *src_f32, const void *rows_i32,
+                               const void *alpha_f32, int64_t n_rows, int64_t n, void *stream);
+
+/* Sum n_parts partial outputs [n_parts][n] in part order 0..n_parts-1 into out[n]: the
+ * deterministic combine of expert-sharded partial sums after they were gathered. */
+int krk_cuda_sum_parts(void *out_f32, const void *parts_f32, int n_parts, int64_t n, void *stream);
+
+/* Device-side status word of the current device: 0, or a KRK_CUDA_ETIMEOUT-class code
+ * written by a kernel whose bounded wait gave up. Synchronises the device. */
+int krk_cuda_device_status(void);
+
+/* Kernels launched by this library since the process started (all threads). */
+int64_t krk_cuda_launch_count(void);
+
+/* ---- host-buffer plumbing: the CudaBackend class of krk_cuda_backend.hpp behind a C face ----
+ * These are the calls a host that is not C++ binds. `be` is the object returned by
+ * krk_cuda_backend_make (make_hip_backend's contract, include/krk/backend.hpp:1886: NULL and a
+ * message in err on failure). alloc/release/upload/download/fill0/sync replace the members of
+ * the same names (include/krk/backend.hpp:361-362, 720, 755, 769, 770); gemm, gemm_accumulate and
+ * gemm_group replace include/krk/backend.hpp:858-860, 894-900, 1040-1056 and, like the
+ * reference, log and abort on a shape they cannot address (ask gemm_k_ok first). host_* pointers
+ * are host memory (pinned memory makes upload asynchronous); all others come from alloc. */
+void *krk_cuda_backend_make(int device_index, char *err, size_t err_len);
+void krk_cuda_backend_free(void *be);
+const char *krk_cuda_backend_describe(void *be);
+void *krk_cuda_backend_alloc(void *be, size_t bytes);
+void krk_cuda_backend_release(void *be, void *p);
+void krk_cuda_backend_upload(void *be, void *dst, const void *host_src, size_t bytes);
+void krk_cuda_backend_download(void *be, void *host_dst, const void *src, size_t bytes);
+void krk_cuda_backend_fill0(void *be, void *p, size_t bytes);
+void krk_cuda_backend_sync(void *be);
+int krk_cuda_backend_gemm_k_ok(void *be, int wt, int64_t k);
+void krk_cuda_backend_gemm(void *be, void *out, const void *x, const void *w, int wt, int64_t n_out,
+                           int64_t n_in, int64_t rows);
+int krk_cuda_backend_gemm_accumulate(void *be, void *dst, const void *x, const void *w, int wt,
+                                     int64_t n_out, int64_t n_in, int64_t rows);
+int krk_cuda_backend_gemm_group(void *be, void *const out[], const void *x, const void *const w[], int wt,
+                                const int64_t n_out[], int64_t n_in, int n_mat, int64_t rows, int silu,
+                                int *silu_fused);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

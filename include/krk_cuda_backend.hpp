@@ -1,0 +1,87 @@
+// krk_cuda_backend.hpp -- the host-side class a Kraken build links to get the sm_100a
+// matmul path: the subset of krk::Backend (include/krk/backend.hpp:337-1878) that the
+// quantized-weight matmul needs, with the same member names, argument meaning and error
+// behaviour, implemented on the C ABI of krk_cuda.h.
+//
+// In a Kraken tree this class derives from krk::Backend; here it
+// stands alone so that it compiles without the reference's headers. All pointers handed to
+// the ops are device pointers obtained from alloc(); the caller owns their lifetime
+// (include/krk/backend.hpp:361-362). Ops are enqueued on one stream, asynchronous and
+// ordered; completion is observed through sync() or download()
+// (include/krk/backend.hpp:772-801). The engine calls a backend from one thread.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+namespace krk_cuda {
+
+using i32 = int32_t;
+using i64 = int64_t;
+using f32 = float;
+
+// GGUF on-disk ids, the values of krk::DType (include/krk/quant.hpp:16-30).
+enum class DType : int { F32 = 0, F16 = 1, Q4_0 = 2, Q8_0 = 8, Q4_K = 12, Q6_K = 14 };
+
+class CudaBackend {
+public:
+    // make_hip_backend's contract (include/krk/backend.hpp:1886): nullptr and *err on failure.
+    static CudaBackend *make(int device_index, std::string *err);
+    ~CudaBackend();
+
+    const char *describe() const { return describe_.c_str(); }   // backend.hpp:805
+    DType act_type() const { return DType::F32; }                // backend.hpp:341-358 (CPU: f32)
+    size_t act_size() const { return sizeof(f32); }
+
+    void *alloc(size_t bytes);                                   // backend.hpp:361
+    void release(void *p);                                       // backend.hpp:362
+    void upload(void *dst, const void *host_src, size_t bytes);  // backend.hpp:720
+    void download(void *host_dst, const void *src, size_t bytes);// backend.hpp:755 (synchronises)
+    void download_f32(f32 *host_dst, const void *src, i64 n);    // backend.hpp:803
+    void upload_i32(i32 *dst, const i32 *host_src, i64 n);       // backend.hpp:1505
+    void fill0(void *p, size_t bytes);                           // backend.hpp:769
+    void sync();                                                 // backend.hpp:770
+
+    // backend.hpp:862-869. The reference's HIP rule is k > 0 && k % 32 == 0; the K-quant
+    // formats additionally need whole 256-value super-blocks, which is asked per type.
+    bool gemm_k_ok(i64 k) const { return k > 0 && k % 32 == 0; }
+    bool gemm_k_ok(DType wt, i64 k) const;
+
+    // out[rows, n_out] = x[rows, n_in] * W[n_out, n_in]^T (backend.hpp:858-860). A shape the
+    // kernels cannot address is a logged error followed by std::abort(), as in
+    // src/hip/backend_hip.hip:3186-3190; ask gemm_k_ok first.
+    void gemm(void *out, const void *x, const void *w, DType wt, i64 n_out, i64 n_in, i64 rows);
+
+    // dst += x * W^T, the residual fold (backend.hpp:894-900). True when the fused form ran;
+    // false (nothing launched) for rows > 8 or a non-zero storage exponent.
+    bool gemm_accumulate(void *dst, const void *x, const void *w, DType wt, i64 n_out, i64 n_in,
+                         i64 rows, const i32 *rexp = nullptr);
+
+    // Up to 16 independent projections in one launch (backend.hpp:1040-1056). True when the
+    // single-launch form ran; otherwise every matrix went through gemm() and false is returned.
+    bool gemm_group(void *const out[], const void *x, const void *const w[], DType wt,
+                    const i64 n_out[], i64 n_in, int n_mat, i64 rows, bool silu = false,
+                    bool *silu_fused = nullptr, bool row_parallel_only = false,
+                    const DType *wts = nullptr, const void *const xs[] = nullptr);
+
+    void silu_mul(void *out, const void *gate, const void *up, i64 n, i64 row_len = 0,
+                  f32 *row_scale = nullptr);                     // backend.hpp:1309
+    void scatter_axpy_rows(void *dst, const void *src, const i32 *rows, const f32 *alpha,
+                           i64 n_rows, i64 n, const f32 *row_scale = nullptr,
+                           i32 *row_exp = nullptr);              // backend.hpp:1473
+
+    void *stream() const { return stream_; }
+    int device() const { return device_; }
+
+private:
+    CudaBackend() = default;
+    void *workspace(size_t bytes);
+    int device_ = 0;
+    void *stream_ = nullptr;
+    void *ws_ = nullptr;
+    size_t ws_bytes_ = 0;
+    std::string describe_;
+};
+
+} // namespace krk_cuda

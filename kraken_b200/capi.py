@@ -1,0 +1,290 @@
+"""ctypes binding of libkrk_cuda.so: one Python function per entry of include/krk_cuda.h.
+
+This is glue, not a second implementation: every function checks nothing and computes
+nothing itself, it passes device pointers (``tensor.data_ptr()``) and sizes to the C ABI
+and raises ``KrkCudaError`` on a non-zero status. torch supplies device memory and streams.
+If the library has not been built, importing this module raises: there is no fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libkrk_cuda.so")
+
+Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
+X_F32, X_F16 = 0, 1
+MAX_GROUP, MAX_ROWS = 16, 8
+
+
+class KrkCudaError(RuntimeError):
+    def __init__(self, rc: int, where: str):
+        self.rc = rc
+        detail = lib.krk_cuda_last_cuda_error().decode() if rc == -5 else ""
+        super().__init__(f"{where}: {lib.krk_cuda_strerror(rc).decode()} (rc={rc}) {detail}".strip())
+
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(f"{LIB_PATH} is missing: build it with `python -m kraken_b200.build` "
+                      "(this package has no fallback path)")
+
+lib = C.CDLL(LIB_PATH)
+
+_vp, _i64, _int, _sz = C.c_void_p, C.c_int64, C.c_int, C.c_size_t
+
+
+class ExpertBank(C.Structure):
+    """struct krk_cuda_expert_bank"""
+    _fields_ = [("gate", _vp), ("up", _vp), ("down", _vp), ("wt_gate_up", _int), ("wt_down", _int),
+                ("n_local", _int), ("expert_base", _int), ("n_embd", _i64), ("n_ff", _i64)]
+
+
+# name -> (restype, argtypes); the list tests/ checks against the header.
+SIGNATURES = {
+    "krk_cuda_strerror": (C.c_char_p, [_int]),
+    "krk_cuda_last_cuda_error": (C.c_char_p, []),
+    "krk_cuda_dtype_ok": (_int, [_int]),
+    "krk_cuda_block_size": (_int, [_int]),
+    "krk_cuda_block_bytes": (_int, [_int]),
+    "krk_cuda_row_bytes": (_sz, [_int, _i64]),
+    "krk_cuda_gemm_k_ok": (_int, [_int, _i64]),
+    "krk_cuda_dequant_rows": (_int, [_vp, _vp, _int, _i64, _i64, _vp]),
+    "krk_cuda_gemv": (_int, [_vp, _vp, _vp, _int, _i64, _i64, _i64, _int, _vp]),
+    "krk_cuda_gemv_group": (_int, [C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_int),
+                                   C.POINTER(_i64), _i64, _int, _int, _vp]),
+    "krk_cuda_gemm_workspace_bytes": (_sz, [_int, _i64, _i64, _i64]),
+    "krk_cuda_gemm": (_int, [_vp, _vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "krk_cuda_route": (_int, [_vp, _vp, _vp, _i64, _int, _int, _vp]),
+    "krk_cuda_moe_workspace_bytes": (_sz, [C.POINTER(ExpertBank), _int, _i64]),
+    "krk_cuda_moe_ffn": (_int, [_vp, _vp, _vp, _vp, C.POINTER(ExpertBank), _int, _i64, _vp, _sz, _vp]),
+    "krk_cuda_silu_mul": (_int, [_vp, _vp, _vp, _i64, _vp]),
+    "krk_cuda_scatter_axpy_rows": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
+    "krk_cuda_sum_parts": (_int, [_vp, _vp, _int, _i64, _vp]),
+    "krk_cuda_device_status": (_int, []),
+    "krk_cuda_launch_count": (_i64, []),
+    "krk_cuda_backend_make": (_vp, [_int, C.c_char_p, _sz]),
+    "krk_cuda_backend_free": (None, [_vp]),
+    "krk_cuda_backend_describe": (C.c_char_p, [_vp]),
+    "krk_cuda_backend_alloc": (_vp, [_vp, _sz]),
+    "krk_cuda_backend_release": (None, [_vp, _vp]),
+    "krk_cuda_backend_upload": (None, [_vp, _vp, _vp, _sz]),
+    "krk_cuda_backend_download": (None, [_vp, _vp, _vp, _sz]),
+    "krk_cuda_backend_fill0": (None, [_vp, _vp, _sz]),
+    "krk_cuda_backend_sync": (None, [_vp]),
+    "krk_cuda_backend_gemm_k_ok": (_int, [_vp, _int, _i64]),
+    "krk_cuda_backend_gemm": (None, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _i64]),
+    "krk_cuda_backend_gemm_accumulate": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _i64]),
+    "krk_cuda_backend_gemm_group": (_int, [_vp, C.POINTER(_vp), _vp, C.POINTER(_vp), _int, C.POINTER(_i64),
+                                           _i64, _int, _i64, _int, C.POINTER(_int)]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)   # AttributeError here = the library does not export a declared symbol
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def _check(rc: int, where: str) -> None:
+    if rc != 0:
+        raise KrkCudaError(rc, where)
+
+
+def _stream_ptr(stream=None):
+    """cudaStream_t of a torch stream (None = torch's current stream)."""
+    import torch
+    s = torch.cuda.current_stream() if stream is None else stream
+    return C.c_void_p(s.cuda_stream)
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+# ---- geometry ---------------------------------------------------------------------------
+
+def row_bytes(wt: int, n_in: int) -> int:
+    return lib.krk_cuda_row_bytes(wt, n_in)
+
+
+def gemm_k_ok(wt: int, k: int) -> bool:
+    return bool(lib.krk_cuda_gemm_k_ok(wt, k))
+
+
+# ---- device-pointer entries ----------------------------------------------------------------
+
+def dequant_rows(w, wt: int, n_rows: int, n_in: int, stream=None):
+    import torch
+    out = torch.empty((n_rows, n_in), dtype=torch.float32, device=w.device)
+    _check(lib.krk_cuda_dequant_rows(_ptr(out), _ptr(w), wt, n_rows, n_in, _stream_ptr(stream)), "dequant_rows")
+    return out
+
+
+def gemv(x, w, wt: int, n_out: int, n_in: int, out=None, accumulate: bool = False, stream=None):
+    """y[rows][n_out] (+)= x[rows][n_in] . W^T; x is f32 [rows, n_in] or [n_in]."""
+    import torch
+    rows = 1 if x.dim() == 1 else x.shape[0]
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate needs an existing output")
+        out = torch.empty((rows, n_out), dtype=torch.float32, device=x.device)
+    _check(lib.krk_cuda_gemv(_ptr(out), _ptr(x), _ptr(w), wt, n_out, n_in, rows, int(accumulate),
+                             _stream_ptr(stream)), "gemv")
+    return out
+
+
+def gemv_group(xs, ws, wts, n_outs, n_in: int, outs=None, fuse_silu_pair: bool = False, stream=None):
+    """One launch for up to 16 single-row GEMVs. xs/ws/outs are lists of tensors."""
+    import torch
+    n = len(ws)
+    if outs is None:
+        outs = [torch.empty((n_outs[m],), dtype=torch.float32, device=ws[m].device) for m in range(n)]
+    ya = (_vp * n)(*[t.data_ptr() for t in outs])
+    xa = (_vp * n)(*[t.data_ptr() for t in xs])
+    wa = (_vp * n)(*[t.data_ptr() for t in ws])
+    ta = (_int * n)(*wts)
+    na = (_i64 * n)(*n_outs)
+    _check(lib.krk_cuda_gemv_group(ya, xa, wa, ta, na, n_in, n, int(fuse_silu_pair), _stream_ptr(stream)),
+           "gemv_group")
+    return outs
+
+
+def gemm_workspace_bytes(x_dtype: int, n_out: int, n_in: int, rows: int) -> int:
+    return lib.krk_cuda_gemm_workspace_bytes(x_dtype, n_out, n_in, rows)
+
+
+def gemm(x, w, wt: int, n_out: int, n_in: int, out=None, workspace=None, stream=None):
+    """Prefill GEMM: x is f16 or f32 [rows, n_in]; returns f32 [rows, n_out]."""
+    import torch
+    rows = x.shape[0]
+    x_dtype = X_F16 if x.dtype == torch.float16 else X_F32
+    need = gemm_workspace_bytes(x_dtype, n_out, n_in, rows)
+    if workspace is None and need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    if out is None:
+        out = torch.empty((rows, n_out), dtype=torch.float32, device=x.device)
+    _check(lib.krk_cuda_gemm(_ptr(out), _ptr(x), x_dtype, _ptr(w), wt, n_out, n_in, rows, _ptr(workspace),
+                             workspace.numel() if workspace is not None else 0, _stream_ptr(stream)), "gemm")
+    return out
+
+
+def route(logits, k: int, stream=None):
+    import torch
+    n_tok, n_expert = logits.shape
+    ids = torch.empty((n_tok, k), dtype=torch.int32, device=logits.device)
+    wts = torch.empty((n_tok, k), dtype=torch.float32, device=logits.device)
+    _check(lib.krk_cuda_route(_ptr(ids), _ptr(wts), _ptr(logits), n_tok, n_expert, k, _stream_ptr(stream)), "route")
+    return ids, wts
+
+
+def make_bank(gate, up, down, wt_gate_up: int, wt_down: int, n_local: int, expert_base: int, n_embd: int,
+              n_ff: int) -> ExpertBank:
+    return ExpertBank(gate.data_ptr() if gate is not None else 0, up.data_ptr() if up is not None else 0,
+                      down.data_ptr() if down is not None else 0, wt_gate_up, wt_down, n_local, expert_base,
+                      n_embd, n_ff)
+
+
+def moe_ffn(x, ids, wts, bank: ExpertBank, out=None, workspace=None, stream=None):
+    import torch
+    n_tok, k = ids.shape
+    need = lib.krk_cuda_moe_workspace_bytes(C.byref(bank), k, n_tok)
+    if workspace is None:
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
+    if out is None:
+        out = torch.empty((n_tok, bank.n_embd), dtype=torch.float32, device=x.device)
+    _check(lib.krk_cuda_moe_ffn(_ptr(out), _ptr(x), _ptr(ids), _ptr(wts), C.byref(bank), k, n_tok, _ptr(workspace),
+                                workspace.numel(), _stream_ptr(stream)), "moe_ffn")
+    return out
+
+
+def silu_mul(gate, up, out=None, stream=None):
+    import torch
+    if out is None:
+        out = torch.empty_like(gate)
+    _check(lib.krk_cuda_silu_mul(_ptr(out), _ptr(gate), _ptr(up), gate.numel(), _stream_ptr(stream)), "silu_mul")
+    return out
+
+
+def scatter_axpy_rows(dst, src, rows, alpha, stream=None):
+    _check(lib.krk_cuda_scatter_axpy_rows(_ptr(dst), _ptr(src), _ptr(rows), _ptr(alpha), src.shape[0],
+                                          src.shape[1], _stream_ptr(stream)), "scatter_axpy_rows")
+    return dst
+
+
+def sum_parts(parts, out=None, stream=None):
+    import torch
+    n_parts = parts.shape[0]
+    n = parts[0].numel()
+    if out is None:
+        out = torch.empty_like(parts[0])
+    _check(lib.krk_cuda_sum_parts(_ptr(out), _ptr(parts), n_parts, n, _stream_ptr(stream)), "sum_parts")
+    return out
+
+
+def device_status() -> int:
+    return lib.krk_cuda_device_status()
+
+
+def launch_count() -> int:
+    return lib.krk_cuda_launch_count()
+
+
+# ---- host-buffer plumbing: the CudaBackend object ---------------------------------------------
+
+class Backend:
+    """The C++ CudaBackend (include/krk_cuda_backend.hpp) driven through its C shim.
+
+    Mirrors the members of krk::Backend this path needs; host arrays are numpy arrays or
+    pinned torch tensors, device memory comes from alloc().
+    """
+
+    def __init__(self, device_index: int = 0):
+        err = C.create_string_buffer(256)
+        self.h = lib.krk_cuda_backend_make(device_index, err, 256)
+        if not self.h:
+            raise RuntimeError(f"make_cuda_backend({device_index}) failed: {err.value.decode()}")
+
+    def close(self):
+        if self.h:
+            lib.krk_cuda_backend_free(self.h)
+            self.h = None
+
+    def describe(self) -> str:
+        return lib.krk_cuda_backend_describe(self.h).decode()
+
+    def alloc(self, nbytes: int) -> int:
+        p = lib.krk_cuda_backend_alloc(self.h, nbytes)
+        if not p:
+            raise MemoryError(f"backend alloc of {nbytes} bytes failed")
+        return p
+
+    def release(self, p: int) -> None:
+        lib.krk_cuda_backend_release(self.h, p)
+
+    def upload(self, dst: int, host_ptr: int, nbytes: int) -> None:
+        lib.krk_cuda_backend_upload(self.h, dst, host_ptr, nbytes)
+
+    def download(self, host_ptr: int, src: int, nbytes: int) -> None:
+        lib.krk_cuda_backend_download(self.h, host_ptr, src, nbytes)
+
+    def fill0(self, p: int, nbytes: int) -> None:
+        lib.krk_cuda_backend_fill0(self.h, p, nbytes)
+
+    def sync(self) -> None:
+        lib.krk_cuda_backend_sync(self.h)
+
+    def gemm_k_ok(self, wt: int, k: int) -> bool:
+        return bool(lib.krk_cuda_backend_gemm_k_ok(self.h, wt, k))
+
+    def gemm(self, out: int, x: int, w: int, wt: int, n_out: int, n_in: int, rows: int) -> None:
+        lib.krk_cuda_backend_gemm(self.h, out, x, w, wt, n_out, n_in, rows)
+
+    def gemm_accumulate(self, dst: int, x: int, w: int, wt: int, n_out: int, n_in: int, rows: int) -> bool:
+        return bool(lib.krk_cuda_backend_gemm_accumulate(self.h, dst, x, w, wt, n_out, n_in, rows))
+
+    def gemm_group(self, outs, x: int, ws, wt: int, n_outs, n_in: int, rows: int = 1, silu: bool = False):
+        n = len(ws)
+        fused = _int(0)
+        ran = lib.krk_cuda_backend_gemm_group(self.h, (_vp * n)(*outs), x, (_vp * n)(*ws), wt, (_i64 * n)(*n_outs),
+                                              n_in, n, rows, int(silu), C.byref(fused))
+        return bool(ran), bool(fused.value)

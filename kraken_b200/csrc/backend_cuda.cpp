@@ -1,0 +1,225 @@
+// CudaBackend: the krk::Backend-shaped host class over the C ABI, plus a C shim so that
+// a non-C++ host (the Python tests, the benchmark) can drive the very same object.
+#include "krk_cuda_backend.hpp"
+
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "krk_cuda.h"
+
+namespace krk_cuda {
+
+namespace {
+
+// The reference routes every HIP call through KRK_HIP(expr) -> hip_check, which logs and
+// aborts (src/hip/krk_hip.hpp:104-115). Same rule here.
+void cuda_check(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return;
+    std::fprintf(stderr, "[krk-cuda] ERROR %s: %s\n", what, cudaGetErrorString(e));
+    std::abort();
+}
+#define KRK_CUDA_CHECK(expr) cuda_check((expr), #expr)
+
+[[noreturn]] void die(const char *op, int rc, i64 n_out, i64 n_in, i64 rows, int wt) {
+    std::fprintf(stderr, "[krk-cuda] ERROR %s refused: %s (wt=%d n_out=%lld n_in=%lld rows=%lld) %s\n", op,
+                 krk_cuda_strerror(rc), wt, (long long)n_out, (long long)n_in, (long long)rows,
+                 krk_cuda_last_cuda_error());
+    std::abort();
+}
+
+} // namespace
+
+CudaBackend *CudaBackend::make(int device_index, std::string *err) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || device_index < 0 || device_index >= n) {
+        if (err) *err = e != cudaSuccess ? cudaGetErrorString(e) : "device index out of range";
+        return nullptr;
+    }
+    cudaDeviceProp prop;
+    if ((e = cudaSetDevice(device_index)) != cudaSuccess ||
+        (e = cudaGetDeviceProperties(&prop, device_index)) != cudaSuccess) {
+        if (err) *err = cudaGetErrorString(e);
+        return nullptr;
+    }
+    if (prop.major != 10) {
+        if (err) *err = std::string("device is sm_") + std::to_string(prop.major * 10 + prop.minor) +
+                        "; this backend is built for sm_100a only";
+        return nullptr;
+    }
+    CudaBackend *be = new CudaBackend();
+    be->device_ = device_index;
+    be->stream_ = nullptr;   // the default stream, like the reference (backend.hpp:775-779)
+    char buf[256];
+    std::snprintf(buf, sizeof buf, "cuda:%d %s sm_%d%d %d SMs %.0f GiB", device_index, prop.name, prop.major,
+                  prop.minor, prop.multiProcessorCount, (double)prop.totalGlobalMem / (1 << 30));
+    be->describe_ = buf;
+    return be;
+}
+
+CudaBackend::~CudaBackend() {
+    if (ws_) cudaFree(ws_);
+}
+
+void *CudaBackend::alloc(size_t bytes) {
+    void *p = nullptr;
+    if (bytes == 0) bytes = 16;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) return nullptr;   // caller checks, as with the reference
+    return p;
+}
+void CudaBackend::release(void *p) {
+    if (p) KRK_CUDA_CHECK(cudaFree(p));
+}
+void CudaBackend::upload(void *dst, const void *host_src, size_t bytes) {
+    if (bytes) KRK_CUDA_CHECK(cudaMemcpyAsync(dst, host_src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream_));
+}
+void CudaBackend::download(void *host_dst, const void *src, size_t bytes) {
+    if (bytes) KRK_CUDA_CHECK(cudaMemcpyAsync(host_dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream_));
+    KRK_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream_));
+}
+void CudaBackend::download_f32(f32 *host_dst, const void *src, i64 n) {
+    download(host_dst, src, sizeof(f32) * (size_t)n);   // activations are f32 already
+}
+void CudaBackend::upload_i32(i32 *dst, const i32 *host_src, i64 n) { upload(dst, host_src, sizeof(i32) * (size_t)n); }
+void CudaBackend::fill0(void *p, size_t bytes) {
+    if (bytes) KRK_CUDA_CHECK(cudaMemsetAsync(p, 0, bytes, (cudaStream_t)stream_));
+}
+void CudaBackend::sync() { KRK_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream_)); }
+
+bool CudaBackend::gemm_k_ok(DType wt, i64 k) const { return krk_cuda_gemm_k_ok((int)wt, k) != 0; }
+
+void *CudaBackend::workspace(size_t bytes) {
+    if (bytes > ws_bytes_) {
+        // Grows only; a grow first drains the stream so no kernel still reads the old block.
+        if (ws_) {
+            KRK_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream_));
+            KRK_CUDA_CHECK(cudaFree(ws_));
+        }
+        KRK_CUDA_CHECK(cudaMalloc(&ws_, bytes));
+        ws_bytes_ = bytes;
+    }
+    return ws_;
+}
+
+void CudaBackend::gemm(void *out, const void *x, const void *w, DType wt, i64 n_out, i64 n_in, i64 rows) {
+    int rc;
+    if (rows <= KRK_CUDA_MAX_ROWS) {
+        rc = krk_cuda_gemv(out, x, w, (int)wt, n_out, n_in, rows, 0, stream_);
+    } else {
+        const size_t need = krk_cuda_gemm_workspace_bytes(KRK_CUDA_X_F32, n_out, n_in, rows);
+        rc = krk_cuda_gemm(out, x, KRK_CUDA_X_F32, w, (int)wt, n_out, n_in, rows, workspace(need), need, stream_);
+    }
+    if (rc != KRK_CUDA_OK) die("gemm", rc, n_out, n_in, rows, (int)wt);
+}
+
+bool CudaBackend::gemm_accumulate(void *dst, const void *x, const void *w, DType wt, i64 n_out, i64 n_in,
+                                  i64 rows, const i32 *rexp) {
+    // A storage exponent belongs to f16 residual streams (backend.hpp:882-893); activations are
+    // f32 here, so only the null form is taken and anything else is "do it the long way".
+    if (rexp != nullptr || rows > KRK_CUDA_MAX_ROWS || rows < 1) return false;
+    if (!krk_cuda_gemm_k_ok((int)wt, n_in)) return false;
+    const int rc = krk_cuda_gemv(dst, x, w, (int)wt, n_out, n_in, rows, 1, stream_);
+    if (rc != KRK_CUDA_OK) die("gemm_accumulate", rc, n_out, n_in, rows, (int)wt);
+    return true;
+}
+
+bool CudaBackend::gemm_group(void *const out[], const void *x, const void *const w[], DType wt,
+                             const i64 n_out[], i64 n_in, int n_mat, i64 rows, bool silu, bool *silu_fused,
+                             bool row_parallel_only, const DType *wts, const void *const xs[]) {
+    (void)row_parallel_only;   // every matrix is one row-parallel pass here; there is no split-K
+    if (silu_fused) *silu_fused = false;
+    const bool fold = silu && n_mat >= 2 && n_out[0] == n_out[1] && !xs &&
+                      (!wts || wts[0] == wts[1]);
+    if (rows == 1 && n_mat >= 1 && n_mat <= KRK_CUDA_MAX_GROUP) {
+        const void *xv[KRK_CUDA_MAX_GROUP];
+        int wtv[KRK_CUDA_MAX_GROUP];
+        for (int m = 0; m < n_mat; m++) {
+            xv[m] = xs ? xs[m] : x;
+            wtv[m] = (int)(wts ? wts[m] : wt);
+        }
+        int rc;
+        if (fold && n_mat == 2) {
+            rc = krk_cuda_gemv_group(out, xv, w, wtv, n_out, n_in, 2, 1, stream_);
+            if (rc == KRK_CUDA_OK && silu_fused) *silu_fused = true;
+        } else {
+            rc = krk_cuda_gemv_group(out, xv, w, wtv, n_out, n_in, n_mat, 0, stream_);
+        }
+        if (rc != KRK_CUDA_OK) die("gemm_group", rc, n_out[0], n_in, rows, wtv[0]);
+        return true;
+    }
+    for (int m = 0; m < n_mat; m++) gemm(out[m], xs ? xs[m] : x, w[m], wts ? wts[m] : wt, n_out[m], n_in, rows);
+    return false;
+}
+
+void CudaBackend::silu_mul(void *out, const void *gate, const void *up, i64 n, i64 row_len, f32 *row_scale) {
+    const int rc = krk_cuda_silu_mul(out, gate, up, n, stream_);
+    if (rc != KRK_CUDA_OK) die("silu_mul", rc, n, 0, 0, 0);
+    // f32 activations carry no storage exponent: one scale of 1.0 per row, as the CPU backend
+    // answers (src/backend_cpu.cpp:2401-2408). row_scale is a host array there and here.
+    if (row_scale && row_len > 0 && n % row_len == 0)
+        for (i64 r = 0; r < n / row_len; r++) row_scale[r] = 1.0f;
+}
+
+void CudaBackend::scatter_axpy_rows(void *dst, const void *src, const i32 *rows, const f32 *alpha, i64 n_rows,
+                                    i64 n, const f32 *row_scale, i32 *row_exp) {
+    (void)row_scale;   // f32 backends fill it with 1.0 and ignore the exponent (backend.hpp:1306-1308)
+    (void)row_exp;
+    const int rc = krk_cuda_scatter_axpy_rows(dst, src, rows, alpha, n_rows, n, stream_);
+    if (rc != KRK_CUDA_OK) die("scatter_axpy_rows", rc, n_rows, n, 0, 0);
+}
+
+} // namespace krk_cuda
+
+// ---- C shim over the class (declared in krk_cuda.h) -------------------------------------------
+using krk_cuda::CudaBackend;
+using krk_cuda::DType;
+
+extern "C" {
+
+void *krk_cuda_backend_make(int device_index, char *err, size_t err_len) {
+    std::string e;
+    CudaBackend *be = CudaBackend::make(device_index, &e);
+    if (!be && err && err_len) {
+        std::strncpy(err, e.c_str(), err_len - 1);
+        err[err_len - 1] = 0;
+    }
+    return be;
+}
+void krk_cuda_backend_free(void *be) { delete static_cast<CudaBackend *>(be); }
+const char *krk_cuda_backend_describe(void *be) { return static_cast<CudaBackend *>(be)->describe(); }
+void *krk_cuda_backend_alloc(void *be, size_t bytes) { return static_cast<CudaBackend *>(be)->alloc(bytes); }
+void krk_cuda_backend_release(void *be, void *p) { static_cast<CudaBackend *>(be)->release(p); }
+void krk_cuda_backend_upload(void *be, void *dst, const void *host_src, size_t bytes) {
+    static_cast<CudaBackend *>(be)->upload(dst, host_src, bytes);
+}
+void krk_cuda_backend_download(void *be, void *host_dst, const void *src, size_t bytes) {
+    static_cast<CudaBackend *>(be)->download(host_dst, src, bytes);
+}
+void krk_cuda_backend_fill0(void *be, void *p, size_t bytes) { static_cast<CudaBackend *>(be)->fill0(p, bytes); }
+void krk_cuda_backend_sync(void *be) { static_cast<CudaBackend *>(be)->sync(); }
+int krk_cuda_backend_gemm_k_ok(void *be, int wt, int64_t k) {
+    return static_cast<CudaBackend *>(be)->gemm_k_ok(static_cast<DType>(wt), k) ? 1 : 0;
+}
+void krk_cuda_backend_gemm(void *be, void *out, const void *x, const void *w, int wt, int64_t n_out,
+                           int64_t n_in, int64_t rows) {
+    static_cast<CudaBackend *>(be)->gemm(out, x, w, static_cast<DType>(wt), n_out, n_in, rows);
+}
+int krk_cuda_backend_gemm_accumulate(void *be, void *dst, const void *x, const void *w, int wt, int64_t n_out,
+                                     int64_t n_in, int64_t rows) {
+    return static_cast<CudaBackend *>(be)->gemm_accumulate(dst, x, w, static_cast<DType>(wt), n_out, n_in, rows)
+               ? 1 : 0;
+}
+int krk_cuda_backend_gemm_group(void *be, void *const out[], const void *x, const void *const w[], int wt,
+                                const int64_t n_out[], int64_t n_in, int n_mat, int64_t rows, int silu,
+                                int *silu_fused) {
+    bool fused = false;
+    const bool ran = static_cast<CudaBackend *>(be)->gemm_group(out, x, w, static_cast<DType>(wt), n_out, n_in,
+                                                                n_mat, rows, silu != 0, &fused);
+    if (silu_fused) *silu_fused = fused ? 1 : 0;
+    return ran ? 1 : 0;
+}
+
+} // extern "C"

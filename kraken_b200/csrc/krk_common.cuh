@@ -1,0 +1,160 @@
+// Shared declarations of the sm_100a backend: error plumbing, block geometry and the
+// bit-exact element decoders every kernel family builds on.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "krk_cuda.h"
+
+namespace krk_cuda {
+
+// ---- host-side plumbing ------------------------------------------------------------
+
+void note_cuda_error(cudaError_t e);   // remembers the text for krk_cuda_last_cuda_error()
+void note_launch(int n = 1);           // counts kernels for krk_cuda_launch_count()
+int *device_status_word();             // per-device int in global memory, 0 unless a wait gave up
+int sm_count();                        // multiprocessors of the current device
+
+inline int check_launch() {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        return KRK_CUDA_ELAUNCH;
+    }
+    return KRK_CUDA_OK;
+}
+
+// ---- geometry (src/quant.cpp:1805-1900) ----------------------------------------------
+
+__host__ __device__ constexpr int block_size(int wt) {
+    return (wt == KRK_CUDA_Q8_0 || wt == KRK_CUDA_Q4_0) ? 32
+           : (wt == KRK_CUDA_Q4_K || wt == KRK_CUDA_Q6_K) ? 256 : 0;
+}
+__host__ __device__ constexpr int block_bytes(int wt) {
+    return wt == KRK_CUDA_Q8_0 ? 34 : wt == KRK_CUDA_Q4_0 ? 18 : wt == KRK_CUDA_Q4_K ? 144
+           : wt == KRK_CUDA_Q6_K ? 210 : 0;
+}
+__host__ __device__ inline size_t row_bytes(int wt, int64_t n_in) {
+    const int bs = block_size(wt);
+    return bs ? (size_t)((n_in + bs - 1) / bs) * (size_t)block_bytes(wt) : 0;
+}
+
+// ---- bit-exact element decode ----------------------------------------------------------
+// Every product is rounded on its own (__fmul_rn / __fsub_rn): nvcc would otherwise
+// contract a*b-c into one fused operation and the result would differ from the host
+// decoders in the last bit.
+
+__device__ __forceinline__ float half_bits_to_float(const uint8_t *p) {
+    return __half2float(__ushort_as_half((unsigned short)(p[0] | (p[1] << 8))));
+}
+
+// The j-th 6-bit scale and min of a Q4_K super-block (src/quant.cpp:427-435).
+__device__ __forceinline__ void scale_min_k4(int j, const uint8_t *p, int &sc, int &mn) {
+    if (j < 4) {
+        sc = p[j] & 63;
+        mn = p[j + 4] & 63;
+    } else {
+        sc = (p[j + 4] & 0xF) | ((p[j - 4] >> 6) << 4);
+        mn = (p[j + 4] >> 4) | ((p[j] >> 6) << 4);
+    }
+}
+
+// Value k of a weight row, exactly as the host decoder of that format produces it.
+template <int WT>
+__device__ __forceinline__ float decode_value(const uint8_t *row, int64_t k);
+
+// src/quant.cpp:381-387
+template <>
+__device__ __forceinline__ float decode_value<KRK_CUDA_Q8_0>(const uint8_t *row, int64_t k) {
+    const uint8_t *b = row + (k >> 5) * 34;
+    return __fmul_rn(half_bits_to_float(b), (float)(int8_t)b[2 + (k & 31)]);
+}
+
+// src/quant.cpp:331-339
+template <>
+__device__ __forceinline__ float decode_value<KRK_CUDA_Q4_0>(const uint8_t *row, int64_t k) {
+    const uint8_t *b = row + (k >> 5) * 18;
+    const int j = (int)(k & 31);
+    const int q = j < 16 ? (b[2 + j] & 0xF) : (b[2 + j - 16] >> 4);
+    return __fmul_rn(half_bits_to_float(b), (float)(q - 8));
+}
+
+// src/quant.cpp:437-460
+template <>
+__device__ __forceinline__ float decode_value<KRK_CUDA_Q4_K>(const uint8_t *row, int64_t k) {
+    const uint8_t *b = row + (k >> 8) * 144;
+    const int e = (int)(k & 255), c = e >> 5, l = e & 31;
+    const uint8_t byte = b[16 + 32 * (c >> 1) + l];
+    const int q = (c & 1) ? (byte >> 4) : (byte & 0xF);
+    int sc, mn;
+    scale_min_k4(c, b + 4, sc, mn);
+    const float dl = __fmul_rn(half_bits_to_float(b), (float)sc);
+    const float ml = __fmul_rn(half_bits_to_float(b + 2), (float)mn);
+    return __fsub_rn(__fmul_rn(dl, (float)q), ml);
+}
+
+// src/quant.cpp:491-512
+template <>
+__device__ __forceinline__ float decode_value<KRK_CUDA_Q6_K>(const uint8_t *row, int64_t k) {
+    const uint8_t *b = row + (k >> 8) * 210;
+    const int e = (int)(k & 255), half = e >> 7, r = e & 127, quad = r >> 5, l = r & 31;
+    const uint8_t *ql = b + 64 * half + ((quad & 1) ? 32 : 0);
+    const uint8_t qh = b[128 + 32 * half + l];
+    const int lo = (quad & 2) ? (ql[l] >> 4) : (ql[l] & 0xF);
+    const int q = lo | (((qh >> (2 * quad)) & 3) << 4);
+    const int sc = (int8_t)b[192 + 8 * half + 2 * quad + (l >> 4)];
+    return __fmul_rn(__fmul_rn(half_bits_to_float(b + 208), (float)sc), (float)(q - 32));
+}
+
+// Runs the statement(s) with `WT` bound to the compile-time weight type matching `wt`
+// (kernels are specialised per format; there is no runtime type switch on the device).
+#define KRK_DISPATCH_WT(wt, ...)                                                        \
+    switch (wt) {                                                                       \
+    case KRK_CUDA_Q8_0: { constexpr int WT = KRK_CUDA_Q8_0; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q4_0: { constexpr int WT = KRK_CUDA_Q4_0; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q4_K: { constexpr int WT = KRK_CUDA_Q4_K; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q6_K: { constexpr int WT = KRK_CUDA_Q6_K; __VA_ARGS__; } break;       \
+    default: break;                                                                     \
+    }
+
+// ---- kernel-family entry points (one .cu file each) -------------------------------------
+
+int launch_dequant_rows(float *out, const uint8_t *w, int wt, int64_t n_rows, int64_t n_in,
+                        cudaStream_t st);
+
+// One GEMV of a grouped launch.
+struct GemvMat {
+    const uint8_t *w;
+    const float *x;   // [rows][n_in]
+    float *y;         // [rows][n_out]
+    int64_t n_out;
+    int wt;
+};
+
+// Reference-shaped kernel (one warp per output row): takes every legal shape.
+int launch_gemv_generic(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accumulate,
+                        int silu_pair, cudaStream_t st);
+// Streaming kernel (bulk-async ring + integer tensor-core dot). Returns 1 when it took
+// the launch, 0 when the shape is outside what it addresses (nothing launched), < 0 on error.
+int launch_gemv_stream(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accumulate,
+                       int silu_pair, cudaStream_t st);
+
+int launch_silu_mul(float *out, const float *gate, const float *up, int64_t n, cudaStream_t st);
+int launch_scatter_axpy_rows(float *dst, const float *src, const int32_t *rows, const float *alpha,
+                             int64_t n_rows, int64_t n, cudaStream_t st);
+int launch_sum_parts(float *out, const float *parts, int n_parts, int64_t n, cudaStream_t st);
+int launch_route(int32_t *ids, float *wts, const float *logits, int64_t n_tok, int n_expert, int k,
+                 cudaStream_t st);
+size_t moe_workspace_bytes(const krk_cuda_expert_bank *bank, int k, int64_t n_tok);
+int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const float *wts,
+                           const krk_cuda_expert_bank *bank, int k, int64_t n_tok, void *workspace,
+                           cudaStream_t st);
+
+// Prefill GEMM on tcgen05 (krk_gemm_tc.cu).
+size_t gemm_workspace_bytes(int x_dtype, int64_t n_in, int64_t rows);
+int launch_gemm_tc(float *y, const void *x, int x_dtype, const uint8_t *w, int wt, int64_t n_out,
+                   int64_t n_in, int64_t rows, void *workspace, cudaStream_t st);
+
+} // namespace krk_cuda

@@ -1,0 +1,267 @@
+// The extern "C" surface declared in include/krk_cuda.h: argument checks, then a launch.
+// Nothing here computes on the host.
+#include <atomic>
+#include <cstring>
+#include <mutex>
+
+#include "krk_common.cuh"
+
+namespace krk_cuda {
+
+namespace {
+thread_local char g_cuda_err[256] = "";
+std::atomic<int64_t> g_launches{0};
+
+struct DeviceState {
+    int *status = nullptr;
+    int sms = 0;
+};
+constexpr int kMaxDevices = 64;
+DeviceState g_dev[kMaxDevices];
+std::mutex g_dev_mu;
+
+DeviceState *device_state() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    DeviceState &s = g_dev[dev];
+    if (s.sms == 0) {
+        std::lock_guard<std::mutex> lk(g_dev_mu);
+        if (s.sms == 0) {
+            int sms = 0;
+            if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
+            int *p = nullptr;
+            if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+            cudaMemset(p, 0, sizeof(int));
+            s.status = p;
+            s.sms = sms;
+        }
+    }
+    return &s;
+}
+} // namespace
+
+void note_cuda_error(cudaError_t e) {
+    std::strncpy(g_cuda_err, cudaGetErrorString(e), sizeof(g_cuda_err) - 1);
+    g_cuda_err[sizeof(g_cuda_err) - 1] = 0;
+}
+void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int *device_status_word() {
+    DeviceState *s = device_state();
+    return s ? s->status : nullptr;
+}
+int sm_count() {
+    DeviceState *s = device_state();
+    return s ? s->sms : 1;
+}
+
+static inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+static int check_matmul_args(const void *y, const void *x, const void *w, int wt, int64_t n_out,
+                             int64_t n_in, int64_t rows) {
+    if (!krk_cuda_dtype_ok(wt)) return KRK_CUDA_EDTYPE;
+    if (n_out < 0 || rows < 0 || !krk_cuda_gemm_k_ok(wt, n_in)) return KRK_CUDA_ESHAPE;
+    if (n_out > 0 && rows > 0 && (!y || !x || !w)) return KRK_CUDA_ENULL;
+    if (!aligned(w, 16) || !aligned(x, 16) || !aligned(y, 4)) return KRK_CUDA_EALIGN;
+    return KRK_CUDA_OK;
+}
+
+} // namespace krk_cuda
+
+using namespace krk_cuda;
+
+extern "C" {
+
+const char *krk_cuda_strerror(int rc) {
+    switch (rc) {
+    case KRK_CUDA_OK: return "ok";
+    case KRK_CUDA_EDTYPE: return "unsupported weight type (want Q8_0, Q4_0, Q4_K or Q6_K)";
+    case KRK_CUDA_ESHAPE: return "shape not addressable (n_in must be a positive whole number of blocks; sizes non-negative; rows in range)";
+    case KRK_CUDA_ENULL: return "null pointer";
+    case KRK_CUDA_EALIGN: return "misaligned pointer (weights and x 16 bytes, y 4 bytes)";
+    case KRK_CUDA_ELAUNCH: return "CUDA launch failed";
+    case KRK_CUDA_EWORKSPACE: return "workspace missing or too small";
+    case KRK_CUDA_EDEVICE: return "no usable CUDA device is current";
+    case KRK_CUDA_EARG: return "bad argument";
+    case KRK_CUDA_ETIMEOUT: return "a bounded device-side wait gave up";
+    default: return "unknown error";
+    }
+}
+
+const char *krk_cuda_last_cuda_error(void) { return g_cuda_err; }
+
+int krk_cuda_dtype_ok(int wt) { return block_size(wt) != 0; }
+int krk_cuda_block_size(int wt) { return block_size(wt); }
+int krk_cuda_block_bytes(int wt) { return block_bytes(wt); }
+size_t krk_cuda_row_bytes(int wt, int64_t n_in) { return n_in < 0 ? 0 : row_bytes(wt, n_in); }
+int krk_cuda_gemm_k_ok(int wt, int64_t k) {
+    const int bs = block_size(wt);
+    return bs != 0 && k > 0 && k % bs == 0;
+}
+
+int krk_cuda_dequant_rows(void *out_f32, const void *w, int wt, int64_t n_rows, int64_t n_in,
+                          void *stream) {
+    if (!krk_cuda_dtype_ok(wt)) return KRK_CUDA_EDTYPE;
+    if (n_rows < 0 || n_in < 0 || n_in % block_size(wt) != 0) return KRK_CUDA_ESHAPE;
+    if (n_rows * n_in == 0) return KRK_CUDA_OK;
+    if (!out_f32 || !w) return KRK_CUDA_ENULL;
+    if (!aligned(out_f32, 4)) return KRK_CUDA_EALIGN;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_dequant_rows(static_cast<float *>(out_f32), static_cast<const uint8_t *>(w), wt,
+                               n_rows, n_in, static_cast<cudaStream_t>(stream));
+}
+
+int krk_cuda_gemv(void *y_f32, const void *x_f32, const void *w, int wt, int64_t n_out, int64_t n_in,
+                  int64_t rows, int accumulate, void *stream) {
+    int rc = check_matmul_args(y_f32, x_f32, w, wt, n_out, n_in, rows);
+    if (rc != KRK_CUDA_OK) return rc;
+    if (rows > KRK_CUDA_MAX_ROWS) return KRK_CUDA_ESHAPE;
+    if (n_out == 0 || rows == 0) return KRK_CUDA_OK;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    GemvMat m;
+    m.w = static_cast<const uint8_t *>(w);
+    m.x = static_cast<const float *>(x_f32);
+    m.y = static_cast<float *>(y_f32);
+    m.n_out = n_out;
+    m.wt = wt;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    rc = launch_gemv_stream(&m, 1, n_in, (int)rows, accumulate, 0, st);
+    if (rc != 0) return rc < 0 ? rc : KRK_CUDA_OK;
+    return launch_gemv_generic(&m, 1, n_in, (int)rows, accumulate, 0, st);
+}
+
+int krk_cuda_gemv_group(void *const host_y[], const void *const host_x[], const void *const host_w[],
+                        const int host_wt[], const int64_t host_n_out[], int64_t n_in, int n_mat,
+                        int fuse_silu_pair, void *stream) {
+    if (n_mat < 0 || n_mat > KRK_CUDA_MAX_GROUP) return KRK_CUDA_EARG;
+    if (n_mat == 0) return KRK_CUDA_OK;
+    if (!host_y || !host_x || !host_w || !host_wt || !host_n_out) return KRK_CUDA_ENULL;
+    if (fuse_silu_pair && (n_mat & 1)) return KRK_CUDA_EARG;
+    GemvMat mats[KRK_CUDA_MAX_GROUP];
+    for (int m = 0; m < n_mat; m++) {
+        const int rc = check_matmul_args(host_y[m], host_x[m], host_w[m], host_wt[m], host_n_out[m], n_in, 1);
+        if (rc != KRK_CUDA_OK) return rc;
+        if (fuse_silu_pair && (m & 1) &&
+            (host_n_out[m] != host_n_out[m - 1] || host_wt[m] != host_wt[m - 1] || host_x[m] != host_x[m - 1]))
+            return KRK_CUDA_EARG;
+        mats[m].w = static_cast<const uint8_t *>(host_w[m]);
+        mats[m].x = static_cast<const float *>(host_x[m]);
+        mats[m].y = static_cast<float *>(host_y[m]);
+        mats[m].n_out = host_n_out[m];
+        mats[m].wt = host_wt[m];
+    }
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int rc = launch_gemv_stream(mats, n_mat, n_in, 1, 0, fuse_silu_pair, st);
+    if (rc != 0) return rc < 0 ? rc : KRK_CUDA_OK;
+    return launch_gemv_generic(mats, n_mat, n_in, 1, 0, fuse_silu_pair, st);
+}
+
+size_t krk_cuda_gemm_workspace_bytes(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows) {
+    (void)n_out;
+    if (rows <= 0 || n_in <= 0) return 0;
+    return gemm_workspace_bytes(x_dtype, n_in, rows);
+}
+
+int krk_cuda_gemm(void *y_f32, const void *x, int x_dtype, const void *w, int wt, int64_t n_out,
+                  int64_t n_in, int64_t rows, void *workspace, size_t ws_bytes, void *stream) {
+    if (x_dtype != KRK_CUDA_X_F32 && x_dtype != KRK_CUDA_X_F16) return KRK_CUDA_EARG;
+    const int rc = check_matmul_args(y_f32, x, w, wt, n_out, n_in, rows);
+    if (rc != KRK_CUDA_OK) return rc;
+    if (n_in % 256 != 0) return KRK_CUDA_ESHAPE;
+    if (n_out == 0 || rows == 0) return KRK_CUDA_OK;
+    const size_t need = gemm_workspace_bytes(x_dtype, n_in, rows);
+    if (need > 0 && (!workspace || ws_bytes < need || !aligned(workspace, 128))) return KRK_CUDA_EWORKSPACE;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_gemm_tc(static_cast<float *>(y_f32), x, x_dtype, static_cast<const uint8_t *>(w), wt,
+                          n_out, n_in, rows, workspace, static_cast<cudaStream_t>(stream));
+}
+
+int krk_cuda_route(void *ids_i32, void *wts_f32, const void *logits_f32, int64_t n_tok, int n_expert,
+                   int k, void *stream) {
+    if (n_tok < 0) return KRK_CUDA_ESHAPE;
+    if (n_tok > 0 && (!ids_i32 || !wts_f32 || !logits_f32)) return KRK_CUDA_ENULL;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_route(static_cast<int32_t *>(ids_i32), static_cast<float *>(wts_f32),
+                        static_cast<const float *>(logits_f32), n_tok, n_expert, k,
+                        static_cast<cudaStream_t>(stream));
+}
+
+static int check_bank(const krk_cuda_expert_bank *b) {
+    if (!b) return KRK_CUDA_ENULL;
+    if (!krk_cuda_dtype_ok(b->wt_gate_up) || !krk_cuda_dtype_ok(b->wt_down)) return KRK_CUDA_EDTYPE;
+    if (b->n_local < 0 || !krk_cuda_gemm_k_ok(b->wt_gate_up, b->n_embd) ||
+        !krk_cuda_gemm_k_ok(b->wt_down, b->n_ff))
+        return KRK_CUDA_ESHAPE;
+    if (b->n_local > 0 && (!b->gate || !b->up || !b->down)) return KRK_CUDA_ENULL;
+    if (!aligned(b->gate, 16) || !aligned(b->up, 16) || !aligned(b->down, 16)) return KRK_CUDA_EALIGN;
+    return KRK_CUDA_OK;
+}
+
+size_t krk_cuda_moe_workspace_bytes(const struct krk_cuda_expert_bank *bank, int k, int64_t n_tok) {
+    if (check_bank(bank) != KRK_CUDA_OK || k <= 0 || n_tok <= 0) return 0;
+    return moe_workspace_bytes(bank, k, n_tok);
+}
+
+int krk_cuda_moe_ffn(void *y_f32, const void *x_f32, const void *ids_i32, const void *wts_f32,
+                     const struct krk_cuda_expert_bank *bank, int k, int64_t n_tok, void *workspace,
+                     size_t ws_bytes, void *stream) {
+    const int rc = check_bank(bank);
+    if (rc != KRK_CUDA_OK) return rc;
+    if (k <= 0 || k > 32) return KRK_CUDA_EARG;
+    if (n_tok < 0 || n_tok > KRK_CUDA_MAX_ROWS) return KRK_CUDA_ESHAPE;
+    if (n_tok == 0) return KRK_CUDA_OK;
+    if (!y_f32 || !x_f32 || !ids_i32 || !wts_f32) return KRK_CUDA_ENULL;
+    if (!aligned(x_f32, 16) || !aligned(y_f32, 4)) return KRK_CUDA_EALIGN;
+    if (!workspace || ws_bytes < moe_workspace_bytes(bank, k, n_tok) || !aligned(workspace, 16))
+        return KRK_CUDA_EWORKSPACE;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_moe_ffn_generic(static_cast<float *>(y_f32), static_cast<const float *>(x_f32),
+                                  static_cast<const int32_t *>(ids_i32),
+                                  static_cast<const float *>(wts_f32), bank, k, n_tok, workspace,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+int krk_cuda_silu_mul(void *out_f32, const void *gate_f32, const void *up_f32, int64_t n, void *stream) {
+    if (n < 0) return KRK_CUDA_ESHAPE;
+    if (n > 0 && (!out_f32 || !gate_f32 || !up_f32)) return KRK_CUDA_ENULL;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_silu_mul(static_cast<float *>(out_f32), static_cast<const float *>(gate_f32),
+                           static_cast<const float *>(up_f32), n, static_cast<cudaStream_t>(stream));
+}
+
+int krk_cuda_scatter_axpy_rows(void *dst_f32, const void *src_f32, const void *rows_i32,
+                               const void *alpha_f32, int64_t n_rows, int64_t n, void *stream) {
+    if (n_rows < 0 || n < 0) return KRK_CUDA_ESHAPE;
+    if (n_rows * n > 0 && (!dst_f32 || !src_f32 || !rows_i32 || !alpha_f32)) return KRK_CUDA_ENULL;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_scatter_axpy_rows(static_cast<float *>(dst_f32), static_cast<const float *>(src_f32),
+                                    static_cast<const int32_t *>(rows_i32),
+                                    static_cast<const float *>(alpha_f32), n_rows, n,
+                                    static_cast<cudaStream_t>(stream));
+}
+
+int krk_cuda_sum_parts(void *out_f32, const void *parts_f32, int n_parts, int64_t n, void *stream) {
+    if (n < 0 || n_parts <= 0) return KRK_CUDA_ESHAPE;
+    if (n > 0 && (!out_f32 || !parts_f32)) return KRK_CUDA_ENULL;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_sum_parts(static_cast<float *>(out_f32), static_cast<const float *>(parts_f32),
+                            n_parts, n, static_cast<cudaStream_t>(stream));
+}
+
+int krk_cuda_device_status(void) {
+    int *p = device_status_word();
+    if (!p) return KRK_CUDA_EDEVICE;
+    int v = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        return KRK_CUDA_ELAUNCH;
+    }
+    if (v != 0) cudaMemset(p, 0, sizeof(int));
+    return v;
+}
+
+int64_t krk_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+} // extern "C"

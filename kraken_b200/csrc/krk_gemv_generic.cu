@@ -1,0 +1,124 @@
+// Shape-agnostic decode GEMV: one warp per output row, lanes stride over 32-value chunks,
+// f32 accumulation, shuffle reduction. It takes every legal shape (any n_in that is a
+// whole number of blocks, any alignment the format allows) and is the path for shapes the
+// streaming kernel does not address and for Q4_0. Same contract as gemv_kernel /
+// gemv_m_kernel of the reference (src/hip/kernels/gemm.hpp:76-167) with f32 activations.
+#include "krk_chunk.cuh"
+
+namespace krk_cuda {
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+struct GenericParams {
+    GemvMat mat[KRK_CUDA_MAX_GROUP];
+    int block_begin[KRK_CUDA_MAX_GROUP + 1];  // first thread block of each matrix
+    int n_mat;
+    int rows;
+    int accumulate;
+    int64_t n_in;
+};
+
+template <int WT, int ROWS>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+gemv_generic_kernel(const __grid_constant__ GenericParams p) {
+    int m = 0;
+    while (m + 1 < p.n_mat && (int)blockIdx.x >= p.block_begin[m + 1]) m++;
+    const GemvMat &mat = p.mat[m];
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)(blockIdx.x - p.block_begin[m]) * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (row >= mat.n_out) return;
+    const int64_t n_chunks = p.n_in >> 5;
+    const uint8_t *wrow = mat.w + (size_t)row * row_bytes(WT, p.n_in);
+
+    float acc[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; r++) acc[r] = 0.0f;
+
+    for (int64_t c = lane; c < n_chunks; c += 32) {
+        float v[32];
+        decode_chunk<WT>(wrow, c, v);
+#pragma unroll
+        for (int r = 0; r < ROWS; r++) {
+            if (r < p.rows) {
+                const float4 *xv = reinterpret_cast<const float4 *>(mat.x + (int64_t)r * p.n_in + c * 32);
+                float s = 0.0f;
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    const float4 t = xv[k];
+                    s = fmaf(v[4 * k + 0], t.x, s);
+                    s = fmaf(v[4 * k + 1], t.y, s);
+                    s = fmaf(v[4 * k + 2], t.z, s);
+                    s = fmaf(v[4 * k + 3], t.w, s);
+                }
+                acc[r] += s;
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; r++) {
+        float s = acc[r];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+        if (lane == 0 && r < p.rows) {
+            float *y = mat.y + (int64_t)r * mat.n_out + row;
+            *y = p.accumulate ? __fadd_rn(*y, s) : s;
+        }
+    }
+}
+
+} // namespace
+
+int launch_gemv_generic(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accumulate,
+                        int silu_pair, cudaStream_t st) {
+    // Matrices of one launch share a weight type here; mixed groups go out as one launch
+    // per run of equal types.
+    int first = 0;
+    while (first < n_mat) {
+        int last = first + 1;
+        while (last < n_mat && mats[last].wt == mats[first].wt) last++;
+        GenericParams p;
+        p.n_mat = 0;
+        p.rows = rows;
+        p.accumulate = accumulate;
+        p.n_in = n_in;
+        int blocks = 0;
+        for (int m = first; m < last; m++) {
+            if (mats[m].n_out == 0) continue;
+            p.mat[p.n_mat] = mats[m];
+            p.block_begin[p.n_mat] = blocks;
+            blocks += (int)((mats[m].n_out + kWarpsPerBlock - 1) / kWarpsPerBlock);
+            p.n_mat++;
+        }
+        p.block_begin[p.n_mat] = blocks;
+        if (blocks > 0) {
+            const int wt = mats[first].wt;
+            if (rows <= 1) {
+                KRK_DISPATCH_WT(wt, gemv_generic_kernel<WT, 1><<<blocks, kWarpsPerBlock * 32, 0, st>>>(p));
+            } else if (rows <= 4) {
+                KRK_DISPATCH_WT(wt, gemv_generic_kernel<WT, 4><<<blocks, kWarpsPerBlock * 32, 0, st>>>(p));
+            } else {
+                KRK_DISPATCH_WT(wt, gemv_generic_kernel<WT, 8><<<blocks, kWarpsPerBlock * 32, 0, st>>>(p));
+            }
+            note_launch();
+            const int rc = check_launch();
+            if (rc != KRK_CUDA_OK) return rc;
+        }
+        first = last;
+    }
+    if (silu_pair) {
+        // The gate/up fold as a second pass: y[2i] = silu(y[2i]) * y[2i+1].
+        for (int m = 0; m + 1 < n_mat; m += 2) {
+            for (int r = 0; r < rows; r++) {
+                float *g = mats[m].y + (int64_t)r * mats[m].n_out;
+                const float *u = mats[m + 1].y + (int64_t)r * mats[m + 1].n_out;
+                const int rc = launch_silu_mul(g, g, u, mats[m].n_out, st);
+                if (rc != KRK_CUDA_OK) return rc;
+            }
+        }
+    }
+    return KRK_CUDA_OK;
+}
+
+} // namespace krk_cuda

@@ -1,0 +1,227 @@
+// Router and routed-expert FFN for decode batches (1..8 tokens).
+//
+// The routing result stays on the device: expert ids are read by the kernels themselves,
+// so no logits or ids cross PCIe (the reference downloads the logits and routes on the
+// host, src/engine.cpp:11678-11920, or reads device ids in its opt-in moe_dispatch,
+// src/hip/kernels/moe_table.hpp:67-180).
+#include "krk_chunk.cuh"
+
+namespace krk_cuda {
+
+namespace {
+
+constexpr int kMaxExperts = 1024;
+constexpr int kMaxK = 32;
+
+// One warp per token. Softmax as the reference computes it: subtract the maximum, sum the
+// exponentials in expert order, multiply by the reciprocal (src/engine.cpp:11704-11713);
+// then k picks of the largest probability, strict '>' so equal probabilities keep the lower
+// id (:11857-11886); then the picked weights are divided by their slot-order sum
+// (:11913-11918).
+__global__ void __launch_bounds__(32)
+route_kernel(int32_t *__restrict__ ids, float *__restrict__ wts, const float *__restrict__ logits,
+             int n_expert, int k) {
+    __shared__ float prob[kMaxExperts];
+    __shared__ float wsel[kMaxK];
+    const int lane = threadIdx.x;
+    const int64_t t = blockIdx.x;
+    const float *lg = logits + t * n_expert;
+
+    float mx = -INFINITY;
+    for (int e = lane; e < n_expert; e += 32) mx = fmaxf(mx, lg[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    for (int e = lane; e < n_expert; e += 32) prob[e] = expf(__fsub_rn(lg[e], mx));
+    __syncwarp();
+    float sum = 0.0f;
+    if (lane == 0)
+        for (int e = 0; e < n_expert; e++) sum = __fadd_rn(sum, prob[e]);
+    sum = __shfl_sync(0xFFFFFFFFu, sum, 0);
+    const float inv = sum > 0.0f ? __fdiv_rn(1.0f, sum) : 0.0f;
+    for (int e = lane; e < n_expert; e += 32) prob[e] = __fmul_rn(prob[e], inv);
+    __syncwarp();
+
+    for (int s = 0; s < k; s++) {
+        float bp = -1.0f;
+        int be = 0x7FFFFFFF;
+        for (int e = lane; e < n_expert; e += 32) {
+            const float pe = prob[e];   // a taken expert is marked with -2
+            if (pe > bp) {
+                bp = pe;
+                be = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float op = __shfl_xor_sync(0xFFFFFFFFu, bp, o);
+            const int oe = __shfl_xor_sync(0xFFFFFFFFu, be, o);
+            if (op > bp || (op == bp && oe < be)) {
+                bp = op;
+                be = oe;
+            }
+        }
+        if (lane == 0) {
+            const bool ok = be < n_expert && bp >= 0.0f;
+            ids[t * k + s] = ok ? be : -1;
+            wsel[s] = ok ? bp : 0.0f;
+            if (ok) prob[be] = -2.0f;
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        float ksum = 0.0f;
+        for (int s = 0; s < k; s++) ksum = __fadd_rn(ksum, wsel[s]);
+        const float kinv = ksum > 0.0f ? __fdiv_rn(1.0f, ksum) : 0.0f;
+        for (int s = 0; s < k; s++) wts[t * k + s] = __fmul_rn(wsel[s], kinv);
+    }
+}
+
+struct MoeParams {
+    const uint8_t *gate, *up, *down;
+    const float *x;        // [n_tok][n_embd]
+    const int32_t *ids;    // [n_tok][k]
+    const float *wts;      // [n_tok][k]
+    float *h;              // [n_tok*k][n_ff]   silu(gate) * up per pick
+    float *d;              // [n_tok*k][n_embd] down projection per pick
+    float *y;              // [n_tok][n_embd]
+    int64_t n_embd, n_ff;
+    int n_local, expert_base, k, n_tok;
+};
+
+__device__ __forceinline__ int local_expert(const MoeParams &p, int pick) {
+    const int e = p.ids[pick] - p.expert_base;
+    return (e >= 0 && e < p.n_local) ? e : -1;
+}
+
+// h[pick][row] = silu(Wgate_e[row] . x_t) * (Wup_e[row] . x_t); one warp per (pick, row).
+template <int WT>
+__global__ void __launch_bounds__(256)
+moe_gate_up_kernel(const __grid_constant__ MoeParams p) {
+    const int pick = blockIdx.y;
+    const int e = local_expert(p, pick);
+    if (e < 0) return;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= p.n_ff) return;
+    const size_t rb = row_bytes(WT, p.n_embd);
+    const uint8_t *g = p.gate + ((size_t)e * p.n_ff + row) * rb;
+    const uint8_t *u = p.up + ((size_t)e * p.n_ff + row) * rb;
+    const float *x = p.x + (int64_t)(pick / p.k) * p.n_embd;
+    float sg = 0.0f, su = 0.0f;
+    for (int64_t c = lane; c < (p.n_embd >> 5); c += 32) {
+        sg += chunk_dot<WT>(g, c, x);
+        su += chunk_dot<WT>(u, c, x);
+    }
+    sg = warp_sum(sg);
+    su = warp_sum(su);
+    if (lane == 0)
+        p.h[(int64_t)pick * p.n_ff + row] = __fmul_rn(__fdiv_rn(sg, __fadd_rn(1.0f, expf(-sg))), su);
+}
+
+// d[pick][row] = Wdown_e[row] . h[pick]
+template <int WT>
+__global__ void __launch_bounds__(256)
+moe_down_kernel(const __grid_constant__ MoeParams p) {
+    const int pick = blockIdx.y;
+    const int e = local_expert(p, pick);
+    if (e < 0) return;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= p.n_embd) return;
+    const uint8_t *w = p.down + ((size_t)e * p.n_embd + row) * row_bytes(WT, p.n_ff);
+    const float *h = p.h + (int64_t)pick * p.n_ff;
+    float s = 0.0f;
+    for (int64_t c = lane; c < (p.n_ff >> 5); c += 32) s += chunk_dot<WT>(w, c, h);
+    s = warp_sum(s);
+    if (lane == 0) p.d[(int64_t)pick * p.n_embd + row] = s;
+}
+
+// y[t][j] = sum over the picks of token t held here, ascending expert id, of w * d[pick][j]
+// starting from zero: the order and the arithmetic of the reference's per-expert
+// scatter_axpy_rows chain (src/engine.cpp:12353-, src/backend_cpu.cpp:3193-3220).
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __grid_constant__ MoeParams p) {
+    const int t = blockIdx.y;
+    int order[kMaxK];
+    int n = 0;
+    for (int s = 0; s < p.k; s++)
+        if (local_expert(p, t * p.k + s) >= 0) order[n++] = s;
+    for (int i = 1; i < n; i++) {   // insertion sort by expert id; k is small
+        const int s = order[i];
+        int j = i - 1;
+        while (j >= 0 && p.ids[t * p.k + order[j]] > p.ids[t * p.k + s]) {
+            order[j + 1] = order[j];
+            j--;
+        }
+        order[j + 1] = s;
+    }
+    for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < p.n_embd;
+         j += (int64_t)gridDim.x * blockDim.x) {
+        float acc = 0.0f;
+        for (int i = 0; i < n; i++) {
+            const int pick = t * p.k + order[i];
+            acc = __fadd_rn(acc, __fmul_rn(p.wts[pick], p.d[(int64_t)pick * p.n_embd + j]));
+        }
+        p.y[(int64_t)t * p.n_embd + j] = acc;
+    }
+}
+
+} // namespace
+
+int launch_route(int32_t *ids, float *wts, const float *logits, int64_t n_tok, int n_expert, int k,
+                 cudaStream_t st) {
+    if (n_expert <= 0 || n_expert > kMaxExperts || k <= 0 || k > kMaxK || k > n_expert)
+        return KRK_CUDA_EARG;
+    if (n_tok == 0) return KRK_CUDA_OK;
+    route_kernel<<<(unsigned)n_tok, 32, 0, st>>>(ids, wts, logits, n_expert, k);
+    note_launch();
+    return check_launch();
+}
+
+size_t moe_workspace_bytes(const krk_cuda_expert_bank *bank, int k, int64_t n_tok) {
+    return sizeof(float) * (size_t)(n_tok * k) * (size_t)(bank->n_ff + bank->n_embd);
+}
+
+int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const float *wts,
+                           const krk_cuda_expert_bank *bank, int k, int64_t n_tok, void *workspace,
+                           cudaStream_t st) {
+    MoeParams p;
+    p.gate = static_cast<const uint8_t *>(bank->gate);
+    p.up = static_cast<const uint8_t *>(bank->up);
+    p.down = static_cast<const uint8_t *>(bank->down);
+    p.x = x;
+    p.ids = ids;
+    p.wts = wts;
+    p.h = static_cast<float *>(workspace);
+    p.d = p.h + (size_t)(n_tok * k) * bank->n_ff;
+    p.y = y;
+    p.n_embd = bank->n_embd;
+    p.n_ff = bank->n_ff;
+    p.n_local = bank->n_local;
+    p.expert_base = bank->expert_base;
+    p.k = k;
+    p.n_tok = (int)n_tok;
+    const int picks = (int)(n_tok * k);
+    {
+        dim3 grid((unsigned)((bank->n_ff + 7) / 8), (unsigned)picks);
+        KRK_DISPATCH_WT(bank->wt_gate_up, moe_gate_up_kernel<WT><<<grid, 256, 0, st>>>(p));
+        note_launch();
+        const int rc = check_launch();
+        if (rc != KRK_CUDA_OK) return rc;
+    }
+    {
+        dim3 grid((unsigned)((bank->n_embd + 7) / 8), (unsigned)picks);
+        KRK_DISPATCH_WT(bank->wt_down, moe_down_kernel<WT><<<grid, 256, 0, st>>>(p));
+        note_launch();
+        const int rc = check_launch();
+        if (rc != KRK_CUDA_OK) return rc;
+    }
+    {
+        dim3 grid((unsigned)((bank->n_embd + 255) / 256), (unsigned)n_tok);
+        moe_combine_kernel<<<grid, 256, 0, st>>>(p);
+        note_launch();
+        return check_launch();
+    }
+}
+
+} // namespace krk_cuda

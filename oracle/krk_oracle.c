@@ -1,0 +1,340 @@
+/*
+ * krk_oracle.c -- CPU restatement of Kraken's scalar f32 quantized-weight matmul.
+ *
+ * TEST INFRASTRUCTURE ONLY: the checker for the CUDA path, never part of it.
+ * Parity status: PINNED against the compiled reference (oracle/_ref) and the
+ * reference suite's known-answer vectors; see krk_oracle.h.
+ *
+ * Build with -ffp-contract=off: the reference's decoders round every product before
+ * the subtract (src/quant.cpp:446-453) and the dot is a chain of separately rounded
+ * multiply and add (src/quant.cpp:5579-5589).
+ */
+#include "krk_oracle.h"
+
+#include <math.h>
+#include <pthread.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* ---- geometry: src/quant.cpp:1805-1900 ---------------------------------------- */
+
+int krk_oracle_block_size(int wt) {
+    switch (wt) {
+    case KRK_ORACLE_Q4_0:
+    case KRK_ORACLE_Q8_0: return 32;
+    case KRK_ORACLE_Q4_K:
+    case KRK_ORACLE_Q6_K: return 256;
+    default: return 0;
+    }
+}
+
+int krk_oracle_block_bytes(int wt) {
+    switch (wt) {
+    case KRK_ORACLE_Q4_0: return 18;
+    case KRK_ORACLE_Q8_0: return 34;
+    case KRK_ORACLE_Q4_K: return 144;
+    case KRK_ORACLE_Q6_K: return 210;
+    default: return 0;
+    }
+}
+
+size_t krk_oracle_row_bytes(int wt, int64_t n_in) {
+    const int bs = krk_oracle_block_size(wt);
+    if (bs == 0 || n_in < 0) return 0;
+    return (size_t)((n_in + bs - 1) / bs) * (size_t)krk_oracle_block_bytes(wt);
+}
+
+/* ---- half -> float: src/common.cpp:161-187 ------------------------------------ */
+
+float krk_oracle_fp16_to_fp32(uint16_t h) {
+    const uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+    uint32_t expo = (h >> 10) & 0x1Fu;
+    uint32_t man = h & 0x3FFu;
+    uint32_t bits;
+    if (expo == 31) {
+        bits = sign | 0x7F800000u | (man << 13);
+    } else if (expo != 0) {
+        bits = sign | ((expo + 112u) << 23) | (man << 13);
+    } else if (man == 0) {
+        bits = sign;
+    } else {
+        /* subnormal half: normalise the mantissa into a float exponent */
+        int shift = 0;
+        while (!(man & 0x400u)) {
+            man <<= 1;
+            shift++;
+        }
+        bits = sign | ((uint32_t)(113 - shift) << 23) | ((man & 0x3FFu) << 13);
+    }
+    float f;
+    memcpy(&f, &bits, sizeof f);
+    return f;
+}
+
+static inline float half_at(const uint8_t *p) {
+    return krk_oracle_fp16_to_fp32((uint16_t)(p[0] | (p[1] << 8)));
+}
+
+/* ---- per-format block decoders ------------------------------------------------- */
+
+/* src/quant.cpp:381-387 */
+static void block_q8_0(const uint8_t *b, float *y) {
+    const float d = half_at(b);
+    for (int k = 0; k < 32; k++) y[k] = d * (float)(int8_t)b[2 + k];
+}
+
+/* src/quant.cpp:331-339: low nibbles are values 0..15, high nibbles 16..31 */
+static void block_q4_0(const uint8_t *b, float *y) {
+    const float d = half_at(b);
+    for (int k = 0; k < 16; k++) {
+        y[k] = d * (float)((int)(b[2 + k] & 0xF) - 8);
+        y[k + 16] = d * (float)((int)(b[2 + k] >> 4) - 8);
+    }
+}
+
+/* src/quant.cpp:427-435: the j-th 6-bit scale and 6-bit min out of 12 packed bytes */
+static void scale_min_k4(int j, const uint8_t *p, int *sc, int *mn) {
+    if (j < 4) {
+        *sc = p[j] & 63;
+        *mn = p[j + 4] & 63;
+    } else {
+        *sc = (p[j + 4] & 0xF) | ((p[j - 4] >> 6) << 4);
+        *mn = (p[j + 4] >> 4) | ((p[j] >> 6) << 4);
+    }
+}
+
+/* src/quant.cpp:437-460: value = (d*sc)*q - (dmin*m), both products rounded first */
+static void block_q4_k(const uint8_t *b, float *y) {
+    const float d = half_at(b);
+    const float dmin = half_at(b + 2);
+    const uint8_t *packed = b + 4;
+    for (int pair = 0; pair < 4; pair++) {
+        const uint8_t *q = b + 16 + 32 * pair;
+        float *yy = y + 64 * pair;
+        int s0, m0, s1, m1;
+        scale_min_k4(2 * pair, packed, &s0, &m0);
+        scale_min_k4(2 * pair + 1, packed, &s1, &m1);
+        const float dl0 = d * (float)s0, mn0 = dmin * (float)m0;
+        const float dl1 = d * (float)s1, mn1 = dmin * (float)m1;
+        for (int l = 0; l < 32; l++) {
+            yy[l] = dl0 * (float)(q[l] & 0xF) - mn0;
+            yy[l + 32] = dl1 * (float)(q[l] >> 4) - mn1;
+        }
+    }
+}
+
+/* src/quant.cpp:491-512: value = (d*scale)*(q-32), left to right */
+static void block_q6_k(const uint8_t *b, float *y) {
+    const float d = half_at(b + 208);
+    for (int half = 0; half < 2; half++) {
+        const uint8_t *ql = b + 64 * half;
+        const uint8_t *qh = b + 128 + 32 * half;
+        const int8_t *sc = (const int8_t *)(b + 192) + 8 * half;
+        float *yy = y + 128 * half;
+        for (int l = 0; l < 32; l++) {
+            const int g = l >> 4;
+            const int q1 = (ql[l] & 0xF) | ((qh[l] & 3) << 4);
+            const int q2 = (ql[l + 32] & 0xF) | (((qh[l] >> 2) & 3) << 4);
+            const int q3 = (ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4);
+            const int q4 = (ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4);
+            yy[l] = d * (float)sc[g] * (float)(q1 - 32);
+            yy[l + 32] = d * (float)sc[g + 2] * (float)(q2 - 32);
+            yy[l + 64] = d * (float)sc[g + 4] * (float)(q3 - 32);
+            yy[l + 96] = d * (float)sc[g + 6] * (float)(q4 - 32);
+        }
+    }
+}
+
+/* src/quant.cpp:1553-1599 */
+static void decode_block(int wt, const uint8_t *b, float *y) {
+    switch (wt) {
+    case KRK_ORACLE_Q8_0: block_q8_0(b, y); break;
+    case KRK_ORACLE_Q4_0: block_q4_0(b, y); break;
+    case KRK_ORACLE_Q4_K: block_q4_k(b, y); break;
+    case KRK_ORACLE_Q6_K: block_q6_k(b, y); break;
+    default: break;
+    }
+}
+
+int krk_oracle_dequant_rows(float *out, const void *w, int wt, int64_t n_rows, int64_t n_in) {
+    const int bs = krk_oracle_block_size(wt);
+    const int bb = krk_oracle_block_bytes(wt);
+    if (bs == 0 || n_in < 0 || n_rows < 0 || n_in % bs != 0) return -1;
+    const int64_t nblk = n_in / bs;
+    const uint8_t *p = (const uint8_t *)w;
+    for (int64_t r = 0; r < n_rows; r++)
+        for (int64_t i = 0; i < nblk; i++, p += bb, out += bs) decode_block(wt, p, out);
+    return 0;
+}
+
+/* ---- dot and GEMM --------------------------------------------------------------- */
+
+/* src/quant.cpp:5579-5589: decode one block, then sum += w[k]*x[k] in index order */
+static float row_dot(int wt, const uint8_t *row, const float *x, int64_t n_in) {
+    const int bs = krk_oracle_block_size(wt);
+    const int bb = krk_oracle_block_bytes(wt);
+    float buf[256];
+    float sum = 0.0f;
+    for (int64_t i = 0; i < n_in; i += bs, row += bb) {
+        decode_block(wt, row, buf);
+        for (int k = 0; k < bs; k++) sum += buf[k] * x[i + k];
+    }
+    return sum;
+}
+
+typedef struct {
+    float *out;
+    const float *x;
+    const uint8_t *w;
+    int wt;
+    int64_t n_out, n_in, rows, o_begin, o_end;
+    size_t row_bytes;
+} gemm_job;
+
+static void *gemm_worker(void *arg) {
+    const gemm_job *j = (const gemm_job *)arg;
+    for (int64_t o = j->o_begin; o < j->o_end; o++) {
+        const uint8_t *wrow = j->w + (size_t)o * j->row_bytes;
+        for (int64_t r = 0; r < j->rows; r++)
+            j->out[r * j->n_out + o] = row_dot(j->wt, wrow, j->x + r * j->n_in, j->n_in);
+    }
+    return NULL;
+}
+
+/* src/backend_cpu.cpp:1303-1320: every output is an independent dot, so outputs may
+ * be split over threads without changing any bit. */
+int krk_oracle_gemm(float *out, const float *x, const void *w, int wt, int64_t n_out,
+                    int64_t n_in, int64_t rows, int n_threads) {
+    const int bs = krk_oracle_block_size(wt);
+    if (bs == 0 || n_in <= 0 || n_in % bs != 0 || n_out < 0 || rows < 0) return -1;
+    if (n_out == 0 || rows == 0) return 0;
+    if (n_threads < 1) n_threads = 1;
+    if (n_threads > 256) n_threads = 256;
+    if ((int64_t)n_threads > n_out) n_threads = (int)n_out;
+    gemm_job jobs[256];
+    pthread_t tids[256];
+    for (int t = 0; t < n_threads; t++) {
+        gemm_job *j = &jobs[t];
+        j->out = out;
+        j->x = x;
+        j->w = (const uint8_t *)w;
+        j->wt = wt;
+        j->n_out = n_out;
+        j->n_in = n_in;
+        j->rows = rows;
+        j->row_bytes = krk_oracle_row_bytes(wt, n_in);
+        j->o_begin = n_out * t / n_threads;
+        j->o_end = n_out * (t + 1) / n_threads;
+    }
+    if (n_threads == 1) {
+        gemm_worker(&jobs[0]);
+        return 0;
+    }
+    for (int t = 0; t < n_threads; t++) pthread_create(&tids[t], NULL, gemm_worker, &jobs[t]);
+    for (int t = 0; t < n_threads; t++) pthread_join(tids[t], NULL);
+    return 0;
+}
+
+/* ---- MoE pieces ------------------------------------------------------------------ */
+
+/* src/engine.cpp:11704-11713 (softmax), :11857-11886 (k picks, strict '>' so a tie
+ * keeps the lower id), :11913-11918 (renormalise over the picks, slot order). */
+int krk_oracle_route(int32_t *ids, float *wts, const float *logits, int64_t n_tok,
+                     int n_expert, int k) {
+    if (n_expert <= 0 || k <= 0 || k > n_expert) return -1;
+    float *prob = (float *)malloc(sizeof(float) * (size_t)n_expert);
+    if (!prob) return -1;
+    for (int64_t t = 0; t < n_tok; t++) {
+        const float *lg = logits + t * n_expert;
+        int32_t *sel = ids + t * k;
+        float *wt = wts + t * k;
+        float mx = lg[0];
+        for (int e = 1; e < n_expert; e++) mx = lg[e] > mx ? lg[e] : mx;
+        float sum = 0.0f;
+        for (int e = 0; e < n_expert; e++) {
+            prob[e] = expf(lg[e] - mx);
+            sum += prob[e];
+        }
+        const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+        for (int e = 0; e < n_expert; e++) prob[e] *= inv;
+        for (int s = 0; s < k; s++) {
+            int best = -1;
+            float bestp = -1.0f;
+            for (int e = 0; e < n_expert; e++) {
+                int taken = 0;
+                for (int p = 0; p < s; p++) taken |= (sel[p] == e);
+                if (taken) continue;
+                if (prob[e] > bestp) {
+                    bestp = prob[e];
+                    best = e;
+                }
+            }
+            sel[s] = best;
+            wt[s] = best >= 0 ? prob[best] : 0.0f;
+        }
+        float ksum = 0.0f;
+        for (int s = 0; s < k; s++) ksum += wt[s];
+        const float kinv = ksum > 0.0f ? 1.0f / ksum : 0.0f;
+        for (int s = 0; s < k; s++) wt[s] *= kinv;
+    }
+    free(prob);
+    return 0;
+}
+
+/* src/backend_cpu.cpp:2394-2400 */
+void krk_oracle_silu_mul(float *out, const float *gate, const float *up, int64_t n) {
+    for (int64_t i = 0; i < n; i++) {
+        const float g = gate[i];
+        out[i] = (g / (1.0f + expf(-g))) * up[i];
+    }
+}
+
+/* src/backend_cpu.cpp:3193-3220 */
+void krk_oracle_scatter_axpy_rows(float *dst, const float *src, const int32_t *rows,
+                                  const float *alpha, int64_t n_rows, int64_t n) {
+    for (int64_t i = 0; i < n_rows; i++) {
+        float *d = dst + (int64_t)rows[i] * n;
+        const float *s = src + i * n;
+        const float a = alpha[i];
+        for (int64_t j = 0; j < n; j++) d[j] += a * s[j];
+    }
+}
+
+/* Per-expert loop of src/engine.cpp:12353-: experts ascending; for each, the tokens
+ * routed to it in token order; gate and up GEMV, silu_mul, down GEMV, weighted
+ * scatter-add into the zero-filled output. */
+int krk_oracle_moe_ffn(float *y, const float *x, const int32_t *ids, const float *wts,
+                       const void *const *gate, const void *const *up,
+                       const void *const *down, int wt_gate_up, int wt_down,
+                       int n_expert, int k, int64_t n_tok, int64_t n_embd, int64_t n_ff,
+                       int n_threads) {
+    float *g = (float *)malloc(sizeof(float) * (size_t)n_ff * 3);
+    float *dn = (float *)malloc(sizeof(float) * (size_t)n_embd);
+    if (!g || !dn) {
+        free(g);
+        free(dn);
+        return -1;
+    }
+    float *u = g + n_ff, *h = g + 2 * n_ff;
+    memset(y, 0, sizeof(float) * (size_t)(n_tok * n_embd));
+    int rc = 0;
+    for (int e = 0; e < n_expert && rc == 0; e++) {
+        if (!gate[e] || !up[e] || !down[e]) continue;
+        for (int64_t t = 0; t < n_tok && rc == 0; t++) {
+            for (int s = 0; s < k; s++) {
+                if (ids[t * k + s] != e) continue;
+                const float *xt = x + t * n_embd;
+                rc |= krk_oracle_gemm(g, xt, gate[e], wt_gate_up, n_ff, n_embd, 1, n_threads);
+                rc |= krk_oracle_gemm(u, xt, up[e], wt_gate_up, n_ff, n_embd, 1, n_threads);
+                krk_oracle_silu_mul(h, g, u, n_ff);
+                rc |= krk_oracle_gemm(dn, h, down[e], wt_down, n_embd, n_ff, 1, n_threads);
+                const int32_t row = (int32_t)t;
+                const float a = wts[t * k + s];
+                krk_oracle_scatter_axpy_rows(y, dn, &row, &a, 1, n_embd);
+            }
+        }
+    }
+    free(g);
+    free(dn);
+    return rc;
+}

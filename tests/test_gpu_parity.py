@@ -1,0 +1,298 @@
+"""Parity of the CUDA path with the CPU checker, through the C ABI, on a B200.
+
+Bars (from the task's north star): decoded blocks bit-exact; GEMV |y - y_ref| <= 1e-4 *
+||w_row|| * ||x||; every integer result (router ids) exact.
+"""
+import numpy as np
+import pytest
+
+from conftest import bound_ok
+from kraken_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+FMTS = [synth.Q8_0, synth.Q4_0, synth.Q4_K, synth.Q6_K]
+GEMV_TOL = 1e-4
+SEED = synth.BASE_SEED
+
+
+def dev(a):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def run_gemv(cuda, oracle, wt, n_out, n_in, rows, seed, random_payload=False, accumulate=False):
+    w = synth.weights(wt, n_out, n_in, seed, stream=wt, random_payload=random_payload)
+    x = synth.activations(rows, n_in, seed)
+    y_ref = oracle.gemm(x, w, wt, n_out, n_in, rows=rows, threads=8)
+    if accumulate:
+        base = synth.activations(rows, n_out, seed, stream=2000)
+        y = cuda.gemv(dev(x), dev(w), wt, n_out, n_in, out=dev(base), accumulate=True).cpu().numpy()
+        y_ref = base + y_ref
+    else:
+        y = cuda.gemv(dev(x), dev(w), wt, n_out, n_in).cpu().numpy()
+    w_deq = oracle.dequant_rows(w, wt, n_out, n_in)
+    ok, worst = bound_ok(y, y_ref, w_deq, x, GEMV_TOL)
+    assert ok, f"wt={wt} {n_out}x{n_in} rows={rows}: worst error is {worst:.3f} of the bound"
+    assert cuda.device_status() == 0
+    return worst
+
+
+# ---- decode: bit-exact --------------------------------------------------------------------
+
+@pytest.mark.parametrize("wt", FMTS)
+@pytest.mark.parametrize("random_payload", [False, True])
+def test_dequant_bit_exact(cuda, oracle, wt, random_payload):
+    for n_rows, n_in in ((1, 256), (5, 1536), (64, 4096), (3, 11008)):
+        w = synth.weights(wt, n_rows, n_in, SEED + 3, stream=wt, random_payload=random_payload)
+        got = cuda.dequant_rows(dev(w), wt, n_rows, n_in).cpu().numpy()
+        assert got.tobytes() == oracle.dequant_rows(w, wt, n_rows, n_in).tobytes()
+
+
+def test_dequant_reference_vectors(cuda, golden):
+    for wt in FMTS:
+        name = synth.NAMES[wt].lower()
+        for tag in ("field", "bytes"):
+            w = golden[f"{name}_{tag}_w"]
+            want = golden[f"{name}_{tag}_deq"]
+            got = cuda.dequant_rows(dev(w), wt, want.shape[0], want.shape[1]).cpu().numpy()
+            assert got.tobytes() == want.tobytes()
+    for key, wt, n in (("kat_q4_0", synth.Q4_0, 32), ("kat_q8_0", synth.Q8_0, 32),
+                       ("kat_q4_k", synth.Q4_K, 256), ("kat_q6_k", synth.Q6_K, 256)):
+        got = cuda.dequant_rows(dev(golden[f"{key}_w"]), wt, 1, n).cpu().numpy()
+        assert got.tobytes() == golden[f"{key}_deq"].tobytes()
+
+
+def test_dequant_every_scale_bit_pattern(cuda, oracle):
+    """All 65536 f16 scale patterns (subnormals, inf, nan included) through one Q8_0 block each."""
+    blocks = np.zeros((65536, 34), np.uint8)
+    h = np.arange(65536, dtype=np.uint32)
+    blocks[:, 0], blocks[:, 1] = h & 0xFF, h >> 8
+    blocks[:, 2:] = np.array([1, 255, 127, 129] * 8, np.uint8)
+    got = cuda.dequant_rows(dev(blocks), synth.Q8_0, 65536, 32).cpu().numpy()
+    want = oracle.dequant_rows(blocks, synth.Q8_0, 65536, 32)
+    assert got.view(np.uint32).tobytes() == want.view(np.uint32).tobytes()
+
+
+# ---- GEMV ----------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("wt", FMTS)
+@pytest.mark.parametrize("rows", [1, 2, 7, 8])
+def test_gemv_shapes(cuda, oracle, wt, rows):
+    bs = synth.BLOCK_SIZE[wt]
+    for n_out, n_in in ((1, bs), (7, 256), (33, 1536), (257, 4096), (100, 11008), (16, 2048), (300, 512)):
+        run_gemv(cuda, oracle, wt, n_out, n_in, rows, SEED + rows)
+
+
+@pytest.mark.parametrize("wt", FMTS)
+def test_gemv_random_bytes_and_accumulate(cuda, oracle, wt):
+    run_gemv(cuda, oracle, wt, 129, 2048, 1, SEED + 21, random_payload=True)
+    run_gemv(cuda, oracle, wt, 129, 2048, 3, SEED + 22, accumulate=True)
+    run_gemv(cuda, oracle, wt, 4096, 4096, 1, SEED + 23, accumulate=True)
+
+
+def test_gemv_reference_vectors(cuda, golden, oracle):
+    for wt in FMTS:
+        name = synth.NAMES[wt].lower()
+        for tag in ("field", "bytes"):
+            w, x, want = golden[f"{name}_{tag}_w"], golden[f"{name}_{tag}_x"], golden[f"{name}_{tag}_y"]
+            n_out, n_in = w.shape[0], x.shape[1]
+            y = cuda.gemv(dev(x), dev(w), wt, n_out, n_in).cpu().numpy()
+            ok, worst = bound_ok(y, want, golden[f"{name}_{tag}_deq"], x, GEMV_TOL)
+            assert ok, f"{name}/{tag}: {worst:.3f} of the bound"
+
+
+def test_config1_q8_0_decode(cuda, oracle):
+    """Q8_0 4096x4096, batch 1: the reference's own CPU-runnable case, at full size."""
+    run_gemv(cuda, oracle, synth.Q8_0, 4096, 4096, 1, SEED + 1)
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096), (11008, 4096), (4096, 11008)])
+def test_config2_q4_k_llama7b_shapes(cuda, oracle, shape):
+    run_gemv(cuda, oracle, synth.Q4_K, shape[0], shape[1], 1, SEED + 2)
+
+
+def test_config4_q6_k_head_slice_and_linearity(cuda, oracle):
+    """An eighth of the 128256x4096 head against the checker, then the full head through
+    size-independent properties: row slices of the full call equal calls on the slices, and
+    y(a*x1 + x2) = a*y(x1) + y(x2) within the bound."""
+    import torch
+    n_in, n_full = 4096, 128256
+    run_gemv(cuda, oracle, synth.Q6_K, n_full // 8, n_in, 1, SEED + 4)
+    part = synth.weights(synth.Q6_K, 2004, n_in, SEED + 4, stream=synth.Q6_K)
+    w = dev(part).repeat(64, 1)                                  # 128256 rows, 431 MB
+    assert w.shape[0] == n_full
+    x1, x2 = synth.activations(1, n_in, SEED + 40), synth.activations(1, n_in, SEED + 41)
+    y1 = cuda.gemv(dev(x1), w, synth.Q6_K, n_full, n_in)
+    y2 = cuda.gemv(dev(x2), w, synth.Q6_K, n_full, n_in)
+    y3 = cuda.gemv(dev(0.5 * x1 + x2), w, synth.Q6_K, n_full, n_in)
+    assert torch.equal(y1.view(64, 2004)[0], y1.view(64, 2004)[63])          # repeated rows, same answer
+    y_slice = cuda.gemv(dev(x1), w[2004 * 5:], synth.Q6_K, 2004 * 3, n_in)
+    assert torch.equal(y_slice.view(-1), y1.view(-1)[2004 * 5:2004 * 8])     # a shard equals its slice
+    w_deq = oracle.dequant_rows(part, synth.Q6_K, 2004, n_in)
+    ok, worst = bound_ok(y3.cpu().numpy()[:, :2004], (0.5 * y1 + y2).cpu().numpy()[:, :2004], w_deq,
+                         np.abs(0.5 * x1) + np.abs(x2), 3 * GEMV_TOL)
+    assert ok, worst
+    ref = oracle.gemm(x1, part, synth.Q6_K, 2004, n_in, threads=8)
+    ok, worst = bound_ok(y1.cpu().numpy()[:, :2004], ref, w_deq, x1, GEMV_TOL)
+    assert ok, worst
+
+
+def test_gemv_empty_and_refusals(cuda):
+    import torch
+    x = torch.zeros(256, device="cuda")
+    w = torch.zeros(144 * 4, dtype=torch.uint8, device="cuda")
+    assert cuda.gemv(x, w, synth.Q4_K, 0, 256).shape == (1, 0)
+    before = cuda.launch_count()
+    with pytest.raises(cuda.KrkCudaError) as e:
+        cuda.gemv(x[:100], w, synth.Q4_K, 4, 100)
+    assert e.value.rc == -2
+    with pytest.raises(cuda.KrkCudaError) as e:
+        cuda.gemv(x, w, 99, 4, 256)
+    assert e.value.rc == -1
+    with pytest.raises(cuda.KrkCudaError) as e:
+        cuda.gemv(x, w[8:], synth.Q4_K, 3, 256)
+    assert e.value.rc == -4
+    assert cuda.launch_count() == before
+
+
+# ---- grouped GEMV ----------------------------------------------------------------------------
+
+def test_gemv_group_shared_x_and_silu_pair(cuda, oracle):
+    n_in, n_ff = 4096, 1536
+    seed = SEED + 6
+    x = synth.activations(1, n_in, seed)
+    ws = [synth.weights(synth.Q4_K, n, n_in, seed, stream=100 + i) for i, n in enumerate((n_ff, n_ff, 512, 40))]
+    n_outs = [w.shape[0] for w in ws]
+    dx = dev(x)
+    outs = cuda.gemv_group([dx] * 4, [dev(w) for w in ws], [synth.Q4_K] * 4, n_outs, n_in)
+    for w, y in zip(ws, outs):
+        ref = oracle.gemm(x, w, synth.Q4_K, w.shape[0], n_in)
+        ok, worst = bound_ok(y.cpu().numpy()[None], ref, oracle.dequant_rows(w, synth.Q4_K, w.shape[0], n_in), x, GEMV_TOL)
+        assert ok, worst
+    # the gate/up fold: y[0] = silu(gate) * up
+    outs = cuda.gemv_group([dx] * 2, [dev(ws[0]), dev(ws[1])], [synth.Q4_K] * 2, n_outs[:2], n_in, fuse_silu_pair=True)
+    g = oracle.gemm(x, ws[0], synth.Q4_K, n_ff, n_in)
+    u = oracle.gemm(x, ws[1], synth.Q4_K, n_ff, n_in)
+    want = oracle.silu_mul(g, u)[0]
+    got = outs[0].cpu().numpy()
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() <= 2e-4 * scale + 1e-6
+
+
+def test_gemv_group_own_x_mixed_types(cuda, oracle):
+    n_in = 1536
+    seed = SEED + 7
+    wts = [synth.Q6_K, synth.Q6_K, synth.Q8_0, synth.Q4_0]
+    n_outs = [4096, 300, 64, 33]
+    ws = [synth.weights(wt, n, n_in, seed, stream=200 + i) for i, (wt, n) in enumerate(zip(wts, n_outs))]
+    xs = [synth.activations(1, n_in, seed, stream=300 + i) for i in range(4)]
+    outs = cuda.gemv_group([dev(x) for x in xs], [dev(w) for w in ws], wts, n_outs, n_in)
+    for wt, w, x, y in zip(wts, ws, xs, outs):
+        ref = oracle.gemm(x, w, wt, w.shape[0], n_in)
+        ok, worst = bound_ok(y.cpu().numpy()[None], ref, oracle.dequant_rows(w, wt, w.shape[0], n_in), x, GEMV_TOL)
+        assert ok, (wt, worst)
+
+
+# ---- MoE --------------------------------------------------------------------------------------
+
+def test_route_ids_exact(cuda, oracle):
+    import torch
+    logits = synth.activations(64, 128, SEED + 8, stream=7)
+    logits[3, 10] = logits[3, 99] = logits[3].max() + 1.0        # an exact tie: the lower id wins
+    logits[4, :] = 0.25                                           # everything ties
+    ids, wts = cuda.route(dev(logits), 8)
+    ids_ref, wts_ref = oracle.route(logits, 8)
+    assert np.array_equal(ids.cpu().numpy(), ids_ref)
+    assert ids_ref[3, 0] == 10 and ids_ref[3, 1] == 99 and ids_ref[4].tolist() == list(range(8))
+    assert np.allclose(wts.cpu().numpy(), wts_ref, rtol=2e-6, atol=1e-9)
+
+
+def moe_case(cuda, oracle, n_embd, n_ff, n_exp, k, n_tok, seed, local=None):
+    import torch
+    gate = [synth.weights(synth.Q4_K, n_ff, n_embd, seed, stream=1000 + e) for e in range(n_exp)]
+    up = [synth.weights(synth.Q4_K, n_ff, n_embd, seed, stream=2000 + e) for e in range(n_exp)]
+    down = [synth.weights(synth.Q6_K, n_embd, n_ff, seed, stream=3000 + e) for e in range(n_exp)]
+    x = synth.activations(n_tok, n_embd, seed)
+    logits = synth.activations(n_tok, n_exp, seed, stream=7)
+    ids_ref, wts_ref = oracle.route(logits, k)
+    ids, wts = cuda.route(dev(logits), k)
+    assert np.array_equal(ids.cpu().numpy(), ids_ref)
+    lo, hi = local if local else (0, n_exp)
+    sel = lambda mats: [m if lo <= e < hi else None for e, m in enumerate(mats)]
+    y_ref = oracle.moe_ffn(x, ids_ref, wts_ref, sel(gate), sel(up), sel(down), synth.Q4_K, synth.Q6_K, n_embd, n_ff,
+                           threads=8)
+    bank = cuda.make_bank(dev(np.stack(gate[lo:hi])), dev(np.stack(up[lo:hi])), dev(np.stack(down[lo:hi])),
+                          synth.Q4_K, synth.Q6_K, hi - lo, lo, n_embd, n_ff)
+    keep = (bank,)
+    y = cuda.moe_ffn(dev(x), ids, wts, bank).cpu().numpy()
+    assert cuda.device_status() == 0
+    rel = np.linalg.norm(y - y_ref) / max(np.linalg.norm(y_ref), 1e-30)
+    assert rel < 2e-4, f"relative L2 error {rel:.2e}"
+    return y, y_ref, keep
+
+
+def test_moe_small(cuda, oracle):
+    moe_case(cuda, oracle, 512, 768, 8, 2, 3, SEED + 9)
+    moe_case(cuda, oracle, 256, 512, 4, 4, 1, SEED + 10)        # every expert picked
+
+
+def test_moe_config5_shapes_and_shards(cuda, oracle):
+    """Qwen3-MoE expert shapes (hidden 4096, expert width 1536, top-8) over a 16-expert bank,
+    batch 1 and 8; then two 8-expert shards whose partial sums add up to the whole."""
+    y1, y1_ref, _ = moe_case(cuda, oracle, 4096, 1536, 16, 8, 1, SEED + 11)
+    y8, y8_ref, _ = moe_case(cuda, oracle, 4096, 1536, 16, 8, 8, SEED + 12)
+    a, a_ref, _ = moe_case(cuda, oracle, 4096, 1536, 16, 8, 8, SEED + 12, local=(0, 8))
+    b, b_ref, _ = moe_case(cuda, oracle, 4096, 1536, 16, 8, 8, SEED + 12, local=(8, 16))
+    parts = dev(np.stack([a, b]))
+    total = cuda.sum_parts(parts).cpu().numpy()
+    assert np.array_equal(total, a + b)
+    assert np.linalg.norm(total - y8_ref) / np.linalg.norm(y8_ref) < 2e-4
+
+
+def test_silu_mul_and_scatter(cuda, golden):
+    got = cuda.silu_mul(dev(golden["silu_gate"]), dev(golden["silu_up"])).cpu().numpy()
+    assert np.allclose(got, golden["silu_out"], rtol=3e-6, atol=1e-7)
+    dst = dev(golden["scatter_dst"])
+    cuda.scatter_axpy_rows(dst, dev(golden["scatter_src"]), dev(golden["scatter_rows"]), dev(golden["scatter_alpha"]))
+    assert dst.cpu().numpy().tobytes() == golden["scatter_out"].tobytes()
+
+
+# ---- the host-buffer boundary: CudaBackend -------------------------------------------------------
+
+def test_backend_host_buffers_roundtrip(cuda, oracle):
+    """upload -> gemm / gemm_accumulate / gemm_group -> download with host arrays, as a Kraken
+    engine drives a backend (include/krk/backend.hpp:720-770, 858-900, 1040-1056)."""
+    be = cuda.Backend(0)
+    assert "sm_100" in be.describe()
+    n_out, n_in = 1000, 4096
+    wt = synth.Q4_K
+    w = synth.weights(wt, n_out, n_in, SEED + 13)
+    x = synth.activations(2, n_in, SEED + 13)
+    assert be.gemm_k_ok(wt, n_in) and not be.gemm_k_ok(wt, 100)
+    d_w, d_x, d_y = be.alloc(w.nbytes), be.alloc(x.nbytes), be.alloc(2 * n_out * 4)
+    be.upload(d_w, w.ctypes.data, w.nbytes)
+    be.upload(d_x, x.ctypes.data, x.nbytes)
+    be.gemm(d_y, d_x, d_w, wt, n_out, n_in, 2)
+    y = np.empty((2, n_out), np.float32)
+    be.download(y.ctypes.data, d_y, y.nbytes)
+    ref = oracle.gemm(x, w, wt, n_out, n_in, rows=2, threads=8)
+    w_deq = oracle.dequant_rows(w, wt, n_out, n_in)
+    ok, worst = bound_ok(y, ref, w_deq, x, GEMV_TOL)
+    assert ok, worst
+    assert be.gemm_accumulate(d_y, d_x, d_w, wt, n_out, n_in, 2)
+    y2 = np.empty_like(y)
+    be.download(y2.ctypes.data, d_y, y2.nbytes)
+    ok, worst = bound_ok(y2, 2 * ref, w_deq, 2 * x, GEMV_TOL)
+    assert ok, worst
+    d_y2 = be.alloc(n_out * 4)
+    be.fill0(d_y2, n_out * 4)
+    ran, fused = be.gemm_group([d_y, d_y2], d_x, [d_w, d_w], wt, [n_out, n_out], n_in, rows=1, silu=True)
+    assert ran and fused
+    h = np.empty(n_out, np.float32)
+    be.download(h.ctypes.data, d_y, h.nbytes)
+    want = oracle.silu_mul(ref[0], ref[0])
+    assert np.abs(h - want).max() <= 2e-4 * np.abs(want).max()
+    for p in (d_w, d_x, d_y, d_y2):
+        be.release(p)
+    be.close()
