@@ -1,0 +1,387 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-weight decode GEMV path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (config.workload): the Q4_K decode GEMV set with Llama-2-7B layer shapes, batch 1:
+per layer four matmuls (N x K) 4096x4096, 11008x4096, 11008x4096, 4096x11008, weights Q4_K,
+activations f32 ~ N(0,1), outputs f32. One STEP is one decode token's pass over all 32 layers
+(128 GEMV launches, 2.74 GB of distinct quantized weights), so every weight byte is read once
+per step and the working set is ~22x the 126 MB L2: the numbers are HBM numbers. Weights are
+seeded synthetic blocks with the value distributions of the real format (no checkpoint).
+
+value   = quantized weight bytes read per second over all GPUs, device-timed with CUDA events,
+          inputs resident in HBM.
+e2e     = the same, measured through the host-buffer boundary (CudaBackend: upload of the
+          step's activations from pinned host memory, 128 gemm() calls, download of the outputs).
+roofline= the streaming GEMV kernel against the measured HBM copy bandwidth.
+cpu_baseline = Kraken's own CPU backend (compiled reference sources when available, else the
+          in-repo restatement) on a bounded sample of the same workload.
+
+With N > 1 every rank runs its own replica of the workload (these dense layers do not shard;
+the sharded head / expert configs are reported under "sharded"), timing is the max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from kraken_b200 import synth  # noqa: E402
+
+LAYER_SHAPES = [(4096, 4096), (11008, 4096), (11008, 4096), (4096, 11008)]   # (n_out, n_in)
+N_LAYERS = 32
+WT = synth.Q4_K
+METRIC = "quant GEMV weight GB/s"
+UNIT = "GB/s"
+WORKLOAD = "q4_k_decode_gemv_llama2_7b_layer_set_x32"
+
+
+def layer_weight_bytes() -> int:
+    return sum(n * synth.row_bytes(WT, k) for n, k in LAYER_SHAPES)
+
+
+def layer_algorithmic_bytes() -> int:
+    # weights once + x + y per matmul
+    return sum(n * synth.row_bytes(WT, k) + 4 * k + 4 * n for n, k in LAYER_SHAPES)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---- clocks ---------------------------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.proc:
+            return out
+        self.proc.terminate()          # our own child, by handle
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ---- our arm ------------------------------------------------------------------------------------
+
+def device_weights(torch, n_out: int, n_in: int, gen):
+    """Q4_K blocks made on the device: payload bytes uniform (so every nibble and every packed
+    6-bit scale/min is uniform, as in the spec), d in [1e-3, 1e-2], dmin in [0, 5e-3] as f16."""
+    nblk = n_in // 256
+    w = torch.randint(0, 256, (n_out, nblk, 144), dtype=torch.uint8, device="cuda", generator=gen)
+    d = (1e-3 + 9e-3 * torch.rand((n_out, nblk), device="cuda", generator=gen)).to(torch.float16)
+    dm = (5e-3 * torch.rand((n_out, nblk), device="cuda", generator=gen)).to(torch.float16)
+    w[..., 0:2] = d.view(torch.uint8).view(n_out, nblk, 2)
+    w[..., 2:4] = dm.view(torch.uint8).view(n_out, nblk, 2)
+    return w.view(n_out, nblk * 144)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from kraken_b200 import capi
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(synth.BASE_SEED % (2 ** 63) + 2 + 1000 * rank)
+    layers = []
+    for _ in range(N_LAYERS):
+        mats = []
+        for n_out, n_in in LAYER_SHAPES:
+            w = device_weights(torch, n_out, n_in, gen)
+            x = torch.randn(n_in, device="cuda", generator=gen)
+            y = torch.empty(n_out, device="cuda")
+            mats.append((w, x, y, n_out, n_in))
+        layers.append(mats)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        for mats in layers:
+            for w, x, y, n_out, n_in in mats:
+                capi.gemv(x, w, WT, n_out, n_in, out=y.view(1, -1), stream=stream)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    assert capi.device_status() == 0, "a device-side wait gave up during warm-up"
+    assert all(torch.isfinite(m[2]).all() for m in layers[0])
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = capi.launch_count()
+    stream_kernels0 = capi.family_count(capi.FAMILY_GEMV_STREAM)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step()
+    ev1.record(stream)
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = capi.launch_count() - launches0
+    stream_kernels = capi.family_count(capi.FAMILY_GEMV_STREAM) - stream_kernels0
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the host-buffer boundary (CudaBackend) ----
+    be = capi.Backend(local)
+    x_host = torch.randn(sum(k for _, k in LAYER_SHAPES) * N_LAYERS, generator=torch.Generator().manual_seed(7)).pin_memory()
+    y_host = torch.empty(sum(n for n, _ in LAYER_SHAPES) * N_LAYERS).pin_memory()
+    d_x = be.alloc(x_host.numel() * 4)
+    d_y = be.alloc(y_host.numel() * 4)
+
+    def e2e_step():
+        be.upload(d_x, x_host.data_ptr(), x_host.numel() * 4)
+        xo = yo = 0
+        for mats in layers:
+            for w, _, _, n_out, n_in in mats:
+                be.gemm(d_y + 4 * yo, d_x + 4 * xo, w.data_ptr(), WT, n_out, n_in, 1)
+                xo += n_in
+                yo += n_out
+        be.download(y_host.data_ptr(), d_y, y_host.numel() * 4)      # synchronises
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(torch.cuda.default_stream())
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record(torch.cuda.default_stream())
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    assert torch.isfinite(y_host).all()
+    be.release(d_x)
+    be.release(d_y)
+    be.close()
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+
+    if rank == 0:
+        wbytes = layer_weight_bytes() * N_LAYERS
+        abytes = layer_algorithmic_bytes() * N_LAYERS
+        per_step_ms = ms / args.steps
+        value = wbytes * world / (per_step_ms * 1e-3) / 1e9
+        peak, peak_kind = measured_peaks()
+        n_launch = 4 * N_LAYERS
+        achieved = abytes / (per_step_ms * 1e-3) / 1e9          # = (bytes per launch) / (avg launch duration)
+        line = {
+            "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(per_step_ms, 5), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "s8 quants x 24-bit fixed-point activations, f32 scales",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "weight_type": "Q4_K", "batch": 1, "layers": N_LAYERS,
+                       "matmuls_per_layer": [list(s) for s in LAYER_SHAPES],
+                       "weight_bytes_per_step": wbytes, "parallelism": f"replicas x{world}",
+                       "l2": "inputs larger than L2: 2.74 GB of distinct weights per step, each byte read once"},
+            "e2e": {"value": round(wbytes * world / (e2e_ms / args.steps * 1e-3) / 1e9, 2), "unit": UNIT,
+                    "h2d_bytes_per_step": x_host.numel() * 4, "d2h_bytes_per_step": y_host.numel() * 4,
+                    "ms_per_step": round(e2e_ms / args.steps, 5)},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "kernel": "gemv_stream_kernel<Q4_K,1>", "achieved": round(achieved, 2),
+                         "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                         "launches_per_step": n_launch, "avg_launch_us": round(per_step_ms * 1e3 / n_launch, 3),
+                         "algorithmic_bytes_per_launch": abytes // n_launch, "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+                         "stream_kernel_launches": int(stream_kernels)},
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(sample_seconds=args.cpu_seconds)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the streaming kernel, from the ncu
+# capture summarised under profiles/ (None until a capture exists).
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+# ---- CPU arms ---------------------------------------------------------------------------------------
+
+def cpu_engine(threads: int):
+    """Kraken's CPU backend: the compiled reference when oracle/_ref travelled with the tree,
+    else the in-repo restatement of its scalar path."""
+    from oracle.krk_oracle import Oracle, Reference
+    if Reference.available():
+        try:
+            return Reference(threads=threads)
+        except OSError:
+            pass
+    return Oracle()
+
+
+def cpu_layer(seed_off: int = 0):
+    seed = synth.BASE_SEED + 2
+    mats = []
+    for i, (n_out, n_in) in enumerate(LAYER_SHAPES):
+        w = synth.weights(WT, n_out, n_in, seed, stream=100 + i + 10 * seed_off)
+        x = synth.activations(1, n_in, seed, stream=200 + i)
+        mats.append((w, x, n_out, n_in))
+    return mats
+
+
+def time_cpu(eng, mats, tier: int, threads: int, budget_s: float):
+    def one_pass():
+        for w, x, n_out, n_in in mats:
+            if eng.kind == "reference":
+                eng.gemm(x, w, WT, n_out, n_in, rows=1, tier=tier)
+            else:
+                eng.gemm(x, w, WT, n_out, n_in, rows=1, threads=threads)
+    one_pass()                                   # warm-up
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        one_pass()
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s or n >= 2000:
+            break
+    return layer_weight_bytes() * n / dt / 1e9, n, dt
+
+
+def cpu_baseline(sample_seconds: float = 10.0):
+    threads = os.cpu_count() or 1
+    eng = cpu_engine(threads)
+    mats = cpu_layer()
+    out = {"unit": UNIT, "cores": threads, "kind": eng.kind}
+    if eng.kind == "reference":
+        v1, n1, t1 = time_cpu(eng, mats, 1, threads, sample_seconds * 0.5)
+        v0, n0, t0 = time_cpu(eng, mats, 0, threads, sample_seconds * 0.5)
+        out.update(value=round(v1, 3), tier="reference default (int8-activation AVX2 tier, lossy)",
+                   exact_scalar_value=round(v0, 3),
+                   sample=f"one layer (4 matmuls, {layer_weight_bytes()} weight bytes) repeated {n1}x default tier "
+                          f"in {t1:.1f}s and {n0}x exact scalar tier in {t0:.1f}s, KRK_THREADS={threads}")
+    else:
+        v0, n0, t0 = time_cpu(eng, mats, 0, threads, sample_seconds)
+        out.update(value=round(v0, 3), tier="exact scalar f32 chain (restatement)",
+                   sample=f"one layer (4 matmuls, {layer_weight_bytes()} weight bytes) repeated {n0}x in {t0:.1f}s, "
+                          f"{threads} threads")
+    return out
+
+
+def run_reference(args):
+    """The reference's own CPU implementation of the path on this box's host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    eng = cpu_engine(threads)
+    mats = cpu_layer()
+    tier = 1 if eng.kind == "reference" else 0
+    # a step = a bounded sample of the workload: one layer's four matmuls
+    for _ in range(max(args.warmup, 1)):
+        time_cpu(eng, mats, tier, threads, 0.0)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for w, x, n_out, n_in in mats:
+            if eng.kind == "reference":
+                eng.gemm(x, w, WT, n_out, n_in, rows=1, tier=tier)
+            else:
+                eng.gemm(x, w, WT, n_out, n_in, rows=1, threads=threads)
+    dt = time.perf_counter() - t0
+    value = layer_weight_bytes() * args.steps / dt / 1e9
+    sample = (f"each step = one layer of the workload (4 matmuls, {layer_weight_bytes()} weight bytes), "
+              f"{'KRK_THREADS' if eng.kind == 'reference' else 'threads'}={threads}")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT,
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": max(args.warmup, 1),
+        "ms_per_step": round(dt / args.steps * 1e3, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 (int8-activation tier)" if tier == 1 else "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "weight_type": "Q4_K", "batch": 1, "layers": N_LAYERS,
+                   "matmuls_per_layer": [list(s) for s in LAYER_SHAPES], "sample": sample},
+        "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": threads, "kind": eng.kind, "sample": sample,
+                         "tier": "reference default (int8-activation AVX2 tier)" if tier == 1 else "exact scalar"},
+        "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -163,6 +163,13 @@ int krk_cuda_device_status(void);
 /* Kernels launched by this library since the process started (all threads). */
 int64_t krk_cuda_launch_count(void);
 
+/* The same count for one kernel family, so that a caller (or a test) can tell which path
+ * served a shape: the streaming GEMV, the shape-agnostic GEMV, or the tensor-core GEMM. */
+#define KRK_CUDA_FAMILY_GEMV_STREAM 1
+#define KRK_CUDA_FAMILY_GEMV_GENERIC 2
+#define KRK_CUDA_FAMILY_GEMM_TC 3
+int64_t krk_cuda_family_count(int family);
+
 /* ---- host-buffer plumbing: the CudaBackend class of krk_cuda_backend.hpp behind a C face ----
  * These are the calls a host that is not C++ binds. `be` is the object returned by
  * krk_cuda_backend_make (make_hip_backend's contract, include/krk/backend.hpp:1886: NULL and a

@@ -63,6 +63,7 @@ SIGNATURES = {
     "krk_cuda_sum_parts": (_int, [_vp, _vp, _int, _i64, _vp]),
     "krk_cuda_device_status": (_int, []),
     "krk_cuda_launch_count": (_i64, []),
+    "krk_cuda_family_count": (_i64, [_int]),
     "krk_cuda_backend_make": (_vp, [_int, C.c_char_p, _sz]),
     "krk_cuda_backend_free": (None, [_vp]),
     "krk_cuda_backend_describe": (C.c_char_p, [_vp]),
@@ -179,9 +180,11 @@ def route(logits, k: int, stream=None):
 
 def make_bank(gate, up, down, wt_gate_up: int, wt_down: int, n_local: int, expert_base: int, n_embd: int,
               n_ff: int) -> ExpertBank:
-    return ExpertBank(gate.data_ptr() if gate is not None else 0, up.data_ptr() if up is not None else 0,
+    bank = ExpertBank(gate.data_ptr() if gate is not None else 0, up.data_ptr() if up is not None else 0,
                       down.data_ptr() if down is not None else 0, wt_gate_up, wt_down, n_local, expert_base,
                       n_embd, n_ff)
+    bank._keep = (gate, up, down)   # the struct holds raw pointers: keep the tensors alive with it
+    return bank
 
 
 def moe_ffn(x, ids, wts, bank: ExpertBank, out=None, workspace=None, stream=None):
@@ -227,6 +230,13 @@ def device_status() -> int:
 
 def launch_count() -> int:
     return lib.krk_cuda_launch_count()
+
+
+FAMILY_GEMV_STREAM, FAMILY_GEMV_GENERIC, FAMILY_GEMM_TC = 1, 2, 3
+
+
+def family_count(family: int) -> int:
+    return lib.krk_cuda_family_count(family)
 
 
 # ---- host-buffer plumbing: the CudaBackend object ---------------------------------------------

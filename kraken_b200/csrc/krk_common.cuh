@@ -13,7 +13,7 @@ namespace krk_cuda {
 // ---- host-side plumbing ------------------------------------------------------------
 
 void note_cuda_error(cudaError_t e);   // remembers the text for krk_cuda_last_cuda_error()
-void note_launch(int n = 1);           // counts kernels for krk_cuda_launch_count()
+void note_launch(int n = 1, int family = 0);   // counts kernels for krk_cuda_launch_count() / _family_count()
 int *device_status_word();             // per-device int in global memory, 0 unless a wait gave up
 int sm_count();                        // multiprocessors of the current device
 

@@ -11,6 +11,7 @@ namespace krk_cuda {
 namespace {
 thread_local char g_cuda_err[256] = "";
 std::atomic<int64_t> g_launches{0};
+std::atomic<int64_t> g_family[4];
 
 struct DeviceState {
     int *status = nullptr;
@@ -44,7 +45,10 @@ void note_cuda_error(cudaError_t e) {
     std::strncpy(g_cuda_err, cudaGetErrorString(e), sizeof(g_cuda_err) - 1);
     g_cuda_err[sizeof(g_cuda_err) - 1] = 0;
 }
-void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+void note_launch(int n, int family) {
+    g_launches.fetch_add(n, std::memory_order_relaxed);
+    if (family > 0 && family < 4) g_family[family].fetch_add(n, std::memory_order_relaxed);
+}
 int *device_status_word() {
     DeviceState *s = device_state();
     return s ? s->status : nullptr;
@@ -263,5 +267,8 @@ int krk_cuda_device_status(void) {
 }
 
 int64_t krk_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+int64_t krk_cuda_family_count(int family) {
+    return (family > 0 && family < 4) ? g_family[family].load(std::memory_order_relaxed) : 0;
+}
 
 } // extern "C"

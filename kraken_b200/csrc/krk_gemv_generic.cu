@@ -101,7 +101,7 @@ int launch_gemv_generic(const GemvMat *mats, int n_mat, int64_t n_in, int rows, 
             } else {
                 KRK_DISPATCH_WT(wt, gemv_generic_kernel<WT, 8><<<blocks, kWarpsPerBlock * 32, 0, st>>>(p));
             }
-            note_launch();
+            note_launch(1, KRK_CUDA_FAMILY_GEMV_GENERIC);
             const int rc = check_launch();
             if (rc != KRK_CUDA_OK) return rc;
         }

@@ -1,5 +1,745 @@
-// placeholder until the streaming kernel lands
+// Streaming decode GEMV for sm_100a: Q4_K, Q6_K and Q8_0 weights, 1..8 activation rows, up to
+// 16 matrices per launch.
+//
+// Design (B200-first, not the reference's one-warp-per-row walk of src/hip/kernels/gemm.hpp:76):
+//
+//  * One persistent CTA per SM owns a contiguous range of output rows. A producer warp streams
+//    that range through a ring of shared-memory stages with bulk-async copies (cp.async.bulk,
+//    one copy per weight row so that rows land on a padded, bank-conflict-free stride) signalled
+//    on mbarriers; 16 consumer warps never touch global memory for weights. The ring keeps
+//    50-150 KB of HBM reads in flight per SM without spending registers on it.
+//
+//  * At 8 TB/s a B200 SM must retire ~40 four-bit weights per clock: unpacking each one to f32
+//    and issuing an FMA for it does not fit the issue budget. So the dot products run on the
+//    tensor cores as EXACT integer arithmetic: the quants are fed as s8 fragments straight from
+//    the packed bytes (one AND per four nibbles) to mma.sync m16n8k32 / m16n8k16 (s8 x s8 -> s32),
+//    16 output rows at a time, and the activation is held as three signed 8-bit limbs of a
+//    24-bit fixed-point number (x ~ s * (l0*65536 + l1*256 + l2)), one limb per MMA column.
+//    The products and sums are exact; the only rounding is the 24-bit quantisation of x
+//    (relative to max|x|, i.e. f32-mantissa sized) and the final f32 scale arithmetic, so the
+//    result sits well inside the 1e-4 * ||w_row|| * ||x|| bound. Sub-block scales are applied
+//    to the s32 partial sums in integer arithmetic, block scales in f32.
+//
+//  * Because a dot product does not care about the order of its terms, each lane takes the
+//    bytes that are cheapest to load and the activation limbs are laid out in the matching
+//    order once per CTA.
+//
+// Every wait on an mbarrier is bounded; a wait that gives up raises the device status word
+// and the CTA drains without touching memory it does not own.
+#include <cfloat>
+
 #include "krk_common.cuh"
+
 namespace krk_cuda {
-int launch_gemv_stream(const GemvMat *, int, int64_t, int, int, int, cudaStream_t) { return 0; }
+
+namespace {
+
+constexpr int kConsumerWarps = 16;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;   // + the producer warp
+constexpr int kTileRows = 16;                     // the M of the MMA
+constexpr int kMaxStages = 8;
+constexpr int kSmemLimit = 227 * 1024;
+constexpr float kFixedOne = 8323072.0f;           // 127 * 65536: |X| <= this keeps every limb in s8
+constexpr long long kWaitCycles = 4000000000LL;   // ~2 s at boost clock, then give up
+
+template <int WT> struct Fmt;
+template <> struct Fmt<KRK_CUDA_Q4_K> { static constexpr int unit_values = 256, unit_bytes = 144, stride_mod = 32; };
+template <> struct Fmt<KRK_CUDA_Q6_K> { static constexpr int unit_values = 256, unit_bytes = 210, stride_mod = 16; };
+template <> struct Fmt<KRK_CUDA_Q8_0> { static constexpr int unit_values = 128, unit_bytes = 136, stride_mod = 16; };
+
+struct StreamParams {
+    GemvMat mat[KRK_CUDA_MAX_GROUP];
+    int gran_begin[KRK_CUDA_MAX_GROUP + 1];   // first row granule of each entry
+    int n_entries;        // matrices, or gate/up pairs when silu_pair
+    int step;             // matrices per entry (2 for gate/up pairs)
+    int rows;             // activation rows
+    int accumulate;
+    int n_in;
+    int units;            // n_in / unit_values
+    int row_bytes;
+    int gran;             // rows per granule: 1, or 8 when rows are not 16-byte multiples
+    int whole_tiles;      // 1: a stage is one contiguous copy of whole rows (unaligned row size)
+    int row_stride;       // bytes between rows inside a stage
+    int stage_bytes;
+    int n_stages;
+    int total_gran;
+    int *status;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void consumer_barrier() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
+__device__ __forceinline__ void mma_s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                           uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0));
+}
+__device__ __forceinline__ int sext_byte(uint32_t w, int i) {
+    int r;
+    asm("bfe.s32 %0, %1, %2, 8;" : "=r"(r) : "r"(w), "r"(8 * i));
+    return r;
+}
+__device__ __forceinline__ float half_lo(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xFFFFu))); }
+__device__ __forceinline__ float half_hi(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
+
+// Bounded wait on an mbarrier phase. Once any wait in the CTA has given up, every later wait
+// returns at once, so the CTA runs to its end (on stale data, inside its own buffers) instead
+// of hanging.
+__device__ __forceinline__ void wait_phase(uint32_t bar, uint32_t parity, volatile int *gave_up, int *status) {
+    if (*gave_up) return;
+    if (mbar_try_wait(bar, parity)) return;
+    const long long t0 = clock64();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return;
+        if (*gave_up) return;
+        if (clock64() - t0 > kWaitCycles) {
+            *gave_up = 1;
+            atomicExch(status, KRK_CUDA_ETIMEOUT);
+            return;
+        }
+    }
+}
+
+// ---- shared-memory map ---------------------------------------------------------------------------
+
+struct Smem {
+    unsigned long long full[kMaxStages];
+    unsigned long long empty[kMaxStages];
+    int gave_up;
+    int pad[3];
+    float xscale[KRK_CUDA_MAX_ROWS];                  // s_r: x ~ s_r * X, X 24-bit signed
+    float warp_max[kConsumerWarps];
+    int warp_bad[kConsumerWarps];
+    float red[2][kConsumerWarps][kTileRows][KRK_CUDA_MAX_ROWS];
+    float gate[kTileRows * KRK_CUDA_MAX_ROWS];       // gate tile kept for the silu fold
+};
+
+__host__ __device__ constexpr int align_up(int v, int a) { return (v + a - 1) / a * a; }
+
+template <int WT>
+__host__ __device__ inline int plane_bytes(int n_in, int rows) { return align_up(rows * 3 * n_in, 128); }
+template <int WT>
+__host__ __device__ inline int chunk_sum_bytes(int n_in, int rows) {
+    return WT == KRK_CUDA_Q4_K ? align_up(rows * (n_in / 32) * 4, 128) : 0;
+}
+
+// ---- the walk over this CTA's stages: identical in the producer and in the consumers -------------
+
+struct StageInfo {
+    int mat;        // matrix index
+    int which;      // 0, or 1 for the `up` half of a gate/up pair
+    int row0;       // first output row of the tile
+    int n_rows;     // valid rows in the tile (1..16)
+    int unit0;      // first K unit of this stage
+    int n_units;    // units in this stage (1..16)
+    int last;       // last stage of the tile
+    int it;         // running stage number of this CTA
+};
+
+template <class SegmentFn, class StageFn>
+__device__ __forceinline__ void walk(const StreamParams &p, SegmentFn &&on_segment, StageFn &&on_stage) {
+    const int g0 = (int)((long long)blockIdx.x * p.total_gran / gridDim.x);
+    const int g1 = (int)((long long)(blockIdx.x + 1) * p.total_gran / gridDim.x);
+    const int ku_max = p.whole_tiles ? p.units : kConsumerWarps;
+    int it = 0;
+    for (int e = 0; e < p.n_entries; e++) {
+        const int lo = max(g0, p.gran_begin[e]), hi = min(g1, p.gran_begin[e + 1]);
+        if (lo >= hi) continue;
+        const int n_out = (int)p.mat[e * p.step].n_out;
+        const int r0 = (lo - p.gran_begin[e]) * p.gran;
+        const int r1 = min(n_out, (hi - p.gran_begin[e]) * p.gran);
+        on_segment(e * p.step);
+        for (int tr = r0; tr < r1; tr += kTileRows) {
+            for (int which = 0; which < p.step; which++) {
+                for (int u0 = 0; u0 < p.units; u0 += ku_max) {
+                    StageInfo s;
+                    s.mat = e * p.step + which;
+                    s.which = which;
+                    s.row0 = tr;
+                    s.n_rows = min(kTileRows, r1 - tr);
+                    s.unit0 = u0;
+                    s.n_units = min(ku_max, p.units - u0);
+                    s.last = u0 + ku_max >= p.units;
+                    s.it = it++;
+                    on_stage(s);
+                }
+            }
+        }
+    }
+}
+
+// ---- activation preparation -------------------------------------------------------------------------
+// For every activation row: s = max|x| / 127*2^16, X = rint(x / s) as three balanced s8 limbs
+// stored as byte planes [row][limb][k] in the order the consumers' B fragments want them, plus
+// (Q4_K) the f32 sum of x over every 32-value chunk for the `min` term.
+
+template <int WT>
+__device__ __forceinline__ void prepare_x(const float *__restrict__ x, int rows, int n_in, Smem *sm,
+                                          int8_t *planes, float *chunk_sum, int ctid) {
+    const int wid = ctid >> 5, lane = ctid & 31;
+    for (int r = 0; r < rows; r++) {
+        const float *xr = x + (size_t)r * n_in;
+        float mx = 0.0f;
+        int bad = 0;
+        for (int i = ctid * 4; i < n_in; i += kConsumerThreads * 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(xr + i);
+            const float a = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+            mx = fmaxf(mx, a);
+            bad |= !(fabsf(v.x) <= FLT_MAX) | !(fabsf(v.y) <= FLT_MAX) | !(fabsf(v.z) <= FLT_MAX) | !(fabsf(v.w) <= FLT_MAX);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+            bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, o);
+        }
+        if (lane == 0) {
+            sm->warp_max[wid] = mx;
+            sm->warp_bad[wid] = bad;
+        }
+        consumer_barrier();
+        for (int w = 0; w < kConsumerWarps; w++) {
+            mx = fmaxf(mx, sm->warp_max[w]);
+            bad |= sm->warp_bad[w];
+        }
+        const float inv = (mx > 0.0f && !bad) ? __fdiv_rn(kFixedOne, mx) : 0.0f;
+        if (ctid == 0) sm->xscale[r] = bad ? __int_as_float(0x7FC00000) : __fdiv_rn(mx, kFixedOne);
+        int8_t *p0 = planes + (size_t)(r * 3 + 0) * n_in;
+        int8_t *p1 = planes + (size_t)(r * 3 + 1) * n_in;
+        int8_t *p2 = planes + (size_t)(r * 3 + 2) * n_in;
+        for (int i = ctid * 4; i < n_in; i += kConsumerThreads * 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(xr + i);
+            const float f[4] = {v.x, v.y, v.z, v.w};
+            uint32_t w0 = 0, w1 = 0, w2 = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int X = __float2int_rn(f[j] * inv);
+                const int l2 = (X << 24) >> 24;
+                const int X1 = (X - l2) >> 8;
+                const int l1 = (X1 << 24) >> 24;
+                const int l0 = (X1 - l1) >> 8;
+                w0 |= (uint32_t)(l0 & 0xFF) << (8 * j);
+                w1 |= (uint32_t)(l1 & 0xFF) << (8 * j);
+                w2 |= (uint32_t)(l2 & 0xFF) << (8 * j);
+            }
+            if (WT == KRK_CUDA_Q8_0 && ((i >> 5) & 1) == 0) {
+                // Even blocks start 2 bytes off a word boundary, so their lanes take the quants in the
+                // order [0,1,30,31, 2..29]; the limbs follow: pair (e, e+1) lands at position pos(e).
+                const int e = i & 31, base = i & ~31;
+                const int k0 = e < 2 ? e : (e >= 30 ? e - 28 : e + 2);
+                const int e2 = e + 2;
+                const int k1 = e2 < 2 ? e2 : (e2 >= 30 ? e2 - 28 : e2 + 2);
+                *reinterpret_cast<uint16_t *>(p0 + base + k0) = (uint16_t)(w0 & 0xFFFF);
+                *reinterpret_cast<uint16_t *>(p0 + base + k1) = (uint16_t)(w0 >> 16);
+                *reinterpret_cast<uint16_t *>(p1 + base + k0) = (uint16_t)(w1 & 0xFFFF);
+                *reinterpret_cast<uint16_t *>(p1 + base + k1) = (uint16_t)(w1 >> 16);
+                *reinterpret_cast<uint16_t *>(p2 + base + k0) = (uint16_t)(w2 & 0xFFFF);
+                *reinterpret_cast<uint16_t *>(p2 + base + k1) = (uint16_t)(w2 >> 16);
+            } else {
+                *reinterpret_cast<uint32_t *>(p0 + i) = w0;
+                *reinterpret_cast<uint32_t *>(p1 + i) = w1;
+                *reinterpret_cast<uint32_t *>(p2 + i) = w2;
+            }
+            if (WT == KRK_CUDA_Q4_K) {
+                float s = (v.x + v.y) + (v.z + v.w);
+                s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+                s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+                s += __shfl_xor_sync(0xFFFFFFFFu, s, 4);
+                if ((lane & 7) == 0) chunk_sum[(size_t)r * (n_in >> 5) + (i >> 5)] = s;
+            }
+        }
+        consumer_barrier();
+    }
+}
+
+// ---- per-format unit kernels -------------------------------------------------------------------------
+// A unit is 256 values (128 for Q8_0) of 16 weight rows: lane (g, t) = (lane/4, lane%4) holds the
+// A fragments of rows g and g+8, column g of the B fragment (limb g%3 of activation row g/3 of
+// the column group), and accumulator columns 2t, 2t+1.
+
+template <int NG>
+struct Accum {
+    float f[NG][4];        // [group][(row g | g+8) x (col 2t | 2t+1)], already times the block scale
+    float m[2][2 * NG];    // Q4_K: dmin * sum(min_c * sum_x_c), per (row half, activation row)
+};
+
+template <int NG>
+__device__ __forceinline__ void accum_zero(Accum<NG> &a) {
+#pragma unroll
+    for (int i = 0; i < NG; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) a.f[i][j] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 2 * NG; j++) a.m[i][j] = 0.0f;
+}
+
+// Byte planes this lane reads its B fragments from: one pointer per column group, or null when
+// the lane's column carries no limb (columns 6, 7, or an activation row past `rows`).
+template <int NG>
+__device__ __forceinline__ void lane_planes(const int8_t *planes, int n_in, int rows, int g, const int8_t *(&bp)[NG]) {
+#pragma unroll
+    for (int mg = 0; mg < NG; mg++) {
+        const int r = 2 * mg + g / 3;
+        bp[mg] = (g < 6 && r < rows) ? planes + (size_t)(r * 3 + g % 3) * n_in : nullptr;
+    }
+}
+
+template <int NG>
+__device__ __forceinline__ void unit_q4_k(const uint8_t *rowA, const uint8_t *rowB, int kbase, const int8_t *const (&bp)[NG],
+                                          const float *chunk_sum, int n_in, int rows, int t, Accum<NG> &acc) {
+    const uint4 hA = *reinterpret_cast<const uint4 *>(rowA);
+    const uint4 hB = *reinterpret_cast<const uint4 *>(rowB);
+    // 6-bit scales and mins of the 8 chunks, four per word (src/quant.cpp:427-435 done bytewise)
+    const uint32_t scA[2] = {hA.y & 0x3F3F3F3Fu, (hA.w & 0x0F0F0F0Fu) | ((hA.y >> 2) & 0x30303030u)};
+    const uint32_t scB[2] = {hB.y & 0x3F3F3F3Fu, (hB.w & 0x0F0F0F0Fu) | ((hB.y >> 2) & 0x30303030u)};
+    const uint32_t mnA[2] = {hA.z & 0x3F3F3F3Fu, ((hA.w >> 4) & 0x0F0F0F0Fu) | ((hA.z >> 2) & 0x30303030u)};
+    const uint32_t mnB[2] = {hB.z & 0x3F3F3F3Fu, ((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u)};
+    int I[NG][4];
+#pragma unroll
+    for (int mg = 0; mg < NG; mg++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) I[mg][j] = 0;
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+        const uint2 qa = *reinterpret_cast<const uint2 *>(rowA + 16 + 32 * p + 8 * t);
+        const uint2 qb = *reinterpret_cast<const uint2 *>(rowB + 16 + 32 * p + 8 * t);
+#pragma unroll
+        for (int nib = 0; nib < 2; nib++) {
+            const int c = 2 * p + nib;
+            const uint32_t a0 = (qa.x >> (4 * nib)) & 0x0F0F0F0Fu, a1 = (qb.x >> (4 * nib)) & 0x0F0F0F0Fu;
+            const uint32_t a2 = (qa.y >> (4 * nib)) & 0x0F0F0F0Fu, a3 = (qb.y >> (4 * nib)) & 0x0F0F0F0Fu;
+            const int sa = (scA[c >> 2] >> (8 * (c & 3))) & 0xFF, sb = (scB[c >> 2] >> (8 * (c & 3))) & 0xFF;
+#pragma unroll
+            for (int mg = 0; mg < NG; mg++) {
+                uint2 b = make_uint2(0u, 0u);
+                if (bp[mg]) b = *reinterpret_cast<const uint2 *>(bp[mg] + kbase + 32 * c + 8 * t);
+                int cc[4] = {0, 0, 0, 0};
+                mma_s8_k32(cc, a0, a1, a2, a3, b.x, b.y);
+                I[mg][0] += sa * cc[0];
+                I[mg][1] += sa * cc[1];
+                I[mg][2] += sb * cc[2];
+                I[mg][3] += sb * cc[3];
+            }
+        }
+    }
+    const float dA = half_lo(hA.x), dB = half_lo(hB.x);
+#pragma unroll
+    for (int mg = 0; mg < NG; mg++) {
+        acc.f[mg][0] = fmaf(dA, (float)I[mg][0], acc.f[mg][0]);
+        acc.f[mg][1] = fmaf(dA, (float)I[mg][1], acc.f[mg][1]);
+        acc.f[mg][2] = fmaf(dB, (float)I[mg][2], acc.f[mg][2]);
+        acc.f[mg][3] = fmaf(dB, (float)I[mg][3], acc.f[mg][3]);
+    }
+    // min term: lane t covers chunks 2t and 2t+1 of the super-block
+    const float nA = half_hi(hA.x), nB = half_hi(hB.x);
+    const int sh = 16 * (t & 1);
+    const float mA0 = (float)((mnA[t >> 1] >> sh) & 0xFF), mA1 = (float)((mnA[t >> 1] >> (sh + 8)) & 0xFF);
+    const float mB0 = (float)((mnB[t >> 1] >> sh) & 0xFF), mB1 = (float)((mnB[t >> 1] >> (sh + 8)) & 0xFF);
+#pragma unroll
+    for (int r = 0; r < 2 * NG; r++) {
+        if (r < rows) {
+            const float2 sx = *reinterpret_cast<const float2 *>(chunk_sum + (size_t)r * (n_in >> 5) + (kbase >> 5) + 2 * t);
+            acc.m[0][r] = fmaf(nA, fmaf(mA0, sx.x, mA1 * sx.y), acc.m[0][r]);
+            acc.m[1][r] = fmaf(nB, fmaf(mB0, sx.x, mB1 * sx.y), acc.m[1][r]);
+        }
+    }
+}
+
+// Four Q8_0 blocks. A block is a 2-byte scale then 32 quants, so blocks at an even index have
+// their quants 2 bytes off a word boundary: their lanes read the aligned words and lane t = 0
+// glues the two half words at the ends into one (the activation limbs are permuted to match).
+template <int NG>
+__device__ __forceinline__ void unit_q8_0(const uint8_t *rowA, const uint8_t *rowB, int kbase, const int8_t *const (&bp)[NG],
+                                          int t, Accum<NG> &acc) {
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+        uint32_t a0, a1, a2, a3;
+        float dA, dB;
+        if ((b & 1) == 0) {
+            const uint32_t *wa = reinterpret_cast<const uint32_t *>(rowA + 34 * b);
+            const uint32_t *wb = reinterpret_cast<const uint32_t *>(rowB + 34 * b);
+            const uint32_t a_first = wa[0], b_first = wb[0];
+            a0 = t == 0 ? __byte_perm(a_first, wa[8], 0x5432) : wa[t];
+            a1 = t == 0 ? __byte_perm(b_first, wb[8], 0x5432) : wb[t];
+            a2 = wa[t + 4];
+            a3 = wb[t + 4];
+            dA = half_lo(a_first);
+            dB = half_lo(b_first);
+        } else {
+            const uint32_t *wa = reinterpret_cast<const uint32_t *>(rowA + 34 * b + 2);
+            const uint32_t *wb = reinterpret_cast<const uint32_t *>(rowB + 34 * b + 2);
+            a0 = wa[t];
+            a1 = wb[t];
+            a2 = wa[t + 4];
+            a3 = wb[t + 4];
+            dA = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(rowA + 34 * b)));
+            dB = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(rowB + 34 * b)));
+        }
+#pragma unroll
+        for (int mg = 0; mg < NG; mg++) {
+            uint32_t b0 = 0u, b1 = 0u;
+            if (bp[mg]) {
+                b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 4 * t);
+                b1 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 16 + 4 * t);
+            }
+            int cc[4] = {0, 0, 0, 0};
+            mma_s8_k32(cc, a0, a1, a2, a3, b0, b1);
+            acc.f[mg][0] = fmaf(dA, (float)cc[0], acc.f[mg][0]);
+            acc.f[mg][1] = fmaf(dA, (float)cc[1], acc.f[mg][1]);
+            acc.f[mg][2] = fmaf(dB, (float)cc[2], acc.f[mg][2]);
+            acc.f[mg][3] = fmaf(dB, (float)cc[3], acc.f[mg][3]);
+        }
+    }
+}
+
+// 32-bit load at a 4-byte-multiple offset of a Q6_K block that itself starts 0 or 2 bytes off
+// a word boundary (blocks are 210 bytes, so odd blocks of a row are misaligned).
+template <bool ODD>
+__device__ __forceinline__ uint32_t ld_q6(const uint8_t *blk, int off) {
+    if (ODD) {
+        const uint32_t lo = *reinterpret_cast<const uint32_t *>(blk + off - 2);
+        const uint32_t hi = *reinterpret_cast<const uint32_t *>(blk + off + 2);
+        return __byte_perm(lo, hi, 0x5432);
+    }
+    return *reinterpret_cast<const uint32_t *>(blk + off);
+}
+
+// q - 32 for four packed 6-bit values: add 0x60 (no carry: q <= 63), flip the sign bit.
+__device__ __forceinline__ uint32_t center_q6(uint32_t q) { return (q + 0x60606060u) ^ 0x80808080u; }
+
+template <int NG, bool ODD>
+__device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *blkB, int kbase, const int8_t *const (&bp)[NG],
+                                          int t, Accum<NG> &acc) {
+    int I[NG][4];
+#pragma unroll
+    for (int mg = 0; mg < NG; mg++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) I[mg][j] = 0;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        uint32_t qlA[4], qlB[4], qhA[2], qhB[2], scA[2], scB[2];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            qlA[i] = ld_q6<ODD>(blkA, 64 * h + 16 * i + 4 * t);
+            qlB[i] = ld_q6<ODD>(blkB, 64 * h + 16 * i + 4 * t);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            qhA[i] = ld_q6<ODD>(blkA, 128 + 32 * h + 16 * i + 4 * t);
+            qhB[i] = ld_q6<ODD>(blkB, 128 + 32 * h + 16 * i + 4 * t);
+            scA[i] = ld_q6<ODD>(blkA, 192 + 8 * h + 4 * i);
+            scB[i] = ld_q6<ODD>(blkB, 192 + 8 * h + 4 * i);
+        }
+        // group G = 2*quad + s covers values 16G..16G+15 of the half (src/quant.cpp:491-512):
+        // low 4 bits from ql[32*(quad&1) + 16s ...] (high nibble when quad >= 2), bits 4-5 from
+        // qh[16s ...] >> 2*quad.
+#pragma unroll
+        for (int G = 0; G < 8; G++) {
+            const int quad = G >> 1, s = G & 1;
+            const uint32_t la = qlA[2 * (quad & 1) + s], lb = qlB[2 * (quad & 1) + s];
+            const uint32_t lowA = (quad & 2) ? (la >> 4) & 0x0F0F0F0Fu : la & 0x0F0F0F0Fu;
+            const uint32_t lowB = (quad & 2) ? (lb >> 4) & 0x0F0F0F0Fu : lb & 0x0F0F0F0Fu;
+            const uint32_t hiA = quad == 0 ? (qhA[s] << 4) : quad == 1 ? (qhA[s] << 2) : quad == 2 ? qhA[s] : (qhA[s] >> 2);
+            const uint32_t hiB = quad == 0 ? (qhB[s] << 4) : quad == 1 ? (qhB[s] << 2) : quad == 2 ? qhB[s] : (qhB[s] >> 2);
+            const uint32_t a0 = center_q6(lowA | (hiA & 0x30303030u));
+            const uint32_t a1 = center_q6(lowB | (hiB & 0x30303030u));
+            const int sa = sext_byte(scA[G >> 2], G & 3), sb = sext_byte(scB[G >> 2], G & 3);
+#pragma unroll
+            for (int mg = 0; mg < NG; mg++) {
+                uint32_t b0 = 0u;
+                if (bp[mg]) b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 128 * h + 16 * G + 4 * t);
+                int cc[4] = {0, 0, 0, 0};
+                mma_s8_k16(cc, a0, a1, b0);
+                I[mg][0] += sa * cc[0];
+                I[mg][1] += sa * cc[1];
+                I[mg][2] += sb * cc[2];
+                I[mg][3] += sb * cc[3];
+            }
+        }
+    }
+    const float dA = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blkA + 208)));
+    const float dB = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blkB + 208)));
+#pragma unroll
+    for (int mg = 0; mg < NG; mg++) {
+        acc.f[mg][0] = fmaf(dA, (float)I[mg][0], acc.f[mg][0]);
+        acc.f[mg][1] = fmaf(dA, (float)I[mg][1], acc.f[mg][1]);
+        acc.f[mg][2] = fmaf(dB, (float)I[mg][2], acc.f[mg][2]);
+        acc.f[mg][3] = fmaf(dB, (float)I[mg][3], acc.f[mg][3]);
+    }
+}
+
+// ---- the kernel ------------------------------------------------------------------------------------------
+
+template <int WT, int NG>
+__global__ void __launch_bounds__(kThreads, 1)
+gemv_stream_kernel(const __grid_constant__ StreamParams p) {
+    using F = Fmt<WT>;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    Smem *sm = reinterpret_cast<Smem *>(smem_raw);
+    int8_t *planes = reinterpret_cast<int8_t *>(smem_raw + align_up((int)sizeof(Smem), 128));
+    float *chunk_sum = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(planes) + plane_bytes<WT>(p.n_in, p.rows));
+    uint8_t *stages = reinterpret_cast<uint8_t *>(chunk_sum) + chunk_sum_bytes<WT>(p.n_in, p.rows);
+
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        for (int s = 0; s < p.n_stages; s++) {
+            mbar_init(smem_u32(&sm->full[s]), 1);
+            mbar_init(smem_u32(&sm->empty[s]), kConsumerWarps);
+        }
+        sm->gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    volatile int *gave_up = &sm->gave_up;
+
+    if (tid >= kConsumerThreads) {
+        // ===== producer warp: weights only, so it can run ahead of everything else =====
+        const int lane = tid - kConsumerThreads;
+        walk(p, [](int) {}, [&](const StageInfo &s) {
+            const int slot = s.it % p.n_stages;
+            const uint32_t full = smem_u32(&sm->full[slot]), empty = smem_u32(&sm->empty[slot]);
+            wait_phase(empty, ((s.it / p.n_stages) & 1) ^ 1, gave_up, p.status);
+            uint8_t *dst = stages + (size_t)slot * p.stage_bytes;
+            const uint8_t *src = p.mat[s.mat].w + (size_t)s.row0 * p.row_bytes;
+            if (!p.whole_tiles) {
+                const uint32_t bytes = (uint32_t)s.n_units * F::unit_bytes;
+                if (lane == 0) mbar_arrive_expect_tx(full, bytes * s.n_rows);
+                __syncwarp();
+                if (lane < s.n_rows)
+                    bulk_g2s(smem_u32(dst + lane * p.row_stride),
+                             src + (size_t)lane * p.row_bytes + (size_t)s.unit0 * F::unit_bytes, bytes, full);
+            } else if (lane == 0) {
+                // rows are not 16-byte multiples: one copy of the whole tile, rounded down to 16 bytes,
+                // and the (< 16 byte, 4-byte granular) tail with plain loads before the arrive
+                const uint32_t total = (uint32_t)s.n_rows * p.row_bytes;
+                const uint32_t bulk = total & ~15u;
+                for (uint32_t o = bulk; o < total; o += 4)
+                    *reinterpret_cast<uint32_t *>(dst + o) = *reinterpret_cast<const uint32_t *>(src + o);
+                mbar_arrive_expect_tx(full, bulk);
+                if (bulk) bulk_g2s(smem_u32(dst), src, bulk, full);
+            }
+            __syncwarp();
+        });
+        return;
+    }
+
+    // ===== consumer warps =====
+    const int wid = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const float *prepared = nullptr;
+    const int8_t *bp[NG];
+    Accum<NG> acc;
+    accum_zero(acc);
+    int tile_it = 0;
+
+    walk(p,
+         [&](int m) {
+             if (p.mat[m].x != prepared) {
+                 consumer_barrier();   // nobody still reads the previous planes
+                 prepare_x<WT>(p.mat[m].x, p.rows, p.n_in, sm, planes, chunk_sum, tid);
+                 prepared = p.mat[m].x;
+                 lane_planes<NG>(planes, p.n_in, p.rows, g, bp);
+             }
+         },
+         [&](const StageInfo &s) {
+             const int slot = s.it % p.n_stages;
+             wait_phase(smem_u32(&sm->full[slot]), (s.it / p.n_stages) & 1, gave_up, p.status);
+             if (wid < s.n_units) {
+                 const uint8_t *base = stages + (size_t)slot * p.stage_bytes + (size_t)wid * F::unit_bytes;
+                 const uint8_t *rowA = base + (size_t)g * p.row_stride, *rowB = rowA + (size_t)8 * p.row_stride;
+                 const int kbase = (s.unit0 + wid) * F::unit_values;
+                 if (WT == KRK_CUDA_Q4_K) {
+                     unit_q4_k<NG>(rowA, rowB, kbase, bp, chunk_sum, p.n_in, p.rows, t, acc);
+                 } else if (WT == KRK_CUDA_Q8_0) {
+                     unit_q8_0<NG>(rowA, rowB, kbase, bp, t, acc);
+                 } else {
+                     if ((s.unit0 + wid) & 1) unit_q6_k<NG, true>(rowA, rowB, kbase, bp, t, acc);
+                     else unit_q6_k<NG, false>(rowA, rowB, kbase, bp, t, acc);
+                 }
+             }
+             __syncwarp();
+             if (lane == 0) mbar_arrive(smem_u32(&sm->empty[slot]));
+             if (!s.last) return;
+
+             // ---- tile epilogue: limbs -> value per (row, activation row), then across warps ----
+             const int buf = tile_it & 1;
+             tile_it++;
+             const int n_warps = min(kConsumerWarps, p.units);
+             const int lane_base = lane & ~3;
+#pragma unroll
+             for (int mg = 0; mg < NG; mg++) {
+#pragma unroll
+                 for (int rh = 0; rh < 2; rh++) {
+                     const float a0 = acc.f[mg][2 * rh], a1 = acc.f[mg][2 * rh + 1];
+                     const float b0 = __shfl_sync(0xFFFFFFFFu, a0, lane_base + 1), b1 = __shfl_sync(0xFFFFFFFFu, a1, lane_base + 1);
+                     const float c0 = __shfl_sync(0xFFFFFFFFu, a0, lane_base + 2), c1 = __shfl_sync(0xFFFFFFFFu, a1, lane_base + 2);
+                     float ve = fmaf(a0, 65536.0f, fmaf(a1, 256.0f, b0));   // activation row 2*mg
+                     float vo = fmaf(b1, 65536.0f, fmaf(c0, 256.0f, c1));   // activation row 2*mg + 1
+                     float me = 0.0f, mo = 0.0f;
+                     if (WT == KRK_CUDA_Q4_K) {
+                         me = acc.m[rh][2 * mg];
+                         mo = acc.m[rh][2 * mg + 1];
+                         me += __shfl_xor_sync(0xFFFFFFFFu, me, 1);
+                         mo += __shfl_xor_sync(0xFFFFFFFFu, mo, 1);
+                         me += __shfl_xor_sync(0xFFFFFFFFu, me, 2);
+                         mo += __shfl_xor_sync(0xFFFFFFFFu, mo, 2);
+                     }
+                     if (t == 0 && wid < n_warps) {
+                         const int row = g + 8 * rh;
+                         if (2 * mg < p.rows) sm->red[buf][wid][row][2 * mg] = fmaf(ve, sm->xscale[2 * mg], -me);
+                         if (2 * mg + 1 < p.rows) sm->red[buf][wid][row][2 * mg + 1] = fmaf(vo, sm->xscale[2 * mg + 1], -mo);
+                     }
+                 }
+             }
+             accum_zero(acc);
+             consumer_barrier();
+             if (tid < kTileRows * p.rows) {
+                 const int row = tid & (kTileRows - 1), r = tid >> 4;
+                 float v = sm->red[buf][0][row][r];
+                 for (int w = 1; w < n_warps; w++) v += sm->red[buf][w][row][r];
+                 if (row < s.n_rows) {
+                     if (p.step == 2 && s.which == 0) {
+                         sm->gate[tid] = v;
+                     } else {
+                         const GemvMat &mat = p.mat[p.step == 2 ? s.mat - 1 : s.mat];
+                         float *y = mat.y + (size_t)r * mat.n_out + s.row0 + row;
+                         if (p.step == 2) {
+                             const float gt = sm->gate[tid];
+                             v = __fmul_rn(__fdiv_rn(gt, __fadd_rn(1.0f, expf(-gt))), v);
+                         }
+                         *y = p.accumulate ? __fadd_rn(*y, v) : v;
+                     }
+                 }
+             }
+         });
+}
+
+template <int WT, int NG>
+int launch_one(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
+    static bool configured[64] = {};   // per instantiation and device: the opt-in is sticky
+    auto kernel = gemv_stream_kernel<WT, NG>;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+        if (e != cudaSuccess) {
+            note_cuda_error(e);
+            return KRK_CUDA_ELAUNCH;
+        }
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    kernel<<<grid, kThreads, smem, st>>>(p);
+    note_launch(1, KRK_CUDA_FAMILY_GEMV_STREAM);
+    return check_launch();
+}
+
+template <int WT>
+int launch_fmt(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accumulate, int silu_pair, cudaStream_t st) {
+    using F = Fmt<WT>;
+    if (n_in % 256 != 0 || n_in > (1 << 20)) return 0;
+    StreamParams p;
+    p.n_in = (int)n_in;
+    p.units = (int)(n_in / F::unit_values);
+    p.row_bytes = (int)row_bytes(WT, n_in);
+    p.rows = rows;
+    p.accumulate = accumulate;
+    p.step = silu_pair ? 2 : 1;
+    p.whole_tiles = 0;
+    p.gran = 1;
+    if (WT == KRK_CUDA_Q6_K && (n_in % 2048) != 0) {
+        // 210-byte blocks: rows are 16-byte multiples only for K % 2048 == 0. Otherwise whole 16-row
+        // tiles are copied contiguously (needs 4-byte-multiple rows and the tile in one stage).
+        if ((p.row_bytes & 3) != 0 || p.units > kConsumerWarps) return 0;
+        p.whole_tiles = 1;
+        p.gran = 8;
+    }
+    const int ku_max = p.whole_tiles ? p.units : (p.units < kConsumerWarps ? p.units : kConsumerWarps);
+    if (p.whole_tiles) {
+        p.row_stride = p.row_bytes;
+        p.stage_bytes = align_up(kTileRows * p.row_bytes, 128);
+    } else {
+        const int raw = ku_max * F::unit_bytes;
+        p.row_stride = raw + ((F::stride_mod - raw % 128) + 128) % 128;
+        p.stage_bytes = align_up(kTileRows * p.row_stride, 128);
+    }
+    const int fixed = align_up((int)sizeof(Smem), 128) + plane_bytes<WT>(p.n_in, rows) + chunk_sum_bytes<WT>(p.n_in, rows);
+    // Past ~96 KB of staged weights per SM more depth buys nothing.
+    const int max_fit = (kSmemLimit - fixed) / p.stage_bytes;
+    int want = (96 * 1024 + p.stage_bytes - 1) / p.stage_bytes;
+    want = want < 3 ? 3 : (want > kMaxStages ? kMaxStages : want);
+    p.n_stages = want < max_fit ? want : max_fit;
+    if (p.n_stages < 2) return 0;
+
+    p.n_entries = 0;
+    int total = 0;
+    for (int m = 0; m < n_mat; m += p.step) {
+        if (mats[m].n_out > (1 << 30)) return 0;
+        for (int j = 0; j < p.step; j++) p.mat[p.n_entries * p.step + j] = mats[m + j];
+        p.gran_begin[p.n_entries] = total;
+        total += (int)((mats[m].n_out + p.gran - 1) / p.gran);
+        p.n_entries++;
+    }
+    p.gran_begin[p.n_entries] = total;
+    p.total_gran = total;
+    if (total == 0) return 1;
+    p.status = device_status_word();
+    if (!p.status) return KRK_CUDA_EDEVICE;
+    const int sms = sm_count();
+    const int grid = total < sms ? total : sms;
+    const size_t smem = (size_t)fixed + (size_t)p.n_stages * p.stage_bytes;
+    int rc;
+    if (rows <= 2) rc = launch_one<WT, 1>(p, grid, smem, st);
+    else if (rows <= 4) rc = launch_one<WT, 2>(p, grid, smem, st);
+    else rc = launch_one<WT, 4>(p, grid, smem, st);
+    return rc == KRK_CUDA_OK ? 1 : rc;
+}
+
+} // namespace
+
+int launch_gemv_stream(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accumulate, int silu_pair,
+                       cudaStream_t st) {
+    if (n_mat < 1 || rows < 1 || rows > KRK_CUDA_MAX_ROWS) return 0;
+    const int wt = mats[0].wt;
+    for (int m = 1; m < n_mat; m++)
+        if (mats[m].wt != wt) return 0;
+    switch (wt) {
+    case KRK_CUDA_Q4_K: return launch_fmt<KRK_CUDA_Q4_K>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
+    case KRK_CUDA_Q6_K: return launch_fmt<KRK_CUDA_Q6_K>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
+    case KRK_CUDA_Q8_0: return launch_fmt<KRK_CUDA_Q8_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
+    default: return 0;   // Q4_0 takes the shape-agnostic kernel
+    }
+}
+
+} // namespace krk_cuda

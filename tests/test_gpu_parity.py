@@ -21,7 +21,8 @@ def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def run_gemv(cuda, oracle, wt, n_out, n_in, rows, seed, random_payload=False, accumulate=False):
+def run_gemv(cuda, oracle, wt, n_out, n_in, rows, seed, random_payload=False, accumulate=False, expect_stream=None):
+    before = cuda.family_count(cuda.FAMILY_GEMV_STREAM), cuda.family_count(cuda.FAMILY_GEMV_GENERIC)
     w = synth.weights(wt, n_out, n_in, seed, stream=wt, random_payload=random_payload)
     x = synth.activations(rows, n_in, seed)
     y_ref = oracle.gemm(x, w, wt, n_out, n_in, rows=rows, threads=8)
@@ -35,6 +36,11 @@ def run_gemv(cuda, oracle, wt, n_out, n_in, rows, seed, random_payload=False, ac
     ok, worst = bound_ok(y, y_ref, w_deq, x, GEMV_TOL)
     assert ok, f"wt={wt} {n_out}x{n_in} rows={rows}: worst error is {worst:.3f} of the bound"
     assert cuda.device_status() == 0
+    after = cuda.family_count(cuda.FAMILY_GEMV_STREAM), cuda.family_count(cuda.FAMILY_GEMV_GENERIC)
+    if expect_stream is True:
+        assert after[0] == before[0] + 1 and after[1] == before[1], "the streaming kernel did not take this shape"
+    elif expect_stream is False:
+        assert after[0] == before[0] and after[1] == before[1] + 1
     return worst
 
 
@@ -71,7 +77,12 @@ def test_dequant_every_scale_bit_pattern(cuda, oracle):
     blocks[:, 2:] = np.array([1, 255, 127, 129] * 8, np.uint8)
     got = cuda.dequant_rows(dev(blocks), synth.Q8_0, 65536, 32).cpu().numpy()
     want = oracle.dequant_rows(blocks, synth.Q8_0, 65536, 32)
-    assert got.view(np.uint32).tobytes() == want.view(np.uint32).tobytes()
+    # A NaN scale gives NaN on both sides; the GPU multiplier returns the canonical NaN while the
+    # host keeps the payload, so NaN results are compared as "both NaN", everything else by bits.
+    nan = np.isnan(want)
+    assert np.array_equal(np.isnan(got), nan)
+    assert np.array_equal(got.view(np.uint32)[~nan], want.view(np.uint32)[~nan])
+    assert nan.sum() == 2 * 1023 * 32 and np.isinf(want).sum() == 2 * 32
 
 
 # ---- GEMV ----------------------------------------------------------------------------------
@@ -104,12 +115,12 @@ def test_gemv_reference_vectors(cuda, golden, oracle):
 
 def test_config1_q8_0_decode(cuda, oracle):
     """Q8_0 4096x4096, batch 1: the reference's own CPU-runnable case, at full size."""
-    run_gemv(cuda, oracle, synth.Q8_0, 4096, 4096, 1, SEED + 1)
+    run_gemv(cuda, oracle, synth.Q8_0, 4096, 4096, 1, SEED + 1, expect_stream=True)
 
 
 @pytest.mark.parametrize("shape", [(4096, 4096), (11008, 4096), (4096, 11008)])
 def test_config2_q4_k_llama7b_shapes(cuda, oracle, shape):
-    run_gemv(cuda, oracle, synth.Q4_K, shape[0], shape[1], 1, SEED + 2)
+    run_gemv(cuda, oracle, synth.Q4_K, shape[0], shape[1], 1, SEED + 2, expect_stream=True)
 
 
 def test_config4_q6_k_head_slice_and_linearity(cuda, oracle):
@@ -118,7 +129,7 @@ def test_config4_q6_k_head_slice_and_linearity(cuda, oracle):
     y(a*x1 + x2) = a*y(x1) + y(x2) within the bound."""
     import torch
     n_in, n_full = 4096, 128256
-    run_gemv(cuda, oracle, synth.Q6_K, n_full // 8, n_in, 1, SEED + 4)
+    run_gemv(cuda, oracle, synth.Q6_K, n_full // 8, n_in, 1, SEED + 4, expect_stream=True)
     part = synth.weights(synth.Q6_K, 2004, n_in, SEED + 4, stream=synth.Q6_K)
     w = dev(part).repeat(64, 1)                                  # 128256 rows, 431 MB
     assert w.shape[0] == n_full
@@ -136,6 +147,28 @@ def test_config4_q6_k_head_slice_and_linearity(cuda, oracle):
     ref = oracle.gemm(x1, part, synth.Q6_K, 2004, n_in, threads=8)
     ok, worst = bound_ok(y1.cpu().numpy()[:, :2004], ref, w_deq, x1, GEMV_TOL)
     assert ok, worst
+
+
+def test_path_selection(cuda, oracle):
+    """Which kernel serves which shape: Q4_0 and K not a multiple of 256 take the shape-agnostic
+    kernel; Q6_K rows that are not 16-byte multiples (K = 1536) still stream, as whole tiles."""
+    run_gemv(cuda, oracle, synth.Q4_0, 64, 1024, 1, SEED + 30, expect_stream=False)
+    run_gemv(cuda, oracle, synth.Q8_0, 64, 96, 1, SEED + 31, expect_stream=False)
+    run_gemv(cuda, oracle, synth.Q6_K, 4096, 1536, 1, SEED + 32, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q6_K, 1001, 1536, 8, SEED + 33, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q4_K, 1536, 4096, 8, SEED + 34, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q8_0, 5, 256, 3, SEED + 35, expect_stream=True)
+
+
+def test_gemv_nonfinite_activation_gives_nan(cuda):
+    import torch
+    w = dev(synth.weights(synth.Q4_K, 32, 512, SEED + 36))
+    x = torch.ones(512, device="cuda")
+    x[100] = float("inf")
+    assert torch.isnan(cuda.gemv(x, w, synth.Q4_K, 32, 512)).all()
+    x[100] = 0.0
+    assert torch.isfinite(cuda.gemv(x, w, synth.Q4_K, 32, 512)).all()
+    assert (cuda.gemv(torch.zeros(512, device="cuda"), w, synth.Q4_K, 32, 512) == 0).all()
 
 
 def test_gemv_empty_and_refusals(cuda):
