@@ -83,7 +83,7 @@ class ClockSampler:
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "50"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+                 "-lms", "20"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
@@ -145,7 +145,7 @@ def run_ours(args):
     gen = torch.Generator(device="cuda")
     gen.manual_seed(synth.BASE_SEED % (2 ** 63) + 2 + 1000 * rank)
     layers = []
-    for _ in range(N_LAYERS):
+    for _ in range(args.layers):
         mats = []
         for n_out, n_in in LAYER_SHAPES:
             w = device_weights(torch, n_out, n_in, gen)
@@ -172,27 +172,51 @@ def run_ours(args):
     assert capi.device_status() == 0, "a device-side wait gave up during warm-up"
     assert all(torch.isfinite(m[2]).all() for m in layers[0])
 
+    # The step's launches are captured once into a CUDA graph and replayed: same kernels, same
+    # order, without a host round trip per launch (a decode loop replays a fixed launch sequence).
+    launches_per_step = 4 * args.layers
+    replay = step
+    if not args.no_graph:
+        cap_stream = torch.cuda.Stream()
+        cap_stream.wait_stream(stream)
+        c0 = capi.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(cap_stream):
+            graph.capture_begin()
+            for mats in layers:
+                for w, x, y, n_out, n_in in mats:
+                    capi.gemv(x, w, WT, n_out, n_in, out=y.view(1, -1), stream=cap_stream)
+            graph.capture_end()
+        launches_per_step = capi.launch_count() - c0
+        stream = cap_stream
+
+        def replay():
+            graph.replay()
+        with torch.cuda.stream(cap_stream):
+            for _ in range(3):
+                replay()
+        barrier()
+
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    launches0 = capi.launch_count()
-    stream_kernels0 = capi.family_count(capi.FAMILY_GEMV_STREAM)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    ev0.record(stream)
-    for _ in range(args.steps):
-        step()
-    ev1.record(stream)
+    with torch.cuda.stream(stream):
+        ev0.record(stream)
+        for _ in range(args.steps):
+            replay()
+        ev1.record(stream)
     barrier()
     ms = ev0.elapsed_time(ev1)
-    launches = capi.launch_count() - launches0
-    stream_kernels = capi.family_count(capi.FAMILY_GEMV_STREAM) - stream_kernels0
+    launches = launches_per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
+    assert capi.device_status() == 0, "a device-side wait gave up during the timed region"
 
     # ---- end to end through the host-buffer boundary (CudaBackend) ----
     be = capi.Backend(local)
-    x_host = torch.randn(sum(k for _, k in LAYER_SHAPES) * N_LAYERS, generator=torch.Generator().manual_seed(7)).pin_memory()
-    y_host = torch.empty(sum(n for n, _ in LAYER_SHAPES) * N_LAYERS).pin_memory()
+    x_host = torch.randn(sum(k for _, k in LAYER_SHAPES) * args.layers, generator=torch.Generator().manual_seed(7)).pin_memory()
+    y_host = torch.empty(sum(n for n, _ in LAYER_SHAPES) * args.layers).pin_memory()
     d_x = be.alloc(x_host.numel() * 4)
     d_y = be.alloc(y_host.numel() * 4)
 
@@ -206,17 +230,18 @@ def run_ours(args):
                 yo += n_out
         be.download(y_host.data_ptr(), d_y, y_host.numel() * 4)      # synchronises
 
-    for _ in range(3):
+    e2e_steps = 0 if args.no_e2e else args.steps
+    for _ in range(3 if e2e_steps else 0):
         e2e_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(torch.cuda.default_stream())
-    for _ in range(args.steps):
+    for _ in range(e2e_steps):
         e2e_step()
     e1.record(torch.cuda.default_stream())
     barrier()
-    e2e_ms = e0.elapsed_time(e1)
-    assert torch.isfinite(y_host).all()
+    e2e_ms = e0.elapsed_time(e1) if e2e_steps else float("nan")
+    assert args.no_e2e or torch.isfinite(y_host).all()
     be.release(d_x)
     be.release(d_y)
     be.close()
@@ -227,21 +252,22 @@ def run_ours(args):
         ms, e2e_ms = t.tolist()
 
     if rank == 0:
-        wbytes = layer_weight_bytes() * N_LAYERS
-        abytes = layer_algorithmic_bytes() * N_LAYERS
+        wbytes = layer_weight_bytes() * args.layers
+        abytes = layer_algorithmic_bytes() * args.layers
         per_step_ms = ms / args.steps
         value = wbytes * world / (per_step_ms * 1e-3) / 1e9
         peak, peak_kind = measured_peaks()
-        n_launch = 4 * N_LAYERS
+        n_launch = launches_per_step
         achieved = abytes / (per_step_ms * 1e-3) / 1e9          # = (bytes per launch) / (avg launch duration)
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(per_step_ms, 5), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "s8 quants x 24-bit fixed-point activations, f32 scales",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "weight_type": "Q4_K", "batch": 1, "layers": N_LAYERS,
+            "config": {"workload": WORKLOAD, "weight_type": "Q4_K", "batch": 1, "layers": args.layers,
                        "matmuls_per_layer": [list(s) for s in LAYER_SHAPES],
                        "weight_bytes_per_step": wbytes, "parallelism": f"replicas x{world}",
+                       "launch": "host launches" if args.no_graph else "CUDA graph replay of the step's launches",
                        "l2": "inputs larger than L2: 2.74 GB of distinct weights per step, each byte read once"},
             "e2e": {"value": round(wbytes * world / (e2e_ms / args.steps * 1e-3) / 1e9, 2), "unit": UNIT,
                     "h2d_bytes_per_step": x_host.numel() * 4, "d2h_bytes_per_step": y_host.numel() * 4,
@@ -251,7 +277,7 @@ def run_ours(args):
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
                          "launches_per_step": n_launch, "avg_launch_us": round(per_step_ms * 1e3 / n_launch, 3),
                          "algorithmic_bytes_per_launch": abytes // n_launch, "traffic": TRAFFIC_BYTES_PER_LAUNCH,
-                         "stream_kernel_launches": int(stream_kernels)},
+                         },
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu:
@@ -371,10 +397,14 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a CUDA graph")
+    ap.add_argument("--layers", type=int, default=N_LAYERS,
+                    help="layers per step; fewer than 32 is for profiler captures only, not a bench value")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     args = ap.parse_args()
     if args.impl == "reference":

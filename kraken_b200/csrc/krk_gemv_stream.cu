@@ -36,7 +36,10 @@ namespace {
 
 constexpr int kConsumerWarps = 16;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;   // + the producer warp
+constexpr int kThreads = kConsumerThreads + 64;   // + the producer warp + the epilogue warp
+// Tiles whose partial sums may wait for the epilogue warp (fewer when more activation rows make a slot larger).
+__host__ __device__ constexpr int red_slots(int ng) { return ng == 1 ? 4 : ng == 2 ? 2 : 1; }
+constexpr int kMaxRedSlots = 4;
 constexpr int kTileRows = 16;                     // the M of the MMA
 constexpr int kMaxStages = 8;
 constexpr int kSmemLimit = 227 * 1024;
@@ -64,8 +67,10 @@ struct StreamParams {
     int stage_bytes;
     int n_stages;
     int total_gran;
+    int gran_q, gran_r;   // total_gran = grid * gran_q + gran_r
     int *status;
 };
+
 
 // ---- PTX wrappers ----------------------------------------------------------------------------
 
@@ -90,19 +95,17 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void consumer_barrier() {
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-}
+// c = A x B with a zero accumulator input (the sub-block scale is applied to c afterwards).
 __device__ __forceinline__ void mma_s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                            uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 __device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(b0));
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(0));
 }
 __device__ __forceinline__ int sext_byte(uint32_t w, int i) {
     int r;
@@ -115,13 +118,13 @@ __device__ __forceinline__ float half_hi(uint32_t w) { return __half2float(__ush
 // Bounded wait on an mbarrier phase. Once any wait in the CTA has given up, every later wait
 // returns at once, so the CTA runs to its end (on stale data, inside its own buffers) instead
 // of hanging.
-__device__ __forceinline__ void wait_phase(uint32_t bar, uint32_t parity, volatile int *gave_up, int *status) {
-    if (*gave_up) return;
-    if (mbar_try_wait(bar, parity)) return;
+__device__ __noinline__ void wait_phase_slow(uint32_t bar, uint32_t parity, volatile int *gave_up, int *status) {
     const long long t0 = clock64();
     for (;;) {
-        for (int i = 0; i < 64; i++)
+        for (int i = 0; i < 32; i++) {
             if (mbar_try_wait(bar, parity)) return;
+            __nanosleep(20);   // leave the issue slots to the warps that have work
+        }
         if (*gave_up) return;
         if (clock64() - t0 > kWaitCycles) {
             *gave_up = 1;
@@ -130,19 +133,24 @@ __device__ __forceinline__ void wait_phase(uint32_t bar, uint32_t parity, volati
         }
     }
 }
+__device__ __forceinline__ void wait_phase(uint32_t bar, uint32_t parity, volatile int *gave_up, int *status) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (*gave_up) return;
+    wait_phase_slow(bar, parity, gave_up, status);
+}
 
 // ---- shared-memory map ---------------------------------------------------------------------------
 
+template <int NG>
 struct Smem {
-    unsigned long long full[kMaxStages];
-    unsigned long long empty[kMaxStages];
+    unsigned long long full[kMaxStages];     // weights of a stage have landed
+    unsigned long long empty[kMaxStages];    // every consumer warp is done with the stage
+    unsigned long long red_full[kMaxRedSlots];  // every consumer warp has written its partial sums of a tile
+    unsigned long long red_empty[kMaxRedSlots]; // the epilogue warp has consumed them
     int gave_up;
     int pad[3];
-    float xscale[KRK_CUDA_MAX_ROWS];                  // s_r: x ~ s_r * X, X 24-bit signed
-    float warp_max[kConsumerWarps];
-    int warp_bad[kConsumerWarps];
-    float red[2][kConsumerWarps][kTileRows][KRK_CUDA_MAX_ROWS];
-    float gate[kTileRows * KRK_CUDA_MAX_ROWS];       // gate tile kept for the silu fold
+    // per consumer lane and column group: its weighted share of (row g | g+8) x (activation row even | odd)
+    float4 red[red_slots(NG)][kConsumerWarps][NG][32];
 };
 
 __host__ __device__ constexpr int align_up(int v, int a) { return (v + a - 1) / a * a; }
@@ -150,7 +158,7 @@ __host__ __device__ constexpr int align_up(int v, int a) { return (v + a - 1) / 
 template <int WT>
 __host__ __device__ inline int plane_bytes(int n_in, int rows) { return align_up(rows * 3 * n_in, 128); }
 template <int WT>
-__host__ __device__ inline int chunk_sum_bytes(int n_in, int rows) {
+__host__ __device__ inline int chunk_sum_bytes(int n_in, int rows) {   // [row][4 limbs][n_in / 32] s8
     return WT == KRK_CUDA_Q4_K ? align_up(rows * (n_in / 32) * 4, 128) : 0;
 }
 
@@ -164,15 +172,18 @@ struct StageInfo {
     int unit0;      // first K unit of this stage
     int n_units;    // units in this stage (1..16)
     int last;       // last stage of the tile
-    int it;         // running stage number of this CTA
+    int slot;       // ring slot of this stage
+    int phase;      // parity of the slot's current use
 };
 
 template <class SegmentFn, class StageFn>
 __device__ __forceinline__ void walk(const StreamParams &p, SegmentFn &&on_segment, StageFn &&on_stage) {
-    const int g0 = (int)((long long)blockIdx.x * p.total_gran / gridDim.x);
-    const int g1 = (int)((long long)(blockIdx.x + 1) * p.total_gran / gridDim.x);
+    // balanced split of the granules over the CTAs: the first gran_r CTAs take one more
+    const int c = (int)blockIdx.x;
+    const int g0 = c * p.gran_q + min(c, p.gran_r);
+    const int g1 = g0 + p.gran_q + (c < p.gran_r ? 1 : 0);
     const int ku_max = p.whole_tiles ? p.units : kConsumerWarps;
-    int it = 0;
+    int slot = 0, phase = 0;
     for (int e = 0; e < p.n_entries; e++) {
         const int lo = max(g0, p.gran_begin[e]), hi = min(g1, p.gran_begin[e + 1]);
         if (lo >= hi) continue;
@@ -191,7 +202,12 @@ __device__ __forceinline__ void walk(const StreamParams &p, SegmentFn &&on_segme
                     s.unit0 = u0;
                     s.n_units = min(ku_max, p.units - u0);
                     s.last = u0 + ku_max >= p.units;
-                    s.it = it++;
+                    s.slot = slot;
+                    s.phase = phase;
+                    if (++slot == p.n_stages) {
+                        slot = 0;
+                        phase ^= 1;
+                    }
                     on_stage(s);
                 }
             }
@@ -200,86 +216,133 @@ __device__ __forceinline__ void walk(const StreamParams &p, SegmentFn &&on_segme
 }
 
 // ---- activation preparation -------------------------------------------------------------------------
-// For every activation row: s = max|x| / 127*2^16, X = rint(x / s) as three balanced s8 limbs
-// stored as byte planes [row][limb][k] in the order the consumers' B fragments want them, plus
-// (Q4_K) the f32 sum of x over every 32-value chunk for the `min` term.
+// Consumer warp w only ever multiplies K units w, w+16, ... so it prepares exactly those slices
+// of x itself: no other warp reads them and no CTA-wide barrier is involved. Per activation row:
+// s = max|x| / (127 * 2^16) over the warp's slices, X = rint(x / s) as three balanced s8 limbs
+// written as byte planes [row][limb][k] in the order the B fragments are read, and (Q4_K) the
+// integer sum of X over every 32-value chunk as four balanced s8 limbs [row][limb][chunk] for
+// the `min` term. s is returned (NaN when a slice holds a non-finite activation, so the output
+// becomes NaN as it would in f32) and multiplies the warp's partial sums at the end of each tile.
+
+__device__ __forceinline__ int sext8(int v) { return (v << 24) >> 24; }
 
 template <int WT>
-__device__ __forceinline__ void prepare_x(const float *__restrict__ x, int rows, int n_in, Smem *sm,
-                                          int8_t *planes, float *chunk_sum, int ctid) {
-    const int wid = ctid >> 5, lane = ctid & 31;
-    for (int r = 0; r < rows; r++) {
-        const float *xr = x + (size_t)r * n_in;
-        float mx = 0.0f;
-        int bad = 0;
-        for (int i = ctid * 4; i < n_in; i += kConsumerThreads * 4) {
-            const float4 v = *reinterpret_cast<const float4 *>(xr + i);
-            const float a = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-            mx = fmaxf(mx, a);
-            bad |= !(fabsf(v.x) <= FLT_MAX) | !(fabsf(v.y) <= FLT_MAX) | !(fabsf(v.z) <= FLT_MAX) | !(fabsf(v.w) <= FLT_MAX);
-        }
+__device__ __forceinline__ void quantize_slice(const float (&f)[Fmt<WT>::unit_values / 32], float inv, int k0, int8_t *p0,
+                                               int8_t *p1, int8_t *p2, int8_t *sums, int n_chunks, int lane) {
+    constexpr int PER = Fmt<WT>::unit_values / 32;
+    int total = 0;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-            bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, o);
-        }
-        if (lane == 0) {
-            sm->warp_max[wid] = mx;
-            sm->warp_bad[wid] = bad;
-        }
-        consumer_barrier();
-        for (int w = 0; w < kConsumerWarps; w++) {
-            mx = fmaxf(mx, sm->warp_max[w]);
-            bad |= sm->warp_bad[w];
-        }
-        const float inv = (mx > 0.0f && !bad) ? __fdiv_rn(kFixedOne, mx) : 0.0f;
-        if (ctid == 0) sm->xscale[r] = bad ? __int_as_float(0x7FC00000) : __fdiv_rn(mx, kFixedOne);
-        int8_t *p0 = planes + (size_t)(r * 3 + 0) * n_in;
-        int8_t *p1 = planes + (size_t)(r * 3 + 1) * n_in;
-        int8_t *p2 = planes + (size_t)(r * 3 + 2) * n_in;
-        for (int i = ctid * 4; i < n_in; i += kConsumerThreads * 4) {
-            const float4 v = *reinterpret_cast<const float4 *>(xr + i);
-            const float f[4] = {v.x, v.y, v.z, v.w};
-            uint32_t w0 = 0, w1 = 0, w2 = 0;
+    for (int j4 = 0; j4 < PER; j4 += 4) {
+        uint32_t w0 = 0, w1 = 0, w2 = 0;
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int X = __float2int_rn(f[j] * inv);
-                const int l2 = (X << 24) >> 24;
-                const int X1 = (X - l2) >> 8;
-                const int l1 = (X1 << 24) >> 24;
-                const int l0 = (X1 - l1) >> 8;
-                w0 |= (uint32_t)(l0 & 0xFF) << (8 * j);
-                w1 |= (uint32_t)(l1 & 0xFF) << (8 * j);
-                w2 |= (uint32_t)(l2 & 0xFF) << (8 * j);
-            }
-            if (WT == KRK_CUDA_Q8_0 && ((i >> 5) & 1) == 0) {
-                // Even blocks start 2 bytes off a word boundary, so their lanes take the quants in the
-                // order [0,1,30,31, 2..29]; the limbs follow: pair (e, e+1) lands at position pos(e).
-                const int e = i & 31, base = i & ~31;
-                const int k0 = e < 2 ? e : (e >= 30 ? e - 28 : e + 2);
-                const int e2 = e + 2;
-                const int k1 = e2 < 2 ? e2 : (e2 >= 30 ? e2 - 28 : e2 + 2);
-                *reinterpret_cast<uint16_t *>(p0 + base + k0) = (uint16_t)(w0 & 0xFFFF);
-                *reinterpret_cast<uint16_t *>(p0 + base + k1) = (uint16_t)(w0 >> 16);
-                *reinterpret_cast<uint16_t *>(p1 + base + k0) = (uint16_t)(w1 & 0xFFFF);
-                *reinterpret_cast<uint16_t *>(p1 + base + k1) = (uint16_t)(w1 >> 16);
-                *reinterpret_cast<uint16_t *>(p2 + base + k0) = (uint16_t)(w2 & 0xFFFF);
-                *reinterpret_cast<uint16_t *>(p2 + base + k1) = (uint16_t)(w2 >> 16);
-            } else {
-                *reinterpret_cast<uint32_t *>(p0 + i) = w0;
-                *reinterpret_cast<uint32_t *>(p1 + i) = w1;
-                *reinterpret_cast<uint32_t *>(p2 + i) = w2;
-            }
-            if (WT == KRK_CUDA_Q4_K) {
-                float s = (v.x + v.y) + (v.z + v.w);
-                s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
-                s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
-                s += __shfl_xor_sync(0xFFFFFFFFu, s, 4);
-                if ((lane & 7) == 0) chunk_sum[(size_t)r * (n_in >> 5) + (i >> 5)] = s;
-            }
+        for (int j = 0; j < 4; j++) {
+            const int X = __float2int_rn(f[j4 + j] * inv);
+            total += X;
+            const int l2 = sext8(X);
+            const int X1 = (X - l2) >> 8;
+            const int l1 = sext8(X1);
+            const int l0 = (X1 - l1) >> 8;
+            w0 |= (uint32_t)(l0 & 0xFF) << (8 * j);
+            w1 |= (uint32_t)(l1 & 0xFF) << (8 * j);
+            w2 |= (uint32_t)(l2 & 0xFF) << (8 * j);
         }
-        consumer_barrier();
+        const int i = k0 + j4;
+        if (WT == KRK_CUDA_Q8_0 && ((i >> 5) & 1) == 0) {
+            // Even blocks start 2 bytes off a word boundary, so their lanes take the quants in the
+            // order [0,1,30,31, 2..29]; the limbs follow: pair (e, e+1) lands at position pos(e).
+            const int e = i & 31, base = i & ~31;
+            const int ka = e < 2 ? e : (e >= 30 ? e - 28 : e + 2);
+            const int e2 = e + 2;
+            const int kb = e2 < 2 ? e2 : (e2 >= 30 ? e2 - 28 : e2 + 2);
+            *reinterpret_cast<uint16_t *>(p0 + base + ka) = (uint16_t)(w0 & 0xFFFF);
+            *reinterpret_cast<uint16_t *>(p0 + base + kb) = (uint16_t)(w0 >> 16);
+            *reinterpret_cast<uint16_t *>(p1 + base + ka) = (uint16_t)(w1 & 0xFFFF);
+            *reinterpret_cast<uint16_t *>(p1 + base + kb) = (uint16_t)(w1 >> 16);
+            *reinterpret_cast<uint16_t *>(p2 + base + ka) = (uint16_t)(w2 & 0xFFFF);
+            *reinterpret_cast<uint16_t *>(p2 + base + kb) = (uint16_t)(w2 >> 16);
+        } else {
+            *reinterpret_cast<uint32_t *>(p0 + i) = w0;
+            *reinterpret_cast<uint32_t *>(p1 + i) = w1;
+            *reinterpret_cast<uint32_t *>(p2 + i) = w2;
+        }
     }
+    if (WT == KRK_CUDA_Q4_K) {
+        // a 32-value chunk is held by 4 consecutive lanes; |sum| <= 32 * 127 * 2^16 < 2^28
+        total += __shfl_xor_sync(0xFFFFFFFFu, total, 1);
+        total += __shfl_xor_sync(0xFFFFFFFFu, total, 2);
+        if ((lane & 3) == 0) {
+            const int c = k0 >> 5;
+            const int l3 = sext8(total);
+            const int s1 = (total - l3) >> 8;
+            const int l2 = sext8(s1);
+            const int s2 = (s1 - l2) >> 8;
+            const int l1 = sext8(s2);
+            const int l0 = (s2 - l1) >> 8;
+            sums[c] = (int8_t)l0;
+            sums[n_chunks + c] = (int8_t)l1;
+            sums[2 * n_chunks + c] = (int8_t)l2;
+            sums[3 * n_chunks + c] = (int8_t)l3;
+        }
+    }
+}
+
+template <int WT>
+__device__ __forceinline__ void load_slice(const float *__restrict__ x, int k0, float (&f)[Fmt<WT>::unit_values / 32],
+                                           float &mx, int &bad) {
+    constexpr int PER = Fmt<WT>::unit_values / 32;
+#pragma unroll
+    for (int j = 0; j < PER; j += 4) {
+        const float4 v = *reinterpret_cast<const float4 *>(x + k0 + j);
+        f[j] = v.x; f[j + 1] = v.y; f[j + 2] = v.z; f[j + 3] = v.w;
+    }
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const float a = fabsf(f[j]);
+        mx = fmaxf(mx, a);
+        bad |= !(a <= FLT_MAX);
+    }
+}
+
+// All slices this warp will read of one activation row; returns the row's scale for this warp.
+template <int WT>
+__device__ __forceinline__ float prepare_x_row(const float *__restrict__ xr, const StreamParams &p, int8_t *p0, int8_t *sums,
+                                               int wid, int lane) {
+    constexpr int UV = Fmt<WT>::unit_values, PER = UV / 32, kHeld = 3;
+    const int n_chunks = p.n_in >> 5;
+    // the first three slices stay in registers between the max and the quantisation (K <= 12288 for
+    // 256-value units); any further ones are read twice
+    float held[kHeld][PER];
+    float mx = 0.0f;
+    int bad = 0;
+#pragma unroll
+    for (int j = 0; j < kHeld; j++) {
+        const int u = wid + j * kConsumerWarps;
+        if (u < p.units) load_slice<WT>(xr, u * UV + lane * PER, held[j], mx, bad);
+    }
+    for (int u = wid + kHeld * kConsumerWarps; u < p.units; u += kConsumerWarps) {
+        float f[PER];
+        load_slice<WT>(xr, u * UV + lane * PER, f, mx, bad);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, o);
+    }
+    const float inv = (mx > 0.0f && !bad) ? __fdiv_rn(kFixedOne, mx) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < kHeld; j++) {
+        const int u = wid + j * kConsumerWarps;
+        if (u < p.units)
+            quantize_slice<WT>(held[j], inv, u * UV + lane * PER, p0, p0 + p.n_in, p0 + 2 * p.n_in, sums, n_chunks, lane);
+    }
+    for (int u = wid + kHeld * kConsumerWarps; u < p.units; u += kConsumerWarps) {
+        float f[PER];
+        float m2 = 0.0f;
+        int b2 = 0;
+        load_slice<WT>(xr, u * UV + lane * PER, f, m2, b2);
+        quantize_slice<WT>(f, inv, u * UV + lane * PER, p0, p0 + p.n_in, p0 + 2 * p.n_in, sums, n_chunks, lane);
+    }
+    return bad ? __int_as_float(0x7FC00000) : __fdiv_rn(mx, kFixedOne);
 }
 
 // ---- per-format unit kernels -------------------------------------------------------------------------
@@ -289,8 +352,8 @@ __device__ __forceinline__ void prepare_x(const float *__restrict__ x, int rows,
 
 template <int NG>
 struct Accum {
-    float f[NG][4];        // [group][(row g | g+8) x (col 2t | 2t+1)], already times the block scale
-    float m[2][2 * NG];    // Q4_K: dmin * sum(min_c * sum_x_c), per (row half, activation row)
+    float f[NG][4];   // [group][(row g | g+8) x (col 2t | 2t+1)], already times the block scale d
+    float m[NG][4];   // Q4_K: the same for dmin * sum(min_c * sum_X_c), columns = 4 limbs x 2 activation rows
 };
 
 template <int NG>
@@ -300,25 +363,30 @@ __device__ __forceinline__ void accum_zero(Accum<NG> &a) {
 #pragma unroll
         for (int j = 0; j < 4; j++) a.f[i][j] = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 2; i++)
+    for (int i = 0; i < NG; i++)
 #pragma unroll
-        for (int j = 0; j < 2 * NG; j++) a.m[i][j] = 0.0f;
+        for (int j = 0; j < 4; j++) a.m[i][j] = 0.0f;
 }
 
-// Byte planes this lane reads its B fragments from: one pointer per column group, or null when
-// the lane's column carries no limb (columns 6, 7, or an activation row past `rows`).
+// Byte planes this lane reads its B fragments from, one per column group. A lane whose column
+// carries no limb (columns 6, 7, or an activation row past `rows`) reads some valid plane: its
+// accumulator columns are never looked at, so what it multiplies does not matter.
 template <int NG>
-__device__ __forceinline__ void lane_planes(const int8_t *planes, int n_in, int rows, int g, const int8_t *(&bp)[NG]) {
+__device__ __forceinline__ void lane_planes(const int8_t *planes, const int8_t *chunk_sum, int n_in, int rows, int g,
+                                            const int8_t *(&bp)[NG], const int8_t *(&sp)[NG]) {
 #pragma unroll
     for (int mg = 0; mg < NG; mg++) {
-        const int r = 2 * mg + g / 3;
-        bp[mg] = (g < 6 && r < rows) ? planes + (size_t)(r * 3 + g % 3) * n_in : nullptr;
+        const int r = min(2 * mg + (g % 6) / 3, rows - 1);
+        bp[mg] = planes + (size_t)(r * 3 + g % 3) * n_in;
+        // chunk sums: column c = limb c%4 of activation row c/4 of the group
+        const int rs = min(2 * mg + g / 4, rows - 1);
+        sp[mg] = chunk_sum + (size_t)(rs * 4 + g % 4) * (n_in >> 5);
     }
 }
 
 template <int NG>
 __device__ __forceinline__ void unit_q4_k(const uint8_t *rowA, const uint8_t *rowB, int kbase, const int8_t *const (&bp)[NG],
-                                          const float *chunk_sum, int n_in, int rows, int t, Accum<NG> &acc) {
+                                          const int8_t *const (&sp)[NG], int t, Accum<NG> &acc) {
     const uint4 hA = *reinterpret_cast<const uint4 *>(rowA);
     const uint4 hB = *reinterpret_cast<const uint4 *>(rowB);
     // 6-bit scales and mins of the 8 chunks, four per word (src/quant.cpp:427-435 done bytewise)
@@ -343,9 +411,8 @@ __device__ __forceinline__ void unit_q4_k(const uint8_t *rowA, const uint8_t *ro
             const int sa = (scA[c >> 2] >> (8 * (c & 3))) & 0xFF, sb = (scB[c >> 2] >> (8 * (c & 3))) & 0xFF;
 #pragma unroll
             for (int mg = 0; mg < NG; mg++) {
-                uint2 b = make_uint2(0u, 0u);
-                if (bp[mg]) b = *reinterpret_cast<const uint2 *>(bp[mg] + kbase + 32 * c + 8 * t);
-                int cc[4] = {0, 0, 0, 0};
+                const uint2 b = *reinterpret_cast<const uint2 *>(bp[mg] + kbase + 32 * c + 8 * t);
+                int cc[4];
                 mma_s8_k32(cc, a0, a1, a2, a3, b.x, b.y);
                 I[mg][0] += sa * cc[0];
                 I[mg][1] += sa * cc[1];
@@ -362,18 +429,19 @@ __device__ __forceinline__ void unit_q4_k(const uint8_t *rowA, const uint8_t *ro
         acc.f[mg][2] = fmaf(dB, (float)I[mg][2], acc.f[mg][2]);
         acc.f[mg][3] = fmaf(dB, (float)I[mg][3], acc.f[mg][3]);
     }
-    // min term: lane t covers chunks 2t and 2t+1 of the super-block
+    // min term, also exact: one k16 MMA of the 8 mins of the super-block (k slots 0..7) against the
+    // per-chunk sums of X, held as 4 limbs x 2 activation rows in the 8 columns
     const float nA = half_hi(hA.x), nB = half_hi(hB.x);
-    const int sh = 16 * (t & 1);
-    const float mA0 = (float)((mnA[t >> 1] >> sh) & 0xFF), mA1 = (float)((mnA[t >> 1] >> (sh + 8)) & 0xFF);
-    const float mB0 = (float)((mnB[t >> 1] >> sh) & 0xFF), mB1 = (float)((mnB[t >> 1] >> (sh + 8)) & 0xFF);
+    const uint32_t a0 = t < 2 ? mnA[t & 1] : 0u, a1 = t < 2 ? mnB[t & 1] : 0u;
 #pragma unroll
-    for (int r = 0; r < 2 * NG; r++) {
-        if (r < rows) {
-            const float2 sx = *reinterpret_cast<const float2 *>(chunk_sum + (size_t)r * (n_in >> 5) + (kbase >> 5) + 2 * t);
-            acc.m[0][r] = fmaf(nA, fmaf(mA0, sx.x, mA1 * sx.y), acc.m[0][r]);
-            acc.m[1][r] = fmaf(nB, fmaf(mB0, sx.x, mB1 * sx.y), acc.m[1][r]);
-        }
+    for (int mg = 0; mg < NG; mg++) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(sp[mg] + (kbase >> 5) + 4 * (t & 1));
+        int cc[4];
+        mma_s8_k16(cc, a0, a1, b0);
+        acc.m[mg][0] = fmaf(nA, (float)cc[0], acc.m[mg][0]);
+        acc.m[mg][1] = fmaf(nA, (float)cc[1], acc.m[mg][1]);
+        acc.m[mg][2] = fmaf(nB, (float)cc[2], acc.m[mg][2]);
+        acc.m[mg][3] = fmaf(nB, (float)cc[3], acc.m[mg][3]);
     }
 }
 
@@ -409,12 +477,9 @@ __device__ __forceinline__ void unit_q8_0(const uint8_t *rowA, const uint8_t *ro
         }
 #pragma unroll
         for (int mg = 0; mg < NG; mg++) {
-            uint32_t b0 = 0u, b1 = 0u;
-            if (bp[mg]) {
-                b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 4 * t);
-                b1 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 16 + 4 * t);
-            }
-            int cc[4] = {0, 0, 0, 0};
+            const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 4 * t);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 16 + 4 * t);
+            int cc[4];
             mma_s8_k32(cc, a0, a1, a2, a3, b0, b1);
             acc.f[mg][0] = fmaf(dA, (float)cc[0], acc.f[mg][0]);
             acc.f[mg][1] = fmaf(dA, (float)cc[1], acc.f[mg][1]);
@@ -478,9 +543,8 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
             const int sa = sext_byte(scA[G >> 2], G & 3), sb = sext_byte(scB[G >> 2], G & 3);
 #pragma unroll
             for (int mg = 0; mg < NG; mg++) {
-                uint32_t b0 = 0u;
-                if (bp[mg]) b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 128 * h + 16 * G + 4 * t);
-                int cc[4] = {0, 0, 0, 0};
+                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 128 * h + 16 * G + 4 * t);
+                int cc[4];
                 mma_s8_k16(cc, a0, a1, b0);
                 I[mg][0] += sa * cc[0];
                 I[mg][1] += sa * cc[1];
@@ -501,22 +565,39 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------------
+// Three roles, connected only by mbarriers, so no warp ever waits at a CTA-wide barrier while
+// weights are streaming:
+//   warp 16       producer: bulk-async copies of weight rows into the stage ring;
+//   warps 0..15   consumers: warp w takes K unit w of every stage (16 rows x 256 values), keeps the
+//                 tile's partial sums in registers and hands them over at the end of the tile;
+//   warp 17       epilogue: adds the 16 partial sums of each tile in warp order (deterministic),
+//                 applies the gate/up fold or the residual add, and writes y.
 
 template <int WT, int NG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     using F = Fmt<WT>;
+    using SmemT = Smem<NG>;
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    Smem *sm = reinterpret_cast<Smem *>(smem_raw);
-    int8_t *planes = reinterpret_cast<int8_t *>(smem_raw + align_up((int)sizeof(Smem), 128));
-    float *chunk_sum = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(planes) + plane_bytes<WT>(p.n_in, p.rows));
+    SmemT *sm = reinterpret_cast<SmemT *>(smem_raw);
+    int8_t *planes = reinterpret_cast<int8_t *>(smem_raw + align_up((int)sizeof(SmemT), 128));
+    int8_t *chunk_sum = planes + plane_bytes<WT>(p.n_in, p.rows);
     uint8_t *stages = reinterpret_cast<uint8_t *>(chunk_sum) + chunk_sum_bytes<WT>(p.n_in, p.rows);
 
     const int tid = threadIdx.x;
+    const int n_warps = min(kConsumerWarps, p.units);   // consumer warps that ever hold a unit
+    // Programmatic dependent launch: the next kernel in the stream may start its prologue (and, being
+    // this same kernel, its weight prefetch) as soon as every CTA here has passed this point and an
+    // SM has room; it still waits for this grid to complete before touching activations or outputs.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (tid == 0) {
         for (int s = 0; s < p.n_stages; s++) {
             mbar_init(smem_u32(&sm->full[s]), 1);
             mbar_init(smem_u32(&sm->empty[s]), kConsumerWarps);
+        }
+        for (int s = 0; s < red_slots(NG); s++) {
+            mbar_init(smem_u32(&sm->red_full[s]), n_warps);
+            mbar_init(smem_u32(&sm->red_empty[s]), 1);
         }
         sm->gave_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -525,13 +606,55 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     __syncthreads();
     volatile int *gave_up = &sm->gave_up;
 
+    if (tid >= kConsumerThreads + 32) {
+        // ===== epilogue warp =====
+        // Output (row, activation row) of a tile is the sum, over the consumer warps in warp order and
+        // their four lanes t = 0..3 of row group g, of the share each lane left in `red`.
+        const int lane = tid - kConsumerThreads - 32;
+        constexpr int kSlots = red_slots(NG);
+        float gate[NG];   // gate tile kept for the silu fold
+        int tile_it = 0;
+        walk(p, [](int) {}, [&](const StageInfo &s) {
+            if (!s.last) return;
+            const int slot = tile_it % kSlots;
+            wait_phase(smem_u32(&sm->red_full[slot]), (tile_it / kSlots) & 1, gave_up, p.status);
+            tile_it++;
+#pragma unroll
+            for (int i = 0; i < NG; i++) {
+                const int idx = lane + 32 * i, row = idx & (kTileRows - 1), r = idx >> 4;   // r = 2*i + (lane >> 4)
+                const float *src = reinterpret_cast<const float *>(&sm->red[slot][0][i][4 * (row & 7)]) + 2 * (row >> 3) + (r & 1);
+                float v = 0.0f;
+                for (int w = 0; w < n_warps; w++) {
+                    const float *q = src + (size_t)w * (NG * 32 * 4);
+                    v += q[0];
+                    v += q[4];
+                    v += q[8];
+                    v += q[12];
+                }
+                if (r < p.rows) {
+                    if (p.step == 2 && s.which == 0) {
+                        gate[i] = v;
+                    } else if (row < s.n_rows) {
+                        const GemvMat &mat = p.mat[p.step == 2 ? s.mat - 1 : s.mat];
+                        float *y = mat.y + (size_t)r * mat.n_out + s.row0 + row;
+                        if (p.step == 2) v = __fmul_rn(__fdiv_rn(gate[i], __fadd_rn(1.0f, expf(-gate[i]))), v);
+                        *y = p.accumulate ? __fadd_rn(*y, v) : v;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sm->red_empty[slot]));
+        });
+        return;
+    }
+
     if (tid >= kConsumerThreads) {
         // ===== producer warp: weights only, so it can run ahead of everything else =====
         const int lane = tid - kConsumerThreads;
         walk(p, [](int) {}, [&](const StageInfo &s) {
-            const int slot = s.it % p.n_stages;
+            const int slot = s.slot;
             const uint32_t full = smem_u32(&sm->full[slot]), empty = smem_u32(&sm->empty[slot]);
-            wait_phase(empty, ((s.it / p.n_stages) & 1) ^ 1, gave_up, p.status);
+            wait_phase(empty, s.phase ^ 1, gave_up, p.status);
             uint8_t *dst = stages + (size_t)slot * p.stage_bytes;
             const uint8_t *src = p.mat[s.mat].w + (size_t)s.row0 * p.row_bytes;
             if (!p.whole_tiles) {
@@ -559,91 +682,106 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     // ===== consumer warps =====
     const int wid = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const float *prepared = nullptr;
-    const int8_t *bp[NG];
+    const int8_t *bp[NG], *sp[NG];
+    float xs[2 * NG];   // this warp's scale of each activation row
     Accum<NG> acc;
     accum_zero(acc);
     int tile_it = 0;
+    const uint32_t lane_off = (uint32_t)wid * F::unit_bytes + (uint32_t)g * p.row_stride;
 
-    walk(p,
-         [&](int m) {
-             if (p.mat[m].x != prepared) {
-                 consumer_barrier();   // nobody still reads the previous planes
-                 prepare_x<WT>(p.mat[m].x, p.rows, p.n_in, sm, planes, chunk_sum, tid);
-                 prepared = p.mat[m].x;
-                 lane_planes<NG>(planes, p.n_in, p.rows, g, bp);
-             }
-         },
-         [&](const StageInfo &s) {
-             const int slot = s.it % p.n_stages;
-             wait_phase(smem_u32(&sm->full[slot]), (s.it / p.n_stages) & 1, gave_up, p.status);
-             if (wid < s.n_units) {
-                 const uint8_t *base = stages + (size_t)slot * p.stage_bytes + (size_t)wid * F::unit_bytes;
-                 const uint8_t *rowA = base + (size_t)g * p.row_stride, *rowB = rowA + (size_t)8 * p.row_stride;
-                 const int kbase = (s.unit0 + wid) * F::unit_values;
-                 if (WT == KRK_CUDA_Q4_K) {
-                     unit_q4_k<NG>(rowA, rowB, kbase, bp, chunk_sum, p.n_in, p.rows, t, acc);
-                 } else if (WT == KRK_CUDA_Q8_0) {
-                     unit_q8_0<NG>(rowA, rowB, kbase, bp, t, acc);
-                 } else {
-                     if ((s.unit0 + wid) & 1) unit_q6_k<NG, true>(rowA, rowB, kbase, bp, t, acc);
-                     else unit_q6_k<NG, false>(rowA, rowB, kbase, bp, t, acc);
-                 }
-             }
-             __syncwarp();
-             if (lane == 0) mbar_arrive(smem_u32(&sm->empty[slot]));
-             if (!s.last) return;
-
-             // ---- tile epilogue: limbs -> value per (row, activation row), then across warps ----
-             const int buf = tile_it & 1;
+    // The same walk as walk() above, written flat: per stage a consumer warp only needs the ring
+    // slot and its K unit, not which matrix or rows the tile belongs to.
+    const int cta = (int)blockIdx.x;
+    const int g0 = cta * p.gran_q + min(cta, p.gran_r);
+    const int g1 = g0 + p.gran_q + (cta < p.gran_r ? 1 : 0);
+    const int n_chunks = p.whole_tiles ? 1 : (p.units + kConsumerWarps - 1) / kConsumerWarps;
+    const uint32_t full0 = smem_u32(&sm->full[0]), empty0 = smem_u32(&sm->empty[0]);
+    int slot = 0;
+    uint32_t phase = 0;
+    for (int e = 0; e < p.n_entries; e++) {
+        const int lo = max(g0, p.gran_begin[e]), hi = min(g1, p.gran_begin[e + 1]);
+        if (lo >= hi) continue;
+        const int m = e * p.step;
+        const int r0 = (lo - p.gran_begin[e]) * p.gran;
+        const int r1 = min((int)p.mat[m].n_out, (hi - p.gran_begin[e]) * p.gran);
+        if (p.mat[m].x != prepared) {
+            // x may be the output of the kernel before this one (and y its input): wait for that grid to
+            // complete. Weights are never written by a kernel in flight, so the producer warp does not wait.
+            if (prepared == nullptr) asm volatile("griddepcontrol.wait;" ::: "memory");
+            prepared = p.mat[m].x;
+#pragma unroll
+            for (int r = 0; r < 2 * NG; r++)
+                xs[r] = r < p.rows ? prepare_x_row<WT>(prepared + (size_t)r * p.n_in, p, planes + (size_t)(r * 3) * p.n_in,
+                                                       chunk_sum + (size_t)(r * 4) * (p.n_in >> 5), wid, lane)
+                                   : 0.0f;
+            __syncwarp();
+            lane_planes<NG>(planes, chunk_sum, p.n_in, p.rows, g, bp, sp);
+        }
+        const int n_tiles = ((r1 - r0 + kTileRows - 1) / kTileRows) * p.step;
+        for (int tile = 0; tile < n_tiles; tile++) {
+            for (int ck = 0; ck < n_chunks; ck++) {
+                wait_phase(full0 + 8 * slot, phase, gave_up, p.status);
+                const int unit = ck * kConsumerWarps + wid;
+                if (unit < p.units) {
+                    const uint8_t *rowA = stages + (size_t)slot * p.stage_bytes + lane_off, *rowB = rowA + (size_t)8 * p.row_stride;
+                    const int kbase = unit * F::unit_values;
+                    if (WT == KRK_CUDA_Q4_K) {
+                        unit_q4_k<NG>(rowA, rowB, kbase, bp, sp, t, acc);
+                    } else if (WT == KRK_CUDA_Q8_0) {
+                        unit_q8_0<NG>(rowA, rowB, kbase, bp, t, acc);
+                    } else {
+                        if (unit & 1) unit_q6_k<NG, true>(rowA, rowB, kbase, bp, t, acc);
+                        else unit_q6_k<NG, false>(rowA, rowB, kbase, bp, t, acc);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + 8 * slot);
+                if (++slot == p.n_stages) {
+                    slot = 0;
+                    phase ^= 1;
+                }
+            }
+            {
+             // ---- end of the tile: each lane leaves its weighted share of the four outputs it touches ----
+             // Column c of a group carries limb c%3 (weights 65536, 256, 1) of activation row c/3; this lane
+             // holds columns 2t and 2t+1, so its accumulators enter the even activation row with (we0, we1)
+             // and the odd one with (wo0, wo1). The Q4_K min term is already a per-lane partial sum.
+             constexpr int kSlots = red_slots(NG);
+             const int rslot = tile_it % kSlots;
+             const uint32_t rphase = (tile_it / kSlots) & 1;
              tile_it++;
-             const int n_warps = min(kConsumerWarps, p.units);
-             const int lane_base = lane & ~3;
+             if (wid >= n_warps) continue;
+             wait_phase(smem_u32(&sm->red_empty[rslot]), rphase ^ 1, gave_up, p.status);
+             const float we0 = t == 0 ? 65536.0f : (t == 1 ? 1.0f : 0.0f), we1 = t == 0 ? 256.0f : 0.0f;
+             const float wo0 = t == 2 ? 256.0f : 0.0f, wo1 = t == 1 ? 65536.0f : (t == 2 ? 1.0f : 0.0f);
+             // min columns: limb c%4 (weights 2^24, 2^16, 2^8, 1) of activation row c/4
+             const float me0 = t == 0 ? 16777216.0f : (t == 1 ? 256.0f : 0.0f), me1 = t == 0 ? 65536.0f : (t == 1 ? 1.0f : 0.0f);
+             const float mo0 = t == 2 ? 16777216.0f : (t == 3 ? 256.0f : 0.0f), mo1 = t == 2 ? 65536.0f : (t == 3 ? 1.0f : 0.0f);
 #pragma unroll
              for (int mg = 0; mg < NG; mg++) {
-#pragma unroll
-                 for (int rh = 0; rh < 2; rh++) {
-                     const float a0 = acc.f[mg][2 * rh], a1 = acc.f[mg][2 * rh + 1];
-                     const float b0 = __shfl_sync(0xFFFFFFFFu, a0, lane_base + 1), b1 = __shfl_sync(0xFFFFFFFFu, a1, lane_base + 1);
-                     const float c0 = __shfl_sync(0xFFFFFFFFu, a0, lane_base + 2), c1 = __shfl_sync(0xFFFFFFFFu, a1, lane_base + 2);
-                     float ve = fmaf(a0, 65536.0f, fmaf(a1, 256.0f, b0));   // activation row 2*mg
-                     float vo = fmaf(b1, 65536.0f, fmaf(c0, 256.0f, c1));   // activation row 2*mg + 1
-                     float me = 0.0f, mo = 0.0f;
-                     if (WT == KRK_CUDA_Q4_K) {
-                         me = acc.m[rh][2 * mg];
-                         mo = acc.m[rh][2 * mg + 1];
-                         me += __shfl_xor_sync(0xFFFFFFFFu, me, 1);
-                         mo += __shfl_xor_sync(0xFFFFFFFFu, mo, 1);
-                         me += __shfl_xor_sync(0xFFFFFFFFu, me, 2);
-                         mo += __shfl_xor_sync(0xFFFFFFFFu, mo, 2);
-                     }
-                     if (t == 0 && wid < n_warps) {
-                         const int row = g + 8 * rh;
-                         if (2 * mg < p.rows) sm->red[buf][wid][row][2 * mg] = fmaf(ve, sm->xscale[2 * mg], -me);
-                         if (2 * mg + 1 < p.rows) sm->red[buf][wid][row][2 * mg + 1] = fmaf(vo, sm->xscale[2 * mg + 1], -mo);
-                     }
+                 float4 o;
+                 o.x = fmaf(we0, acc.f[mg][0], we1 * acc.f[mg][1]);   // row g,   even activation row
+                 o.y = fmaf(wo0, acc.f[mg][0], wo1 * acc.f[mg][1]);   // row g,   odd
+                 o.z = fmaf(we0, acc.f[mg][2], we1 * acc.f[mg][3]);   // row g+8, even
+                 o.w = fmaf(wo0, acc.f[mg][2], wo1 * acc.f[mg][3]);   // row g+8, odd
+                 if (WT == KRK_CUDA_Q4_K) {
+                     o.x -= fmaf(me0, acc.m[mg][0], me1 * acc.m[mg][1]);
+                     o.y -= fmaf(mo0, acc.m[mg][0], mo1 * acc.m[mg][1]);
+                     o.z -= fmaf(me0, acc.m[mg][2], me1 * acc.m[mg][3]);
+                     o.w -= fmaf(mo0, acc.m[mg][2], mo1 * acc.m[mg][3]);
                  }
+                 o.x *= xs[2 * mg];
+                 o.y *= xs[2 * mg + 1];
+                 o.z *= xs[2 * mg];
+                 o.w *= xs[2 * mg + 1];
+                 sm->red[rslot][wid][mg][lane] = o;
              }
              accum_zero(acc);
-             consumer_barrier();
-             if (tid < kTileRows * p.rows) {
-                 const int row = tid & (kTileRows - 1), r = tid >> 4;
-                 float v = sm->red[buf][0][row][r];
-                 for (int w = 1; w < n_warps; w++) v += sm->red[buf][w][row][r];
-                 if (row < s.n_rows) {
-                     if (p.step == 2 && s.which == 0) {
-                         sm->gate[tid] = v;
-                     } else {
-                         const GemvMat &mat = p.mat[p.step == 2 ? s.mat - 1 : s.mat];
-                         float *y = mat.y + (size_t)r * mat.n_out + s.row0 + row;
-                         if (p.step == 2) {
-                             const float gt = sm->gate[tid];
-                             v = __fmul_rn(__fdiv_rn(gt, __fadd_rn(1.0f, expf(-gt))), v);
-                         }
-                         *y = p.accumulate ? __fadd_rn(*y, v) : v;
-                     }
-                 }
-             }
-         });
+             __syncwarp();
+             if (lane == 0) mbar_arrive(smem_u32(&sm->red_full[rslot]));
+            }
+        }
+    }
 }
 
 template <int WT, int NG>
@@ -660,9 +798,24 @@ int launch_one(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
         }
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kernel<<<grid, kThreads, smem, st>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, p);
     note_launch(1, KRK_CUDA_FAMILY_GEMV_STREAM);
-    return check_launch();
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        (void)cudaGetLastError();
+        return KRK_CUDA_ELAUNCH;
+    }
+    return KRK_CUDA_OK;
 }
 
 template <int WT>
@@ -694,7 +847,8 @@ int launch_fmt(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accum
         p.row_stride = raw + ((F::stride_mod - raw % 128) + 128) % 128;
         p.stage_bytes = align_up(kTileRows * p.row_stride, 128);
     }
-    const int fixed = align_up((int)sizeof(Smem), 128) + plane_bytes<WT>(p.n_in, rows) + chunk_sum_bytes<WT>(p.n_in, rows);
+    const int smem_struct = rows <= 2 ? (int)sizeof(Smem<1>) : rows <= 4 ? (int)sizeof(Smem<2>) : (int)sizeof(Smem<4>);
+    const int fixed = align_up(smem_struct, 128) + plane_bytes<WT>(p.n_in, rows) + chunk_sum_bytes<WT>(p.n_in, rows);
     // Past ~96 KB of staged weights per SM more depth buys nothing.
     const int max_fit = (kSmemLimit - fixed) / p.stage_bytes;
     int want = (96 * 1024 + p.stage_bytes - 1) / p.stage_bytes;
@@ -718,6 +872,8 @@ int launch_fmt(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accum
     if (!p.status) return KRK_CUDA_EDEVICE;
     const int sms = sm_count();
     const int grid = total < sms ? total : sms;
+    p.gran_q = total / grid;
+    p.gran_r = total % grid;
     const size_t smem = (size_t)fixed + (size_t)p.n_stages * p.stage_bytes;
     int rc;
     if (rows <= 2) rc = launch_one<WT, 1>(p, grid, smem, st);
