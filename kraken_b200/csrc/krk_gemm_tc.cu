@@ -1,6 +1,458 @@
-// placeholder until the tcgen05 GEMM lands
+// Prefill GEMM for sm_100a: Y[rows][n_out] = X[rows][n_in] . W^T with W block-quantized in HBM,
+// decoded to f16 K-major tiles in shared memory and contracted on the 5th-generation tensor
+// cores (tcgen05.mma, f32 accumulators in tensor memory).
+//
+// Mapping. The weight tile is the MMA's A operand (128 weight rows = the 128 TMEM lanes), the
+// token tile its B operand (up to 256 tokens = TMEM columns), so a weight tile is decoded once
+// per 256 tokens and the accumulator D[weight row][token] is Y transposed: the epilogue reads one
+// TMEM lane per thread and 32 neighbouring weight rows of one token form one coalesced 128-byte
+// store.
+//
+// One persistent CTA per SM, warp-specialised, everything connected by mbarriers:
+//   warps 0..3  decode: thread r owns weight row r of the tile; it reads that row's raw quantized
+//               bytes of the current 64-value K step straight from global memory (the weights are
+//               read once per token tile, from HBM or L2) and writes 64 f16 values as one 128-byte
+//               row of the A tile in the 128-byte-swizzled K-major layout the MMA descriptor names;
+//   warps 4..7  epilogue: tcgen05.ld of the accumulator (warp w%4 owns TMEM lanes 32*(w%4)..),
+//               f32 stores of Y; two accumulator buffers, so the stores of tile i overlap the MMAs
+//               of tile i+1;
+//   warp 8      TMA producer of the X tile (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast);
+//   warp 9      TMEM allocation and the single thread that issues tcgen05.mma / tcgen05.commit.
+//
+// Same contract as gemm_wmma_kernel of the reference (src/hip/kernels/gemm.hpp:621-970): f16
+// staged operands, f32 accumulation; here the output stays f32.
+//
+// Every mbarrier wait is bounded; a wait that gives up raises the device status word, and the CTA
+// runs to its end without waiting again and frees its tensor memory.
+#include <cuda.h>
+
 #include "krk_common.cuh"
+
 namespace krk_cuda {
-size_t gemm_workspace_bytes(int, int64_t, int64_t) { return 0; }
-int launch_gemm_tc(float *, const void *, int, const uint8_t *, int, int64_t, int64_t, int64_t, void *, cudaStream_t) { return KRK_CUDA_EARG; }
+
+namespace {
+
+constexpr int kTileN = 128;            // weight rows per tile (MMA M)
+constexpr int kMaxTileM = 256;         // tokens per tile (MMA N)
+constexpr int kBK = 64;                // K values per stage: one 128-byte swizzle row of f16
+constexpr int kStages = 4;
+constexpr int kDecodeThreads = 128, kEpilogueThreads = 128;
+constexpr int kThreads = kDecodeThreads + kEpilogueThreads + 64;
+constexpr int kTmemCols = 512;
+constexpr long long kWaitCycles = 4000000000LL;
+
+struct GemmParams {
+    const uint8_t *w;
+    float *y;
+    int64_t n_out, n_in, rows;
+    int tile_m;          // tokens per tile: multiple of 16, <= 256
+    int n_tiles_n, n_tiles_m;
+    int row_bytes;
+    int *status;
+};
+
+struct __align__(1024) GemmSmem {
+    uint8_t a[kStages][kTileN * 128];          // decoded W tiles, [128 rows][64 f16], 128B swizzle
+    uint8_t b[kStages][kMaxTileM * 128];       // X tiles, [tokens][64 f16], 128B swizzle (TMA)
+    unsigned long long full_x[kStages], full_w[kStages], empty[kStages];
+    unsigned long long tmem_full[2], tmem_empty[2];
+    uint32_t tmem_base;
+    int gave_up;
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __noinline__ void wait_slow(uint32_t bar, uint32_t parity, volatile int *gave_up, int *status) {
+    const long long t0 = clock64();
+    for (;;) {
+        for (int i = 0; i < 32; i++) {
+            if (mbar_try_wait(bar, parity)) return;
+            __nanosleep(20);
+        }
+        if (*gave_up) return;
+        if (clock64() - t0 > kWaitCycles) {
+            *gave_up = 1;
+            atomicExch(status, KRK_CUDA_ETIMEOUT);
+            return;
+        }
+    }
+}
+__device__ __forceinline__ void wait_phase(uint32_t bar, uint32_t parity, volatile int *gave_up, int *status) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (*gave_up) return;
+    wait_slow(bar, parity, gave_up, status);
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile of 128-byte rows in the 128-byte swizzle:
+// start address >> 4 in bits 0-13, leading byte offset (unused for this layout) 1 in bits 16-29,
+// stride byte offset 1024 >> 4 (eight rows) in bits 32-45, descriptor version 1 in bits 46-47,
+// layout type 2 (SWIZZLE_128B) in bits 61-63.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::f16: D f32 (bits 4-5 = 1), A and B f16 (0), both K-major (0),
+// N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---- decode of one weight row's 64 values of a K step to f16 --------------------------------------
+// out[j] holds values 2j, 2j+1 (low, high half). f16 arithmetic on exact small integers: the scale
+// products are formed in f32 as the host decoder forms them and rounded to f16 once.
+
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+
+template <int WT>
+__device__ __forceinline__ void decode64(const uint8_t *row, int kstep, uint32_t (&out)[32]);
+
+// Q4_K: K step s covers chunks 2p, 2p+1 (p = s % 4) of super-block s / 4 (src/quant.cpp:437-460).
+template <>
+__device__ __forceinline__ void decode64<KRK_CUDA_Q4_K>(const uint8_t *row, int kstep, uint32_t (&out)[32]) {
+    const uint8_t *b = row + (size_t)(kstep >> 2) * 144;
+    const int p = kstep & 3;
+    const uint4 hdr = *reinterpret_cast<const uint4 *>(b);
+    const uint4 q0 = *reinterpret_cast<const uint4 *>(b + 16 + 32 * p);
+    const uint4 q1 = *reinterpret_cast<const uint4 *>(b + 32 + 32 * p);
+    // 6-bit scales / mins of chunks 2p and 2p+1 out of the 12 packed bytes in hdr.y, hdr.z, hdr.w
+    // (src/quant.cpp:427-435), without taking the address of a register
+    int s0, m0, s1, m1;
+    if (p < 2) {
+        const int sh = 16 * p;
+        s0 = (hdr.y >> sh) & 63;
+        s1 = (hdr.y >> (sh + 8)) & 63;
+        m0 = (hdr.z >> sh) & 63;
+        m1 = (hdr.z >> (sh + 8)) & 63;
+    } else {
+        const int sh = 16 * (p - 2);
+        s0 = ((hdr.w >> sh) & 0xF) | (((hdr.y >> (sh + 6)) & 3) << 4);
+        s1 = ((hdr.w >> (sh + 8)) & 0xF) | (((hdr.y >> (sh + 14)) & 3) << 4);
+        m0 = ((hdr.w >> (sh + 4)) & 0xF) | (((hdr.z >> (sh + 6)) & 3) << 4);
+        m1 = ((hdr.w >> (sh + 12)) & 0xF) | (((hdr.z >> (sh + 14)) & 3) << 4);
+    }
+    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF)));
+    const float dm = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+    const __half2 d0 = __float2half2_rn(__fmul_rn(d, (float)s0)), n0 = __float2half2_rn(-__fmul_rn(dm, (float)m0));
+    const __half2 d1 = __float2half2_rn(__fmul_rn(d, (float)s1)), n1 = __float2half2_rn(-__fmul_rn(dm, (float)m1));
+    const __half2 k1024 = __float2half2_rn(1024.0f);
+    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        // bytes 4i..4i+3 of the 32-byte group: low nibbles are values 4i.. of chunk 2p, high of 2p+1
+        const uint32_t w = qw[i];
+        uint32_t lo01 = (w & 0x0000000Fu) | ((w & 0x00000F00u) << 8) | 0x64006400u;
+        uint32_t lo23 = ((w >> 16) & 0x0000000Fu) | ((w >> 8) & 0x000F0000u) | 0x64006400u;
+        uint32_t hi01 = ((w >> 4) & 0x0000000Fu) | ((w << 4) & 0x000F0000u) | 0x64006400u;
+        uint32_t hi23 = ((w >> 20) & 0x0000000Fu) | ((w >> 12) & 0x000F0000u) | 0x64006400u;
+        out[2 * i] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2 *>(&lo01), k1024), d0, n0));
+        out[2 * i + 1] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2 *>(&lo23), k1024), d0, n0));
+        out[16 + 2 * i] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2 *>(&hi01), k1024), d1, n1));
+        out[16 + 2 * i + 1] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2 *>(&hi23), k1024), d1, n1));
+    }
+}
+
+// The other formats decode through the element decoder (exact f32 value, rounded to f16 once).
+template <int WT>
+__device__ __forceinline__ void decode64(const uint8_t *row, int kstep, uint32_t (&out)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        const float a = decode_value<WT>(row, (int64_t)kstep * kBK + 2 * j);
+        const float c = decode_value<WT>(row, (int64_t)kstep * kBK + 2 * j + 1);
+        out[j] = h2_bits(__floats2half2_rn(a, c));
+    }
+}
+
+// ---- the kernel ------------------------------------------------------------------------------------
+
+template <int WT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap x_map) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    GemmSmem *sm = reinterpret_cast<GemmSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    volatile int *gave_up = &sm->gave_up;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(smem_u32(&sm->full_x[s]), 1);
+            mbar_init(smem_u32(&sm->full_w[s]), kDecodeThreads / 32);
+            mbar_init(smem_u32(&sm->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(smem_u32(&sm->tmem_full[b]), 1);
+            mbar_init(smem_u32(&sm->tmem_empty[b]), kEpilogueThreads / 32);
+        }
+        sm->gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 9) {
+        tmem_alloc(smem_u32(&sm->tmem_base), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sm->tmem_base;
+
+    const int n_tiles = p.n_tiles_n * p.n_tiles_m;
+    const int k_steps = (int)(p.n_in / kBK);
+
+    if (warp < 4) {
+        // ===== decode warps: thread r <-> weight row r of the tile =====
+        const int r = tid;
+        int slot = 0;
+        uint32_t phase = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            const int64_t n0 = (int64_t)(tile / p.n_tiles_m) * kTileN;
+            const bool valid = n0 + r < p.n_out;
+            const uint8_t *row = p.w + (size_t)(valid ? n0 + r : 0) * p.row_bytes;
+            for (int ks = 0; ks < k_steps; ks++) {
+                uint32_t v[32];
+                decode64<WT>(row, ks, v);   // global loads and arithmetic first, then wait for the slot
+                wait_phase(smem_u32(&sm->empty[slot]), phase ^ 1, gave_up, p.status);
+                uint8_t *dst = sm->a[slot] + r * 128;
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    // 16-byte chunk c of row r lives at chunk c ^ (r & 7) of that row (128-byte swizzle)
+                    uint4 val = valid ? make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]) : make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4 *>(dst + ((c ^ (r & 7)) << 4)) = val;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the stores visible to the MMA
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sm->full_w[slot]));
+                if (++slot == kStages) {
+                    slot = 0;
+                    phase ^= 1;
+                }
+            }
+        }
+    } else if (warp < 8) {
+        // ===== epilogue warps: TMEM lane = weight row, column = token =====
+        const int ew = warp - 4;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, it++) {
+            const int64_t n0 = (int64_t)(tile / p.n_tiles_m) * kTileN, m0 = (int64_t)(tile % p.n_tiles_m) * p.tile_m;
+            const int buf = it & 1;
+            wait_phase(smem_u32(&sm->tmem_full[buf]), (it >> 1) & 1, gave_up, p.status);
+            tc_fence_after();
+            const int64_t n = n0 + 32 * ew + lane;
+            for (int c0 = 0; c0 < p.tile_m; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(32 * ew) << 16) + (uint32_t)(buf * kMaxTileM + c0), v);
+                tmem_ld_wait();
+                if (n < p.n_out) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int64_t m = m0 + c0 + j;
+                        if (m < p.rows) p.y[m * p.n_out + n] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[buf]));
+        }
+    } else if (warp == 8) {
+        // ===== TMA producer of X tiles =====
+        if (lane == 0) {
+            int slot = 0;
+            uint32_t phase = 0;
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                const int m0 = (tile % p.n_tiles_m) * p.tile_m;
+                for (int ks = 0; ks < k_steps; ks++) {
+                    wait_phase(smem_u32(&sm->empty[slot]), phase ^ 1, gave_up, p.status);
+                    const uint32_t bar = smem_u32(&sm->full_x[slot]);
+                    mbar_arrive_expect_tx(bar, (uint32_t)p.tile_m * 128u);
+                    tma_load_2d(smem_u32(sm->b[slot]), &x_map, ks * kBK, m0, bar);
+                    if (++slot == kStages) {
+                        slot = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else {
+        // ===== MMA issuer =====
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(kTileN, p.tile_m);
+            int slot = 0, it = 0;
+            uint32_t phase = 0;
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, it++) {
+                const int buf = it & 1;
+                wait_phase(smem_u32(&sm->tmem_empty[buf]), ((it >> 1) & 1) ^ 1, gave_up, p.status);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kMaxTileM);
+                for (int ks = 0; ks < k_steps; ks++) {
+                    wait_phase(smem_u32(&sm->full_x[slot]), phase, gave_up, p.status);
+                    wait_phase(smem_u32(&sm->full_w[slot]), phase, gave_up, p.status);
+                    tc_fence_after();
+                    const uint64_t adesc = smem_desc(smem_u32(sm->a[slot])), bdesc = smem_desc(smem_u32(sm->b[slot]));
+#pragma unroll
+                    for (int kk = 0; kk < kBK / 16; kk++)   // +32 bytes (>> 4 = 2) per 16-value K slice inside the swizzle row
+                        umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) ? 1u : 0u);
+                    umma_commit(smem_u32(&sm->empty[slot]));   // frees the stage when these MMAs have read it
+                    if (++slot == kStages) {
+                        slot = 0;
+                        phase ^= 1;
+                    }
+                }
+                umma_commit(smem_u32(&sm->tmem_full[buf]));
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+__global__ void __launch_bounds__(256) f32_to_f16_kernel(__half *__restrict__ out, const float *__restrict__ in, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = __float2half_rn(in[i]);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+template <int WT>
+int launch_wt(const GemmParams &p, const CUtensorMap &map, int grid, cudaStream_t st) {
+    static bool configured[64] = {};
+    auto kernel = gemm_tc_kernel<WT>;
+    const size_t smem = sizeof(GemmSmem) + 1024;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            note_cuda_error(e);
+            return KRK_CUDA_ELAUNCH;
+        }
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    kernel<<<grid, kThreads, smem, st>>>(p, map);
+    note_launch(1, KRK_CUDA_FAMILY_GEMM_TC);
+    return check_launch();
+}
+
+} // namespace
+
+size_t gemm_workspace_bytes(int x_dtype, int64_t n_in, int64_t rows) {
+    return x_dtype == KRK_CUDA_X_F32 ? (size_t)rows * (size_t)n_in * sizeof(__half) : 0;
+}
+
+int launch_gemm_tc(float *y, const void *x, int x_dtype, const uint8_t *w, int wt, int64_t n_out, int64_t n_in,
+                   int64_t rows, void *workspace, cudaStream_t st) {
+    if (rows > (1 << 24) || n_out > (1 << 30) || n_in > (1 << 24)) return KRK_CUDA_ESHAPE;
+    const __half *xh = static_cast<const __half *>(x);
+    if (x_dtype == KRK_CUDA_X_F32) {
+        const int64_t n = rows * n_in;
+        const int64_t want = (n + 255) / 256;
+        const int grid = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
+        f32_to_f16_kernel<<<grid, 256, 0, st>>>(static_cast<__half *>(workspace), static_cast<const float *>(x), n);
+        note_launch();
+        const int rc = check_launch();
+        if (rc != KRK_CUDA_OK) return rc;
+        xh = static_cast<const __half *>(workspace);
+    }
+    GemmParams p;
+    p.w = w;
+    p.y = y;
+    p.n_out = n_out;
+    p.n_in = n_in;
+    p.rows = rows;
+    p.tile_m = rows >= kMaxTileM ? kMaxTileM : (int)((rows + 15) / 16 * 16);
+    p.n_tiles_n = (int)((n_out + kTileN - 1) / kTileN);
+    p.n_tiles_m = (int)((rows + p.tile_m - 1) / p.tile_m);
+    p.row_bytes = (int)row_bytes(wt, n_in);
+    p.status = device_status_word();
+    if (!p.status) return KRK_CUDA_EDEVICE;
+
+    EncodeTiledFn encode = encode_tiled();
+    if (!encode) return KRK_CUDA_EDEVICE;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)n_in, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)n_in * sizeof(__half)};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)p.tile_m};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult cr = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(xh), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return KRK_CUDA_ELAUNCH;
+
+    const int tiles = p.n_tiles_n * p.n_tiles_m;
+    const int sms = sm_count();
+    const int grid = tiles < sms ? tiles : sms;
+    int rc = KRK_CUDA_EDTYPE;
+    KRK_DISPATCH_WT(wt, rc = launch_wt<WT>(p, map, grid, st));
+    return rc;
+}
+
+} // namespace krk_cuda
