@@ -280,12 +280,42 @@ def run_ours(args):
                          },
             "clocks": clocks,
         }
+        if world == 1 and not args.no_extras:
+            line["extra"] = {"prefill": prefill_extra(torch, capi, gen)}
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(sample_seconds=args.cpu_seconds)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def prefill_extra(torch, capi, gen):
+    """Config 3: Q4_K prefill GEMM, N=14336, K=4096, M in {128, 512, 2048}: f16 X, f32 Y, tensor cores.
+    Four weight replicas (132 MB) are rotated so that no launch finds its weights in L2."""
+    n_out, n_in = 14336, 4096
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    ws = [device_weights(torch, n_out, n_in, gen) for _ in range(4)]
+    out = []
+    for rows in (128, 512, 2048):
+        x = torch.randn((rows, n_in), device="cuda", generator=gen).to(torch.float16)
+        y = torch.empty((rows, n_out), device="cuda")
+        for i in range(4):
+            capi.gemm(x, ws[i], WT, n_out, n_in, out=y)
+        torch.cuda.synchronize()
+        reps = 20
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            capi.gemm(x, ws[i % 4], WT, n_out, n_in, out=y)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        tf = 2.0 * rows * n_out * n_in / (ms * 1e-3) / 1e12
+        out.append({"M": rows, "ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_measured_bf16_peak": round(tf / peak, 4)})
+    return {"workload": "q4_k_prefill_gemm_N14336_K4096", "kernel": "gemm_tc_kernel<Q4_K> (tcgen05)", "peak_tflops": peak,
+            "results": out}
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the streaming kernel, from the ncu
@@ -402,6 +432,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the prefill GEMM side measurements")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--layers", type=int, default=N_LAYERS,
                     help="layers per step; fewer than 32 is for profiler captures only, not a bench value")

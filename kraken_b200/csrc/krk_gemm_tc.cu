@@ -9,15 +9,17 @@
 // store.
 //
 // One persistent CTA per SM, warp-specialised, everything connected by mbarriers:
-//   warps 0..3  decode: thread r owns weight row r of the tile; it reads that row's raw quantized
-//               bytes of the current 64-value K step straight from global memory (the weights are
-//               read once per token tile, from HBM or L2) and writes 64 f16 values as one 128-byte
-//               row of the A tile in the 128-byte-swizzled K-major layout the MMA descriptor names;
-//   warps 4..7  epilogue: tcgen05.ld of the accumulator (warp w%4 owns TMEM lanes 32*(w%4)..),
-//               f32 stores of Y; two accumulator buffers, so the stores of tile i overlap the MMAs
-//               of tile i+1;
-//   warp 8      TMA producer of the X tile (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast);
-//   warp 9      TMEM allocation and the single thread that issues tcgen05.mma / tcgen05.commit.
+//   warps 0..7   decode: two threads per weight row of the tile, 32 values each per 64-value K step;
+//                a thread reads the row's raw quantized bytes straight from global memory (a
+//                super-block ahead, into registers; the weights are read once per token tile, from
+//                HBM or L2) and writes 32 f16 values as half of a 128-byte row of the A tile in the
+//                128-byte-swizzled K-major layout the MMA descriptor names; two K steps are
+//                written per proxy fence;
+//   warps 8..11  epilogue: tcgen05.ld of the accumulator (warp w%4 owns TMEM lanes 32*(w%4)..),
+//                f32 stores of Y; two accumulator buffers, so the stores of tile i overlap the MMAs
+//                of tile i+1;
+//   warp 12      TMA producer of the X tile (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast);
+//   warp 13      TMEM allocation and the single thread that issues tcgen05.mma / tcgen05.commit.
 //
 // Same contract as gemm_wmma_kernel of the reference (src/hip/kernels/gemm.hpp:621-970): f16
 // staged operands, f32 accumulation; here the output stays f32.
@@ -36,7 +38,7 @@ constexpr int kTileN = 128;            // weight rows per tile (MMA M)
 constexpr int kMaxTileM = 256;         // tokens per tile (MMA N)
 constexpr int kBK = 64;                // K values per stage: one 128-byte swizzle row of f16
 constexpr int kStages = 4;
-constexpr int kDecodeThreads = 128, kEpilogueThreads = 128;
+constexpr int kDecodeThreads = 256, kEpilogueThreads = 128;   // two decode threads per weight row
 constexpr int kThreads = kDecodeThreads + kEpilogueThreads + 64;
 constexpr int kTmemCols = 512;
 constexpr long long kWaitCycles = 4000000000LL;
@@ -148,70 +150,76 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// ---- decode of one weight row's 64 values of a K step to f16 --------------------------------------
-// out[j] holds values 2j, 2j+1 (low, high half). f16 arithmetic on exact small integers: the scale
-// products are formed in f32 as the host decoder forms them and rounded to f16 once.
+// ---- decode of half a weight row's K step (32 values) to f16 ---------------------------------------
+// A decode thread first LOADS the raw bytes it needs (Raw), ahead of time, and later CONVERTS
+// them: out[j] holds values 2j, 2j+1 (low, high half) of its 32. f16 arithmetic runs on exact
+// small integers; the scale products are formed in f32 as the host decoder forms them and rounded
+// to f16 once.
 
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
 
 template <int WT>
-__device__ __forceinline__ void decode64(const uint8_t *row, int kstep, uint32_t (&out)[32]);
+struct Raw {   // formats without a fast path keep only the row pointer and decode element by element
+    static constexpr int kSteps = 2;   // K steps covered by one load()
+    const uint8_t *row;
+    int kstep;
+    __device__ __forceinline__ void load(const uint8_t *r, int ks) {
+        row = r;
+        kstep = ks;
+    }
+    __device__ __forceinline__ void convert(int j, int half, uint32_t (&out)[16]) const {
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int64_t k = (int64_t)(kstep + j) * kBK + 32 * half + 2 * i;
+            out[i] = h2_bits(__floats2half2_rn(decode_value<WT>(row, k), decode_value<WT>(row, k + 1)));
+        }
+    }
+};
 
-// Q4_K: K step s covers chunks 2p, 2p+1 (p = s % 4) of super-block s / 4 (src/quant.cpp:437-460).
+// Q4_K: one load() fetches a whole 144-byte super-block = four K steps, so the fetch of the next
+// super-block is in flight for four steps (longer than an HBM round trip). K step p of the block
+// covers chunks 2p, 2p+1: the low and the high nibbles of the same 32 bytes
+// (src/quant.cpp:437-460). Thread half h converts chunk 2p+h.
 template <>
-__device__ __forceinline__ void decode64<KRK_CUDA_Q4_K>(const uint8_t *row, int kstep, uint32_t (&out)[32]) {
-    const uint8_t *b = row + (size_t)(kstep >> 2) * 144;
-    const int p = kstep & 3;
-    const uint4 hdr = *reinterpret_cast<const uint4 *>(b);
-    const uint4 q0 = *reinterpret_cast<const uint4 *>(b + 16 + 32 * p);
-    const uint4 q1 = *reinterpret_cast<const uint4 *>(b + 32 + 32 * p);
-    // 6-bit scales / mins of chunks 2p and 2p+1 out of the 12 packed bytes in hdr.y, hdr.z, hdr.w
-    // (src/quant.cpp:427-435), without taking the address of a register
-    int s0, m0, s1, m1;
-    if (p < 2) {
-        const int sh = 16 * p;
-        s0 = (hdr.y >> sh) & 63;
-        s1 = (hdr.y >> (sh + 8)) & 63;
-        m0 = (hdr.z >> sh) & 63;
-        m1 = (hdr.z >> (sh + 8)) & 63;
-    } else {
-        const int sh = 16 * (p - 2);
-        s0 = ((hdr.w >> sh) & 0xF) | (((hdr.y >> (sh + 6)) & 3) << 4);
-        s1 = ((hdr.w >> (sh + 8)) & 0xF) | (((hdr.y >> (sh + 14)) & 3) << 4);
-        m0 = ((hdr.w >> (sh + 4)) & 0xF) | (((hdr.z >> (sh + 6)) & 3) << 4);
-        m1 = ((hdr.w >> (sh + 12)) & 0xF) | (((hdr.z >> (sh + 14)) & 3) << 4);
-    }
-    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF)));
-    const float dm = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-    const __half2 d0 = __float2half2_rn(__fmul_rn(d, (float)s0)), n0 = __float2half2_rn(-__fmul_rn(dm, (float)m0));
-    const __half2 d1 = __float2half2_rn(__fmul_rn(d, (float)s1)), n1 = __float2half2_rn(-__fmul_rn(dm, (float)m1));
-    const __half2 k1024 = __float2half2_rn(1024.0f);
-    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+struct Raw<KRK_CUDA_Q4_K> {
+    static constexpr int kSteps = 4;
+    uint4 hdr, q[8];
+    __device__ __forceinline__ void load(const uint8_t *row, int ks) {
+        const uint4 *b = reinterpret_cast<const uint4 *>(row + (size_t)(ks >> 2) * 144);
+        hdr = b[0];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        // bytes 4i..4i+3 of the 32-byte group: low nibbles are values 4i.. of chunk 2p, high of 2p+1
-        const uint32_t w = qw[i];
-        uint32_t lo01 = (w & 0x0000000Fu) | ((w & 0x00000F00u) << 8) | 0x64006400u;
-        uint32_t lo23 = ((w >> 16) & 0x0000000Fu) | ((w >> 8) & 0x000F0000u) | 0x64006400u;
-        uint32_t hi01 = ((w >> 4) & 0x0000000Fu) | ((w << 4) & 0x000F0000u) | 0x64006400u;
-        uint32_t hi23 = ((w >> 20) & 0x0000000Fu) | ((w >> 12) & 0x000F0000u) | 0x64006400u;
-        out[2 * i] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2 *>(&lo01), k1024), d0, n0));
-        out[2 * i + 1] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2 *>(&lo23), k1024), d0, n0));
-        out[16 + 2 * i] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2 *>(&hi01), k1024), d1, n1));
-        out[16 + 2 * i + 1] = h2_bits(__hfma2(__hsub2(*reinterpret_cast<__half2 *>(&hi23), k1024), d1, n1));
+        for (int i = 0; i < 8; i++) q[i] = b[1 + i];
     }
-}
-
-// The other formats decode through the element decoder (exact f32 value, rounded to f16 once).
-template <int WT>
-__device__ __forceinline__ void decode64(const uint8_t *row, int kstep, uint32_t (&out)[32]) {
+    __device__ __forceinline__ void convert(int p, int half, uint32_t (&out)[16]) const {
+        // 6-bit scale / min of chunk c = 2p + half out of the 12 packed bytes in hdr.y, hdr.z, hdr.w
+        // (src/quant.cpp:427-435)
+        const int c = 2 * p + half;
+        int sc, mn;
+        if (c < 4) {
+            sc = (hdr.y >> (8 * c)) & 63;
+            mn = (hdr.z >> (8 * c)) & 63;
+        } else {
+            const int sh = 8 * (c - 4);
+            sc = ((hdr.w >> sh) & 0xF) | (((hdr.y >> (sh + 6)) & 3) << 4);
+            mn = ((hdr.w >> (sh + 4)) & 0xF) | (((hdr.z >> (sh + 6)) & 3) << 4);
+        }
+        const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF)));
+        const float dm = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+        const __half2 dl = __float2half2_rn(__fmul_rn(d, (float)sc)), ml = __float2half2_rn(-__fmul_rn(dm, (float)mn));
+        const __half2 k1024 = __float2half2_rn(1024.0f);
+        const uint32_t qw[8] = {q[2 * p].x, q[2 * p].y, q[2 * p].z, q[2 * p].w, q[2 * p + 1].x, q[2 * p + 1].y, q[2 * p + 1].z, q[2 * p + 1].w};
+        const int shift = 4 * half;
 #pragma unroll
-    for (int j = 0; j < 32; j++) {
-        const float a = decode_value<WT>(row, (int64_t)kstep * kBK + 2 * j);
-        const float c = decode_value<WT>(row, (int64_t)kstep * kBK + 2 * j + 1);
-        out[j] = h2_bits(__floats2half2_rn(a, c));
+        for (int i = 0; i < 8; i++) {
+            // bytes 4i..4i+3 hold values 4i..4i+3 of the chunk; 0x6400 | q is the half 1024 + q
+            const uint32_t t = (qw[i] >> shift) & 0x0F0F0F0Fu;
+            const uint32_t v01 = __byte_perm(t, 0x64646464u, 0x5140), v23 = __byte_perm(t, 0x64646464u, 0x7362);
+            out[2 * i] = h2_bits(__hfma2(__hsub2(bits_h2(v01), k1024), dl, ml));
+            out[2 * i + 1] = h2_bits(__hfma2(__hsub2(bits_h2(v23), k1024), dl, ml));
+        }
     }
-}
+};
 
 // ---- the kernel ------------------------------------------------------------------------------------
 
@@ -237,7 +245,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 9) {
+    if (warp == 13) {
         tmem_alloc(smem_u32(&sm->tmem_base), kTmemCols);
         tmem_relinquish();
     }
@@ -249,38 +257,57 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     const int n_tiles = p.n_tiles_n * p.n_tiles_m;
     const int k_steps = (int)(p.n_in / kBK);
 
-    if (warp < 4) {
-        // ===== decode warps: thread r <-> weight row r of the tile =====
-        const int r = tid;
+    if (warp < 8) {
+        // ===== decode warps: threads r and r + 128 <-> weight row r of the tile, 32 values each =====
+        const int r = tid & 127, half = tid >> 7;
         int slot = 0;
         uint32_t phase = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
             const int64_t n0 = (int64_t)(tile / p.n_tiles_m) * kTileN;
             const bool valid = n0 + r < p.n_out;
             const uint8_t *row = p.w + (size_t)(valid ? n0 + r : 0) * p.row_bytes;
-            for (int ks = 0; ks < k_steps; ks++) {
-                uint32_t v[32];
-                decode64<WT>(row, ks, v);   // global loads and arithmetic first, then wait for the slot
-                wait_phase(smem_u32(&sm->empty[slot]), phase ^ 1, gave_up, p.status);
-                uint8_t *dst = sm->a[slot] + r * 128;
+            Raw<WT> cur, nxt;
+            cur.load(row, 0);
+            for (int ks0 = 0; ks0 < k_steps; ks0 += Raw<WT>::kSteps) {
+                if (ks0 + Raw<WT>::kSteps < k_steps) nxt.load(row, ks0 + Raw<WT>::kSteps);   // in flight while this block converts
 #pragma unroll
-                for (int c = 0; c < 8; c++) {
-                    // 16-byte chunk c of row r lives at chunk c ^ (r & 7) of that row (128-byte swizzle)
-                    uint4 val = valid ? make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]) : make_uint4(0, 0, 0, 0);
-                    *reinterpret_cast<uint4 *>(dst + ((c ^ (r & 7)) << 4)) = val;
+                for (int j = 0; j < Raw<WT>::kSteps; j += 2) {
+                    // two K steps per proxy fence: both are converted, written to their stages, fenced once
+                    // and then announced (n_in is a multiple of 256, so K steps come in fours)
+                    uint32_t v[2][16];
+                    cur.convert(j, half, v[0]);
+                    cur.convert(j + 1, half, v[1]);
+                    int slots[2];
+#pragma unroll
+                    for (int u = 0; u < 2; u++) {
+                        wait_phase(smem_u32(&sm->empty[slot]), phase ^ 1, gave_up, p.status);
+                        uint8_t *dst = sm->a[slot] + r * 128;
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            // 16-byte chunk 4*half + c of row r lives at chunk (4*half + c) ^ (r & 7) (128-byte swizzle)
+                            const uint4 val = valid ? make_uint4(v[u][4 * c], v[u][4 * c + 1], v[u][4 * c + 2], v[u][4 * c + 3])
+                                                    : make_uint4(0, 0, 0, 0);
+                            *reinterpret_cast<uint4 *>(dst + (((4 * half + c) ^ (r & 7)) << 4)) = val;
+                        }
+                        slots[u] = slot;
+                        if (++slot == kStages) {
+                            slot = 0;
+                            phase ^= 1;
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the stores visible to the MMA
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(smem_u32(&sm->full_w[slots[0]]));
+                        mbar_arrive(smem_u32(&sm->full_w[slots[1]]));
+                    }
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the stores visible to the MMA
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&sm->full_w[slot]));
-                if (++slot == kStages) {
-                    slot = 0;
-                    phase ^= 1;
-                }
+                cur = nxt;
             }
         }
-    } else if (warp < 8) {
+    } else if (warp < 12) {
         // ===== epilogue warps: TMEM lane = weight row, column = token =====
-        const int ew = warp - 4;
+        const int ew = warp - 8;
         int it = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, it++) {
             const int64_t n0 = (int64_t)(tile / p.n_tiles_m) * kTileN, m0 = (int64_t)(tile % p.n_tiles_m) * p.tile_m;
@@ -304,7 +331,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[buf]));
         }
-    } else if (warp == 8) {
+    } else if (warp == 12) {
         // ===== TMA producer of X tiles =====
         if (lane == 0) {
             int slot = 0;
@@ -355,7 +382,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == 13) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
