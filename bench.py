@@ -176,6 +176,7 @@ def run_ours(args):
     # order, without a host round trip per launch (a decode loop replays a fixed launch sequence).
     launches_per_step = 4 * args.layers
     replay = step
+    graph_holder = []
     if not args.no_graph:
         cap_stream = torch.cuda.Stream()
         cap_stream.wait_stream(stream)
@@ -189,6 +190,7 @@ def run_ours(args):
             graph.capture_end()
         launches_per_step = capi.launch_count() - c0
         stream = cap_stream
+        graph_holder.append(graph)
 
         def replay():
             graph.replay()
@@ -246,10 +248,15 @@ def run_ours(args):
     be.release(d_y)
     be.close()
 
-    if world > 1:
-        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+    def reduce_max(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = t.tolist()
+        return float(t.item())
+
+    ms, e2e_ms = reduce_max(ms), reduce_max(e2e_ms)
+    sharded = None if args.no_extras else sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max)
 
     if rank == 0:
         wbytes = layer_weight_bytes() * args.layers
@@ -280,6 +287,8 @@ def run_ours(args):
                          },
             "clocks": clocks,
         }
+        if sharded is not None:
+            line["sharded"] = sharded
         if world == 1 and not args.no_extras:
             line["extra"] = {"prefill": prefill_extra(torch, capi, gen)}
         if world == 1 and not args.no_cpu:
@@ -288,6 +297,95 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def device_weights_q6k(torch, n_out: int, n_in: int, gen):
+    """Q6_K blocks made on the device: ql/qh bytes uniform (6-bit q uniform), int8 sub-scales uniform in
+    [-64, 63], d in [1e-4, 2e-3] as f16."""
+    nblk = n_in // 256
+    w = torch.randint(0, 256, (n_out, nblk, 210), dtype=torch.uint8, device="cuda", generator=gen)
+    w[..., 192:208] = ((w[..., 192:208] & 127).to(torch.int16) - 64).to(torch.int8).view(torch.uint8)
+    d = (1e-4 + 1.9e-3 * torch.rand((n_out, nblk), device="cuda", generator=gen)).to(torch.float16)
+    w[..., 208:210] = d.view(torch.uint8).view(n_out, nblk, 2)
+    return w.view(n_out, nblk * 210)
+
+
+def timed(torch, fn, reps, barrier):
+    """Device time per call of fn(i), events on the current stream, after 3 warm-up calls."""
+    for i in range(3):
+        fn(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        fn(i)
+    e1.record()
+    barrier()
+    return e0.elapsed_time(e1) / reps
+
+
+def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
+    """Configs 4 and 5 over `world` GPUs (world = 1 gives the unsharded numbers the others scale from).
+
+    Head: Q6_K 128256 x 4096, rows split over the ranks, logits all-gathered. Weights of a rank are
+    replicated R times in HBM and rotated so that a call never finds them in L2.
+    MoE: 128 experts, top-8, hidden 4096, expert width 1536 (gate/up Q4_K, down Q6_K), experts split
+    over the ranks, partial sums all-gathered and added in rank order; batch 1 and batch 8, sixteen
+    different tokens rotated so that successive calls hit different experts."""
+    from kraken_b200 import shard
+    out = {"n_gpus": world}
+    # ---- head ----
+    n_out, n_in = 128256, 4096
+    begin, count = shard.row_range(n_out, world, rank, 8)
+    slice_bytes = count * synth.row_bytes(synth.Q6_K, n_in)
+    n_rep = max(2, int(4 * 126e6 / slice_bytes) + 1)
+    ws = [device_weights_q6k(torch, count, n_in, gen) for _ in range(n_rep)]
+    x = torch.randn((1, n_in), device="cuda", generator=torch.Generator(device="cuda").manual_seed(11))
+    state = {"w": ws[0]}
+    head = shard.ShardedHead(n_out, lambda v: capi.gemv(v, state["w"], synth.Q6_K, count, n_in), align=8)
+
+    def head_call(i):
+        state["w"] = ws[i % n_rep]
+        return head.forward(x)
+
+    def head_local(i):
+        return capi.gemv(x, ws[i % n_rep], synth.Q6_K, count, n_in)
+    ms_full = reduce_max(timed(torch, head_call, 50, barrier))
+    ms_local = reduce_max(timed(torch, head_local, 50, barrier))
+    wbytes = n_out * synth.row_bytes(synth.Q6_K, n_in)
+    out["head_q6_k_128256x4096"] = {
+        "ms_per_token": round(ms_full, 5), "ms_gemv_only": round(ms_local, 5),
+        "weight_gbps_all_gpus": round(wbytes / (ms_full * 1e-3) / 1e9, 1),
+        "weight_gbps_gemv_only": round(wbytes / (ms_local * 1e-3) / 1e9, 1),
+        "rows_per_gpu": count, "gathered_bytes": n_out * 4, "replicas_rotated": n_rep}
+    del ws
+    # ---- MoE ----
+    n_embd, n_ff, n_exp, k = 4096, 1536, 128, 8
+    base, n_local = shard.expert_range(n_exp, world, rank)
+    gate = device_weights(torch, n_local * n_ff, n_embd, gen)
+    up = device_weights(torch, n_local * n_ff, n_embd, gen)
+    down = device_weights_q6k(torch, n_local * n_embd, n_ff, gen)
+    bank = capi.make_bank(gate, up, down, synth.Q4_K, synth.Q6_K, n_local, base, n_embd, n_ff)
+    rgen = torch.Generator(device="cuda").manual_seed(12)          # the same tokens and logits on every rank
+    toks = torch.randn((16, 8, n_embd), device="cuda", generator=rgen)
+    logits = torch.randn((16, 8, n_exp), device="cuda", generator=rgen)
+    route_fn, local_fn, combine_fn = shard.cuda_moe_fns(bank, k)
+    moe = shard.ShardedMoE(n_exp, route_fn, local_fn, combine_fn)
+    per_expert = 2 * n_ff * synth.row_bytes(synth.Q4_K, n_embd) + n_embd * synth.row_bytes(synth.Q6_K, n_ff)
+    for batch in (1, 8):
+        def moe_call(i):
+            return moe.forward(toks[i % 16, :batch], logits[i % 16, :batch])
+        ms = reduce_max(timed(torch, moe_call, 32, barrier))
+        distinct = []
+        for i in range(16):
+            ids, _ = capi.route(logits[i, :batch], k)
+            distinct.append(len(set(ids.cpu().reshape(-1).tolist())))
+        mean_distinct = sum(distinct) / len(distinct)
+        out[f"moe_qwen3_top8_batch{batch}"] = {
+            "ms_per_step": round(ms, 5), "distinct_experts_mean": round(mean_distinct, 2),
+            "expert_weight_gbps_all_gpus": round(mean_distinct * per_expert / (ms * 1e-3) / 1e9, 1),
+            "experts_per_gpu": n_local}
+    return out
 
 
 def prefill_extra(torch, capi, gen):

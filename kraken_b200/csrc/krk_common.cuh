@@ -133,6 +133,17 @@ struct GemvMat {
     int wt;
 };
 
+// A list of single-row GEMVs in device memory, for launches whose matrices are chosen on the device
+// (the routed experts). Entries are matrices, or gate/up pairs (2 matrices per entry); gran_begin is
+// the running count of row granules (see stream_gran) before each entry.
+constexpr int kStreamTableEntries = 64;
+struct StreamTable {
+    GemvMat mat[2 * kStreamTableEntries];
+    int gran_begin[kStreamTableEntries + 1];
+    int n_entries;
+    int total_gran;
+};
+
 // Reference-shaped kernel (one warp per output row): takes every legal shape.
 int launch_gemv_generic(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accumulate,
                         int silu_pair, cudaStream_t st);
@@ -140,6 +151,13 @@ int launch_gemv_generic(const GemvMat *mats, int n_mat, int64_t n_in, int rows, 
 // the launch, 0 when the shape is outside what it addresses (nothing launched), < 0 on error.
 int launch_gemv_stream(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accumulate,
                        int silu_pair, cudaStream_t st);
+
+// Rows per granule the streaming kernel splits matrices of this type and width by (1 or 8), or 0 when
+// it does not address the shape (then the shape-agnostic kernels serve it).
+int stream_gran(int wt, int64_t n_in);
+// The streaming kernel over a device-side table (one activation row per matrix; all matrices of type
+// wt and width n_in). Returns 1 when launched, 0 when the shape is not addressed, < 0 on error.
+int launch_gemv_stream_table(const StreamTable *table, int wt, int64_t n_in, int silu_pair, cudaStream_t st);
 
 int launch_silu_mul(float *out, const float *gate, const float *up, int64_t n, cudaStream_t st);
 int launch_scatter_axpy_rows(float *dst, const float *src, const int32_t *rows, const float *alpha,

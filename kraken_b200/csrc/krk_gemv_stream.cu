@@ -68,6 +68,7 @@ struct StreamParams {
     int n_stages;
     int total_gran;
     int gran_q, gran_r;   // total_gran = grid * gran_q + gran_r
+    const StreamTable *dev_table;   // when set, matrices and granule prefix come from device memory
     int *status;
 };
 
@@ -176,20 +177,49 @@ struct StageInfo {
     int phase;      // parity of the slot's current use
 };
 
+// Where the list of matrices lives: the kernel parameters (host-built launches) or a table in
+// device memory written by an earlier kernel (the routed-expert launches, whose matrices depend on
+// expert ids that never leave the device).
+struct TableView {
+    const GemvMat *mat;
+    const int *gran_begin;
+    int n_entries;
+    int gran_q, gran_r;
+};
+
+__device__ __forceinline__ TableView table_view(const StreamParams &p) {
+    TableView tv;
+    if (p.dev_table) {
+        tv.mat = p.dev_table->mat;
+        tv.gran_begin = p.dev_table->gran_begin;
+        tv.n_entries = p.dev_table->n_entries;
+        const int total = p.dev_table->total_gran;
+        tv.gran_q = total / (int)gridDim.x;
+        tv.gran_r = total % (int)gridDim.x;
+    } else {
+        tv.mat = p.mat;
+        tv.gran_begin = p.gran_begin;
+        tv.n_entries = p.n_entries;
+        tv.gran_q = p.gran_q;
+        tv.gran_r = p.gran_r;
+    }
+    return tv;
+}
+
 template <class SegmentFn, class StageFn>
-__device__ __forceinline__ void walk(const StreamParams &p, SegmentFn &&on_segment, StageFn &&on_stage) {
+__device__ __forceinline__ void walk(const StreamParams &p, const TableView &tv, SegmentFn &&on_segment, StageFn &&on_stage) {
     // balanced split of the granules over the CTAs: the first gran_r CTAs take one more
     const int c = (int)blockIdx.x;
-    const int g0 = c * p.gran_q + min(c, p.gran_r);
-    const int g1 = g0 + p.gran_q + (c < p.gran_r ? 1 : 0);
+    const int g0 = c * tv.gran_q + min(c, tv.gran_r);
+    const int g1 = g0 + tv.gran_q + (c < tv.gran_r ? 1 : 0);
     const int ku_max = p.whole_tiles ? p.units : kConsumerWarps;
     int slot = 0, phase = 0;
-    for (int e = 0; e < p.n_entries; e++) {
-        const int lo = max(g0, p.gran_begin[e]), hi = min(g1, p.gran_begin[e + 1]);
+    for (int e = 0; e < tv.n_entries; e++) {
+        const int lo = max(g0, tv.gran_begin[e]), hi = min(g1, tv.gran_begin[e + 1]);
         if (lo >= hi) continue;
-        const int n_out = (int)p.mat[e * p.step].n_out;
-        const int r0 = (lo - p.gran_begin[e]) * p.gran;
-        const int r1 = min(n_out, (hi - p.gran_begin[e]) * p.gran);
+        const int n_out = (int)tv.mat[e * p.step].n_out;
+        const int r0 = (lo - tv.gran_begin[e]) * p.gran;
+        const int r1 = min(n_out, (hi - tv.gran_begin[e]) * p.gran);
         on_segment(e * p.step);
         for (int tr = r0; tr < r1; tr += kTileRows) {
             for (int which = 0; which < p.step; which++) {
@@ -590,6 +620,9 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     // this same kernel, its weight prefetch) as soon as every CTA here has passed this point and an
     // SM has room; it still waits for this grid to complete before touching activations or outputs.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // A device-side table is the output of the kernel before this one: every role waits for that grid.
+    if (p.dev_table) asm volatile("griddepcontrol.wait;" ::: "memory");
+    const TableView tv = table_view(p);
     if (tid == 0) {
         for (int s = 0; s < p.n_stages; s++) {
             mbar_init(smem_u32(&sm->full[s]), 1);
@@ -614,7 +647,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         constexpr int kSlots = red_slots(NG);
         float gate[NG];   // gate tile kept for the silu fold
         int tile_it = 0;
-        walk(p, [](int) {}, [&](const StageInfo &s) {
+        walk(p, tv, [](int) {}, [&](const StageInfo &s) {
             if (!s.last) return;
             const int slot = tile_it % kSlots;
             wait_phase(smem_u32(&sm->red_full[slot]), (tile_it / kSlots) & 1, gave_up, p.status);
@@ -635,7 +668,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                     if (p.step == 2 && s.which == 0) {
                         gate[i] = v;
                     } else if (row < s.n_rows) {
-                        const GemvMat &mat = p.mat[p.step == 2 ? s.mat - 1 : s.mat];
+                        const GemvMat &mat = tv.mat[p.step == 2 ? s.mat - 1 : s.mat];
                         float *y = mat.y + (size_t)r * mat.n_out + s.row0 + row;
                         if (p.step == 2) v = __fmul_rn(__fdiv_rn(gate[i], __fadd_rn(1.0f, expf(-gate[i]))), v);
                         *y = p.accumulate ? __fadd_rn(*y, v) : v;
@@ -651,12 +684,12 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     if (tid >= kConsumerThreads) {
         // ===== producer warp: weights only, so it can run ahead of everything else =====
         const int lane = tid - kConsumerThreads;
-        walk(p, [](int) {}, [&](const StageInfo &s) {
+        walk(p, tv, [](int) {}, [&](const StageInfo &s) {
             const int slot = s.slot;
             const uint32_t full = smem_u32(&sm->full[slot]), empty = smem_u32(&sm->empty[slot]);
             wait_phase(empty, s.phase ^ 1, gave_up, p.status);
             uint8_t *dst = stages + (size_t)slot * p.stage_bytes;
-            const uint8_t *src = p.mat[s.mat].w + (size_t)s.row0 * p.row_bytes;
+            const uint8_t *src = tv.mat[s.mat].w + (size_t)s.row0 * p.row_bytes;
             if (!p.whole_tiles) {
                 const uint32_t bytes = (uint32_t)s.n_units * F::unit_bytes;
                 if (lane == 0) mbar_arrive_expect_tx(full, bytes * s.n_rows);
@@ -692,23 +725,23 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     // The same walk as walk() above, written flat: per stage a consumer warp only needs the ring
     // slot and its K unit, not which matrix or rows the tile belongs to.
     const int cta = (int)blockIdx.x;
-    const int g0 = cta * p.gran_q + min(cta, p.gran_r);
-    const int g1 = g0 + p.gran_q + (cta < p.gran_r ? 1 : 0);
+    const int g0 = cta * tv.gran_q + min(cta, tv.gran_r);
+    const int g1 = g0 + tv.gran_q + (cta < tv.gran_r ? 1 : 0);
     const int n_chunks = p.whole_tiles ? 1 : (p.units + kConsumerWarps - 1) / kConsumerWarps;
     const uint32_t full0 = smem_u32(&sm->full[0]), empty0 = smem_u32(&sm->empty[0]);
     int slot = 0;
     uint32_t phase = 0;
-    for (int e = 0; e < p.n_entries; e++) {
-        const int lo = max(g0, p.gran_begin[e]), hi = min(g1, p.gran_begin[e + 1]);
+    for (int e = 0; e < tv.n_entries; e++) {
+        const int lo = max(g0, tv.gran_begin[e]), hi = min(g1, tv.gran_begin[e + 1]);
         if (lo >= hi) continue;
         const int m = e * p.step;
-        const int r0 = (lo - p.gran_begin[e]) * p.gran;
-        const int r1 = min((int)p.mat[m].n_out, (hi - p.gran_begin[e]) * p.gran);
-        if (p.mat[m].x != prepared) {
+        const int r0 = (lo - tv.gran_begin[e]) * p.gran;
+        const int r1 = min((int)tv.mat[m].n_out, (hi - tv.gran_begin[e]) * p.gran);
+        if (tv.mat[m].x != prepared) {
             // x may be the output of the kernel before this one (and y its input): wait for that grid to
             // complete. Weights are never written by a kernel in flight, so the producer warp does not wait.
             if (prepared == nullptr) asm volatile("griddepcontrol.wait;" ::: "memory");
-            prepared = p.mat[m].x;
+            prepared = tv.mat[m].x;
 #pragma unroll
             for (int r = 0; r < 2 * NG; r++)
                 xs[r] = r < p.rows ? prepare_x_row<WT>(prepared + (size_t)r * p.n_in, p, planes + (size_t)(r * 3) * p.n_in,
@@ -818,23 +851,25 @@ int launch_one(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
     return KRK_CUDA_OK;
 }
 
+// Fills the fields that depend only on the format, the width and the activation row count.
+// Returns false when the streaming kernel does not address the shape.
 template <int WT>
-int launch_fmt(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accumulate, int silu_pair, cudaStream_t st) {
+bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t *smem_out) {
     using F = Fmt<WT>;
-    if (n_in % 256 != 0 || n_in > (1 << 20)) return 0;
-    StreamParams p;
+    if (n_in % 256 != 0 || n_in > (1 << 20) || rows < 1 || rows > KRK_CUDA_MAX_ROWS) return false;
     p.n_in = (int)n_in;
     p.units = (int)(n_in / F::unit_values);
     p.row_bytes = (int)row_bytes(WT, n_in);
     p.rows = rows;
-    p.accumulate = accumulate;
+    p.accumulate = 0;
     p.step = silu_pair ? 2 : 1;
     p.whole_tiles = 0;
     p.gran = 1;
+    p.dev_table = nullptr;
     if (WT == KRK_CUDA_Q6_K && (n_in % 2048) != 0) {
         // 210-byte blocks: rows are 16-byte multiples only for K % 2048 == 0. Otherwise whole 16-row
         // tiles are copied contiguously (needs 4-byte-multiple rows and the tile in one stage).
-        if ((p.row_bytes & 3) != 0 || p.units > kConsumerWarps) return 0;
+        if ((p.row_bytes & 3) != 0 || p.units > kConsumerWarps) return false;
         p.whole_tiles = 1;
         p.gran = 8;
     }
@@ -854,8 +889,24 @@ int launch_fmt(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accum
     int want = (96 * 1024 + p.stage_bytes - 1) / p.stage_bytes;
     want = want < 3 ? 3 : (want > kMaxStages ? kMaxStages : want);
     p.n_stages = want < max_fit ? want : max_fit;
-    if (p.n_stages < 2) return 0;
+    if (p.n_stages < 2) return false;
+    *smem_out = (size_t)fixed + (size_t)p.n_stages * p.stage_bytes;
+    return true;
+}
 
+template <int WT>
+int launch_rows(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
+    if (p.rows <= 2) return launch_one<WT, 1>(p, grid, smem, st);
+    if (p.rows <= 4) return launch_one<WT, 2>(p, grid, smem, st);
+    return launch_one<WT, 4>(p, grid, smem, st);
+}
+
+template <int WT>
+int launch_fmt(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accumulate, int silu_pair, cudaStream_t st) {
+    StreamParams p;
+    size_t smem = 0;
+    if (!setup_format<WT>(p, n_in, rows, silu_pair, &smem)) return 0;
+    p.accumulate = accumulate;
     p.n_entries = 0;
     int total = 0;
     for (int m = 0; m < n_mat; m += p.step) {
@@ -874,12 +925,30 @@ int launch_fmt(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accum
     const int grid = total < sms ? total : sms;
     p.gran_q = total / grid;
     p.gran_r = total % grid;
-    const size_t smem = (size_t)fixed + (size_t)p.n_stages * p.stage_bytes;
-    int rc;
-    if (rows <= 2) rc = launch_one<WT, 1>(p, grid, smem, st);
-    else if (rows <= 4) rc = launch_one<WT, 2>(p, grid, smem, st);
-    else rc = launch_one<WT, 4>(p, grid, smem, st);
+    const int rc = launch_rows<WT>(p, grid, smem, st);
     return rc == KRK_CUDA_OK ? 1 : rc;
+}
+
+template <int WT>
+int launch_table_fmt(const StreamTable *table, int64_t n_in, int silu_pair, cudaStream_t st) {
+    StreamParams p;
+    size_t smem = 0;
+    if (!setup_format<WT>(p, n_in, 1, silu_pair, &smem)) return 0;
+    p.n_entries = 0;
+    p.total_gran = 0;
+    p.gran_q = p.gran_r = 0;
+    p.dev_table = table;
+    p.status = device_status_word();
+    if (!p.status) return KRK_CUDA_EDEVICE;
+    const int rc = launch_rows<WT>(p, sm_count(), smem, st);
+    return rc == KRK_CUDA_OK ? 1 : rc;
+}
+
+template <int WT>
+int gran_fmt(int64_t n_in) {
+    StreamParams p;
+    size_t smem = 0;
+    return setup_format<WT>(p, n_in, 1, 0, &smem) ? p.gran : 0;
 }
 
 } // namespace
@@ -895,6 +964,24 @@ int launch_gemv_stream(const GemvMat *mats, int n_mat, int64_t n_in, int rows, i
     case KRK_CUDA_Q6_K: return launch_fmt<KRK_CUDA_Q6_K>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q8_0: return launch_fmt<KRK_CUDA_Q8_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     default: return 0;   // Q4_0 takes the shape-agnostic kernel
+    }
+}
+
+int launch_gemv_stream_table(const StreamTable *table, int wt, int64_t n_in, int silu_pair, cudaStream_t st) {
+    switch (wt) {
+    case KRK_CUDA_Q4_K: return launch_table_fmt<KRK_CUDA_Q4_K>(table, n_in, silu_pair, st);
+    case KRK_CUDA_Q6_K: return launch_table_fmt<KRK_CUDA_Q6_K>(table, n_in, silu_pair, st);
+    case KRK_CUDA_Q8_0: return launch_table_fmt<KRK_CUDA_Q8_0>(table, n_in, silu_pair, st);
+    default: return 0;
+    }
+}
+
+int stream_gran(int wt, int64_t n_in) {
+    switch (wt) {
+    case KRK_CUDA_Q4_K: return gran_fmt<KRK_CUDA_Q4_K>(n_in);
+    case KRK_CUDA_Q6_K: return gran_fmt<KRK_CUDA_Q6_K>(n_in);
+    case KRK_CUDA_Q8_0: return gran_fmt<KRK_CUDA_Q8_0>(n_in);
+    default: return 0;
     }
 }
 

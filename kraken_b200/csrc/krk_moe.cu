@@ -166,6 +166,54 @@ moe_combine_kernel(const __grid_constant__ MoeParams p) {
     }
 }
 
+// Builds the two device-side matrix tables of the streaming path from the routed expert ids: one
+// gate/up pair and one down matrix per pick this bank holds, ordered by expert id so that an expert
+// picked by several tokens is streamed by neighbouring CTAs at about the same time (its second read
+// comes from L2). One block; picks <= kStreamTableEntries.
+__global__ void __launch_bounds__(kStreamTableEntries)
+moe_plan_kernel(const __grid_constant__ MoeParams p, StreamTable *gate_up, StreamTable *down, int wt_gate_up, int wt_down,
+                size_t rb_gate_up, size_t rb_down, int gran_gate_up, int gran_down) {
+    __shared__ int key[kStreamTableEntries];
+    const int n_pick = p.n_tok * p.k, pick = threadIdx.x;
+    int e = -1;
+    if (pick < n_pick) e = local_expert(p, pick);
+    key[pick] = e >= 0 ? e * kStreamTableEntries + pick : 0x7FFFFFFF;
+    __syncthreads();
+    if (e >= 0) {
+        int rank = 0;
+        for (int j = 0; j < n_pick; j++) rank += key[j] < key[pick];
+        const float *x = p.x + (int64_t)(pick / p.k) * p.n_embd;
+        float *h = p.h + (int64_t)pick * p.n_ff;
+        GemvMat g, u, d;
+        g.w = p.gate + (size_t)e * p.n_ff * rb_gate_up;
+        u.w = p.up + (size_t)e * p.n_ff * rb_gate_up;
+        g.x = u.x = x;
+        g.y = u.y = h;            // the pair's fold writes silu(gate) * up through the gate's pointer
+        g.n_out = u.n_out = p.n_ff;
+        g.wt = u.wt = wt_gate_up;
+        d.w = p.down + (size_t)e * p.n_embd * rb_down;
+        d.x = h;
+        d.y = p.d + (int64_t)pick * p.n_embd;
+        d.n_out = p.n_embd;
+        d.wt = wt_down;
+        gate_up->mat[2 * rank] = g;
+        gate_up->mat[2 * rank + 1] = u;
+        down->mat[rank] = d;
+    }
+    if (threadIdx.x == 0) {
+        int n = 0;
+        for (int j = 0; j < n_pick; j++) n += key[j] != 0x7FFFFFFF;
+        const int gu = (int)((p.n_ff + gran_gate_up - 1) / gran_gate_up), dn = (int)((p.n_embd + gran_down - 1) / gran_down);
+        for (int i = 0; i <= n; i++) {
+            gate_up->gran_begin[i] = i * gu;
+            down->gran_begin[i] = i * dn;
+        }
+        gate_up->n_entries = down->n_entries = n;
+        gate_up->total_gran = n * gu;
+        down->total_gran = n * dn;
+    }
+}
+
 } // namespace
 
 int launch_route(int32_t *ids, float *wts, const float *logits, int64_t n_tok, int n_expert, int k,
@@ -178,8 +226,14 @@ int launch_route(int32_t *ids, float *wts, const float *logits, int64_t n_tok, i
     return check_launch();
 }
 
+static size_t moe_float_bytes(const krk_cuda_expert_bank *bank, int k, int64_t n_tok) {
+    const size_t b = sizeof(float) * (size_t)(n_tok * k) * (size_t)(bank->n_ff + bank->n_embd);
+    return (b + 255) & ~(size_t)255;
+}
+
 size_t moe_workspace_bytes(const krk_cuda_expert_bank *bank, int k, int64_t n_tok) {
-    return sizeof(float) * (size_t)(n_tok * k) * (size_t)(bank->n_ff + bank->n_embd);
+    // per-pick h and d rows, then the two matrix tables of the streaming path
+    return moe_float_bytes(bank, k, n_tok) + 2 * ((sizeof(StreamTable) + 255) & ~(size_t)255);
 }
 
 int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const float *wts,
@@ -202,6 +256,27 @@ int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const f
     p.k = k;
     p.n_tok = (int)n_tok;
     const int picks = (int)(n_tok * k);
+    // Streaming path: the same kernel as the dense decode GEMV, fed from device-side tables.
+    const int gran_gu = stream_gran(bank->wt_gate_up, bank->n_embd), gran_dn = stream_gran(bank->wt_down, bank->n_ff);
+    if (gran_gu > 0 && gran_dn > 0 && picks <= kStreamTableEntries) {
+        uint8_t *tables = static_cast<uint8_t *>(workspace) + moe_float_bytes(bank, k, n_tok);
+        StreamTable *ta = reinterpret_cast<StreamTable *>(tables);
+        StreamTable *tb = reinterpret_cast<StreamTable *>(tables + ((sizeof(StreamTable) + 255) & ~(size_t)255));
+        moe_plan_kernel<<<1, kStreamTableEntries, 0, st>>>(p, ta, tb, bank->wt_gate_up, bank->wt_down,
+                                                            row_bytes(bank->wt_gate_up, bank->n_embd),
+                                                            row_bytes(bank->wt_down, bank->n_ff), gran_gu, gran_dn);
+        note_launch();
+        int rc = check_launch();
+        if (rc != KRK_CUDA_OK) return rc;
+        rc = launch_gemv_stream_table(ta, bank->wt_gate_up, bank->n_embd, 1, st);
+        if (rc < 0) return rc;
+        rc = launch_gemv_stream_table(tb, bank->wt_down, bank->n_ff, 0, st);
+        if (rc < 0) return rc;
+        dim3 grid((unsigned)((bank->n_embd + 255) / 256), (unsigned)n_tok);
+        moe_combine_kernel<<<grid, 256, 0, st>>>(p);
+        note_launch();
+        return check_launch();
+    }
     {
         dim3 grid((unsigned)((bank->n_ff + 7) / 8), (unsigned)picks);
         KRK_DISPATCH_WT(bank->wt_gate_up, moe_gate_up_kernel<WT><<<grid, 256, 0, st>>>(p));

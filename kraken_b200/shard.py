@@ -1,0 +1,164 @@
+"""Sharding of the output head and of the routed-expert bank over the GPUs of one box.
+
+The reference has no multi-GPU path at all (one process, one device, one stream:
+src/hip/backend_hip.hip:5036-5043), so nothing here replaces a reference file; the two
+shardings follow from the shape of the matmul itself:
+
+* output rows are independent dot products (the reference's CPU pool splits them the same way,
+  src/backend_cpu.cpp:1274-1276), so GPU g owns a contiguous block of rows of the head, computes
+  its slice of the logits, and one all-gather over NVLink assembles the row on every rank;
+* experts are independent until the weighted sum, so expert e lives on GPU e // (n_expert/G),
+  every rank runs the same deterministic routing on the replicated logits, computes the partial
+  sum of the picks it holds, and the partials are all-gathered and added in rank order (rank
+  order = ascending expert id blocks, so the result does not depend on timing).
+
+One process per GPU; ``torch.distributed`` carries the collectives (NCCL on GPUs, gloo in the CPU
+tests). The compute is injected as a callable so that the same logic runs over the CUDA library
+(``cuda_head_fn`` / ``cuda_moe_fn``) or, in the tests, over the CPU checker.
+"""
+from __future__ import annotations
+
+from typing import Callable, Tuple
+
+
+def row_range(n: int, world: int, rank: int, align: int = 1) -> Tuple[int, int]:
+    """Contiguous, balanced split of ``n`` rows in units of ``align``: (begin, count) of ``rank``.
+
+    The first ``units % world`` ranks take one more unit; a tail shorter than ``align`` goes to
+    the last non-empty rank. Counts sum to ``n`` and begins are multiples of ``align``.
+    """
+    if world <= 0 or not 0 <= rank < world or n < 0 or align <= 0:
+        raise ValueError("bad split arguments")
+    units = (n + align - 1) // align
+    q, r = divmod(units, world)
+    first = rank * q + min(rank, r)
+    count = q + (1 if rank < r else 0)
+    begin = min(first * align, n)
+    end = min((first + count) * align, n)
+    return begin, end - begin
+
+
+def expert_range(n_expert: int, world: int, rank: int) -> Tuple[int, int]:
+    """(expert_base, n_local): contiguous blocks, ascending with the rank."""
+    return row_range(n_expert, world, rank, 1)
+
+
+class ShardedHead:
+    """logits[rows, n_out] = x . W^T with the rows of W split over the ranks of ``group``.
+
+    ``local_fn(x) -> [rows, count]`` computes this rank's slice (f32). ``forward`` returns the
+    full row on every rank. Slices of unequal length are padded to the longest for the
+    collective and trimmed afterwards.
+    """
+
+    def __init__(self, n_out: int, local_fn: Callable, group=None, align: int = 8):
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n_out = n_out
+        self.ranges = [row_range(n_out, self.world, r, align) for r in range(self.world)]
+        self.begin, self.count = self.ranges[self.rank]
+        self.max_count = max(c for _, c in self.ranges)
+        self.even = all(c == self.max_count for _, c in self.ranges)
+        self.local_fn = local_fn
+        self._gather = None
+
+    def forward(self, x):
+        import torch
+        local = self.local_fn(x)                                   # [rows, count]
+        rows = local.shape[0]
+        if self.world == 1:
+            return local
+        if self._gather is None or self._gather.shape[1] != rows or self._gather.device != local.device:
+            # the collective concatenates along dim 0: [world * rows, max_count], viewed per rank below
+            self._flat = torch.empty((self.world * rows, self.max_count), dtype=local.dtype, device=local.device)
+            self._gather = self._flat.view(self.world, rows, self.max_count)
+            self._pad = torch.zeros((rows, self.max_count), dtype=local.dtype, device=local.device)
+        if self.even:
+            send = local.contiguous()
+        else:
+            self._pad[:, :self.count] = local
+            send = self._pad
+        self.dist.all_gather_into_tensor(self._flat, send, group=self.group)
+        if self.even:
+            return self._gather.permute(1, 0, 2).reshape(rows, self.n_out)
+        return torch.cat([self._gather[r, :, :c] for r, (_, c) in enumerate(self.ranges)], dim=1)
+
+
+class ShardedMoE:
+    """Routed-expert FFN with the expert bank split over the ranks of ``group``.
+
+    ``route_fn(logits) -> (ids, wts)`` is the replicated router; ``local_fn(x, ids, wts) ->
+    [n_tok, n_embd]`` is the partial sum over the picks this rank holds. ``combine_fn(parts) ->
+    [n_tok, n_embd]`` adds the gathered partials ``[world, n_tok, n_embd]`` in rank order.
+    """
+
+    def __init__(self, n_expert: int, route_fn: Callable, local_fn: Callable, combine_fn: Callable = None, group=None):
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n_expert = n_expert
+        self.expert_base, self.n_local = expert_range(n_expert, self.world, self.rank)
+        self.route_fn, self.local_fn = route_fn, local_fn
+        self.combine_fn = combine_fn or sum_in_rank_order
+        self._gather = None
+
+    def forward(self, x, router_logits):
+        import torch
+        ids, wts = self.route_fn(router_logits)
+        part = self.local_fn(x, ids, wts)
+        if self.world == 1:
+            return part
+        if self._gather is None or self._gather.shape[1:] != part.shape or self._gather.device != part.device:
+            self._flat = torch.empty((self.world * part.shape[0],) + tuple(part.shape[1:]), dtype=part.dtype, device=part.device)
+            self._gather = self._flat.view((self.world,) + tuple(part.shape))
+        self.dist.all_gather_into_tensor(self._flat, part.contiguous(), group=self.group)
+        return self.combine_fn(self._gather)
+
+    def picks_per_rank(self, ids):
+        """Histogram of the routed picks over the ranks (the load each GPU carries for this batch)."""
+        flat = ids.reshape(-1).cpu()
+        out = []
+        for r in range(self.world):
+            b, c = expert_range(self.n_expert, self.world, r)
+            out.append(int(((flat >= b) & (flat < b + c)).sum()))
+        return out
+
+
+def sum_in_rank_order(parts):
+    """((p0 + p1) + p2) + ... : a fixed association, identical on every rank and every run."""
+    out = parts[0].clone()
+    for r in range(1, parts.shape[0]):
+        out += parts[r]
+    return out
+
+
+# ---- the CUDA library as the compute ------------------------------------------------------------
+
+def cuda_head_fn(w_local, wt: int, count: int, n_in: int):
+    """local_fn for ShardedHead over libkrk_cuda.so: w_local is this rank's [count, row_bytes] slice."""
+    from . import capi
+
+    def fn(x):
+        return capi.gemv(x, w_local, wt, count, n_in)
+    return fn
+
+
+def cuda_moe_fns(bank, k: int):
+    """(route_fn, local_fn, combine_fn) for ShardedMoE over libkrk_cuda.so; ``bank`` is this rank's
+    capi.ExpertBank (expert_base / n_local already set to this rank's block)."""
+    from . import capi
+
+    def route_fn(logits):
+        return capi.route(logits, k)
+
+    def local_fn(x, ids, wts):
+        return capi.moe_ffn(x, ids, wts, bank)
+
+    def combine_fn(parts):
+        return capi.sum_parts(parts)
+    return route_fn, local_fn, combine_fn
