@@ -47,6 +47,7 @@ extern "C" {
 #define KRK_CUDA_EDEVICE (-7)   /* no sm_100 device is current */
 #define KRK_CUDA_EARG (-8)      /* any other bad argument (n_mat, k, flags) */
 #define KRK_CUDA_ETIMEOUT (-9)  /* a bounded device-side wait gave up; see krk_cuda_device_status() */
+#define KRK_CUDA_ETOOBIG (-10)  /* larger than the fixed scratch of krk_cuda_gemm_f32_static */
 
 #define KRK_CUDA_MAX_GROUP 16   /* matrices per grouped launch */
 #define KRK_CUDA_MAX_ROWS 8     /* activation rows per GEMV launch */
@@ -106,6 +107,24 @@ int krk_cuda_gemv_group(void *const host_y[], const void *const host_x[],
 size_t krk_cuda_gemm_workspace_bytes(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows);
 int krk_cuda_gemm(void *y_f32, const void *x, int x_dtype, const void *w, int wt, int64_t n_out,
                   int64_t n_in, int64_t rows, void *workspace, size_t ws_bytes, void *stream);
+
+/* The f32-activation prefill GEMM for hosts that must not allocate: no counterpart in the reference.
+ * Same result as krk_cuda_gemm(..., KRK_CUDA_X_F32, ...), but the f16 copy of X goes to a fixed 8 MiB
+ * array inside the library's device image instead of a caller workspace, and the call performs no
+ * device allocation of any kind (krk_cuda_gemm itself allocates a 4-byte status word per device on first
+ * use). Meant for an engine that has committed all device memory at load time, or that cannot accept
+ * the implicit device-wide synchronisation of an allocation between decode steps.
+ *  - Limit: rows * n_in <= 4,194,304 values (e.g. 1024 x 4096); beyond it the call returns
+ *    KRK_CUDA_ETOOBIG and launches nothing.
+ *  - The first call on each device looks up the array's device address (with that device current);
+ *    make that first call outside any stream capture.
+ *  - Every device that loads the library carries the 8 MiB until the process exits.
+ *  - All calls on one device share the array: a call rewrites the part it uses before reading it, so
+ *    back-to-back calls on one stream are fine, but two calls whose kernels can overlap on the GPU
+ *    (different streams) race on it. A bounded-wait give-up of this entry's kernels is recorded in a
+ *    word of that array, not in krk_cuda_device_status(). */
+int krk_cuda_gemm_f32_static(void *y_f32, const void *x_f32, const void *w, int wt, int64_t n_out,
+                             int64_t n_in, int64_t rows, void *stream);
 
 /* Router on the device: softmax over n_expert logits per token, k picks of the largest
  * probability (ties to the lower id), weights renormalised over the picks. Replaces the

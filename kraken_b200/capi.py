@@ -55,6 +55,7 @@ SIGNATURES = {
                                    C.POINTER(_i64), _i64, _int, _int, _vp]),
     "krk_cuda_gemm_workspace_bytes": (_sz, [_int, _i64, _i64, _i64]),
     "krk_cuda_gemm": (_int, [_vp, _vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "krk_cuda_gemm_f32_static": (_int, [_vp, _vp, _vp, _int, _i64, _i64, _i64, _vp]),
     "krk_cuda_route": (_int, [_vp, _vp, _vp, _i64, _int, _int, _vp]),
     "krk_cuda_moe_workspace_bytes": (_sz, [C.POINTER(ExpertBank), _int, _i64]),
     "krk_cuda_moe_ffn": (_int, [_vp, _vp, _vp, _vp, C.POINTER(ExpertBank), _int, _i64, _vp, _sz, _vp]),
@@ -166,6 +167,17 @@ def gemm(x, w, wt: int, n_out: int, n_in: int, out=None, workspace=None, stream=
         out = torch.empty((rows, n_out), dtype=torch.float32, device=x.device)
     _check(lib.krk_cuda_gemm(_ptr(out), _ptr(x), x_dtype, _ptr(w), wt, n_out, n_in, rows, _ptr(workspace),
                              workspace.numel() if workspace is not None else 0, _stream_ptr(stream)), "gemm")
+    return out
+
+
+def gemm_f32_static(x, w, wt: int, n_out: int, n_in: int, out=None, stream=None):
+    """krk_cuda_gemm_f32_static: f32 x [rows, n_in] -> f32 [rows, n_out], scratch inside the library."""
+    import torch
+    rows = x.shape[0]
+    if out is None:
+        out = torch.empty((rows, n_out), dtype=torch.float32, device=x.device)
+    _check(lib.krk_cuda_gemm_f32_static(_ptr(out), _ptr(x), _ptr(w), wt, n_out, n_in, rows, _stream_ptr(stream)),
+           "gemm_f32_static")
     return out
 
 

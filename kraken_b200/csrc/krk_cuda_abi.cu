@@ -87,6 +87,7 @@ const char *krk_cuda_strerror(int rc) {
     case KRK_CUDA_EDEVICE: return "no usable CUDA device is current";
     case KRK_CUDA_EARG: return "bad argument";
     case KRK_CUDA_ETIMEOUT: return "a bounded device-side wait gave up";
+    case KRK_CUDA_ETOOBIG: return "problem larger than the fixed scratch array of the no-allocation entry (rows * n_in <= 4194304)";
     default: return "unknown error";
     }
 }

@@ -482,4 +482,86 @@ int launch_gemm_tc(float *y, const void *x, int x_dtype, const uint8_t *w, int w
     return rc;
 }
 
+// ---- prefill GEMM for callers that must not allocate --------------------------------------------------
+// The f32-activation form of the prefill GEMM needs an f16 copy of X. krk_cuda_gemm takes that space
+// from the caller; this entry takes it from a fixed array that lives in the library's device image, so
+// that a host which has already committed all device memory (an engine that sizes weights and KV cache
+// against a budget at load time and allocates nothing afterwards), or which cannot tolerate the implicit
+// device synchronisation of an allocation in the middle of a decode loop, can still run it.
+
+constexpr int64_t kStaticHalves = 4ll << 20;   // rows * n_in <= 4 Mi values (8 MiB of f16), e.g. 1024 x 4096
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticHalves * 2 + 256];   // f16 X, then a status word
+
 } // namespace krk_cuda
+
+using namespace krk_cuda;
+
+extern "C" int krk_cuda_gemm_f32_static(void *y_f32, const void *x_f32, const void *w, int wt, int64_t n_out, int64_t n_in,
+                                        int64_t rows, void *stream) {
+    if (!krk_cuda_dtype_ok(wt)) return KRK_CUDA_EDTYPE;
+    if (n_out < 0 || rows < 0 || !krk_cuda_gemm_k_ok(wt, n_in) || n_in % 256 != 0) return KRK_CUDA_ESHAPE;
+    if (rows > (1 << 24) || n_out > (1 << 30) || n_in > (1 << 24)) return KRK_CUDA_ESHAPE;
+    if (n_out == 0 || rows == 0) return KRK_CUDA_OK;
+    if (!y_f32 || !x_f32 || !w) return KRK_CUDA_ENULL;
+    if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x_f32) & 15) || (reinterpret_cast<uintptr_t>(y_f32) & 3))
+        return KRK_CUDA_EALIGN;
+    if (rows * n_in > kStaticHalves) return KRK_CUDA_ETOOBIG;   // larger than the fixed array: use krk_cuda_gemm
+
+    // Once per device, with that device current: the device address of the array. In host code the
+    // array's name is only a handle for this query, never a pointer a kernel may be given.
+    static unsigned char *scratch_of[64] = {};
+    static int sms_of[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) return KRK_CUDA_EDEVICE;
+    if (!scratch_of[dev]) {
+        void *ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms_of[dev], cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess || !ptr) {
+            if (e != cudaSuccess) note_cuda_error(e);
+            return KRK_CUDA_EDEVICE;
+        }
+        scratch_of[dev] = static_cast<unsigned char *>(ptr);
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    __half *xh = reinterpret_cast<__half *>(scratch_of[dev]);
+    int *status = reinterpret_cast<int *>(scratch_of[dev] + kStaticHalves * 2);
+
+    // Every call overwrites the part of the array it uses before reading it (the conversion kernel
+    // below), so nothing of the previous call's contents is ever consumed.
+    const int64_t n = rows * n_in;
+    const int64_t want = (n + 255) / 256;
+    const int cgrid = (int)(want < (int64_t)sms_of[dev] * 8 ? want : (int64_t)sms_of[dev] * 8);
+    f32_to_f16_kernel<<<cgrid, 256, 0, st>>>(xh, static_cast<const float *>(x_f32), n);
+    note_launch();
+    int rc = check_launch();
+    if (rc != KRK_CUDA_OK) return rc;
+
+    GemmParams p;
+    p.w = static_cast<const uint8_t *>(w);
+    p.y = static_cast<float *>(y_f32);
+    p.n_out = n_out;
+    p.n_in = n_in;
+    p.rows = rows;
+    p.tile_m = rows >= kMaxTileM ? kMaxTileM : (int)((rows + 15) / 16 * 16);
+    p.n_tiles_n = (int)((n_out + kTileN - 1) / kTileN);
+    p.n_tiles_m = (int)((rows + p.tile_m - 1) / p.tile_m);
+    p.row_bytes = (int)row_bytes(wt, n_in);
+    p.status = status;
+    EncodeTiledFn encode = encode_tiled();
+    if (!encode) return KRK_CUDA_EDEVICE;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)n_in, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)n_in * sizeof(__half)};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)p.tile_m};
+    const cuuint32_t estr[2] = {1, 1};
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return KRK_CUDA_ELAUNCH;
+    const int tiles = p.n_tiles_n * p.n_tiles_m;
+    const int grid = tiles < sms_of[dev] ? tiles : sms_of[dev];
+    rc = KRK_CUDA_EDTYPE;
+    KRK_DISPATCH_WT(wt, rc = launch_wt<WT>(p, map, grid, st));
+    return rc;
+}
