@@ -416,9 +416,9 @@ def prefill_extra(torch, capi, gen):
             "results": out}
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the streaming kernel, from the ncu
-# capture summarised under profiles/ (None until a capture exists).
-TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the streaming kernel (mean over the four
+# launch shapes of a layer), from the ncu capture summarised in profiles/gemv_stream_q4k_llama7b_layer.md.
+TRAFFIC_BYTES_PER_LAUNCH = 21466880
 
 
 # ---- CPU arms ---------------------------------------------------------------------------------------
