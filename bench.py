@@ -310,16 +310,40 @@ def device_weights_q6k(torch, n_out: int, n_in: int, gen):
     return w.view(n_out, nblk * 210)
 
 
-def timed(torch, fn, reps, barrier):
-    """Device time per call of fn(i), events on the current stream, after 3 warm-up calls."""
-    for i in range(3):
+def timed(torch, fn, reps, barrier, variants=0):
+    """Device time per call of fn(i), events on the launching stream, after warm-up calls. With
+    `variants` > 0 the calls fn(0..variants-1) are captured once each into CUDA graphs (kernels and, on
+    several GPUs, the NCCL collective) and the graphs are replayed in turn: a decode loop replays a fixed
+    launch sequence, and a latency-bound collective should not pay a host launch per token."""
+    for i in range(max(3, variants)):
         fn(i)
     barrier()
+    stream = torch.cuda.current_stream()
+    run = fn
+    if variants > 0:
+        cap = torch.cuda.Stream()
+        cap.wait_stream(stream)
+        graphs = []
+        with torch.cuda.stream(cap):
+            for v in range(variants):
+                g = torch.cuda.CUDAGraph()
+                g.capture_begin()
+                fn(v)
+                g.capture_end()
+                graphs.append(g)
+            for g in graphs:
+                g.replay()
+        barrier()
+        stream = cap
+
+        def run(i):
+            graphs[i % variants].replay()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(reps):
-        fn(i)
-    e1.record()
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for i in range(reps):
+            run(i)
+        e1.record(stream)
     barrier()
     return e0.elapsed_time(e1) / reps
 
@@ -350,11 +374,13 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
 
     def head_local(i):
         return capi.gemv(x, ws[i % n_rep], synth.Q6_K, count, n_in)
-    ms_full = reduce_max(timed(torch, head_call, 50, barrier))
-    ms_local = reduce_max(timed(torch, head_local, 50, barrier))
+    ms_full = reduce_max(timed(torch, head_call, 60, barrier, variants=n_rep))
+    ms_local = reduce_max(timed(torch, head_local, 60, barrier, variants=n_rep))
+    ms_full_host = reduce_max(timed(torch, head_call, 60, barrier))
     wbytes = n_out * synth.row_bytes(synth.Q6_K, n_in)
     out["head_q6_k_128256x4096"] = {
-        "ms_per_token": round(ms_full, 5), "ms_gemv_only": round(ms_local, 5),
+        "ms_per_token": round(ms_full, 5), "ms_gemv_only": round(ms_local, 5), "ms_per_token_host_launched": round(ms_full_host, 5),
+        "launch": "CUDA graph replay (GEMV + all-gather)",
         "weight_gbps_all_gpus": round(wbytes / (ms_full * 1e-3) / 1e9, 1),
         "weight_gbps_gemv_only": round(wbytes / (ms_local * 1e-3) / 1e9, 1),
         "rows_per_gpu": count, "gathered_bytes": n_out * 4, "replicas_rotated": n_rep}
@@ -375,7 +401,7 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
     for batch in (1, 8):
         def moe_call(i):
             return moe.forward(toks[i % 16, :batch], logits[i % 16, :batch])
-        ms = reduce_max(timed(torch, moe_call, 32, barrier))
+        ms = reduce_max(timed(torch, moe_call, 32, barrier, variants=16))
         distinct = []
         for i in range(16):
             ids, _ = capi.route(logits[i, :batch], k)

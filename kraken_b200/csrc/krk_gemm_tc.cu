@@ -1,6 +1,6 @@
 // Prefill GEMM for sm_100a: Y[rows][n_out] = X[rows][n_in] . W^T with W block-quantized in HBM,
-// decoded to f16 K-major tiles in shared memory and contracted on the 5th-generation tensor
-// cores (tcgen05.mma, f32 accumulators in tensor memory).
+// decoded to f16 and contracted on the 5th-generation tensor cores (tcgen05.mma, f32 accumulators
+// in tensor memory).
 //
 // Mapping. The weight tile is the MMA's A operand (128 weight rows = the 128 TMEM lanes), the
 // token tile its B operand (up to 256 tokens = TMEM columns), so a weight tile is decoded once
@@ -8,18 +8,22 @@
 // TMEM lane per thread and 32 neighbouring weight rows of one token form one coalesced 128-byte
 // store.
 //
+// The decoded weights never touch shared memory: a decode thread owns a weight row = a TMEM lane,
+// so it writes its f16 values straight into tensor memory (tcgen05.st) and the MMA takes A from
+// TMEM. Shared memory then carries only the X tiles (TMA, 128-byte swizzle) and the raw quantized
+// bytes, which leaves its bandwidth to the one operand the MMA still reads from it.
+//
 // One persistent CTA per SM, warp-specialised, everything connected by mbarriers:
-//   warps 0..7   decode: two threads per weight row of the tile, 32 values each per 64-value K step;
-//                a thread reads the row's raw quantized bytes straight from global memory (a
-//                super-block ahead, into registers; the weights are read once per token tile, from
-//                HBM or L2) and writes 32 f16 values as half of a 128-byte row of the A tile in the
-//                128-byte-swizzled K-major layout the MMA descriptor names; two K steps are
-//                written per proxy fence;
-//   warps 8..11  epilogue: tcgen05.ld of the accumulator (warp w%4 owns TMEM lanes 32*(w%4)..),
-//                f32 stores of Y; two accumulator buffers, so the stores of tile i overlap the MMAs
-//                of tile i+1;
-//   warp 12      TMA producer of the X tile (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast);
-//   warp 13      TMEM allocation and the single thread that issues tcgen05.mma / tcgen05.commit.
+//   warps 0..7   decode: two threads per weight row, 32 values each per 64-value K step. Q4_K
+//                super-blocks arrive in shared memory by TMA (a 2-D tensor map over the raw byte
+//                matrix, box = 144 bytes x 128 rows, three super-blocks ahead); other formats are
+//                read from global memory element-wise. 16 x 32-bit TMEM columns per thread and step;
+//   warps 8..11  epilogue: tcgen05.ld of the accumulator (warp w%4 owns TMEM lanes 32*(w%4)..), f32
+//                stores of Y;
+//   warp 12      TMA producer of X tiles (cp.async.bulk.tensor.2d, no multicast);
+//   warp 13      TMA producer of raw Q4_K super-block columns;
+//   warp 14      TMEM allocation and the single thread that issues tcgen05.mma / tcgen05.commit.
+// Tensor memory: columns 0..255 the accumulator, 256..511 eight A stages of 32 columns.
 //
 // Same contract as gemm_wmma_kernel of the reference (src/hip/kernels/gemm.hpp:621-970): f16
 // staged operands, f32 accumulation; here the output stays f32.
@@ -36,11 +40,14 @@ namespace {
 
 constexpr int kTileN = 128;            // weight rows per tile (MMA M)
 constexpr int kMaxTileM = 256;         // tokens per tile (MMA N)
-constexpr int kBK = 64;                // K values per stage: one 128-byte swizzle row of f16
-constexpr int kStages = 4;
+constexpr int kBK = 64;                // K values per step: one 128-byte swizzle row of f16 X, 32 TMEM columns of A
+constexpr int kBStages = 4;            // X tiles in shared memory
+constexpr int kAStages = 8;            // decoded weight tiles in tensor memory
+constexpr int kRawStages = 3;          // raw Q4_K super-block columns in shared memory
+constexpr int kRawBytes = kTileN * 144;
 constexpr int kDecodeThreads = 256, kEpilogueThreads = 128;   // two decode threads per weight row
-constexpr int kThreads = kDecodeThreads + kEpilogueThreads + 64;
-constexpr int kTmemCols = 512;
+constexpr int kThreads = kDecodeThreads + kEpilogueThreads + 96;
+constexpr int kTmemCols = 512, kTmemA = 256;
 constexpr long long kWaitCycles = 4000000000LL;
 
 struct GemmParams {
@@ -54,10 +61,12 @@ struct GemmParams {
 };
 
 struct __align__(1024) GemmSmem {
-    uint8_t a[kStages][kTileN * 128];          // decoded W tiles, [128 rows][64 f16], 128B swizzle
-    uint8_t b[kStages][kMaxTileM * 128];       // X tiles, [tokens][64 f16], 128B swizzle (TMA)
-    unsigned long long full_x[kStages], full_w[kStages], empty[kStages];
-    unsigned long long tmem_full[2], tmem_empty[2];
+    uint8_t b[kBStages][kMaxTileM * 128];      // X tiles, [tokens][64 f16], 128B swizzle (TMA)
+    uint8_t raw[kRawStages][kRawBytes];        // raw Q4_K bytes, [128 rows][144] (TMA)
+    unsigned long long b_full[kBStages], b_empty[kBStages];
+    unsigned long long a_full[kAStages], a_empty[kAStages];
+    unsigned long long raw_full[kRawStages], raw_empty[kRawStages];
+    unsigned long long d_full, d_empty;
     uint32_t tmem_base;
     int gave_up;
 };
@@ -117,6 +126,17 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                  ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// A from tensor memory (lane = row, 32-bit column = two consecutive K values), B from shared memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+                   "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -177,20 +197,20 @@ struct Raw {   // formats without a fast path keep only the row pointer and deco
     }
 };
 
-// Q4_K: one load() fetches a whole 144-byte super-block = four K steps, so the fetch of the next
-// super-block is in flight for four steps (longer than an HBM round trip). K step p of the block
-// covers chunks 2p, 2p+1: the low and the high nibbles of the same 32 bytes
-// (src/quant.cpp:437-460). Thread half h converts chunk 2p+h.
+// Q4_K: one load() takes a whole 144-byte super-block = four K steps (from the TMA-staged tile in
+// shared memory). K step p of the block covers chunks 2p, 2p+1: the low and the high nibbles of the
+// same 32 bytes (src/quant.cpp:437-460). Thread half h converts chunk 2p+h.
 template <>
 struct Raw<KRK_CUDA_Q4_K> {
     static constexpr int kSteps = 4;
     uint4 hdr, q[8];
-    __device__ __forceinline__ void load(const uint8_t *row, int ks) {
-        const uint4 *b = reinterpret_cast<const uint4 *>(row + (size_t)(ks >> 2) * 144);
+    __device__ __forceinline__ void load_block(const uint8_t *block) {
+        const uint4 *b = reinterpret_cast<const uint4 *>(block);
         hdr = b[0];
 #pragma unroll
         for (int i = 0; i < 8; i++) q[i] = b[1 + i];
     }
+    __device__ __forceinline__ void load(const uint8_t *row, int ks) { load_block(row + (size_t)(ks >> 2) * 144); }
     __device__ __forceinline__ void convert(int p, int half, uint32_t (&out)[16]) const {
         // 6-bit scale / min of chunk c = 2p + half out of the 12 packed bytes in hdr.y, hdr.z, hdr.w
         // (src/quant.cpp:427-435)
@@ -225,27 +245,34 @@ struct Raw<KRK_CUDA_Q4_K> {
 
 template <int WT>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap x_map) {
+gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap x_map,
+               const __grid_constant__ CUtensorMap w_map) {
+    constexpr bool kStagedRaw = WT == KRK_CUDA_Q4_K;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     GemmSmem *sm = reinterpret_cast<GemmSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     volatile int *gave_up = &sm->gave_up;
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; s++) {
-            mbar_init(smem_u32(&sm->full_x[s]), 1);
-            mbar_init(smem_u32(&sm->full_w[s]), kDecodeThreads / 32);
-            mbar_init(smem_u32(&sm->empty[s]), 1);
+        for (int s = 0; s < kBStages; s++) {
+            mbar_init(smem_u32(&sm->b_full[s]), 1);
+            mbar_init(smem_u32(&sm->b_empty[s]), 1);
         }
-        for (int b = 0; b < 2; b++) {
-            mbar_init(smem_u32(&sm->tmem_full[b]), 1);
-            mbar_init(smem_u32(&sm->tmem_empty[b]), kEpilogueThreads / 32);
+        for (int s = 0; s < kAStages; s++) {
+            mbar_init(smem_u32(&sm->a_full[s]), kDecodeThreads / 32);
+            mbar_init(smem_u32(&sm->a_empty[s]), 1);
         }
+        for (int s = 0; s < kRawStages; s++) {
+            mbar_init(smem_u32(&sm->raw_full[s]), 1);
+            mbar_init(smem_u32(&sm->raw_empty[s]), kDecodeThreads / 32);
+        }
+        mbar_init(smem_u32(&sm->d_full), 1);
+        mbar_init(smem_u32(&sm->d_empty), kEpilogueThreads / 32);
         sm->gave_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 13) {
+    if (warp == 14) {
         tmem_alloc(smem_u32(&sm->tmem_base), kTmemCols);
         tmem_relinquish();
     }
@@ -258,66 +285,64 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     const int k_steps = (int)(p.n_in / kBK);
 
     if (warp < 8) {
-        // ===== decode warps: threads r and r + 128 <-> weight row r of the tile, 32 values each =====
+        // ===== decode warps: threads r and r + 128 <-> weight row r = TMEM lane r, 32 values each =====
         const int r = tid & 127, half = tid >> 7;
-        int slot = 0;
-        uint32_t phase = 0;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + kTmemA + 16 * half;
+        int sa = 0, sr = 0;
+        uint32_t pa = 0, pr = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
             const int64_t n0 = (int64_t)(tile / p.n_tiles_m) * kTileN;
             const bool valid = n0 + r < p.n_out;
             const uint8_t *row = p.w + (size_t)(valid ? n0 + r : 0) * p.row_bytes;
-            Raw<WT> cur, nxt;
-            cur.load(row, 0);
+            Raw<WT> cur;
             for (int ks0 = 0; ks0 < k_steps; ks0 += Raw<WT>::kSteps) {
-                if (ks0 + Raw<WT>::kSteps < k_steps) nxt.load(row, ks0 + Raw<WT>::kSteps);   // in flight while this block converts
-#pragma unroll
-                for (int j = 0; j < Raw<WT>::kSteps; j += 2) {
-                    // two K steps per proxy fence: both are converted, written to their stages, fenced once
-                    // and then announced (n_in is a multiple of 256, so K steps come in fours)
-                    uint32_t v[2][16];
-                    cur.convert(j, half, v[0]);
-                    cur.convert(j + 1, half, v[1]);
-                    int slots[2];
-#pragma unroll
-                    for (int u = 0; u < 2; u++) {
-                        wait_phase(smem_u32(&sm->empty[slot]), phase ^ 1, gave_up, p.status);
-                        uint8_t *dst = sm->a[slot] + r * 128;
-#pragma unroll
-                        for (int c = 0; c < 4; c++) {
-                            // 16-byte chunk 4*half + c of row r lives at chunk (4*half + c) ^ (r & 7) (128-byte swizzle)
-                            const uint4 val = valid ? make_uint4(v[u][4 * c], v[u][4 * c + 1], v[u][4 * c + 2], v[u][4 * c + 3])
-                                                    : make_uint4(0, 0, 0, 0);
-                            *reinterpret_cast<uint4 *>(dst + (((4 * half + c) ^ (r & 7)) << 4)) = val;
-                        }
-                        slots[u] = slot;
-                        if (++slot == kStages) {
-                            slot = 0;
-                            phase ^= 1;
-                        }
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the stores visible to the MMA
+                if constexpr (kStagedRaw) {
+                    wait_phase(smem_u32(&sm->raw_full[sr]), pr, gave_up, p.status);
+                    cur.load_block(sm->raw[sr] + r * 144);
                     __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(smem_u32(&sm->full_w[slots[0]]));
-                        mbar_arrive(smem_u32(&sm->full_w[slots[1]]));
+                    if (lane == 0) mbar_arrive(smem_u32(&sm->raw_empty[sr]));   // the bytes are in registers now
+                    if (++sr == kRawStages) {
+                        sr = 0;
+                        pr ^= 1;
+                    }
+                } else {
+                    cur.load(row, ks0);
+                }
+#pragma unroll
+                for (int j = 0; j < Raw<WT>::kSteps; j++) {
+                    uint32_t v[16];
+                    cur.convert(j, half, v);
+                    if (!valid) {
+#pragma unroll
+                        for (int i = 0; i < 16; i++) v[i] = 0u;
+                    }
+                    wait_phase(smem_u32(&sm->a_empty[sa]), pa ^ 1, gave_up, p.status);
+                    tc_fence_after();
+                    tmem_st16(lane_addr + 32 * sa, v);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&sm->a_full[sa]));
+                    if (++sa == kAStages) {
+                        sa = 0;
+                        pa ^= 1;
                     }
                 }
-                cur = nxt;
             }
         }
     } else if (warp < 12) {
         // ===== epilogue warps: TMEM lane = weight row, column = token =====
         const int ew = warp - 8;
-        int it = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, it++) {
+        uint32_t ph = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
             const int64_t n0 = (int64_t)(tile / p.n_tiles_m) * kTileN, m0 = (int64_t)(tile % p.n_tiles_m) * p.tile_m;
-            const int buf = it & 1;
-            wait_phase(smem_u32(&sm->tmem_full[buf]), (it >> 1) & 1, gave_up, p.status);
+            wait_phase(smem_u32(&sm->d_full), ph, gave_up, p.status);
+            ph ^= 1;
             tc_fence_after();
             const int64_t n = n0 + 32 * ew + lane;
             for (int c0 = 0; c0 < p.tile_m; c0 += 32) {
                 uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(32 * ew) << 16) + (uint32_t)(buf * kMaxTileM + c0), v);
+                tmem_ld32(tmem_base + ((uint32_t)(32 * ew) << 16) + (uint32_t)c0, v);
                 tmem_ld_wait();
                 if (n < p.n_out) {
 #pragma unroll
@@ -329,23 +354,42 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sm->tmem_empty[buf]));
+            if (lane == 0) mbar_arrive(smem_u32(&sm->d_empty));
         }
     } else if (warp == 12) {
         // ===== TMA producer of X tiles =====
         if (lane == 0) {
-            int slot = 0;
-            uint32_t phase = 0;
+            int sb = 0;
+            uint32_t pb = 0;
             for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
                 const int m0 = (tile % p.n_tiles_m) * p.tile_m;
                 for (int ks = 0; ks < k_steps; ks++) {
-                    wait_phase(smem_u32(&sm->empty[slot]), phase ^ 1, gave_up, p.status);
-                    const uint32_t bar = smem_u32(&sm->full_x[slot]);
+                    wait_phase(smem_u32(&sm->b_empty[sb]), pb ^ 1, gave_up, p.status);
+                    const uint32_t bar = smem_u32(&sm->b_full[sb]);
                     mbar_arrive_expect_tx(bar, (uint32_t)p.tile_m * 128u);
-                    tma_load_2d(smem_u32(sm->b[slot]), &x_map, ks * kBK, m0, bar);
-                    if (++slot == kStages) {
-                        slot = 0;
-                        phase ^= 1;
+                    tma_load_2d(smem_u32(sm->b[sb]), &x_map, ks * kBK, m0, bar);
+                    if (++sb == kBStages) {
+                        sb = 0;
+                        pb ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 13) {
+        // ===== TMA producer of raw Q4_K super-block columns: 144 bytes x 128 rows each =====
+        if (kStagedRaw && lane == 0) {
+            int sr = 0;
+            uint32_t pr = 0;
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                const int n0 = (tile / p.n_tiles_m) * kTileN;
+                for (int blk = 0; blk < k_steps / 4; blk++) {
+                    wait_phase(smem_u32(&sm->raw_empty[sr]), pr ^ 1, gave_up, p.status);
+                    const uint32_t bar = smem_u32(&sm->raw_full[sr]);
+                    mbar_arrive_expect_tx(bar, (uint32_t)kRawBytes);
+                    tma_load_2d(smem_u32(sm->raw[sr]), &w_map, blk * 144, n0, bar);
+                    if (++sr == kRawStages) {
+                        sr = 0;
+                        pr ^= 1;
                     }
                 }
             }
@@ -354,35 +398,40 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         // ===== MMA issuer =====
         if (lane == 0) {
             const uint32_t idesc = instr_desc(kTileN, p.tile_m);
-            int slot = 0, it = 0;
-            uint32_t phase = 0;
-            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, it++) {
-                const int buf = it & 1;
-                wait_phase(smem_u32(&sm->tmem_empty[buf]), ((it >> 1) & 1) ^ 1, gave_up, p.status);
+            int sa = 0, sb = 0;
+            uint32_t pa = 0, pb = 0, pd = 0;
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                wait_phase(smem_u32(&sm->d_empty), pd ^ 1, gave_up, p.status);   // the epilogue has drained the accumulator
+                pd ^= 1;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kMaxTileM);
                 for (int ks = 0; ks < k_steps; ks++) {
-                    wait_phase(smem_u32(&sm->full_x[slot]), phase, gave_up, p.status);
-                    wait_phase(smem_u32(&sm->full_w[slot]), phase, gave_up, p.status);
+                    wait_phase(smem_u32(&sm->b_full[sb]), pb, gave_up, p.status);
+                    wait_phase(smem_u32(&sm->a_full[sa]), pa, gave_up, p.status);
                     tc_fence_after();
-                    const uint64_t adesc = smem_desc(smem_u32(sm->a[slot])), bdesc = smem_desc(smem_u32(sm->b[slot]));
+                    const uint64_t bdesc = smem_desc(smem_u32(sm->b[sb]));
+                    const uint32_t a_tmem = tmem_base + kTmemA + 32 * sa;
 #pragma unroll
-                    for (int kk = 0; kk < kBK / 16; kk++)   // +32 bytes (>> 4 = 2) per 16-value K slice inside the swizzle row
-                        umma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kk) ? 1u : 0u);
-                    umma_commit(smem_u32(&sm->empty[slot]));   // frees the stage when these MMAs have read it
-                    if (++slot == kStages) {
-                        slot = 0;
-                        phase ^= 1;
+                    for (int kk = 0; kk < kBK / 16; kk++)   // 16 K values = 8 TMEM columns of A, 32 bytes of every B row
+                        umma_f16_ts(tmem_base, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, (ks | kk) ? 1u : 0u);
+                    umma_commit(smem_u32(&sm->a_empty[sa]));   // both stages are free once these MMAs have read them
+                    umma_commit(smem_u32(&sm->b_empty[sb]));
+                    if (++sa == kAStages) {
+                        sa = 0;
+                        pa ^= 1;
+                    }
+                    if (++sb == kBStages) {
+                        sb = 0;
+                        pb ^= 1;
                     }
                 }
-                umma_commit(smem_u32(&sm->tmem_full[buf]));
+                umma_commit(smem_u32(&sm->d_full));
             }
         }
     }
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 13) {
+    if (warp == 14) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
@@ -409,8 +458,32 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
+// Tensor map over the raw weight bytes as a [n_out][row_bytes] byte matrix, box = one Q4_K super-block
+// (144 bytes) x 128 rows. For the formats that are not staged this way a 16-byte-wide box of the same
+// matrix is encoded so that the kernel always receives a valid map.
+bool encode_w_map(CUtensorMap *map, const uint8_t *w, int wt, int64_t n_out, int row_bytes) {
+    EncodeTiledFn encode = encode_tiled();
+    if (!encode) return false;
+    const bool staged = wt == KRK_CUDA_Q4_K;
+    const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)n_out};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t box[2] = {staged ? 144u : 16u, staged ? (cuuint32_t)kTileN : 1u};
+    const cuuint32_t estr[2] = {1, 1};
+    if (!staged && (row_bytes % 16) != 0) {
+        // never used by the kernel; describe a 16-byte row of the same buffer so that encoding succeeds
+        const cuuint64_t d2[2] = {16, 1};
+        const cuuint64_t s2[1] = {16};
+        return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w), d2, s2, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int WT>
 int launch_wt(const GemmParams &p, const CUtensorMap &map, int grid, cudaStream_t st) {
+    CUtensorMap w_map;
+    if (!encode_w_map(&w_map, p.w, WT, p.n_out, p.row_bytes)) return KRK_CUDA_ELAUNCH;
     static bool configured[64] = {};
     auto kernel = gemm_tc_kernel<WT>;
     const size_t smem = sizeof(GemmSmem) + 1024;
@@ -424,7 +497,7 @@ int launch_wt(const GemmParams &p, const CUtensorMap &map, int grid, cudaStream_
         }
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kernel<<<grid, kThreads, smem, st>>>(p, map);
+    kernel<<<grid, kThreads, smem, st>>>(p, map, w_map);
     note_launch(1, KRK_CUDA_FAMILY_GEMM_TC);
     return check_launch();
 }
