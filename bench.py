@@ -290,7 +290,7 @@ def run_ours(args):
         if sharded is not None:
             line["sharded"] = sharded
         if world == 1 and not args.no_extras:
-            line["extra"] = {"prefill": prefill_extra(torch, capi, gen)}
+            line["extra"] = {"prefill": prefill_extra(torch, capi, gen), "decode": decode_extra(torch, capi, gen, barrier)}
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(sample_seconds=args.cpu_seconds)
         print(json.dumps(line), flush=True)
@@ -414,6 +414,45 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
     return out
 
 
+def device_weights_q8_0(torch, n_out: int, n_in: int, gen):
+    """Q8_0 blocks made on the device: int8 quants uniform in [-127, 127], d in [1e-3, 2e-2] as f16."""
+    nblk = n_in // 32
+    w = torch.empty((n_out, nblk, 34), dtype=torch.uint8, device="cuda")
+    q = torch.randint(-127, 128, (n_out, nblk, 32), dtype=torch.int8, device="cuda", generator=gen)
+    w[..., 2:34] = q.view(torch.uint8)
+    d = (1e-3 + 1.9e-2 * torch.rand((n_out, nblk), device="cuda", generator=gen)).to(torch.float16)
+    w[..., 0:2] = d.view(torch.uint8).view(n_out, nblk, 2)
+    return w.view(n_out, nblk * 34)
+
+
+def decode_extra(torch, capi, gen, barrier):
+    """The decode GEMV on the other shapes the spec names, batch 1, weights rotated through replicas that
+    together exceed 4x the L2, each replay a CUDA graph: config 1 (Q8_0 4096 x 4096) and one large matrix
+    per format, where the per-launch fixed cost no longer matters and the number is the kernel's
+    steady-state bandwidth."""
+    peak, _ = measured_peaks()
+    cases = [("config1_q8_0_4096x4096", synth.Q8_0, 4096, 4096, device_weights_q8_0),
+             ("steady_q8_0_65536x4096", synth.Q8_0, 65536, 4096, device_weights_q8_0),
+             ("steady_q4_k_131072x4096", synth.Q4_K, 131072, 4096, device_weights),
+             ("steady_q6_k_128256x4096", synth.Q6_K, 128256, 4096, device_weights_q6k)]
+    out = {}
+    for name, wt, n_out, n_in, make in cases:
+        wbytes = n_out * synth.row_bytes(wt, n_in)
+        n_rep = max(2, int(4 * 126e6 / wbytes) + 1)
+        ws = [make(torch, n_out, n_in, gen) for _ in range(n_rep)]
+        x = torch.randn((1, n_in), device="cuda", generator=gen)
+        y = torch.empty((1, n_out), device="cuda")
+
+        def call(i):
+            capi.gemv(x, ws[i % n_rep], wt, n_out, n_in, out=y)
+        ms = timed(torch, call, 20 * n_rep, barrier, variants=n_rep)
+        abytes = wbytes + 4 * n_in + 4 * n_out
+        out[name] = {"us_per_launch": round(ms * 1e3, 3), "algorithmic_gbps": round(abytes / (ms * 1e-3) / 1e9, 1),
+                     "frac_of_measured_hbm": round(abytes / (ms * 1e-3) / 1e9 / peak, 4), "replicas_rotated": n_rep}
+        del ws
+    return out
+
+
 def prefill_extra(torch, capi, gen):
     """Config 3: Q4_K prefill GEMM, N=14336, K=4096, M in {128, 512, 2048}: f16 X, f32 Y, tensor cores.
     Four weight replicas (132 MB) are rotated so that no launch finds its weights in L2."""
@@ -425,14 +464,15 @@ def prefill_extra(torch, capi, gen):
     for rows in (128, 512, 2048):
         x = torch.randn((rows, n_in), device="cuda", generator=gen).to(torch.float16)
         y = torch.empty((rows, n_out), device="cuda")
+        scratch = torch.empty(max(capi.gemm_workspace_bytes(capi.X_F16, n_out, n_in, rows), 256), dtype=torch.uint8, device="cuda")
         for i in range(4):
-            capi.gemm(x, ws[i], WT, n_out, n_in, out=y)
+            capi.gemm(x, ws[i], WT, n_out, n_in, out=y, workspace=scratch)
         torch.cuda.synchronize()
         reps = 20
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(reps):
-            capi.gemm(x, ws[i % 4], WT, n_out, n_in, out=y)
+            capi.gemm(x, ws[i % 4], WT, n_out, n_in, out=y, workspace=scratch)
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / reps

@@ -171,7 +171,7 @@ int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const f
                            cudaStream_t st);
 
 // Prefill GEMM on tcgen05 (krk_gemm_tc.cu).
-size_t gemm_workspace_bytes(int x_dtype, int64_t n_in, int64_t rows);
+size_t gemm_workspace_bytes(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows);
 int launch_gemm_tc(float *y, const void *x, int x_dtype, const uint8_t *w, int wt, int64_t n_out,
                    int64_t n_in, int64_t rows, void *workspace, cudaStream_t st);
 

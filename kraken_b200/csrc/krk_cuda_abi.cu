@@ -162,9 +162,8 @@ int krk_cuda_gemv_group(void *const host_y[], const void *const host_x[], const 
 }
 
 size_t krk_cuda_gemm_workspace_bytes(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows) {
-    (void)n_out;
-    if (rows <= 0 || n_in <= 0) return 0;
-    return gemm_workspace_bytes(x_dtype, n_in, rows);
+    if (rows <= 0 || n_in <= 0 || n_out <= 0) return 0;
+    return gemm_workspace_bytes(x_dtype, n_out, n_in, rows);
 }
 
 int krk_cuda_gemm(void *y_f32, const void *x, int x_dtype, const void *w, int wt, int64_t n_out,
@@ -174,7 +173,7 @@ int krk_cuda_gemm(void *y_f32, const void *x, int x_dtype, const void *w, int wt
     if (rc != KRK_CUDA_OK) return rc;
     if (n_in % 256 != 0) return KRK_CUDA_ESHAPE;
     if (n_out == 0 || rows == 0) return KRK_CUDA_OK;
-    const size_t need = gemm_workspace_bytes(x_dtype, n_in, rows);
+    const size_t need = gemm_workspace_bytes(x_dtype, n_out, n_in, rows);
     if (need > 0 && (!workspace || ws_bytes < need || !aligned(workspace, 128))) return KRK_CUDA_EWORKSPACE;
     if (!device_state()) return KRK_CUDA_EDEVICE;
     return launch_gemm_tc(static_cast<float *>(y_f32), x, x_dtype, static_cast<const uint8_t *>(w), wt,

@@ -32,6 +32,8 @@
 // runs to its end without waiting again and frees its tensor memory.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "krk_common.cuh"
 
 namespace krk_cuda {
@@ -58,6 +60,9 @@ struct GemmParams {
     int n_tiles_n, n_tiles_m;
     int row_bytes;
     int *status;
+    int split_tail;        // 1: cut the tiles left after the last whole wave over all CTAs (needs the two below)
+    unsigned *tail_count;  // one counter per tail tile, zero at launch
+    float *tail_part;      // [2 * grid][tile_m * 128] f32: the pieces' partial tiles
 };
 
 struct __align__(1024) GemmSmem {
@@ -69,6 +74,7 @@ struct __align__(1024) GemmSmem {
     unsigned long long d_full, d_empty;
     uint32_t tmem_base;
     int gave_up;
+    int tail_last;
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -243,6 +249,55 @@ struct Raw<KRK_CUDA_Q4_K> {
 
 // ---- the kernel ------------------------------------------------------------------------------------
 
+// ---- work items ---------------------------------------------------------------------------------------
+// Tiles are dealt to the persistent CTAs in whole waves; the tiles left over after the last whole wave
+// (all of them when there are fewer tiles than CTAs) would keep only some SMs busy, so their K range is
+// cut into equal pieces over ALL CTAs instead (in units of four K steps = one super-block). A tile that
+// is cut this way has its pieces written to a scratch slot each; the CTA that finishes a tile's last
+// piece (a counter tells it so, nobody waits for anybody) adds the pieces in K order and writes Y, so
+// the result is the same on every run.
+struct Item {
+    int tile;      // tile index
+    int k0, nk;    // K steps [k0, k0 + nk)
+    int partial;   // 1: a piece of a cut tile (accumulate into Y), 0: the whole tile (store)
+};
+
+struct ItemIter {
+    int next_full, n_full, stride;   // whole tiles: next_full, next_full + stride, ... < n_full
+    int b, e, k_blocks, tail0;       // tail pieces in units of 4 K steps: [b, e) of the tail's block range
+    __device__ __forceinline__ void init(int cta, int grid, int n_tiles, int k_steps, int split_tail) {
+        n_full = split_tail ? (n_tiles / grid) * grid : n_tiles;
+        next_full = cta;
+        stride = grid;
+        k_blocks = k_steps / 4;
+        tail0 = n_full;
+        const long long total = (long long)(n_tiles - n_full) * k_blocks;
+        b = (int)(total * cta / grid);
+        e = (int)(total * (cta + 1) / grid);
+    }
+    __device__ __forceinline__ bool next(Item &it) {
+        if (next_full < n_full) {
+            it.tile = next_full;
+            it.k0 = 0;
+            it.nk = k_blocks * 4;
+            it.partial = 0;
+            next_full += stride;
+            return true;
+        }
+        if (b < e) {
+            const int t = b / k_blocks, kb = b - t * k_blocks;
+            const int n = min(k_blocks - kb, e - b);
+            it.tile = tail0 + t;
+            it.k0 = kb * 4;
+            it.nk = n * 4;
+            it.partial = n != k_blocks;
+            b += n;
+            return true;
+        }
+        return false;
+    }
+};
+
 template <int WT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap x_map,
@@ -283,6 +338,9 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
 
     const int n_tiles = p.n_tiles_n * p.n_tiles_m;
     const int k_steps = (int)(p.n_in / kBK);
+    ItemIter iter;
+    iter.init((int)blockIdx.x, (int)gridDim.x, n_tiles, k_steps, p.split_tail);
+    Item it;
 
     if (warp < 8) {
         // ===== decode warps: threads r and r + 128 <-> weight row r = TMEM lane r, 32 values each =====
@@ -290,12 +348,12 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + kTmemA + 16 * half;
         int sa = 0, sr = 0;
         uint32_t pa = 0, pr = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-            const int64_t n0 = (int64_t)(tile / p.n_tiles_m) * kTileN;
+        while (iter.next(it)) {
+            const int64_t n0 = (int64_t)(it.tile / p.n_tiles_m) * kTileN;
             const bool valid = n0 + r < p.n_out;
             const uint8_t *row = p.w + (size_t)(valid ? n0 + r : 0) * p.row_bytes;
             Raw<WT> cur;
-            for (int ks0 = 0; ks0 < k_steps; ks0 += Raw<WT>::kSteps) {
+            for (int ks0 = it.k0; ks0 < it.k0 + it.nk; ks0 += Raw<WT>::kSteps) {
                 if constexpr (kStagedRaw) {
                     wait_phase(smem_u32(&sm->raw_full[sr]), pr, gave_up, p.status);
                     cur.load_block(sm->raw[sr] + r * 144);
@@ -332,19 +390,27 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         }
     } else if (warp < 12) {
         // ===== epilogue warps: TMEM lane = weight row, column = token =====
-        const int ew = warp - 8;
+        const int ew = warp - 8, et = tid - kDecodeThreads;
+        const int grid = (int)gridDim.x;
+        const long long tail_total = (long long)(n_tiles - iter.n_full) * iter.k_blocks;
+        const size_t part_elems = (size_t)p.tile_m * kTileN;
+        int n_piece = 0;   // tail pieces this CTA has produced so far (0..2): its slots are 2*cta, 2*cta+1
         uint32_t ph = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-            const int64_t n0 = (int64_t)(tile / p.n_tiles_m) * kTileN, m0 = (int64_t)(tile % p.n_tiles_m) * p.tile_m;
+        while (iter.next(it)) {
+            const int64_t n0 = (int64_t)(it.tile / p.n_tiles_m) * kTileN, m0 = (int64_t)(it.tile % p.n_tiles_m) * p.tile_m;
             wait_phase(smem_u32(&sm->d_full), ph, gave_up, p.status);
             ph ^= 1;
             tc_fence_after();
             const int64_t n = n0 + 32 * ew + lane;
+            float *part = it.partial ? p.tail_part + (size_t)(2 * blockIdx.x + n_piece) * part_elems : nullptr;
             for (int c0 = 0; c0 < p.tile_m; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(32 * ew) << 16) + (uint32_t)c0, v);
                 tmem_ld_wait();
-                if (n < p.n_out) {
+                if (it.partial) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) part[(size_t)(c0 + j) * kTileN + 32 * ew + lane] = __uint_as_float(v[j]);
+                } else if (n < p.n_out) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int64_t m = m0 + c0 + j;
@@ -354,16 +420,76 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sm->d_empty));
+            if (lane == 0) mbar_arrive(smem_u32(&sm->d_empty));   // the accumulator is free again
+            if (!it.partial) continue;
+            n_piece++;
+            // Whoever completes the tile's last piece adds all of them, in K order, into Y.
+            __threadfence();
+            asm volatile("bar.sync 2, %0;" ::"n"(kEpilogueThreads) : "memory");
+            const int t = it.tile - iter.tail0;
+            const long long lo = (long long)t * iter.k_blocks, hi = lo + iter.k_blocks;
+            // CTAs whose share [total*c/grid, total*(c+1)/grid) meets this tile's blocks [lo, hi)
+            int c_lo = (int)(lo * grid / tail_total), c_hi = (int)((hi * grid + tail_total - 1) / tail_total);
+            c_lo = max(c_lo - 1, 0);
+            c_hi = min(c_hi + 1, grid);
+            int pieces = 0;
+            for (int c = c_lo; c < c_hi; c++) {
+                const long long b = tail_total * c / grid, e = tail_total * (c + 1) / grid;
+                pieces += (max(b, lo) < min(e, hi)) ? 1 : 0;
+            }
+            if (et == 0) sm->tail_last = (atomicAdd(p.tail_count + t, 1u) == (unsigned)(pieces - 1)) ? 1 : 0;
+            asm volatile("bar.sync 2, %0;" ::"n"(kEpilogueThreads) : "memory");
+            if (!sm->tail_last) continue;
+            __threadfence();
+            // warp ew takes tokens ew, ew+4, ...; a lane takes four neighbouring weight rows (one float4 per
+            // piece); eight tokens are in flight at once so that the L2 round trips overlap
+            for (int c0 = ew; c0 < p.tile_m; c0 += 4 * 8) {
+                float4 acc[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) acc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int c = c_lo; c < c_hi; c++) {
+                    const long long b = tail_total * c / grid, e = tail_total * (c + 1) / grid;
+                    if (max(b, lo) >= min(e, hi)) continue;
+                    // the slot of CTA c's piece of this tile: its first piece unless its share began in an earlier tile
+                    const float *src = p.tail_part + (size_t)(2 * c + ((b < lo) ? 1 : 0)) * part_elems + 4 * lane;
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const int tok = c0 + 4 * u;
+                        if (tok < p.tile_m) {
+                            const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)tok * kTileN));
+                            acc[u].x += v.x;
+                            acc[u].y += v.y;
+                            acc[u].z += v.z;
+                            acc[u].w += v.w;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int tok = c0 + 4 * u;
+                    const int64_t m = m0 + tok, nn = n0 + 4 * lane;
+                    if (tok < p.tile_m && m < p.rows) {
+                        float *dst = p.y + m * p.n_out + nn;
+                        if (nn + 3 < p.n_out && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                            *reinterpret_cast<float4 *>(dst) = acc[u];
+                        } else {
+                            if (nn < p.n_out) dst[0] = acc[u].x;
+                            if (nn + 1 < p.n_out) dst[1] = acc[u].y;
+                            if (nn + 2 < p.n_out) dst[2] = acc[u].z;
+                            if (nn + 3 < p.n_out) dst[3] = acc[u].w;
+                        }
+                    }
+                }
+            }
         }
     } else if (warp == 12) {
         // ===== TMA producer of X tiles =====
         if (lane == 0) {
             int sb = 0;
             uint32_t pb = 0;
-            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-                const int m0 = (tile % p.n_tiles_m) * p.tile_m;
-                for (int ks = 0; ks < k_steps; ks++) {
+            while (iter.next(it)) {
+                const int m0 = (it.tile % p.n_tiles_m) * p.tile_m;
+                for (int ks = it.k0; ks < it.k0 + it.nk; ks++) {
                     wait_phase(smem_u32(&sm->b_empty[sb]), pb ^ 1, gave_up, p.status);
                     const uint32_t bar = smem_u32(&sm->b_full[sb]);
                     mbar_arrive_expect_tx(bar, (uint32_t)p.tile_m * 128u);
@@ -380,9 +506,9 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         if (kStagedRaw && lane == 0) {
             int sr = 0;
             uint32_t pr = 0;
-            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-                const int n0 = (tile / p.n_tiles_m) * kTileN;
-                for (int blk = 0; blk < k_steps / 4; blk++) {
+            while (iter.next(it)) {
+                const int n0 = (it.tile / p.n_tiles_m) * kTileN;
+                for (int blk = it.k0 / 4; blk < (it.k0 + it.nk) / 4; blk++) {
                     wait_phase(smem_u32(&sm->raw_empty[sr]), pr ^ 1, gave_up, p.status);
                     const uint32_t bar = smem_u32(&sm->raw_full[sr]);
                     mbar_arrive_expect_tx(bar, (uint32_t)kRawBytes);
@@ -400,11 +526,11 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             const uint32_t idesc = instr_desc(kTileN, p.tile_m);
             int sa = 0, sb = 0;
             uint32_t pa = 0, pb = 0, pd = 0;
-            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            while (iter.next(it)) {
                 wait_phase(smem_u32(&sm->d_empty), pd ^ 1, gave_up, p.status);   // the epilogue has drained the accumulator
                 pd ^= 1;
                 tc_fence_after();
-                for (int ks = 0; ks < k_steps; ks++) {
+                for (int ks = 0; ks < it.nk; ks++) {
                     wait_phase(smem_u32(&sm->b_full[sb]), pb, gave_up, p.status);
                     wait_phase(smem_u32(&sm->a_full[sa]), pa, gave_up, p.status);
                     tc_fence_after();
@@ -504,23 +630,64 @@ int launch_wt(const GemmParams &p, const CUtensorMap &map, int grid, cudaStream_
 
 } // namespace
 
-size_t gemm_workspace_bytes(int x_dtype, int64_t n_in, int64_t rows) {
-    return x_dtype == KRK_CUDA_X_F32 ? (size_t)rows * (size_t)n_in * sizeof(__half) : 0;
+namespace {
+
+struct GemmPlan {
+    int tile_m, n_tiles_n, n_tiles_m, grid, tail;   // tail: tiles left after the last whole wave (0 = none)
+    size_t x_bytes, count_bytes, part_bytes;
+};
+
+int grid_bound() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
+        return sms;
+    (void)cudaGetLastError();
+    return 148;
+}
+
+GemmPlan plan_gemm(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows) {
+    GemmPlan g;
+    g.tile_m = rows >= kMaxTileM ? kMaxTileM : (int)((rows + 15) / 16 * 16);
+    g.n_tiles_n = (int)((n_out + kTileN - 1) / kTileN);
+    g.n_tiles_m = (int)((rows + g.tile_m - 1) / g.tile_m);
+    const int tiles = g.n_tiles_n * g.n_tiles_m, sms = grid_bound();
+    g.grid = tiles < sms ? tiles : sms;
+    // Cutting the left-over tiles is opt-in (KRK_CUDA_GEMM_SPLIT=1, read once, in the style of the
+    // reference's KRK_* A/B switches): measured on config 3 the fixed-order combine of the pieces costs
+    // more than the idle SMs it saves (M = 512: 639 vs 776 TFLOP/s), so whole tiles are the default.
+    static const bool split_on = [] {
+        const char *e = std::getenv("KRK_CUDA_GEMM_SPLIT");
+        return e && e[0] == '1';
+    }();
+    g.tail = (split_on && tiles >= sms) ? tiles % sms : 0;
+    g.x_bytes = x_dtype == KRK_CUDA_X_F32 ? (((size_t)rows * (size_t)n_in * sizeof(__half) + 255) & ~(size_t)255) : 0;
+    g.count_bytes = g.tail ? (((size_t)g.tail * sizeof(unsigned) + 255) & ~(size_t)255) : 0;
+    g.part_bytes = g.tail ? (size_t)2 * g.grid * g.tile_m * kTileN * sizeof(float) : 0;
+    return g;
+}
+
+} // namespace
+
+size_t gemm_workspace_bytes(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows) {
+    const GemmPlan g = plan_gemm(x_dtype, n_out, n_in, rows);
+    return g.x_bytes + g.count_bytes + g.part_bytes;
 }
 
 int launch_gemm_tc(float *y, const void *x, int x_dtype, const uint8_t *w, int wt, int64_t n_out, int64_t n_in,
                    int64_t rows, void *workspace, cudaStream_t st) {
     if (rows > (1 << 24) || n_out > (1 << 30) || n_in > (1 << 24)) return KRK_CUDA_ESHAPE;
+    const GemmPlan g = plan_gemm(x_dtype, n_out, n_in, rows);
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
     const __half *xh = static_cast<const __half *>(x);
     if (x_dtype == KRK_CUDA_X_F32) {
         const int64_t n = rows * n_in;
         const int64_t want = (n + 255) / 256;
-        const int grid = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
-        f32_to_f16_kernel<<<grid, 256, 0, st>>>(static_cast<__half *>(workspace), static_cast<const float *>(x), n);
+        const int cgrid = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
+        f32_to_f16_kernel<<<cgrid, 256, 0, st>>>(reinterpret_cast<__half *>(ws), static_cast<const float *>(x), n);
         note_launch();
         const int rc = check_launch();
         if (rc != KRK_CUDA_OK) return rc;
-        xh = static_cast<const __half *>(workspace);
+        xh = reinterpret_cast<const __half *>(ws);
     }
     GemmParams p;
     p.w = w;
@@ -528,12 +695,22 @@ int launch_gemm_tc(float *y, const void *x, int x_dtype, const uint8_t *w, int w
     p.n_out = n_out;
     p.n_in = n_in;
     p.rows = rows;
-    p.tile_m = rows >= kMaxTileM ? kMaxTileM : (int)((rows + 15) / 16 * 16);
-    p.n_tiles_n = (int)((n_out + kTileN - 1) / kTileN);
-    p.n_tiles_m = (int)((rows + p.tile_m - 1) / p.tile_m);
+    p.tile_m = g.tile_m;
+    p.n_tiles_n = g.n_tiles_n;
+    p.n_tiles_m = g.n_tiles_m;
     p.row_bytes = (int)row_bytes(wt, n_in);
+    p.split_tail = g.tail ? 1 : 0;
+    p.tail_count = reinterpret_cast<unsigned *>(ws + g.x_bytes);
+    p.tail_part = reinterpret_cast<float *>(ws + g.x_bytes + g.count_bytes);
     p.status = device_status_word();
     if (!p.status) return KRK_CUDA_EDEVICE;
+    if (g.tail) {
+        const cudaError_t e = cudaMemsetAsync(p.tail_count, 0, g.count_bytes, st);
+        if (e != cudaSuccess) {
+            note_cuda_error(e);
+            return KRK_CUDA_ELAUNCH;
+        }
+    }
 
     EncodeTiledFn encode = encode_tiled();
     if (!encode) return KRK_CUDA_EDEVICE;
@@ -547,11 +724,8 @@ int launch_gemm_tc(float *y, const void *x, int x_dtype, const uint8_t *w, int w
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return KRK_CUDA_ELAUNCH;
 
-    const int tiles = p.n_tiles_n * p.n_tiles_m;
-    const int sms = sm_count();
-    const int grid = tiles < sms ? tiles : sms;
     int rc = KRK_CUDA_EDTYPE;
-    KRK_DISPATCH_WT(wt, rc = launch_wt<WT>(p, map, grid, st));
+    KRK_DISPATCH_WT(wt, rc = launch_wt<WT>(p, map, g.grid, st));
     return rc;
 }
 
@@ -621,6 +795,9 @@ extern "C" int krk_cuda_gemm_f32_static(void *y_f32, const void *x_f32, const vo
     p.n_tiles_n = (int)((n_out + kTileN - 1) / kTileN);
     p.n_tiles_m = (int)((rows + p.tile_m - 1) / p.tile_m);
     p.row_bytes = (int)row_bytes(wt, n_in);
+    p.split_tail = 0;   // cutting tiles needs scratch for the pieces; this entry keeps whole tiles
+    p.tail_count = nullptr;
+    p.tail_part = nullptr;
     p.status = status;
     EncodeTiledFn encode = encode_tiled();
     if (!encode) return KRK_CUDA_EDEVICE;

@@ -99,3 +99,36 @@ def test_backend_gemm_rows_over_8_uses_tensor_cores(cuda, oracle):
     for ptr in (d_w, d_x, d_y):
         be.release(ptr)
     be.close()
+
+
+def test_gemm_cut_tail_tiles_opt_in(oracle):
+    """KRK_CUDA_GEMM_SPLIT=1 (read once per process, so a child process): the tiles left after the last
+    whole wave are cut over all CTAs and their pieces added in K order; same bar, and bit-identical runs."""
+    import os
+    import subprocess
+    import sys
+    import tempfile
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    n_out, n_in, rows = 128 * 150, 512, 300        # 300 tiles on 148 SMs: two whole waves and a cut tail
+    code = f"""
+import sys, numpy as np, torch
+sys.path.insert(0, {root!r})
+from kraken_b200 import capi, synth
+w = torch.from_numpy(synth.weights(synth.Q4_K, {n_out}, {n_in}, {SEED + 95})).cuda()
+x = torch.from_numpy(synth.activations_f16({rows}, {n_in}, {SEED + 95})).cuda()
+y1 = capi.gemm(x, w, synth.Q4_K, {n_out}, {n_in})
+y2 = capi.gemm(x, w, synth.Q4_K, {n_out}, {n_in})
+assert capi.device_status() == 0 and torch.equal(y1, y2)
+np.save(sys.argv[1], y1.cpu().numpy())
+"""
+    with tempfile.TemporaryDirectory() as tmp:
+        out = os.path.join(tmp, "y.npy")
+        env = dict(os.environ, KRK_CUDA_GEMM_SPLIT="1")
+        subprocess.run([sys.executable, "-c", code, out], check=True, env=env, timeout=300)
+        y = np.load(out)
+    w = synth.weights(synth.Q4_K, n_out, n_in, SEED + 95)
+    x = synth.activations_f16(rows, n_in, SEED + 95).astype(np.float32)
+    sel = np.arange(0, n_out, 53)
+    ref = oracle.gemm(x, w[sel], synth.Q4_K, len(sel), n_in, rows=rows, threads=8)
+    ok, worst = bound_ok(y[:, sel], ref, oracle.dequant_rows(w[sel], synth.Q4_K, len(sel), n_in), x, GEMM_TOL)
+    assert ok, worst
