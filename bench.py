@@ -377,10 +377,21 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
     ms_full = reduce_max(timed(torch, head_call, 60, barrier, variants=n_rep))
     ms_local = reduce_max(timed(torch, head_local, 60, barrier, variants=n_rep))
     ms_full_host = reduce_max(timed(torch, head_call, 60, barrier))
+    ms_peer = None
+    if world > 1:
+        # the fused form: the GEMV's epilogue stores into every GPU's logits row, then a bounded flag wait
+        peer = shard.PeerHead(n_out, n_in, synth.Q6_K, ws[0], rows=1, align=8)
+
+        def peer_call(i):
+            peer.w_local = ws[i % n_rep]
+            return peer.forward(x)
+        ms_peer = reduce_max(timed(torch, peer_call, 60, barrier))
     wbytes = n_out * synth.row_bytes(synth.Q6_K, n_in)
     out["head_q6_k_128256x4096"] = {
         "ms_per_token": round(ms_full, 5), "ms_gemv_only": round(ms_local, 5), "ms_per_token_host_launched": round(ms_full_host, 5),
-        "launch": "CUDA graph replay (GEMV + all-gather)",
+        "launch": "CUDA graph replay (GEMV + NCCL all-gather)",
+        "ms_per_token_peer_store_fused": None if ms_peer is None else round(ms_peer, 5),
+        "weight_gbps_peer_store_fused": None if ms_peer is None else round(n_out * synth.row_bytes(synth.Q6_K, n_in) / (ms_peer * 1e-3) / 1e9, 1),
         "weight_gbps_all_gpus": round(wbytes / (ms_full * 1e-3) / 1e9, 1),
         "weight_gbps_gemv_only": round(wbytes / (ms_local * 1e-3) / 1e9, 1),
         "rows_per_gpu": count, "gathered_bytes": n_out * 4, "replicas_rotated": n_rep}

@@ -42,7 +42,7 @@ extern "C" {
 #define KRK_CUDA_ESHAPE (-2)    /* n_in not a whole number of blocks, negative size, rows out of range */
 #define KRK_CUDA_ENULL (-3)     /* a required pointer is NULL */
 #define KRK_CUDA_EALIGN (-4)    /* weight base or x not 16-byte aligned, or y not 4-byte aligned */
-#define KRK_CUDA_ELAUNCH (-5)   /* the CUDA runtime refused the launch; see krk_cuda_last_cuda_error() */
+#define KRK_CUDA_ELAUNCH (-5)   /* the CUDA runtime refused the launch or call; see krk_cuda_last_cuda_error() */
 #define KRK_CUDA_EWORKSPACE (-6)/* workspace missing or smaller than the _workspace_bytes() answer */
 #define KRK_CUDA_EDEVICE (-7)   /* no sm_100 device is current */
 #define KRK_CUDA_EARG (-8)      /* any other bad argument (n_mat, k, flags) */
@@ -51,6 +51,7 @@ extern "C" {
 
 #define KRK_CUDA_MAX_GROUP 16   /* matrices per grouped launch */
 #define KRK_CUDA_MAX_ROWS 8     /* activation rows per GEMV launch */
+#define KRK_CUDA_MAX_PEERS 8    /* GPUs of one box a fused GEMV + all-gather writes to */
 
 const char *krk_cuda_strerror(int rc);
 
@@ -174,6 +175,38 @@ int krk_cuda_scatter_axpy_rows(void *dst_f32, const void *src_f32, const void *r
 /* Sum n_parts partial outputs [n_parts][n] in part order 0..n_parts-1 into out[n]: the
  * deterministic combine of expert-sharded partial sums after they were gathered. */
 int krk_cuda_sum_parts(void *out_f32, const void *parts_f32, int n_parts, int64_t n, void *stream);
+
+/* Row-sharded GEMV fused with the all-gather of its output over NVLink peer memory; no counterpart in
+ * the reference, which is single-device (src/hip/backend_hip.hip:5036-5043). This GPU holds rows
+ * [slice_offset, slice_offset + n_out_local) of a matrix with n_out_total rows. The kernel is the decode
+ * GEMV of krk_cuda_gemv, but its epilogue stores every output value into the full
+ * [rows][n_out_total] row of EVERY GPU: host_y_peers[q] is that buffer on GPU q as mapped into this
+ * process (this GPU's own buffer at q == my_rank). When all CTAs have stored, the kernel writes `epoch`
+ * into host_flag_peers[q][my_rank] on every GPU. Loads never touch peer memory; only plain stores do.
+ * A step is complete on a GPU after krk_cuda_wait_flags. Use two output buffers alternately (epoch
+ * parity) so that a fast GPU's next step cannot overwrite a row a slow GPU is still reading, and a
+ * strictly increasing epoch. Shapes the streaming kernel does not address return KRK_CUDA_ESHAPE. */
+int krk_cuda_gemv_allgather(void *const host_y_peers[], void *const host_flag_peers[], int n_peers, int my_rank,
+                            int epoch, int64_t slice_offset, int64_t n_out_total, const void *x_f32,
+                            const void *w, int wt, int64_t n_out_local, int64_t n_in, int64_t rows,
+                            void *stream);
+
+/* Buffers that peers store into. The reference is single-device (src/hip/backend_hip.hip:5036-5043), so
+ * these have no counterpart there. krk_cuda_peer_alloc: zero-filled device memory on the current device
+ * plus its 64-byte inter-process handle, which the host passes to the other processes of the box by any
+ * means. krk_cuda_peer_open maps another process's buffer into this one WITH the current device as the
+ * accessor: it enables peer access from the current device to the owner's and refuses
+ * (KRK_CUDA_EDEVICE) when the two GPUs cannot reach each other, so that a kernel never meets an
+ * unmapped address. close unmaps; free releases an own buffer (after every peer closed it). */
+#define KRK_CUDA_IPC_HANDLE_BYTES 64
+int krk_cuda_peer_alloc(void **dev_ptr, size_t bytes, unsigned char handle[KRK_CUDA_IPC_HANDLE_BYTES]);
+int krk_cuda_peer_open(void **dev_ptr, const unsigned char handle[KRK_CUDA_IPC_HANDLE_BYTES]);
+int krk_cuda_peer_close(void *dev_ptr);
+int krk_cuda_peer_free(void *dev_ptr);
+
+/* Enqueues a bounded wait until flags_i32[q] >= epoch for every q < n_peers (flags_i32 is this GPU's own
+ * flag array). A wait that runs out (about 2 s) raises krk_cuda_device_status() instead of hanging. */
+int krk_cuda_wait_flags(const void *flags_i32, int n_peers, int epoch, void *stream);
 
 /* Device-side status word of the current device: 0, or a KRK_CUDA_ETIMEOUT-class code
  * written by a kernel whose bounded wait gave up. Synchronises the device. */

@@ -62,6 +62,13 @@ SIGNATURES = {
     "krk_cuda_silu_mul": (_int, [_vp, _vp, _vp, _i64, _vp]),
     "krk_cuda_scatter_axpy_rows": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     "krk_cuda_sum_parts": (_int, [_vp, _vp, _int, _i64, _vp]),
+    "krk_cuda_gemv_allgather": (_int, [C.POINTER(_vp), C.POINTER(_vp), _int, _int, _int, _i64, _i64, _vp, _vp, _int, _i64,
+                                       _i64, _i64, _vp]),
+    "krk_cuda_wait_flags": (_int, [_vp, _int, _int, _vp]),
+    "krk_cuda_peer_alloc": (_int, [C.POINTER(_vp), C.c_size_t, C.c_char_p]),
+    "krk_cuda_peer_open": (_int, [C.POINTER(_vp), C.c_char_p]),
+    "krk_cuda_peer_close": (_int, [_vp]),
+    "krk_cuda_peer_free": (_int, [_vp]),
     "krk_cuda_device_status": (_int, []),
     "krk_cuda_launch_count": (_i64, []),
     "krk_cuda_family_count": (_i64, [_int]),
@@ -234,6 +241,66 @@ def sum_parts(parts, out=None, stream=None):
         out = torch.empty_like(parts[0])
     _check(lib.krk_cuda_sum_parts(_ptr(out), _ptr(parts), n_parts, n, _stream_ptr(stream)), "sum_parts")
     return out
+
+
+def gemv_allgather(y_peer_ptrs, flag_peer_ptrs, my_rank: int, epoch: int, slice_offset: int, n_out_total: int, x, w,
+                   wt: int, n_out_local: int, n_in: int, stream=None):
+    """Fused row-sharded GEMV + all-gather: y_peer_ptrs / flag_peer_ptrs are device addresses (ints) of every
+    GPU's full output buffer and flag array as mapped into this process."""
+    n = len(y_peer_ptrs)
+    rows = 1 if x.dim() == 1 else x.shape[0]
+    _check(lib.krk_cuda_gemv_allgather((_vp * n)(*y_peer_ptrs), (_vp * n)(*flag_peer_ptrs), n, my_rank, epoch, slice_offset,
+                                       n_out_total, _ptr(x), _ptr(w), wt, n_out_local, n_in, rows, _stream_ptr(stream)),
+           "gemv_allgather")
+
+
+def wait_flags(flags, n_peers: int, epoch: int, stream=None):
+    _check(lib.krk_cuda_wait_flags(_ptr(flags), n_peers, epoch, _stream_ptr(stream)), "wait_flags")
+
+
+class PeerBuffer:
+    """Device memory that other processes of the box can map (krk_cuda_peer_alloc / _open). ``tensor``
+    views it as a torch tensor on ``device`` (the accessor's device for a mapped buffer: the address is
+    only ever handed to this library's kernels, which store through NVLink)."""
+
+    def __init__(self, ptr: int, nbytes: int, handle: bytes, owned: bool):
+        self.ptr, self.nbytes, self.handle, self.owned = ptr, nbytes, handle, owned
+
+    @classmethod
+    def alloc(cls, nbytes: int) -> "PeerBuffer":
+        ptr, handle = _vp(), C.create_string_buffer(64)
+        _check(lib.krk_cuda_peer_alloc(C.byref(ptr), nbytes, handle), "peer_alloc")
+        return cls(ptr.value, nbytes, handle.raw, True)
+
+    @classmethod
+    def open(cls, handle: bytes, nbytes: int) -> "PeerBuffer":
+        ptr = _vp()
+        _check(lib.krk_cuda_peer_open(C.byref(ptr), handle), "peer_open")
+        return cls(ptr.value, nbytes, handle, False)
+
+    def tensor(self, shape, dtype):
+        """The buffer as a tensor of the current device (own buffers only)."""
+        import torch
+        if not self.owned:
+            raise ValueError("a mapped peer buffer is only addressed by kernels of this library")
+        itemsize = torch.empty(0, dtype=dtype).element_size()
+        typestr = {torch.float32: "<f4", torch.int32: "<i4", torch.uint8: "|u1"}[dtype]
+        n = 1
+        for d in shape:
+            n *= int(d)
+        if n * itemsize > self.nbytes:
+            raise ValueError("view larger than the buffer")
+
+        class _View:
+            __cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (self.ptr, False), "version": 2}
+        t = torch.as_tensor(_View(), device=torch.device("cuda", torch.cuda.current_device()))
+        t._krk_owner = self
+        return t
+
+    def release(self):
+        if self.ptr:
+            (lib.krk_cuda_peer_free if self.owned else lib.krk_cuda_peer_close)(self.ptr)
+            self.ptr = 0
 
 
 def device_status() -> int:

@@ -152,6 +152,16 @@ int launch_gemv_generic(const GemvMat *mats, int n_mat, int64_t n_in, int rows, 
 int launch_gemv_stream(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accumulate,
                        int silu_pair, cudaStream_t st);
 
+// Destination of a fused GEMV + all-gather: the full output row in every peer's memory.
+struct PeerScatter {
+    float *y[KRK_CUDA_MAX_PEERS];    // base of the full [rows][row_stride] output on each GPU (own one included)
+    int *flag[KRK_CUDA_MAX_PEERS];   // each GPU's flag array, one int per rank
+    int n_peers, my_rank, epoch;
+    long long row_stride, offset;    // n_out of the whole head; first row of this shard
+};
+int launch_gemv_stream_peers(const GemvMat &mat, int64_t n_in, int rows, const PeerScatter &ps, cudaStream_t st);
+int launch_flag_wait(const int *flags, int n, int epoch, cudaStream_t st);
+
 // Rows per granule the streaming kernel splits matrices of this type and width by (1 or 8), or 0 when
 // it does not address the shape (then the shape-agnostic kernels serve it).
 int stream_gran(int wt, int64_t n_in);

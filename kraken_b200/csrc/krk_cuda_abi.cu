@@ -252,6 +252,126 @@ int krk_cuda_sum_parts(void *out_f32, const void *parts_f32, int n_parts, int64_
                             n_parts, n, static_cast<cudaStream_t>(stream));
 }
 
+int krk_cuda_gemv_allgather(void *const host_y_peers[], void *const host_flag_peers[], int n_peers, int my_rank,
+                            int epoch, int64_t slice_offset, int64_t n_out_total, const void *x_f32, const void *w,
+                            int wt, int64_t n_out_local, int64_t n_in, int64_t rows, void *stream) {
+    if (n_peers < 1 || n_peers > KRK_CUDA_MAX_PEERS || my_rank < 0 || my_rank >= n_peers) return KRK_CUDA_EARG;
+    if (!host_y_peers || !host_flag_peers) return KRK_CUDA_ENULL;
+    if (slice_offset < 0 || n_out_total < slice_offset + n_out_local) return KRK_CUDA_ESHAPE;
+    const int rc = check_matmul_args(host_y_peers[my_rank], x_f32, w, wt, n_out_local, n_in, rows);
+    if (rc != KRK_CUDA_OK) return rc;
+    if (rows < 1 || rows > KRK_CUDA_MAX_ROWS || n_out_local < 1) return KRK_CUDA_ESHAPE;
+    PeerScatter ps;
+    for (int q = 0; q < n_peers; q++) {
+        if (!host_y_peers[q] || !host_flag_peers[q]) return KRK_CUDA_ENULL;
+        ps.y[q] = static_cast<float *>(host_y_peers[q]);
+        ps.flag[q] = static_cast<int *>(host_flag_peers[q]);
+    }
+    ps.n_peers = n_peers;
+    ps.my_rank = my_rank;
+    ps.epoch = epoch;
+    ps.row_stride = n_out_total;
+    ps.offset = slice_offset;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    GemvMat m;
+    m.w = static_cast<const uint8_t *>(w);
+    m.x = static_cast<const float *>(x_f32);
+    m.y = nullptr;
+    m.n_out = n_out_local;
+    m.wt = wt;
+    const int took = launch_gemv_stream_peers(m, n_in, (int)rows, ps, static_cast<cudaStream_t>(stream));
+    if (took < 0) return took;
+    return took == 1 ? KRK_CUDA_OK : KRK_CUDA_ESHAPE;
+}
+
+int krk_cuda_peer_alloc(void **dev_ptr, size_t bytes, unsigned char handle[KRK_CUDA_IPC_HANDLE_BYTES]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == KRK_CUDA_IPC_HANDLE_BYTES, "handle size");
+    if (!dev_ptr || !handle) return KRK_CUDA_ENULL;
+    if (bytes == 0) return KRK_CUDA_EARG;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        if (p) cudaFree(p);
+        return KRK_CUDA_ELAUNCH;
+    }
+    memcpy(handle, &h, sizeof h);
+    *dev_ptr = p;
+    return KRK_CUDA_OK;
+}
+
+int krk_cuda_peer_open(void **dev_ptr, const unsigned char handle[KRK_CUDA_IPC_HANDLE_BYTES]) {
+    if (!dev_ptr || !handle) return KRK_CUDA_ENULL;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    int me = 0;
+    cudaGetDevice(&me);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    void *p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        return KRK_CUDA_ELAUNCH;
+    }
+    // Make sure that kernels of THIS device can store there before anyone launches one.
+    cudaPointerAttributes attr;
+    e = cudaPointerGetAttributes(&attr, p);
+    if (e == cudaSuccess && attr.device != me) {
+        int can = 0;
+        e = cudaDeviceCanAccessPeer(&can, me, attr.device);
+        if (e == cudaSuccess && !can) {
+            cudaIpcCloseMemHandle(p);
+            return KRK_CUDA_EDEVICE;
+        }
+        if (e == cudaSuccess) {
+            e = cudaDeviceEnablePeerAccess(attr.device, 0);
+            if (e == cudaErrorPeerAccessAlreadyEnabled) {
+                cudaGetLastError();
+                e = cudaSuccess;
+            }
+        }
+    }
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        cudaIpcCloseMemHandle(p);
+        return KRK_CUDA_ELAUNCH;
+    }
+    *dev_ptr = p;
+    return KRK_CUDA_OK;
+}
+
+int krk_cuda_peer_close(void *dev_ptr) {
+    if (!dev_ptr) return KRK_CUDA_ENULL;
+    const cudaError_t e = cudaIpcCloseMemHandle(dev_ptr);
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        return KRK_CUDA_ELAUNCH;
+    }
+    return KRK_CUDA_OK;
+}
+
+int krk_cuda_peer_free(void *dev_ptr) {
+    if (!dev_ptr) return KRK_CUDA_ENULL;
+    const cudaError_t e = cudaFree(dev_ptr);
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        return KRK_CUDA_ELAUNCH;
+    }
+    return KRK_CUDA_OK;
+}
+
+int krk_cuda_wait_flags(const void *flags_i32, int n_peers, int epoch, void *stream) {
+    if (n_peers < 1 || n_peers > KRK_CUDA_MAX_PEERS) return KRK_CUDA_EARG;
+    if (!flags_i32) return KRK_CUDA_ENULL;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_flag_wait(static_cast<const int *>(flags_i32), n_peers, epoch, static_cast<cudaStream_t>(stream));
+}
+
 int krk_cuda_device_status(void) {
     int *p = device_status_word();
     if (!p) return KRK_CUDA_EDEVICE;

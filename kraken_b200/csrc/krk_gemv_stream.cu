@@ -27,6 +27,7 @@
 // Every wait on an mbarrier is bounded; a wait that gives up raises the device status word
 // and the CTA drains without touching memory it does not own.
 #include <cfloat>
+#include <cstdlib>
 
 #include "krk_common.cuh"
 
@@ -69,6 +70,13 @@ struct StreamParams {
     int total_gran;
     int gran_q, gran_r;   // total_gran = grid * gran_q + gran_r
     const StreamTable *dev_table;   // when set, matrices and granule prefix come from device memory
+    // Fused all-gather (single-matrix launches of a row shard): y goes to slot `peer_offset` of the full
+    // output row in every peer's memory (this GPU's own buffer included), then the peers are told.
+    float *peer_y[KRK_CUDA_MAX_PEERS];
+    int *peer_flag[KRK_CUDA_MAX_PEERS];   // peer_flag[q][my_rank] <- epoch once every CTA here has stored
+    int n_peers, my_rank, epoch;
+    long long peer_row_stride, peer_offset;
+    unsigned *done_counter;
     int *status;
 };
 
@@ -668,16 +676,36 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                     if (p.step == 2 && s.which == 0) {
                         gate[i] = v;
                     } else if (row < s.n_rows) {
-                        const GemvMat &mat = tv.mat[p.step == 2 ? s.mat - 1 : s.mat];
-                        float *y = mat.y + (size_t)r * mat.n_out + s.row0 + row;
-                        if (p.step == 2) v = __fmul_rn(__fdiv_rn(gate[i], __fadd_rn(1.0f, expf(-gate[i]))), v);
-                        *y = p.accumulate ? __fadd_rn(*y, v) : v;
+                        if (p.n_peers > 0) {
+                            // plain stores into every GPU's copy of the full row (NVLink peer stores)
+                            const long long at = (long long)r * p.peer_row_stride + p.peer_offset + s.row0 + row;
+                            for (int q = 0; q < p.n_peers; q++) p.peer_y[q][at] = v;
+                        } else {
+                            const GemvMat &mat = tv.mat[p.step == 2 ? s.mat - 1 : s.mat];
+                            float *y = mat.y + (size_t)r * mat.n_out + s.row0 + row;
+                            if (p.step == 2) v = __fmul_rn(__fdiv_rn(gate[i], __fadd_rn(1.0f, expf(-gate[i]))), v);
+                            *y = p.accumulate ? __fadd_rn(*y, v) : v;
+                        }
                     }
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sm->red_empty[slot]));
         });
+        if (p.n_peers > 0) {
+            // This CTA's stores are out; the CTA that reports last publishes the epoch to every peer.
+            __threadfence_system();
+            __syncwarp();
+            if (lane == 0) {
+                const unsigned done = atomicAdd(p.done_counter, 1u);
+                if (done == gridDim.x - 1) {
+                    *p.done_counter = 0;
+                    __threadfence_system();
+                    for (int q = 0; q < p.n_peers; q++) *reinterpret_cast<volatile int *>(p.peer_flag[q] + p.my_rank) = p.epoch;
+                    __threadfence_system();
+                }
+            }
+        }
         return;
     }
 
@@ -866,6 +894,10 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
     p.whole_tiles = 0;
     p.gran = 1;
     p.dev_table = nullptr;
+    p.n_peers = 0;
+    p.my_rank = p.epoch = 0;
+    p.peer_row_stride = p.peer_offset = 0;
+    p.done_counter = nullptr;
     if (WT == KRK_CUDA_Q6_K && (n_in % 2048) != 0) {
         // 210-byte blocks: rows are 16-byte multiples only for K % 2048 == 0. Otherwise whole 16-row
         // tiles are copied contiguously (needs 4-byte-multiple rows and the tile in one stage).
@@ -884,9 +916,14 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
     }
     const int smem_struct = rows <= 2 ? (int)sizeof(Smem<1>) : rows <= 4 ? (int)sizeof(Smem<2>) : (int)sizeof(Smem<4>);
     const int fixed = align_up(smem_struct, 128) + plane_bytes<WT>(p.n_in, rows) + chunk_sum_bytes<WT>(p.n_in, rows);
-    // Past ~96 KB of staged weights per SM more depth buys nothing.
+    // Depth of the ring: KRK_CUDA_GEMV_STAGE_KB of staged weights per SM (default 96), at least 3 stages.
+    static const int stage_kb = [] {
+        const char *e = std::getenv("KRK_CUDA_GEMV_STAGE_KB");
+        const int v = e ? std::atoi(e) : 0;
+        return v > 0 ? v : 96;
+    }();
     const int max_fit = (kSmemLimit - fixed) / p.stage_bytes;
-    int want = (96 * 1024 + p.stage_bytes - 1) / p.stage_bytes;
+    int want = (stage_kb * 1024 + p.stage_bytes - 1) / p.stage_bytes;
     want = want < 3 ? 3 : (want > kMaxStages ? kMaxStages : want);
     p.n_stages = want < max_fit ? want : max_fit;
     if (p.n_stages < 2) return false;
@@ -945,6 +982,63 @@ int launch_table_fmt(const StreamTable *table, int64_t n_in, int silu_pair, cuda
 }
 
 template <int WT>
+int launch_peers_fmt(const GemvMat &mat, int64_t n_in, int rows, const PeerScatter &ps, cudaStream_t st) {
+    StreamParams p;
+    size_t smem = 0;
+    if (!setup_format<WT>(p, n_in, rows, 0, &smem)) return 0;
+    if (mat.n_out > (1 << 30) || mat.n_out <= 0) return 0;
+    p.mat[0] = mat;
+    p.n_entries = 1;
+    p.gran_begin[0] = 0;
+    const int total = (int)((mat.n_out + p.gran - 1) / p.gran);
+    p.gran_begin[1] = total;
+    p.total_gran = total;
+    p.status = device_status_word();
+    if (!p.status) return KRK_CUDA_EDEVICE;
+    static unsigned *counter_of[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return KRK_CUDA_EDEVICE;
+    if (!counter_of[dev]) {
+        if (cudaMalloc(&counter_of[dev], sizeof(unsigned)) != cudaSuccess) return KRK_CUDA_EDEVICE;
+        cudaMemset(counter_of[dev], 0, sizeof(unsigned));
+    }
+    p.done_counter = counter_of[dev];
+    p.n_peers = ps.n_peers;
+    for (int q = 0; q < ps.n_peers; q++) {
+        p.peer_y[q] = ps.y[q];
+        p.peer_flag[q] = ps.flag[q];
+    }
+    p.my_rank = ps.my_rank;
+    p.epoch = ps.epoch;
+    p.peer_row_stride = ps.row_stride;
+    p.peer_offset = ps.offset;
+    const int sms = sm_count();
+    const int grid = total < sms ? total : sms;
+    p.gran_q = total / grid;
+    p.gran_r = total % grid;
+    const int rc = launch_rows<WT>(p, grid, smem, st);
+    return rc == KRK_CUDA_OK ? 1 : rc;
+}
+
+// One warp: lane q waits (bounded) until flag[q] has reached `epoch`, i.e. until peer q has stored its
+// slice of the row into this GPU's buffer. A wait that gives up raises the device status word.
+__global__ void __launch_bounds__(32) flag_wait_kernel(const int *flags, int n, int epoch, int *status) {
+    const int q = threadIdx.x;
+    if (q < n) {
+        const long long t0 = clock64();
+        while (*reinterpret_cast<const volatile int *>(flags + q) < epoch) {
+            __nanosleep(200);
+            if (clock64() - t0 > kWaitCycles) {
+                atomicExch(status, KRK_CUDA_ETIMEOUT);
+                break;
+            }
+        }
+    }
+    __threadfence_system();
+}
+
+template <int WT>
 int gran_fmt(int64_t n_in) {
     StreamParams p;
     size_t smem = 0;
@@ -974,6 +1068,23 @@ int launch_gemv_stream_table(const StreamTable *table, int wt, int64_t n_in, int
     case KRK_CUDA_Q8_0: return launch_table_fmt<KRK_CUDA_Q8_0>(table, n_in, silu_pair, st);
     default: return 0;
     }
+}
+
+int launch_gemv_stream_peers(const GemvMat &mat, int64_t n_in, int rows, const PeerScatter &ps, cudaStream_t st) {
+    switch (mat.wt) {
+    case KRK_CUDA_Q4_K: return launch_peers_fmt<KRK_CUDA_Q4_K>(mat, n_in, rows, ps, st);
+    case KRK_CUDA_Q6_K: return launch_peers_fmt<KRK_CUDA_Q6_K>(mat, n_in, rows, ps, st);
+    case KRK_CUDA_Q8_0: return launch_peers_fmt<KRK_CUDA_Q8_0>(mat, n_in, rows, ps, st);
+    default: return 0;
+    }
+}
+
+int launch_flag_wait(const int *flags, int n, int epoch, cudaStream_t st) {
+    int *status = device_status_word();
+    if (!status) return KRK_CUDA_EDEVICE;
+    flag_wait_kernel<<<1, 32, 0, st>>>(flags, n, epoch, status);
+    note_launch();
+    return check_launch();
 }
 
 int stream_gran(int wt, int64_t n_in) {

@@ -87,6 +87,69 @@ class ShardedHead:
         return torch.cat([self._gather[r, :, :c] for r, (_, c) in enumerate(self.ranges)], dim=1)
 
 
+class PeerHead:
+    """Row-sharded head whose GEMV epilogue stores its slice straight into every GPU's copy of the logits
+    row (krk_cuda_gemv_allgather): compute and all-gather are one kernel over NVLink peer memory, followed
+    by a bounded flag wait. Two output buffers alternate so that a fast rank's next step never overwrites a
+    row a slow rank still reads. One process per GPU of one box; the buffers come from krk_cuda_peer_alloc and
+    their 64-byte handles travel through the process group. Results are bit-identical to the unsharded GEMV.
+    """
+
+    def __init__(self, n_out: int, n_in: int, wt: int, w_local, rows: int = 1, group=None, align: int = 8):
+        import torch
+        import torch.distributed as dist
+        from . import capi
+        self.capi, self.group = capi, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.n_out, self.n_in, self.wt, self.w_local = n_out, n_in, wt, w_local
+        self.begin, self.count = row_range(n_out, self.world, self.rank, align)
+        # two logits buffers and one flag word per peer, in memory the other processes can map
+        out_bytes, flag_bytes = rows * n_out * 4, 4 * self.world
+        self._own = [capi.PeerBuffer.alloc(out_bytes), capi.PeerBuffer.alloc(out_bytes), capi.PeerBuffer.alloc(flag_bytes)]
+        self.out = [self._own[b].tensor((rows, n_out), torch.float32) for b in range(2)]
+        self.flags = self._own[2].tensor((self.world,), torch.int32)
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, [buf.handle for buf in self._own], group=group)
+        self._mapped = []          # the peers' buffers as mapped here
+        self.peer_out = [[], []]
+        self.peer_flags = []
+        for q, handles in enumerate(everyone):
+            if q == self.rank:
+                bufs = self._own
+            else:
+                bufs = [capi.PeerBuffer.open(h, n) for h, n in zip(handles, (out_bytes, out_bytes, flag_bytes))]
+                self._mapped.append(bufs)
+            self.peer_out[0].append(bufs[0].ptr)
+            self.peer_out[1].append(bufs[1].ptr)
+            self.peer_flags.append(bufs[2].ptr)
+        self.epoch = 0
+        dist.barrier(group=group)
+
+    def close(self):
+        """Unmap the peers' buffers, then (after a barrier: nobody still maps ours) free our own."""
+        import torch
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        for bufs in self._mapped:
+            for buf in bufs:
+                buf.release()
+        self._mapped = []
+        dist.barrier(group=self.group)
+        self.out, self.flags = [], None
+        for buf in self._own:
+            buf.release()
+        self._own = []
+
+    def forward(self, x):
+        """x: f32 [rows, n_in] on this GPU (the same on every rank). Returns the full [rows, n_out] row."""
+        self.epoch += 1
+        b = self.epoch & 1
+        self.capi.gemv_allgather(self.peer_out[b], self.peer_flags, self.rank, self.epoch, self.begin, self.n_out, x,
+                                 self.w_local, self.wt, self.count, self.n_in)
+        self.capi.wait_flags(self.flags, self.world, self.epoch)
+        return self.out[b]
+
+
 class ShardedMoE:
     """Routed-expert FFN with the expert bank split over the ranks of ``group``.
 

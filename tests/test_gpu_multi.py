@@ -1,0 +1,73 @@
+"""Two GPUs of one box: the fused GEMV + all-gather over peer stores, and the NCCL paths, against the
+unsharded kernels. Skipped on a single-GPU box (the host logic is covered on CPU over gloo)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from kraken_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, ret):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from kraken_b200 import capi, shard
+        seed = synth.BASE_SEED + 44
+        n_out, n_in, wt = 4008, 4096, synth.Q6_K
+        w_full = torch.from_numpy(synth.weights(wt, n_out, n_in, seed)).cuda()
+        begin, count = shard.row_range(n_out, world, rank, 8)
+        w_local = w_full[begin:begin + count].contiguous()
+        for rows in (1, 3):
+            head = shard.PeerHead(n_out, n_in, wt, w_local, rows=rows)
+            nccl_head = shard.ShardedHead(n_out, shard.cuda_head_fn(w_local, wt, count, n_in), align=8)
+            for step in range(5):          # several steps: both buffers, increasing epochs
+                x = torch.from_numpy(synth.activations(rows, n_in, seed + step)).cuda()
+                want = capi.gemv(x, w_full, wt, n_out, n_in)
+                got = head.forward(x)
+                torch.cuda.synchronize()
+                assert capi.device_status() == 0
+                assert torch.equal(got, want), f"peer-store head differs at step {step}"
+                assert torch.equal(nccl_head.forward(x), want)
+            head.close()
+            dist.barrier()
+        ret[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpus_peer_head_and_nccl_head():
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(240)
+        for p in procs:
+            if p.is_alive():
+                p.kill()          # our own child, by handle
+        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+        assert dict(ret) == {0: "ok", 1: "ok"}
