@@ -68,16 +68,52 @@ def measured_peaks():
 # ---- clocks ---------------------------------------------------------------------------------
 
 class ClockSampler:
+    """SM clock and throttle reasons of one GPU, read through NVML from a thread of this process every few
+    milliseconds (read-only queries). `mark()` brackets the timed region: only samples taken inside it are
+    reported, so a short run still carries a few. Falls back to an `nvidia-smi -lms` child when the NVML
+    binding is missing."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index = index
-        self.proc = None
-        self.path = None
+    def __init__(self, index: int, uuid: str = None):
+        self.index, self.uuid = index, uuid
+        self.proc = self.path = self.thread = None
+        self.samples = []          # (time, sm_mhz, reasons bitmask)
+        self.t0 = self.t1 = None
+        self.sm_max = None
+        self._stop = False
 
     def start(self):
+        try:
+            import threading
+            import pynvml
+            pynvml.nvmlInit()
+            handle = None
+            if self.uuid:
+                try:
+                    handle = pynvml.nvmlDeviceGetHandleByUUID(self.uuid)
+                except Exception:
+                    handle = None
+            if handle is None:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+
+            def loop():
+                while not self._stop:
+                    try:
+                        mhz = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                        self.samples.append((time.perf_counter(), mhz, int(reasons_fn(handle))))
+                    except Exception:
+                        pass
+                    time.sleep(0.004)
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -87,8 +123,28 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def mark(self):
+        """First call: the timed region starts; second call: it has ended."""
+        if self.t0 is None:
+            self.t0 = time.perf_counter()
+        else:
+            self.t1 = time.perf_counter()
+
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.thread is not None:
+            self._stop = True
+            self.thread.join(timeout=2)
+            inside = [s for s in self.samples if self.t0 is None or self.t1 is None or self.t0 <= s[0] <= self.t1]
+            # NVML bit masks of the reasons that invalidate (or annotate) a measurement
+            bits = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20}
+            if inside:
+                mask = 0
+                for _, _, r in inside:
+                    mask |= r
+                out.update(sm_mhz=statistics.median(s[1] for s in inside), sm_max_mhz=self.sm_max,
+                           reasons=sorted(n for n, b in bits.items() if mask & b), samples=len(inside), source="nvml")
+            return out
         if not self.proc:
             return out
         self.proc.terminate()          # our own child, by handle
@@ -112,7 +168,8 @@ class ClockSampler:
                     reasons.add(name)
         os.unlink(self.path)
         if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm))
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm),
+                       source="nvidia-smi")
         return out
 
 
@@ -199,17 +256,23 @@ def run_ours(args):
                 replay()
         barrier()
 
-    sampler = ClockSampler(local)
+    try:
+        uuid = "GPU-" + str(torch.cuda.get_device_properties(local).uuid)
+    except Exception:
+        uuid = None
+    sampler = ClockSampler(local, uuid)
     if rank == 0:
         sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark()
     with torch.cuda.stream(stream):
         ev0.record(stream)
         for _ in range(args.steps):
             replay()
         ev1.record(stream)
     barrier()
+    sampler.mark()
     ms = ev0.elapsed_time(ev1)
     launches = launches_per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
@@ -256,7 +319,8 @@ def run_ours(args):
         return float(t.item())
 
     ms, e2e_ms = reduce_max(ms), reduce_max(e2e_ms)
-    sharded = None if args.no_extras else sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max)
+    extras = set() if args.no_extras else {e for e in args.extras.split(",") if e}
+    sharded = None if "sharded" not in extras else sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max)
 
     if rank == 0:
         wbytes = layer_weight_bytes() * args.layers
@@ -289,8 +353,12 @@ def run_ours(args):
         }
         if sharded is not None:
             line["sharded"] = sharded
-        if world == 1 and not args.no_extras:
-            line["extra"] = {"prefill": prefill_extra(torch, capi, gen), "decode": decode_extra(torch, capi, gen, barrier)}
+        if world == 1 and extras & {"prefill", "decode"}:
+            line["extra"] = {}
+            if "prefill" in extras:
+                line["extra"]["prefill"] = prefill_extra(torch, capi, gen)
+            if "decode" in extras:
+                line["extra"]["decode"] = decode_extra(torch, capi, gen, barrier)
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(sample_seconds=args.cpu_seconds)
         print(json.dumps(line), flush=True)
@@ -377,20 +445,28 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
     ms_full = reduce_max(timed(torch, head_call, 60, barrier, variants=n_rep))
     ms_local = reduce_max(timed(torch, head_local, 60, barrier, variants=n_rep))
     ms_full_host = reduce_max(timed(torch, head_call, 60, barrier))
-    ms_peer = None
+    ms_peer = ms_peer_host = None
     if world > 1:
-        # the fused form: the GEMV's epilogue stores into every GPU's logits row, then a bounded flag wait
+        # the fused form: the GEMV's epilogue stores into every GPU's logits row and its last CTA waits
+        # (bounded) for the peers' slices. An even number of captured steps keeps the two output buffers
+        # alternating across replays.
         peer = shard.PeerHead(n_out, n_in, synth.Q6_K, ws[0], rows=1, align=8)
 
         def peer_call(i):
             peer.w_local = ws[i % n_rep]
             return peer.forward(x)
-        ms_peer = reduce_max(timed(torch, peer_call, 60, barrier))
+        ms_peer = reduce_max(timed(torch, peer_call, 60, barrier, variants=n_rep if n_rep % 2 == 0 else 2 * n_rep))
+        ms_peer_host = reduce_max(timed(torch, peer_call, 60, barrier))
+        torch.cuda.synchronize()
+        if capi.device_status() != 0:
+            raise RuntimeError("a bounded wait of the fused all-gather gave up")
+        peer.close()
     wbytes = n_out * synth.row_bytes(synth.Q6_K, n_in)
     out["head_q6_k_128256x4096"] = {
         "ms_per_token": round(ms_full, 5), "ms_gemv_only": round(ms_local, 5), "ms_per_token_host_launched": round(ms_full_host, 5),
         "launch": "CUDA graph replay (GEMV + NCCL all-gather)",
         "ms_per_token_peer_store_fused": None if ms_peer is None else round(ms_peer, 5),
+        "ms_per_token_peer_store_fused_host_launched": None if ms_peer_host is None else round(ms_peer_host, 5),
         "weight_gbps_peer_store_fused": None if ms_peer is None else round(n_out * synth.row_bytes(synth.Q6_K, n_in) / (ms_peer * 1e-3) / 1e9, 1),
         "weight_gbps_all_gpus": round(wbytes / (ms_full * 1e-3) / 1e9, 1),
         "weight_gbps_gemv_only": round(wbytes / (ms_local * 1e-3) / 1e9, 1),
@@ -607,7 +683,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
-    ap.add_argument("--no-extras", action="store_true", help="skip the prefill GEMM side measurements")
+    ap.add_argument("--no-extras", action="store_true", help="skip every side measurement")
+    ap.add_argument("--extras", default="prefill,decode,sharded",
+                    help="side measurements to run: any of prefill,decode,sharded (profiling runs pick one)")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--layers", type=int, default=N_LAYERS,
                     help="layers per step; fewer than 32 is for profiler captures only, not a bench value")

@@ -176,20 +176,26 @@ int krk_cuda_scatter_axpy_rows(void *dst_f32, const void *src_f32, const void *r
  * deterministic combine of expert-sharded partial sums after they were gathered. */
 int krk_cuda_sum_parts(void *out_f32, const void *parts_f32, int n_parts, int64_t n, void *stream);
 
-/* Row-sharded GEMV fused with the all-gather of its output over NVLink peer memory; no counterpart in
- * the reference, which is single-device (src/hip/backend_hip.hip:5036-5043). This GPU holds rows
- * [slice_offset, slice_offset + n_out_local) of a matrix with n_out_total rows. The kernel is the decode
- * GEMV of krk_cuda_gemv, but its epilogue stores every output value into the full
+/* Row-sharded GEMV fused with its all-gather over NVLink (the reference is single-device, so this has no
+ * counterpart there). This GPU holds rows [slice_offset, slice_offset + n_out_local) of a head of
+ * n_out_total rows; the kernel's epilogue stores its slice of y straight into the
  * [rows][n_out_total] row of EVERY GPU: host_y_peers[q] is that buffer on GPU q as mapped into this
- * process (this GPU's own buffer at q == my_rank). When all CTAs have stored, the kernel writes `epoch`
- * into host_flag_peers[q][my_rank] on every GPU. Loads never touch peer memory; only plain stores do.
- * A step is complete on a GPU after krk_cuda_wait_flags. Use two output buffers alternately (epoch
- * parity) so that a fast GPU's next step cannot overwrite a row a slow GPU is still reading, and a
- * strictly increasing epoch. Shapes the streaming kernel does not address return KRK_CUDA_ESHAPE. */
+ * process by krk_cuda_peer_open (this GPU's own buffer at q == my_rank). When all CTAs have stored, the
+ * kernel writes the step's epoch into host_flag_peers[q][my_rank] on every GPU. Loads never touch peer
+ * memory; only plain stores do.
+ *   epoch > 0: the host counts steps (strictly increasing, the same on every GPU).
+ *   epoch == 0: the step count lives on the device, in host_flag_peers[my_rank][n_peers] (so each flag
+ *     array holds n_peers + 1 ints, zero at start); the launch carries no per-step value and can be
+ *     replayed from a CUDA graph.
+ *   wait_in_kernel != 0: the last CTA also waits (bounded, about 2 s, then krk_cuda_device_status() is
+ *     raised) until every peer's epoch has arrived here, so the end of the kernel is the end of the
+ *     all-gather on this GPU. With 0 the host enqueues krk_cuda_wait_flags where it wants the row.
+ * Use two output buffers alternately so that a fast GPU's next step cannot overwrite a row a slow GPU
+ * is still reading. Shapes the streaming kernel does not address return KRK_CUDA_ESHAPE. */
 int krk_cuda_gemv_allgather(void *const host_y_peers[], void *const host_flag_peers[], int n_peers, int my_rank,
-                            int epoch, int64_t slice_offset, int64_t n_out_total, const void *x_f32,
-                            const void *w, int wt, int64_t n_out_local, int64_t n_in, int64_t rows,
-                            void *stream);
+                            int epoch, int wait_in_kernel, int64_t slice_offset, int64_t n_out_total,
+                            const void *x_f32, const void *w, int wt, int64_t n_out_local, int64_t n_in,
+                            int64_t rows, void *stream);
 
 /* Buffers that peers store into. The reference is single-device (src/hip/backend_hip.hip:5036-5043), so
  * these have no counterpart there. krk_cuda_peer_alloc: zero-filled device memory on the current device

@@ -62,7 +62,7 @@ SIGNATURES = {
     "krk_cuda_silu_mul": (_int, [_vp, _vp, _vp, _i64, _vp]),
     "krk_cuda_scatter_axpy_rows": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     "krk_cuda_sum_parts": (_int, [_vp, _vp, _int, _i64, _vp]),
-    "krk_cuda_gemv_allgather": (_int, [C.POINTER(_vp), C.POINTER(_vp), _int, _int, _int, _i64, _i64, _vp, _vp, _int, _i64,
+    "krk_cuda_gemv_allgather": (_int, [C.POINTER(_vp), C.POINTER(_vp), _int, _int, _int, _int, _i64, _i64, _vp, _vp, _int, _i64,
                                        _i64, _i64, _vp]),
     "krk_cuda_wait_flags": (_int, [_vp, _int, _int, _vp]),
     "krk_cuda_peer_alloc": (_int, [C.POINTER(_vp), C.c_size_t, C.c_char_p]),
@@ -244,12 +244,12 @@ def sum_parts(parts, out=None, stream=None):
 
 
 def gemv_allgather(y_peer_ptrs, flag_peer_ptrs, my_rank: int, epoch: int, slice_offset: int, n_out_total: int, x, w,
-                   wt: int, n_out_local: int, n_in: int, stream=None):
+                   wt: int, n_out_local: int, n_in: int, wait_in_kernel: bool = True, stream=None):
     """Fused row-sharded GEMV + all-gather: y_peer_ptrs / flag_peer_ptrs are device addresses (ints) of every
     GPU's full output buffer and flag array as mapped into this process."""
     n = len(y_peer_ptrs)
     rows = 1 if x.dim() == 1 else x.shape[0]
-    _check(lib.krk_cuda_gemv_allgather((_vp * n)(*y_peer_ptrs), (_vp * n)(*flag_peer_ptrs), n, my_rank, epoch, slice_offset,
+    _check(lib.krk_cuda_gemv_allgather((_vp * n)(*y_peer_ptrs), (_vp * n)(*flag_peer_ptrs), n, my_rank, epoch, int(wait_in_kernel), slice_offset,
                                        n_out_total, _ptr(x), _ptr(w), wt, n_out_local, n_in, rows, _stream_ptr(stream)),
            "gemv_allgather")
 

@@ -156,7 +156,8 @@ int launch_gemv_stream(const GemvMat *mats, int n_mat, int64_t n_in, int rows, i
 struct PeerScatter {
     float *y[KRK_CUDA_MAX_PEERS];    // base of the full [rows][row_stride] output on each GPU (own one included)
     int *flag[KRK_CUDA_MAX_PEERS];   // each GPU's flag array, one int per rank
-    int n_peers, my_rank, epoch;
+    int n_peers, my_rank, epoch;     // epoch 0: counted on the device, in flag[my_rank][n_peers]
+    int wait_peers;                  // the kernel itself waits for every peer's epoch before it ends
     long long row_stride, offset;    // n_out of the whole head; first row of this shard
 };
 int launch_gemv_stream_peers(const GemvMat &mat, int64_t n_in, int rows, const PeerScatter &ps, cudaStream_t st);

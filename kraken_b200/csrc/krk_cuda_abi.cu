@@ -253,8 +253,10 @@ int krk_cuda_sum_parts(void *out_f32, const void *parts_f32, int n_parts, int64_
 }
 
 int krk_cuda_gemv_allgather(void *const host_y_peers[], void *const host_flag_peers[], int n_peers, int my_rank,
-                            int epoch, int64_t slice_offset, int64_t n_out_total, const void *x_f32, const void *w,
-                            int wt, int64_t n_out_local, int64_t n_in, int64_t rows, void *stream) {
+                            int epoch, int wait_in_kernel, int64_t slice_offset, int64_t n_out_total,
+                            const void *x_f32, const void *w, int wt, int64_t n_out_local, int64_t n_in,
+                            int64_t rows, void *stream) {
+    if (epoch < 0) return KRK_CUDA_EARG;
     if (n_peers < 1 || n_peers > KRK_CUDA_MAX_PEERS || my_rank < 0 || my_rank >= n_peers) return KRK_CUDA_EARG;
     if (!host_y_peers || !host_flag_peers) return KRK_CUDA_ENULL;
     if (slice_offset < 0 || n_out_total < slice_offset + n_out_local) return KRK_CUDA_ESHAPE;
@@ -270,6 +272,7 @@ int krk_cuda_gemv_allgather(void *const host_y_peers[], void *const host_flag_pe
     ps.n_peers = n_peers;
     ps.my_rank = my_rank;
     ps.epoch = epoch;
+    ps.wait_peers = wait_in_kernel != 0;
     ps.row_stride = n_out_total;
     ps.offset = slice_offset;
     if (!device_state()) return KRK_CUDA_EDEVICE;

@@ -74,7 +74,7 @@ struct StreamParams {
     // output row in every peer's memory (this GPU's own buffer included), then the peers are told.
     float *peer_y[KRK_CUDA_MAX_PEERS];
     int *peer_flag[KRK_CUDA_MAX_PEERS];   // peer_flag[q][my_rank] <- epoch once every CTA here has stored
-    int n_peers, my_rank, epoch;
+    int n_peers, my_rank, epoch, wait_peers;
     long long peer_row_stride, peer_offset;
     unsigned *done_counter;
     int *status;
@@ -693,17 +693,39 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
             if (lane == 0) mbar_arrive(smem_u32(&sm->red_empty[slot]));
         });
         if (p.n_peers > 0) {
-            // This CTA's stores are out; the CTA that reports last publishes the epoch to every peer.
+            // This CTA's stores are out. The CTA that reports last publishes the epoch to every peer and
+            // then waits (bounded) until every peer has published the same epoch here, so that the end
+            // of this kernel is the end of the all-gather on this GPU.
             __threadfence_system();
             __syncwarp();
-            if (lane == 0) {
-                const unsigned done = atomicAdd(p.done_counter, 1u);
-                if (done == gridDim.x - 1) {
+            unsigned done = 0;
+            if (lane == 0) done = atomicAdd(p.done_counter, 1u);
+            done = __shfl_sync(0xffffffffu, done, 0);
+            if (done == gridDim.x - 1) {
+                int *own = p.peer_flag[p.my_rank];
+                int epoch = p.epoch;
+                if (lane == 0) {
                     *p.done_counter = 0;
+                    if (epoch == 0) {   // device-counted steps: the count lives behind this GPU's flags
+                        epoch = own[p.n_peers] + 1;
+                        own[p.n_peers] = epoch;
+                    }
                     __threadfence_system();
-                    for (int q = 0; q < p.n_peers; q++) *reinterpret_cast<volatile int *>(p.peer_flag[q] + p.my_rank) = p.epoch;
+                    for (int q = 0; q < p.n_peers; q++) *reinterpret_cast<volatile int *>(p.peer_flag[q] + p.my_rank) = epoch;
                     __threadfence_system();
                 }
+                epoch = __shfl_sync(0xffffffffu, epoch, 0);
+                if (p.wait_peers && lane < p.n_peers) {
+                    const long long t0 = clock64();
+                    while (*reinterpret_cast<const volatile int *>(own + lane) < epoch) {
+                        __nanosleep(100);
+                        if (clock64() - t0 > kWaitCycles) {
+                            atomicExch(p.status, KRK_CUDA_ETIMEOUT);
+                            break;
+                        }
+                    }
+                }
+                __threadfence_system();
             }
         }
         return;
@@ -1011,6 +1033,7 @@ int launch_peers_fmt(const GemvMat &mat, int64_t n_in, int rows, const PeerScatt
     }
     p.my_rank = ps.my_rank;
     p.epoch = ps.epoch;
+    p.wait_peers = ps.wait_peers;
     p.peer_row_stride = ps.row_stride;
     p.peer_offset = ps.offset;
     const int sms = sm_count();

@@ -89,25 +89,26 @@ class ShardedHead:
 
 class PeerHead:
     """Row-sharded head whose GEMV epilogue stores its slice straight into every GPU's copy of the logits
-    row (krk_cuda_gemv_allgather): compute and all-gather are one kernel over NVLink peer memory, followed
-    by a bounded flag wait. Two output buffers alternate so that a fast rank's next step never overwrites a
+    row (krk_cuda_gemv_allgather): compute and all-gather are one kernel over NVLink peer memory, whose last
+    CTA waits (bounded) for the peers' slices; ``host_counted`` keeps the wait as a second small kernel. Two output buffers alternate so that a fast rank's next step never overwrites a
     row a slow rank still reads. One process per GPU of one box; the buffers come from krk_cuda_peer_alloc and
     their 64-byte handles travel through the process group. Results are bit-identical to the unsharded GEMV.
     """
 
-    def __init__(self, n_out: int, n_in: int, wt: int, w_local, rows: int = 1, group=None, align: int = 8):
+    def __init__(self, n_out: int, n_in: int, wt: int, w_local, rows: int = 1, group=None, align: int = 8,
+                 host_counted: bool = False):
         import torch
         import torch.distributed as dist
         from . import capi
-        self.capi, self.group = capi, group
+        self.capi, self.group, self.host_counted = capi, group, host_counted
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.n_out, self.n_in, self.wt, self.w_local = n_out, n_in, wt, w_local
         self.begin, self.count = row_range(n_out, self.world, self.rank, align)
         # two logits buffers and one flag word per peer, in memory the other processes can map
-        out_bytes, flag_bytes = rows * n_out * 4, 4 * self.world
+        out_bytes, flag_bytes = rows * n_out * 4, 4 * (self.world + 1)   # + the device-side step count
         self._own = [capi.PeerBuffer.alloc(out_bytes), capi.PeerBuffer.alloc(out_bytes), capi.PeerBuffer.alloc(flag_bytes)]
         self.out = [self._own[b].tensor((rows, n_out), torch.float32) for b in range(2)]
-        self.flags = self._own[2].tensor((self.world,), torch.int32)
+        self.flags = self._own[2].tensor((self.world + 1,), torch.int32)
         everyone = [None] * self.world
         dist.all_gather_object(everyone, [buf.handle for buf in self._own], group=group)
         self._mapped = []          # the peers' buffers as mapped here
@@ -141,12 +142,18 @@ class PeerHead:
         self._own = []
 
     def forward(self, x):
-        """x: f32 [rows, n_in] on this GPU (the same on every rank). Returns the full [rows, n_out] row."""
+        """x: f32 [rows, n_in] on this GPU (the same on every rank). Returns the full [rows, n_out] row,
+        complete in stream order. Steps alternate between the two buffers; with device-counted steps
+        (the default) a pair of consecutive calls can be captured into a CUDA graph and replayed."""
         self.epoch += 1
         b = self.epoch & 1
-        self.capi.gemv_allgather(self.peer_out[b], self.peer_flags, self.rank, self.epoch, self.begin, self.n_out, x,
-                                 self.w_local, self.wt, self.count, self.n_in)
-        self.capi.wait_flags(self.flags, self.world, self.epoch)
+        if self.host_counted:
+            self.capi.gemv_allgather(self.peer_out[b], self.peer_flags, self.rank, self.epoch, self.begin, self.n_out, x,
+                                     self.w_local, self.wt, self.count, self.n_in, wait_in_kernel=False)
+            self.capi.wait_flags(self.flags, self.world, self.epoch)
+        else:
+            self.capi.gemv_allgather(self.peer_out[b], self.peer_flags, self.rank, 0, self.begin, self.n_out, x,
+                                     self.w_local, self.wt, self.count, self.n_in, wait_in_kernel=True)
         return self.out[b]
 
 

@@ -34,8 +34,8 @@ def _worker(rank, world, port, ret):
         w_full = torch.from_numpy(synth.weights(wt, n_out, n_in, seed)).cuda()
         begin, count = shard.row_range(n_out, world, rank, 8)
         w_local = w_full[begin:begin + count].contiguous()
-        for rows in (1, 3):
-            head = shard.PeerHead(n_out, n_in, wt, w_local, rows=rows)
+        for rows, host_counted in ((1, False), (3, False), (2, True)):
+            head = shard.PeerHead(n_out, n_in, wt, w_local, rows=rows, host_counted=host_counted)
             nccl_head = shard.ShardedHead(n_out, shard.cuda_head_fn(w_local, wt, count, n_in), align=8)
             for step in range(5):          # several steps: both buffers, increasing epochs
                 x = torch.from_numpy(synth.activations(rows, n_in, seed + step)).cuda()
