@@ -484,20 +484,34 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
     logits = torch.randn((16, 8, n_exp), device="cuda", generator=rgen)
     route_fn, local_fn, combine_fn = shard.cuda_moe_fns(bank, k)
     moe = shard.ShardedMoE(n_exp, route_fn, local_fn, combine_fn)
+    peer_sum = shard.PeerSum(8 * n_embd) if world > 1 else None
+    moe_peer = shard.ShardedMoE(n_exp, route_fn, local_fn, combine_fn, exchange=peer_sum) if world > 1 else None
     per_expert = 2 * n_ff * synth.row_bytes(synth.Q4_K, n_embd) + n_embd * synth.row_bytes(synth.Q6_K, n_ff)
     for batch in (1, 8):
         def moe_call(i):
             return moe.forward(toks[i % 16, :batch], logits[i % 16, :batch])
         ms = reduce_max(timed(torch, moe_call, 32, barrier, variants=16))
+        ms_peer = None
+        if moe_peer is not None:
+            def moe_peer_call(i):
+                return moe_peer.forward(toks[i % 16, :batch], logits[i % 16, :batch])
+            ms_peer = reduce_max(timed(torch, moe_peer_call, 32, barrier, variants=16))
+            torch.cuda.synchronize()
+            if capi.device_status() != 0:
+                raise RuntimeError("a bounded wait of the fused exchange gave up")
         distinct = []
         for i in range(16):
             ids, _ = capi.route(logits[i, :batch], k)
             distinct.append(len(set(ids.cpu().reshape(-1).tolist())))
         mean_distinct = sum(distinct) / len(distinct)
         out[f"moe_qwen3_top8_batch{batch}"] = {
-            "ms_per_step": round(ms, 5), "distinct_experts_mean": round(mean_distinct, 2),
+            "ms_per_step": round(ms, 5), "exchange": "NCCL all-gather + rank-ordered sum" if world > 1 else "none",
+            "ms_per_step_peer_store_exchange": None if ms_peer is None else round(ms_peer, 5),
+            "distinct_experts_mean": round(mean_distinct, 2),
             "expert_weight_gbps_all_gpus": round(mean_distinct * per_expert / (ms * 1e-3) / 1e9, 1),
             "experts_per_gpu": n_local}
+    if peer_sum is not None:
+        peer_sum.close()
     return out
 
 

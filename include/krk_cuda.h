@@ -197,6 +197,19 @@ int krk_cuda_gemv_allgather(void *const host_y_peers[], void *const host_flag_pe
                             const void *x_f32, const void *w, int wt, int64_t n_out_local, int64_t n_in,
                             int64_t rows, void *stream);
 
+/* Expert-sharded FFN, exchange step: all-gather of partial sums over NVLink peer stores fused with the
+ * rank-ordered sum that follows (no counterpart in the reference, which is single-device). part_f32
+ * holds this GPU's partial sum (n floats, n % 4 == 0, 16-byte aligned like out_f32); the kernel stores it
+ * into slot my_rank of EVERY GPU's gather buffer, publishes the step to every GPU, waits (bounded, about
+ * 2 s, then krk_cuda_device_status() is raised) until every peer's slot has arrived here, and writes
+ * out = ((slot 0 + slot 1) + slot 2) + ... : the same bits on every GPU. host_gather_peers[q] is GPU q's
+ * gather buffer as mapped into this process (krk_cuda_peer_open; own buffer at q == my_rank), laid out
+ * [2][n_peers][slot_stride] floats (two steps deep; slot_stride >= n, % 4 == 0); host_flag_peers[q] is
+ * GPU q's flag array of n_peers + 1 ints, zero at start. Steps are counted on the device, so the launch
+ * replays from a CUDA graph. Every GPU must make the same sequence of calls. */
+int krk_cuda_allgather_sum(void *const host_gather_peers[], void *const host_flag_peers[], int n_peers, int my_rank,
+                           int64_t slot_stride, const void *part_f32, void *out_f32, int64_t n, void *stream);
+
 /* Buffers that peers store into. The reference is single-device (src/hip/backend_hip.hip:5036-5043), so
  * these have no counterpart there. krk_cuda_peer_alloc: zero-filled device memory on the current device
  * plus its 64-byte inter-process handle, which the host passes to the other processes of the box by any

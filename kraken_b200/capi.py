@@ -65,6 +65,7 @@ SIGNATURES = {
     "krk_cuda_gemv_allgather": (_int, [C.POINTER(_vp), C.POINTER(_vp), _int, _int, _int, _int, _i64, _i64, _vp, _vp, _int, _i64,
                                        _i64, _i64, _vp]),
     "krk_cuda_wait_flags": (_int, [_vp, _int, _int, _vp]),
+    "krk_cuda_allgather_sum": (_int, [C.POINTER(_vp), C.POINTER(_vp), _int, _int, _i64, _vp, _vp, _i64, _vp]),
     "krk_cuda_peer_alloc": (_int, [C.POINTER(_vp), C.c_size_t, C.c_char_p]),
     "krk_cuda_peer_open": (_int, [C.POINTER(_vp), C.c_char_p]),
     "krk_cuda_peer_close": (_int, [_vp]),
@@ -256,6 +257,14 @@ def gemv_allgather(y_peer_ptrs, flag_peer_ptrs, my_rank: int, epoch: int, slice_
 
 def wait_flags(flags, n_peers: int, epoch: int, stream=None):
     _check(lib.krk_cuda_wait_flags(_ptr(flags), n_peers, epoch, _stream_ptr(stream)), "wait_flags")
+
+
+def allgather_sum(gather_peer_ptrs, flag_peer_ptrs, my_rank: int, slot_stride: int, part, out, stream=None):
+    """Exchange step of an expert-sharded FFN: all-gather of `part` over peer stores + rank-ordered sum."""
+    n = len(gather_peer_ptrs)
+    _check(lib.krk_cuda_allgather_sum((_vp * n)(*gather_peer_ptrs), (_vp * n)(*flag_peer_ptrs), n, my_rank, slot_stride,
+                                      _ptr(part), _ptr(out), part.numel(), _stream_ptr(stream)), "allgather_sum")
+    return out
 
 
 class PeerBuffer:

@@ -162,6 +162,10 @@ struct PeerScatter {
 };
 int launch_gemv_stream_peers(const GemvMat &mat, int64_t n_in, int rows, const PeerScatter &ps, cudaStream_t st);
 int launch_flag_wait(const int *flags, int n, int epoch, cudaStream_t st);
+// All-gather of this GPU's partial sum into every GPU's gather buffer (peer stores), bounded wait for the
+// peers, rank-ordered sum into `out`; one kernel, steps counted on the device. n a multiple of 4.
+int launch_allgather_sum(float *const gather[], int *const flag[], int n_peers, int my_rank, int64_t slot_stride,
+                         const float *part, float *out, int64_t n, cudaStream_t st);
 
 // Rows per granule the streaming kernel splits matrices of this type and width by (1 or 8), or 0 when
 // it does not address the shape (then the shape-agnostic kernels serve it).

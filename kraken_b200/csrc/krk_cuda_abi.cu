@@ -287,6 +287,26 @@ int krk_cuda_gemv_allgather(void *const host_y_peers[], void *const host_flag_pe
     return took == 1 ? KRK_CUDA_OK : KRK_CUDA_ESHAPE;
 }
 
+int krk_cuda_allgather_sum(void *const host_gather_peers[], void *const host_flag_peers[], int n_peers, int my_rank,
+                           int64_t slot_stride, const void *part_f32, void *out_f32, int64_t n, void *stream) {
+    if (n_peers < 1 || n_peers > KRK_CUDA_MAX_PEERS || my_rank < 0 || my_rank >= n_peers) return KRK_CUDA_EARG;
+    if (!host_gather_peers || !host_flag_peers) return KRK_CUDA_ENULL;
+    if (n < 0 || n % 4 != 0 || slot_stride < n || slot_stride % 4 != 0) return KRK_CUDA_ESHAPE;
+    if (n > 0 && (!part_f32 || !out_f32)) return KRK_CUDA_ENULL;
+    if ((reinterpret_cast<uintptr_t>(part_f32) | reinterpret_cast<uintptr_t>(out_f32)) & 15) return KRK_CUDA_EALIGN;
+    float *gather[KRK_CUDA_MAX_PEERS];
+    int *flag[KRK_CUDA_MAX_PEERS];
+    for (int q = 0; q < n_peers; q++) {
+        if (!host_gather_peers[q] || !host_flag_peers[q]) return KRK_CUDA_ENULL;
+        if (reinterpret_cast<uintptr_t>(host_gather_peers[q]) & 15) return KRK_CUDA_EALIGN;
+        gather[q] = static_cast<float *>(host_gather_peers[q]);
+        flag[q] = static_cast<int *>(host_flag_peers[q]);
+    }
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_allgather_sum(gather, flag, n_peers, my_rank, slot_stride, static_cast<const float *>(part_f32),
+                                static_cast<float *>(out_f32), n, static_cast<cudaStream_t>(stream));
+}
+
 int krk_cuda_peer_alloc(void **dev_ptr, size_t bytes, unsigned char handle[KRK_CUDA_IPC_HANDLE_BYTES]) {
     static_assert(sizeof(cudaIpcMemHandle_t) == KRK_CUDA_IPC_HANDLE_BYTES, "handle size");
     if (!dev_ptr || !handle) return KRK_CUDA_ENULL;

@@ -87,6 +87,72 @@ class ShardedHead:
         return torch.cat([self._gather[r, :, :c] for r, (_, c) in enumerate(self.ranges)], dim=1)
 
 
+class _PeerBuffers:
+    """A set of device buffers per GPU that every process of the group has mapped: ``own[i]`` is this
+    GPU's i-th buffer (capi.PeerBuffer), ``ptrs[i][q]`` its address on GPU q as seen from this process.
+    The 64-byte handles travel through the process group."""
+
+    def __init__(self, capi, sizes, group=None):
+        import torch.distributed as dist
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.own = [capi.PeerBuffer.alloc(n) for n in sizes]
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, [buf.handle for buf in self.own], group=group)
+        self.mapped = []
+        self.ptrs = [[] for _ in sizes]
+        for q, handles in enumerate(everyone):
+            if q == self.rank:
+                bufs = self.own
+            else:
+                bufs = [capi.PeerBuffer.open(h, n) for h, n in zip(handles, sizes)]
+                self.mapped.append(bufs)
+            for i, buf in enumerate(bufs):
+                self.ptrs[i].append(buf.ptr)
+        dist.barrier(group=group)
+
+    def close(self):
+        """Unmap the peers' buffers, then (after a barrier: nobody still maps ours) free our own."""
+        import torch
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        for bufs in self.mapped:
+            for buf in bufs:
+                buf.release()
+        self.mapped = []
+        dist.barrier(group=self.group)
+        for buf in self.own:
+            buf.release()
+        self.own = []
+
+
+class PeerSum:
+    """combine step of ShardedMoE over NVLink peer stores (krk_cuda_allgather_sum): ``PeerSum(n_max)(part)``
+    returns ((p0 + p1) + p2) + ... over the ranks' partial sums, the same bits on every GPU, from one kernel
+    that stores this GPU's part into every GPU's gather buffer, waits (bounded) for the peers and adds."""
+
+    def __init__(self, n_max: int, group=None):
+        import torch.distributed as dist
+        from . import capi
+        self.capi = capi
+        world = dist.get_world_size(group)
+        self.slot = (n_max + 3) // 4 * 4
+        self.bufs = _PeerBuffers(capi, [2 * world * self.slot * 4, 4 * (world + 1)], group)
+        self.rank = self.bufs.rank
+        self._out = None
+
+    def __call__(self, part):
+        import torch
+        if part.numel() > self.slot or part.numel() % 4:
+            raise ValueError("partial sum larger than the gather slot, or not a multiple of 4 floats")
+        if self._out is None or self._out.shape != part.shape:
+            self._out = torch.empty_like(part)
+        return self.capi.allgather_sum(self.bufs.ptrs[0], self.bufs.ptrs[1], self.rank, self.slot, part.contiguous(), self._out)
+
+    def close(self):
+        self.bufs.close()
+
+
 class PeerHead:
     """Row-sharded head whose GEMV epilogue stores its slice straight into every GPU's copy of the logits
     row (krk_cuda_gemv_allgather): compute and all-gather are one kernel over NVLink peer memory, whose last
@@ -104,42 +170,19 @@ class PeerHead:
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.n_out, self.n_in, self.wt, self.w_local = n_out, n_in, wt, w_local
         self.begin, self.count = row_range(n_out, self.world, self.rank, align)
-        # two logits buffers and one flag word per peer, in memory the other processes can map
-        out_bytes, flag_bytes = rows * n_out * 4, 4 * (self.world + 1)   # + the device-side step count
-        self._own = [capi.PeerBuffer.alloc(out_bytes), capi.PeerBuffer.alloc(out_bytes), capi.PeerBuffer.alloc(flag_bytes)]
-        self.out = [self._own[b].tensor((rows, n_out), torch.float32) for b in range(2)]
-        self.flags = self._own[2].tensor((self.world + 1,), torch.int32)
-        everyone = [None] * self.world
-        dist.all_gather_object(everyone, [buf.handle for buf in self._own], group=group)
-        self._mapped = []          # the peers' buffers as mapped here
-        self.peer_out = [[], []]
-        self.peer_flags = []
-        for q, handles in enumerate(everyone):
-            if q == self.rank:
-                bufs = self._own
-            else:
-                bufs = [capi.PeerBuffer.open(h, n) for h, n in zip(handles, (out_bytes, out_bytes, flag_bytes))]
-                self._mapped.append(bufs)
-            self.peer_out[0].append(bufs[0].ptr)
-            self.peer_out[1].append(bufs[1].ptr)
-            self.peer_flags.append(bufs[2].ptr)
+        # two logits buffers and one flag word per peer (+ the device-side step count), in memory the
+        # other processes map
+        out_bytes, flag_bytes = rows * n_out * 4, 4 * (self.world + 1)
+        self._bufs = _PeerBuffers(capi, [out_bytes, out_bytes, flag_bytes], group)
+        self.out = [self._bufs.own[b].tensor((rows, n_out), torch.float32) for b in range(2)]
+        self.flags = self._bufs.own[2].tensor((self.world + 1,), torch.int32)
+        self.peer_out = [self._bufs.ptrs[0], self._bufs.ptrs[1]]
+        self.peer_flags = self._bufs.ptrs[2]
         self.epoch = 0
-        dist.barrier(group=group)
 
     def close(self):
-        """Unmap the peers' buffers, then (after a barrier: nobody still maps ours) free our own."""
-        import torch
-        import torch.distributed as dist
-        torch.cuda.synchronize()
-        for bufs in self._mapped:
-            for buf in bufs:
-                buf.release()
-        self._mapped = []
-        dist.barrier(group=self.group)
         self.out, self.flags = [], None
-        for buf in self._own:
-            buf.release()
-        self._own = []
+        self._bufs.close()
 
     def forward(self, x):
         """x: f32 [rows, n_in] on this GPU (the same on every rank). Returns the full [rows, n_out] row,
@@ -162,10 +205,12 @@ class ShardedMoE:
 
     ``route_fn(logits) -> (ids, wts)`` is the replicated router; ``local_fn(x, ids, wts) ->
     [n_tok, n_embd]`` is the partial sum over the picks this rank holds. ``combine_fn(parts) ->
-    [n_tok, n_embd]`` adds the gathered partials ``[world, n_tok, n_embd]`` in rank order.
+    [n_tok, n_embd]`` adds the gathered partials ``[world, n_tok, n_embd]`` in rank order. With
+    ``exchange`` (a PeerSum) the all-gather and the sum are one kernel over NVLink peer stores instead.
     """
 
-    def __init__(self, n_expert: int, route_fn: Callable, local_fn: Callable, combine_fn: Callable = None, group=None):
+    def __init__(self, n_expert: int, route_fn: Callable, local_fn: Callable, combine_fn: Callable = None, group=None,
+                 exchange: Callable = None):
         import torch.distributed as dist
         self.dist = dist
         self.group = group
@@ -175,6 +220,7 @@ class ShardedMoE:
         self.expert_base, self.n_local = expert_range(n_expert, self.world, self.rank)
         self.route_fn, self.local_fn = route_fn, local_fn
         self.combine_fn = combine_fn or sum_in_rank_order
+        self.exchange = exchange          # part -> combined, replacing all-gather + combine_fn (PeerSum)
         self._gather = None
 
     def forward(self, x, router_logits):
@@ -183,6 +229,8 @@ class ShardedMoE:
         part = self.local_fn(x, ids, wts)
         if self.world == 1:
             return part
+        if self.exchange is not None:
+            return self.exchange(part)
         if self._gather is None or self._gather.shape[1:] != part.shape or self._gather.device != part.device:
             self._flat = torch.empty((self.world * part.shape[0],) + tuple(part.shape[1:]), dtype=part.dtype, device=part.device)
             self._gather = self._flat.view((self.world,) + tuple(part.shape))

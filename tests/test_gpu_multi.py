@@ -47,6 +47,34 @@ def _worker(rank, world, port, ret):
                 assert torch.equal(nccl_head.forward(x), want)
             head.close()
             dist.barrier()
+        # ---- expert-sharded FFN: partial sums through peer stores == through NCCL, and close to the whole ----
+        n_embd, n_ff, n_exp, k = 1024, 512, 8, 4
+        mk = lambda wt, r, c, st: [synth.weights(wt, r, c, seed, stream=st + e) for e in range(n_exp)]
+        gate, up, down = mk(synth.Q4_K, n_ff, n_embd, 1000), mk(synth.Q4_K, n_ff, n_embd, 2000), mk(synth.Q6_K, n_embd, n_ff, 3000)
+        stack = lambda mats, lo, hi: torch.from_numpy(np.stack(mats[lo:hi])).cuda()
+        whole = capi.make_bank(stack(gate, 0, n_exp), stack(up, 0, n_exp), stack(down, 0, n_exp), synth.Q4_K, synth.Q6_K,
+                               n_exp, 0, n_embd, n_ff)
+        base, n_local = shard.expert_range(n_exp, world, rank)
+        bank = capi.make_bank(stack(gate, base, base + n_local), stack(up, base, base + n_local),
+                              stack(down, base, base + n_local), synth.Q4_K, synth.Q6_K, n_local, base, n_embd, n_ff)
+        route_fn, local_fn, combine_fn = shard.cuda_moe_fns(bank, k)
+        peer_sum = shard.PeerSum(8 * n_embd)
+        moe_peer = shard.ShardedMoE(n_exp, route_fn, local_fn, combine_fn, exchange=peer_sum)
+        moe_nccl = shard.ShardedMoE(n_exp, route_fn, local_fn, combine_fn)
+        for step, n_tok in enumerate((1, 8, 3, 8, 1)):
+            x = torch.from_numpy(synth.activations(n_tok, n_embd, seed + 50 + step)).cuda()
+            logits = torch.from_numpy(synth.activations(n_tok, n_exp, seed + 60 + step, stream=7)).cuda()
+            got = moe_peer.forward(x, logits).clone()
+            via_nccl = moe_nccl.forward(x, logits)
+            torch.cuda.synchronize()
+            assert capi.device_status() == 0
+            assert torch.equal(got, via_nccl), f"peer-store exchange differs from NCCL at step {step}"
+            ids, wts = capi.route(logits, k)
+            ref = capi.moe_ffn(x, ids, wts, whole)
+            rel = float((got - ref).norm() / ref.norm())
+            assert rel < 1e-5, rel
+        peer_sum.close()
+        dist.barrier()
         ret[rank] = "ok"
     finally:
         dist.destroy_process_group()
