@@ -158,6 +158,10 @@ struct Smem {
     unsigned long long red_empty[kMaxRedSlots]; // the epilogue warp has consumed them
     int gave_up;
     int pad[3];
+    // this launch's list of matrices and granule prefix, copied once per CTA: the walks below index them
+    // with run-time subscripts, which is slow against the kernel parameters and slower against global memory
+    GemvMat tmat[2 * kStreamTableEntries];
+    int tgran[kStreamTableEntries + 4];
     // per consumer lane and column group: its weighted share of (row g | g+8) x (activation row even | odd)
     float4 red[red_slots(NG)][kConsumerWarps][NG][32];
 };
@@ -195,22 +199,48 @@ struct TableView {
     int gran_q, gran_r;
 };
 
-__device__ __forceinline__ TableView table_view(const StreamParams &p) {
+// The list is copied into shared memory once per CTA (the caller synchronises the CTA). Kernel parameters
+// are read with compile-time subscripts (one entry per thread), which keeps them in the constant bank; a
+// run-time subscript would turn every access into a slow generic load.
+__device__ __forceinline__ TableView table_view(const StreamParams &p, GemvMat *tmat, int *tgran) {
+    static_assert(sizeof(GemvMat) % 8 == 0, "copied as 64-bit words");
     TableView tv;
     if (p.dev_table) {
-        tv.mat = p.dev_table->mat;
-        tv.gran_begin = p.dev_table->gran_begin;
+        const GemvMat *src_mat = p.dev_table->mat;
+        const int *src_gran = p.dev_table->gran_begin;
         tv.n_entries = p.dev_table->n_entries;
         const int total = p.dev_table->total_gran;
         tv.gran_q = total / (int)gridDim.x;
         tv.gran_r = total % (int)gridDim.x;
+        const int n_words = tv.n_entries * p.step * (int)(sizeof(GemvMat) / 8);
+        for (int i = threadIdx.x; i < n_words; i += blockDim.x)
+            reinterpret_cast<unsigned long long *>(tmat)[i] = reinterpret_cast<const unsigned long long *>(src_mat)[i];
+        for (int i = threadIdx.x; i <= tv.n_entries; i += blockDim.x) tgran[i] = src_gran[i];
     } else {
-        tv.mat = p.mat;
-        tv.gran_begin = p.gran_begin;
         tv.n_entries = p.n_entries;
         tv.gran_q = p.gran_q;
         tv.gran_r = p.gran_r;
+        const int n_mat = p.n_entries * p.step;
+        if (n_mat <= 4) {
+            // the usual launch: one matrix, a q/k/v triple or a gate/up pair
+            if (threadIdx.x < 4) {
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    if ((int)threadIdx.x == i && i < n_mat) tmat[i] = p.mat[i];
+            } else if (threadIdx.x >= 32 && threadIdx.x < 37) {
+#pragma unroll
+                for (int i = 0; i <= 4; i++)
+                    if ((int)threadIdx.x == 32 + i) tgran[i] = p.gran_begin[i];
+            }
+        } else {
+            const int n_words = n_mat * (int)(sizeof(GemvMat) / 8);
+            for (int i = threadIdx.x; i < n_words; i += blockDim.x)
+                reinterpret_cast<unsigned long long *>(tmat)[i] = reinterpret_cast<const unsigned long long *>(p.mat)[i];
+            for (int i = threadIdx.x; i <= p.n_entries; i += blockDim.x) tgran[i] = p.gran_begin[i];
+        }
     }
+    tv.mat = tmat;
+    tv.gran_begin = tgran;
     return tv;
 }
 
@@ -264,6 +294,12 @@ __device__ __forceinline__ void walk(const StreamParams &p, const TableView &tv,
 
 __device__ __forceinline__ int sext8(int v) { return (v << 24) >> 24; }
 
+// Balanced signed-byte limbs of a fixed-point value: adding 128 at every byte position turns the limbs
+// l in [-128, 127] into the bytes l + 128 of an unsigned number (carries do the balancing), and flipping
+// bit 7 of every byte turns l + 128 back into l as a two's complement byte.
+__device__ __forceinline__ uint32_t limbs3(int X) { return ((uint32_t)X + 0x00808080u) ^ 0x00808080u; }   // |X| < 2^23
+__device__ __forceinline__ uint32_t limbs4(int X) { return ((uint32_t)X + 0x80808080u) ^ 0x80808080u; }
+
 template <int WT>
 __device__ __forceinline__ void quantize_slice(const float (&f)[Fmt<WT>::unit_values / 32], float inv, int k0, int8_t *p0,
                                                int8_t *p1, int8_t *p2, int8_t *sums, int n_chunks, int lane) {
@@ -271,19 +307,16 @@ __device__ __forceinline__ void quantize_slice(const float (&f)[Fmt<WT>::unit_va
     int total = 0;
 #pragma unroll
     for (int j4 = 0; j4 < PER; j4 += 4) {
-        uint32_t w0 = 0, w1 = 0, w2 = 0;
+        uint32_t z[4];   // byte 0: limb 2 (weight 1), byte 1: limb 1 (256), byte 2: limb 0 (65536)
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int X = __float2int_rn(f[j4 + j] * inv);
             total += X;
-            const int l2 = sext8(X);
-            const int X1 = (X - l2) >> 8;
-            const int l1 = sext8(X1);
-            const int l0 = (X1 - l1) >> 8;
-            w0 |= (uint32_t)(l0 & 0xFF) << (8 * j);
-            w1 |= (uint32_t)(l1 & 0xFF) << (8 * j);
-            w2 |= (uint32_t)(l2 & 0xFF) << (8 * j);
+            z[j] = limbs3(X);
         }
+        const uint32_t lo01 = __byte_perm(z[0], z[1], 0x5140), lo23 = __byte_perm(z[2], z[3], 0x5140);   // l2a l2b l1a l1b
+        const uint32_t w2 = __byte_perm(lo01, lo23, 0x5410), w1 = __byte_perm(lo01, lo23, 0x7632);
+        const uint32_t w0 = __byte_perm(__byte_perm(z[0], z[1], 0x0062), __byte_perm(z[2], z[3], 0x0062), 0x5410);
         const int i = k0 + j4;
         if (WT == KRK_CUDA_Q8_0 && ((i >> 5) & 1) == 0) {
             // Even blocks start 2 bytes off a word boundary, so their lanes take the quants in the
@@ -310,16 +343,11 @@ __device__ __forceinline__ void quantize_slice(const float (&f)[Fmt<WT>::unit_va
         total += __shfl_xor_sync(0xFFFFFFFFu, total, 2);
         if ((lane & 3) == 0) {
             const int c = k0 >> 5;
-            const int l3 = sext8(total);
-            const int s1 = (total - l3) >> 8;
-            const int l2 = sext8(s1);
-            const int s2 = (s1 - l2) >> 8;
-            const int l1 = sext8(s2);
-            const int l0 = (s2 - l1) >> 8;
-            sums[c] = (int8_t)l0;
-            sums[n_chunks + c] = (int8_t)l1;
-            sums[2 * n_chunks + c] = (int8_t)l2;
-            sums[3 * n_chunks + c] = (int8_t)l3;
+            const uint32_t z = limbs4(total);   // byte 0: limb 3 (weight 1) ... byte 3: limb 0 (2^24)
+            sums[c] = (int8_t)(z >> 24);
+            sums[n_chunks + c] = (int8_t)(z >> 16);
+            sums[2 * n_chunks + c] = (int8_t)(z >> 8);
+            sums[3 * n_chunks + c] = (int8_t)z;
         }
     }
 }
@@ -630,7 +658,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // A device-side table is the output of the kernel before this one: every role waits for that grid.
     if (p.dev_table) asm volatile("griddepcontrol.wait;" ::: "memory");
-    const TableView tv = table_view(p);
+    const TableView tv = table_view(p, sm->tmat, sm->tgran);
     if (tid == 0) {
         for (int s = 0; s < p.n_stages; s++) {
             mbar_init(smem_u32(&sm->full[s]), 1);
