@@ -41,6 +41,7 @@ constexpr int kThreads = kConsumerThreads + 64;   // + the producer warp + the e
 // Tiles whose partial sums may wait for the epilogue warp (fewer when more activation rows make a slot larger).
 __host__ __device__ constexpr int red_slots(int ng) { return ng == 1 ? 4 : ng == 2 ? 2 : 1; }
 constexpr int kMaxRedSlots = 4;
+constexpr int kMaxStack = 4;      // 16-row tiles per stage at most
 constexpr int kTileRows = 16;                     // the M of the MMA
 constexpr int kMaxStages = 8;
 constexpr int kSmemLimit = 227 * 1024;
@@ -64,6 +65,9 @@ struct StreamParams {
     int row_bytes;
     int gran;             // rows per granule: 1, or 8 when rows are not 16-byte multiples
     int whole_tiles;      // 1: a stage is one contiguous copy of whole rows (unaligned row size)
+    int tps;              // 16-row tiles stacked in one stage (> 1 when a row has so few K units that one
+                          // tile would leave most consumer warps idle: warp w takes unit w % units of
+                          // sub-tile w / units)
     int row_stride;       // bytes between rows inside a stage
     int stage_bytes;
     int n_stages;
@@ -158,10 +162,7 @@ struct Smem {
     unsigned long long red_empty[kMaxRedSlots]; // the epilogue warp has consumed them
     int gave_up;
     int pad[3];
-    // this launch's list of matrices and granule prefix, copied once per CTA: the walks below index them
-    // with run-time subscripts, which is slow against the kernel parameters and slower against global memory
-    GemvMat tmat[2 * kStreamTableEntries];
-    int tgran[kStreamTableEntries + 4];
+    float gate[kMaxStack][NG][32];   // epilogue warp: the gate tile(s) of a gate/up pair, until the up tile arrives
     // per consumer lane and column group: its weighted share of (row g | g+8) x (activation row even | odd)
     float4 red[red_slots(NG)][kConsumerWarps][NG][32];
 };
@@ -181,7 +182,7 @@ struct StageInfo {
     int mat;        // matrix index
     int which;      // 0, or 1 for the `up` half of a gate/up pair
     int row0;       // first output row of the tile
-    int n_rows;     // valid rows in the tile (1..16)
+    int n_rows;     // valid rows in the stage (1..16 * tps)
     int unit0;      // first K unit of this stage
     int n_units;    // units in this stage (1..16)
     int last;       // last stage of the tile
@@ -199,53 +200,27 @@ struct TableView {
     int gran_q, gran_r;
 };
 
-// The list is copied into shared memory once per CTA (the caller synchronises the CTA). Kernel parameters
-// are read with compile-time subscripts (one entry per thread), which keeps them in the constant bank; a
-// run-time subscript would turn every access into a slow generic load.
-__device__ __forceinline__ TableView table_view(const StreamParams &p, GemvMat *tmat, int *tgran) {
-    static_assert(sizeof(GemvMat) % 8 == 0, "copied as 64-bit words");
+__device__ __forceinline__ TableView table_view(const StreamParams &p) {
     TableView tv;
     if (p.dev_table) {
-        const GemvMat *src_mat = p.dev_table->mat;
-        const int *src_gran = p.dev_table->gran_begin;
+        tv.mat = p.dev_table->mat;
+        tv.gran_begin = p.dev_table->gran_begin;
         tv.n_entries = p.dev_table->n_entries;
         const int total = p.dev_table->total_gran;
         tv.gran_q = total / (int)gridDim.x;
         tv.gran_r = total % (int)gridDim.x;
-        const int n_words = tv.n_entries * p.step * (int)(sizeof(GemvMat) / 8);
-        for (int i = threadIdx.x; i < n_words; i += blockDim.x)
-            reinterpret_cast<unsigned long long *>(tmat)[i] = reinterpret_cast<const unsigned long long *>(src_mat)[i];
-        for (int i = threadIdx.x; i <= tv.n_entries; i += blockDim.x) tgran[i] = src_gran[i];
     } else {
+        tv.mat = p.mat;
+        tv.gran_begin = p.gran_begin;
         tv.n_entries = p.n_entries;
         tv.gran_q = p.gran_q;
         tv.gran_r = p.gran_r;
-        const int n_mat = p.n_entries * p.step;
-        if (n_mat <= 4) {
-            // the usual launch: one matrix, a q/k/v triple or a gate/up pair
-            if (threadIdx.x < 4) {
-#pragma unroll
-                for (int i = 0; i < 4; i++)
-                    if ((int)threadIdx.x == i && i < n_mat) tmat[i] = p.mat[i];
-            } else if (threadIdx.x >= 32 && threadIdx.x < 37) {
-#pragma unroll
-                for (int i = 0; i <= 4; i++)
-                    if ((int)threadIdx.x == 32 + i) tgran[i] = p.gran_begin[i];
-            }
-        } else {
-            const int n_words = n_mat * (int)(sizeof(GemvMat) / 8);
-            for (int i = threadIdx.x; i < n_words; i += blockDim.x)
-                reinterpret_cast<unsigned long long *>(tmat)[i] = reinterpret_cast<const unsigned long long *>(p.mat)[i];
-            for (int i = threadIdx.x; i <= p.n_entries; i += blockDim.x) tgran[i] = p.gran_begin[i];
-        }
     }
-    tv.mat = tmat;
-    tv.gran_begin = tgran;
     return tv;
 }
 
 template <class SegmentFn, class StageFn>
-__device__ __forceinline__ void walk(const StreamParams &p, const TableView &tv, SegmentFn &&on_segment, StageFn &&on_stage) {
+__device__ __forceinline__ void walk(const StreamParams &p, const TableView &tv, int tps, SegmentFn &&on_segment, StageFn &&on_stage) {
     // balanced split of the granules over the CTAs: the first gran_r CTAs take one more
     const int c = (int)blockIdx.x;
     const int g0 = c * tv.gran_q + min(c, tv.gran_r);
@@ -259,14 +234,15 @@ __device__ __forceinline__ void walk(const StreamParams &p, const TableView &tv,
         const int r0 = (lo - tv.gran_begin[e]) * p.gran;
         const int r1 = min(n_out, (hi - tv.gran_begin[e]) * p.gran);
         on_segment(e * p.step);
-        for (int tr = r0; tr < r1; tr += kTileRows) {
+        const int stage_rows = kTileRows * tps;
+        for (int tr = r0; tr < r1; tr += stage_rows) {
             for (int which = 0; which < p.step; which++) {
                 for (int u0 = 0; u0 < p.units; u0 += ku_max) {
                     StageInfo s;
                     s.mat = e * p.step + which;
                     s.which = which;
                     s.row0 = tr;
-                    s.n_rows = min(kTileRows, r1 - tr);
+                    s.n_rows = min(stage_rows, r1 - tr);
                     s.unit0 = u0;
                     s.n_units = min(ku_max, p.units - u0);
                     s.last = u0 + ku_max >= p.units;
@@ -639,26 +615,32 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
 //   warp 17       epilogue: adds the 16 partial sums of each tile in warp order (deterministic),
 //                 applies the gate/up fold or the residual add, and writes y.
 
-template <int WT, int NG>
+template <int WT, int NG, bool STACK>
 __global__ void __launch_bounds__(kThreads, 1)
 gemv_stream_kernel(const __grid_constant__ StreamParams p) {
+    // STACK: several 16-row tiles per stage (p.tps of them); compiled apart so that the usual one-tile
+    // form carries none of its index arithmetic
+    const int tps = STACK ? p.tps : 1;
     using F = Fmt<WT>;
     using SmemT = Smem<NG>;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     SmemT *sm = reinterpret_cast<SmemT *>(smem_raw);
     int8_t *planes = reinterpret_cast<int8_t *>(smem_raw + align_up((int)sizeof(SmemT), 128));
-    int8_t *chunk_sum = planes + plane_bytes<WT>(p.n_in, p.rows);
-    uint8_t *stages = reinterpret_cast<uint8_t *>(chunk_sum) + chunk_sum_bytes<WT>(p.n_in, p.rows);
+    // one copy of the prepared activation per stacked sub-tile: the warps of a sub-tile move on to the next
+    // matrix (and its activation) on their own, so they must not share planes with another sub-tile
+    int8_t *chunk_sum = planes + tps * plane_bytes<WT>(p.n_in, p.rows);
+    uint8_t *stages = reinterpret_cast<uint8_t *>(chunk_sum) + tps * chunk_sum_bytes<WT>(p.n_in, p.rows);
 
     const int tid = threadIdx.x;
-    const int n_warps = min(kConsumerWarps, p.units);   // consumer warps that ever hold a unit
+    const int n_warps = min(kConsumerWarps, p.units * tps);   // consumer warps that ever hold a unit
+    const int sub_warps = STACK ? p.units : n_warps;         // warps that share one 16-row tile
     // Programmatic dependent launch: the next kernel in the stream may start its prologue (and, being
     // this same kernel, its weight prefetch) as soon as every CTA here has passed this point and an
     // SM has room; it still waits for this grid to complete before touching activations or outputs.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // A device-side table is the output of the kernel before this one: every role waits for that grid.
     if (p.dev_table) asm volatile("griddepcontrol.wait;" ::: "memory");
-    const TableView tv = table_view(p, sm->tmat, sm->tgran);
+    const TableView tv = table_view(p);
     if (tid == 0) {
         for (int s = 0; s < p.n_stages; s++) {
             mbar_init(smem_u32(&sm->full[s]), 1);
@@ -681,38 +663,46 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         // their four lanes t = 0..3 of row group g, of the share each lane left in `red`.
         const int lane = tid - kConsumerThreads - 32;
         constexpr int kSlots = red_slots(NG);
-        float gate[NG];   // gate tile kept for the silu fold
+        float gate_reg[NG];   // gate tile kept for the silu fold (stacked tiles keep theirs in shared memory)
         int tile_it = 0;
-        walk(p, tv, [](int) {}, [&](const StageInfo &s) {
+        walk(p, tv, tps, [](int) {}, [&](const StageInfo &s) {
             if (!s.last) return;
             const int slot = tile_it % kSlots;
             wait_phase(smem_u32(&sm->red_full[slot]), (tile_it / kSlots) & 1, gave_up, p.status);
             tile_it++;
 #pragma unroll
-            for (int i = 0; i < NG; i++) {
-                const int idx = lane + 32 * i, row = idx & (kTileRows - 1), r = idx >> 4;   // r = 2*i + (lane >> 4)
-                const float *src = reinterpret_cast<const float *>(&sm->red[slot][0][i][4 * (row & 7)]) + 2 * (row >> 3) + (r & 1);
-                float v = 0.0f;
-                for (int w = 0; w < n_warps; w++) {
-                    const float *q = src + (size_t)w * (NG * 32 * 4);
-                    v += q[0];
-                    v += q[4];
-                    v += q[8];
-                    v += q[12];
-                }
-                if (r < p.rows) {
-                    if (p.step == 2 && s.which == 0) {
-                        gate[i] = v;
-                    } else if (row < s.n_rows) {
-                        if (p.n_peers > 0) {
-                            // plain stores into every GPU's copy of the full row (NVLink peer stores)
-                            const long long at = (long long)r * p.peer_row_stride + p.peer_offset + s.row0 + row;
-                            for (int q = 0; q < p.n_peers; q++) p.peer_y[q][at] = v;
-                        } else {
-                            const GemvMat &mat = tv.mat[p.step == 2 ? s.mat - 1 : s.mat];
-                            float *y = mat.y + (size_t)r * mat.n_out + s.row0 + row;
-                            if (p.step == 2) v = __fmul_rn(__fdiv_rn(gate[i], __fadd_rn(1.0f, expf(-gate[i]))), v);
-                            *y = p.accumulate ? __fadd_rn(*y, v) : v;
+            for (int sub = 0; sub < (STACK ? kMaxStack : 1); sub++) {
+                if (sub >= tps) break;
+#pragma unroll
+                for (int i = 0; i < NG; i++) {
+                    const int idx = lane + 32 * i, row = idx & (kTileRows - 1), r = idx >> 4;   // r = 2*i + (lane >> 4)
+                    const float *src = reinterpret_cast<const float *>(&sm->red[slot][sub * sub_warps][i][4 * (row & 7)]) +
+                                       2 * (row >> 3) + (r & 1);
+                    float v = 0.0f;
+                    for (int w = 0; w < sub_warps; w++) {
+                        const float *q = src + (size_t)w * (NG * 32 * 4);
+                        v += q[0];
+                        v += q[4];
+                        v += q[8];
+                        v += q[12];
+                    }
+                    const int srow = kTileRows * sub + row;   // row inside the stage
+                    if (r < p.rows) {
+                        if (p.step == 2 && s.which == 0) {
+                            if (STACK) sm->gate[sub][i][lane] = v;   // kept for the silu fold with the `up` tile
+                            else gate_reg[i] = v;
+                        } else if (srow < s.n_rows) {
+                            if (p.n_peers > 0) {
+                                // plain stores into every GPU's copy of the full row (NVLink peer stores)
+                                const long long at = (long long)r * p.peer_row_stride + p.peer_offset + s.row0 + srow;
+                                for (int q = 0; q < p.n_peers; q++) p.peer_y[q][at] = v;
+                            } else {
+                                const GemvMat &mat = tv.mat[p.step == 2 ? s.mat - 1 : s.mat];
+                                float *y = mat.y + (size_t)r * mat.n_out + s.row0 + srow;
+                                const float gt = STACK ? sm->gate[sub][i][lane] : gate_reg[i];
+                                if (p.step == 2) v = __fmul_rn(__fdiv_rn(gt, __fadd_rn(1.0f, expf(-gt))), v);
+                                *y = p.accumulate ? __fadd_rn(*y, v) : v;
+                            }
                         }
                     }
                 }
@@ -762,7 +752,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     if (tid >= kConsumerThreads) {
         // ===== producer warp: weights only, so it can run ahead of everything else =====
         const int lane = tid - kConsumerThreads;
-        walk(p, tv, [](int) {}, [&](const StageInfo &s) {
+        walk(p, tv, tps, [](int) {}, [&](const StageInfo &s) {
             const int slot = s.slot;
             const uint32_t full = smem_u32(&sm->full[slot]), empty = smem_u32(&sm->empty[slot]);
             wait_phase(empty, s.phase ^ 1, gave_up, p.status);
@@ -772,9 +762,9 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                 const uint32_t bytes = (uint32_t)s.n_units * F::unit_bytes;
                 if (lane == 0) mbar_arrive_expect_tx(full, bytes * s.n_rows);
                 __syncwarp();
-                if (lane < s.n_rows)
-                    bulk_g2s(smem_u32(dst + lane * p.row_stride),
-                             src + (size_t)lane * p.row_bytes + (size_t)s.unit0 * F::unit_bytes, bytes, full);
+                for (int r = lane; r < (STACK ? s.n_rows : min(s.n_rows, 32)); r += 32)
+                    bulk_g2s(smem_u32(dst + r * p.row_stride),
+                             src + (size_t)r * p.row_bytes + (size_t)s.unit0 * F::unit_bytes, bytes, full);
             } else if (lane == 0) {
                 // rows are not 16-byte multiples: one copy of the whole tile, rounded down to 16 bytes,
                 // and the (< 16 byte, 4-byte granular) tail with plain loads before the arrive
@@ -798,7 +788,16 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     Accum<NG> acc;
     accum_zero(acc);
     int tile_it = 0;
-    const uint32_t lane_off = (uint32_t)wid * F::unit_bytes + (uint32_t)g * p.row_stride;
+    // With stacked tiles warp w holds unit w % units of sub-tile w / units of every stage; otherwise unit
+    // w of every 16-unit chunk of the one tile in the stage.
+    const int my_sub = STACK ? wid / p.units : 0;
+    const int my_unit = STACK ? wid - my_sub * p.units : wid;
+    const bool stacked_idle = STACK && my_sub >= tps;
+    const uint32_t lane_off = (uint32_t)my_unit * F::unit_bytes + (uint32_t)(kTileRows * my_sub + g) * p.row_stride;
+    if (!stacked_idle) {
+        planes += my_sub * plane_bytes<WT>(p.n_in, p.rows);
+        chunk_sum += my_sub * chunk_sum_bytes<WT>(p.n_in, p.rows);
+    }
 
     // The same walk as walk() above, written flat: per stage a consumer warp only needs the ring
     // slot and its K unit, not which matrix or rows the tile belongs to.
@@ -822,18 +821,21 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
             prepared = tv.mat[m].x;
 #pragma unroll
             for (int r = 0; r < 2 * NG; r++)
+                // (stacked tiles: every sub-tile prepares its own copy)
                 xs[r] = r < p.rows ? prepare_x_row<WT>(prepared + (size_t)r * p.n_in, p, planes + (size_t)(r * 3) * p.n_in,
-                                                       chunk_sum + (size_t)(r * 4) * (p.n_in >> 5), wid, lane)
+                                                       chunk_sum + (size_t)(r * 4) * (p.n_in >> 5),
+                                                       stacked_idle ? kConsumerWarps : my_unit, lane)
                                    : 0.0f;
             __syncwarp();
             lane_planes<NG>(planes, chunk_sum, p.n_in, p.rows, g, bp, sp);
         }
-        const int n_tiles = ((r1 - r0 + kTileRows - 1) / kTileRows) * p.step;
+        const int stage_rows = kTileRows * tps;
+        const int n_tiles = ((r1 - r0 + stage_rows - 1) / stage_rows) * p.step;
         for (int tile = 0; tile < n_tiles; tile++) {
             for (int ck = 0; ck < n_chunks; ck++) {
                 wait_phase(full0 + 8 * slot, phase, gave_up, p.status);
-                const int unit = ck * kConsumerWarps + wid;
-                if (unit < p.units) {
+                const int unit = ck * kConsumerWarps + my_unit;
+                if (unit < p.units && !stacked_idle) {
                     const uint8_t *rowA = stages + (size_t)slot * p.stage_bytes + lane_off, *rowB = rowA + (size_t)8 * p.row_stride;
                     const int kbase = unit * F::unit_values;
                     if (WT == KRK_CUDA_Q4_K) {
@@ -895,10 +897,10 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     }
 }
 
-template <int WT, int NG>
+template <int WT, int NG, bool STACK>
 int launch_one(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
     static bool configured[64] = {};   // per instantiation and device: the opt-in is sticky
-    auto kernel = gemv_stream_kernel<WT, NG>;
+    auto kernel = gemv_stream_kernel<WT, NG, STACK>;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -956,16 +958,18 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
         p.gran = 8;
     }
     const int ku_max = p.whole_tiles ? p.units : (p.units < kConsumerWarps ? p.units : kConsumerWarps);
+    p.tps = kConsumerWarps / p.units;   // 0 when a tile has more units than there are consumer warps
+    p.tps = p.tps < 1 ? 1 : (p.tps > kMaxStack ? kMaxStack : p.tps);
     if (p.whole_tiles) {
         p.row_stride = p.row_bytes;
-        p.stage_bytes = align_up(kTileRows * p.row_bytes, 128);
+        p.stage_bytes = align_up(kTileRows * p.tps * p.row_bytes, 128);
     } else {
         const int raw = ku_max * F::unit_bytes;
         p.row_stride = raw + ((F::stride_mod - raw % 128) + 128) % 128;
-        p.stage_bytes = align_up(kTileRows * p.row_stride, 128);
+        p.stage_bytes = align_up(kTileRows * p.tps * p.row_stride, 128);
     }
     const int smem_struct = rows <= 2 ? (int)sizeof(Smem<1>) : rows <= 4 ? (int)sizeof(Smem<2>) : (int)sizeof(Smem<4>);
-    const int fixed = align_up(smem_struct, 128) + plane_bytes<WT>(p.n_in, rows) + chunk_sum_bytes<WT>(p.n_in, rows);
+    const int fixed = align_up(smem_struct, 128) + p.tps * (plane_bytes<WT>(p.n_in, rows) + chunk_sum_bytes<WT>(p.n_in, rows));
     // Depth of the ring: KRK_CUDA_GEMV_STAGE_KB of staged weights per SM (default 96), at least 3 stages.
     static const int stage_kb = [] {
         const char *e = std::getenv("KRK_CUDA_GEMV_STAGE_KB");
@@ -983,9 +987,14 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
 
 template <int WT>
 int launch_rows(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
-    if (p.rows <= 2) return launch_one<WT, 1>(p, grid, smem, st);
-    if (p.rows <= 4) return launch_one<WT, 2>(p, grid, smem, st);
-    return launch_one<WT, 4>(p, grid, smem, st);
+    if (p.tps > 1) {
+        if (p.rows <= 2) return launch_one<WT, 1, true>(p, grid, smem, st);
+        if (p.rows <= 4) return launch_one<WT, 2, true>(p, grid, smem, st);
+        return launch_one<WT, 4, true>(p, grid, smem, st);
+    }
+    if (p.rows <= 2) return launch_one<WT, 1, false>(p, grid, smem, st);
+    if (p.rows <= 4) return launch_one<WT, 2, false>(p, grid, smem, st);
+    return launch_one<WT, 4, false>(p, grid, smem, st);
 }
 
 template <int WT>
