@@ -483,9 +483,10 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
     toks = torch.randn((16, 8, n_embd), device="cuda", generator=rgen)
     logits = torch.randn((16, 8, n_exp), device="cuda", generator=rgen)
     route_fn, local_fn, combine_fn = shard.cuda_moe_fns(bank, k)
-    moe = shard.ShardedMoE(n_exp, route_fn, local_fn, combine_fn)
+    routed_fn = shard.cuda_moe_routed_fn(bank, k)          # routing folded into the FFN's first kernel
+    moe = shard.ShardedMoE(n_exp, route_fn, local_fn, combine_fn, routed_fn=routed_fn)
     peer_sum = shard.PeerSum(8 * n_embd) if world > 1 else None
-    moe_peer = shard.ShardedMoE(n_exp, route_fn, local_fn, combine_fn, exchange=peer_sum) if world > 1 else None
+    moe_peer = shard.ShardedMoE(n_exp, route_fn, local_fn, combine_fn, exchange=peer_sum, routed_fn=routed_fn) if world > 1 else None
     per_expert = 2 * n_ff * synth.row_bytes(synth.Q4_K, n_embd) + n_embd * synth.row_bytes(synth.Q6_K, n_ff)
     for batch in (1, 8):
         def moe_call(i):

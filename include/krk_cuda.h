@@ -161,6 +161,14 @@ int krk_cuda_moe_ffn(void *y_f32, const void *x_f32, const void *ids_i32, const 
                      const struct krk_cuda_expert_bank *bank, int k, int64_t n_tok,
                      void *workspace, size_t ws_bytes, void *stream);
 
+/* The same with the routing folded in (krk_cuda_route + krk_cuda_moe_ffn in one call, one kernel fewer on
+ * the streaming path): router_logits_f32 is [n_tok][n_expert] over ALL experts of the layer; ids_i32 and
+ * wts_f32 ([n_tok][k], device memory) are OUTPUTS and hold what krk_cuda_route would have written.
+ * Replaces the same reference code as the two calls it combines. */
+int krk_cuda_moe_ffn_routed(void *y_f32, const void *x_f32, const void *router_logits_f32, int n_expert,
+                            void *ids_i32, void *wts_f32, const struct krk_cuda_expert_bank *bank, int k,
+                            int64_t n_tok, void *workspace, size_t ws_bytes, void *stream);
+
 /* out = silu(gate) * up elementwise (Backend::silu_mul, include/krk/backend.hpp:1309;
  * src/backend_cpu.cpp:2394-2400). */
 int krk_cuda_silu_mul(void *out_f32, const void *gate_f32, const void *up_f32, int64_t n,

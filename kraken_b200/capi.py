@@ -59,6 +59,7 @@ SIGNATURES = {
     "krk_cuda_route": (_int, [_vp, _vp, _vp, _i64, _int, _int, _vp]),
     "krk_cuda_moe_workspace_bytes": (_sz, [C.POINTER(ExpertBank), _int, _i64]),
     "krk_cuda_moe_ffn": (_int, [_vp, _vp, _vp, _vp, C.POINTER(ExpertBank), _int, _i64, _vp, _sz, _vp]),
+    "krk_cuda_moe_ffn_routed": (_int, [_vp, _vp, _vp, _int, _vp, _vp, C.POINTER(ExpertBank), _int, _i64, _vp, _sz, _vp]),
     "krk_cuda_silu_mul": (_int, [_vp, _vp, _vp, _i64, _vp]),
     "krk_cuda_scatter_axpy_rows": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     "krk_cuda_sum_parts": (_int, [_vp, _vp, _int, _i64, _vp]),
@@ -218,6 +219,22 @@ def moe_ffn(x, ids, wts, bank: ExpertBank, out=None, workspace=None, stream=None
     _check(lib.krk_cuda_moe_ffn(_ptr(out), _ptr(x), _ptr(ids), _ptr(wts), C.byref(bank), k, n_tok, _ptr(workspace),
                                 workspace.numel(), _stream_ptr(stream)), "moe_ffn")
     return out
+
+
+def moe_ffn_routed(x, logits, k: int, bank: ExpertBank, out=None, workspace=None, stream=None):
+    """Routing + routed-expert FFN in one call. Returns (y, ids, wts); ids / wts are what route() gives."""
+    import torch
+    n_tok, n_expert = logits.shape
+    ids = torch.empty((n_tok, k), dtype=torch.int32, device=x.device)
+    wts = torch.empty((n_tok, k), dtype=torch.float32, device=x.device)
+    need = lib.krk_cuda_moe_workspace_bytes(C.byref(bank), k, n_tok)
+    if workspace is None:
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
+    if out is None:
+        out = torch.empty((n_tok, bank.n_embd), dtype=torch.float32, device=x.device)
+    _check(lib.krk_cuda_moe_ffn_routed(_ptr(out), _ptr(x), _ptr(logits), n_expert, _ptr(ids), _ptr(wts), C.byref(bank), k,
+                                       n_tok, _ptr(workspace), workspace.numel(), _stream_ptr(stream)), "moe_ffn_routed")
+    return out, ids, wts
 
 
 def silu_mul(gate, up, out=None, stream=None):

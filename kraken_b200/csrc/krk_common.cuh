@@ -181,9 +181,10 @@ int launch_sum_parts(float *out, const float *parts, int n_parts, int64_t n, cud
 int launch_route(int32_t *ids, float *wts, const float *logits, int64_t n_tok, int n_expert, int k,
                  cudaStream_t st);
 size_t moe_workspace_bytes(const krk_cuda_expert_bank *bank, int k, int64_t n_tok);
+// With `logits` (and n_expert) the routing runs first and ids / wts are outputs.
 int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const float *wts,
                            const krk_cuda_expert_bank *bank, int k, int64_t n_tok, void *workspace,
-                           cudaStream_t st);
+                           cudaStream_t st, const float *logits = nullptr, int n_expert = 0);
 
 // Prefill GEMM on tcgen05 (krk_gemm_tc.cu).
 size_t gemm_workspace_bytes(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows);

@@ -225,6 +225,25 @@ int krk_cuda_moe_ffn(void *y_f32, const void *x_f32, const void *ids_i32, const 
                                   static_cast<cudaStream_t>(stream));
 }
 
+int krk_cuda_moe_ffn_routed(void *y_f32, const void *x_f32, const void *router_logits_f32, int n_expert,
+                            void *ids_i32, void *wts_f32, const struct krk_cuda_expert_bank *bank, int k,
+                            int64_t n_tok, void *workspace, size_t ws_bytes, void *stream) {
+    const int rc = check_bank(bank);
+    if (rc != KRK_CUDA_OK) return rc;
+    if (k <= 0 || k > 32 || n_expert <= 0 || n_expert > 1024 || k > n_expert) return KRK_CUDA_EARG;
+    if (n_tok < 0 || n_tok > KRK_CUDA_MAX_ROWS) return KRK_CUDA_ESHAPE;
+    if (n_tok == 0) return KRK_CUDA_OK;
+    if (!y_f32 || !x_f32 || !router_logits_f32 || !ids_i32 || !wts_f32) return KRK_CUDA_ENULL;
+    if (!aligned(x_f32, 16) || !aligned(y_f32, 4)) return KRK_CUDA_EALIGN;
+    if (!workspace || ws_bytes < moe_workspace_bytes(bank, k, n_tok) || !aligned(workspace, 16))
+        return KRK_CUDA_EWORKSPACE;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_moe_ffn_generic(static_cast<float *>(y_f32), static_cast<const float *>(x_f32),
+                                  static_cast<const int32_t *>(ids_i32), static_cast<const float *>(wts_f32), bank, k,
+                                  n_tok, workspace, static_cast<cudaStream_t>(stream),
+                                  static_cast<const float *>(router_logits_f32), n_expert);
+}
+
 int krk_cuda_silu_mul(void *out_f32, const void *gate_f32, const void *up_f32, int64_t n, void *stream) {
     if (n < 0) return KRK_CUDA_ESHAPE;
     if (n > 0 && (!out_f32 || !gate_f32 || !up_f32)) return KRK_CUDA_ENULL;

@@ -18,15 +18,8 @@ constexpr int kMaxK = 32;
 // then k picks of the largest probability, strict '>' so equal probabilities keep the lower
 // id (:11857-11886); then the picked weights are divided by their slot-order sum
 // (:11913-11918).
-__global__ void __launch_bounds__(32)
-route_kernel(int32_t *__restrict__ ids, float *__restrict__ wts, const float *__restrict__ logits,
-             int n_expert, int k) {
-    __shared__ float prob[kMaxExperts];
-    __shared__ float wsel[kMaxK];
-    const int lane = threadIdx.x;
-    const int64_t t = blockIdx.x;
-    const float *lg = logits + t * n_expert;
-
+__device__ __forceinline__ void route_token(int32_t *__restrict__ ids, float *__restrict__ wts, const float *__restrict__ lg,
+                                            int n_expert, int k, float *prob, float *wsel, int lane) {
     float mx = -INFINITY;
     for (int e = lane; e < n_expert; e += 32) mx = fmaxf(mx, lg[e]);
 #pragma unroll
@@ -62,7 +55,7 @@ route_kernel(int32_t *__restrict__ ids, float *__restrict__ wts, const float *__
         }
         if (lane == 0) {
             const bool ok = be < n_expert && bp >= 0.0f;
-            ids[t * k + s] = ok ? be : -1;
+            ids[s] = ok ? be : -1;
             wsel[s] = ok ? bp : 0.0f;
             if (ok) prob[be] = -2.0f;
         }
@@ -72,8 +65,17 @@ route_kernel(int32_t *__restrict__ ids, float *__restrict__ wts, const float *__
         float ksum = 0.0f;
         for (int s = 0; s < k; s++) ksum = __fadd_rn(ksum, wsel[s]);
         const float kinv = ksum > 0.0f ? __fdiv_rn(1.0f, ksum) : 0.0f;
-        for (int s = 0; s < k; s++) wts[t * k + s] = __fmul_rn(wsel[s], kinv);
+        for (int s = 0; s < k; s++) wts[s] = __fmul_rn(wsel[s], kinv);
     }
+}
+
+__global__ void __launch_bounds__(32)
+route_kernel(int32_t *__restrict__ ids, float *__restrict__ wts, const float *__restrict__ logits,
+             int n_expert, int k) {
+    __shared__ float prob[kMaxExperts];
+    __shared__ float wsel[kMaxK];
+    const int64_t t = blockIdx.x;
+    route_token(ids + t * k, wts + t * k, logits + t * n_expert, n_expert, k, prob, wsel, threadIdx.x);
 }
 
 struct MoeParams {
@@ -141,27 +143,38 @@ moe_down_kernel(const __grid_constant__ MoeParams p) {
 // scatter_axpy_rows chain (src/engine.cpp:12353-, src/backend_cpu.cpp:3193-3220).
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __grid_constant__ MoeParams p) {
+    __shared__ int s_pick[kMaxK];
+    __shared__ float s_w[kMaxK];
+    __shared__ int s_n;
     const int t = blockIdx.y;
-    int order[kMaxK];
-    int n = 0;
-    for (int s = 0; s < p.k; s++)
-        if (local_expert(p, t * p.k + s) >= 0) order[n++] = s;
-    for (int i = 1; i < n; i++) {   // insertion sort by expert id; k is small
-        const int s = order[i];
-        int j = i - 1;
-        while (j >= 0 && p.ids[t * p.k + order[j]] > p.ids[t * p.k + s]) {
-            order[j + 1] = order[j];
-            j--;
+    if (threadIdx.x < 32) {
+        // lane s looks at slot s of this token: its place among the slots held here, by expert id
+        const int s = threadIdx.x;
+        int id = 0x7FFFFFFF, e = -1;
+        if (s < p.k) {
+            id = p.ids[t * p.k + s];
+            e = local_expert(p, t * p.k + s);
         }
-        order[j + 1] = s;
+        int rank = 0, n = 0;
+        for (int j = 0; j < p.k; j++) {
+            const int idj = __shfl_sync(0xFFFFFFFFu, id, j), ej = __shfl_sync(0xFFFFFFFFu, e, j);
+            if (ej >= 0) {
+                n++;
+                rank += (idj < id || (idj == id && j < s)) ? 1 : 0;
+            }
+        }
+        if (e >= 0) {
+            s_pick[rank] = t * p.k + s;
+            s_w[rank] = p.wts[t * p.k + s];
+        }
+        if (s == 0) s_n = n;
     }
+    __syncthreads();
+    const int n = s_n;
     for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < p.n_embd;
          j += (int64_t)gridDim.x * blockDim.x) {
         float acc = 0.0f;
-        for (int i = 0; i < n; i++) {
-            const int pick = t * p.k + order[i];
-            acc = __fadd_rn(acc, __fmul_rn(p.wts[pick], p.d[(int64_t)pick * p.n_embd + j]));
-        }
+        for (int i = 0; i < n; i++) acc = __fadd_rn(acc, __fmul_rn(s_w[i], p.d[(int64_t)s_pick[i] * p.n_embd + j]));
         p.y[(int64_t)t * p.n_embd + j] = acc;
     }
 }
@@ -170,14 +183,26 @@ moe_combine_kernel(const __grid_constant__ MoeParams p) {
 // gate/up pair and one down matrix per pick this bank holds, ordered by expert id so that an expert
 // picked by several tokens is streamed by neighbouring CTAs at about the same time (its second read
 // comes from L2). One block; picks <= kStreamTableEntries.
-__global__ void __launch_bounds__(kStreamTableEntries)
+// With `logits` the routing itself runs first, one warp per token (n_tok <= 8), writing p.ids / p.wts.
+constexpr int kPlanThreads = 256;
+constexpr int kPlanRouteExperts = 1024;   // experts the fused routing holds in shared memory, per token
+__global__ void __launch_bounds__(kPlanThreads)
 moe_plan_kernel(const __grid_constant__ MoeParams p, StreamTable *gate_up, StreamTable *down, int wt_gate_up, int wt_down,
-                size_t rb_gate_up, size_t rb_down, int gran_gate_up, int gran_down) {
+                size_t rb_gate_up, size_t rb_down, int gran_gate_up, int gran_down, const float *logits, int n_expert) {
     __shared__ int key[kStreamTableEntries];
+    __shared__ float prob[KRK_CUDA_MAX_ROWS][kPlanRouteExperts];
+    __shared__ float wsel[KRK_CUDA_MAX_ROWS][kMaxK];
+    if (logits) {
+        const int t = threadIdx.x >> 5;
+        if (t < p.n_tok)
+            route_token(const_cast<int32_t *>(p.ids) + t * p.k, const_cast<float *>(p.wts) + t * p.k,
+                        logits + (int64_t)t * n_expert, n_expert, p.k, prob[t], wsel[t], threadIdx.x & 31);
+        __syncthreads();   // the ids written above are read below by other threads of this block
+    }
     const int n_pick = p.n_tok * p.k, pick = threadIdx.x;
     int e = -1;
     if (pick < n_pick) e = local_expert(p, pick);
-    key[pick] = e >= 0 ? e * kStreamTableEntries + pick : 0x7FFFFFFF;
+    if (pick < kStreamTableEntries) key[pick] = e >= 0 ? e * kStreamTableEntries + pick : 0x7FFFFFFF;
     __syncthreads();
     if (e >= 0) {
         int rank = 0;
@@ -238,7 +263,10 @@ size_t moe_workspace_bytes(const krk_cuda_expert_bank *bank, int k, int64_t n_to
 
 int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const float *wts,
                            const krk_cuda_expert_bank *bank, int k, int64_t n_tok, void *workspace,
-                           cudaStream_t st) {
+                           cudaStream_t st, const float *logits, int n_expert) {
+    // `logits` set: route first (ids / wts are outputs). The streaming path folds the routing into its plan
+    // kernel; every other path runs the routing kernel on its own.
+    bool routed = logits == nullptr;
     MoeParams p;
     p.gate = static_cast<const uint8_t *>(bank->gate);
     p.up = static_cast<const uint8_t *>(bank->up);
@@ -259,12 +287,19 @@ int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const f
     // Streaming path: the same kernel as the dense decode GEMV, fed from device-side tables.
     const int gran_gu = stream_gran(bank->wt_gate_up, bank->n_embd), gran_dn = stream_gran(bank->wt_down, bank->n_ff);
     if (gran_gu > 0 && gran_dn > 0 && picks <= kStreamTableEntries) {
+        const bool fuse_route = !routed && n_expert <= kPlanRouteExperts && n_tok * 32 <= kPlanThreads;
+        if (!routed && !fuse_route) {
+            const int rc = launch_route(const_cast<int32_t *>(ids), const_cast<float *>(wts), logits, n_tok, n_expert, k, st);
+            if (rc != KRK_CUDA_OK) return rc;
+        }
+        routed = true;
         uint8_t *tables = static_cast<uint8_t *>(workspace) + moe_float_bytes(bank, k, n_tok);
         StreamTable *ta = reinterpret_cast<StreamTable *>(tables);
         StreamTable *tb = reinterpret_cast<StreamTable *>(tables + ((sizeof(StreamTable) + 255) & ~(size_t)255));
-        moe_plan_kernel<<<1, kStreamTableEntries, 0, st>>>(p, ta, tb, bank->wt_gate_up, bank->wt_down,
-                                                            row_bytes(bank->wt_gate_up, bank->n_embd),
-                                                            row_bytes(bank->wt_down, bank->n_ff), gran_gu, gran_dn);
+        moe_plan_kernel<<<1, kPlanThreads, 0, st>>>(p, ta, tb, bank->wt_gate_up, bank->wt_down,
+                                                     row_bytes(bank->wt_gate_up, bank->n_embd),
+                                                     row_bytes(bank->wt_down, bank->n_ff), gran_gu, gran_dn,
+                                                     fuse_route ? logits : nullptr, n_expert);
         note_launch();
         int rc = check_launch();
         if (rc != KRK_CUDA_OK) return rc;
@@ -276,6 +311,10 @@ int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const f
         moe_combine_kernel<<<grid, 256, 0, st>>>(p);
         note_launch();
         return check_launch();
+    }
+    if (!routed) {
+        const int rc = launch_route(const_cast<int32_t *>(ids), const_cast<float *>(wts), logits, n_tok, n_expert, k, st);
+        if (rc != KRK_CUDA_OK) return rc;
     }
     {
         dim3 grid((unsigned)((bank->n_ff + 7) / 8), (unsigned)picks);

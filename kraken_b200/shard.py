@@ -210,7 +210,7 @@ class ShardedMoE:
     """
 
     def __init__(self, n_expert: int, route_fn: Callable, local_fn: Callable, combine_fn: Callable = None, group=None,
-                 exchange: Callable = None):
+                 exchange: Callable = None, routed_fn: Callable = None):
         import torch.distributed as dist
         self.dist = dist
         self.group = group
@@ -221,12 +221,16 @@ class ShardedMoE:
         self.route_fn, self.local_fn = route_fn, local_fn
         self.combine_fn = combine_fn or sum_in_rank_order
         self.exchange = exchange          # part -> combined, replacing all-gather + combine_fn (PeerSum)
+        self.routed_fn = routed_fn        # (x, logits) -> part, replacing route_fn + local_fn (one launch fewer)
         self._gather = None
 
     def forward(self, x, router_logits):
         import torch
-        ids, wts = self.route_fn(router_logits)
-        part = self.local_fn(x, ids, wts)
+        if self.routed_fn is not None:
+            part = self.routed_fn(x, router_logits)
+        else:
+            ids, wts = self.route_fn(router_logits)
+            part = self.local_fn(x, ids, wts)
         if self.world == 1:
             return part
         if self.exchange is not None:
@@ -280,3 +284,12 @@ def cuda_moe_fns(bank, k: int):
     def combine_fn(parts):
         return capi.sum_parts(parts)
     return route_fn, local_fn, combine_fn
+
+
+def cuda_moe_routed_fn(bank, k: int):
+    """routed_fn for ShardedMoE over libkrk_cuda.so: routing folded into the FFN's first kernel."""
+    from . import capi
+
+    def fn(x, logits):
+        return capi.moe_ffn_routed(x, logits, k, bank)[0]
+    return fn

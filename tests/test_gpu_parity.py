@@ -265,6 +265,27 @@ def moe_case(cuda, oracle, n_embd, n_ff, n_exp, k, n_tok, seed, local=None):
     return y, y_ref, keep
 
 
+def test_moe_routed_equals_route_then_ffn(cuda):
+    """krk_cuda_moe_ffn_routed gives the bits of krk_cuda_route followed by krk_cuda_moe_ffn, on the streaming
+    path (routing folded into the plan kernel) and on the shape-agnostic one, whole bank and a shard."""
+    import torch
+    for n_embd, n_ff, n_exp, k, n_tok, local in ((4096, 1536, 16, 8, 8, None), (4096, 1536, 16, 8, 1, (8, 16)),
+                                                  (512, 768, 8, 2, 3, None)):
+        seed = SEED + 70 + n_tok
+        lo, hi = local if local else (0, n_exp)
+        mk = lambda wt, r, c, st: dev(np.stack([synth.weights(wt, r, c, seed, stream=st + e) for e in range(lo, hi)]))
+        bank = cuda.make_bank(mk(synth.Q4_K, n_ff, n_embd, 1000), mk(synth.Q4_K, n_ff, n_embd, 2000),
+                              mk(synth.Q6_K, n_embd, n_ff, 3000), synth.Q4_K, synth.Q6_K, hi - lo, lo, n_embd, n_ff)
+        x = dev(synth.activations(n_tok, n_embd, seed))
+        logits = dev(synth.activations(n_tok, n_exp, seed, stream=7))
+        ids, wts = cuda.route(logits, k)
+        want = cuda.moe_ffn(x, ids, wts, bank)
+        got, ids2, wts2 = cuda.moe_ffn_routed(x, logits, k, bank)
+        assert cuda.device_status() == 0
+        assert torch.equal(ids, ids2) and torch.equal(wts, wts2)
+        assert torch.equal(got, want)
+
+
 def test_moe_small(cuda, oracle):
     moe_case(cuda, oracle, 512, 768, 8, 2, 3, SEED + 9)
     moe_case(cuda, oracle, 256, 512, 4, 4, 1, SEED + 10)        # every expert picked
