@@ -348,7 +348,7 @@ def run_ours(args):
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
                          "launches_per_step": n_launch, "avg_launch_us": round(per_step_ms * 1e3 / n_launch, 3),
                          "algorithmic_bytes_per_launch": abytes // n_launch, "traffic": TRAFFIC_BYTES_PER_LAUNCH,
-                         },
+                         "frac_of_spec_8000_gbs": round(achieved / 8000.0, 4)},
             "clocks": clocks,
         }
         if sharded is not None:
@@ -550,7 +550,14 @@ def decode_extra(torch, capi, gen, barrier):
         ms = timed(torch, call, 20 * n_rep, barrier, variants=n_rep)
         abytes = wbytes + 4 * n_in + 4 * n_out
         out[name] = {"us_per_launch": round(ms * 1e3, 3), "algorithmic_gbps": round(abytes / (ms * 1e-3) / 1e9, 1),
-                     "frac_of_measured_hbm": round(abytes / (ms * 1e-3) / 1e9 / peak, 4), "replicas_rotated": n_rep}
+                     "frac_of_measured_hbm": round(abytes / (ms * 1e-3) / 1e9 / peak, 4),
+                     "frac_of_spec_8000_gbs": round(abytes / (ms * 1e-3) / 1e9 / 8000.0, 4), "replicas_rotated": n_rep}
+        if name.startswith("config1"):
+            # the same launch over ONE replica: the weights stay in the 126 MB L2 (not an HBM number)
+            def warm(i):
+                capi.gemv(x, ws[0], wt, n_out, n_in, out=y)
+            ms_warm = timed(torch, warm, 200, barrier, variants=1)
+            out[name]["us_per_launch_l2_resident"] = round(ms_warm * 1e3, 3)
         del ws
     return out
 
@@ -579,14 +586,15 @@ def prefill_extra(torch, capi, gen):
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / reps
         tf = 2.0 * rows * n_out * n_in / (ms * 1e-3) / 1e12
-        out.append({"M": rows, "ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_measured_bf16_peak": round(tf / peak, 4)})
+        out.append({"M": rows, "ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_measured_bf16_peak": round(tf / peak, 4),
+                    "frac_of_spec_2250_tflops": round(tf / 2250.0, 4)})
     return {"workload": "q4_k_prefill_gemm_N14336_K4096", "kernel": "gemm_tc_kernel<Q4_K> (tcgen05)", "peak_tflops": peak,
             "results": out}
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the streaming kernel (mean over the four
 # launch shapes of a layer), from the ncu capture summarised in profiles/gemv_stream_q4k_llama7b_layer.md.
-TRAFFIC_BYTES_PER_LAUNCH = 21466880
+TRAFFIC_BYTES_PER_LAUNCH = 21467136
 
 
 # ---- CPU arms ---------------------------------------------------------------------------------------
