@@ -50,6 +50,7 @@ constexpr int kRawBytes = kTileN * 144;
 constexpr int kDecodeThreads = 256, kEpilogueThreads = 128;   // two decode threads per weight row
 constexpr int kThreads = kDecodeThreads + kEpilogueThreads + 96;
 constexpr int kTmemCols = 512, kTmemA = 256;
+constexpr int kYChunk = 32;            // tokens per TMA store of the read-out
 constexpr long long kWaitCycles = 4000000000LL;
 
 struct GemmParams {
@@ -63,11 +64,13 @@ struct GemmParams {
     int split_tail;        // 1: cut the tiles left after the last whole wave over all CTAs (needs the two below)
     unsigned *tail_count;  // one counter per tail tile, zero at launch
     float *tail_part;      // [2 * grid][tile_m * 128] f32: the pieces' partial tiles
+    int y_tma;             // 1: whole tiles leave through shared memory and TMA stores (y 16-byte aligned, n_out % 4 == 0)
 };
 
 struct __align__(1024) GemmSmem {
     uint8_t b[kBStages][kMaxTileM * 128];      // X tiles, [tokens][64 f16], 128B swizzle (TMA)
     uint8_t raw[kRawStages][kRawBytes];        // raw Q4_K bytes, [128 rows][144] (TMA)
+    float ystage[2][kYChunk][kTileN];          // accumulator read-out on its way to Y: [tokens][weight rows] (TMA store)
     unsigned long long b_full[kBStages], b_empty[kBStages];
     unsigned long long a_full[kAStages], a_empty[kAStages];
     unsigned long long raw_full[kRawStages], raw_empty[kRawStages];
@@ -119,6 +122,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
 }
@@ -301,7 +311,7 @@ struct ItemIter {
 template <int WT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap x_map,
-               const __grid_constant__ CUtensorMap w_map) {
+               const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap y_map) {
     constexpr bool kStagedRaw = WT == KRK_CUDA_Q4_K;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     GemmSmem *sm = reinterpret_cast<GemmSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -395,6 +405,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         const long long tail_total = (long long)(n_tiles - iter.n_full) * iter.k_blocks;
         const size_t part_elems = (size_t)p.tile_m * kTileN;
         int n_piece = 0;   // tail pieces this CTA has produced so far (0..2): its slots are 2*cta, 2*cta+1
+        int ybuf = 0;
         uint32_t ph = 0;
         while (iter.next(it)) {
             const int64_t n0 = (int64_t)(it.tile / p.n_tiles_m) * kTileN, m0 = (int64_t)(it.tile % p.n_tiles_m) * p.tile_m;
@@ -403,10 +414,37 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             tc_fence_after();
             const int64_t n = n0 + 32 * ew + lane;
             float *part = it.partial ? p.tail_part + (size_t)(2 * blockIdx.x + n_piece) * part_elems : nullptr;
-            for (int c0 = 0; c0 < p.tile_m; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(32 * ew) << 16) + (uint32_t)c0, v);
-                tmem_ld_wait();
+            const uint32_t d_addr = tmem_base + ((uint32_t)(32 * ew) << 16);
+            if (p.y_tma && !it.partial) {
+                // Whole tile: the accumulator goes to shared memory as [token][weight row] chunks of 32 tokens
+                // and leaves by TMA stores, so the accumulator is free again as soon as it has been read,
+                // not when Y has been written (this read-out is not hidden behind MMAs: its length counts).
+                // Rows past the end of Y are clipped by the tensor map.
+                for (int c0 = 0; c0 < p.tile_m; c0 += kYChunk) {
+                    uint32_t v[32];
+                    tmem_ld32(d_addr + (uint32_t)c0, v);
+                    tmem_ld_wait();
+                    if (et == 0) tma_store_wait_read<1>();   // the store that read this buffer two chunks ago is done with it
+                    asm volatile("bar.sync 2, %0;" ::"n"(kEpilogueThreads) : "memory");
+                    float *dst = &sm->ystage[ybuf][0][32 * ew + lane];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) dst[j * kTileN] = __uint_as_float(v[j]);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("bar.sync 2, %0;" ::"n"(kEpilogueThreads) : "memory");
+                    if (et == 0) {
+                        tma_store_2d(&y_map, (int)n0, (int)(m0 + c0), smem_u32(sm->ystage[ybuf]));
+                        tma_store_commit();
+                    }
+                    ybuf ^= 1;
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sm->d_empty));   // the accumulator is free again
+                continue;
+            }
+            // Direct form (cut tiles, or a Y the tensor map cannot describe), pipelined: while 32 columns are
+            // being stored, the next 32 are already on their way out of tensor memory.
+            auto put = [&](const uint32_t (&v)[32], int c0) {
                 if (it.partial) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) part[(size_t)(c0 + j) * kTileN + 32 * ew + lane] = __uint_as_float(v[j]);
@@ -416,6 +454,19 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         const int64_t m = m0 + c0 + j;
                         if (m < p.rows) p.y[m * p.n_out + n] = __uint_as_float(v[j]);
                     }
+                }
+            };
+            uint32_t va[32], vb[32];
+            tmem_ld32(d_addr, va);
+            for (int c0 = 0; c0 < p.tile_m; c0 += 64) {
+                tmem_ld_wait();
+                const bool more = c0 + 32 < p.tile_m;
+                if (more) tmem_ld32(d_addr + (uint32_t)(c0 + 32), vb);
+                put(va, c0);
+                if (more) {
+                    tmem_ld_wait();
+                    if (c0 + 64 < p.tile_m) tmem_ld32(d_addr + (uint32_t)(c0 + 64), va);
+                    put(vb, c0 + 32);
                 }
             }
             tc_fence_before();
@@ -482,6 +533,8 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                 }
             }
         }
+        // the staging buffers must outlive the stores that read them
+        if (et == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     } else if (warp == 12) {
         // ===== TMA producer of X tiles =====
         if (lane == 0) {
@@ -606,10 +659,32 @@ bool encode_w_map(CUtensorMap *map, const uint8_t *w, int wt, int64_t n_out, int
                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Tensor map over Y as a [rows][n_out] f32 matrix, box = 128 weight rows x kYChunk tokens, for the TMA stores
+// of the read-out. A Y that is not 16-byte aligned with 16-byte-multiple rows cannot be described: then a
+// dummy map over the first 16 bytes of the weights is encoded (never used) and the kernel stores directly.
+bool encode_y_map(CUtensorMap *map, float *y, const uint8_t *w, int64_t n_out, int64_t rows, bool usable) {
+    EncodeTiledFn encode = encode_tiled();
+    if (!encode) return false;
+    const cuuint32_t estr[2] = {1, 1};
+    if (!usable) {
+        const cuuint64_t d2[2] = {16, 1};
+        const cuuint64_t s2[1] = {16};
+        const cuuint32_t b2[2] = {16, 1};
+        return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w), d2, s2, b2, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)n_out, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)n_out * sizeof(float)};
+    const cuuint32_t box[2] = {(cuuint32_t)kTileN, (cuuint32_t)kYChunk};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int WT>
 int launch_wt(const GemmParams &p, const CUtensorMap &map, int grid, cudaStream_t st) {
-    CUtensorMap w_map;
+    CUtensorMap w_map, y_map;
     if (!encode_w_map(&w_map, p.w, WT, p.n_out, p.row_bytes)) return KRK_CUDA_ELAUNCH;
+    if (!encode_y_map(&y_map, p.y, p.w, p.n_out, p.rows, p.y_tma != 0)) return KRK_CUDA_ELAUNCH;
     static bool configured[64] = {};
     auto kernel = gemm_tc_kernel<WT>;
     const size_t smem = sizeof(GemmSmem) + 1024;
@@ -623,7 +698,7 @@ int launch_wt(const GemmParams &p, const CUtensorMap &map, int grid, cudaStream_
         }
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kernel<<<grid, kThreads, smem, st>>>(p, map, w_map);
+    kernel<<<grid, kThreads, smem, st>>>(p, map, w_map, y_map);
     note_launch(1, KRK_CUDA_FAMILY_GEMM_TC);
     return check_launch();
 }
@@ -700,6 +775,7 @@ int launch_gemm_tc(float *y, const void *x, int x_dtype, const uint8_t *w, int w
     p.n_tiles_m = g.n_tiles_m;
     p.row_bytes = (int)row_bytes(wt, n_in);
     p.split_tail = g.tail ? 1 : 0;
+    p.y_tma = ((reinterpret_cast<uintptr_t>(y) & 15) == 0 && (n_out % 4) == 0) ? 1 : 0;
     p.tail_count = reinterpret_cast<unsigned *>(ws + g.x_bytes);
     p.tail_part = reinterpret_cast<float *>(ws + g.x_bytes + g.count_bytes);
     p.status = device_status_word();
