@@ -51,6 +51,7 @@ constexpr int kDecodeThreads = 256, kEpilogueThreads = 128;   // two decode thre
 constexpr int kThreads = kDecodeThreads + kEpilogueThreads + 96;
 constexpr int kTmemCols = 512, kTmemA = 256;
 constexpr int kYChunk = 32;            // tokens per TMA store of the read-out
+constexpr int kMaxPieces = 4;          // a cut tile has about this many pieces at most
 constexpr long long kWaitCycles = 4000000000LL;
 
 struct GemmParams {
@@ -61,9 +62,8 @@ struct GemmParams {
     int n_tiles_n, n_tiles_m;
     int row_bytes;
     int *status;
-    int split_tail;        // 1: cut the tiles left after the last whole wave over all CTAs (needs the two below)
-    unsigned *tail_count;  // one counter per tail tile, zero at launch
-    float *tail_part;      // [2 * grid][tile_m * 128] f32: the pieces' partial tiles
+    int split_tail;        // 1: cut the tiles left after the last whole wave over the CTAs along K (needs y_tma and the counters)
+    unsigned *tail_count;  // per tail tile: how many of its pieces (in K order) are in Y; zero at launch
     int y_tma;             // 1: whole tiles leave through shared memory and TMA stores (y 16-byte aligned, n_out % 4 == 0)
 };
 
@@ -77,7 +77,6 @@ struct __align__(1024) GemmSmem {
     unsigned long long d_full, d_empty;
     uint32_t tmem_base;
     int gave_up;
-    int tail_last;
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -124,6 +123,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, uint32_t src) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, int x, int y, uint32_t src) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
                  ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
@@ -275,15 +278,22 @@ struct Item {
 struct ItemIter {
     int next_full, n_full, stride;   // whole tiles: next_full, next_full + stride, ... < n_full
     int b, e, k_blocks, tail0;       // tail pieces in units of 4 K steps: [b, e) of the tail's block range
+    int tail_grid;                   // CTAs that share the tail (at most kMaxPieces per tile, so the last piece's
+                                     // additions stay short)
     __device__ __forceinline__ void init(int cta, int grid, int n_tiles, int k_steps, int split_tail) {
         n_full = split_tail ? (n_tiles / grid) * grid : n_tiles;
         next_full = cta;
         stride = grid;
         k_blocks = k_steps / 4;
         tail0 = n_full;
-        const long long total = (long long)(n_tiles - n_full) * k_blocks;
-        b = (int)(total * cta / grid);
-        e = (int)(total * (cta + 1) / grid);
+        const int tail_tiles = n_tiles - n_full;
+        tail_grid = min(grid, tail_tiles * kMaxPieces);
+        const long long total = (long long)tail_tiles * k_blocks;
+        b = e = 0;
+        if (cta < tail_grid) {
+            b = (int)(total * cta / tail_grid);
+            e = (int)(total * (cta + 1) / tail_grid);
+        }
     }
     __device__ __forceinline__ bool next(Item &it) {
         if (next_full < n_full) {
@@ -295,13 +305,19 @@ struct ItemIter {
             return true;
         }
         if (b < e) {
-            const int t = b / k_blocks, kb = b - t * k_blocks;
-            const int n = min(k_blocks - kb, e - b);
+            // A share that runs from the middle of one tile into the next gives its piece of the LATER tile
+            // first: that piece starts the tile's sum and waits for nobody, so the chain of pieces waiting
+            // for their predecessor in K order never gets longer than one tile's pieces.
+            const int t_b = b / k_blocks, t_e = (e - 1) / k_blocks;
+            int from = b, to = e;
+            if (t_e > t_b) from = t_e * k_blocks;
+            const int t = from / k_blocks, kb = from - t * k_blocks;
+            const int n = to - from;
             it.tile = tail0 + t;
             it.k0 = kb * 4;
             it.nk = n * 4;
             it.partial = n != k_blocks;
-            b += n;
+            e = from;   // what is left is the earlier tile's piece (or nothing)
             return true;
         }
         return false;
@@ -400,137 +416,102 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         }
     } else if (warp < 12) {
         // ===== epilogue warps: TMEM lane = weight row, column = token =====
+        // Whole tiles and cut tiles leave the same way: the accumulator is read 32 tokens at a time, written to
+        // shared memory as [token][weight row] and stored by TMA, so the accumulator is free again as soon as
+        // it has been read (this read-out is not hidden behind MMAs: its length counts). Rows past the end of
+        // Y are clipped by the tensor map.
         const int ew = warp - 8, et = tid - kDecodeThreads;
-        const int grid = (int)gridDim.x;
+        const int tgrid = iter.tail_grid;
         const long long tail_total = (long long)(n_tiles - iter.n_full) * iter.k_blocks;
-        const size_t part_elems = (size_t)p.tile_m * kTileN;
-        int n_piece = 0;   // tail pieces this CTA has produced so far (0..2): its slots are 2*cta, 2*cta+1
+        const uint32_t d_addr = tmem_base + ((uint32_t)(32 * ew) << 16);
         int ybuf = 0;
         uint32_t ph = 0;
+        // one chunk: registers -> staging buffer -> TMA store through `map` at (x, y)
+        auto ship = [&](const uint32_t (&v)[32], const CUtensorMap *map, int x, int y, bool add) {
+            if (et == 0) tma_store_wait_read<1>();   // the store that read this buffer two chunks ago is done with it
+            asm volatile("bar.sync 2, %0;" ::"n"(kEpilogueThreads) : "memory");
+            float *dst = &sm->ystage[ybuf][0][32 * ew + lane];
+#pragma unroll
+            for (int j = 0; j < 32; j++) dst[j * kTileN] = __uint_as_float(v[j]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync 2, %0;" ::"n"(kEpilogueThreads) : "memory");
+            if (et == 0) {
+                if (add) tma_reduce_add_2d(map, x, y, smem_u32(sm->ystage[ybuf]));
+                else tma_store_2d(map, x, y, smem_u32(sm->ystage[ybuf]));
+                tma_store_commit();
+            }
+            ybuf ^= 1;
+        };
+        // one chunk straight to Y (a Y the tensor map cannot describe)
+        auto put = [&](const uint32_t (&v)[32], int64_t n, int64_t m_first) {
+            if (n < p.n_out) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const int64_t m = m_first + j;
+                    if (m < p.rows) p.y[m * p.n_out + n] = __uint_as_float(v[j]);
+                }
+            }
+        };
         while (iter.next(it)) {
             const int64_t n0 = (int64_t)(it.tile / p.n_tiles_m) * kTileN, m0 = (int64_t)(it.tile % p.n_tiles_m) * p.tile_m;
             wait_phase(smem_u32(&sm->d_full), ph, gave_up, p.status);
             ph ^= 1;
             tc_fence_after();
             const int64_t n = n0 + 32 * ew + lane;
-            float *part = it.partial ? p.tail_part + (size_t)(2 * blockIdx.x + n_piece) * part_elems : nullptr;
-            const uint32_t d_addr = tmem_base + ((uint32_t)(32 * ew) << 16);
-            if (p.y_tma && !it.partial) {
-                // Whole tile: the accumulator goes to shared memory as [token][weight row] chunks of 32 tokens
-                // and leaves by TMA stores, so the accumulator is free again as soon as it has been read,
-                // not when Y has been written (this read-out is not hidden behind MMAs: its length counts).
-                // Rows past the end of Y are clipped by the tensor map.
+            if (!it.partial) {
                 for (int c0 = 0; c0 < p.tile_m; c0 += kYChunk) {
                     uint32_t v[32];
                     tmem_ld32(d_addr + (uint32_t)c0, v);
                     tmem_ld_wait();
-                    if (et == 0) tma_store_wait_read<1>();   // the store that read this buffer two chunks ago is done with it
-                    asm volatile("bar.sync 2, %0;" ::"n"(kEpilogueThreads) : "memory");
-                    float *dst = &sm->ystage[ybuf][0][32 * ew + lane];
-#pragma unroll
-                    for (int j = 0; j < 32; j++) dst[j * kTileN] = __uint_as_float(v[j]);
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    asm volatile("bar.sync 2, %0;" ::"n"(kEpilogueThreads) : "memory");
-                    if (et == 0) {
-                        tma_store_2d(&y_map, (int)n0, (int)(m0 + c0), smem_u32(sm->ystage[ybuf]));
-                        tma_store_commit();
-                    }
-                    ybuf ^= 1;
+                    if (p.y_tma) ship(v, &y_map, (int)n0, (int)(m0 + c0), false);
+                    else put(v, n, m0 + c0);
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&sm->d_empty));   // the accumulator is free again
                 continue;
             }
-            // Direct form (cut tiles, or a Y the tensor map cannot describe), pipelined: while 32 columns are
-            // being stored, the next 32 are already on their way out of tensor memory.
-            auto put = [&](const uint32_t (&v)[32], int c0) {
-                if (it.partial) {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) part[(size_t)(c0 + j) * kTileN + 32 * ew + lane] = __uint_as_float(v[j]);
-                } else if (n < p.n_out) {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int64_t m = m0 + c0 + j;
-                        if (m < p.rows) p.y[m * p.n_out + n] = __uint_as_float(v[j]);
+            // ---- a piece of a cut tile: added into Y in K order ----
+            // Piece k of the tile (k = how many CTAs hold earlier blocks of it) waits, bounded, until the
+            // tile's count says that pieces 0..k-1 are in Y; piece 0 stores, the others add (TMA reduction in
+            // L2); then the count goes up. The order of the additions is the K order whoever finishes first.
+            const int t = it.tile - iter.tail0;
+            const long long lo = (long long)t * iter.k_blocks, hi = lo + iter.k_blocks;
+            int c_lo = (int)(lo * tgrid / tail_total);
+            c_lo = max(c_lo - 1, 0);
+            int k_piece = 0;
+            for (int c = c_lo; c < (int)blockIdx.x; c++) {
+                const long long sb = tail_total * c / tgrid, se = tail_total * (c + 1) / tgrid;
+                k_piece += (max(sb, lo) < min(se, hi)) ? 1 : 0;
+            }
+            if (k_piece > 0) {
+                if (et == 0) {
+                    const long long t0 = clock64();
+                    while (*reinterpret_cast<volatile unsigned *>(p.tail_count + t) < (unsigned)k_piece) {
+                        __nanosleep(64);
+                        if (clock64() - t0 > kWaitCycles) {
+                            atomicExch(p.status, KRK_CUDA_ETIMEOUT);
+                            break;
+                        }
                     }
+                    __threadfence();
                 }
-            };
-            uint32_t va[32], vb[32];
-            tmem_ld32(d_addr, va);
-            for (int c0 = 0; c0 < p.tile_m; c0 += 64) {
+                asm volatile("bar.sync 2, %0;" ::"n"(kEpilogueThreads) : "memory");
+            }
+            for (int c0 = 0; c0 < p.tile_m; c0 += kYChunk) {
+                uint32_t v[32];
+                tmem_ld32(d_addr + (uint32_t)c0, v);
                 tmem_ld_wait();
-                const bool more = c0 + 32 < p.tile_m;
-                if (more) tmem_ld32(d_addr + (uint32_t)(c0 + 32), vb);
-                put(va, c0);
-                if (more) {
-                    tmem_ld_wait();
-                    if (c0 + 64 < p.tile_m) tmem_ld32(d_addr + (uint32_t)(c0 + 64), va);
-                    put(vb, c0 + 32);
-                }
+                ship(v, &y_map, (int)n0, (int)(m0 + c0), k_piece > 0);
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sm->d_empty));   // the accumulator is free again
-            if (!it.partial) continue;
-            n_piece++;
-            // Whoever completes the tile's last piece adds all of them, in K order, into Y.
-            __threadfence();
-            asm volatile("bar.sync 2, %0;" ::"n"(kEpilogueThreads) : "memory");
-            const int t = it.tile - iter.tail0;
-            const long long lo = (long long)t * iter.k_blocks, hi = lo + iter.k_blocks;
-            // CTAs whose share [total*c/grid, total*(c+1)/grid) meets this tile's blocks [lo, hi)
-            int c_lo = (int)(lo * grid / tail_total), c_hi = (int)((hi * grid + tail_total - 1) / tail_total);
-            c_lo = max(c_lo - 1, 0);
-            c_hi = min(c_hi + 1, grid);
-            int pieces = 0;
-            for (int c = c_lo; c < c_hi; c++) {
-                const long long b = tail_total * c / grid, e = tail_total * (c + 1) / grid;
-                pieces += (max(b, lo) < min(e, hi)) ? 1 : 0;
-            }
-            if (et == 0) sm->tail_last = (atomicAdd(p.tail_count + t, 1u) == (unsigned)(pieces - 1)) ? 1 : 0;
-            asm volatile("bar.sync 2, %0;" ::"n"(kEpilogueThreads) : "memory");
-            if (!sm->tail_last) continue;
-            __threadfence();
-            // warp ew takes tokens ew, ew+4, ...; a lane takes four neighbouring weight rows (one float4 per
-            // piece); eight tokens are in flight at once so that the L2 round trips overlap
-            for (int c0 = ew; c0 < p.tile_m; c0 += 4 * 8) {
-                float4 acc[8];
-#pragma unroll
-                for (int u = 0; u < 8; u++) acc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                for (int c = c_lo; c < c_hi; c++) {
-                    const long long b = tail_total * c / grid, e = tail_total * (c + 1) / grid;
-                    if (max(b, lo) >= min(e, hi)) continue;
-                    // the slot of CTA c's piece of this tile: its first piece unless its share began in an earlier tile
-                    const float *src = p.tail_part + (size_t)(2 * c + ((b < lo) ? 1 : 0)) * part_elems + 4 * lane;
-#pragma unroll
-                    for (int u = 0; u < 8; u++) {
-                        const int tok = c0 + 4 * u;
-                        if (tok < p.tile_m) {
-                            const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)tok * kTileN));
-                            acc[u].x += v.x;
-                            acc[u].y += v.y;
-                            acc[u].z += v.z;
-                            acc[u].w += v.w;
-                        }
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 8; u++) {
-                    const int tok = c0 + 4 * u;
-                    const int64_t m = m0 + tok, nn = n0 + 4 * lane;
-                    if (tok < p.tile_m && m < p.rows) {
-                        float *dst = p.y + m * p.n_out + nn;
-                        if (nn + 3 < p.n_out && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-                            *reinterpret_cast<float4 *>(dst) = acc[u];
-                        } else {
-                            if (nn < p.n_out) dst[0] = acc[u].x;
-                            if (nn + 1 < p.n_out) dst[1] = acc[u].y;
-                            if (nn + 2 < p.n_out) dst[2] = acc[u].z;
-                            if (nn + 3 < p.n_out) dst[3] = acc[u].w;
-                        }
-                    }
-                }
+            if (lane == 0) mbar_arrive(smem_u32(&sm->d_empty));
+            if (et == 0) {
+                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // this piece is in Y
+                asm volatile("fence.proxy.async;" ::: "memory");
+                __threadfence();
+                atomicAdd(p.tail_count + t, 1u);
             }
         }
         // the staging buffers must outlive the stores that read them
@@ -709,7 +690,7 @@ namespace {
 
 struct GemmPlan {
     int tile_m, n_tiles_n, n_tiles_m, grid, tail;   // tail: tiles left after the last whole wave (0 = none)
-    size_t x_bytes, count_bytes, part_bytes;
+    size_t x_bytes, count_bytes;
 };
 
 int grid_bound() {
@@ -727,9 +708,10 @@ GemmPlan plan_gemm(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows) {
     g.n_tiles_m = (int)((rows + g.tile_m - 1) / g.tile_m);
     const int tiles = g.n_tiles_n * g.n_tiles_m, sms = grid_bound();
     g.grid = tiles < sms ? tiles : sms;
-    // Cutting the left-over tiles is opt-in (KRK_CUDA_GEMM_SPLIT=1, read once, in the style of the
-    // reference's KRK_* A/B switches): measured on config 3 the fixed-order combine of the pieces costs
-    // more than the idle SMs it saves (M = 512: 639 vs 776 TFLOP/s), so whole tiles are the default.
+    // Cutting the left-over tiles along K is opt-in (KRK_CUDA_GEMM_SPLIT=1, read once, in the style of the
+    // reference's KRK_* A/B switches): the pieces meet in Y through ordered TMA reductions, without scratch,
+    // but every extra piece pays a pipeline fill and a read-out, and measured on config 3 that eats what the
+    // better balance gains (M = 512: 65.1 vs 64.9 us), so whole tiles are the default.
     static const bool split_on = [] {
         const char *e = std::getenv("KRK_CUDA_GEMM_SPLIT");
         return e && e[0] == '1';
@@ -737,7 +719,6 @@ GemmPlan plan_gemm(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows) {
     g.tail = (split_on && tiles >= sms) ? tiles % sms : 0;
     g.x_bytes = x_dtype == KRK_CUDA_X_F32 ? (((size_t)rows * (size_t)n_in * sizeof(__half) + 255) & ~(size_t)255) : 0;
     g.count_bytes = g.tail ? (((size_t)g.tail * sizeof(unsigned) + 255) & ~(size_t)255) : 0;
-    g.part_bytes = g.tail ? (size_t)2 * g.grid * g.tile_m * kTileN * sizeof(float) : 0;
     return g;
 }
 
@@ -745,7 +726,7 @@ GemmPlan plan_gemm(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows) {
 
 size_t gemm_workspace_bytes(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows) {
     const GemmPlan g = plan_gemm(x_dtype, n_out, n_in, rows);
-    return g.x_bytes + g.count_bytes + g.part_bytes;
+    return g.x_bytes + g.count_bytes;
 }
 
 int launch_gemm_tc(float *y, const void *x, int x_dtype, const uint8_t *w, int wt, int64_t n_out, int64_t n_in,
@@ -774,10 +755,9 @@ int launch_gemm_tc(float *y, const void *x, int x_dtype, const uint8_t *w, int w
     p.n_tiles_n = g.n_tiles_n;
     p.n_tiles_m = g.n_tiles_m;
     p.row_bytes = (int)row_bytes(wt, n_in);
-    p.split_tail = g.tail ? 1 : 0;
     p.y_tma = ((reinterpret_cast<uintptr_t>(y) & 15) == 0 && (n_out % 4) == 0) ? 1 : 0;
+    p.split_tail = (g.tail && p.y_tma) ? 1 : 0;   // the pieces of a cut tile meet in Y through TMA reductions
     p.tail_count = reinterpret_cast<unsigned *>(ws + g.x_bytes);
-    p.tail_part = reinterpret_cast<float *>(ws + g.x_bytes + g.count_bytes);
     p.status = device_status_word();
     if (!p.status) return KRK_CUDA_EDEVICE;
     if (g.tail) {
@@ -871,9 +851,8 @@ extern "C" int krk_cuda_gemm_f32_static(void *y_f32, const void *x_f32, const vo
     p.n_tiles_n = (int)((n_out + kTileN - 1) / kTileN);
     p.n_tiles_m = (int)((rows + p.tile_m - 1) / p.tile_m);
     p.row_bytes = (int)row_bytes(wt, n_in);
-    p.split_tail = 0;   // cutting tiles needs scratch for the pieces; this entry keeps whole tiles
+    p.split_tail = 0;   // cutting tiles needs counters in a workspace; this entry keeps whole tiles
     p.tail_count = nullptr;
-    p.tail_part = nullptr;
     p.status = status;
     EncodeTiledFn encode = encode_tiled();
     if (!encode) return KRK_CUDA_EDEVICE;
