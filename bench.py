@@ -559,6 +559,24 @@ def decode_extra(torch, capi, gen, barrier):
             ms_warm = timed(torch, warm, 200, barrier, variants=1)
             out[name]["us_per_launch_l2_resident"] = round(ms_warm * 1e3, 3)
         del ws
+    # the steps either side of the head, on the device: top-k of config 4's logits row and an embedding gather
+    n_vocab = 128256
+    logits = torch.randn(n_vocab, device="cuda", generator=gen) * 3.0
+    for k in (1, 40):
+        ws_k = torch.empty(capi.lib.krk_cuda_logits_topk_workspace_bytes(n_vocab, k), dtype=torch.uint8, device="cuda")
+
+        def topk_call(i):
+            capi.logits_topk(logits, k, workspace=ws_k)
+        ms = timed(torch, topk_call, 100, barrier, variants=1)
+        out[f"logits_topk_128256_k{k}"] = {"us_per_call": round(ms * 1e3, 3), "kernels": 2,
+                                            "replaces": "513,024-byte logits download + host ranking per token"}
+    table = device_weights_q6k(torch, 32768, 4096, gen)
+    toks = torch.randint(0, 32768, (8,), dtype=torch.int32, device="cuda", generator=gen)
+
+    def embed_call(i):
+        capi.embed(table, synth.Q6_K, 32768, 4096, toks)
+    ms = timed(torch, embed_call, 100, barrier, variants=1)
+    out["embed_q6_k_8_tokens_x4096"] = {"us_per_call": round(ms * 1e3, 3)}
     return out
 
 

@@ -205,6 +205,24 @@ int krk_cuda_gemv_allgather(void *const host_y_peers[], void *const host_flag_pe
                             const void *x_f32, const void *w, int wt, int64_t n_out_local, int64_t n_in,
                             int64_t rows, void *stream);
 
+/* ---- the steps either side of the output head ---- */
+
+/* Replaces Backend::embed (include/krk/backend.hpp:838; src/backend_cpu.cpp:746-778): out_f32[t] = decoded
+ * row tokens_i32[t] of the quantized table (row-major [n_vocab][row_bytes]); an id outside [0, n_vocab)
+ * gives a zero row. tokens_i32 is device memory. Bit-exact with krk::dequant_row. */
+int krk_cuda_embed(void *out_f32, const void *tok_embd, int wt, int64_t n_vocab, int64_t n_embd,
+                   const void *tokens_i32, int64_t n_tok, void *stream);
+
+/* Replaces Backend::logits_topk (include/krk/backend.hpp:902-922; src/backend_cpu.cpp:862-912) for f32
+ * logits: softcap clamp and repetition penalty (pen_mask_u32: one bit per token id, may be NULL) before
+ * ranking; k ids and values in descending order, ties toward the lower id, -1 / -FLT_MAX past the row's
+ * length; mass_f32 (may be NULL) = sum over the whole row of exp((key - max) / temp). All pointers are
+ * device memory; 1 <= k <= 64. The candidate buffer of the reference is the workspace here. */
+size_t krk_cuda_logits_topk_workspace_bytes(int64_t n, int k);
+int krk_cuda_logits_topk(const void *logits_f32, int64_t n, int k, const void *pen_mask_u32, float rep_pen,
+                         float softcap, float temp, void *ids_i32, void *vals_f32, void *mass_f32,
+                         void *workspace, size_t ws_bytes, void *stream);
+
 /* Expert-sharded FFN, exchange step: all-gather of partial sums over NVLink peer stores fused with the
  * rank-ordered sum that follows (no counterpart in the reference, which is single-device). part_f32
  * holds this GPU's partial sum (n floats, n % 4 == 0, 16-byte aligned like out_f32); the kernel stores it

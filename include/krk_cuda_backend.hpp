@@ -71,6 +71,16 @@ public:
                            i64 n_rows, i64 n, const f32 *row_scale = nullptr,
                            i32 *row_exp = nullptr);              // backend.hpp:1473
 
+    // out[n_tok, n_embd] <- rows of the quantized table selected by tokens (backend.hpp:838). `tokens` is
+    // HOST memory, as the Backend contract has it; it is staged into device scratch on the stream. An id
+    // outside [0, n_vocab) gives a zero row (src/backend_cpu.cpp:746-778).
+    void embed(void *out, const void *tok_embd, DType tt, i64 n_vocab, i64 n_embd, const i32 *tokens, i64 n_tok);
+    // Top-k of one f32 logits row on the device (backend.hpp:902-922): ids, vals, mass_out and count_out
+    // are device pointers, as on the HIP backend; scratch / cand_cap are accepted and not needed (the
+    // candidate buffer is the backend's own workspace, and the set is never truncated: *count_out = min(n, k)).
+    void logits_topk(const void *logits, i64 n, i32 k, const void *pen_mask, f32 rep_pen, f32 softcap, f32 temp,
+                     i32 *ids, f32 *vals, f32 *mass_out, void *scratch, i32 cand_cap, i64 *count_out);
+
     void *stream() const { return stream_; }
     int device() const { return device_; }
 

@@ -66,6 +66,9 @@ SIGNATURES = {
     "krk_cuda_gemv_allgather": (_int, [C.POINTER(_vp), C.POINTER(_vp), _int, _int, _int, _int, _i64, _i64, _vp, _vp, _int, _i64,
                                        _i64, _i64, _vp]),
     "krk_cuda_wait_flags": (_int, [_vp, _int, _int, _vp]),
+    "krk_cuda_embed": (_int, [_vp, _vp, _int, _i64, _i64, _vp, _i64, _vp]),
+    "krk_cuda_logits_topk_workspace_bytes": (_sz, [_i64, _int]),
+    "krk_cuda_logits_topk": (_int, [_vp, _i64, _int, _vp, C.c_float, C.c_float, C.c_float, _vp, _vp, _vp, _vp, _sz, _vp]),
     "krk_cuda_allgather_sum": (_int, [C.POINTER(_vp), C.POINTER(_vp), _int, _int, _i64, _vp, _vp, _i64, _vp]),
     "krk_cuda_peer_alloc": (_int, [C.POINTER(_vp), C.c_size_t, C.c_char_p]),
     "krk_cuda_peer_open": (_int, [C.POINTER(_vp), C.c_char_p]),
@@ -274,6 +277,33 @@ def gemv_allgather(y_peer_ptrs, flag_peer_ptrs, my_rank: int, epoch: int, slice_
 
 def wait_flags(flags, n_peers: int, epoch: int, stream=None):
     _check(lib.krk_cuda_wait_flags(_ptr(flags), n_peers, epoch, _stream_ptr(stream)), "wait_flags")
+
+
+def embed(table, wt: int, n_vocab: int, n_embd: int, tokens, out=None, stream=None):
+    """Rows of a quantized embedding table by token id (device int32 tensor) as f32; bad ids give zero rows."""
+    import torch
+    n_tok = tokens.numel()
+    if out is None:
+        out = torch.empty((n_tok, n_embd), dtype=torch.float32, device=table.device)
+    _check(lib.krk_cuda_embed(_ptr(out), _ptr(table), wt, n_vocab, n_embd, _ptr(tokens), n_tok, _stream_ptr(stream)), "embed")
+    return out
+
+
+def logits_topk(logits, k: int, pen_mask=None, rep_pen: float = 1.0, softcap: float = 0.0, temp: float = 1.0,
+                want_mass: bool = True, workspace=None, stream=None):
+    """Device top-k of one f32 logits row: (ids int32 [k], vals f32 [k], mass f32 [1] or None)."""
+    import torch
+    n = logits.numel()
+    ids = torch.empty(k, dtype=torch.int32, device=logits.device)
+    vals = torch.empty(k, dtype=torch.float32, device=logits.device)
+    mass = torch.empty(1, dtype=torch.float32, device=logits.device) if want_mass else None
+    need = lib.krk_cuda_logits_topk_workspace_bytes(n, k)
+    if workspace is None:
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=logits.device)
+    _check(lib.krk_cuda_logits_topk(_ptr(logits), n, k, _ptr(pen_mask) if pen_mask is not None else None, rep_pen, softcap,
+                                    temp, _ptr(ids), _ptr(vals), _ptr(mass) if mass is not None else None, _ptr(workspace),
+                                    workspace.numel(), _stream_ptr(stream)), "logits_topk")
+    return ids, vals, mass
 
 
 def allgather_sum(gather_peer_ptrs, flag_peer_ptrs, my_rank: int, slot_stride: int, part, out, stream=None):

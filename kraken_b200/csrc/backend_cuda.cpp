@@ -171,6 +171,33 @@ void CudaBackend::scatter_axpy_rows(void *dst, const void *src, const i32 *rows,
     if (rc != KRK_CUDA_OK) die("scatter_axpy_rows", rc, n_rows, n, 0, 0);
 }
 
+void CudaBackend::embed(void *out, const void *tok_embd, DType tt, i64 n_vocab, i64 n_embd, const i32 *tokens,
+                        i64 n_tok) {
+    if (n_tok <= 0) return;
+    const size_t need = (size_t)n_tok * sizeof(i32);
+    void *dev_tokens = workspace(need);
+    KRK_CUDA_CHECK(cudaMemcpyAsync(dev_tokens, tokens, need, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream_)));
+    const int rc = krk_cuda_embed(out, tok_embd, (int)tt, n_vocab, n_embd, dev_tokens, n_tok, stream_);
+    if (rc != KRK_CUDA_OK) die("embed", rc, n_vocab, n_embd, n_tok, (int)tt);
+}
+
+void CudaBackend::logits_topk(const void *logits, i64 n, i32 k, const void *pen_mask, f32 rep_pen, f32 softcap,
+                              f32 temp, i32 *ids, f32 *vals, f32 *mass_out, void *scratch, i32 cand_cap,
+                              i64 *count_out) {
+    (void)scratch;
+    (void)cand_cap;
+    if (n <= 0 || k <= 0) return;
+    const size_t need = krk_cuda_logits_topk_workspace_bytes(n, k);
+    const int rc = krk_cuda_logits_topk(logits, n, k, pen_mask, rep_pen, softcap, temp, ids, vals, mass_out,
+                                        workspace(need), need, stream_);
+    if (rc != KRK_CUDA_OK) die("logits_topk", rc, n, k, 0, 0);
+    if (count_out) {   // min(n, k) <= 64 as a little-endian i64, without a host buffer that must outlive the copy
+        const i64 keep = n < k ? n : k;
+        KRK_CUDA_CHECK(cudaMemsetAsync(count_out, 0, sizeof(i64), static_cast<cudaStream_t>(stream_)));
+        KRK_CUDA_CHECK(cudaMemsetAsync(count_out, (int)keep, 1, static_cast<cudaStream_t>(stream_)));
+    }
+}
+
 } // namespace krk_cuda
 
 // ---- C shim over the class (declared in krk_cuda.h) -------------------------------------------

@@ -178,6 +178,12 @@ int launch_silu_mul(float *out, const float *gate, const float *up, int64_t n, c
 int launch_scatter_axpy_rows(float *dst, const float *src, const int32_t *rows, const float *alpha,
                              int64_t n_rows, int64_t n, cudaStream_t st);
 int launch_sum_parts(float *out, const float *parts, int n_parts, int64_t n, cudaStream_t st);
+// Embedding gather (decoded rows by token id) and device top-k of a logits row.
+int launch_embed(float *out, const uint8_t *table, int wt, int64_t n_vocab, int64_t n_embd, const int32_t *tokens,
+                 int64_t n_tok, cudaStream_t st);
+size_t logits_topk_workspace_bytes(int64_t n, int k);
+int launch_logits_topk(const float *logits, int64_t n, int k, const uint32_t *pen_mask, float rep_pen, float softcap,
+                       float temp, int32_t *ids, float *vals, float *mass_out, void *workspace, cudaStream_t st);
 int launch_route(int32_t *ids, float *wts, const float *logits, int64_t n_tok, int n_expert, int k,
                  cudaStream_t st);
 size_t moe_workspace_bytes(const krk_cuda_expert_bank *bank, int k, int64_t n_tok);

@@ -306,6 +306,36 @@ int krk_cuda_gemv_allgather(void *const host_y_peers[], void *const host_flag_pe
     return took == 1 ? KRK_CUDA_OK : KRK_CUDA_ESHAPE;
 }
 
+int krk_cuda_embed(void *out_f32, const void *tok_embd, int wt, int64_t n_vocab, int64_t n_embd,
+                   const void *tokens_i32, int64_t n_tok, void *stream) {
+    if (!krk_cuda_dtype_ok(wt)) return KRK_CUDA_EDTYPE;
+    if (n_vocab < 0 || n_embd < 0 || n_tok < 0 || n_embd % block_size(wt) != 0) return KRK_CUDA_ESHAPE;
+    if (n_tok * n_embd == 0) return KRK_CUDA_OK;
+    if (!out_f32 || !tok_embd || !tokens_i32) return KRK_CUDA_ENULL;
+    if (!aligned(out_f32, 4) || !aligned(tokens_i32, 4)) return KRK_CUDA_EALIGN;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_embed(static_cast<float *>(out_f32), static_cast<const uint8_t *>(tok_embd), wt, n_vocab, n_embd,
+                        static_cast<const int32_t *>(tokens_i32), n_tok, static_cast<cudaStream_t>(stream));
+}
+
+size_t krk_cuda_logits_topk_workspace_bytes(int64_t n, int k) {
+    if (n < 1 || k < 1 || k > 64) return 0;
+    return logits_topk_workspace_bytes(n, k);
+}
+
+int krk_cuda_logits_topk(const void *logits_f32, int64_t n, int k, const void *pen_mask_u32, float rep_pen,
+                         float softcap, float temp, void *ids_i32, void *vals_f32, void *mass_f32,
+                         void *workspace, size_t ws_bytes, void *stream) {
+    if (n < 1) return KRK_CUDA_ESHAPE;
+    if (k < 1 || k > 64) return KRK_CUDA_EARG;
+    if (!logits_f32 || !ids_i32 || !vals_f32) return KRK_CUDA_ENULL;
+    if (!workspace || ws_bytes < logits_topk_workspace_bytes(n, k) || !aligned(workspace, 16)) return KRK_CUDA_EWORKSPACE;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_logits_topk(static_cast<const float *>(logits_f32), n, k, static_cast<const uint32_t *>(pen_mask_u32),
+                              rep_pen, softcap, temp, static_cast<int32_t *>(ids_i32), static_cast<float *>(vals_f32),
+                              static_cast<float *>(mass_f32), workspace, static_cast<cudaStream_t>(stream));
+}
+
 int krk_cuda_allgather_sum(void *const host_gather_peers[], void *const host_flag_peers[], int n_peers, int my_rank,
                            int64_t slot_stride, const void *part_f32, void *out_f32, int64_t n, void *stream) {
     if (n_peers < 1 || n_peers > KRK_CUDA_MAX_PEERS || my_rank < 0 || my_rank >= n_peers) return KRK_CUDA_EARG;

@@ -11,6 +11,7 @@
  */
 #include "krk_oracle.h"
 
+#include <float.h>
 #include <math.h>
 #include <pthread.h>
 #include <stdlib.h>
@@ -287,6 +288,70 @@ void krk_oracle_silu_mul(float *out, const float *gate, const float *up, int64_t
         const float g = gate[i];
         out[i] = (g / (1.0f + expf(-g))) * up[i];
     }
+}
+
+/* src/backend_cpu.cpp:746-778: rows of the table by token id; an id outside [0, n_vocab) gives a zero row */
+int krk_oracle_embed(float *out, const void *table, int wt, int64_t n_vocab, int64_t n_embd,
+                     const int32_t *tokens, int64_t n_tok) {
+    const size_t rb = krk_oracle_row_bytes(wt, n_embd);
+    if (rb == 0 && n_embd != 0) return -1;
+    for (int64_t t = 0; t < n_tok; t++) {
+        float *dst = out + t * n_embd;
+        const int32_t id = tokens[t];
+        if (id < 0 || (int64_t)id >= n_vocab) {
+            memset(dst, 0, (size_t)n_embd * sizeof(float));
+            continue;
+        }
+        if (krk_oracle_dequant_rows(dst, (const uint8_t *)table + (size_t)id * rb, wt, 1, n_embd) != 0) return -1;
+    }
+    return 0;
+}
+
+/* src/backend_cpu.cpp:862-912: key = logit, clamped to +-softcap, then the repetition penalty where the
+ * token's mask bit is set; the k largest keys, descending, ties toward the lower id; -1 / -FLT_MAX past
+ * the row's length; mass = sum in index order of exp((key - max) / temp). */
+static float topk_key(const float *l, const uint32_t *pm, float rep_pen, float softcap, int32_t i) {
+    float v = l[i];
+    if (softcap > 0.0f) v = v > softcap ? softcap : (v < -softcap ? -softcap : v);
+    if (pm && rep_pen > 0.0f && rep_pen != 1.0f && ((pm[(uint32_t)i >> 5] >> ((uint32_t)i & 31)) & 1u))
+        v = v > 0.0f ? v / rep_pen : v * rep_pen;
+    return v;
+}
+
+int krk_oracle_logits_topk(const float *logits, int64_t n, int k, const uint32_t *pen_mask, float rep_pen,
+                           float softcap, float temp, int32_t *ids, float *vals, float *mass_out) {
+    if (n < 1 || k < 1) return -1;
+    const int64_t keep = n < k ? n : k;
+    uint8_t *taken = (uint8_t *)calloc((size_t)n, 1);
+    if (!taken) return -1;
+    for (int r = 0; r < k; r++) {
+        if (r >= keep) {
+            ids[r] = -1;
+            vals[r] = -FLT_MAX;
+            continue;
+        }
+        int64_t best = -1;
+        float bv = 0.0f;
+        for (int64_t i = 0; i < n; i++) {   /* first maximum in index order = lower id on ties */
+            if (taken[i]) continue;
+            const float v = topk_key(logits, pen_mask, rep_pen, softcap, (int32_t)i);
+            if (best < 0 || v > bv) {
+                best = i;
+                bv = v;
+            }
+        }
+        taken[best] = 1;
+        ids[r] = (int32_t)best;
+        vals[r] = bv;
+    }
+    free(taken);
+    if (mass_out) {
+        const float inv = temp > 0.0f ? 1.0f / temp : 1.0f, maxv = vals[0];
+        float m = 0.0f;
+        for (int64_t i = 0; i < n; i++) m += expf((topk_key(logits, pen_mask, rep_pen, softcap, (int32_t)i) - maxv) * inv);
+        *mass_out = m;
+    }
+    return 0;
 }
 
 /* src/backend_cpu.cpp:3193-3220 */

@@ -59,6 +59,10 @@ int krk_oracle_route(int32_t *ids, float *wts, const float *logits, int64_t n_to
 
 /* out[i] = (g/(1+exp(-g))) * u  (src/backend_cpu.cpp:2394-2400). */
 void krk_oracle_silu_mul(float *out, const float *gate, const float *up, int64_t n);
+int krk_oracle_embed(float *out, const void *table, int wt, int64_t n_vocab, int64_t n_embd,
+                     const int32_t *tokens, int64_t n_tok);
+int krk_oracle_logits_topk(const float *logits, int64_t n, int k, const uint32_t *pen_mask, float rep_pen,
+                           float softcap, float temp, int32_t *ids, float *vals, float *mass_out);
 
 /* dst[rows[i]] += alpha[i] * src[i]  (src/backend_cpu.cpp:3193-3220). */
 void krk_oracle_scatter_axpy_rows(float *dst, const float *src, const int32_t *rows,

@@ -54,6 +54,9 @@ class Oracle:
         L.krk_oracle_silu_mul.restype = None
         L.krk_oracle_scatter_axpy_rows.argtypes = [_f32p, _f32p, _i32p, _f32p, C.c_int64, C.c_int64]
         L.krk_oracle_scatter_axpy_rows.restype = None
+        L.krk_oracle_embed.argtypes = [_f32p, _u8p, C.c_int, C.c_int64, C.c_int64, _i32p, C.c_int64]
+        L.krk_oracle_logits_topk.argtypes = [_f32p, C.c_int64, C.c_int, C.c_void_p, C.c_float, C.c_float, C.c_float, _i32p,
+                                             _f32p, _f32p]
         L.krk_oracle_moe_ffn.argtypes = [_f32p, _f32p, _i32p, _f32p, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64,
                                          C.c_int64, C.c_int]
@@ -97,6 +100,23 @@ class Oracle:
         if rc != 0:
             raise ValueError("route refused its arguments")
         return ids, wts
+
+    def embed(self, table, wt, n_vocab, n_embd, tokens):
+        table, tokens = _c(table, np.uint8), _c(tokens, np.int32)
+        out = np.empty((tokens.size, n_embd), dtype=np.float32)
+        fn = getattr(self.L, "krk_oracle_embed", None) or self.L.krk_ref_embed
+        fn(out, table.reshape(-1), wt, n_vocab, n_embd, tokens.reshape(-1), tokens.size)
+        return out
+
+    def logits_topk(self, logits, k, pen_mask=None, rep_pen=1.0, softcap=0.0, temp=1.0):
+        logits = _c(logits, np.float32).reshape(-1)
+        ids = np.empty(k, dtype=np.int32)
+        vals = np.empty(k, dtype=np.float32)
+        mass = np.empty(1, dtype=np.float32)
+        pm = None if pen_mask is None else _c(pen_mask, np.uint32)
+        fn = getattr(self.L, "krk_oracle_logits_topk", None) or self.L.krk_ref_logits_topk
+        fn(logits, logits.size, k, None if pm is None else pm.ctypes.data_as(C.c_void_p), rep_pen, softcap, temp, ids, vals, mass)
+        return ids, vals, float(mass[0])
 
     def silu_mul(self, gate, up):
         gate = _c(gate, np.float32)
@@ -165,6 +185,11 @@ class Reference:
         L.krk_ref_silu_mul.restype = None
         L.krk_ref_scatter_axpy_rows.argtypes = [_f32p, _f32p, _i32p, _f32p, C.c_int64, C.c_int64]
         L.krk_ref_scatter_axpy_rows.restype = None
+        L.krk_ref_embed.argtypes = [_f32p, _u8p, C.c_int, C.c_int64, C.c_int64, _i32p, C.c_int64]
+        L.krk_ref_embed.restype = None
+        L.krk_ref_logits_topk.argtypes = [_f32p, C.c_int64, C.c_int, C.c_void_p, C.c_float, C.c_float, C.c_float, _i32p, _f32p,
+                                          _f32p]
+        L.krk_ref_logits_topk.restype = None
         self.L = L
 
     @staticmethod
@@ -205,6 +230,23 @@ class Reference:
         out = np.empty((rows, n_out), dtype=np.float32)
         self.L.krk_ref_gemm(out.reshape(-1), x, w, wt, n_out, n_in, rows, tier)
         return out
+
+    def embed(self, table, wt, n_vocab, n_embd, tokens):
+        table, tokens = _c(table, np.uint8), _c(tokens, np.int32)
+        out = np.empty((tokens.size, n_embd), dtype=np.float32)
+        fn = getattr(self.L, "krk_oracle_embed", None) or self.L.krk_ref_embed
+        fn(out, table.reshape(-1), wt, n_vocab, n_embd, tokens.reshape(-1), tokens.size)
+        return out
+
+    def logits_topk(self, logits, k, pen_mask=None, rep_pen=1.0, softcap=0.0, temp=1.0):
+        logits = _c(logits, np.float32).reshape(-1)
+        ids = np.empty(k, dtype=np.int32)
+        vals = np.empty(k, dtype=np.float32)
+        mass = np.empty(1, dtype=np.float32)
+        pm = None if pen_mask is None else _c(pen_mask, np.uint32)
+        fn = getattr(self.L, "krk_oracle_logits_topk", None) or self.L.krk_ref_logits_topk
+        fn(logits, logits.size, k, None if pm is None else pm.ctypes.data_as(C.c_void_p), rep_pen, softcap, temp, ids, vals, mass)
+        return ids, vals, float(mass[0])
 
     def silu_mul(self, gate, up):
         gate = _c(gate, np.float32)

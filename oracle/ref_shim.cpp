@@ -96,6 +96,18 @@ void krk_ref_scatter_axpy_rows(float *dst, const float *src, const int32_t *rows
     cpu_backend()->scatter_axpy_rows(dst, src, rows, alpha, n_rows, n);
 }
 
+// CpuBackend::embed (src/backend_cpu.cpp:746-778) and CpuBackend::logits_topk (:862-912).
+void krk_ref_embed(float *out, const void *table, int wt, int64_t n_vocab, int64_t n_embd,
+                   const int32_t *tokens, int64_t n_tok) {
+    cpu_backend()->embed(out, table, static_cast<krk::DType>(wt), n_vocab, n_embd, tokens, n_tok);
+}
+
+void krk_ref_logits_topk(const float *logits, int64_t n, int k, const uint32_t *pen_mask, float rep_pen,
+                         float softcap, float temp, int32_t *ids, float *vals, float *mass_out) {
+    int64_t count = 0;
+    cpu_backend()->logits_topk(logits, n, k, pen_mask, rep_pen, softcap, temp, ids, vals, mass_out, nullptr, 0, &count);
+}
+
 // Bit 0: int8 tier on by default; bit 1: four-lane order; bit 2: fused AVX2; bit 3: wide.
 int krk_ref_default_tiers(void) {
     const TierDefaults &d = tier_defaults();

@@ -6,7 +6,7 @@ Run in a container where the reference tree is mounted (it cannot travel):
 
 Every array stored here was produced by oracle/_ref/libkrk_ref.so, i.e. by the reference's
 unmodified sources (krk::dequant_row, CpuBackend::gemm with the three lossy/reordered tiers
-switched off, CpuBackend::silu_mul / scatter_axpy_rows); the inputs are the seeded synthetic
+switched off, CpuBackend::silu_mul / scatter_axpy_rows / embed / logits_topk); the inputs are the seeded synthetic
 blocks of kraken_b200.synth plus the hand-built blocks of the reference's known-answer tests
 (tests/test_kraken.cpp:456-469, 563-573, 981-1001, 1026-1042). Nothing under /root/reference is
 read by the tests themselves: they read only the .npz files.
@@ -86,6 +86,24 @@ def main():
     alpha = np.array([0.25, 1.0, -1.5], np.float32)
     data["scatter_dst"], data["scatter_src"], data["scatter_rows"], data["scatter_alpha"] = dst.copy(), src, rows, alpha
     data["scatter_out"] = ref.scatter_axpy_rows(dst, src, rows, alpha)
+    # the steps either side of the head: embedding gather (bad ids give zero rows) and top-k of a logits row
+    for wt in SHAPES:
+        name = synth.NAMES[wt].lower()
+        table = synth.weights(wt, 40, 512, SEED, stream=900 + wt)
+        toks = np.array([3, 39, -1, 40, 0, 17, 3], np.int32)
+        data[f"embed_{name}_table"], data[f"embed_{name}_tokens"] = table, toks
+        data[f"embed_{name}_out"] = ref.embed(table, wt, 40, 512, toks)
+    lg = synth.normal(5000, SEED, 904) * 4.0
+    lg[100] = lg[4000] = lg.max() + 1.0           # an exact tie at the top: the lower id first
+    pm = np.zeros((5000 + 31) // 32, np.uint32)
+    pm[3], pm[125] = 0xFFFF00FF, 0x00000101        # ids 96..103, 112..127, 4000, 4008 are penalised
+    data["topk_logits"], data["topk_mask"] = lg, pm
+    for tag, (k, cap, pen, temp) in {"a": (1, 0.0, 1.0, 1.0), "b": (8, 3.0, 1.3, 0.7), "c": (64, 0.0, 1.1, 1.0)}.items():
+        ids, vals, mass = ref.logits_topk(lg, k, pm, pen, cap, temp)
+        data[f"topk_{tag}_args"] = np.array([k, cap, pen, temp], np.float32)
+        data[f"topk_{tag}_ids"], data[f"topk_{tag}_vals"], data[f"topk_{tag}_mass"] = ids, vals, np.float32(mass)
+    ids, vals, _ = ref.logits_topk(lg[:5], 8)      # fewer elements than k: -1 / -FLT_MAX markers
+    data["topk_short_ids"], data["topk_short_vals"] = ids, vals
     np.savez_compressed(os.path.join(OUT, "reference_vectors.npz"), **data)
     print("wrote", os.path.join(OUT, "reference_vectors.npz"),
           os.path.getsize(os.path.join(OUT, "reference_vectors.npz")), "bytes")

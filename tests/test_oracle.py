@@ -61,6 +61,25 @@ def test_silu_and_scatter(oracle, golden):
     assert dst.tobytes() == golden["scatter_out"].tobytes()
 
 
+def test_embed_and_topk_match_reference_vectors(oracle, golden):
+    for wt in FMTS:
+        name = synth.NAMES[wt].lower()
+        out = oracle.embed(golden[f"embed_{name}_table"], wt, 40, 512, golden[f"embed_{name}_tokens"])
+        assert out.tobytes() == golden[f"embed_{name}_out"].tobytes()
+        assert not out[2].any() and not out[3].any()                    # ids -1 and 40: zero rows
+    lg, pm = golden["topk_logits"], golden["topk_mask"]
+    for tag in "abc":
+        k, cap, pen, temp = golden[f"topk_{tag}_args"]
+        ids, vals, mass = oracle.logits_topk(lg, int(k), pm, float(pen), float(cap), float(temp))
+        assert np.array_equal(ids, golden[f"topk_{tag}_ids"])
+        assert vals.tobytes() == golden[f"topk_{tag}_vals"].tobytes()
+        assert np.float32(mass) == golden[f"topk_{tag}_mass"]
+    assert golden["topk_a_ids"][0] == 100                               # the tie goes to the lower id
+    ids, vals, _ = oracle.logits_topk(lg[:5], 8)
+    assert np.array_equal(ids, golden["topk_short_ids"]) and ids[5] == -1
+    assert vals.tobytes() == golden["topk_short_vals"].tobytes()
+
+
 def test_refusals(oracle):
     w = np.zeros(144, np.uint8)
     with pytest.raises(ValueError):
@@ -128,3 +147,8 @@ def test_oracle_equals_compiled_reference_live(oracle, reference, wt):
     assert oracle.gemm(x, w, wt, n_rows, n_in, rows=2).tobytes() == \
         reference.gemm(x, w, wt, n_rows, n_in, rows=2, tier=0).tobytes()
     assert np.float32(reference.vec_dot(wt, w[0], x[0])) == oracle.gemm(x[0], w[:1], wt, 1, n_in)[0, 0]
+    toks = np.array([0, 32, 7, 33, -5], np.int32)
+    assert oracle.embed(w, wt, n_rows, n_in, toks).tobytes() == reference.embed(w, wt, n_rows, n_in, toks).tobytes()
+    lg = synth.normal(3000, 20261125, 40 + wt) * 3.0
+    a, b = oracle.logits_topk(lg, 16, None, 1.0, 2.5, 0.8), reference.logits_topk(lg, 16, None, 1.0, 2.5, 0.8)
+    assert np.array_equal(a[0], b[0]) and a[1].tobytes() == b[1].tobytes() and a[2] == b[2]
