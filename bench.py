@@ -212,10 +212,24 @@ def run_ours(args):
         layers.append(mats)
     stream = torch.cuda.current_stream()
 
+    # Gate and up read the same activation row and leave in ONE grouped launch, which is how Kraken's engine
+    # issues them (Backend::gemm_group, include/krk/backend.hpp:1040-1056); --ungrouped launches all four apart.
+    grouped = not args.ungrouped
+    assert LAYER_SHAPES[1] == LAYER_SHAPES[2]
+
+    def launch_layer(mats, st):
+        (w0, x0, y0, n0, k0), (wg, xg, yg, ng, kg), (wu, _, yu, nu, _), (wd, xd, yd, nd, kd) = mats
+        capi.gemv(x0, w0, WT, n0, k0, out=y0.view(1, -1), stream=st)
+        if grouped:
+            capi.gemv_group([xg, xg], [wg, wu], [WT, WT], [ng, nu], kg, outs=[yg, yu], stream=st)
+        else:
+            capi.gemv(xg, wg, WT, ng, kg, out=yg.view(1, -1), stream=st)
+            capi.gemv(xg, wu, WT, nu, kg, out=yu.view(1, -1), stream=st)
+        capi.gemv(xd, wd, WT, nd, kd, out=yd.view(1, -1), stream=st)
+
     def step():
         for mats in layers:
-            for w, x, y, n_out, n_in in mats:
-                capi.gemv(x, w, WT, n_out, n_in, out=y.view(1, -1), stream=stream)
+            launch_layer(mats, stream)
 
     def barrier():
         torch.cuda.synchronize()
@@ -231,7 +245,7 @@ def run_ours(args):
 
     # The step's launches are captured once into a CUDA graph and replayed: same kernels, same
     # order, without a host round trip per launch (a decode loop replays a fixed launch sequence).
-    launches_per_step = 4 * args.layers
+    launches_per_step = (3 if grouped else 4) * args.layers
     replay = step
     graph_holder = []
     if not args.no_graph:
@@ -242,8 +256,7 @@ def run_ours(args):
         with torch.cuda.stream(cap_stream):
             graph.capture_begin()
             for mats in layers:
-                for w, x, y, n_out, n_in in mats:
-                    capi.gemv(x, w, WT, n_out, n_in, out=y.view(1, -1), stream=cap_stream)
+                launch_layer(mats, cap_stream)
             graph.capture_end()
         launches_per_step = capi.launch_count() - c0
         stream = cap_stream
@@ -289,10 +302,21 @@ def run_ours(args):
         be.upload(d_x, x_host.data_ptr(), x_host.numel() * 4)
         xo = yo = 0
         for mats in layers:
-            for w, _, _, n_out, n_in in mats:
+            i = 0
+            while i < len(mats):
+                w, _, _, n_out, n_in = mats[i]
+                if grouped and i == 1:      # gate and up: one gemm_group call on the gate's activation row
+                    wu = mats[2][0]
+                    be.gemm_group([d_y + 4 * yo, d_y + 4 * (yo + n_out)], d_x + 4 * xo, [w.data_ptr(), wu.data_ptr()], WT,
+                                  [n_out, n_out], n_in, 1)
+                    xo += 2 * n_in
+                    yo += 2 * n_out
+                    i += 2
+                    continue
                 be.gemm(d_y + 4 * yo, d_x + 4 * xo, w.data_ptr(), WT, n_out, n_in, 1)
                 xo += n_in
                 yo += n_out
+                i += 1
         be.download(y_host.data_ptr(), d_y, y_host.numel() * 4)      # synchronises
 
     e2e_steps = 0 if args.no_e2e else args.steps
@@ -339,6 +363,8 @@ def run_ours(args):
                        "matmuls_per_layer": [list(s) for s in LAYER_SHAPES],
                        "weight_bytes_per_step": wbytes, "parallelism": f"replicas x{world}",
                        "launch": "host launches" if args.no_graph else "CUDA graph replay of the step's launches",
+                       "launches_per_layer": ("3: gemm(4096x4096), gemm_group(gate, up), gemm(4096x11008) - the engine's call pattern"
+                                              if grouped else "4: one gemm per matrix"),
                        "l2": "inputs larger than L2: 2.74 GB of distinct weights per step, each byte read once"},
             "e2e": {"value": round(wbytes * world / (e2e_ms / args.steps * 1e-3) / 1e9, 2), "unit": UNIT,
                     "h2d_bytes_per_step": x_host.numel() * 4, "d2h_bytes_per_step": y_host.numel() * 4,
@@ -347,7 +373,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "kernel": "gemv_stream_kernel<Q4_K,1>", "achieved": round(achieved, 2),
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
                          "launches_per_step": n_launch, "avg_launch_us": round(per_step_ms * 1e3 / n_launch, 3),
-                         "algorithmic_bytes_per_launch": abytes // n_launch, "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+                         "algorithmic_bytes_per_launch": abytes // n_launch, "traffic": (TRAFFIC_BYTES_PER_LAYER_GROUPED if grouped else TRAFFIC_BYTES_PER_LAYER) // (n_launch // args.layers),
                          "frac_of_spec_8000_gbs": round(achieved / 8000.0, 4)},
             "clocks": clocks,
         }
@@ -610,9 +636,11 @@ def prefill_extra(torch, capi, gen):
             "results": out}
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the streaming kernel (mean over the four
-# launch shapes of a layer), from the ncu capture summarised in profiles/gemv_stream_q4k_llama7b_layer.md.
-TRAFFIC_BYTES_PER_LAUNCH = 21467136
+# dram__bytes_read.sum + dram__bytes_write.sum of the streaming kernel over the launches of one layer, from the
+# ncu capture summarised in profiles/gemv_stream_q4k_llama7b_layer.md; the bench line divides it by the launches
+# per layer.
+TRAFFIC_BYTES_PER_LAYER = 85868544            # four launches: 9,516,288 + 25,441,280 + 25,441,792 + 25,469,184
+TRAFFIC_BYTES_PER_LAYER_GROUPED = 85795328    # three launches: 9,521,408 + 50,804,480 (gate and up) + 25,469,440
 
 
 # ---- CPU arms ---------------------------------------------------------------------------------------
@@ -727,6 +755,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip every side measurement")
     ap.add_argument("--extras", default="prefill,decode,sharded",
                     help="side measurements to run: any of prefill,decode,sharded (profiling runs pick one)")
+    ap.add_argument("--ungrouped", action="store_true", help="launch gate and up apart (four launches per layer instead of three)")
     ap.add_argument("--no-graph", action="store_true", help="launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--layers", type=int, default=N_LAYERS,
                     help="layers per step; fewer than 32 is for profiler captures only, not a bench value")
