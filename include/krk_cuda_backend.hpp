@@ -3,7 +3,7 @@
 // quantized-weight matmul needs, with the same member names, argument meaning and error
 // behaviour, implemented on the C ABI of krk_cuda.h.
 //
-// In a Kraken tree this class derives from krk::Backend; here it
+// In a Kraken tree this class derives from krk::Backend (add the base class and `override`); here it
 // stands alone so that it compiles without the reference's headers. All pointers handed to
 // the ops are device pointers obtained from alloc(); the caller owns their lifetime
 // (include/krk/backend.hpp:361-362). Ops are enqueued on one stream, asynchronous and

@@ -8,7 +8,7 @@ Every array stored here was produced by oracle/_ref/libkrk_ref.so, i.e. by the r
 unmodified sources (krk::dequant_row, CpuBackend::gemm with the three lossy/reordered tiers
 switched off, CpuBackend::silu_mul / scatter_axpy_rows / embed / logits_topk); the inputs are the seeded synthetic
 blocks of kraken_b200.synth plus the hand-built blocks of the reference's known-answer tests
-(tests/test_kraken.cpp:456-469, 563-573, 981-1001, 1026-1042). Nothing under /root/reference is
+(tests/test_kraken.cpp:456-469, 563-573, 981-1001, 1026-1042). Nothing under the reference tree is
 read by the tests themselves: they read only the .npz files.
 """
 from __future__ import annotations
