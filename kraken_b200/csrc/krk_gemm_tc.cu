@@ -18,9 +18,9 @@
 //                super-blocks arrive in shared memory by TMA (a 2-D tensor map over the raw byte
 //                matrix, box = 144 bytes x 128 rows, three super-blocks ahead); other formats are
 //                read from global memory element-wise. 16 x 32-bit TMEM columns per thread and step;
-//   warps 8..11  epilogue: tcgen05.ld of the accumulator (warp w%4 owns TMEM lanes 32*(w%4)..), f32
-//                stores of Y;
-//   warp 12      TMA producer of X tiles (cp.async.bulk.tensor.2d, no multicast);
+//   warps 8..11  epilogue: tcgen05.ld of the accumulator (warp w%4 owns TMEM lanes 32*(w%4)..), 32 tokens
+//                at a time into a [token][weight row] staging buffer in shared memory, TMA stores of Y;
+//   warp 12      TMA producer of X tiles (cp.async.bulk.tensor.2d, each CTA loads its own copy);
 //   warp 13      TMA producer of raw Q4_K super-block columns;
 //   warp 14      TMEM allocation and the single thread that issues tcgen05.mma / tcgen05.commit.
 // Tensor memory: columns 0..255 the accumulator, 256..511 eight A stages of 32 columns.
