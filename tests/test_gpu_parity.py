@@ -350,3 +350,56 @@ def test_backend_host_buffers_roundtrip(cuda, oracle):
     for p in (d_w, d_x, d_y, d_y2):
         be.release(p)
     be.close()
+
+
+def test_decode_layer_matmuls_through_backend(cuda, oracle):
+    """The matmuls of one decode layer as Kraken's engine issues them on a backend (include/krk/backend.hpp:
+    858-900, 1040-1056): q/k/v in one gemm_group, the attention output folded into the residual with
+    gemm_accumulate, gate/up in one gemm_group with the silu fold, the down projection folded into the
+    residual. Mixed formats as in a Q4_K_M file (Q4_K projections, Q6_K value and down). Attention itself is
+    out of scope: q stands in for its output. Checked against the oracle's composition of the same steps."""
+    be = cuda.Backend(0)
+    n_embd, n_ff, n_kv = 1024, 2816, 256
+    seed = SEED + 21
+    mk = lambda wt, n, k, st: synth.weights(wt, n, k, seed, stream=st)
+    wq, wk = mk(synth.Q4_K, n_embd, n_embd, 1), mk(synth.Q4_K, n_kv, n_embd, 2)
+    wv, wo = mk(synth.Q6_K, n_kv, n_embd, 3), mk(synth.Q4_K, n_embd, n_embd, 4)
+    wg, wu = mk(synth.Q4_K, n_ff, n_embd, 5), mk(synth.Q4_K, n_ff, n_embd, 6)
+    wd = mk(synth.Q6_K, n_embd, n_ff, 7)
+    x = synth.activations(1, n_embd, seed)
+    resid0 = synth.activations(1, n_embd, seed, stream=9)
+
+    def up(a):
+        p = be.alloc(a.nbytes)
+        be.upload(p, a.ctypes.data, a.nbytes)
+        return p
+
+    def down(p, n):
+        out = np.empty(n, np.float32)
+        be.download(out.ctypes.data, p, out.nbytes)
+        return out
+
+    d = {k: up(v) for k, v in dict(wq=wq, wk=wk, wv=wv, wo=wo, wg=wg, wu=wu, wd=wd, x=x, resid=resid0).items()}
+    d_q, d_k, d_v, d_h, d_u = (be.alloc(4 * n) for n in (n_embd, n_kv, n_kv, n_ff, n_ff))
+    # q, k (same type) in one group; v has another type, so it goes alone, as Backend::gemm_group's `wt` asks
+    ran, _ = be.gemm_group([d_q, d_k], d["x"], [d["wq"], d["wk"]], synth.Q4_K, [n_embd, n_kv], n_embd, rows=1)
+    assert ran
+    be.gemm(d_v, d["x"], d["wv"], synth.Q6_K, n_kv, n_embd, 1)
+    assert be.gemm_accumulate(d["resid"], d_q, d["wo"], synth.Q4_K, n_embd, n_embd, 1)       # resid += Wo . attn
+    ran, fused = be.gemm_group([d_h, d_u], d["resid"], [d["wg"], d["wu"]], synth.Q4_K, [n_ff, n_ff], n_embd, rows=1, silu=True)
+    assert ran and fused                                                                   # h = silu(Wg r) * (Wu r)
+    assert be.gemm_accumulate(d["resid"], d_h, d["wd"], synth.Q6_K, n_embd, n_ff, 1)          # resid += Wd . h
+
+    g = lambda xx, w, wt, n, k: oracle.gemm(xx, w, wt, n, k, rows=1, threads=8)
+    q_ref, k_ref, v_ref = g(x, wq, synth.Q4_K, n_embd, n_embd), g(x, wk, synth.Q4_K, n_kv, n_embd), g(x, wv, synth.Q6_K, n_kv, n_embd)
+    r1 = resid0 + g(q_ref, wo, synth.Q4_K, n_embd, n_embd)
+    h_ref = oracle.silu_mul(g(r1, wg, synth.Q4_K, n_ff, n_embd)[0], g(r1, wu, synth.Q4_K, n_ff, n_embd)[0])[None, :]
+    r2 = r1 + g(h_ref, wd, synth.Q6_K, n_embd, n_ff)
+    for name, got, want in (("q", down(d_q, n_embd), q_ref[0]), ("k", down(d_k, n_kv), k_ref[0]), ("v", down(d_v, n_kv), v_ref[0]),
+                            ("h", down(d_h, n_ff), h_ref[0]), ("resid", down(d["resid"], n_embd), r2[0])):
+        rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+        assert rel < 2e-5, f"{name}: relative L2 error {rel:.2e}"
+    assert cuda.device_status() == 0
+    for p in list(d.values()) + [d_q, d_k, d_v, d_h, d_u]:
+        be.release(p)
+    be.close()
