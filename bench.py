@@ -404,11 +404,13 @@ def device_weights_q6k(torch, n_out: int, n_in: int, gen):
     return w.view(n_out, nblk * 210)
 
 
-def timed(torch, fn, reps, barrier, variants=0):
+def timed(torch, fn, reps, barrier, variants=0, chain=False):
     """Device time per call of fn(i), events on the launching stream, after warm-up calls. With
     `variants` > 0 the calls fn(0..variants-1) are captured once each into CUDA graphs (kernels and, on
     several GPUs, the NCCL collective) and the graphs are replayed in turn: a decode loop replays a fixed
-    launch sequence, and a latency-bound collective should not pay a host launch per token."""
+    launch sequence, and a latency-bound collective should not pay a host launch per token. With `chain` the
+    calls are captured into ONE graph, back to back as a decode loop issues them, so that consecutive launches
+    overlap their boundaries (programmatic dependent launch) as they do in the main measurement."""
     for i in range(max(3, variants)):
         fn(i)
     barrier()
@@ -419,19 +421,29 @@ def timed(torch, fn, reps, barrier, variants=0):
         cap.wait_stream(stream)
         graphs = []
         with torch.cuda.stream(cap):
-            for v in range(variants):
+            if chain:
                 g = torch.cuda.CUDAGraph()
                 g.capture_begin()
-                fn(v)
+                for v in range(variants):
+                    fn(v)
                 g.capture_end()
                 graphs.append(g)
+            else:
+                for v in range(variants):
+                    g = torch.cuda.CUDAGraph()
+                    g.capture_begin()
+                    fn(v)
+                    g.capture_end()
+                    graphs.append(g)
             for g in graphs:
                 g.replay()
         barrier()
         stream = cap
+        if chain:
+            reps = max(1, reps // variants)
 
         def run(i):
-            graphs[i % variants].replay()
+            graphs[i % len(graphs)].replay()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         e0.record(stream)
@@ -439,7 +451,7 @@ def timed(torch, fn, reps, barrier, variants=0):
             run(i)
         e1.record(stream)
     barrier()
-    return e0.elapsed_time(e1) / reps
+    return e0.elapsed_time(e1) / (reps * (variants if chain and variants > 0 else 1))
 
 
 def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
@@ -573,7 +585,7 @@ def decode_extra(torch, capi, gen, barrier):
 
         def call(i):
             capi.gemv(x, ws[i % n_rep], wt, n_out, n_in, out=y)
-        ms = timed(torch, call, 20 * n_rep, barrier, variants=n_rep)
+        ms = timed(torch, call, 20 * n_rep, barrier, variants=n_rep, chain=True)
         abytes = wbytes + 4 * n_in + 4 * n_out
         out[name] = {"us_per_launch": round(ms * 1e3, 3), "algorithmic_gbps": round(abytes / (ms * 1e-3) / 1e9, 1),
                      "frac_of_measured_hbm": round(abytes / (ms * 1e-3) / 1e9 / peak, 4),
