@@ -22,7 +22,7 @@ using i64 = int64_t;
 using f32 = float;
 
 // GGUF on-disk ids, the values of krk::DType (include/krk/quant.hpp:16-30).
-enum class DType : int { F32 = 0, F16 = 1, Q4_0 = 2, Q8_0 = 8, Q4_K = 12, Q6_K = 14 };
+enum class DType : int { F32 = 0, F16 = 1, Q4_0 = 2, Q5_0 = 6, Q5_1 = 7, Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14 };
 
 class CudaBackend {
 public:

@@ -14,6 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libkrk_cuda.so")
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
+Q5_0, Q5_1, Q5_K = 6, 7, 13
 X_F32, X_F16 = 0, 1
 MAX_GROUP, MAX_ROWS = 16, 8
 

@@ -62,6 +62,17 @@ __device__ __forceinline__ void decode_chunk<KRK_CUDA_Q6_K>(const uint8_t *row, 
     }
 }
 
+// The 5-bit formats decode element by element (they ride the shape-agnostic kernels only).
+#define KRK_CHUNK_BY_ELEMENT(WT_)                                                                                        \
+    template <>                                                                                                          \
+    __device__ __forceinline__ void decode_chunk<WT_>(const uint8_t *row, int64_t c, float (&v)[32]) {                    \
+        _Pragma("unroll") for (int k = 0; k < 32; k++) v[k] = decode_value<WT_>(row, c * 32 + k);                          \
+    }
+KRK_CHUNK_BY_ELEMENT(KRK_CUDA_Q5_0)
+KRK_CHUNK_BY_ELEMENT(KRK_CUDA_Q5_1)
+KRK_CHUNK_BY_ELEMENT(KRK_CUDA_Q5_K)
+#undef KRK_CHUNK_BY_ELEMENT
+
 // Dot of chunk c of a weight row with the matching 32 activations (x 16-byte aligned).
 template <int WT>
 __device__ __forceinline__ float chunk_dot(const uint8_t *row, int64_t c, const float *x) {

@@ -29,12 +29,13 @@ inline int check_launch() {
 // ---- geometry (src/quant.cpp:1805-1900) ----------------------------------------------
 
 __host__ __device__ constexpr int block_size(int wt) {
-    return (wt == KRK_CUDA_Q8_0 || wt == KRK_CUDA_Q4_0) ? 32
-           : (wt == KRK_CUDA_Q4_K || wt == KRK_CUDA_Q6_K) ? 256 : 0;
+    return (wt == KRK_CUDA_Q8_0 || wt == KRK_CUDA_Q4_0 || wt == KRK_CUDA_Q5_0 || wt == KRK_CUDA_Q5_1) ? 32
+           : (wt == KRK_CUDA_Q4_K || wt == KRK_CUDA_Q6_K || wt == KRK_CUDA_Q5_K) ? 256 : 0;
 }
 __host__ __device__ constexpr int block_bytes(int wt) {
     return wt == KRK_CUDA_Q8_0 ? 34 : wt == KRK_CUDA_Q4_0 ? 18 : wt == KRK_CUDA_Q4_K ? 144
-           : wt == KRK_CUDA_Q6_K ? 210 : 0;
+           : wt == KRK_CUDA_Q6_K ? 210 : wt == KRK_CUDA_Q5_0 ? 22 : wt == KRK_CUDA_Q5_1 ? 24
+           : wt == KRK_CUDA_Q5_K ? 176 : 0;
 }
 __host__ __device__ inline size_t row_bytes(int wt, int64_t n_in) {
     const int bs = block_size(wt);
@@ -108,6 +109,42 @@ __device__ __forceinline__ float decode_value<KRK_CUDA_Q6_K>(const uint8_t *row,
     return __fmul_rn(__fmul_rn(half_bits_to_float(b + 208), (float)sc), (float)(q - 32));
 }
 
+// src/quant.cpp:352-364: 4 low bits in the nibbles, the fifth in the 32-bit mask after the scale
+template <>
+__device__ __forceinline__ float decode_value<KRK_CUDA_Q5_0>(const uint8_t *row, int64_t k) {
+    const uint8_t *b = row + (k >> 5) * 22;
+    const int j = (int)(k & 31);
+    const uint32_t qh = (uint32_t)b[2] | ((uint32_t)b[3] << 8) | ((uint32_t)b[4] << 16) | ((uint32_t)b[5] << 24);
+    const int lo4 = j < 16 ? (b[6 + j] & 0xF) : (b[6 + j - 16] >> 4);
+    const int q = lo4 | (int)(((qh >> j) & 1u) << 4);
+    return __fmul_rn(half_bits_to_float(b), (float)(q - 16));
+}
+
+// src/quant.cpp:366-379: as Q5_0 with an unsigned quant and a per-block offset m: d * q + m
+template <>
+__device__ __forceinline__ float decode_value<KRK_CUDA_Q5_1>(const uint8_t *row, int64_t k) {
+    const uint8_t *b = row + (k >> 5) * 24;
+    const int j = (int)(k & 31);
+    const uint32_t qh = (uint32_t)b[4] | ((uint32_t)b[5] << 8) | ((uint32_t)b[6] << 16) | ((uint32_t)b[7] << 24);
+    const int lo4 = j < 16 ? (b[8 + j] & 0xF) : (b[8 + j - 16] >> 4);
+    const int q = lo4 | (int)(((qh >> j) & 1u) << 4);
+    return __fadd_rn(__fmul_rn(half_bits_to_float(b), (float)q), half_bits_to_float(b + 2));
+}
+
+// src/quant.cpp:462-489: Q4_K's scales and mins, a fifth quant bit per value in 32 bytes of masks
+template <>
+__device__ __forceinline__ float decode_value<KRK_CUDA_Q5_K>(const uint8_t *row, int64_t k) {
+    const uint8_t *b = row + (k >> 8) * 176;
+    const int e = (int)(k & 255), c = e >> 5, l = e & 31;
+    const uint8_t byte = b[48 + 32 * (c >> 1) + l];
+    const int q = ((c & 1) ? (byte >> 4) : (byte & 0xF)) + (((b[16 + l] >> c) & 1) ? 16 : 0);
+    int sc, mn;
+    scale_min_k4(c, b + 4, sc, mn);
+    const float dl = __fmul_rn(half_bits_to_float(b), (float)sc);
+    const float ml = __fmul_rn(half_bits_to_float(b + 2), (float)mn);
+    return __fsub_rn(__fmul_rn(dl, (float)q), ml);
+}
+
 // Runs the statement(s) with `WT` bound to the compile-time weight type matching `wt`
 // (kernels are specialised per format; there is no runtime type switch on the device).
 #define KRK_DISPATCH_WT(wt, ...)                                                        \
@@ -116,6 +153,9 @@ __device__ __forceinline__ float decode_value<KRK_CUDA_Q6_K>(const uint8_t *row,
     case KRK_CUDA_Q4_0: { constexpr int WT = KRK_CUDA_Q4_0; __VA_ARGS__; } break;       \
     case KRK_CUDA_Q4_K: { constexpr int WT = KRK_CUDA_Q4_K; __VA_ARGS__; } break;       \
     case KRK_CUDA_Q6_K: { constexpr int WT = KRK_CUDA_Q6_K; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q5_0: { constexpr int WT = KRK_CUDA_Q5_0; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q5_1: { constexpr int WT = KRK_CUDA_Q5_1; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q5_K: { constexpr int WT = KRK_CUDA_Q5_K; __VA_ARGS__; } break;       \
     default: break;                                                                     \
     }
 

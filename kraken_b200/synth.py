@@ -21,12 +21,14 @@ from __future__ import annotations
 import numpy as np
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
+Q5_0, Q5_1, Q5_K = 6, 7, 13          # the further formats of mixed files (shape-agnostic kernels only)
 FORMATS = (Q8_0, Q4_0, Q4_K, Q6_K)
-NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K"}
-BLOCK_SIZE = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256}
-BLOCK_BYTES = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210}
+MORE_FORMATS = (Q5_0, Q5_1, Q5_K)
+NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K", Q5_0: "Q5_0", Q5_1: "Q5_1", Q5_K: "Q5_K"}
+BLOCK_SIZE = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256, Q5_0: 32, Q5_1: 32, Q5_K: 256}
+BLOCK_BYTES = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210, Q5_0: 22, Q5_1: 24, Q5_K: 176}
 # 64-bit words of randomness drawn per block
-_WORDS = {Q4_0: 3, Q8_0: 9, Q4_K: 19, Q6_K: 27}
+_WORDS = {Q4_0: 3, Q8_0: 9, Q4_K: 19, Q6_K: 27, Q5_0: 4, Q5_1: 4, Q5_K: 23}
 
 _GOLDEN = np.uint64(0x9E3779B97F4A7C15)
 _M1 = np.uint64(0xBF58476D1CE4E5B9)
@@ -131,6 +133,22 @@ def weights(wt: int, n_rows: int, n_in: int, seed: int, stream: int = 0, row_beg
         else:
             blocks[..., 192:208] = ((by[..., 192:208] & 127).astype(np.int16) - 64).astype(np.int8).view(np.uint8)
         _put_u16(blocks, 208, _f16_bits(1e-4, 2e-3, u_lo))
+    elif wt == Q5_0:      # d, 4 bytes of fifth bits, 16 bytes of nibbles: every payload byte uniform
+        _put_u16(blocks, 0, _f16_bits(1e-3, 2e-2, u_lo))
+        blocks[..., 2:22] = by[..., 0:20]
+    elif wt == Q5_1:      # d, offset m, fifth bits, nibbles
+        _put_u16(blocks, 0, _f16_bits(1e-3, 2e-2, u_lo))
+        _put_u16(blocks, 2, _f16_bits(-0.2, 0.2, u_hi))
+        blocks[..., 4:24] = by[..., 0:20]
+    elif wt == Q5_K:      # d, dmin, 12 packed scale bytes, 32 bytes of fifth bits, 128 bytes of nibbles
+        _put_u16(blocks, 0, _f16_bits(1e-3, 1e-2, u_lo))
+        _put_u16(blocks, 2, _f16_bits(0.0, 5e-3, u_hi))
+        if random_payload:
+            blocks[..., 4:16] = by[..., 160:172]
+        else:
+            six = by[..., 160:176] & 63
+            blocks[..., 4:16] = pack_scales_k4(six[..., 0:8], six[..., 8:16])
+        blocks[..., 16:176] = by[..., 0:160]
     else:
         raise ValueError(f"unsupported weight type {wt}")
     return blocks.reshape(n_rows, nblk * BLOCK_BYTES[wt])

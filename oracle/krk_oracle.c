@@ -22,8 +22,11 @@
 int krk_oracle_block_size(int wt) {
     switch (wt) {
     case KRK_ORACLE_Q4_0:
+    case KRK_ORACLE_Q5_0:
+    case KRK_ORACLE_Q5_1:
     case KRK_ORACLE_Q8_0: return 32;
     case KRK_ORACLE_Q4_K:
+    case KRK_ORACLE_Q5_K:
     case KRK_ORACLE_Q6_K: return 256;
     default: return 0;
     }
@@ -35,6 +38,9 @@ int krk_oracle_block_bytes(int wt) {
     case KRK_ORACLE_Q8_0: return 34;
     case KRK_ORACLE_Q4_K: return 144;
     case KRK_ORACLE_Q6_K: return 210;
+    case KRK_ORACLE_Q5_0: return 22;
+    case KRK_ORACLE_Q5_1: return 24;
+    case KRK_ORACLE_Q5_K: return 176;
     default: return 0;
     }
 }
@@ -146,6 +152,49 @@ static void block_q6_k(const uint8_t *b, float *y) {
     }
 }
 
+/* src/quant.cpp:352-364 */
+static void block_q5_0(const uint8_t *b, float *y) {
+    const float d = half_at(b);
+    uint32_t qh;
+    memcpy(&qh, b + 2, 4);
+    for (int k = 0; k < 16; k++) {
+        const int lo = (b[6 + k] & 0xF) | (int)(((qh >> k) & 1u) << 4);
+        const int hi = (b[6 + k] >> 4) | (int)(((qh >> (k + 16)) & 1u) << 4);
+        y[k] = d * (float)(lo - 16);
+        y[k + 16] = d * (float)(hi - 16);
+    }
+}
+
+/* src/quant.cpp:366-379 */
+static void block_q5_1(const uint8_t *b, float *y) {
+    const float d = half_at(b), m = half_at(b + 2);
+    uint32_t qh;
+    memcpy(&qh, b + 4, 4);
+    for (int k = 0; k < 16; k++) {
+        const int lo = (b[8 + k] & 0xF) | (int)(((qh >> k) & 1u) << 4);
+        const int hi = (b[8 + k] >> 4) | (int)(((qh >> (k + 16)) & 1u) << 4);
+        y[k] = d * (float)lo + m;
+        y[k + 16] = d * (float)hi + m;
+    }
+}
+
+/* src/quant.cpp:462-489 */
+static void block_q5_k(const uint8_t *b, float *y) {
+    const float d = half_at(b), dmin = half_at(b + 2);
+    const uint8_t *scales = b + 4, *qh = b + 16, *q = b + 48;
+    for (int j = 0; j < 4; j++, q += 32, y += 64) {
+        int s0, m0, s1, m1;
+        scale_min_k4(2 * j, scales, &s0, &m0);
+        scale_min_k4(2 * j + 1, scales, &s1, &m1);
+        const float d1 = d * (float)s0, mm1 = dmin * (float)m0, d2 = d * (float)s1, mm2 = dmin * (float)m1;
+        const uint8_t u1 = (uint8_t)(1u << (2 * j)), u2 = (uint8_t)(2u << (2 * j));
+        for (int l = 0; l < 32; l++) {
+            y[l] = d1 * (float)((q[l] & 0xF) + ((qh[l] & u1) ? 16 : 0)) - mm1;
+            y[l + 32] = d2 * (float)((q[l] >> 4) + ((qh[l] & u2) ? 16 : 0)) - mm2;
+        }
+    }
+}
+
 /* src/quant.cpp:1553-1599 */
 static void decode_block(int wt, const uint8_t *b, float *y) {
     switch (wt) {
@@ -153,6 +202,9 @@ static void decode_block(int wt, const uint8_t *b, float *y) {
     case KRK_ORACLE_Q4_0: block_q4_0(b, y); break;
     case KRK_ORACLE_Q4_K: block_q4_k(b, y); break;
     case KRK_ORACLE_Q6_K: block_q6_k(b, y); break;
+    case KRK_ORACLE_Q5_0: block_q5_0(b, y); break;
+    case KRK_ORACLE_Q5_1: block_q5_1(b, y); break;
+    case KRK_ORACLE_Q5_K: block_q5_k(b, y); break;
     default: break;
     }
 }

@@ -29,10 +29,13 @@ enum {
     KRK_ORACLE_Q4_0 = 2,
     KRK_ORACLE_Q8_0 = 8,
     KRK_ORACLE_Q4_K = 12,
-    KRK_ORACLE_Q6_K = 14
+    KRK_ORACLE_Q6_K = 14,
+    KRK_ORACLE_Q5_0 = 6,
+    KRK_ORACLE_Q5_1 = 7,
+    KRK_ORACLE_Q5_K = 13
 };
 
-/* Geometry (src/quant.cpp:1805-1900). Return 0 for a type outside the four above. */
+/* Geometry (src/quant.cpp:1805-1900). Return 0 for a type outside those above. */
 int krk_oracle_block_size(int wt);
 int krk_oracle_block_bytes(int wt);
 size_t krk_oracle_row_bytes(int wt, int64_t n_in);

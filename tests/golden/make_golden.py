@@ -71,6 +71,14 @@ def main():
             data[f"{name}_{tag}_x"] = x
             data[f"{name}_{tag}_deq"] = ref.dequant_rows(w, wt, n_rows, n_in)
             data[f"{name}_{tag}_y"] = ref.gemm(x, w, wt, n_rows, n_in, rows=3, tier=0)
+    # the further formats of mixed files (decode and exact GEMM of random-payload blocks)
+    for wt in synth.MORE_FORMATS:
+        name = synth.NAMES[wt].lower()
+        w = synth.weights(wt, 5, 1024, SEED, stream=wt, random_payload=True)
+        x = synth.activations(2, 1024, SEED, stream=600 + wt)
+        data[f"{name}_bytes_w"], data[f"{name}_bytes_x"] = w, x
+        data[f"{name}_bytes_deq"] = ref.dequant_rows(w, wt, 5, 1024)
+        data[f"{name}_bytes_y"] = ref.gemm(x, w, wt, 5, 1024, rows=2, tier=0)
     for key, (wt, blk, n) in kat_blocks(ref).items():
         data[f"{key}_w"] = blk
         data[f"{key}_deq"] = ref.dequant_rows(blk, wt, 1, n)

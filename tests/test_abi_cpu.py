@@ -33,10 +33,11 @@ def test_geometry_matches_reference_tables():
     assert capi.row_bytes(capi.Q8_0, 64) == 68
     assert capi.row_bytes(capi.Q4_K, 4096) == 2304 and capi.row_bytes(capi.Q6_K, 4096) == 3360
     assert capi.row_bytes(capi.Q8_0, 4096) == 4352 and capi.row_bytes(capi.Q6_K, 1536) == 1260
-    for wt in synth.FORMATS:
+    for wt in synth.FORMATS + synth.MORE_FORMATS:
         assert capi.lib.krk_cuda_dtype_ok(wt) == 1
         assert capi.row_bytes(wt, 2048) == synth.row_bytes(wt, 2048)
-    for wt in (0, 1, 3, 13, 15, 99, -1):
+    assert capi.row_bytes(capi.Q5_0, 4096) == 2816 and capi.row_bytes(capi.Q5_K, 4096) == 2816 and capi.row_bytes(capi.Q5_1, 64) == 48
+    for wt in (0, 1, 3, 9, 10, 11, 15, 99, -1):
         assert capi.lib.krk_cuda_dtype_ok(wt) == 0 and capi.row_bytes(wt, 256) == 0
 
 
