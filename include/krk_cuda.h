@@ -63,7 +63,8 @@ const char *krk_cuda_strerror(int rc);
 /* Text of the last CUDA runtime error seen by this library on this thread ("" if none). */
 const char *krk_cuda_last_cuda_error(void);
 
-/* 1 if `wt` is Q8_0, Q4_0, Q4_K or Q6_K. Replaces krk::dtype_supported for this path
+/* 1 if `wt` is one of the formats above (Q8_0, Q4_0, Q4_K, Q6_K, Q5_0, Q5_1, Q5_K). Replaces
+ * krk::dtype_supported for this path
  * (include/krk/quant.hpp:180-186). */
 int krk_cuda_dtype_ok(int wt);
 
