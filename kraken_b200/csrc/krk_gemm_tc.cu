@@ -199,18 +199,46 @@ __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cas
 __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
 
 template <int WT>
-struct Raw {   // formats without a fast path keep only the row pointer and decode element by element
-    static constexpr int kSteps = 2;   // K steps covered by one load()
-    const uint8_t *row;
-    int kstep;
-    __device__ __forceinline__ void load(const uint8_t *r, int ks) {
-        row = r;
-        kstep = ks;
+struct Raw {   // formats without a fast decoder: raw bytes staged in shared memory, decoded element by element
+    static constexpr int kSteps = WT == KRK_CUDA_Q8_0 ? 2 : 4;                             // K steps per stage
+    static constexpr int kRowSeg = kSteps * kBK / block_size(WT) * block_bytes(WT);       // bytes of one row per stage
+    static constexpr int kStageBytes = kTileN * kRowSeg;
+    static constexpr int kU16 = kStageBytes / 2;                                           // every block size is even
+    static constexpr int kPer = (kU16 + kDecodeThreads - 1) / kDecodeThreads;              // 16-bit loads per thread
+    static constexpr int kRegs = (kPer + 1) / 2;
+    static_assert(kStageBytes <= kRawStages * kRawBytes / 2, "two stages must fit the raw staging area");
+    uint32_t pre[kRegs];      // this thread's share of the NEXT stage, on its way from global memory
+    const uint8_t *stage;     // the stage being decoded, [128 rows][kRowSeg]
+    // Loads of stage `ks` (K steps ks .. ks + kSteps of weight rows n0 ..): 2-byte loads, neighbouring threads
+    // take neighbouring halfwords of a row. Rows past n_out read as zero blocks.
+    __device__ __forceinline__ void fetch(const uint8_t *w, int64_t n0, int64_t n_out, int row_bytes, int ks, int tid) {
+        const size_t seg = (size_t)(ks * kBK / block_size(WT)) * block_bytes(WT);
+#pragma unroll
+        for (int j = 0; j < kPer; j++) {
+            const int i = tid + j * kDecodeThreads;
+            uint32_t v = 0;
+            if (i < kU16) {
+                const int rr = i / (kRowSeg / 2), col = i - rr * (kRowSeg / 2);
+                if (n0 + rr < n_out)
+                    v = __ldg(reinterpret_cast<const unsigned short *>(w + (size_t)(n0 + rr) * row_bytes + seg) + col);
+            }
+            if (j & 1) pre[j >> 1] |= v << 16;
+            else pre[j >> 1] = v;
+        }
     }
-    __device__ __forceinline__ void convert(int j, int half, uint32_t (&out)[16]) const {
+    __device__ __forceinline__ void stash(uint8_t *dst, int tid) {
+#pragma unroll
+        for (int j = 0; j < kPer; j++) {
+            const int i = tid + j * kDecodeThreads;
+            if (i < kU16) reinterpret_cast<unsigned short *>(dst)[i] = (unsigned short)((j & 1) ? (pre[j >> 1] >> 16) : (pre[j >> 1] & 0xFFFF));
+        }
+        stage = dst;
+    }
+    __device__ __forceinline__ void convert(int j, int half, int r, uint32_t (&out)[16]) const {
+        const uint8_t *row = stage + (size_t)r * kRowSeg;
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-            const int64_t k = (int64_t)(kstep + j) * kBK + 32 * half + 2 * i;
+            const int64_t k = (int64_t)j * kBK + 32 * half + 2 * i;   // relative to the stage: stages start on block boundaries
             out[i] = h2_bits(__floats2half2_rn(decode_value<WT>(row, k), decode_value<WT>(row, k + 1)));
         }
     }
@@ -230,7 +258,7 @@ struct Raw<KRK_CUDA_Q4_K> {
         for (int i = 0; i < 8; i++) q[i] = b[1 + i];
     }
     __device__ __forceinline__ void load(const uint8_t *row, int ks) { load_block(row + (size_t)(ks >> 2) * 144); }
-    __device__ __forceinline__ void convert(int p, int half, uint32_t (&out)[16]) const {
+    __device__ __forceinline__ void convert(int p, int half, int, uint32_t (&out)[16]) const {
         // 6-bit scale / min of chunk c = 2p + half out of the 12 packed bytes in hdr.y, hdr.z, hdr.w
         // (src/quant.cpp:427-435)
         const int c = 2 * p + half;
@@ -379,6 +407,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             const bool valid = n0 + r < p.n_out;
             const uint8_t *row = p.w + (size_t)(valid ? n0 + r : 0) * p.row_bytes;
             Raw<WT> cur;
+            if constexpr (!kStagedRaw) cur.fetch(p.w, n0, p.n_out, p.row_bytes, it.k0, tid);
             for (int ks0 = it.k0; ks0 < it.k0 + it.nk; ks0 += Raw<WT>::kSteps) {
                 if constexpr (kStagedRaw) {
                     wait_phase(smem_u32(&sm->raw_full[sr]), pr, gave_up, p.status);
@@ -390,12 +419,19 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         pr ^= 1;
                     }
                 } else {
-                    cur.load(row, ks0);
+                    // The bytes fetched a stage ago go to the buffer nobody reads any more (the one before
+                    // last); one barrier of the decode warps makes them visible, and the next stage's loads
+                    // fly while this one is decoded.
+                    cur.stash(&sm->raw[0][0] + (size_t)(sr & 1) * (kRawStages * kRawBytes / 2), tid);
+                    sr++;
+                    asm volatile("bar.sync 1, %0;" ::"n"(kDecodeThreads) : "memory");
+                    if (ks0 + Raw<WT>::kSteps < it.k0 + it.nk)
+                        cur.fetch(p.w, n0, p.n_out, p.row_bytes, ks0 + Raw<WT>::kSteps, tid);
                 }
 #pragma unroll
                 for (int j = 0; j < Raw<WT>::kSteps; j++) {
                     uint32_t v[16];
-                    cur.convert(j, half, v);
+                    cur.convert(j, half, r, v);
                     if (!valid) {
 #pragma unroll
                         for (int i = 0; i < 16; i++) v[i] = 0u;
