@@ -236,6 +236,39 @@ struct Raw {   // formats without a fast decoder: raw bytes staged in shared mem
     }
     __device__ __forceinline__ void convert(int j, int half, int r, uint32_t (&out)[16]) const {
         const uint8_t *row = stage + (size_t)r * kRowSeg;
+        if constexpr (WT == KRK_CUDA_Q8_0) {
+            // one 34-byte block per thread and K step: f16 d, then 32 int8 (src/quant.cpp:381-387). Two quants
+            // per 16-bit load; q ^ 0x80 under a 0x64 high byte is the half 1024 + 128 + q, exactly.
+            const unsigned short *b = reinterpret_cast<const unsigned short *>(row + (2 * j + half) * 34);
+            const __half2 d2 = __half2half2(__ushort_as_half(b[0]));
+            const __half2 bias = __float2half2_rn(1152.0f);
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const uint32_t t = (uint32_t)b[1 + i] ^ 0x8080u;
+                out[i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(t, 0x64646464u, 0x5140)), bias), d2));
+            }
+            return;
+        }
+        if constexpr (WT == KRK_CUDA_Q6_K) {
+            // chunk c = 2j + half of the 210-byte block (src/quant.cpp:491-512): 32 low nibbles (or high ones)
+            // of ql, 2 bits each out of 32 qh bytes, two int8 scales, f16 d. Two values per 16-bit load;
+            // f16(d * scale) is formed in f32 as the host decoder forms d * scale.
+            const int c = 2 * j + half, hf = c >> 2, quad = c & 3;
+            const unsigned short *ql = reinterpret_cast<const unsigned short *>(row + 64 * hf + 32 * (quad & 1));
+            const unsigned short *qh = reinterpret_cast<const unsigned short *>(row + 128 + 32 * hf);
+            const int8_t *sc = reinterpret_cast<const int8_t *>(row + 192) + 8 * hf + 2 * quad;
+            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(row + 208)));
+            const __half2 dl0 = __float2half2_rn(__fmul_rn(d, (float)sc[0])), dl1 = __float2half2_rn(__fmul_rn(d, (float)sc[1]));
+            const __half2 bias = __float2half2_rn(1056.0f);   // 1024 + 32
+            const int nib = (quad & 2) ? 4 : 0, hs = 2 * quad;
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const uint32_t lo = ((uint32_t)ql[i] >> nib) & 0x0F0Fu, hi = (((uint32_t)qh[i] >> hs) & 0x0303u) << 4;
+                const __half2 q = __hsub2(bits_h2(__byte_perm(lo | hi, 0x64646464u, 0x5140)), bias);
+                out[i] = h2_bits(__hmul2(q, i < 8 ? dl0 : dl1));
+            }
+            return;
+        }
 #pragma unroll
         for (int i = 0; i < 16; i++) {
             const int64_t k = (int64_t)j * kBK + 32 * half + 2 * i;   // relative to the stage: stages start on block boundaries
