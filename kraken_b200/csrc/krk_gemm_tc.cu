@@ -203,34 +203,48 @@ struct Raw {   // formats without a fast decoder: raw bytes staged in shared mem
     static constexpr int kSteps = WT == KRK_CUDA_Q8_0 ? 2 : 4;                             // K steps per stage
     static constexpr int kRowSeg = kSteps * kBK / block_size(WT) * block_bytes(WT);       // bytes of one row per stage
     static constexpr int kStageBytes = kTileN * kRowSeg;
-    static constexpr int kU16 = kStageBytes / 2;                                           // every block size is even
-    static constexpr int kPer = (kU16 + kDecodeThreads - 1) / kDecodeThreads;              // 16-bit loads per thread
-    static constexpr int kRegs = (kPer + 1) / 2;
+    // Staging granule: 8 bytes where a row segment is a multiple of 8 bytes (every format but Q6_K: with K a
+    // multiple of 256 the rows and the segments then start 8-byte aligned), else 2 bytes (every block size is even).
+    static constexpr int kUnit = (kRowSeg % 8 == 0) ? 8 : 2;
+    static constexpr int kUnits = kStageBytes / kUnit;
+    static constexpr int kPer = (kUnits + kDecodeThreads - 1) / kDecodeThreads;            // loads per thread
+    static constexpr int kRegs = kUnit == 8 ? 2 * kPer : (kPer + 1) / 2;
     static_assert(kStageBytes <= kRawStages * kRawBytes / 2, "two stages must fit the raw staging area");
     uint32_t pre[kRegs];      // this thread's share of the NEXT stage, on its way from global memory
     const uint8_t *stage;     // the stage being decoded, [128 rows][kRowSeg]
-    // Loads of stage `ks` (K steps ks .. ks + kSteps of weight rows n0 ..): 2-byte loads, neighbouring threads
-    // take neighbouring halfwords of a row. Rows past n_out read as zero blocks.
+    // Loads of stage `ks` (K steps ks .. ks + kSteps of weight rows n0 ..): neighbouring threads take
+    // neighbouring granules of a row. Rows past n_out read as zero blocks.
     __device__ __forceinline__ void fetch(const uint8_t *w, int64_t n0, int64_t n_out, int row_bytes, int ks, int tid) {
         const size_t seg = (size_t)(ks * kBK / block_size(WT)) * block_bytes(WT);
 #pragma unroll
         for (int j = 0; j < kPer; j++) {
             const int i = tid + j * kDecodeThreads;
-            uint32_t v = 0;
-            if (i < kU16) {
-                const int rr = i / (kRowSeg / 2), col = i - rr * (kRowSeg / 2);
-                if (n0 + rr < n_out)
-                    v = __ldg(reinterpret_cast<const unsigned short *>(w + (size_t)(n0 + rr) * row_bytes + seg) + col);
+            const int rr = i / (kRowSeg / kUnit), col = i - rr * (kRowSeg / kUnit);
+            const bool ok = i < kUnits && n0 + rr < n_out;
+            const uint8_t *src = w + (size_t)(n0 + (ok ? rr : 0)) * row_bytes + seg + (size_t)(ok ? col : 0) * kUnit;
+            if constexpr (kUnit == 8) {
+                uint2 v = make_uint2(0u, 0u);
+                if (ok) v = __ldg(reinterpret_cast<const uint2 *>(src));
+                pre[2 * j] = v.x;
+                pre[2 * j + 1] = v.y;
+            } else {
+                uint32_t v = 0;
+                if (ok) v = __ldg(reinterpret_cast<const unsigned short *>(src));
+                if (j & 1) pre[j >> 1] |= v << 16;
+                else pre[j >> 1] = v;
             }
-            if (j & 1) pre[j >> 1] |= v << 16;
-            else pre[j >> 1] = v;
         }
     }
     __device__ __forceinline__ void stash(uint8_t *dst, int tid) {
 #pragma unroll
         for (int j = 0; j < kPer; j++) {
             const int i = tid + j * kDecodeThreads;
-            if (i < kU16) reinterpret_cast<unsigned short *>(dst)[i] = (unsigned short)((j & 1) ? (pre[j >> 1] >> 16) : (pre[j >> 1] & 0xFFFF));
+            if (i < kUnits) {
+                if constexpr (kUnit == 8)
+                    reinterpret_cast<uint2 *>(dst)[i] = make_uint2(pre[2 * j], pre[2 * j + 1]);
+                else
+                    reinterpret_cast<unsigned short *>(dst)[i] = (unsigned short)((j & 1) ? (pre[j >> 1] >> 16) : (pre[j >> 1] & 0xFFFF));
+            }
         }
         stage = dst;
     }
