@@ -210,12 +210,36 @@ struct Raw {   // formats without a fast decoder: raw bytes staged in shared mem
     static constexpr int kPer = (kUnits + kDecodeThreads - 1) / kDecodeThreads;            // loads per thread
     static constexpr int kRegs = kUnit == 8 ? 2 * kPer : (kPer + 1) / 2;
     static_assert(kStageBytes <= kRawStages * kRawBytes / 2, "two stages must fit the raw staging area");
+    // Q6_K with 4-byte-multiple rows (an even number of 210-byte blocks): 53 aligned words per row cover the
+    // block, starting 2 bytes early for an odd block index (never past the row: the last block is an odd one).
+    static constexpr bool kWideQ6 = WT == KRK_CUDA_Q6_K;
+    static constexpr int kWords6 = 53, kSlot6 = 4 * kWords6;
+    static_assert(!kWideQ6 || kTileN * kSlot6 <= kRawStages * kRawBytes / 2, "two stages must fit the raw staging area");
     uint32_t pre[kRegs];      // this thread's share of the NEXT stage, on its way from global memory
-    const uint8_t *stage;     // the stage being decoded, [128 rows][kRowSeg]
+    const uint8_t *stage;     // the stage being decoded, [128 rows][row_pitch]
+    int row_pitch = kRowSeg, lead = 0, lead_next = 0;   // bytes per staged row; bytes before the block in it
+    bool wide = false;
     // Loads of stage `ks` (K steps ks .. ks + kSteps of weight rows n0 ..): neighbouring threads take
     // neighbouring granules of a row. Rows past n_out read as zero blocks.
     __device__ __forceinline__ void fetch(const uint8_t *w, int64_t n0, int64_t n_out, int row_bytes, int ks, int tid) {
         const size_t seg = (size_t)(ks * kBK / block_size(WT)) * block_bytes(WT);
+        if constexpr (kWideQ6) {
+            wide = (row_bytes & 3) == 0;
+            if (wide) {
+                lead_next = (int)(seg & 2);
+                constexpr int kN = kTileN * kWords6, kP = (kN + kDecodeThreads - 1) / kDecodeThreads;
+                static_assert(kP <= kRegs, "register share");
+#pragma unroll
+                for (int j = 0; j < kP; j++) {
+                    const int i = tid + j * kDecodeThreads;
+                    const int rr = i / kWords6, col = i - rr * kWords6;
+                    const bool ok = i < kN && n0 + rr < n_out;
+                    pre[j] = ok ? __ldg(reinterpret_cast<const uint32_t *>(w + (size_t)(n0 + rr) * row_bytes + seg - lead_next) + col) : 0u;
+                }
+                return;
+            }
+            lead_next = 0;
+        }
 #pragma unroll
         for (int j = 0; j < kPer; j++) {
             const int i = tid + j * kDecodeThreads;
@@ -236,6 +260,20 @@ struct Raw {   // formats without a fast decoder: raw bytes staged in shared mem
         }
     }
     __device__ __forceinline__ void stash(uint8_t *dst, int tid) {
+        stage = dst;
+        lead = lead_next;
+        if constexpr (kWideQ6) {
+            row_pitch = wide ? kSlot6 : kRowSeg;
+            if (wide) {
+                constexpr int kN = kTileN * kWords6, kP = (kN + kDecodeThreads - 1) / kDecodeThreads;
+#pragma unroll
+                for (int j = 0; j < kP; j++) {
+                    const int i = tid + j * kDecodeThreads;
+                    if (i < kN) reinterpret_cast<uint32_t *>(dst)[i] = pre[j];
+                }
+                return;
+            }
+        }
 #pragma unroll
         for (int j = 0; j < kPer; j++) {
             const int i = tid + j * kDecodeThreads;
@@ -249,7 +287,7 @@ struct Raw {   // formats without a fast decoder: raw bytes staged in shared mem
         stage = dst;
     }
     __device__ __forceinline__ void convert(int j, int half, int r, uint32_t (&out)[16]) const {
-        const uint8_t *row = stage + (size_t)r * kRowSeg;
+        const uint8_t *row = stage + (size_t)r * row_pitch + lead;
         if constexpr (WT == KRK_CUDA_Q8_0) {
             // one 34-byte block per thread and K step: f16 d, then 32 int8 (src/quant.cpp:381-387). Two quants
             // per 16-bit load; q ^ 0x80 under a 0x64 high byte is the half 1024 + 128 + q, exactly.
