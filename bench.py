@@ -565,6 +565,27 @@ def device_weights_q8_0(torch, n_out: int, n_in: int, gen):
     return w.view(n_out, nblk * 34)
 
 
+def device_weights_q4_0(torch, n_out: int, n_in: int, gen):
+    """Q4_0 blocks made on the device: nibbles uniform, d in [1e-3, 2e-2] as f16."""
+    nblk = n_in // 32
+    w = torch.randint(0, 256, (n_out, nblk, 18), dtype=torch.uint8, device="cuda", generator=gen)
+    d = (1e-3 + 1.9e-2 * torch.rand((n_out, nblk), device="cuda", generator=gen)).to(torch.float16)
+    w[..., 0:2] = d.view(torch.uint8).view(n_out, nblk, 2)
+    return w.view(n_out, nblk * 18)
+
+
+def device_weights_q5_k(torch, n_out: int, n_in: int, gen):
+    """Q5_K blocks made on the device: payload bytes uniform (5-bit quants and packed 6-bit scale/min uniform),
+    d in [5e-4, 5e-3], dmin in [0, 5e-3] as f16."""
+    nblk = n_in // 256
+    w = torch.randint(0, 256, (n_out, nblk, 176), dtype=torch.uint8, device="cuda", generator=gen)
+    d = (5e-4 + 4.5e-3 * torch.rand((n_out, nblk), device="cuda", generator=gen)).to(torch.float16)
+    dm = (5e-3 * torch.rand((n_out, nblk), device="cuda", generator=gen)).to(torch.float16)
+    w[..., 0:2] = d.view(torch.uint8).view(n_out, nblk, 2)
+    w[..., 2:4] = dm.view(torch.uint8).view(n_out, nblk, 2)
+    return w.view(n_out, nblk * 176)
+
+
 def decode_extra(torch, capi, gen, barrier):
     """The decode GEMV on the other shapes the spec names, batch 1, weights rotated through replicas that
     together exceed 4x the L2, each replay a CUDA graph: config 1 (Q8_0 4096 x 4096) and one large matrix
@@ -648,7 +669,8 @@ def prefill_extra(torch, capi, gen):
     # 16-byte multiples, so the decode warps stage the raw bytes themselves)
     other = {}
     del ws
-    for name, wt, make in (("q6_k", synth.Q6_K, device_weights_q6k), ("q8_0", synth.Q8_0, device_weights_q8_0)):
+    for name, wt, make in (("q6_k", synth.Q6_K, device_weights_q6k), ("q8_0", synth.Q8_0, device_weights_q8_0),
+                           ("q4_0", synth.Q4_0, device_weights_q4_0), ("q5_k", synth.Q5_K, device_weights_q5_k)):
         wf = [make(torch, n_out, n_in, gen) for _ in range(3)]
         rows = 512
         x = torch.randn((rows, n_in), device="cuda", generator=gen).to(torch.float16)

@@ -321,6 +321,42 @@ struct Raw {   // formats without a fast decoder: raw bytes staged in shared mem
             }
             return;
         }
+        if constexpr (WT == KRK_CUDA_Q4_0) {
+            // one 18-byte block per thread and K step (src/quant.cpp:331-339): values 0..15 are the low nibbles of
+            // the 16 bytes, 16..31 the high ones; 0x6400 | q is the half 1024 + q.
+            const unsigned short *b = reinterpret_cast<const unsigned short *>(row + (2 * j + half) * 18);
+            const __half2 d2 = __half2half2(__ushort_as_half(b[0]));
+            const __half2 bias = __float2half2_rn(1032.0f);   // 1024 + 8
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t t = b[1 + i];
+                out[i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(t & 0x0F0Fu, 0x64646464u, 0x5140)), bias), d2));
+                out[8 + i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm((t >> 4) & 0x0F0Fu, 0x64646464u, 0x5140)), bias), d2));
+            }
+            return;
+        }
+        if constexpr (WT == KRK_CUDA_Q5_K) {
+            // chunk c = 2j + half of the 176-byte block (src/quant.cpp:462-489): Q4_K's nibbles and 6-bit scales
+            // plus bit c of 32 mask bytes as the fifth quant bit. Staged rows are 16-byte aligned.
+            const int c = 2 * j + half;
+            int sc, mn;
+            scale_min_k4(c, row + 4, sc, mn);
+            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(row)));
+            const float dm = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(row + 2)));
+            const __half2 dl = __float2half2_rn(__fmul_rn(d, (float)sc)), ml = __float2half2_rn(-__fmul_rn(dm, (float)mn));
+            const __half2 k1024 = __float2half2_rn(1024.0f);
+            const uint32_t *q = reinterpret_cast<const uint32_t *>(row + 48 + 32 * (c >> 1));
+            const uint32_t *qh = reinterpret_cast<const uint32_t *>(row + 16);
+            const int shift = 4 * (c & 1);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t t = ((q[i] >> shift) & 0x0F0F0F0Fu) | (((qh[i] >> c) & 0x01010101u) << 4);
+                const uint32_t v01 = __byte_perm(t, 0x64646464u, 0x5140), v23 = __byte_perm(t, 0x64646464u, 0x7362);
+                out[2 * i] = h2_bits(__hfma2(__hsub2(bits_h2(v01), k1024), dl, ml));
+                out[2 * i + 1] = h2_bits(__hfma2(__hsub2(bits_h2(v23), k1024), dl, ml));
+            }
+            return;
+        }
 #pragma unroll
         for (int i = 0; i < 16; i++) {
             const int64_t k = (int64_t)j * kBK + 32 * half + 2 * i;   // relative to the stage: stages start on block boundaries
