@@ -45,8 +45,14 @@ constexpr int kMaxTileM = 256;         // tokens per tile (MMA N)
 constexpr int kBK = 64;                // K values per step: one 128-byte swizzle row of f16 X, 32 TMEM columns of A
 constexpr int kBStages = 4;            // X tiles in shared memory
 constexpr int kAStages = 8;            // decoded weight tiles in tensor memory
-constexpr int kRawStages = 3;          // raw Q4_K super-block columns in shared memory
+constexpr int kRawStages = 3;          // raw block columns (256 values x 128 rows) in shared memory, at most
 constexpr int kRawBytes = kTileN * 144;
+// Formats whose 256-value row segment is a multiple of 16 bytes arrive by TMA: Q4_K (144), Q4_0 (8 x 18 = 144),
+// Q5_K (176, two stages in the same area).
+__host__ __device__ constexpr bool tma_staged(int wt) { return wt == KRK_CUDA_Q4_K || wt == KRK_CUDA_Q4_0 || wt == KRK_CUDA_Q5_K; }
+__host__ __device__ constexpr int raw_seg(int wt) { return wt == KRK_CUDA_Q5_K ? 176 : 144; }
+__host__ __device__ constexpr int raw_stages(int wt) { return wt == KRK_CUDA_Q5_K ? 2 : 3; }
+static_assert(2 * kTileN * 176 <= kRawStages * kRawBytes, "Q5_K stages fit the raw area");
 constexpr int kDecodeThreads = 256, kEpilogueThreads = 128;   // two decode threads per weight row
 constexpr int kThreads = kDecodeThreads + kEpilogueThreads + 96;
 constexpr int kTmemCols = 512, kTmemA = 256;
@@ -69,7 +75,7 @@ struct GemmParams {
 
 struct __align__(1024) GemmSmem {
     uint8_t b[kBStages][kMaxTileM * 128];      // X tiles, [tokens][64 f16], 128B swizzle (TMA)
-    uint8_t raw[kRawStages][kRawBytes];        // raw Q4_K bytes, [128 rows][144] (TMA)
+    uint8_t raw[kRawStages][kRawBytes];        // raw block bytes, stages of [128 rows][144 or 176] (TMA), or the decode warps' own staging
     float ystage[2][kYChunk][kTileN];          // accumulator read-out on its way to Y: [tokens][weight rows] (TMA store)
     unsigned long long b_full[kBStages], b_empty[kBStages];
     unsigned long long a_full[kAStages], a_empty[kAStages];
@@ -321,42 +327,6 @@ struct Raw {   // formats without a fast decoder: raw bytes staged in shared mem
             }
             return;
         }
-        if constexpr (WT == KRK_CUDA_Q4_0) {
-            // one 18-byte block per thread and K step (src/quant.cpp:331-339): values 0..15 are the low nibbles of
-            // the 16 bytes, 16..31 the high ones; 0x6400 | q is the half 1024 + q.
-            const unsigned short *b = reinterpret_cast<const unsigned short *>(row + (2 * j + half) * 18);
-            const __half2 d2 = __half2half2(__ushort_as_half(b[0]));
-            const __half2 bias = __float2half2_rn(1032.0f);   // 1024 + 8
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const uint32_t t = b[1 + i];
-                out[i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(t & 0x0F0Fu, 0x64646464u, 0x5140)), bias), d2));
-                out[8 + i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm((t >> 4) & 0x0F0Fu, 0x64646464u, 0x5140)), bias), d2));
-            }
-            return;
-        }
-        if constexpr (WT == KRK_CUDA_Q5_K) {
-            // chunk c = 2j + half of the 176-byte block (src/quant.cpp:462-489): Q4_K's nibbles and 6-bit scales
-            // plus bit c of 32 mask bytes as the fifth quant bit. Staged rows are 16-byte aligned.
-            const int c = 2 * j + half;
-            int sc, mn;
-            scale_min_k4(c, row + 4, sc, mn);
-            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(row)));
-            const float dm = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(row + 2)));
-            const __half2 dl = __float2half2_rn(__fmul_rn(d, (float)sc)), ml = __float2half2_rn(-__fmul_rn(dm, (float)mn));
-            const __half2 k1024 = __float2half2_rn(1024.0f);
-            const uint32_t *q = reinterpret_cast<const uint32_t *>(row + 48 + 32 * (c >> 1));
-            const uint32_t *qh = reinterpret_cast<const uint32_t *>(row + 16);
-            const int shift = 4 * (c & 1);
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const uint32_t t = ((q[i] >> shift) & 0x0F0F0F0Fu) | (((qh[i] >> c) & 0x01010101u) << 4);
-                const uint32_t v01 = __byte_perm(t, 0x64646464u, 0x5140), v23 = __byte_perm(t, 0x64646464u, 0x7362);
-                out[2 * i] = h2_bits(__hfma2(__hsub2(bits_h2(v01), k1024), dl, ml));
-                out[2 * i + 1] = h2_bits(__hfma2(__hsub2(bits_h2(v23), k1024), dl, ml));
-            }
-            return;
-        }
 #pragma unroll
         for (int i = 0; i < 16; i++) {
             const int64_t k = (int64_t)j * kBK + 32 * half + 2 * i;   // relative to the stage: stages start on block boundaries
@@ -402,6 +372,93 @@ struct Raw<KRK_CUDA_Q4_K> {
         for (int i = 0; i < 8; i++) {
             // bytes 4i..4i+3 hold values 4i..4i+3 of the chunk; 0x6400 | q is the half 1024 + q
             const uint32_t t = (qw[i] >> shift) & 0x0F0F0F0Fu;
+            const uint32_t v01 = __byte_perm(t, 0x64646464u, 0x5140), v23 = __byte_perm(t, 0x64646464u, 0x7362);
+            out[2 * i] = h2_bits(__hfma2(__hsub2(bits_h2(v01), k1024), dl, ml));
+            out[2 * i + 1] = h2_bits(__hfma2(__hsub2(bits_h2(v23), k1024), dl, ml));
+        }
+    }
+};
+
+// Q4_0: eight 18-byte blocks per 256 values = the same 144-byte column as Q4_K. K step p covers blocks 2p
+// (thread half 0) and 2p + 1 (half 1): block 2p starts on a word of the 144 bytes, block 2p + 1 half a word
+// later, so its 16 quant bytes are whole words (src/quant.cpp:331-339).
+template <>
+struct Raw<KRK_CUDA_Q4_0> {
+    static constexpr int kSteps = 4;
+    uint32_t w[36];
+    __device__ __forceinline__ void load_block(const uint8_t *block) {
+        const uint4 *b = reinterpret_cast<const uint4 *>(block);
+#pragma unroll
+        for (int i = 0; i < 9; i++) {
+            const uint4 v = b[i];
+            w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
+        }
+    }
+    __device__ __forceinline__ void convert(int p, int half, int, uint32_t (&out)[16]) const {
+        uint32_t q[4], dbits;
+        if (half == 0) {
+            dbits = w[9 * p] & 0xFFFFu;
+#pragma unroll
+            for (int i = 0; i < 4; i++) q[i] = __funnelshift_r(w[9 * p + i], w[9 * p + i + 1], 16);
+        } else {
+            dbits = w[9 * p + 4] >> 16;
+#pragma unroll
+            for (int i = 0; i < 4; i++) q[i] = w[9 * p + 5 + i];
+        }
+        const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)dbits));
+        const __half2 bias = __float2half2_rn(1032.0f);   // 0x6400 | q is the half 1024 + q; the quant is q - 8
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            // byte b of the block: value b in its low nibble, value 16 + b in its high one
+            const uint32_t lo = q[i] & 0x0F0F0F0Fu, hi = (q[i] >> 4) & 0x0F0F0F0Fu;
+            out[2 * i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(lo, 0x64646464u, 0x5140)), bias), d2));
+            out[2 * i + 1] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(lo, 0x64646464u, 0x7362)), bias), d2));
+            out[8 + 2 * i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(hi, 0x64646464u, 0x5140)), bias), d2));
+            out[8 + 2 * i + 1] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(hi, 0x64646464u, 0x7362)), bias), d2));
+        }
+    }
+};
+
+// Q5_K: the 176-byte super-block (src/quant.cpp:462-489) is Q4_K's header and nibbles plus 32 mask bytes whose
+// bit c is the fifth quant bit of chunk c. K step p covers chunks 2p, 2p + 1; thread half h converts 2p + h.
+template <>
+struct Raw<KRK_CUDA_Q5_K> {
+    static constexpr int kSteps = 4;
+    uint4 hdr;
+    uint32_t qh[8], q[32];
+    __device__ __forceinline__ void load_block(const uint8_t *block) {
+        const uint4 *b = reinterpret_cast<const uint4 *>(block);
+        hdr = b[0];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const uint4 v = b[1 + i];
+            qh[4 * i] = v.x, qh[4 * i + 1] = v.y, qh[4 * i + 2] = v.z, qh[4 * i + 3] = v.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint4 v = b[3 + i];
+            q[4 * i] = v.x, q[4 * i + 1] = v.y, q[4 * i + 2] = v.z, q[4 * i + 3] = v.w;
+        }
+    }
+    __device__ __forceinline__ void convert(int p, int half, int, uint32_t (&out)[16]) const {
+        const int c = 2 * p + half;
+        int sc, mn;
+        if (c < 4) {
+            sc = (hdr.y >> (8 * c)) & 63;
+            mn = (hdr.z >> (8 * c)) & 63;
+        } else {
+            const int sh = 8 * (c - 4);
+            sc = ((hdr.w >> sh) & 0xF) | (((hdr.y >> (sh + 6)) & 3) << 4);
+            mn = ((hdr.w >> (sh + 4)) & 0xF) | (((hdr.z >> (sh + 6)) & 3) << 4);
+        }
+        const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFF)));
+        const float dm = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+        const __half2 dl = __float2half2_rn(__fmul_rn(d, (float)sc)), ml = __float2half2_rn(-__fmul_rn(dm, (float)mn));
+        const __half2 k1024 = __float2half2_rn(1024.0f);
+        const int shift = 4 * half;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t t = ((q[8 * p + i] >> shift) & 0x0F0F0F0Fu) | (((qh[i] >> c) & 0x01010101u) << 4);
             const uint32_t v01 = __byte_perm(t, 0x64646464u, 0x5140), v23 = __byte_perm(t, 0x64646464u, 0x7362);
             out[2 * i] = h2_bits(__hfma2(__hsub2(bits_h2(v01), k1024), dl, ml));
             out[2 * i + 1] = h2_bits(__hfma2(__hsub2(bits_h2(v23), k1024), dl, ml));
@@ -477,7 +534,8 @@ template <int WT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap x_map,
                const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap y_map) {
-    constexpr bool kStagedRaw = WT == KRK_CUDA_Q4_K;
+    constexpr bool kStagedRaw = tma_staged(WT);
+    constexpr int kSeg = raw_seg(WT), kNRaw = raw_stages(WT);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     GemmSmem *sm = reinterpret_cast<GemmSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -532,10 +590,10 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             for (int ks0 = it.k0; ks0 < it.k0 + it.nk; ks0 += Raw<WT>::kSteps) {
                 if constexpr (kStagedRaw) {
                     wait_phase(smem_u32(&sm->raw_full[sr]), pr, gave_up, p.status);
-                    cur.load_block(sm->raw[sr] + r * 144);
+                    cur.load_block(&sm->raw[0][0] + (size_t)sr * (kTileN * kSeg) + r * kSeg);
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&sm->raw_empty[sr]));   // the bytes are in registers now
-                    if (++sr == kRawStages) {
+                    if (++sr == kNRaw) {
                         sr = 0;
                         pr ^= 1;
                     }
@@ -702,9 +760,9 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                 for (int blk = it.k0 / 4; blk < (it.k0 + it.nk) / 4; blk++) {
                     wait_phase(smem_u32(&sm->raw_empty[sr]), pr ^ 1, gave_up, p.status);
                     const uint32_t bar = smem_u32(&sm->raw_full[sr]);
-                    mbar_arrive_expect_tx(bar, (uint32_t)kRawBytes);
-                    tma_load_2d(smem_u32(sm->raw[sr]), &w_map, blk * 144, n0, bar);
-                    if (++sr == kRawStages) {
+                    mbar_arrive_expect_tx(bar, (uint32_t)(kTileN * kSeg));
+                    tma_load_2d(smem_u32(&sm->raw[0][0] + (size_t)sr * (kTileN * kSeg)), &w_map, blk * kSeg, n0, bar);
+                    if (++sr == kNRaw) {
                         sr = 0;
                         pr ^= 1;
                     }
@@ -781,10 +839,10 @@ EncodeTiledFn encode_tiled() {
 bool encode_w_map(CUtensorMap *map, const uint8_t *w, int wt, int64_t n_out, int row_bytes) {
     EncodeTiledFn encode = encode_tiled();
     if (!encode) return false;
-    const bool staged = wt == KRK_CUDA_Q4_K;
+    const bool staged = tma_staged(wt);
     const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)n_out};
     const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-    const cuuint32_t box[2] = {staged ? 144u : 16u, staged ? (cuuint32_t)kTileN : 1u};
+    const cuuint32_t box[2] = {staged ? (cuuint32_t)raw_seg(wt) : 16u, staged ? (cuuint32_t)kTileN : 1u};
     const cuuint32_t estr[2] = {1, 1};
     if (!staged && (row_bytes % 16) != 0) {
         // never used by the kernel; describe a 16-byte row of the same buffer so that encoding succeeds
