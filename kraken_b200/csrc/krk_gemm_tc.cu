@@ -48,8 +48,11 @@ constexpr int kAStages = 8;            // decoded weight tiles in tensor memory
 constexpr int kRawStages = 3;          // raw block columns (256 values x 128 rows) in shared memory, at most
 constexpr int kRawBytes = kTileN * 144;
 // Formats whose 256-value row segment is a multiple of 16 bytes arrive by TMA: Q4_K (144), Q4_0 (8 x 18 = 144),
-// Q5_K (176, two stages in the same area).
-__host__ __device__ constexpr bool tma_staged(int wt) { return wt == KRK_CUDA_Q4_K || wt == KRK_CUDA_Q4_0 || wt == KRK_CUDA_Q5_K; }
+// Q5_K (176, two stages in the same area). Q8_0 arrives 128 values at a time: four 34-byte blocks = 136 bytes,
+// which start 0 or 8 bytes after a 16-byte boundary, so a 144-byte box that starts on the boundary covers them.
+__host__ __device__ constexpr bool tma_staged(int wt) {
+    return wt == KRK_CUDA_Q4_K || wt == KRK_CUDA_Q4_0 || wt == KRK_CUDA_Q5_K || wt == KRK_CUDA_Q8_0;
+}
 __host__ __device__ constexpr int raw_seg(int wt) { return wt == KRK_CUDA_Q5_K ? 176 : 144; }
 __host__ __device__ constexpr int raw_stages(int wt) { return wt == KRK_CUDA_Q5_K ? 2 : 3; }
 static_assert(2 * kTileN * 176 <= kRawStages * kRawBytes, "Q5_K stages fit the raw area");
@@ -342,13 +345,12 @@ template <>
 struct Raw<KRK_CUDA_Q4_K> {
     static constexpr int kSteps = 4;
     uint4 hdr, q[8];
-    __device__ __forceinline__ void load_block(const uint8_t *block) {
+    __device__ __forceinline__ void load_block(const uint8_t *block, int, int) {
         const uint4 *b = reinterpret_cast<const uint4 *>(block);
         hdr = b[0];
 #pragma unroll
         for (int i = 0; i < 8; i++) q[i] = b[1 + i];
     }
-    __device__ __forceinline__ void load(const uint8_t *row, int ks) { load_block(row + (size_t)(ks >> 2) * 144); }
     __device__ __forceinline__ void convert(int p, int half, int, uint32_t (&out)[16]) const {
         // 6-bit scale / min of chunk c = 2p + half out of the 12 packed bytes in hdr.y, hdr.z, hdr.w
         // (src/quant.cpp:427-435)
@@ -386,7 +388,7 @@ template <>
 struct Raw<KRK_CUDA_Q4_0> {
     static constexpr int kSteps = 4;
     uint32_t w[36];
-    __device__ __forceinline__ void load_block(const uint8_t *block) {
+    __device__ __forceinline__ void load_block(const uint8_t *block, int, int) {
         const uint4 *b = reinterpret_cast<const uint4 *>(block);
 #pragma unroll
         for (int i = 0; i < 9; i++) {
@@ -426,7 +428,7 @@ struct Raw<KRK_CUDA_Q5_K> {
     static constexpr int kSteps = 4;
     uint4 hdr;
     uint32_t qh[8], q[32];
-    __device__ __forceinline__ void load_block(const uint8_t *block) {
+    __device__ __forceinline__ void load_block(const uint8_t *block, int, int) {
         const uint4 *b = reinterpret_cast<const uint4 *>(block);
         hdr = b[0];
 #pragma unroll
@@ -462,6 +464,45 @@ struct Raw<KRK_CUDA_Q5_K> {
             const uint32_t v01 = __byte_perm(t, 0x64646464u, 0x5140), v23 = __byte_perm(t, 0x64646464u, 0x7362);
             out[2 * i] = h2_bits(__hfma2(__hsub2(bits_h2(v01), k1024), dl, ml));
             out[2 * i + 1] = h2_bits(__hfma2(__hsub2(bits_h2(v23), k1024), dl, ml));
+        }
+    }
+};
+
+// Q8_0: a stage is 128 values = four 34-byte blocks (f16 d, 32 int8; src/quant.cpp:381-387) inside a 144-byte
+// box that starts 0 (even stage) or 8 (odd stage) bytes before them. K step p covers blocks 2p (thread half 0)
+// and 2p + 1 (half 1); a thread takes only its own two blocks, as nine words each: block 2p starts on a word,
+// block 2p + 1 half a word later, so its quants are whole words.
+template <>
+struct Raw<KRK_CUDA_Q8_0> {
+    static constexpr int kSteps = 2;
+    uint32_t w[2][9];
+    int odd;
+    __device__ __forceinline__ void load_block(const uint8_t *box, int half, int ks) {
+        odd = half;
+        const uint32_t *b = reinterpret_cast<const uint32_t *>(box + 8 * ((ks >> 1) & 1) + 32 * half);
+#pragma unroll
+        for (int p = 0; p < 2; p++)
+#pragma unroll
+            for (int i = 0; i < 9; i++) w[p][i] = b[17 * p + i];
+    }
+    __device__ __forceinline__ void convert(int p, int, int, uint32_t (&out)[16]) const {
+        uint32_t q[8], dbits;
+        if (odd == 0) {
+            dbits = w[p][0] & 0xFFFFu;
+#pragma unroll
+            for (int i = 0; i < 8; i++) q[i] = __funnelshift_r(w[p][i], w[p][i + 1], 16);
+        } else {
+            dbits = w[p][0] >> 16;
+#pragma unroll
+            for (int i = 0; i < 8; i++) q[i] = w[p][1 + i];
+        }
+        const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)dbits));
+        const __half2 bias = __float2half2_rn(1152.0f);   // q ^ 0x80 under a 0x64 high byte is the half 1024 + 128 + q
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t t = q[i] ^ 0x80808080u;
+            out[2 * i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(t, 0x64646464u, 0x5140)), bias), d2));
+            out[2 * i + 1] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(t, 0x64646464u, 0x7362)), bias), d2));
         }
     }
 };
@@ -590,7 +631,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             for (int ks0 = it.k0; ks0 < it.k0 + it.nk; ks0 += Raw<WT>::kSteps) {
                 if constexpr (kStagedRaw) {
                     wait_phase(smem_u32(&sm->raw_full[sr]), pr, gave_up, p.status);
-                    cur.load_block(&sm->raw[0][0] + (size_t)sr * (kTileN * kSeg) + r * kSeg);
+                    cur.load_block(&sm->raw[0][0] + (size_t)sr * (kTileN * kSeg) + r * kSeg, half, ks0);
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&sm->raw_empty[sr]));   // the bytes are in registers now
                     if (++sr == kNRaw) {
@@ -757,11 +798,13 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             uint32_t pr = 0;
             while (iter.next(it)) {
                 const int n0 = (it.tile / p.n_tiles_m) * kTileN;
-                for (int blk = it.k0 / 4; blk < (it.k0 + it.nk) / 4; blk++) {
+                constexpr int kPer = Raw<WT>::kSteps;   // K steps per stage
+                for (int blk = it.k0 / kPer; blk < (it.k0 + it.nk) / kPer; blk++) {
                     wait_phase(smem_u32(&sm->raw_empty[sr]), pr ^ 1, gave_up, p.status);
                     const uint32_t bar = smem_u32(&sm->raw_full[sr]);
                     mbar_arrive_expect_tx(bar, (uint32_t)(kTileN * kSeg));
-                    tma_load_2d(smem_u32(&sm->raw[0][0] + (size_t)sr * (kTileN * kSeg)), &w_map, blk * kSeg, n0, bar);
+                    const int x0 = WT == KRK_CUDA_Q8_0 ? 136 * blk - 8 * (blk & 1) : blk * kSeg;   // a multiple of 16
+                    tma_load_2d(smem_u32(&sm->raw[0][0] + (size_t)sr * (kTileN * kSeg)), &w_map, x0, n0, bar);
                     if (++sr == kNRaw) {
                         sr = 0;
                         pr ^= 1;
