@@ -208,132 +208,113 @@ __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cas
 __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
 
 template <int WT>
-struct Raw {   // formats without a fast decoder: raw bytes staged in shared memory, decoded element by element
-    static constexpr int kSteps = WT == KRK_CUDA_Q8_0 ? 2 : 4;                             // K steps per stage
+struct Raw {   // formats without a packed decoder (Q5_0, Q5_1): raw bytes staged in shared memory, decoded element by element
+    static constexpr int kSteps = 4;                                                       // K steps per stage
     static constexpr int kRowSeg = kSteps * kBK / block_size(WT) * block_bytes(WT);       // bytes of one row per stage
     static constexpr int kStageBytes = kTileN * kRowSeg;
-    // Staging granule: 8 bytes where a row segment is a multiple of 8 bytes (every format but Q6_K: with K a
-    // multiple of 256 the rows and the segments then start 8-byte aligned), else 2 bytes (every block size is even).
-    static constexpr int kUnit = (kRowSeg % 8 == 0) ? 8 : 2;
-    static constexpr int kUnits = kStageBytes / kUnit;
+    // Staging granule: with K a multiple of 256 the rows and the segments start 8-byte aligned.
+    static_assert(kRowSeg % 8 == 0, "8-byte staging granules");
+    static constexpr int kUnits = kStageBytes / 8;
     static constexpr int kPer = (kUnits + kDecodeThreads - 1) / kDecodeThreads;            // loads per thread
-    static constexpr int kRegs = kUnit == 8 ? 2 * kPer : (kPer + 1) / 2;
     static_assert(kStageBytes <= kRawStages * kRawBytes / 2, "two stages must fit the raw staging area");
-    // Q6_K with 4-byte-multiple rows (an even number of 210-byte blocks): 53 aligned words per row cover the
-    // block, starting 2 bytes early for an odd block index (never past the row: the last block is an odd one).
-    static constexpr bool kWideQ6 = WT == KRK_CUDA_Q6_K;
-    static constexpr int kWords6 = 53, kSlot6 = 4 * kWords6;
-    static_assert(!kWideQ6 || kTileN * kSlot6 <= kRawStages * kRawBytes / 2, "two stages must fit the raw staging area");
-    uint32_t pre[kRegs];      // this thread's share of the NEXT stage, on its way from global memory
-    const uint8_t *stage;     // the stage being decoded, [128 rows][row_pitch]
-    int row_pitch = kRowSeg, lead = 0, lead_next = 0;   // bytes per staged row; bytes before the block in it
-    bool wide = false;
+    uint32_t pre[2 * kPer];   // this thread's share of the NEXT stage, on its way from global memory
+    const uint8_t *stage;     // the stage being decoded, [128 rows][kRowSeg]
     // Loads of stage `ks` (K steps ks .. ks + kSteps of weight rows n0 ..): neighbouring threads take
     // neighbouring granules of a row. Rows past n_out read as zero blocks.
     __device__ __forceinline__ void fetch(const uint8_t *w, int64_t n0, int64_t n_out, int row_bytes, int ks, int tid) {
         const size_t seg = (size_t)(ks * kBK / block_size(WT)) * block_bytes(WT);
-        if constexpr (kWideQ6) {
-            wide = (row_bytes & 3) == 0;
-            if (wide) {
-                lead_next = (int)(seg & 2);
-                constexpr int kN = kTileN * kWords6, kP = (kN + kDecodeThreads - 1) / kDecodeThreads;
-                static_assert(kP <= kRegs, "register share");
-#pragma unroll
-                for (int j = 0; j < kP; j++) {
-                    const int i = tid + j * kDecodeThreads;
-                    const int rr = i / kWords6, col = i - rr * kWords6;
-                    const bool ok = i < kN && n0 + rr < n_out;
-                    pre[j] = ok ? __ldg(reinterpret_cast<const uint32_t *>(w + (size_t)(n0 + rr) * row_bytes + seg - lead_next) + col) : 0u;
-                }
-                return;
-            }
-            lead_next = 0;
-        }
 #pragma unroll
         for (int j = 0; j < kPer; j++) {
             const int i = tid + j * kDecodeThreads;
-            const int rr = i / (kRowSeg / kUnit), col = i - rr * (kRowSeg / kUnit);
+            const int rr = i / (kRowSeg / 8), col = i - rr * (kRowSeg / 8);
             const bool ok = i < kUnits && n0 + rr < n_out;
-            const uint8_t *src = w + (size_t)(n0 + (ok ? rr : 0)) * row_bytes + seg + (size_t)(ok ? col : 0) * kUnit;
-            if constexpr (kUnit == 8) {
-                uint2 v = make_uint2(0u, 0u);
-                if (ok) v = __ldg(reinterpret_cast<const uint2 *>(src));
-                pre[2 * j] = v.x;
-                pre[2 * j + 1] = v.y;
-            } else {
-                uint32_t v = 0;
-                if (ok) v = __ldg(reinterpret_cast<const unsigned short *>(src));
-                if (j & 1) pre[j >> 1] |= v << 16;
-                else pre[j >> 1] = v;
-            }
+            uint2 v = make_uint2(0u, 0u);
+            if (ok) v = __ldg(reinterpret_cast<const uint2 *>(w + (size_t)(n0 + rr) * row_bytes + seg) + col);
+            pre[2 * j] = v.x;
+            pre[2 * j + 1] = v.y;
         }
     }
     __device__ __forceinline__ void stash(uint8_t *dst, int tid) {
-        stage = dst;
-        lead = lead_next;
-        if constexpr (kWideQ6) {
-            row_pitch = wide ? kSlot6 : kRowSeg;
-            if (wide) {
-                constexpr int kN = kTileN * kWords6, kP = (kN + kDecodeThreads - 1) / kDecodeThreads;
-#pragma unroll
-                for (int j = 0; j < kP; j++) {
-                    const int i = tid + j * kDecodeThreads;
-                    if (i < kN) reinterpret_cast<uint32_t *>(dst)[i] = pre[j];
-                }
-                return;
-            }
-        }
 #pragma unroll
         for (int j = 0; j < kPer; j++) {
             const int i = tid + j * kDecodeThreads;
-            if (i < kUnits) {
-                if constexpr (kUnit == 8)
-                    reinterpret_cast<uint2 *>(dst)[i] = make_uint2(pre[2 * j], pre[2 * j + 1]);
-                else
-                    reinterpret_cast<unsigned short *>(dst)[i] = (unsigned short)((j & 1) ? (pre[j >> 1] >> 16) : (pre[j >> 1] & 0xFFFF));
-            }
+            if (i < kUnits) reinterpret_cast<uint2 *>(dst)[i] = make_uint2(pre[2 * j], pre[2 * j + 1]);
         }
         stage = dst;
     }
     __device__ __forceinline__ void convert(int j, int half, int r, uint32_t (&out)[16]) const {
-        const uint8_t *row = stage + (size_t)r * row_pitch + lead;
-        if constexpr (WT == KRK_CUDA_Q8_0) {
-            // one 34-byte block per thread and K step: f16 d, then 32 int8 (src/quant.cpp:381-387). Two quants
-            // per 16-bit load; q ^ 0x80 under a 0x64 high byte is the half 1024 + 128 + q, exactly.
-            const unsigned short *b = reinterpret_cast<const unsigned short *>(row + (2 * j + half) * 34);
-            const __half2 d2 = __half2half2(__ushort_as_half(b[0]));
-            const __half2 bias = __float2half2_rn(1152.0f);
-#pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const uint32_t t = (uint32_t)b[1 + i] ^ 0x8080u;
-                out[i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(t, 0x64646464u, 0x5140)), bias), d2));
-            }
-            return;
-        }
-        if constexpr (WT == KRK_CUDA_Q6_K) {
-            // chunk c = 2j + half of the 210-byte block (src/quant.cpp:491-512): 32 low nibbles (or high ones)
-            // of ql, 2 bits each out of 32 qh bytes, two int8 scales, f16 d. Two values per 16-bit load;
-            // f16(d * scale) is formed in f32 as the host decoder forms d * scale.
-            const int c = 2 * j + half, hf = c >> 2, quad = c & 3;
-            const unsigned short *ql = reinterpret_cast<const unsigned short *>(row + 64 * hf + 32 * (quad & 1));
-            const unsigned short *qh = reinterpret_cast<const unsigned short *>(row + 128 + 32 * hf);
-            const int8_t *sc = reinterpret_cast<const int8_t *>(row + 192) + 8 * hf + 2 * quad;
-            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(row + 208)));
-            const __half2 dl0 = __float2half2_rn(__fmul_rn(d, (float)sc[0])), dl1 = __float2half2_rn(__fmul_rn(d, (float)sc[1]));
-            const __half2 bias = __float2half2_rn(1056.0f);   // 1024 + 32
-            const int nib = (quad & 2) ? 4 : 0, hs = 2 * quad;
-#pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const uint32_t lo = ((uint32_t)ql[i] >> nib) & 0x0F0Fu, hi = (((uint32_t)qh[i] >> hs) & 0x0303u) << 4;
-                const __half2 q = __hsub2(bits_h2(__byte_perm(lo | hi, 0x64646464u, 0x5140)), bias);
-                out[i] = h2_bits(__hmul2(q, i < 8 ? dl0 : dl1));
-            }
-            return;
-        }
+        const uint8_t *row = stage + (size_t)r * kRowSeg;
 #pragma unroll
         for (int i = 0; i < 16; i++) {
             const int64_t k = (int64_t)j * kBK + 32 * half + 2 * i;   // relative to the stage: stages start on block boundaries
             out[i] = h2_bits(__floats2half2_rn(decode_value<WT>(row, k), decode_value<WT>(row, k + 1)));
+        }
+    }
+};
+
+// Q6_K: 210-byte blocks (src/quant.cpp:491-512) start on even addresses only, so a row's block is staged as the
+// 53 aligned words that cover it, beginning 0 or 2 bytes before the block (`lead`, a property of the row and
+// the block index); the odd pitch keeps the 128 rows on different banks. The decoder shifts each pair of
+// neighbouring words by 8 * lead bits to get the block's own words and converts four quants at a time.
+template <>
+struct Raw<KRK_CUDA_Q6_K> {
+    static constexpr int kSteps = 4;
+    static constexpr int kWords = 53, kN = kTileN * kWords, kPer = (kN + kDecodeThreads - 1) / kDecodeThreads;
+    static_assert(2 * kN * 4 <= kRawStages * kRawBytes, "two stages must fit the raw staging area");
+    uint32_t pre[kPer];
+    const uint32_t *stage;
+    int lead = 0, lead_next = 0;
+    __device__ __forceinline__ void fetch(const uint8_t *w, int64_t n0, int64_t n_out, int row_bytes, int ks, int tid) {
+        const size_t seg = (size_t)(ks >> 2) * 210;
+        const size_t total = (size_t)n_out * row_bytes;   // the last word of the last row's last block may end 2 bytes past it
+        lead_next = (int)(((size_t)(n0 + (tid & 127)) * row_bytes + seg) & 2);
+#pragma unroll
+        for (int j = 0; j < kPer; j++) {
+            const int i = tid + j * kDecodeThreads;
+            const int rr = i / kWords, col = i - rr * kWords;
+            const size_t at = (((size_t)(n0 + rr) * row_bytes + seg) & ~(size_t)3) + 4 * (size_t)col;
+            const bool ok = i < kN && n0 + rr < n_out;
+            uint32_t v = 0u;
+            if (ok && at + 4 <= total) v = __ldg(reinterpret_cast<const uint32_t *>(w + at));
+            else if (ok && at + 2 <= total) v = __ldg(reinterpret_cast<const unsigned short *>(w + at));   // d of the very last block
+            pre[j] = v;
+        }
+    }
+    __device__ __forceinline__ void stash(uint8_t *dst, int tid) {
+#pragma unroll
+        for (int j = 0; j < kPer; j++) {
+            const int i = tid + j * kDecodeThreads;
+            if (i < kN) reinterpret_cast<uint32_t *>(dst)[i] = pre[j];
+        }
+        stage = reinterpret_cast<const uint32_t *>(dst);
+        lead = lead_next;
+    }
+    // chunk c = 2j + half of the block: quad = c & 3 of 128-value half hf = c >> 2 takes the low (quad < 2) or
+    // high nibbles of 32 ql bytes and bit pair `quad` of 32 qh bytes; two int8 scales; f16 d. f16(d * scale) is
+    // formed in f32 as the host decoder forms d * scale.
+    __device__ __forceinline__ void convert(int j, int half, int r, uint32_t (&out)[16]) const {
+        const uint32_t *rw = stage + r * kWords;
+        const int sh = 8 * lead;
+        const int hf = j >> 1, nib = (j & 1) ? 4 : 0, hs = 4 * (j & 1) + 2 * half;
+        const uint32_t *qlw = rw + 16 * hf + 8 * half, *qhw = rw + 32 + 8 * hf;
+        const int so = 192 + 8 * hf + 4 * (j & 1) + 2 * half + lead;   // the two scales, an aligned 16-bit pair
+        const uint32_t spair = rw[so >> 2] >> (8 * (so & 2));
+        const uint32_t dbits = rw[(208 + lead) >> 2] >> (8 * ((208 + lead) & 2));
+        const float d = __half2float(__ushort_as_half((unsigned short)(dbits & 0xFFFF)));
+        const __half2 dl0 = __float2half2_rn(__fmul_rn(d, (float)(int8_t)(spair & 0xFF)));
+        const __half2 dl1 = __float2half2_rn(__fmul_rn(d, (float)(int8_t)((spair >> 8) & 0xFF)));
+        const __half2 bias = __float2half2_rn(1056.0f);   // 0x6400 | q is the half 1024 + q; the quant is q - 32
+        uint32_t a = qlw[0], b = qhw[0];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t a1 = qlw[i + 1], b1 = qhw[i + 1];
+            const uint32_t lo = (__funnelshift_r(a, a1, sh) >> nib) & 0x0F0F0F0Fu;
+            const uint32_t hi = ((__funnelshift_r(b, b1, sh) >> hs) & 0x03030303u) << 4;
+            const uint32_t t = lo | hi;
+            const __half2 dl = i < 4 ? dl0 : dl1;
+            out[2 * i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(t, 0x64646464u, 0x5140)), bias), dl));
+            out[2 * i + 1] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(t, 0x64646464u, 0x7362)), bias), dl));
+            a = a1, b = b1;
         }
     }
 };

@@ -42,13 +42,17 @@ def test_gemm_smallest_first(cuda, oracle):
     run_gemm(cuda, oracle, synth.Q4_K, 128, 1024, 64, SEED + 1)
 
 
-@pytest.mark.parametrize("wt", [synth.Q4_K, synth.Q8_0, synth.Q6_K, synth.Q4_0])
+@pytest.mark.parametrize("wt", [synth.Q4_K, synth.Q8_0, synth.Q6_K, synth.Q4_0, synth.Q5_K, synth.Q5_0])
 def test_gemm_tile_boundaries(cuda, oracle, wt):
     # the reference suite's row counts around its tile edges (tests/test_kraken.cpp:759), plus ours
     for rows in (9, 13, 16, 37, 255, 256, 257):
         run_gemm(cuda, oracle, wt, 200, 512, rows, SEED + rows)
     run_gemm(cuda, oracle, wt, 129, 256, 300, SEED + 50)
     run_gemm(cuda, oracle, wt, 1000, 1024, 130, SEED + 51)
+    # an odd number of 256-value blocks per row (Q6_K rows then start on every other 2-byte boundary), and
+    # enough K for the staging ring to wrap several times
+    run_gemm(cuda, oracle, wt, 131, 768, 20, SEED + 52)
+    run_gemm(cuda, oracle, wt, 260, 4352, 33, SEED + 53)
 
 
 def test_gemm_f32_activations(cuda, oracle):
