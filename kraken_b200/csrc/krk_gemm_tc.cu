@@ -50,12 +50,28 @@ constexpr int kRawBytes = kTileN * 144;
 // Formats whose 256-value row segment is a multiple of 16 bytes arrive by TMA: Q4_K (144), Q4_0 (8 x 18 = 144),
 // Q5_K (176, two stages in the same area). Q8_0 arrives 128 values at a time: four 34-byte blocks = 136 bytes,
 // which start 0 or 8 bytes after a 16-byte boundary, so a 144-byte box that starts on the boundary covers them.
+
+// Q6_K's 210-byte blocks start on even addresses only, but eight rows on, the address is the same modulo 16
+// (row lengths are even): the rows r = c (mod 8) of the matrix, seen from the 16-byte boundary at or before row
+// c, are a tensor with a 16-byte-multiple pitch. One map per c; a stage is eight boxes of 16 rows x 224 bytes
+// (the 16-byte granules that hold a block), and the 128 staged rows are in the order (c, k) <-> row c + 8k.
+__host__ __device__ constexpr bool row_phased(int wt) { return wt == KRK_CUDA_Q6_K; }
+constexpr int kPhases = 8;
 __host__ __device__ constexpr bool tma_staged(int wt) {
-    return wt == KRK_CUDA_Q4_K || wt == KRK_CUDA_Q4_0 || wt == KRK_CUDA_Q5_K || wt == KRK_CUDA_Q8_0;
+    return wt == KRK_CUDA_Q4_K || wt == KRK_CUDA_Q4_0 || wt == KRK_CUDA_Q5_K || wt == KRK_CUDA_Q8_0 || row_phased(wt);
 }
-__host__ __device__ constexpr int raw_seg(int wt) { return wt == KRK_CUDA_Q5_K ? 176 : 144; }
-__host__ __device__ constexpr int raw_stages(int wt) { return wt == KRK_CUDA_Q5_K ? 2 : 3; }
-static_assert(2 * kTileN * 176 <= kRawStages * kRawBytes, "Q5_K stages fit the raw area");
+__host__ __device__ constexpr int raw_seg(int wt) { return wt == KRK_CUDA_Q5_K ? 176 : wt == KRK_CUDA_Q6_K ? 224 : 144; }
+// Which staged row and which weight row of the tile the decode thread of TMEM lane t works on. Phased formats:
+// a warp's 32 lanes take the rows 32w .. 32w + 31 of the tile (so the read-out writes 32 different banks) in
+// an order whose neighbouring lanes read staged rows on different banks.
+__host__ __device__ constexpr int tile_row(int wt, int t) { return row_phased(wt) ? ((t & 31) >> 2) + 8 * (4 * (t >> 5) + (t & 3)) : t; }
+__host__ __device__ constexpr int tile_slot(int wt, int t) { return row_phased(wt) ? 16 * ((t & 31) >> 2) + 4 * (t >> 5) + (t & 3) : t; }
+struct WMaps {
+    CUtensorMap m[kPhases];   // m[0] alone for the formats staged as one box
+};
+__host__ __device__ constexpr int raw_stages(int wt) { return (wt == KRK_CUDA_Q5_K || wt == KRK_CUDA_Q6_K) ? 2 : 3; }
+constexpr int kRawArea = 2 * kTileN * 224;
+static_assert(2 * kTileN * 176 <= kRawArea && kRawStages * kRawBytes <= kRawArea, "every format's stages fit the raw area");
 constexpr int kDecodeThreads = 256, kEpilogueThreads = 128;   // two decode threads per weight row
 constexpr int kThreads = kDecodeThreads + kEpilogueThreads + 96;
 constexpr int kTmemCols = 512, kTmemA = 256;
@@ -78,7 +94,7 @@ struct GemmParams {
 
 struct __align__(1024) GemmSmem {
     uint8_t b[kBStages][kMaxTileM * 128];      // X tiles, [tokens][64 f16], 128B swizzle (TMA)
-    uint8_t raw[kRawStages][kRawBytes];        // raw block bytes, stages of [128 rows][144 or 176] (TMA), or the decode warps' own staging
+    uint8_t raw[kRawArea];                     // raw block bytes, stages of [128 rows][144, 176 or 224] (TMA), or the decode warps' own staging
     float ystage[2][kYChunk][kTileN];          // accumulator read-out on its way to Y: [tokens][weight rows] (TMA store)
     unsigned long long b_full[kBStages], b_empty[kBStages];
     unsigned long long a_full[kAStages], a_empty[kAStages];
@@ -252,69 +268,55 @@ struct Raw {   // formats without a packed decoder (Q5_0, Q5_1): raw bytes stage
     }
 };
 
-// Q6_K: 210-byte blocks (src/quant.cpp:491-512) start on even addresses only, so a row's block is staged as the
-// 53 aligned words that cover it, beginning 0 or 2 bytes before the block (`lead`, a property of the row and
-// the block index); the odd pitch keeps the 128 rows on different banks. The decoder shifts each pair of
-// neighbouring words by 8 * lead bits to get the block's own words and converts four quants at a time.
+// Q6_K: the staged slot of a row holds its 210-byte block (src/quant.cpp:491-512) `lead` bytes (even, 0..14)
+// after the slot's 16-byte-aligned start. A thread (half h of its row) takes what its four chunks need into
+// registers at once: for each 128-value half hf the 32 ql bytes at 64 hf + 32 h and the 32 qh bytes at
+// 128 + 32 hf, each read as three 128-bit words and moved down by lead's word and half-word parts; its four
+// scale pairs; d. Chunk c = 2j + h then is quad = c & 3 of half hf = j >> 1: the low (quad < 2) or high nibbles
+// of those ql bytes and bit pair `quad` of the qh bytes, four quants per step.
 template <>
 struct Raw<KRK_CUDA_Q6_K> {
     static constexpr int kSteps = 4;
-    static constexpr int kWords = 53, kN = kTileN * kWords, kPer = (kN + kDecodeThreads - 1) / kDecodeThreads;
-    static_assert(2 * kN * 4 <= kRawStages * kRawBytes, "two stages must fit the raw staging area");
-    uint32_t pre[kPer];
-    const uint32_t *stage;
-    int lead = 0, lead_next = 0;
-    __device__ __forceinline__ void fetch(const uint8_t *w, int64_t n0, int64_t n_out, int row_bytes, int ks, int tid) {
-        const size_t seg = (size_t)(ks >> 2) * 210;
-        const size_t total = (size_t)n_out * row_bytes;   // the last word of the last row's last block may end 2 bytes past it
-        lead_next = (int)(((size_t)(n0 + (tid & 127)) * row_bytes + seg) & 2);
+    uint32_t ql[2][8], qh[2][8], sc[4], dbits;
+    int lead = 0;
+    // the eight words that start `o` bytes (even) into the slot
+    __device__ __forceinline__ static void window(const uint8_t *slot, int o, uint32_t (&y)[8]) {
+        const uint4 *b = reinterpret_cast<const uint4 *>(slot + (o & ~15));
+        const uint4 v0 = b[0], v1 = b[1], v2 = b[2];
+        uint32_t x[12] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w, v2.x, v2.y, v2.z, v2.w};
+        const bool by2 = (o & 8) != 0, by1 = (o & 4) != 0;
 #pragma unroll
-        for (int j = 0; j < kPer; j++) {
-            const int i = tid + j * kDecodeThreads;
-            const int rr = i / kWords, col = i - rr * kWords;
-            const size_t at = (((size_t)(n0 + rr) * row_bytes + seg) & ~(size_t)3) + 4 * (size_t)col;
-            const bool ok = i < kN && n0 + rr < n_out;
-            uint32_t v = 0u;
-            if (ok && at + 4 <= total) v = __ldg(reinterpret_cast<const uint32_t *>(w + at));
-            else if (ok && at + 2 <= total) v = __ldg(reinterpret_cast<const unsigned short *>(w + at));   // d of the very last block
-            pre[j] = v;
-        }
-    }
-    __device__ __forceinline__ void stash(uint8_t *dst, int tid) {
+        for (int i = 0; i < 10; i++) x[i] = by2 ? x[i + 2] : x[i];
 #pragma unroll
-        for (int j = 0; j < kPer; j++) {
-            const int i = tid + j * kDecodeThreads;
-            if (i < kN) reinterpret_cast<uint32_t *>(dst)[i] = pre[j];
-        }
-        stage = reinterpret_cast<const uint32_t *>(dst);
-        lead = lead_next;
+        for (int i = 0; i < 9; i++) x[i] = by1 ? x[i + 1] : x[i];
+        const int sh = 8 * (o & 2);
+#pragma unroll
+        for (int i = 0; i < 8; i++) y[i] = __funnelshift_r(x[i], x[i + 1], sh);
     }
-    // chunk c = 2j + half of the block: quad = c & 3 of 128-value half hf = c >> 2 takes the low (quad < 2) or
-    // high nibbles of 32 ql bytes and bit pair `quad` of 32 qh bytes; two int8 scales; f16 d. f16(d * scale) is
-    // formed in f32 as the host decoder forms d * scale.
-    __device__ __forceinline__ void convert(int j, int half, int r, uint32_t (&out)[16]) const {
-        const uint32_t *rw = stage + r * kWords;
-        const int sh = 8 * lead;
+    __device__ __forceinline__ void load_block(const uint8_t *slot, int half, int) {
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+            window(slot, lead + 64 * hf + 32 * half, ql[hf]);
+            window(slot, lead + 128 + 32 * hf, qh[hf]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            sc[j] = *reinterpret_cast<const unsigned short *>(slot + lead + 192 + 8 * (j >> 1) + 4 * (j & 1) + 2 * half);
+        dbits = *reinterpret_cast<const unsigned short *>(slot + lead + 208);
+    }
+    // f16(d * scale) is formed in f32 as the host decoder forms d * scale.
+    __device__ __forceinline__ void convert(int j, int half, int, uint32_t (&out)[16]) const {
         const int hf = j >> 1, nib = (j & 1) ? 4 : 0, hs = 4 * (j & 1) + 2 * half;
-        const uint32_t *qlw = rw + 16 * hf + 8 * half, *qhw = rw + 32 + 8 * hf;
-        const int so = 192 + 8 * hf + 4 * (j & 1) + 2 * half + lead;   // the two scales, an aligned 16-bit pair
-        const uint32_t spair = rw[so >> 2] >> (8 * (so & 2));
-        const uint32_t dbits = rw[(208 + lead) >> 2] >> (8 * ((208 + lead) & 2));
-        const float d = __half2float(__ushort_as_half((unsigned short)(dbits & 0xFFFF)));
-        const __half2 dl0 = __float2half2_rn(__fmul_rn(d, (float)(int8_t)(spair & 0xFF)));
-        const __half2 dl1 = __float2half2_rn(__fmul_rn(d, (float)(int8_t)((spair >> 8) & 0xFF)));
+        const float d = __half2float(__ushort_as_half((unsigned short)dbits));
+        const __half2 dl0 = __float2half2_rn(__fmul_rn(d, (float)(int8_t)(sc[j] & 0xFF)));
+        const __half2 dl1 = __float2half2_rn(__fmul_rn(d, (float)(int8_t)(sc[j] >> 8)));
         const __half2 bias = __float2half2_rn(1056.0f);   // 0x6400 | q is the half 1024 + q; the quant is q - 32
-        uint32_t a = qlw[0], b = qhw[0];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            const uint32_t a1 = qlw[i + 1], b1 = qhw[i + 1];
-            const uint32_t lo = (__funnelshift_r(a, a1, sh) >> nib) & 0x0F0F0F0Fu;
-            const uint32_t hi = ((__funnelshift_r(b, b1, sh) >> hs) & 0x03030303u) << 4;
-            const uint32_t t = lo | hi;
+            const uint32_t t = ((ql[hf][i] >> nib) & 0x0F0F0F0Fu) | (((qh[hf][i] >> hs) & 0x03030303u) << 4);
             const __half2 dl = i < 4 ? dl0 : dl1;
             out[2 * i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(t, 0x64646464u, 0x5140)), bias), dl));
             out[2 * i + 1] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(t, 0x64646464u, 0x7362)), bias), dl));
-            a = a1, b = b1;
         }
     }
 };
@@ -555,7 +557,7 @@ struct ItemIter {
 template <int WT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap x_map,
-               const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap y_map) {
+               const __grid_constant__ WMaps w_maps, const __grid_constant__ CUtensorMap y_map) {
     constexpr bool kStagedRaw = tma_staged(WT);
     constexpr int kSeg = raw_seg(WT), kNRaw = raw_stages(WT);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -600,19 +602,21 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     if (warp < 8) {
         // ===== decode warps: threads r and r + 128 <-> weight row r = TMEM lane r, 32 values each =====
         const int r = tid & 127, half = tid >> 7;
+        const int trow = tile_row(WT, r), tslot = tile_slot(WT, r);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + kTmemA + 16 * half;
         int sa = 0, sr = 0;
         uint32_t pa = 0, pr = 0;
         while (iter.next(it)) {
             const int64_t n0 = (int64_t)(it.tile / p.n_tiles_m) * kTileN;
-            const bool valid = n0 + r < p.n_out;
-            const uint8_t *row = p.w + (size_t)(valid ? n0 + r : 0) * p.row_bytes;
+            const bool valid = n0 + trow < p.n_out;
             Raw<WT> cur;
             if constexpr (!kStagedRaw) cur.fetch(p.w, n0, p.n_out, p.row_bytes, it.k0, tid);
             for (int ks0 = it.k0; ks0 < it.k0 + it.nk; ks0 += Raw<WT>::kSteps) {
                 if constexpr (kStagedRaw) {
                     wait_phase(smem_u32(&sm->raw_full[sr]), pr, gave_up, p.status);
-                    cur.load_block(&sm->raw[0][0] + (size_t)sr * (kTileN * kSeg) + r * kSeg, half, ks0);
+                    if constexpr (row_phased(WT))
+                        cur.lead = (int)(((size_t)trow * p.row_bytes + (size_t)(ks0 >> 2) * 210) & 15);   // n0 rows are a multiple of 16 bytes
+                    cur.load_block(sm->raw + (size_t)sr * (kTileN * kSeg) + tslot * kSeg, half, ks0);
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&sm->raw_empty[sr]));   // the bytes are in registers now
                     if (++sr == kNRaw) {
@@ -623,7 +627,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     // The bytes fetched a stage ago go to the buffer nobody reads any more (the one before
                     // last); one barrier of the decode warps makes them visible, and the next stage's loads
                     // fly while this one is decoded.
-                    cur.stash(&sm->raw[0][0] + (size_t)(sr & 1) * (kRawStages * kRawBytes / 2), tid);
+                    cur.stash(sm->raw + (size_t)(sr & 1) * (kRawStages * kRawBytes / 2), tid);
                     sr++;
                     asm volatile("bar.sync 1, %0;" ::"n"(kDecodeThreads) : "memory");
                     if (ks0 + Raw<WT>::kSteps < it.k0 + it.nk)
@@ -667,7 +671,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         auto ship = [&](const uint32_t (&v)[32], const CUtensorMap *map, int x, int y, bool add) {
             if (et == 0) tma_store_wait_read<1>();   // the store that read this buffer two chunks ago is done with it
             asm volatile("bar.sync 2, %0;" ::"n"(kEpilogueThreads) : "memory");
-            float *dst = &sm->ystage[ybuf][0][32 * ew + lane];
+            float *dst = &sm->ystage[ybuf][0][tile_row(WT, 32 * ew + lane)];
 #pragma unroll
             for (int j = 0; j < 32; j++) dst[j * kTileN] = __uint_as_float(v[j]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -694,7 +698,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             wait_phase(smem_u32(&sm->d_full), ph, gave_up, p.status);
             ph ^= 1;
             tc_fence_after();
-            const int64_t n = n0 + 32 * ew + lane;
+            const int64_t n = n0 + tile_row(WT, 32 * ew + lane);
             if (!it.partial) {
                 for (int c0 = 0; c0 < p.tile_m; c0 += kYChunk) {
                     uint32_t v[32];
@@ -773,8 +777,31 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             }
         }
     } else if (warp == 13) {
-        // ===== TMA producer of raw Q4_K super-block columns: 144 bytes x 128 rows each =====
-        if (kStagedRaw && lane == 0) {
+        // ===== producer of raw block columns: one TMA box of 128 rows per stage, or one bulk copy per row =====
+        if constexpr (row_phased(WT)) {
+            if (lane == 0) {
+                int sr = 0;
+                uint32_t pr = 0;
+                while (iter.next(it)) {
+                    const int n0 = (it.tile / p.n_tiles_m) * kTileN;
+                    for (int blk = it.k0 / 4; blk < (it.k0 + it.nk) / 4; blk++) {
+                        wait_phase(smem_u32(&sm->raw_empty[sr]), pr ^ 1, gave_up, p.status);
+                        const uint32_t bar = smem_u32(&sm->raw_full[sr]);
+                        mbar_arrive_expect_tx(bar, (uint32_t)(kTileN * kSeg));
+                        const uint32_t stage = smem_u32(sm->raw + (size_t)sr * (kTileN * kSeg));
+                        for (int c = 0; c < kPhases; c++) {
+                            // map c starts (c * row_bytes) % 16 bytes before row c; the block's granules from there
+                            const int x0 = (int)((((size_t)c * p.row_bytes) & 15) + (size_t)blk * 210) & ~15;
+                            tma_load_2d(stage + c * (kTileN / kPhases) * kSeg, &w_maps.m[c], x0, n0 / kPhases, bar);
+                        }
+                        if (++sr == kNRaw) {
+                            sr = 0;
+                            pr ^= 1;
+                        }
+                    }
+                }
+            }
+        } else if (kStagedRaw && lane == 0) {
             int sr = 0;
             uint32_t pr = 0;
             while (iter.next(it)) {
@@ -785,7 +812,7 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     const uint32_t bar = smem_u32(&sm->raw_full[sr]);
                     mbar_arrive_expect_tx(bar, (uint32_t)(kTileN * kSeg));
                     const int x0 = WT == KRK_CUDA_Q8_0 ? 136 * blk - 8 * (blk & 1) : blk * kSeg;   // a multiple of 16
-                    tma_load_2d(smem_u32(&sm->raw[0][0] + (size_t)sr * (kTileN * kSeg)), &w_map, x0, n0, bar);
+                    tma_load_2d(smem_u32(sm->raw + (size_t)sr * (kTileN * kSeg)), &w_maps.m[0], x0, n0, bar);
                     if (++sr == kNRaw) {
                         sr = 0;
                         pr ^= 1;
@@ -863,7 +890,7 @@ EncodeTiledFn encode_tiled() {
 bool encode_w_map(CUtensorMap *map, const uint8_t *w, int wt, int64_t n_out, int row_bytes) {
     EncodeTiledFn encode = encode_tiled();
     if (!encode) return false;
-    const bool staged = tma_staged(wt);
+    const bool staged = tma_staged(wt) && !row_phased(wt);   // phased formats: encode_phase_maps
     const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)n_out};
     const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
     const cuuint32_t box[2] = {staged ? (cuuint32_t)raw_seg(wt) : 16u, staged ? (cuuint32_t)kTileN : 1u};
@@ -877,6 +904,28 @@ bool encode_w_map(CUtensorMap *map, const uint8_t *w, int wt, int64_t n_out, int
     }
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Phased formats: map c covers the rows c, c + 8, c + 16, ... of the matrix from the 16-byte boundary at or before
+// row c: inner extent = the lead bytes + one row (so nothing past a row's own end is ever read, and what the box
+// holds beyond it is zero fill), pitch = eight rows, box = 224 bytes x 16 rows. A c with no row at all (fewer than
+// eight rows in the matrix) repeats map 0; its staged rows are never used.
+bool encode_phase_maps(WMaps *maps, const uint8_t *w, int64_t n_out, int row_bytes) {
+    EncodeTiledFn encode = encode_tiled();
+    if (!encode) return false;
+    const cuuint32_t box[2] = {224u, (cuuint32_t)(kTileN / kPhases)};
+    const cuuint32_t estr[2] = {1, 1};
+    for (int c = 0; c < kPhases; c++) {
+        const int cc = c < n_out ? c : 0;
+        const size_t start = (size_t)cc * row_bytes, lead = start & 15;
+        const cuuint64_t dims[2] = {(cuuint64_t)(lead + row_bytes), (cuuint64_t)((n_out - cc + kPhases - 1) / kPhases)};
+        const cuuint64_t strides[1] = {(cuuint64_t)kPhases * row_bytes};
+        if (encode(&maps->m[c], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w + (start - lead)), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return false;
+    }
+    return true;
 }
 
 // Tensor map over Y as a [rows][n_out] f32 matrix, box = 128 weight rows x kYChunk tokens, for the TMA stores
@@ -902,8 +951,11 @@ bool encode_y_map(CUtensorMap *map, float *y, const uint8_t *w, int64_t n_out, i
 
 template <int WT>
 int launch_wt(const GemmParams &p, const CUtensorMap &map, int grid, cudaStream_t st) {
-    CUtensorMap w_map, y_map;
-    if (!encode_w_map(&w_map, p.w, WT, p.n_out, p.row_bytes)) return KRK_CUDA_ELAUNCH;
+    WMaps w_maps;
+    CUtensorMap y_map;
+    if (!encode_w_map(&w_maps.m[0], p.w, WT, p.n_out, p.row_bytes)) return KRK_CUDA_ELAUNCH;
+    for (int c = 1; c < kPhases; c++) w_maps.m[c] = w_maps.m[0];
+    if (row_phased(WT) && !encode_phase_maps(&w_maps, p.w, p.n_out, p.row_bytes)) return KRK_CUDA_ELAUNCH;
     if (!encode_y_map(&y_map, p.y, p.w, p.n_out, p.rows, p.y_tma != 0)) return KRK_CUDA_ELAUNCH;
     static bool configured[64] = {};
     auto kernel = gemm_tc_kernel<WT>;
@@ -918,7 +970,7 @@ int launch_wt(const GemmParams &p, const CUtensorMap &map, int grid, cudaStream_
         }
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kernel<<<grid, kThreads, smem, st>>>(p, map, w_map, y_map);
+    kernel<<<grid, kThreads, smem, st>>>(p, map, w_maps, y_map);
     note_launch(1, KRK_CUDA_FAMILY_GEMM_TC);
     return check_launch();
 }
