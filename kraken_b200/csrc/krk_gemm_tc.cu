@@ -14,14 +14,16 @@
 // bytes, which leaves its bandwidth to the one operand the MMA still reads from it.
 //
 // One persistent CTA per SM, warp-specialised, everything connected by mbarriers:
-//   warps 0..7   decode: two threads per weight row, 32 values each per 64-value K step. Q4_K
-//                super-blocks arrive in shared memory by TMA (a 2-D tensor map over the raw byte
-//                matrix, box = 144 bytes x 128 rows, three super-blocks ahead); other formats are
-//                read from global memory element-wise. 16 x 32-bit TMEM columns per thread and step;
+//   warps 0..7   decode: two threads per weight row, 32 values each per 64-value K step. The raw blocks of
+//                128 rows x 256 values (Q8_0: 128 values) arrive in shared memory by TMA: a 2-D tensor map
+//                over the raw byte matrix for Q4_K / Q4_0 / Q5_K / Q8_0, eight maps (rows 8 apart) for
+//                Q6_K, whose rows do not start on 16-byte boundaries; a thread takes its row's bytes into
+//                registers and decodes with packed half2 arithmetic. Q5_0 / Q5_1 are staged by the decode
+//                warps themselves and decoded element by element. 16 x 32-bit TMEM columns per thread and step;
 //   warps 8..11  epilogue: tcgen05.ld of the accumulator (warp w%4 owns TMEM lanes 32*(w%4)..), 32 tokens
 //                at a time into a [token][weight row] staging buffer in shared memory, TMA stores of Y;
 //   warp 12      TMA producer of X tiles (cp.async.bulk.tensor.2d, each CTA loads its own copy);
-//   warp 13      TMA producer of raw Q4_K super-block columns;
+//   warp 13      TMA producer of the raw block columns;
 //   warp 14      TMEM allocation and the single thread that issues tcgen05.mma / tcgen05.commit.
 // Tensor memory: columns 0..255 the accumulator, 256..511 eight A stages of 32 columns.
 //
