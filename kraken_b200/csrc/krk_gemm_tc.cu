@@ -635,17 +635,19 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     if (ks0 + Raw<WT>::kSteps < it.k0 + it.nk)
                         cur.fetch(p.w, n0, p.n_out, p.row_bytes, ks0 + Raw<WT>::kSteps, tid);
                 }
+                // The next K step is converted while this one's tensor-memory store is in flight.
+                uint32_t v[2][16];
+                cur.convert(0, half, r, v[0]);
 #pragma unroll
                 for (int j = 0; j < Raw<WT>::kSteps; j++) {
-                    uint32_t v[16];
-                    cur.convert(j, half, r, v);
                     if (!valid) {
 #pragma unroll
-                        for (int i = 0; i < 16; i++) v[i] = 0u;
+                        for (int i = 0; i < 16; i++) v[j & 1][i] = 0u;
                     }
                     wait_phase(smem_u32(&sm->a_empty[sa]), pa ^ 1, gave_up, p.status);
                     tc_fence_after();
-                    tmem_st16(lane_addr + 32 * sa, v);
+                    tmem_st16(lane_addr + 32 * sa, v[j & 1]);
+                    if (j + 1 < Raw<WT>::kSteps) cur.convert(j + 1, half, r, v[(j + 1) & 1]);
                     tmem_st_wait();
                     tc_fence_before();
                     __syncwarp();
