@@ -180,6 +180,12 @@ int krk_cuda_moe_ffn_routed(void *y_f32, const void *x_f32, const void *router_l
 int krk_cuda_silu_mul(void *out_f32, const void *gate_f32, const void *up_f32, int64_t n,
                       void *stream);
 
+/* dst[i] = src[rows[i]] over rows of n floats (Backend::gather_rows, include/krk/backend.hpp:1451):
+ * the permute that puts the tokens of one expert into a contiguous block. rows: n_rows device i32;
+ * dst must not overlap src. */
+int krk_cuda_gather_rows(void *dst_f32, const void *src_f32, const void *rows_i32, int64_t n_rows,
+                         int64_t n, void *stream);
+
 /* dst[rows[i]] += alpha[i] * src[i] over rows of n floats (Backend::scatter_axpy_rows,
  * include/krk/backend.hpp:1473; src/backend_cpu.cpp:3193-3220). Row indices must be
  * distinct within one call. */

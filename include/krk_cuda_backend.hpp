@@ -67,6 +67,10 @@ public:
 
     void silu_mul(void *out, const void *gate, const void *up, i64 n, i64 row_len = 0,
                   f32 *row_scale = nullptr);                     // backend.hpp:1309
+    // silu_mul over `count` one-row buffers (backend.hpp:1320): exactly `count` silu_mul calls, scale[i] = 1.0
+    void silu_mul_rows(void *const out[], const void *const gate[], const void *const up[], i64 row_len, int count,
+                       f32 *const scale[]);
+    void gather_rows(void *dst, const void *src, const i32 *rows, i64 n_rows, i64 n);   // backend.hpp:1451
     void scatter_axpy_rows(void *dst, const void *src, const i32 *rows, const f32 *alpha,
                            i64 n_rows, i64 n, const f32 *row_scale = nullptr,
                            i32 *row_exp = nullptr);              // backend.hpp:1473

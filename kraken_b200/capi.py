@@ -62,6 +62,7 @@ SIGNATURES = {
     "krk_cuda_moe_ffn": (_int, [_vp, _vp, _vp, _vp, C.POINTER(ExpertBank), _int, _i64, _vp, _sz, _vp]),
     "krk_cuda_moe_ffn_routed": (_int, [_vp, _vp, _vp, _int, _vp, _vp, C.POINTER(ExpertBank), _int, _i64, _vp, _sz, _vp]),
     "krk_cuda_silu_mul": (_int, [_vp, _vp, _vp, _i64, _vp]),
+    "krk_cuda_gather_rows": (_int, [_vp, _vp, _vp, _i64, _i64, _vp]),
     "krk_cuda_scatter_axpy_rows": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     "krk_cuda_sum_parts": (_int, [_vp, _vp, _int, _i64, _vp]),
     "krk_cuda_gemv_allgather": (_int, [C.POINTER(_vp), C.POINTER(_vp), _int, _int, _int, _int, _i64, _i64, _vp, _vp, _int, _i64,
@@ -247,6 +248,13 @@ def silu_mul(gate, up, out=None, stream=None):
         out = torch.empty_like(gate)
     _check(lib.krk_cuda_silu_mul(_ptr(out), _ptr(gate), _ptr(up), gate.numel(), _stream_ptr(stream)), "silu_mul")
     return out
+
+
+def gather_rows(dst, src, rows, stream=None):
+    """dst[i] = src[rows[i]]; dst [n_rows][n] f32, rows device i32."""
+    _check(lib.krk_cuda_gather_rows(_ptr(dst), _ptr(src), _ptr(rows), dst.shape[0], dst.shape[1],
+                                    _stream_ptr(stream)), "gather_rows")
+    return dst
 
 
 def scatter_axpy_rows(dst, src, rows, alpha, stream=None):

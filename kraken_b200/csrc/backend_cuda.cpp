@@ -163,6 +163,18 @@ void CudaBackend::silu_mul(void *out, const void *gate, const void *up, i64 n, i
         for (i64 r = 0; r < n / row_len; r++) row_scale[r] = 1.0f;
 }
 
+void CudaBackend::silu_mul_rows(void *const out[], const void *const gate[], const void *const up[], i64 row_len,
+                                int count, f32 *const scale[]) {
+    // The reference's default is `count` silu_mul calls and a batched form has to match them bit for bit
+    // (backend.hpp:1312-1319); the element-wise kernel has no per-launch state, so the calls are the form.
+    for (int i = 0; i < count; i++) silu_mul(out[i], gate[i], up[i], row_len, row_len, scale ? scale[i] : nullptr);
+}
+
+void CudaBackend::gather_rows(void *dst, const void *src, const i32 *rows, i64 n_rows, i64 n) {
+    const int rc = krk_cuda_gather_rows(dst, src, rows, n_rows, n, stream_);
+    if (rc != KRK_CUDA_OK) die("gather_rows", rc, n_rows, n, 0, 0);
+}
+
 void CudaBackend::scatter_axpy_rows(void *dst, const void *src, const i32 *rows, const f32 *alpha, i64 n_rows,
                                     i64 n, const f32 *row_scale, i32 *row_exp) {
     (void)row_scale;   // f32 backends fill it with 1.0 and ignore the exponent (backend.hpp:1306-1308)

@@ -215,6 +215,7 @@ int stream_gran(int wt, int64_t n_in);
 int launch_gemv_stream_table(const StreamTable *table, int wt, int64_t n_in, int silu_pair, cudaStream_t st);
 
 int launch_silu_mul(float *out, const float *gate, const float *up, int64_t n, cudaStream_t st);
+int launch_gather_rows(float *dst, const float *src, const int32_t *rows, int64_t n_rows, int64_t n, cudaStream_t st);
 int launch_scatter_axpy_rows(float *dst, const float *src, const int32_t *rows, const float *alpha,
                              int64_t n_rows, int64_t n, cudaStream_t st);
 int launch_sum_parts(float *out, const float *parts, int n_parts, int64_t n, cudaStream_t st);

@@ -252,6 +252,15 @@ int krk_cuda_silu_mul(void *out_f32, const void *gate_f32, const void *up_f32, i
                            static_cast<const float *>(up_f32), n, static_cast<cudaStream_t>(stream));
 }
 
+int krk_cuda_gather_rows(void *dst_f32, const void *src_f32, const void *rows_i32, int64_t n_rows, int64_t n,
+                         void *stream) {
+    if (n_rows < 0 || n < 0) return KRK_CUDA_ESHAPE;
+    if (n_rows * n > 0 && (!dst_f32 || !src_f32 || !rows_i32)) return KRK_CUDA_ENULL;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_gather_rows(static_cast<float *>(dst_f32), static_cast<const float *>(src_f32),
+                              static_cast<const int32_t *>(rows_i32), n_rows, n, static_cast<cudaStream_t>(stream));
+}
+
 int krk_cuda_scatter_axpy_rows(void *dst_f32, const void *src_f32, const void *rows_i32,
                                const void *alpha_f32, int64_t n_rows, int64_t n, void *stream) {
     if (n_rows < 0 || n < 0) return KRK_CUDA_ESHAPE;

@@ -76,6 +76,37 @@ int launch_scatter_axpy_rows(float *dst, const float *src, const int32_t *rows, 
     return check_launch();
 }
 
+// dst[i][j] = src[rows[i]][j] (Backend::gather_rows, include/krk/backend.hpp:1451): the tokens that picked an
+// expert, permuted into one contiguous block. Four floats per thread where the rows allow it.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(float *__restrict__ dst, const float *__restrict__ src, const int32_t *__restrict__ rows,
+                   int64_t n_rows, int64_t n, int vec) {
+    if (vec) {
+        const int64_t n4 = n >> 2, total = n_rows * n4;
+        for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+            const int64_t r = i / n4, j = i - r * n4;
+            reinterpret_cast<float4 *>(dst)[i] = __ldg(reinterpret_cast<const float4 *>(src + (int64_t)rows[r] * n) + j);
+        }
+        return;
+    }
+    const int64_t total = n_rows * n;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / n, j = i - r * n;
+        dst[i] = src[(int64_t)rows[r] * n + j];
+    }
+}
+
+int launch_gather_rows(float *dst, const float *src, const int32_t *rows, int64_t n_rows, int64_t n, cudaStream_t st) {
+    const int64_t total = n_rows * n;
+    if (total == 0) return KRK_CUDA_OK;
+    const int vec = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) == 0;
+    const int64_t want = ((vec ? total / 4 : total) + 255) / 256;
+    const int grid = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
+    gather_rows_kernel<<<grid, 256, 0, st>>>(dst, src, rows, n_rows, n, vec);
+    note_launch();
+    return check_launch();
+}
+
 // out[j] = ((parts[0][j] + parts[1][j]) + parts[2][j]) + ... : fixed order, so the combined
 // output of an expert-sharded layer has the same bits on every rank and every run.
 __global__ void __launch_bounds__(256)

@@ -125,6 +125,12 @@ class Oracle:
         self.L.krk_oracle_silu_mul(out.reshape(-1), gate.reshape(-1), up.reshape(-1), gate.size)
         return out
 
+    @staticmethod
+    def gather_rows(src, rows):
+        """dst[i * n + j] = src[rows[i] * n + j] (include/krk/backend.hpp:1443-1452): a move of f32 rows, no
+        arithmetic."""
+        return np.ascontiguousarray(_c(src, np.float32)[np.asarray(rows, np.int64)])
+
     def scatter_axpy_rows(self, dst, src, rows, alpha):
         src = _c(src, np.float32)
         self.L.krk_oracle_scatter_axpy_rows(dst.reshape(-1), src.reshape(-1), _c(rows, np.int32),

@@ -58,6 +58,35 @@ int main() {
         if (std::fabs(y[r] - want) > 1e-4f * (std::fabs(want) + 1.0f)) bad++;
     }
     std::printf("%s: %d of %d rows off\n", be->describe(), bad, n_out);
+    // the MoE batching helpers: gather two rows of a 3 x 8 matrix, activate them as two one-row buffers
+    {
+        std::vector<float> m(24), g(16, -7.0f), act(16, -7.0f);
+        for (int i = 0; i < 24; i++) m[i] = 0.25f * (float)(i - 9);
+        const int32_t pick[2] = {2, 0};
+        void *d_m = be->alloc(96), *d_g = be->alloc(64), *d_a = be->alloc(64);
+        int32_t *d_pick = static_cast<int32_t *>(be->alloc(8));
+        be->upload(d_m, m.data(), 96);
+        be->upload_i32(d_pick, pick, 2);
+        be->gather_rows(d_g, d_m, d_pick, 2, 8);
+        be->download(g.data(), d_g, 64);
+        for (int i = 0; i < 8; i++)
+            if (g[i] != m[16 + i] || g[8 + i] != m[i]) bad++;
+        void *outs[2] = {d_a, static_cast<float *>(d_a) + 8};
+        const void *gates[2] = {d_g, static_cast<const float *>(d_g) + 8}, *ups[2] = {d_g, static_cast<const float *>(d_g) + 8};
+        float s0 = 0.0f, s1 = 0.0f;
+        float *scales[2] = {&s0, &s1};
+        be->silu_mul_rows(outs, gates, ups, 8, 2, scales);
+        be->download(act.data(), d_a, 64);
+        for (int i = 0; i < 16; i++) {
+            const float want = g[i] / (1.0f + std::exp(-g[i])) * g[i];
+            if (std::fabs(act[i] - want) > 1e-5f * (std::fabs(want) + 1.0f)) bad++;
+        }
+        if (s0 != 1.0f || s1 != 1.0f) bad++;
+        be->release(d_m);
+        be->release(d_g);
+        be->release(d_a);
+        be->release(d_pick);
+    }
     be->release(d_w);
     be->release(d_x);
     be->release(d_y);

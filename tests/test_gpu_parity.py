@@ -312,6 +312,29 @@ def test_silu_mul_and_scatter(cuda, golden):
     assert dst.cpu().numpy().tobytes() == golden["scatter_out"].tobytes()
 
 
+def test_gather_rows_then_scatter_is_the_weighted_permute(cuda, oracle):
+    """gather_rows (include/krk/backend.hpp:1451) against the oracle's row move, bit for bit, on aligned and odd
+    row lengths, repeated and empty index lists; then gather -> scatter_axpy_rows with alpha 1 onto zeros puts
+    every picked row back where it came from."""
+    import torch
+    rng = np.random.default_rng(SEED + 70)
+    for n_src, n, n_rows in ((64, 4096, 23), (9, 1537, 9), (5, 8, 0), (300, 1536, 300)):
+        src = rng.standard_normal((n_src, n)).astype(np.float32)
+        rows = rng.integers(0, n_src, n_rows).astype(np.int32)
+        dst = torch.empty((n_rows, n), dtype=torch.float32, device="cuda")
+        cuda.gather_rows(dst, dev(src), dev(rows))
+        assert dst.cpu().numpy().tobytes() == oracle.gather_rows(src, rows).tobytes()
+    src = rng.standard_normal((40, 1536)).astype(np.float32)
+    rows = rng.permutation(40)[:17].astype(np.int32)
+    picked = torch.empty((17, 1536), dtype=torch.float32, device="cuda")
+    cuda.gather_rows(picked, dev(src), dev(rows))
+    back = torch.zeros((40, 1536), dtype=torch.float32, device="cuda")
+    cuda.scatter_axpy_rows(back, picked, dev(rows), dev(np.ones(17, np.float32)))
+    want = np.zeros_like(src)
+    want[rows] = src[rows]
+    assert back.cpu().numpy().tobytes() == want.tobytes()
+
+
 # ---- the host-buffer boundary: CudaBackend -------------------------------------------------------
 
 def test_backend_host_buffers_roundtrip(cuda, oracle):
