@@ -610,7 +610,8 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         uint32_t pa = 0, pr = 0;
         while (iter.next(it)) {
             const int64_t n0 = (int64_t)(it.tile / p.n_tiles_m) * kTileN;
-            const bool valid = n0 + trow < p.n_out;
+            // Rows past n_out need no care here: their staged bytes are zero (the tensor maps fill what lies
+            // outside the matrix with zeros, and fetch() does the same), and a zero block decodes to zeros.
             Raw<WT> cur;
             if constexpr (!kStagedRaw) cur.fetch(p.w, n0, p.n_out, p.row_bytes, it.k0, tid);
             for (int ks0 = it.k0; ks0 < it.k0 + it.nk; ks0 += Raw<WT>::kSteps) {
@@ -640,10 +641,6 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                 cur.convert(0, half, r, v[0]);
 #pragma unroll
                 for (int j = 0; j < Raw<WT>::kSteps; j++) {
-                    if (!valid) {
-#pragma unroll
-                        for (int i = 0; i < 16; i++) v[j & 1][i] = 0u;
-                    }
                     wait_phase(smem_u32(&sm->a_empty[sa]), pa ^ 1, gave_up, p.status);
                     tc_fence_after();
                     tmem_st16(lane_addr + 32 * sa, v[j & 1]);
@@ -796,7 +793,9 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         for (int c = 0; c < kPhases; c++) {
                             // map c starts (c * row_bytes) % 16 bytes before row c; the block's granules from there
                             const int x0 = (int)((((size_t)c * p.row_bytes) & 15) + (size_t)blk * 210) & ~15;
-                            tma_load_2d(stage + c * (kTileN / kPhases) * kSeg, &w_maps.m[c], x0, n0 / kPhases, bar);
+                            // a matrix of fewer than eight rows has no row c: read outside the map, which fills zeros
+                            const int y0 = c < p.n_out ? n0 / kPhases : (1 << 24);
+                            tma_load_2d(stage + c * (kTileN / kPhases) * kSeg, &w_maps.m[c], x0, y0, bar);
                         }
                         if (++sr == kNRaw) {
                             sr = 0;
