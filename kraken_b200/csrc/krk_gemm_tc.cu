@@ -25,7 +25,7 @@
 //   warp 12      TMA producer of X tiles (cp.async.bulk.tensor.2d, each CTA loads its own copy);
 //   warp 13      TMA producer of the raw block columns;
 //   warp 14      TMEM allocation and the single thread that issues tcgen05.mma / tcgen05.commit.
-// Tensor memory: columns 0..255 the accumulator, 256..511 eight A stages of 32 columns.
+// Tensor memory: columns 0..255 the accumulator, 256..511 four A stages of 64 columns (two K steps each).
 //
 // Same contract as gemm_wmma_kernel of the reference (src/hip/kernels/gemm.hpp:621-970): f16
 // staged operands, f32 accumulation; here the output stays f32.
@@ -46,7 +46,7 @@ constexpr int kTileN = 128;            // weight rows per tile (MMA M)
 constexpr int kMaxTileM = 256;         // tokens per tile (MMA N)
 constexpr int kBK = 64;                // K values per step: one 128-byte swizzle row of f16 X, 32 TMEM columns of A
 constexpr int kBStages = 4;            // X tiles in shared memory
-constexpr int kAStages = 8;            // decoded weight tiles in tensor memory
+constexpr int kAStages = 4;            // decoded weight tiles in tensor memory, two K steps (64 columns) each
 constexpr int kRawStages = 3;          // raw block columns (256 values x 128 rows) in shared memory, at most
 constexpr int kRawBytes = kTileN * 144;
 // Formats whose 256-value row segment is a multiple of 16 bytes arrive by TMA: Q4_K (144), Q4_0 (8 x 18 = 144),
@@ -636,22 +636,27 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     if (ks0 + Raw<WT>::kSteps < it.k0 + it.nk)
                         cur.fetch(p.w, n0, p.n_out, p.row_bytes, ks0 + Raw<WT>::kSteps, tid);
                 }
-                // The next K step is converted while this one's tensor-memory store is in flight.
+                // Two K steps share one tensor-memory stage and one hand-over to the MMA thread; the next K step
+                // is converted while this one's store is in flight.
                 uint32_t v[2][16];
                 cur.convert(0, half, r, v[0]);
 #pragma unroll
                 for (int j = 0; j < Raw<WT>::kSteps; j++) {
-                    wait_phase(smem_u32(&sm->a_empty[sa]), pa ^ 1, gave_up, p.status);
-                    tc_fence_after();
-                    tmem_st16(lane_addr + 32 * sa, v[j & 1]);
+                    if ((j & 1) == 0) {
+                        wait_phase(smem_u32(&sm->a_empty[sa]), pa ^ 1, gave_up, p.status);
+                        tc_fence_after();
+                    }
+                    tmem_st16(lane_addr + 64 * sa + 32 * (j & 1), v[j & 1]);
                     if (j + 1 < Raw<WT>::kSteps) cur.convert(j + 1, half, r, v[(j + 1) & 1]);
-                    tmem_st_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&sm->a_full[sa]));
-                    if (++sa == kAStages) {
-                        sa = 0;
-                        pa ^= 1;
+                    if (j & 1) {
+                        tmem_st_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&sm->a_full[sa]));
+                        if (++sa == kAStages) {
+                            sa = 0;
+                            pa ^= 1;
+                        }
                     }
                 }
             }
@@ -833,20 +838,22 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                 wait_phase(smem_u32(&sm->d_empty), pd ^ 1, gave_up, p.status);   // the epilogue has drained the accumulator
                 pd ^= 1;
                 tc_fence_after();
-                for (int ks = 0; ks < it.nk; ks++) {
+                for (int ks = 0; ks < it.nk; ks++) {   // nk is even: a stage of decoded A holds two K steps
                     wait_phase(smem_u32(&sm->b_full[sb]), pb, gave_up, p.status);
-                    wait_phase(smem_u32(&sm->a_full[sa]), pa, gave_up, p.status);
+                    if ((ks & 1) == 0) wait_phase(smem_u32(&sm->a_full[sa]), pa, gave_up, p.status);
                     tc_fence_after();
                     const uint64_t bdesc = smem_desc(smem_u32(sm->b[sb]));
-                    const uint32_t a_tmem = tmem_base + kTmemA + 32 * sa;
+                    const uint32_t a_tmem = tmem_base + kTmemA + 64 * sa + 32 * (ks & 1);
 #pragma unroll
                     for (int kk = 0; kk < kBK / 16; kk++)   // 16 K values = 8 TMEM columns of A, 32 bytes of every B row
                         umma_f16_ts(tmem_base, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, (ks | kk) ? 1u : 0u);
-                    umma_commit(smem_u32(&sm->a_empty[sa]));   // both stages are free once these MMAs have read them
-                    umma_commit(smem_u32(&sm->b_empty[sb]));
-                    if (++sa == kAStages) {
-                        sa = 0;
-                        pa ^= 1;
+                    umma_commit(smem_u32(&sm->b_empty[sb]));   // a stage is free once the MMAs that read it are done
+                    if (ks & 1) {
+                        umma_commit(smem_u32(&sm->a_empty[sa]));
+                        if (++sa == kAStages) {
+                            sa = 0;
+                            pa ^= 1;
+                        }
                     }
                     if (++sb == kBStages) {
                         sb = 0;
