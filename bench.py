@@ -187,6 +187,43 @@ def device_weights(torch, n_out: int, n_in: int, gen):
     return w.view(n_out, nblk * 144)
 
 
+def workload_config(layers: int, world: int) -> dict:
+    """The `config` of the bench line: the same dictionary from both arms."""
+    return {"workload": WORKLOAD, "weight_type": "Q4_K", "batch": 1, "layers": layers,
+            "matmuls_per_layer": [list(s) for s in LAYER_SHAPES],
+            "weight_bytes_per_step": layer_weight_bytes() * layers, "parallelism": f"replicas x{world}",
+            "l2": "inputs larger than L2: every layer of a step has its own weights in memory, each byte read once per step"}
+
+
+def layer_shift(li: int, n_out: int) -> int:
+    """Rows by which layer li's matrices are rotated against layer 0's (layer li row r = layer 0 row r + shift)."""
+    return (li * 1031) % n_out
+
+
+def check_step(torch, layers, base, grouped):
+    """What the timed step computes, against the CPU checker, before anything is timed: the four outputs of
+    layer 0 and of the last layer within 1e-4 * ||w_row|| * ||x|| of the exact scalar chain on the same bytes
+    (the last layer's rows are layer 0's rotated, so the checker multiplies layer 0's matrix by that layer's x)."""
+    from oracle.krk_oracle import Oracle
+    orc = Oracle()
+    worst = 0.0
+    for li in sorted({0, len(layers) - 1}):
+        for mi, (w_np, _, n_out, n_in) in enumerate(base):
+            _, x, y, _, _ = layers[li][mi]
+            x_np = x.cpu().numpy().reshape(1, -1)
+            ref = orc.gemm(x_np, w_np, WT, n_out, n_in, threads=os.cpu_count() or 1)[0]
+            wd = orc.dequant_rows(w_np, WT, n_out, n_in).astype(np.float64)
+            lim = 1e-4 * np.sqrt((wd ** 2).sum(axis=1)) * np.sqrt((x_np.astype(np.float64) ** 2).sum())
+            got = np.roll(y.cpu().numpy().astype(np.float64), layer_shift(li, n_out))
+            err = np.abs(got - ref)
+            if not (err <= lim).all():
+                raise AssertionError(f"bench step differs from the CPU checker: layer {li} matmul {mi}, "
+                                     f"worst {float((err / lim).max()):.3g} of the bound")
+            worst = max(worst, float((err / np.maximum(lim, 1e-300)).max()))
+    return {"layers_checked": sorted({0, len(layers) - 1}), "bound": "1e-4 * ||w_row|| * ||x||",
+            "worst_fraction_of_bound": round(worst, 5)}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -201,12 +238,18 @@ def run_ours(args):
 
     gen = torch.Generator(device="cuda")
     gen.manual_seed(synth.BASE_SEED % (2 ** 63) + 2 + 1000 * rank)
+    # Layer 0 is the seeded synthetic layer the CPU legs use, byte for byte (synth.weights / synth.activations
+    # with the same seed and streams). The other layers hold the same rows rotated by a layer-specific count:
+    # every row keeps the format's field distributions, every layer has its own 85 MB in HBM (2.74 GB of distinct
+    # addresses per step), and any layer's output is layer 0's rotated, so the checker can vouch for all of them.
+    base = cpu_layer()
+    base_dev = [(torch.from_numpy(w).cuda(), n_out, n_in) for w, _, n_out, n_in in base]
     layers = []
-    for _ in range(args.layers):
+    for li in range(args.layers):
         mats = []
-        for n_out, n_in in LAYER_SHAPES:
-            w = device_weights(torch, n_out, n_in, gen)
-            x = torch.randn(n_in, device="cuda", generator=gen)
+        for mi, (w0, n_out, n_in) in enumerate(base_dev):
+            w = w0 if li == 0 else torch.roll(w0, shifts=-layer_shift(li, n_out), dims=0).contiguous()
+            x = torch.from_numpy(synth.activations(1, n_in, synth.BASE_SEED + 2, stream=200 + mi + 10 * li)).cuda().view(-1)
             y = torch.empty(n_out, device="cuda")
             mats.append((w, x, y, n_out, n_in))
         layers.append(mats)
@@ -242,6 +285,7 @@ def run_ours(args):
     barrier()
     assert capi.device_status() == 0, "a device-side wait gave up during warm-up"
     assert all(torch.isfinite(m[2]).all() for m in layers[0])
+    checked = check_step(torch, layers, base, grouped) if rank == 0 and not args.no_check else None
 
     # The step's launches are captured once into a CUDA graph and replayed: same kernels, same
     # order, without a host round trip per launch (a decode loop replays a fixed launch sequence).
@@ -359,13 +403,10 @@ def run_ours(args):
             "warmup": max(args.warmup, 3), "ms_per_step": round(per_step_ms, 5), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "s8 quants x 24-bit fixed-point activations, f32 scales",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "weight_type": "Q4_K", "batch": 1, "layers": args.layers,
-                       "matmuls_per_layer": [list(s) for s in LAYER_SHAPES],
-                       "weight_bytes_per_step": wbytes, "parallelism": f"replicas x{world}",
-                       "launch": "host launches" if args.no_graph else "CUDA graph replay of the step's launches",
-                       "launches_per_layer": ("3: gemm(4096x4096), gemm_group(gate, up), gemm(4096x11008) - the engine's call pattern"
-                                              if grouped else "4: one gemm per matrix"),
-                       "l2": "inputs larger than L2: 2.74 GB of distinct weights per step, each byte read once"},
+            "config": workload_config(args.layers, world),
+            "run": {"launch": "host launches" if args.no_graph else "CUDA graph replay of the step's launches",
+                    "launches_per_layer": ("3: gemm(4096x4096), gemm_group(gate, up), gemm(4096x11008) - the engine's call pattern"
+                                           if grouped else "4: one gemm per matrix")},
             "e2e": {"value": round(wbytes * world / (e2e_ms / args.steps * 1e-3) / 1e9, 2), "unit": UNIT,
                     "h2d_bytes_per_step": x_host.numel() * 4, "d2h_bytes_per_step": y_host.numel() * 4,
                     "ms_per_step": round(e2e_ms / args.steps, 5)},
@@ -376,9 +417,11 @@ def run_ours(args):
                          "algorithmic_bytes_per_launch": abytes // n_launch, "traffic": (TRAFFIC_BYTES_PER_LAYER_GROUPED if grouped else TRAFFIC_BYTES_PER_LAYER) // (n_launch // args.layers),
                          "frac_of_spec_8000_gbs": round(achieved / 8000.0, 4)},
             "clocks": clocks,
+            "checked": checked,
         }
         if sharded is not None:
             line["sharded"] = sharded
+            line["sharded_parity"] = sharded.get("sharded_parity")
         if world == 1 and extras & {"prefill", "decode"}:
             line["extra"] = {}
             if "prefill" in extras:
@@ -386,7 +429,7 @@ def run_ours(args):
             if "decode" in extras:
                 line["extra"]["decode"] = decode_extra(torch, capi, gen, barrier)
         if world == 1 and not args.no_cpu:
-            line["cpu_baseline"] = cpu_baseline(sample_seconds=args.cpu_seconds)
+            line["cpu_baseline"] = cpu_baseline(sample_seconds=args.cpu_seconds, layers=args.layers)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -464,6 +507,7 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
     different tokens rotated so that successive calls hit different experts."""
     from kraken_b200 import shard
     out = {"n_gpus": world}
+    parity = {}
     # ---- head ----
     n_out, n_in = 128256, 4096
     begin, count = shard.row_range(n_out, world, rank, 8)
@@ -498,6 +542,14 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
         torch.cuda.synchronize()
         if capi.device_status() != 0:
             raise RuntimeError("a bounded wait of the fused all-gather gave up")
+        # What was timed, checked: on every rank the fused kernel's gathered row and the NCCL form's row must be
+        # the same bits, and this rank's slice of it must be what the unsharded kernel gives for these rows.
+        state["w"] = peer.w_local = ws[0]
+        row_nccl = head.forward(x).clone()
+        row_peer = peer.forward(x).clone()
+        own = capi.gemv(x, ws[0], synth.Q6_K, count, n_in)
+        torch.cuda.synchronize()
+        parity["head"] = bool(torch.equal(row_nccl, row_peer) and torch.equal(row_peer[:, begin:begin + count], own))
         peer.close()
     wbytes = n_out * synth.row_bytes(synth.Q6_K, n_in)
     out["head_q6_k_128256x4096"] = {
@@ -538,6 +590,11 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
             torch.cuda.synchronize()
             if capi.device_status() != 0:
                 raise RuntimeError("a bounded wait of the fused exchange gave up")
+            # the two exchanges (NCCL all-gather + rank-ordered sum, fused peer-store kernel) must agree bit for bit
+            y_nccl = moe.forward(toks[3, :batch], logits[3, :batch]).clone()
+            y_peer = moe_peer.forward(toks[3, :batch], logits[3, :batch]).clone()
+            torch.cuda.synchronize()
+            parity[f"moe_batch{batch}"] = bool(torch.equal(y_nccl, y_peer) and torch.isfinite(y_peer).all())
         distinct = []
         for i in range(16):
             ids, _ = capi.route(logits[i, :batch], k)
@@ -551,6 +608,16 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
             "experts_per_gpu": n_local}
     if peer_sum is not None:
         peer_sum.close()
+    if world > 1:
+        # every rank must have seen every check pass; a failed check fails the run
+        ok = torch.tensor([1.0 if parity and all(parity.values()) else 0.0], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok.item()) != 1.0:
+            raise RuntimeError(f"sharded results differ between the fused and the NCCL forms on rank {rank}: {parity}")
+        out["sharded_parity"] = "ok"
+        out["sharded_parity_checks"] = sorted(parity)
+    else:
+        out["sharded_parity"] = "single GPU: nothing to compare"
     return out
 
 
@@ -665,8 +732,7 @@ def prefill_extra(torch, capi, gen):
         tf = 2.0 * rows * n_out * n_in / (ms * 1e-3) / 1e12
         out.append({"M": rows, "ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_measured_bf16_peak": round(tf / peak, 4),
                     "frac_of_spec_2250_tflops": round(tf / 2250.0, 4)})
-    # the same GEMM at M = 512 for the other two formats of the spec (no TMA staging: their blocks are not
-    # 16-byte multiples, so the decode warps stage the raw bytes themselves)
+    # the same GEMM at M = 512 for the other formats
     other = {}
     del ws
     for name, wt, make in (("q6_k", synth.Q6_K, device_weights_q6k), ("q8_0", synth.Q8_0, device_weights_q8_0),
@@ -693,9 +759,8 @@ def prefill_extra(torch, capi, gen):
             "results": out, "other_formats_M512": other}
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the streaming kernel over the launches of one layer, from the
-# ncu capture summarised in profiles/gemv_stream_q4k_llama7b_layer.md; the bench line divides it by the launches
-# per layer.
+# ncu dram__bytes_read.sum + dram__bytes_write.sum of the streaming kernel over the launches of one layer (a one-layer
+# run of this file under ncu); the bench line divides it by the launches per layer. Re-measure when the kernel changes.
 TRAFFIC_BYTES_PER_LAYER = 85868544            # four launches: 9,516,288 + 25,441,280 + 25,441,792 + 25,469,184
 TRAFFIC_BYTES_PER_LAYER_GROUPED = 85795328    # three launches: 9,521,408 + 50,804,480 (gate and up) + 25,469,440
 
@@ -724,81 +789,123 @@ def cpu_layer(seed_off: int = 0):
     return mats
 
 
-def time_cpu(eng, mats, tier: int, threads: int, budget_s: float):
-    def one_pass():
-        for w, x, n_out, n_in in mats:
-            if eng.kind == "reference":
-                eng.gemm(x, w, WT, n_out, n_in, rows=1, tier=tier)
-            else:
-                eng.gemm(x, w, WT, n_out, n_in, rows=1, threads=threads)
-    one_pass()                                   # warm-up
+def cpu_step_fn(eng, layers: int, threads: int):
+    """one_step(tier): one token's pass over `layers` layers on the CPU engine. Eight copies of the seeded layer
+    (rows rotated, as on the GPU) are cycled so that a step streams its weights from memory rather than from the
+    last-level cache."""
+    base = cpu_layer()
+    copies = []
+    for c in range(8):
+        copies.append([(w if c == 0 else np.ascontiguousarray(np.roll(w, -layer_shift(c, n_out), axis=0)), x, n_out, n_in)
+                       for w, x, n_out, n_in in base])
+
+    def one_step(tier):
+        for li in range(layers):
+            for w, x, n_out, n_in in copies[li % len(copies)]:
+                if eng.kind == "reference":
+                    eng.gemm(x, w, WT, n_out, n_in, rows=1, tier=tier)
+                else:
+                    eng.gemm(x, w, WT, n_out, n_in, rows=1, threads=threads)
+    return one_step
+
+
+def time_cpu_steps(one_step, tier: int, layers: int, budget_s: float, warm_s: float = 1.0):
+    """GB/s of whole steps for about budget_s seconds after warm_s seconds of warm-up."""
+    t_w = time.perf_counter()
+    one_step(tier)
+    while time.perf_counter() - t_w < warm_s:
+        one_step(tier)
     t0 = time.perf_counter()
     n = 0
     while True:
-        one_pass()
+        one_step(tier)
         n += 1
         dt = time.perf_counter() - t0
         if dt >= budget_s or n >= 2000:
             break
-    return layer_weight_bytes() * n / dt / 1e9, n, dt
+    return layer_weight_bytes() * layers * n / dt / 1e9, n, dt
 
 
-def cpu_baseline(sample_seconds: float = 10.0):
+def cpu_baseline(sample_seconds: float = 10.0, layers: int = N_LAYERS):
     threads = os.cpu_count() or 1
     eng = cpu_engine(threads)
-    mats = cpu_layer()
+    one_step = cpu_step_fn(eng, layers, threads)
     out = {"unit": UNIT, "cores": threads, "kind": eng.kind}
+    what = f"steps of {layers} layers x 4 matmuls ({layer_weight_bytes() * layers} weight bytes per step, 8 rotated copies of the seeded layer cycled)"
     if eng.kind == "reference":
-        v1, n1, t1 = time_cpu(eng, mats, 1, threads, sample_seconds * 0.5)
-        v0, n0, t0 = time_cpu(eng, mats, 0, threads, sample_seconds * 0.5)
+        v1, n1, t1 = time_cpu_steps(one_step, 1, layers, sample_seconds * 0.5)
+        v0, n0, t0 = time_cpu_steps(one_step, 0, layers, sample_seconds * 0.5, warm_s=0.0)
         out.update(value=round(v1, 3), tier="reference default (int8-activation AVX2 tier, lossy)",
                    exact_scalar_value=round(v0, 3),
-                   sample=f"one layer (4 matmuls, {layer_weight_bytes()} weight bytes) repeated {n1}x default tier "
-                          f"in {t1:.1f}s and {n0}x exact scalar tier in {t0:.1f}s, KRK_THREADS={threads}")
+                   sample=f"{n1} {what} on the default tier in {t1:.1f}s after 1s of warm-up, {n0} on the exact scalar tier "
+                          f"in {t0:.1f}s, KRK_THREADS={threads}")
     else:
-        v0, n0, t0 = time_cpu(eng, mats, 0, threads, sample_seconds)
+        v0, n0, t0 = time_cpu_steps(one_step, 0, layers, sample_seconds)
         out.update(value=round(v0, 3), tier="exact scalar f32 chain (restatement)",
-                   sample=f"one layer (4 matmuls, {layer_weight_bytes()} weight bytes) repeated {n0}x in {t0:.1f}s, "
-                          f"{threads} threads")
+                   sample=f"{n0} {what} in {t0:.1f}s, {threads} threads")
     return out
 
 
 def run_reference(args):
-    """The reference's own CPU implementation of the path on this box's host cores."""
+    """The reference's own CPU implementation of the path on this box's host cores, same workload and config as
+    the GPU arm: a step is one token's pass over all the layers' four matmuls. Eight copies of the seeded layer
+    (rows rotated, as on the GPU) are cycled so that a step streams its weights from memory rather than from
+    the last-level cache. The run is warmed up for at least a second before it is timed."""
     rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
     eng = cpu_engine(threads)
-    mats = cpu_layer()
+    one_step = cpu_step_fn(eng, args.layers, threads)
     tier = 1 if eng.kind == "reference" else 0
-    # a step = a bounded sample of the workload: one layer's four matmuls
-    for _ in range(max(args.warmup, 1)):
-        time_cpu(eng, mats, tier, threads, 0.0)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        for w, x, n_out, n_in in mats:
-            if eng.kind == "reference":
-                eng.gemm(x, w, WT, n_out, n_in, rows=1, tier=tier)
-            else:
-                eng.gemm(x, w, WT, n_out, n_in, rows=1, threads=threads)
-    dt = time.perf_counter() - t0
-    value = layer_weight_bytes() * args.steps / dt / 1e9
-    sample = (f"each step = one layer of the workload (4 matmuls, {layer_weight_bytes()} weight bytes), "
+
+    def timed_steps(t, steps, warm_s):
+        t_w = time.perf_counter()
+        n_w = 0
+        while n_w < max(args.warmup, 1) or time.perf_counter() - t_w < warm_s:
+            one_step(t)
+            n_w += 1
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            one_step(t)
+        return time.perf_counter() - t0, n_w
+
+    dt, n_warm = timed_steps(tier, args.steps, 1.0)
+    value = layer_weight_bytes() * args.layers * args.steps / dt / 1e9
+    exact = None
+    if eng.kind == "reference":     # the exact scalar tier beside it, on fewer steps (it is several times slower)
+        es = max(1, args.steps // 10)
+        dte, _ = timed_steps(0, es, 0.0)
+        exact = layer_weight_bytes() * args.layers * es / dte / 1e9
+    sample = (f"{args.steps} steps of {args.layers} layers x 4 matmuls ({layer_weight_bytes() * args.layers} weight bytes per step) "
+              f"in {dt:.2f}s after {n_warm} warm-up steps, 8 rotated copies of the seeded layer cycled, "
               f"{'KRK_THREADS' if eng.kind == 'reference' else 'threads'}={threads}")
     line = {
         "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT,
-        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": max(args.warmup, 1),
+        "n_gpus": world, "steps": args.steps, "warmup": n_warm,
         "ms_per_step": round(dt / args.steps * 1e3, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32 (int8-activation tier)" if tier == 1 else "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "weight_type": "Q4_K", "batch": 1, "layers": N_LAYERS,
-                   "matmuls_per_layer": [list(s) for s in LAYER_SHAPES], "sample": sample},
+        "config": workload_config(args.layers, world),
         "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": threads, "kind": eng.kind, "sample": sample,
-                         "tier": "reference default (int8-activation AVX2 tier)" if tier == 1 else "exact scalar"},
+                         "tier": "reference default (int8-activation AVX2 tier, lossy)" if tier == 1 else "exact scalar",
+                         "exact_scalar_value": None if exact is None else round(exact, 3)},
         "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def run_issue_rates():
+    """Cycles per instruction and sub-partition for the instruction kinds the decode GEMV could be built from."""
+    from kraken_b200 import capi
+    rows = []
+    for kind, name in enumerate(capi.PROBE_KINDS):
+        thr = [round(capi.probe_issue(kind, w, 2048), 2) for w in (4, 8, 16)]
+        lat = round(capi.probe_issue(kind, 1, 2048, chained=True), 1)
+        rows.append({"instruction": name, "cycles_per_instr_per_smsp_at_1_2_4_warps": thr, "dependent_issue_latency": lat})
+        print(f"{name:28s} {thr}  latency {lat}", file=sys.stderr)
+    print(json.dumps({"issue_rates": rows}), flush=True)
 
 
 def main():
@@ -808,6 +915,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-check", action="store_true", help="skip the check of the step against the CPU checker (profiling runs)")
+    ap.add_argument("--issue-rates", action="store_true", help="print the instruction issue-rate table and exit")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--no-extras", action="store_true", help="skip every side measurement")
     ap.add_argument("--extras", default="prefill,decode,sharded",
@@ -818,7 +927,9 @@ def main():
                     help="layers per step; fewer than 32 is for profiler captures only, not a bench value")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.issue_rates:
+        run_issue_rates()
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -129,9 +129,14 @@ int krk_cuda_gemm(void *y_f32, const void *x, int x_dtype, const void *w, int wt
  *  - All calls on one device share the array: a call rewrites the part it uses before reading it, so
  *    back-to-back calls on one stream are fine, but two calls whose kernels can overlap on the GPU
  *    (different streams) race on it. A bounded-wait give-up of this entry's kernels is recorded in a
- *    word of that array, not in krk_cuda_device_status(). */
+ *    word of that array, not in krk_cuda_device_status(): krk_cuda_gemm_f32_static_status() reads it. */
 int krk_cuda_gemm_f32_static(void *y_f32, const void *x_f32, const void *w, int wt, int64_t n_out,
                              int64_t n_in, int64_t rows, void *stream);
+
+/* Companion of krk_cuda_gemm_f32_static (no counterpart in the reference): 0, or the KRK_CUDA_ETIMEOUT-class
+ * code a kernel of that entry left in the array's status word on the current device; a non-zero word is
+ * cleared by the read. Synchronises the device; copies four bytes through the symbol and allocates nothing. */
+int krk_cuda_gemm_f32_static_status(void);
 
 /* Router on the device: softmax over n_expert logits per token, k picks of the largest
  * probability (ties to the lower id), weights renormalised over the picks. Replaces the
@@ -140,6 +145,23 @@ int krk_cuda_gemm_f32_static(void *y_f32, const void *x_f32, const void *w, int 
  * ids_i32 and wts_f32 are [n_tok][k]. */
 int krk_cuda_route(void *ids_i32, void *wts_f32, const void *logits_f32, int64_t n_tok,
                    int n_expert, int k, void *stream);
+
+/* The router in the three steps of the Backend interface, for an engine that drives them one at a time
+ * (Engine::moe_ffn with KRK_DEVICE_SOFTMAX / the device plan). All pointers are device memory.
+ *  - krk_cuda_router_softmax replaces Backend::router_softmax (include/krk/backend.hpp:934-937): probs_f32
+ *    [n_rows][n_expert] = softmax of the logits rows, maximum subtracted, summed in expert order.
+ *  - krk_cuda_router_topk replaces Backend::router_topk (include/krk/backend.hpp:950-954): k picks of the
+ *    largest probability per row, a tie keeps the lower id; weights are the picked probabilities, divided by
+ *    their slot-order sum when normalize != 0, then multiplied by scale.
+ *  - krk_cuda_moe_plan_build replaces Backend::moe_plan_build (include/krk/backend.hpp:975-980; device twin
+ *    src/hip/kernels/router.hpp:252-289): off_i32[n_expert + 1], rows_i32[n_rows * k] and wt_f32[n_rows * k]
+ *    in expert-major order, entries of one expert in (token, slot) order, exactly the host's plan
+ *    (src/engine.cpp:12215-12248). wts_f32 may be NULL (then wt_f32 is zero-filled). */
+int krk_cuda_router_softmax(void *probs_f32, const void *logits_f32, int64_t n_rows, int n_expert, void *stream);
+int krk_cuda_router_topk(const void *probs_f32, int64_t n_rows, int n_expert, int k, void *ids_i32, void *wts_f32,
+                         int normalize, float scale, void *stream);
+int krk_cuda_moe_plan_build(const void *ids_i32, int64_t n_rows, int k, int n_expert, void *off_i32, void *rows_i32,
+                            void *wt_f32, const void *wts_f32, void *stream);
 
 /* One bank of routed experts held by this device: expert e (global id) is held when
  * expert_base <= e < expert_base + n_local; its matrices are the e-expert_base'th
@@ -204,9 +226,11 @@ int krk_cuda_sum_parts(void *out_f32, const void *parts_f32, int n_parts, int64_
  * kernel writes the step's epoch into host_flag_peers[q][my_rank] on every GPU. Loads never touch peer
  * memory; only plain stores do.
  *   epoch > 0: the host counts steps (strictly increasing, the same on every GPU).
- *   epoch == 0: the step count lives on the device, in host_flag_peers[my_rank][n_peers] (so each flag
- *     array holds n_peers + 1 ints, zero at start); the launch carries no per-step value and can be
- *     replayed from a CUDA graph.
+ *   epoch == 0: the step count lives on the device, in host_flag_peers[my_rank][n_peers]; the launch
+ *     carries no per-step value and can be replayed from a CUDA graph.
+ *   Each flag array holds n_peers + 2 ints, zero at start: one epoch per peer, the step count, and the
+ *   kernel's count of CTAs that have stored (so every exchange object has its own; objects that share a
+ *   flag array must not run at the same time).
  *   wait_in_kernel != 0: the last CTA also waits (bounded, about 2 s, then krk_cuda_device_status() is
  *     raised) until every peer's epoch has arrived here, so the end of the kernel is the end of the
  *     all-gather on this GPU. With 0 the host enqueues krk_cuda_wait_flags where it wants the row.
@@ -243,7 +267,7 @@ int krk_cuda_logits_topk(const void *logits_f32, int64_t n, int k, const void *p
  * out = ((slot 0 + slot 1) + slot 2) + ... : the same bits on every GPU. host_gather_peers[q] is GPU q's
  * gather buffer as mapped into this process (krk_cuda_peer_open; own buffer at q == my_rank), laid out
  * [2][n_peers][slot_stride] floats (two steps deep; slot_stride >= n, % 4 == 0); host_flag_peers[q] is
- * GPU q's flag array of n_peers + 1 ints, zero at start. Steps are counted on the device, so the launch
+ * GPU q's flag array of n_peers + 2 ints (epochs, step count, CTA count), zero at start. Steps are counted on the device, so the launch
  * replays from a CUDA graph. Every GPU must make the same sequence of calls. */
 int krk_cuda_allgather_sum(void *const host_gather_peers[], void *const host_flag_peers[], int n_peers, int my_rank,
                            int64_t slot_stride, const void *part_f32, void *out_f32, int64_t n, void *stream);
@@ -260,6 +284,22 @@ int krk_cuda_peer_alloc(void **dev_ptr, size_t bytes, unsigned char handle[KRK_C
 int krk_cuda_peer_open(void **dev_ptr, const unsigned char handle[KRK_CUDA_IPC_HANDLE_BYTES]);
 int krk_cuda_peer_close(void *dev_ptr);
 int krk_cuda_peer_free(void *dev_ptr);
+
+/* The exchange step over NCCL for a C/C++ host (the reference is single-device: no counterpart there):
+ * ncclAllGather of slice_bytes bytes from every rank into full (n_ranks * slice_bytes bytes, rank order), on
+ * `stream`; in place when slice == full + rank * slice_bytes. nccl_comm is an ncclComm_t of the host's own
+ * (ncclCommInitRank) or one made by krk_cuda_nccl_comm_init below. Follow it with krk_cuda_sum_parts for
+ * expert-sharded partial sums. The NCCL library is looked up at run time (libnccl.so.2); KRK_CUDA_EDEVICE when
+ * it cannot be found, KRK_CUDA_ELAUNCH (text in krk_cuda_nccl_last_error) when NCCL refuses.
+ * krk_cuda_nccl_unique_id / _comm_init / _comm_destroy wrap ncclGetUniqueId / ncclCommInitRank /
+ * ncclCommDestroy for hosts that do not link NCCL themselves: rank 0 makes the 128-byte id, every rank passes it
+ * (by any channel) to _comm_init with its device current. */
+#define KRK_CUDA_NCCL_ID_BYTES 128
+int krk_cuda_shard_allgather(void *full, const void *slice, size_t slice_bytes, void *nccl_comm, void *stream);
+int krk_cuda_nccl_unique_id(unsigned char id[KRK_CUDA_NCCL_ID_BYTES]);
+int krk_cuda_nccl_comm_init(void **comm, int n_ranks, int rank, const unsigned char id[KRK_CUDA_NCCL_ID_BYTES]);
+int krk_cuda_nccl_comm_destroy(void *comm);
+const char *krk_cuda_nccl_last_error(void);
 
 /* Enqueues a bounded wait until flags_i32[q] >= epoch for every q < n_peers (flags_i32 is this GPU's own
  * flag array). A wait that runs out (about 2 s) raises krk_cuda_device_status() instead of hanging. */
@@ -279,6 +319,14 @@ int64_t krk_cuda_launch_count(void);
 #define KRK_CUDA_FAMILY_GEMM_TC 3
 int64_t krk_cuda_family_count(int family);
 
+/* Diagnostic, no counterpart in the reference: cycles between two instructions of one kind on one SM
+ * sub-partition, measured with every SM busy. kind: 0 mma.sync m16n8k32 s8, 1 m16n8k16 s8, 2 m16n8k16 f16,
+ * 3 m16n8k16 bf16, 4 m16n8k32 e4m3, 5 dp4a, 6 mad.lo.s32, 7 fma.rn.f16x2, 8 lop3, 9 fma.rn.f32,
+ * 10 m16n8k8 f16. `warps` per CTA (1..32, one CTA per SM); chained != 0 measures the dependent-issue
+ * latency instead of the throughput. Allocates and frees its own buffers and synchronises the device;
+ * `bench.py --issue-rates` prints the table the kernel formulations were chosen from. */
+int krk_cuda_probe_issue(int kind, int warps, int iters, int chained, double *host_cycles_per_instr);
+
 /* ---- host-buffer plumbing: the CudaBackend class of krk_cuda_backend.hpp behind a C face ----
  * These are the calls a host that is not C++ binds. `be` is the object returned by
  * krk_cuda_backend_make (make_hip_backend's contract, include/krk/backend.hpp:1886: NULL and a
@@ -292,8 +340,30 @@ void krk_cuda_backend_free(void *be);
 const char *krk_cuda_backend_describe(void *be);
 void *krk_cuda_backend_alloc(void *be, size_t bytes);
 void krk_cuda_backend_release(void *be, void *p);
-void krk_cuda_backend_upload(void *be, void *dst, const void *host_src, size_t bytes);
-void krk_cuda_backend_download(void *be, void *host_dst, const void *src, size_t bytes);
+/* off: byte offset into the device side (dst of an upload, src of a download), as Backend::upload / download
+ * have it (include/krk/backend.hpp:720, 755; src/backend_cpu.cpp:676-683) */
+void krk_cuda_backend_upload(void *be, void *dst, const void *host_src, size_t bytes, size_t off);
+void krk_cuda_backend_download(void *be, void *host_dst, const void *src, size_t bytes, size_t off);
+void krk_cuda_backend_download_f32(void *be, float *host_dst, const void *src, int64_t n);          /* backend.hpp:803 */
+void krk_cuda_backend_upload_i32(void *be, int32_t *dst, const int32_t *host_src, int64_t n);       /* backend.hpp:1505 */
+/* the members either side of the matmuls, with the reference's argument lists (include/krk/backend.hpp:838,
+ * 902-922, 1309, 1451, 1473, 934-986); host_* are host memory, everything else device memory from alloc */
+void krk_cuda_backend_embed(void *be, void *out, const void *tok_embd, int tt, int64_t n_vocab, int64_t n_embd,
+                            const int32_t *host_tokens, int64_t n_tok);
+void krk_cuda_backend_logits_topk(void *be, const void *logits, int64_t n, int32_t k, const void *pen_mask, float rep_pen,
+                                  float softcap, float temp, int32_t *ids, float *vals, float *mass_out, void *scratch,
+                                  int32_t cand_cap, int64_t *count_out);
+void krk_cuda_backend_silu_mul(void *be, void *out, const void *gate, const void *up, int64_t n, int64_t row_len,
+                               float *host_row_scale);
+void krk_cuda_backend_gather_rows(void *be, void *dst, const void *src, const int32_t *rows, int64_t n_rows, int64_t n);
+void krk_cuda_backend_scatter_axpy_rows(void *be, void *dst, const void *src, const int32_t *rows, const float *alpha,
+                                        int64_t n_rows, int64_t n);
+void krk_cuda_backend_router_softmax(void *be, void *probs, const void *logits, int64_t n_rows, int32_t n_expert);
+void krk_cuda_backend_router_topk(void *be, const void *probs, int64_t n_rows, int32_t n_expert, int32_t k, void *ids,
+                                  void *wts, int32_t normalize, float scale);
+void krk_cuda_backend_moe_plan_build(void *be, const void *ids, int64_t n_rows, int32_t k, int32_t n_expert, void *off,
+                                     void *rows, void *wt, const void *wts);
+int krk_cuda_backend_device(void *be);
 void krk_cuda_backend_fill0(void *be, void *p, size_t bytes);
 void krk_cuda_backend_sync(void *be);
 int krk_cuda_backend_gemm_k_ok(void *be, int wt, int64_t k);
@@ -304,6 +374,36 @@ int krk_cuda_backend_gemm_accumulate(void *be, void *dst, const void *x, const v
 int krk_cuda_backend_gemm_group(void *be, void *const out[], const void *x, const void *const w[], int wt,
                                 const int64_t n_out[], int64_t n_in, int n_mat, int64_t rows, int silu,
                                 int *silu_fused);
+
+/* ---- the on-disk format either side of the path: a GGUF v2 / v3 tensor reader ----
+ * Replaces krk::Gguf for this path (include/krk/gguf.hpp; src/gguf.cpp): one file, mapped read-only; header,
+ * key/value block and tensor directory are parsed, tensor data is never copied or repacked on the host.
+ * krk_gguf_open returns NULL and a message in err on a file it cannot read (bad magic, version other than 2 or 3,
+ * truncated directory, tensor data past the end of the file). Host-only: no device is touched except by
+ * krk_gguf_upload_tensor. */
+struct krk_gguf_tensor {
+    const char *name;        /* valid until krk_gguf_close */
+    int type_id;             /* GGUF type id = krk::DType value */
+    int supported;           /* 1 when krk_cuda_dtype_ok(type_id) */
+    int n_dims;
+    int64_t ne[4];           /* ne[0] = row length (n_in), ne[1] = rows (n_out), as GGUF stores them */
+    const void *host_data;   /* the tensor's bytes inside the mapping */
+    size_t n_bytes;          /* rows * row_bytes; 0 for a type this library does not size */
+};
+void *krk_gguf_open(const char *path, char *err, size_t err_len);
+void krk_gguf_close(void *gguf);
+int krk_gguf_version(void *gguf);
+int64_t krk_gguf_tensor_count(void *gguf);
+int64_t krk_gguf_kv_count(void *gguf);
+int64_t krk_gguf_find_tensor(void *gguf, const char *name);                 /* index, or -1 */
+int krk_gguf_tensor_info(void *gguf, int64_t index, struct krk_gguf_tensor *out);
+int krk_gguf_get_i64(void *gguf, const char *key, int64_t *out);            /* any integer, bool or float value */
+int krk_gguf_get_f64(void *gguf, const char *key, double *out);
+int64_t krk_gguf_get_str(void *gguf, const char *key, char *buf, size_t buf_len);   /* length, or -1 */
+int64_t krk_gguf_get_array_count(void *gguf, const char *key, int *elem_type);       /* count, or -1 */
+/* alloc() on the backend + upload of the tensor's unmodified bytes (Backend::upload, include/krk/backend.hpp:720);
+ * the caller releases the pointer with krk_cuda_backend_release. NULL for an unsized type or a failed alloc. */
+void *krk_gguf_upload_tensor(void *gguf, int64_t index, void *backend);
 
 #ifdef __cplusplus
 }

@@ -36,8 +36,12 @@ public:
 
     void *alloc(size_t bytes);                                   // backend.hpp:361
     void release(void *p);                                       // backend.hpp:362
-    void upload(void *dst, const void *host_src, size_t bytes);  // backend.hpp:720
-    void download(void *host_dst, const void *src, size_t bytes);// backend.hpp:755 (synchronises)
+    // backend.hpp:720 / :755: `off` is a byte offset into the DEVICE side (dst of an upload, src of a
+    // download), as in src/backend_cpu.cpp:676-683. An upload from pageable host memory has been staged by
+    // the driver when the call returns; from pinned memory it is asynchronous and the source must stay
+    // valid until sync() or a download. download synchronises.
+    void upload(void *dst, const void *host_src, size_t bytes, size_t off = 0);
+    void download(void *host_dst, const void *src, size_t bytes, size_t off = 0);
     void download_f32(f32 *host_dst, const void *src, i64 n);    // backend.hpp:803
     void upload_i32(i32 *dst, const i32 *host_src, i64 n);       // backend.hpp:1505
     void fill0(void *p, size_t bytes);                           // backend.hpp:769
@@ -85,12 +89,23 @@ public:
     void logits_topk(const void *logits, i64 n, i32 k, const void *pen_mask, f32 rep_pen, f32 softcap, f32 temp,
                      i32 *ids, f32 *vals, f32 *mass_out, void *scratch, i32 cand_cap, i64 *count_out);
 
+    // The router on the device, in the interface's three steps (backend.hpp:934-986); all pointers device memory.
+    bool router_softmax_supported() const { return true; }
+    void router_softmax(void *probs, const void *logits, i64 n_rows, i32 n_expert);
+    bool router_topk_supported() const { return true; }
+    void router_topk(const void *probs, i64 n_rows, i32 n_expert, i32 k, void *ids, void *wts, i32 normalize, f32 scale);
+    void moe_plan_build(const void *ids, i64 n_rows, i32 k, i32 n_expert, void *off, void *rows, void *wt, const void *wts);
+    // moe_dispatch (backend.hpp:1002) reads the reference's expert-cache residency table, which this build does
+    // not have; the routed-expert FFN over a resident bank is krk_cuda_moe_ffn(_routed) instead.
+    bool moe_dispatch_supported() const { return false; }
+
     void *stream() const { return stream_; }
     int device() const { return device_; }
 
 private:
     CudaBackend() = default;
     void *workspace(size_t bytes);
+    void use() const;   // makes this backend's device current (a second backend may have changed it)
     int device_ = 0;
     void *stream_ = nullptr;
     void *ws_ = nullptr;

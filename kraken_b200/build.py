@@ -86,7 +86,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if p.endswith(".o") and p not in keep:
             os.remove(p)
     if jobs or force or not os.path.exists(LIB):
-        cmd = [cc] + ARCH + ["-shared", "-o", LIB] + objs
+        cmd = [cc] + ARCH + ["-shared", "-o", LIB] + objs + ["-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"linking libkrk_cuda.so failed:\n{r.stdout}\n{r.stderr}")

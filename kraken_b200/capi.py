@@ -35,6 +35,12 @@ lib = C.CDLL(LIB_PATH)
 _vp, _i64, _int, _sz = C.c_void_p, C.c_int64, C.c_int, C.c_size_t
 
 
+class GgufTensorInfo(C.Structure):
+    """struct krk_gguf_tensor"""
+    _fields_ = [("name", C.c_char_p), ("type_id", _int), ("supported", _int), ("n_dims", _int), ("ne", _i64 * 4),
+                ("host_data", _vp), ("n_bytes", _sz)]
+
+
 class ExpertBank(C.Structure):
     """struct krk_cuda_expert_bank"""
     _fields_ = [("gate", _vp), ("up", _vp), ("down", _vp), ("wt_gate_up", _int), ("wt_down", _int),
@@ -57,7 +63,16 @@ SIGNATURES = {
     "krk_cuda_gemm_workspace_bytes": (_sz, [_int, _i64, _i64, _i64]),
     "krk_cuda_gemm": (_int, [_vp, _vp, _int, _vp, _int, _i64, _i64, _i64, _vp, _sz, _vp]),
     "krk_cuda_gemm_f32_static": (_int, [_vp, _vp, _vp, _int, _i64, _i64, _i64, _vp]),
+    "krk_cuda_gemm_f32_static_status": (_int, []),
     "krk_cuda_route": (_int, [_vp, _vp, _vp, _i64, _int, _int, _vp]),
+    "krk_cuda_router_softmax": (_int, [_vp, _vp, _i64, _int, _vp]),
+    "krk_cuda_router_topk": (_int, [_vp, _i64, _int, _int, _vp, _vp, _int, C.c_float, _vp]),
+    "krk_cuda_moe_plan_build": (_int, [_vp, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp]),
+    "krk_cuda_shard_allgather": (_int, [_vp, _vp, _sz, _vp, _vp]),
+    "krk_cuda_nccl_unique_id": (_int, [C.c_char_p]),
+    "krk_cuda_nccl_comm_init": (_int, [C.POINTER(_vp), _int, _int, C.c_char_p]),
+    "krk_cuda_nccl_comm_destroy": (_int, [_vp]),
+    "krk_cuda_nccl_last_error": (C.c_char_p, []),
     "krk_cuda_moe_workspace_bytes": (_sz, [C.POINTER(ExpertBank), _int, _i64]),
     "krk_cuda_moe_ffn": (_int, [_vp, _vp, _vp, _vp, C.POINTER(ExpertBank), _int, _i64, _vp, _sz, _vp]),
     "krk_cuda_moe_ffn_routed": (_int, [_vp, _vp, _vp, _int, _vp, _vp, C.POINTER(ExpertBank), _int, _i64, _vp, _sz, _vp]),
@@ -79,13 +94,38 @@ SIGNATURES = {
     "krk_cuda_device_status": (_int, []),
     "krk_cuda_launch_count": (_i64, []),
     "krk_cuda_family_count": (_i64, [_int]),
+    "krk_cuda_probe_issue": (_int, [_int, _int, _int, _int, C.POINTER(C.c_double)]),
     "krk_cuda_backend_make": (_vp, [_int, C.c_char_p, _sz]),
     "krk_cuda_backend_free": (None, [_vp]),
     "krk_cuda_backend_describe": (C.c_char_p, [_vp]),
     "krk_cuda_backend_alloc": (_vp, [_vp, _sz]),
     "krk_cuda_backend_release": (None, [_vp, _vp]),
-    "krk_cuda_backend_upload": (None, [_vp, _vp, _vp, _sz]),
-    "krk_cuda_backend_download": (None, [_vp, _vp, _vp, _sz]),
+    "krk_cuda_backend_upload": (None, [_vp, _vp, _vp, _sz, _sz]),
+    "krk_cuda_backend_download": (None, [_vp, _vp, _vp, _sz, _sz]),
+    "krk_cuda_backend_download_f32": (None, [_vp, _vp, _vp, _i64]),
+    "krk_cuda_backend_upload_i32": (None, [_vp, _vp, _vp, _i64]),
+    "krk_cuda_backend_embed": (None, [_vp, _vp, _vp, _int, _i64, _i64, _vp, _i64]),
+    "krk_cuda_backend_logits_topk": (None, [_vp, _vp, _i64, C.c_int32, _vp, C.c_float, C.c_float, C.c_float, _vp, _vp, _vp, _vp,
+                                            C.c_int32, _vp]),
+    "krk_cuda_backend_silu_mul": (None, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
+    "krk_cuda_backend_gather_rows": (None, [_vp, _vp, _vp, _vp, _i64, _i64]),
+    "krk_cuda_backend_scatter_axpy_rows": (None, [_vp, _vp, _vp, _vp, _vp, _i64, _i64]),
+    "krk_cuda_backend_router_softmax": (None, [_vp, _vp, _vp, _i64, C.c_int32]),
+    "krk_cuda_backend_router_topk": (None, [_vp, _vp, _i64, C.c_int32, C.c_int32, _vp, _vp, C.c_int32, C.c_float]),
+    "krk_cuda_backend_moe_plan_build": (None, [_vp, _vp, _i64, C.c_int32, C.c_int32, _vp, _vp, _vp, _vp]),
+    "krk_cuda_backend_device": (_int, [_vp]),
+    "krk_gguf_open": (_vp, [C.c_char_p, C.c_char_p, _sz]),
+    "krk_gguf_close": (None, [_vp]),
+    "krk_gguf_version": (_int, [_vp]),
+    "krk_gguf_tensor_count": (_i64, [_vp]),
+    "krk_gguf_kv_count": (_i64, [_vp]),
+    "krk_gguf_find_tensor": (_i64, [_vp, C.c_char_p]),
+    "krk_gguf_tensor_info": (_int, [_vp, _i64, C.POINTER(GgufTensorInfo)]),
+    "krk_gguf_get_i64": (_int, [_vp, C.c_char_p, C.POINTER(_i64)]),
+    "krk_gguf_get_f64": (_int, [_vp, C.c_char_p, C.POINTER(C.c_double)]),
+    "krk_gguf_get_str": (_i64, [_vp, C.c_char_p, C.c_char_p, _sz]),
+    "krk_gguf_get_array_count": (_i64, [_vp, C.c_char_p, C.POINTER(_int)]),
+    "krk_gguf_upload_tensor": (_vp, [_vp, _i64, _vp]),
     "krk_cuda_backend_fill0": (None, [_vp, _vp, _sz]),
     "krk_cuda_backend_sync": (None, [_vp]),
     "krk_cuda_backend_gemm_k_ok": (_int, [_vp, _int, _i64]),
@@ -195,6 +235,10 @@ def gemm_f32_static(x, w, wt: int, n_out: int, n_in: int, out=None, stream=None)
     return out
 
 
+def gemm_f32_static_status() -> int:
+    return lib.krk_cuda_gemm_f32_static_status()
+
+
 def route(logits, k: int, stream=None):
     import torch
     n_tok, n_expert = logits.shape
@@ -202,6 +246,62 @@ def route(logits, k: int, stream=None):
     wts = torch.empty((n_tok, k), dtype=torch.float32, device=logits.device)
     _check(lib.krk_cuda_route(_ptr(ids), _ptr(wts), _ptr(logits), n_tok, n_expert, k, _stream_ptr(stream)), "route")
     return ids, wts
+
+
+def router_softmax(logits, stream=None):
+    import torch
+    probs = torch.empty_like(logits)
+    _check(lib.krk_cuda_router_softmax(_ptr(probs), _ptr(logits), logits.shape[0], logits.shape[1], _stream_ptr(stream)),
+           "router_softmax")
+    return probs
+
+
+def router_topk(probs, k: int, normalize: bool = True, scale: float = 1.0, stream=None):
+    import torch
+    n_rows, n_expert = probs.shape
+    ids = torch.empty((n_rows, k), dtype=torch.int32, device=probs.device)
+    wts = torch.empty((n_rows, k), dtype=torch.float32, device=probs.device)
+    _check(lib.krk_cuda_router_topk(_ptr(probs), n_rows, n_expert, k, _ptr(ids), _ptr(wts), int(normalize), scale,
+                                    _stream_ptr(stream)), "router_topk")
+    return ids, wts
+
+
+def moe_plan_build(ids, wts, n_expert: int, stream=None):
+    """Expert-major plan of a layer: (off int32 [n_expert + 1], rows int32 [n * k], wt f32 [n * k])."""
+    import torch
+    n_rows, k = ids.shape
+    off = torch.empty(n_expert + 1, dtype=torch.int32, device=ids.device)
+    rows = torch.full((n_rows * k,), -1, dtype=torch.int32, device=ids.device)
+    wt = torch.zeros(n_rows * k, dtype=torch.float32, device=ids.device)
+    _check(lib.krk_cuda_moe_plan_build(_ptr(ids), n_rows, k, n_expert, _ptr(off), _ptr(rows), _ptr(wt),
+                                       _ptr(wts) if wts is not None else None, _stream_ptr(stream)), "moe_plan_build")
+    return off, rows, wt
+
+
+class NcclComm:
+    """An NCCL communicator made through the library's own wrappers (krk_cuda_nccl_*), for the C-side
+    all-gather krk_cuda_shard_allgather."""
+
+    def __init__(self, n_ranks: int, rank: int, unique_id: bytes):
+        self.h = _vp()
+        _check(lib.krk_cuda_nccl_comm_init(C.byref(self.h), n_ranks, rank, unique_id), "nccl_comm_init")
+        self.n_ranks, self.rank = n_ranks, rank
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        _check(lib.krk_cuda_nccl_unique_id(buf), "nccl_unique_id")
+        return buf.raw
+
+    def allgather(self, full, slice_, stream=None):
+        nbytes = slice_.numel() * slice_.element_size()
+        _check(lib.krk_cuda_shard_allgather(_ptr(full), _ptr(slice_), nbytes, self.h, _stream_ptr(stream)), "shard_allgather")
+        return full
+
+    def close(self):
+        if self.h:
+            lib.krk_cuda_nccl_comm_destroy(self.h)
+            self.h = _vp()
 
 
 def make_bank(gate, up, down, wt_gate_up: int, wt_down: int, n_local: int, expert_base: int, n_embd: int,
@@ -383,6 +483,18 @@ def family_count(family: int) -> int:
     return lib.krk_cuda_family_count(family)
 
 
+PROBE_KINDS = ("mma.sync.m16n8k32.s8", "mma.sync.m16n8k16.s8", "mma.sync.m16n8k16.f16", "mma.sync.m16n8k16.bf16",
+               "mma.sync.m16n8k32.e4m3", "dp4a.s32", "mad.lo.s32", "fma.rn.f16x2", "lop3.b32", "fma.rn.f32",
+               "mma.sync.m16n8k8.f16")
+
+
+def probe_issue(kind: int, warps: int, iters: int = 4096, chained: bool = False) -> float:
+    """Cycles per instruction of one kind on one SM sub-partition (krk_cuda_probe_issue)."""
+    out = C.c_double(0.0)
+    _check(lib.krk_cuda_probe_issue(kind, warps, iters, int(chained), C.byref(out)), "probe_issue")
+    return out.value
+
+
 # ---- host-buffer plumbing: the CudaBackend object ---------------------------------------------
 
 class Backend:
@@ -415,11 +527,21 @@ class Backend:
     def release(self, p: int) -> None:
         lib.krk_cuda_backend_release(self.h, p)
 
-    def upload(self, dst: int, host_ptr: int, nbytes: int) -> None:
-        lib.krk_cuda_backend_upload(self.h, dst, host_ptr, nbytes)
+    def upload(self, dst: int, host_ptr: int, nbytes: int, off: int = 0) -> None:
+        lib.krk_cuda_backend_upload(self.h, dst, host_ptr, nbytes, off)
 
-    def download(self, host_ptr: int, src: int, nbytes: int) -> None:
-        lib.krk_cuda_backend_download(self.h, host_ptr, src, nbytes)
+    def download(self, host_ptr: int, src: int, nbytes: int, off: int = 0) -> None:
+        lib.krk_cuda_backend_download(self.h, host_ptr, src, nbytes, off)
+
+    def router_softmax(self, probs: int, logits: int, n_rows: int, n_expert: int) -> None:
+        lib.krk_cuda_backend_router_softmax(self.h, probs, logits, n_rows, n_expert)
+
+    def router_topk(self, probs: int, n_rows: int, n_expert: int, k: int, ids: int, wts: int, normalize: bool = True,
+                    scale: float = 1.0) -> None:
+        lib.krk_cuda_backend_router_topk(self.h, probs, n_rows, n_expert, k, ids, wts, int(normalize), scale)
+
+    def moe_plan_build(self, ids: int, n_rows: int, k: int, n_expert: int, off: int, rows: int, wt: int, wts: int) -> None:
+        lib.krk_cuda_backend_moe_plan_build(self.h, ids, n_rows, k, n_expert, off, rows, wt, wts)
 
     def fill0(self, p: int, nbytes: int) -> None:
         lib.krk_cuda_backend_fill0(self.h, p, nbytes)
@@ -442,3 +564,71 @@ class Backend:
         ran = lib.krk_cuda_backend_gemm_group(self.h, (_vp * n)(*outs), x, (_vp * n)(*ws), wt, (_i64 * n)(*n_outs),
                                               n_in, n, rows, int(silu), C.byref(fused))
         return bool(ran), bool(fused.value)
+
+
+class Gguf:
+    """A GGUF file through the library's reader (krk_gguf_*): tensors as views of the mapped file."""
+
+    def __init__(self, path: str):
+        err = C.create_string_buffer(256)
+        self.h = lib.krk_gguf_open(path.encode(), err, 256)
+        if not self.h:
+            raise ValueError(f"{path}: {err.value.decode()}")
+
+    def close(self):
+        if self.h:
+            lib.krk_gguf_close(self.h)
+            self.h = None
+
+    @property
+    def version(self) -> int:
+        return lib.krk_gguf_version(self.h)
+
+    def __len__(self) -> int:
+        return lib.krk_gguf_tensor_count(self.h)
+
+    def kv_count(self) -> int:
+        return lib.krk_gguf_kv_count(self.h)
+
+    def info(self, index: int) -> GgufTensorInfo:
+        out = GgufTensorInfo()
+        _check(lib.krk_gguf_tensor_info(self.h, index, C.byref(out)), "gguf_tensor_info")
+        return out
+
+    def find(self, name: str) -> int:
+        return lib.krk_gguf_find_tensor(self.h, name.encode())
+
+    def tensor_bytes(self, index: int):
+        """uint8 numpy copy of the tensor's bytes."""
+        import numpy as np
+        t = self.info(index)
+        if not t.n_bytes:
+            raise ValueError("a tensor of a type this library does not size")
+        return np.ctypeslib.as_array(C.cast(t.host_data, C.POINTER(C.c_uint8)), shape=(t.n_bytes,)).copy()
+
+    def get_int(self, key: str):
+        out = _i64(0)
+        return out.value if lib.krk_gguf_get_i64(self.h, key.encode(), C.byref(out)) == 0 else None
+
+    def get_float(self, key: str):
+        out = C.c_double(0.0)
+        return out.value if lib.krk_gguf_get_f64(self.h, key.encode(), C.byref(out)) == 0 else None
+
+    def get_str(self, key: str):
+        n = lib.krk_gguf_get_str(self.h, key.encode(), None, 0)
+        if n < 0:
+            return None
+        buf = C.create_string_buffer(n + 1)
+        lib.krk_gguf_get_str(self.h, key.encode(), buf, n + 1)
+        return buf.value.decode(errors="replace")
+
+    def array_count(self, key: str):
+        et = _int(0)
+        n = lib.krk_gguf_get_array_count(self.h, key.encode(), C.byref(et))
+        return (n, et.value) if n >= 0 else None
+
+    def upload(self, index: int, backend: "Backend") -> int:
+        p = lib.krk_gguf_upload_tensor(self.h, index, backend.h)
+        if not p:
+            raise MemoryError("gguf upload failed (unsized type or allocation)")
+        return p

@@ -64,7 +64,13 @@ CudaBackend::~CudaBackend() {
     if (ws_) cudaFree(ws_);
 }
 
+void CudaBackend::use() const {
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != device_) KRK_CUDA_CHECK(cudaSetDevice(device_));
+}
+
 void *CudaBackend::alloc(size_t bytes) {
+    use();
     void *p = nullptr;
     if (bytes == 0) bytes = 16;
     if (cudaMalloc(&p, bytes) != cudaSuccess) return nullptr;   // caller checks, as with the reference
@@ -73,11 +79,15 @@ void *CudaBackend::alloc(size_t bytes) {
 void CudaBackend::release(void *p) {
     if (p) KRK_CUDA_CHECK(cudaFree(p));
 }
-void CudaBackend::upload(void *dst, const void *host_src, size_t bytes) {
-    if (bytes) KRK_CUDA_CHECK(cudaMemcpyAsync(dst, host_src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream_));
+void CudaBackend::upload(void *dst, const void *host_src, size_t bytes, size_t off) {
+    use();
+    if (bytes)
+        KRK_CUDA_CHECK(cudaMemcpyAsync(static_cast<char *>(dst) + off, host_src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream_));
 }
-void CudaBackend::download(void *host_dst, const void *src, size_t bytes) {
-    if (bytes) KRK_CUDA_CHECK(cudaMemcpyAsync(host_dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream_));
+void CudaBackend::download(void *host_dst, const void *src, size_t bytes, size_t off) {
+    use();
+    if (bytes)
+        KRK_CUDA_CHECK(cudaMemcpyAsync(host_dst, static_cast<const char *>(src) + off, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream_));
     KRK_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream_));
 }
 void CudaBackend::download_f32(f32 *host_dst, const void *src, i64 n) {
@@ -85,9 +95,13 @@ void CudaBackend::download_f32(f32 *host_dst, const void *src, i64 n) {
 }
 void CudaBackend::upload_i32(i32 *dst, const i32 *host_src, i64 n) { upload(dst, host_src, sizeof(i32) * (size_t)n); }
 void CudaBackend::fill0(void *p, size_t bytes) {
+    use();
     if (bytes) KRK_CUDA_CHECK(cudaMemsetAsync(p, 0, bytes, (cudaStream_t)stream_));
 }
-void CudaBackend::sync() { KRK_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream_)); }
+void CudaBackend::sync() {
+    use();
+    KRK_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream_));
+}
 
 bool CudaBackend::gemm_k_ok(DType wt, i64 k) const { return krk_cuda_gemm_k_ok((int)wt, k) != 0; }
 
@@ -105,6 +119,7 @@ void *CudaBackend::workspace(size_t bytes) {
 }
 
 void CudaBackend::gemm(void *out, const void *x, const void *w, DType wt, i64 n_out, i64 n_in, i64 rows) {
+    use();
     int rc;
     if (rows <= KRK_CUDA_MAX_ROWS) {
         rc = krk_cuda_gemv(out, x, w, (int)wt, n_out, n_in, rows, 0, stream_);
@@ -121,6 +136,7 @@ bool CudaBackend::gemm_accumulate(void *dst, const void *x, const void *w, DType
     // f32 here, so only the null form is taken and anything else is "do it the long way".
     if (rexp != nullptr || rows > KRK_CUDA_MAX_ROWS || rows < 1) return false;
     if (!krk_cuda_gemm_k_ok((int)wt, n_in)) return false;
+    use();
     const int rc = krk_cuda_gemv(dst, x, w, (int)wt, n_out, n_in, rows, 1, stream_);
     if (rc != KRK_CUDA_OK) die("gemm_accumulate", rc, n_out, n_in, rows, (int)wt);
     return true;
@@ -130,6 +146,7 @@ bool CudaBackend::gemm_group(void *const out[], const void *x, const void *const
                              const i64 n_out[], i64 n_in, int n_mat, i64 rows, bool silu, bool *silu_fused,
                              bool row_parallel_only, const DType *wts, const void *const xs[]) {
     (void)row_parallel_only;   // every matrix is one row-parallel pass here; there is no split-K
+    use();
     if (silu_fused) *silu_fused = false;
     const bool fold = silu && n_mat >= 2 && n_out[0] == n_out[1] && !xs &&
                       (!wts || wts[0] == wts[1]);
@@ -154,7 +171,28 @@ bool CudaBackend::gemm_group(void *const out[], const void *x, const void *const
     return false;
 }
 
+void CudaBackend::router_softmax(void *probs, const void *logits, i64 n_rows, i32 n_expert) {
+    use();
+    const int rc = krk_cuda_router_softmax(probs, logits, n_rows, n_expert, stream_);
+    if (rc != KRK_CUDA_OK) die("router_softmax", rc, n_rows, n_expert, 0, 0);
+}
+
+void CudaBackend::router_topk(const void *probs, i64 n_rows, i32 n_expert, i32 k, void *ids, void *wts, i32 normalize,
+                              f32 scale) {
+    use();
+    const int rc = krk_cuda_router_topk(probs, n_rows, n_expert, k, ids, wts, normalize, scale, stream_);
+    if (rc != KRK_CUDA_OK) die("router_topk", rc, n_rows, n_expert, k, 0);
+}
+
+void CudaBackend::moe_plan_build(const void *ids, i64 n_rows, i32 k, i32 n_expert, void *off, void *rows, void *wt,
+                                 const void *wts) {
+    use();
+    const int rc = krk_cuda_moe_plan_build(ids, n_rows, k, n_expert, off, rows, wt, wts, stream_);
+    if (rc != KRK_CUDA_OK) die("moe_plan_build", rc, n_rows, n_expert, k, 0);
+}
+
 void CudaBackend::silu_mul(void *out, const void *gate, const void *up, i64 n, i64 row_len, f32 *row_scale) {
+    use();
     const int rc = krk_cuda_silu_mul(out, gate, up, n, stream_);
     if (rc != KRK_CUDA_OK) die("silu_mul", rc, n, 0, 0, 0);
     // f32 activations carry no storage exponent: one scale of 1.0 per row, as the CPU backend
@@ -171,6 +209,7 @@ void CudaBackend::silu_mul_rows(void *const out[], const void *const gate[], con
 }
 
 void CudaBackend::gather_rows(void *dst, const void *src, const i32 *rows, i64 n_rows, i64 n) {
+    use();
     const int rc = krk_cuda_gather_rows(dst, src, rows, n_rows, n, stream_);
     if (rc != KRK_CUDA_OK) die("gather_rows", rc, n_rows, n, 0, 0);
 }
@@ -179,6 +218,7 @@ void CudaBackend::scatter_axpy_rows(void *dst, const void *src, const i32 *rows,
                                     i64 n, const f32 *row_scale, i32 *row_exp) {
     (void)row_scale;   // f32 backends fill it with 1.0 and ignore the exponent (backend.hpp:1306-1308)
     (void)row_exp;
+    use();
     const int rc = krk_cuda_scatter_axpy_rows(dst, src, rows, alpha, n_rows, n, stream_);
     if (rc != KRK_CUDA_OK) die("scatter_axpy_rows", rc, n_rows, n, 0, 0);
 }
@@ -186,6 +226,7 @@ void CudaBackend::scatter_axpy_rows(void *dst, const void *src, const i32 *rows,
 void CudaBackend::embed(void *out, const void *tok_embd, DType tt, i64 n_vocab, i64 n_embd, const i32 *tokens,
                         i64 n_tok) {
     if (n_tok <= 0) return;
+    use();
     const size_t need = (size_t)n_tok * sizeof(i32);
     void *dev_tokens = workspace(need);
     KRK_CUDA_CHECK(cudaMemcpyAsync(dev_tokens, tokens, need, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream_)));
@@ -199,6 +240,7 @@ void CudaBackend::logits_topk(const void *logits, i64 n, i32 k, const void *pen_
     (void)scratch;
     (void)cand_cap;
     if (n <= 0 || k <= 0) return;
+    use();
     const size_t need = krk_cuda_logits_topk_workspace_bytes(n, k);
     const int rc = krk_cuda_logits_topk(logits, n, k, pen_mask, rep_pen, softcap, temp, ids, vals, mass_out,
                                         workspace(need), need, stream_);
@@ -231,12 +273,51 @@ void krk_cuda_backend_free(void *be) { delete static_cast<CudaBackend *>(be); }
 const char *krk_cuda_backend_describe(void *be) { return static_cast<CudaBackend *>(be)->describe(); }
 void *krk_cuda_backend_alloc(void *be, size_t bytes) { return static_cast<CudaBackend *>(be)->alloc(bytes); }
 void krk_cuda_backend_release(void *be, void *p) { static_cast<CudaBackend *>(be)->release(p); }
-void krk_cuda_backend_upload(void *be, void *dst, const void *host_src, size_t bytes) {
-    static_cast<CudaBackend *>(be)->upload(dst, host_src, bytes);
+void krk_cuda_backend_upload(void *be, void *dst, const void *host_src, size_t bytes, size_t off) {
+    static_cast<CudaBackend *>(be)->upload(dst, host_src, bytes, off);
 }
-void krk_cuda_backend_download(void *be, void *host_dst, const void *src, size_t bytes) {
-    static_cast<CudaBackend *>(be)->download(host_dst, src, bytes);
+void krk_cuda_backend_download(void *be, void *host_dst, const void *src, size_t bytes, size_t off) {
+    static_cast<CudaBackend *>(be)->download(host_dst, src, bytes, off);
 }
+void krk_cuda_backend_download_f32(void *be, float *host_dst, const void *src, int64_t n) {
+    static_cast<CudaBackend *>(be)->download_f32(host_dst, src, n);
+}
+void krk_cuda_backend_upload_i32(void *be, int32_t *dst, const int32_t *host_src, int64_t n) {
+    static_cast<CudaBackend *>(be)->upload_i32(dst, host_src, n);
+}
+void krk_cuda_backend_embed(void *be, void *out, const void *tok_embd, int tt, int64_t n_vocab, int64_t n_embd,
+                            const int32_t *host_tokens, int64_t n_tok) {
+    static_cast<CudaBackend *>(be)->embed(out, tok_embd, static_cast<DType>(tt), n_vocab, n_embd, host_tokens, n_tok);
+}
+void krk_cuda_backend_logits_topk(void *be, const void *logits, int64_t n, int32_t k, const void *pen_mask, float rep_pen,
+                                  float softcap, float temp, int32_t *ids, float *vals, float *mass_out, void *scratch,
+                                  int32_t cand_cap, int64_t *count_out) {
+    static_cast<CudaBackend *>(be)->logits_topk(logits, n, k, pen_mask, rep_pen, softcap, temp, ids, vals, mass_out, scratch,
+                                                cand_cap, count_out);
+}
+void krk_cuda_backend_silu_mul(void *be, void *out, const void *gate, const void *up, int64_t n, int64_t row_len,
+                               float *host_row_scale) {
+    static_cast<CudaBackend *>(be)->silu_mul(out, gate, up, n, row_len, host_row_scale);
+}
+void krk_cuda_backend_gather_rows(void *be, void *dst, const void *src, const int32_t *rows, int64_t n_rows, int64_t n) {
+    static_cast<CudaBackend *>(be)->gather_rows(dst, src, rows, n_rows, n);
+}
+void krk_cuda_backend_scatter_axpy_rows(void *be, void *dst, const void *src, const int32_t *rows, const float *alpha,
+                                        int64_t n_rows, int64_t n) {
+    static_cast<CudaBackend *>(be)->scatter_axpy_rows(dst, src, rows, alpha, n_rows, n);
+}
+void krk_cuda_backend_router_softmax(void *be, void *probs, const void *logits, int64_t n_rows, int32_t n_expert) {
+    static_cast<CudaBackend *>(be)->router_softmax(probs, logits, n_rows, n_expert);
+}
+void krk_cuda_backend_router_topk(void *be, const void *probs, int64_t n_rows, int32_t n_expert, int32_t k, void *ids,
+                                  void *wts, int32_t normalize, float scale) {
+    static_cast<CudaBackend *>(be)->router_topk(probs, n_rows, n_expert, k, ids, wts, normalize, scale);
+}
+void krk_cuda_backend_moe_plan_build(void *be, const void *ids, int64_t n_rows, int32_t k, int32_t n_expert, void *off,
+                                     void *rows, void *wt, const void *wts) {
+    static_cast<CudaBackend *>(be)->moe_plan_build(ids, n_rows, k, n_expert, off, rows, wt, wts);
+}
+int krk_cuda_backend_device(void *be) { return static_cast<CudaBackend *>(be)->device(); }
 void krk_cuda_backend_fill0(void *be, void *p, size_t bytes) { static_cast<CudaBackend *>(be)->fill0(p, bytes); }
 void krk_cuda_backend_sync(void *be) { static_cast<CudaBackend *>(be)->sync(); }
 int krk_cuda_backend_gemm_k_ok(void *be, int wt, int64_t k) {

@@ -26,6 +26,13 @@ inline int check_launch() {
     return KRK_CUDA_OK;
 }
 
+// exp of an f32 the way the host computes it: the host's expf (the reference's std::exp on a float,
+// src/engine.cpp:11704-11713, src/backend_cpu.cpp:2394-2400) is the correctly rounded result in all
+// but a fraction of a percent of its arguments; the device's own expf is only good to a unit in the
+// last place. Going through double gives the correctly rounded f32 here too, so that probabilities
+// ranked on the device collide and order exactly as they do on the host.
+__device__ __forceinline__ float exp_as_host(float x) { return (float)exp((double)x); }
+
 // ---- geometry (src/quant.cpp:1805-1900) ----------------------------------------------
 
 __host__ __device__ constexpr int block_size(int wt) {
@@ -227,6 +234,11 @@ int launch_logits_topk(const float *logits, int64_t n, int k, const uint32_t *pe
                        float temp, int32_t *ids, float *vals, float *mass_out, void *workspace, cudaStream_t st);
 int launch_route(int32_t *ids, float *wts, const float *logits, int64_t n_tok, int n_expert, int k,
                  cudaStream_t st);
+int launch_router_softmax(float *probs, const float *logits, int64_t n_rows, int n_expert, cudaStream_t st);
+int launch_router_topk(const float *probs, int64_t n_rows, int n_expert, int k, int32_t *ids, float *wts, int normalize,
+                       float scale, cudaStream_t st);
+int launch_moe_plan_build(const int32_t *ids, int64_t n_rows, int k, int n_expert, int32_t *off, int32_t *rows, float *wt,
+                          const float *wts, cudaStream_t st);
 size_t moe_workspace_bytes(const krk_cuda_expert_bank *bank, int k, int64_t n_tok);
 // With `logits` (and n_expert) the routing runs first and ids / wts are outputs.
 int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const float *wts,

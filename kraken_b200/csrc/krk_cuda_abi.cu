@@ -78,7 +78,7 @@ extern "C" {
 const char *krk_cuda_strerror(int rc) {
     switch (rc) {
     case KRK_CUDA_OK: return "ok";
-    case KRK_CUDA_EDTYPE: return "unsupported weight type (want Q8_0, Q4_0, Q4_K or Q6_K)";
+    case KRK_CUDA_EDTYPE: return "unsupported weight type (want Q8_0, Q4_0, Q4_K, Q6_K, Q5_0, Q5_1 or Q5_K)";
     case KRK_CUDA_ESHAPE: return "shape not addressable (n_in must be a positive whole number of blocks; sizes non-negative; rows in range)";
     case KRK_CUDA_ENULL: return "null pointer";
     case KRK_CUDA_EALIGN: return "misaligned pointer (weights and x 16 bytes, y 4 bytes)";
@@ -163,6 +163,7 @@ int krk_cuda_gemv_group(void *const host_y[], const void *const host_x[], const 
 
 size_t krk_cuda_gemm_workspace_bytes(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows) {
     if (rows <= 0 || n_in <= 0 || n_out <= 0) return 0;
+    if (n_in % 256 != 0) return 0;   // the row-batch rung below needs none
     return gemm_workspace_bytes(x_dtype, n_out, n_in, rows);
 }
 
@@ -171,7 +172,26 @@ int krk_cuda_gemm(void *y_f32, const void *x, int x_dtype, const void *w, int wt
     if (x_dtype != KRK_CUDA_X_F32 && x_dtype != KRK_CUDA_X_F16) return KRK_CUDA_EARG;
     const int rc = check_matmul_args(y_f32, x, w, wt, n_out, n_in, rows);
     if (rc != KRK_CUDA_OK) return rc;
-    if (n_in % 256 != 0) return KRK_CUDA_ESHAPE;
+    if (n_in % 256 != 0) {
+        // The fallback rung (the place of gemm_simt_kernel, src/hip/kernels/gemm.hpp:1013-1134): 32-value
+        // block formats whose K is a whole number of blocks but not of 256. Correct, not fast: the
+        // shape-agnostic GEMV over batches of KRK_CUDA_MAX_ROWS activation rows. f32 activations only.
+        if (x_dtype != KRK_CUDA_X_F32) return KRK_CUDA_ESHAPE;
+        if (n_out == 0 || rows == 0) return KRK_CUDA_OK;
+        if (!device_state()) return KRK_CUDA_EDEVICE;
+        for (int64_t r0 = 0; r0 < rows; r0 += KRK_CUDA_MAX_ROWS) {
+            const int64_t nr = rows - r0 < KRK_CUDA_MAX_ROWS ? rows - r0 : KRK_CUDA_MAX_ROWS;
+            GemvMat m;
+            m.w = static_cast<const uint8_t *>(w);
+            m.x = static_cast<const float *>(x) + r0 * n_in;
+            m.y = static_cast<float *>(y_f32) + r0 * n_out;
+            m.n_out = n_out;
+            m.wt = wt;
+            const int grc = launch_gemv_generic(&m, 1, n_in, (int)nr, 0, 0, static_cast<cudaStream_t>(stream));
+            if (grc != KRK_CUDA_OK) return grc;
+        }
+        return KRK_CUDA_OK;
+    }
     if (n_out == 0 || rows == 0) return KRK_CUDA_OK;
     const size_t need = gemm_workspace_bytes(x_dtype, n_out, n_in, rows);
     if (need > 0 && (!workspace || ws_bytes < need || !aligned(workspace, 128))) return KRK_CUDA_EWORKSPACE;
@@ -188,6 +208,33 @@ int krk_cuda_route(void *ids_i32, void *wts_f32, const void *logits_f32, int64_t
     return launch_route(static_cast<int32_t *>(ids_i32), static_cast<float *>(wts_f32),
                         static_cast<const float *>(logits_f32), n_tok, n_expert, k,
                         static_cast<cudaStream_t>(stream));
+}
+
+int krk_cuda_router_softmax(void *probs_f32, const void *logits_f32, int64_t n_rows, int n_expert, void *stream) {
+    if (n_rows < 0) return KRK_CUDA_ESHAPE;
+    if (n_rows > 0 && (!probs_f32 || !logits_f32)) return KRK_CUDA_ENULL;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_router_softmax(static_cast<float *>(probs_f32), static_cast<const float *>(logits_f32), n_rows, n_expert,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+int krk_cuda_router_topk(const void *probs_f32, int64_t n_rows, int n_expert, int k, void *ids_i32, void *wts_f32,
+                         int normalize, float scale, void *stream) {
+    if (n_rows < 0) return KRK_CUDA_ESHAPE;
+    if (n_rows > 0 && (!probs_f32 || !ids_i32 || !wts_f32)) return KRK_CUDA_ENULL;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_router_topk(static_cast<const float *>(probs_f32), n_rows, n_expert, k, static_cast<int32_t *>(ids_i32),
+                              static_cast<float *>(wts_f32), normalize, scale, static_cast<cudaStream_t>(stream));
+}
+
+int krk_cuda_moe_plan_build(const void *ids_i32, int64_t n_rows, int k, int n_expert, void *off_i32, void *rows_i32,
+                            void *wt_f32, const void *wts_f32, void *stream) {
+    if (n_rows < 0) return KRK_CUDA_ESHAPE;
+    if (!off_i32 || (n_rows > 0 && (!ids_i32 || !rows_i32 || !wt_f32))) return KRK_CUDA_ENULL;
+    if (!device_state()) return KRK_CUDA_EDEVICE;
+    return launch_moe_plan_build(static_cast<const int32_t *>(ids_i32), n_rows, k, n_expert, static_cast<int32_t *>(off_i32),
+                                 static_cast<int32_t *>(rows_i32), static_cast<float *>(wt_f32),
+                                 static_cast<const float *>(wts_f32), static_cast<cudaStream_t>(stream));
 }
 
 static int check_bank(const krk_cuda_expert_bank *b) {

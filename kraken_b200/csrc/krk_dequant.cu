@@ -37,7 +37,7 @@ silu_mul_kernel(float *__restrict__ out, const float *__restrict__ gate,
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (int64_t)gridDim.x * blockDim.x) {
         const float g = gate[i];
-        out[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), up[i]);
+        out[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, exp_as_host(-g))), up[i]);
     }
 }
 

@@ -35,6 +35,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <mutex>
 
 #include "krk_common.cuh"
 
@@ -1046,7 +1047,7 @@ int launch_gemm_tc(float *y, const void *x, int x_dtype, const uint8_t *w, int w
         if (rc != KRK_CUDA_OK) return rc;
         xh = reinterpret_cast<const __half *>(ws);
     }
-    GemmParams p;
+    GemmParams p{};
     p.w = w;
     p.y = y;
     p.n_out = n_out;
@@ -1095,6 +1096,9 @@ int launch_gemm_tc(float *y, const void *x, int x_dtype, const uint8_t *w, int w
 
 constexpr int64_t kStaticHalves = 4ll << 20;   // rows * n_in <= 4 Mi values (8 MiB of f16), e.g. 1024 x 4096
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticHalves * 2 + 256];   // f16 X, then a status word
+std::mutex g_static_mu;
+unsigned char *g_static_addr[64] = {};   // device address of the array, per device, once looked up
+int g_static_sms[64] = {};
 
 } // namespace krk_cuda
 
@@ -1113,36 +1117,35 @@ extern "C" int krk_cuda_gemm_f32_static(void *y_f32, const void *x_f32, const vo
 
     // Once per device, with that device current: the device address of the array. In host code the
     // array's name is only a handle for this query, never a pointer a kernel may be given.
-    static unsigned char *scratch_of[64] = {};
-    static int sms_of[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= 64) return KRK_CUDA_EDEVICE;
-    if (!scratch_of[dev]) {
-        void *ptr = nullptr;
-        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
-        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms_of[dev], cudaDevAttrMultiProcessorCount, dev);
-        if (e != cudaSuccess || !ptr) {
-            if (e != cudaSuccess) note_cuda_error(e);
-            return KRK_CUDA_EDEVICE;
+    unsigned char *scratch = nullptr;
+    int sms = 0;
+    {
+        // first use on this device, under a lock so that a second host thread never sees half of it
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        if (!g_static_addr[dev]) {
+            void *ptr = nullptr;
+            int n_sm = 0;
+            e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+            if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+            if (e != cudaSuccess || !ptr || n_sm <= 0) {
+                if (e != cudaSuccess) note_cuda_error(e);
+                return KRK_CUDA_EDEVICE;
+            }
+            g_static_sms[dev] = n_sm;
+            g_static_addr[dev] = static_cast<unsigned char *>(ptr);
         }
-        scratch_of[dev] = static_cast<unsigned char *>(ptr);
+        scratch = g_static_addr[dev];
+        sms = g_static_sms[dev];
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    __half *xh = reinterpret_cast<__half *>(scratch_of[dev]);
-    int *status = reinterpret_cast<int *>(scratch_of[dev] + kStaticHalves * 2);
+    __half *xh = reinterpret_cast<__half *>(scratch);
+    int *status = reinterpret_cast<int *>(scratch + kStaticHalves * 2);
 
-    // Every call overwrites the part of the array it uses before reading it (the conversion kernel
-    // below), so nothing of the previous call's contents is ever consumed.
-    const int64_t n = rows * n_in;
-    const int64_t want = (n + 255) / 256;
-    const int cgrid = (int)(want < (int64_t)sms_of[dev] * 8 ? want : (int64_t)sms_of[dev] * 8);
-    f32_to_f16_kernel<<<cgrid, 256, 0, st>>>(xh, static_cast<const float *>(x_f32), n);
-    note_launch();
-    int rc = check_launch();
-    if (rc != KRK_CUDA_OK) return rc;
-
-    GemmParams p;
+    // Everything that can fail on the host comes before the first launch.
+    GemmParams p{};
     p.w = static_cast<const uint8_t *>(w);
     p.y = static_cast<float *>(y_f32);
     p.n_out = n_out;
@@ -1152,6 +1155,8 @@ extern "C" int krk_cuda_gemm_f32_static(void *y_f32, const void *x_f32, const vo
     p.n_tiles_n = (int)((n_out + kTileN - 1) / kTileN);
     p.n_tiles_m = (int)((rows + p.tile_m - 1) / p.tile_m);
     p.row_bytes = (int)row_bytes(wt, n_in);
+    // Y leaves by tensor stores only where a tensor map can describe it; otherwise element by element
+    p.y_tma = ((reinterpret_cast<uintptr_t>(y_f32) & 15) == 0 && (n_out % 4) == 0) ? 1 : 0;
     p.split_tail = 0;   // cutting tiles needs counters in a workspace; this entry keeps whole tiles
     p.tail_count = nullptr;
     p.status = status;
@@ -1165,9 +1170,38 @@ extern "C" int krk_cuda_gemm_f32_static(void *y_f32, const void *x_f32, const vo
     if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return KRK_CUDA_ELAUNCH;
+    {
+        CUtensorMap probe_map;   // the maps launch_wt will encode: refuse now rather than after the first kernel
+        if (!encode_w_map(&probe_map, p.w, wt, n_out, p.row_bytes) || !encode_y_map(&probe_map, p.y, p.w, n_out, rows, p.y_tma != 0))
+            return KRK_CUDA_ELAUNCH;
+    }
+
+    // Every call overwrites the part of the array it uses before reading it (the conversion kernel
+    // below), so nothing of the previous call's contents is ever consumed.
+    const int64_t n = rows * n_in;
+    const int64_t want = (n + 255) / 256;
+    const int cgrid = (int)(want < (int64_t)sms * 8 ? want : (int64_t)sms * 8);
+    f32_to_f16_kernel<<<cgrid, 256, 0, st>>>(xh, static_cast<const float *>(x_f32), n);
+    note_launch();
+    int rc = check_launch();
+    if (rc != KRK_CUDA_OK) return rc;
     const int tiles = p.n_tiles_n * p.n_tiles_m;
-    const int grid = tiles < sms_of[dev] ? tiles : sms_of[dev];
+    const int grid = tiles < sms ? tiles : sms;
     rc = KRK_CUDA_EDTYPE;
     KRK_DISPATCH_WT(wt, rc = launch_wt<WT>(p, map, grid, st));
     return rc;
+}
+
+extern "C" int krk_cuda_gemm_f32_static_status(void) {
+    // The word behind the f16 area: 0, or the code a bounded wait of this entry's kernels left there.
+    // Read and cleared through the symbol itself (copies, no allocation); synchronises the device.
+    int v = 0;
+    const size_t at = (size_t)kStaticHalves * 2;
+    if (cudaDeviceSynchronize() != cudaSuccess) return KRK_CUDA_ELAUNCH;
+    if (cudaMemcpyFromSymbol(&v, g_static_scratch, sizeof v, at) != cudaSuccess) return KRK_CUDA_EDEVICE;
+    if (v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_static_scratch, &zero, sizeof zero, at);
+    }
+    return v;
 }

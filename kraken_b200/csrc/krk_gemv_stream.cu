@@ -6,8 +6,14 @@
 //  * One persistent CTA per SM owns a contiguous range of output rows. A producer warp streams
 //    that range through a ring of shared-memory stages with bulk-async copies (cp.async.bulk,
 //    one copy per weight row so that rows land on a padded, bank-conflict-free stride) signalled
-//    on mbarriers; 16 consumer warps never touch global memory for weights. The ring keeps
-//    50-150 KB of HBM reads in flight per SM without spending registers on it.
+//    on mbarriers; 8 consumer warps never touch global memory for weights. The ring keeps
+//    50-90 KB of HBM reads in flight per SM without spending registers on it.
+//
+//  * A CTA takes HALF an SM (320 threads, <= 113 KB of shared memory), so the CTA of the NEXT launch
+//    in the stream becomes resident (programmatic dependent launch) while this one is still
+//    streaming: it sets itself up and fills its ring with weights, which no kernel in flight
+//    writes, and only then waits for this grid to complete before it reads activations. The gap
+//    between two launches is then a CTA start, not a CTA start plus a pipeline fill.
 //
 //  * At 8 TB/s a B200 SM must retire ~40 four-bit weights per clock: unpacking each one to f32
 //    and issuing an FMA for it does not fit the issue budget. So the dot products run on the
@@ -26,8 +32,12 @@
 //
 // Every wait on an mbarrier is bounded; a wait that gives up raises the device status word
 // and the CTA drains without touching memory it does not own.
+#include <cuda.h>
+
 #include <cfloat>
 #include <cstdlib>
+#include <mutex>
+#include <unordered_map>
 
 #include "krk_common.cuh"
 
@@ -35,23 +45,27 @@ namespace krk_cuda {
 
 namespace {
 
-constexpr int kConsumerWarps = 16;
+constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 64;   // + the producer warp + the epilogue warp
+constexpr int kThreads = kConsumerThreads + 64;   // warp 0: producer, warps 1..8: consumers, warp 9: epilogue
+constexpr int kEpilogueWarp = kConsumerWarps + 1;
 // Tiles whose partial sums may wait for the epilogue warp (fewer when more activation rows make a slot larger).
 __host__ __device__ constexpr int red_slots(int ng) { return ng == 1 ? 4 : ng == 2 ? 2 : 1; }
 constexpr int kMaxRedSlots = 4;
 constexpr int kMaxStack = 4;      // 16-row tiles per stage at most
 constexpr int kTileRows = 16;                     // the M of the MMA
 constexpr int kMaxStages = 8;
-constexpr int kSmemLimit = 227 * 1024;
+constexpr int kSmemLimit = 113 * 1024;           // two CTAs per SM (228 KB, 1 KB reserved per CTA)
+constexpr int kSmemWhole = 227 * 1024;
+constexpr int kPlanePad = 32;                     // bytes between limb planes beyond n_in: spreads the B-fragment loads over the banks
 constexpr float kFixedOne = 8323072.0f;           // 127 * 65536: |X| <= this keeps every limb in s8
 constexpr long long kWaitCycles = 4000000000LL;   // ~2 s at boost clock, then give up
 
 template <int WT> struct Fmt;
-template <> struct Fmt<KRK_CUDA_Q4_K> { static constexpr int unit_values = 256, unit_bytes = 144, stride_mod = 32; };
-template <> struct Fmt<KRK_CUDA_Q6_K> { static constexpr int unit_values = 256, unit_bytes = 210, stride_mod = 16; };
-template <> struct Fmt<KRK_CUDA_Q8_0> { static constexpr int unit_values = 128, unit_bytes = 136, stride_mod = 16; };
+// tma: a unit is a whole number of 16-byte granules, so a stage can arrive as one tiled tensor copy
+template <> struct Fmt<KRK_CUDA_Q4_K> { static constexpr int unit_values = 256, unit_bytes = 144, stride_mod = 32; static constexpr bool tma = true; };
+template <> struct Fmt<KRK_CUDA_Q6_K> { static constexpr int unit_values = 256, unit_bytes = 210, stride_mod = 16; static constexpr bool tma = false; };
+template <> struct Fmt<KRK_CUDA_Q8_0> { static constexpr int unit_values = 128, unit_bytes = 136, stride_mod = 16; static constexpr bool tma = false; };
 
 struct StreamParams {
     GemvMat mat[KRK_CUDA_MAX_GROUP];
@@ -69,6 +83,9 @@ struct StreamParams {
                           // tile would leave most consumer warps idle: warp w takes unit w % units of
                           // sub-tile w / units)
     int row_stride;       // bytes between rows inside a stage
+    int unit_stride;      // bytes between the K units of one row group inside a stage
+    int use_tma;          // 1: a stage arrives as one tiled tensor copy, laid out [unit][row][unit_bytes]
+    int box_bytes;        // bytes one tensor copy signals (the whole box, also where the matrix clips it)
     int stage_bytes;
     int n_stages;
     int total_gran;
@@ -80,8 +97,10 @@ struct StreamParams {
     int *peer_flag[KRK_CUDA_MAX_PEERS];   // peer_flag[q][my_rank] <- epoch once every CTA here has stored
     int n_peers, my_rank, epoch, wait_peers;
     long long peer_row_stride, peer_offset;
-    unsigned *done_counter;
     int *status;
+    // per matrix: the weights as a 3-d tensor {unit_bytes, n_out rows, units per row}; box = {unit_bytes,
+    // rows of a stage, units of a stage}
+    CUtensorMap wmap[KRK_CUDA_MAX_GROUP];
 };
 
 
@@ -108,12 +127,35 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+// One tiled tensor copy global -> shared (no multicast): box origin (0, row, unit).
+__device__ __forceinline__ void tma_box(uint32_t dst, const CUtensorMap *map, int row, int unit, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(map), "r"(0), "r"(row), "r"(unit), "r"(bar) : "memory");
+}
 // c = A x B with a zero accumulator input (the sub-block scale is applied to c afterwards).
 __device__ __forceinline__ void mma_s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                            uint32_t b0, uint32_t b1) {
     asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+// The same with unsigned A bytes (raw nibble pairs q_lo + 16 q_hi, or masked nibbles).
+__device__ __forceinline__ void mma_u8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                           uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+// k16 with the accumulator preset to the bits of 1.5 * 2^23: for |sum| < 2^22 the s32 result read as a
+// float is exactly 12582912 + sum, so the conversion to float costs one subtraction instead of an I2F.
+constexpr float kMagic = 12582912.0f;
+__device__ __forceinline__ void mma_s8_k16_biased(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    int r[4];
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(0x4B400000));
+#pragma unroll
+    for (int i = 0; i < 4; i++) c[i] = __int_as_float(r[i]) - kMagic;
 }
 __device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
     asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
@@ -163,14 +205,15 @@ struct Smem {
     int gave_up;
     int pad[3];
     float gate[kMaxStack][NG][32];   // epilogue warp: the gate tile(s) of a gate/up pair, until the up tile arrives
-    // per consumer lane and column group: its weighted share of (row g | g+8) x (activation row even | odd)
-    float4 red[red_slots(NG)][kConsumerWarps][NG][32];
+    // per consumer warp, column group and row pair (g, g+8): {row g x even activation row, g x odd, g+8 x even, g+8 x odd}
+    float4 red[red_slots(NG)][kConsumerWarps][NG][8];
 };
 
 __host__ __device__ constexpr int align_up(int v, int a) { return (v + a - 1) / a * a; }
 
+__host__ __device__ inline int plane_stride(int n_in) { return n_in + kPlanePad; }
 template <int WT>
-__host__ __device__ inline int plane_bytes(int n_in, int rows) { return align_up(rows * 3 * n_in, 128); }
+__host__ __device__ inline int plane_bytes(int n_in, int rows) { return align_up(rows * 3 * plane_stride(n_in), 128); }
 template <int WT>
 __host__ __device__ inline int chunk_sum_bytes(int n_in, int rows) {   // [row][4 limbs][n_in / 32] s8
     return WT == KRK_CUDA_Q4_K ? align_up(rows * (n_in / 32) * 4, 128) : 0;
@@ -349,9 +392,9 @@ __device__ __forceinline__ void load_slice(const float *__restrict__ x, int k0, 
 template <int WT>
 __device__ __forceinline__ float prepare_x_row(const float *__restrict__ xr, const StreamParams &p, int8_t *p0, int8_t *sums,
                                                int wid, int lane) {
-    constexpr int UV = Fmt<WT>::unit_values, PER = UV / 32, kHeld = 3;
-    const int n_chunks = p.n_in >> 5;
-    // the first three slices stay in registers between the max and the quantisation (K <= 12288 for
+    constexpr int UV = Fmt<WT>::unit_values, PER = UV / 32, kHeld = 2;
+    const int n_chunks = p.n_in >> 5, ps = plane_stride(p.n_in);
+    // the first two slices stay in registers between the max and the quantisation (K <= 4096 for
     // 256-value units); any further ones are read twice
     float held[kHeld][PER];
     float mx = 0.0f;
@@ -375,14 +418,14 @@ __device__ __forceinline__ float prepare_x_row(const float *__restrict__ xr, con
     for (int j = 0; j < kHeld; j++) {
         const int u = wid + j * kConsumerWarps;
         if (u < p.units)
-            quantize_slice<WT>(held[j], inv, u * UV + lane * PER, p0, p0 + p.n_in, p0 + 2 * p.n_in, sums, n_chunks, lane);
+            quantize_slice<WT>(held[j], inv, u * UV + lane * PER, p0, p0 + ps, p0 + 2 * ps, sums, n_chunks, lane);
     }
     for (int u = wid + kHeld * kConsumerWarps; u < p.units; u += kConsumerWarps) {
         float f[PER];
         float m2 = 0.0f;
         int b2 = 0;
         load_slice<WT>(xr, u * UV + lane * PER, f, m2, b2);
-        quantize_slice<WT>(f, inv, u * UV + lane * PER, p0, p0 + p.n_in, p0 + 2 * p.n_in, sums, n_chunks, lane);
+        quantize_slice<WT>(f, inv, u * UV + lane * PER, p0, p0 + ps, p0 + 2 * ps, sums, n_chunks, lane);
     }
     return bad ? __int_as_float(0x7FC00000) : __fdiv_rn(mx, kFixedOne);
 }
@@ -419,7 +462,7 @@ __device__ __forceinline__ void lane_planes(const int8_t *planes, const int8_t *
 #pragma unroll
     for (int mg = 0; mg < NG; mg++) {
         const int r = min(2 * mg + (g % 6) / 3, rows - 1);
-        bp[mg] = planes + (size_t)(r * 3 + g % 3) * n_in;
+        bp[mg] = planes + (size_t)(r * 3 + g % 3) * plane_stride(n_in);
         // chunk sums: column c = limb c%4 of activation row c/4 of the group
         const int rs = min(2 * mg + g / 4, rows - 1);
         sp[mg] = chunk_sum + (size_t)(rs * 4 + g % 4) * (n_in >> 5);
@@ -485,6 +528,71 @@ __device__ __forceinline__ void unit_q4_k(const uint8_t *rowA, const uint8_t *ro
         acc.m[mg][2] = fmaf(nB, (float)cc[2], acc.m[mg][2]);
         acc.m[mg][3] = fmaf(nB, (float)cc[3], acc.m[mg][3]);
     }
+}
+
+// Q4_K with ONE activation row: both nibbles of a byte go through the tensor core unshifted.
+// The 32 bytes of a group hold chunk 2p in their low nibbles and chunk 2p+1 in their high ones.
+// Column 2j of the B fragment carries limb j of x over chunk 2p, column 2j+1 limb j over chunk
+// 2p+1. Two MMAs per group: L = (bytes & 0x0F) x B and R = (raw bytes) x B. Then, per limb,
+//   low chunk  = L[even column],     high chunk = (R[odd column] - L[odd column]) / 16,
+// because raw = q_lo + 16 q_hi. One AND per four bytes replaces the AND, shift, AND of the
+// two-MMA-per-chunk form; lane t keeps limb t of rows g and g+8 (t = 3 multiplies nothing).
+struct AccumSingle {
+    float f[2];   // rows g, g+8: limb t of d * sum over sub-blocks, times 16
+    float m[4];   // the min term as in Accum::m of one column group
+};
+// The B fragments of a unit (x limbs, chunk sums) are the same for every row tile: a warp that always works
+// on the same K units keeps them in registers (BFrag) instead of reading them from shared memory per tile.
+struct BFrag {
+    uint2 b[4];     // per group of two chunks
+    uint32_t m;     // chunk sums for the min term
+};
+__device__ __forceinline__ BFrag load_bfrag(const int8_t *bq, const int8_t *sq, int t) {
+    BFrag f;
+#pragma unroll
+    for (int p = 0; p < 4; p++) f.b[p] = *reinterpret_cast<const uint2 *>(bq + 64 * p + 8 * t);
+    f.m = *reinterpret_cast<const uint32_t *>(sq + 4 * (t & 1));
+    return f;
+}
+__device__ __forceinline__ void unit_q4_k_single(const uint8_t *rowA, const uint8_t *rowB, const BFrag &bf, int t,
+                                                 AccumSingle &acc) {
+    const uint4 hA = *reinterpret_cast<const uint4 *>(rowA);
+    const uint4 hB = *reinterpret_cast<const uint4 *>(rowB);
+    const uint32_t scA[2] = {hA.y & 0x3F3F3F3Fu, (hA.w & 0x0F0F0F0Fu) | ((hA.y >> 2) & 0x30303030u)};
+    const uint32_t scB[2] = {hB.y & 0x3F3F3F3Fu, (hB.w & 0x0F0F0F0Fu) | ((hB.y >> 2) & 0x30303030u)};
+    const uint32_t mnA[2] = {hA.z & 0x3F3F3F3Fu, ((hA.w >> 4) & 0x0F0F0F0Fu) | ((hA.z >> 2) & 0x30303030u)};
+    const uint32_t mnB[2] = {hB.z & 0x3F3F3F3Fu, ((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u)};
+    int loA = 0, hrA = 0, hlA = 0, loB = 0, hrB = 0, hlB = 0;
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+        const uint2 qa = *reinterpret_cast<const uint2 *>(rowA + 16 + 32 * p + 8 * t);
+        const uint2 qb = *reinterpret_cast<const uint2 *>(rowB + 16 + 32 * p + 8 * t);
+        const uint2 b = bf.b[p];
+        int cl[4], cr[4];
+        mma_u8_k32(cl, qa.x & 0x0F0F0F0Fu, qb.x & 0x0F0F0F0Fu, qa.y & 0x0F0F0F0Fu, qb.y & 0x0F0F0F0Fu, b.x, b.y);
+        mma_u8_k32(cr, qa.x, qb.x, qa.y, qb.y, b.x, b.y);
+        const int c0 = 2 * p, c1 = 2 * p + 1;
+        const int sA0 = (scA[c0 >> 2] >> (8 * (c0 & 3))) & 0xFF, sA1 = (scA[c1 >> 2] >> (8 * (c1 & 3))) & 0xFF;
+        const int sB0 = (scB[c0 >> 2] >> (8 * (c0 & 3))) & 0xFF, sB1 = (scB[c1 >> 2] >> (8 * (c1 & 3))) & 0xFF;
+        loA += sA0 * cl[0];
+        hrA += sA1 * cr[1];
+        hlA += sA1 * cl[1];
+        loB += sB0 * cl[2];
+        hrB += sB1 * cr[3];
+        hlB += sB1 * cl[3];
+    }
+    // |16 lo + hr - hl| < 2^29: 4 groups x 63 x 32 x (16 * 15 + 255 + 15) x 128
+    const float dA = half_lo(hA.x), dB = half_lo(hB.x);
+    acc.f[0] = fmaf(dA, (float)(16 * loA + hrA - hlA), acc.f[0]);
+    acc.f[1] = fmaf(dB, (float)(16 * loB + hrB - hlB), acc.f[1]);
+    const float nA = half_hi(hA.x), nB = half_hi(hB.x);
+    const uint32_t a0 = t < 2 ? mnA[t & 1] : 0u, a1 = t < 2 ? mnB[t & 1] : 0u;
+    float cm[4];
+    mma_s8_k16_biased(cm, a0, a1, bf.m);   // |sum| <= 8 x 63 x 128 < 2^22
+    acc.m[0] = fmaf(nA, cm[0], acc.m[0]);
+    acc.m[1] = fmaf(nA, cm[1], acc.m[1]);
+    acc.m[2] = fmaf(nB, cm[2], acc.m[2]);
+    acc.m[3] = fmaf(nB, cm[3], acc.m[3]);
 }
 
 // Four Q8_0 blocks. A block is a 2-byte scale then 32 quants, so blocks at an even index have
@@ -609,17 +717,22 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
 // ---- the kernel ------------------------------------------------------------------------------------------
 // Three roles, connected only by mbarriers, so no warp ever waits at a CTA-wide barrier while
 // weights are streaming:
-//   warp 16       producer: bulk-async copies of weight rows into the stage ring;
-//   warps 0..15   consumers: warp w takes K unit w of every stage (16 rows x 256 values), keeps the
+//   warp 0        producer: bulk-async copies of weight rows into the stage ring. It is the first warp of
+//                 the CTA to run, sets the barriers up itself and issues its first copies without waiting
+//                 for the other warps to start;
+//   warps 1..8    consumers: warp w takes K unit w of every stage (16 rows x 256 values), keeps the
 //                 tile's partial sums in registers and hands them over at the end of the tile;
-//   warp 17       epilogue: adds the 16 partial sums of each tile in warp order (deterministic),
+//   warp 9        epilogue: adds the partial sums of each tile in warp order (deterministic),
 //                 applies the gate/up fold or the residual add, and writes y.
 
-template <int WT, int NG, bool STACK>
-__global__ void __launch_bounds__(kThreads, 1)
+// SINGLE: 0 the general form; 1 Q4_K with one activation row (unit_q4_k_single); 2 the same with the B
+// fragments of the warp's (at most two) K units held in registers, for rows of at most 16 units.
+template <int WT, int NG, bool STACK, int SINGLE>
+__global__ void __launch_bounds__(kThreads, NG == 1 ? 2 : 1)
 gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     // STACK: several 16-row tiles per stage (p.tps of them); compiled apart so that the usual one-tile
-    // form carries none of its index arithmetic
+    // form carries none of its index arithmetic.
+    static_assert(!SINGLE || (WT == KRK_CUDA_Q4_K && NG == 1), "the single-row form is Q4_K only");
     const int tps = STACK ? p.tps : 1;
     using F = Fmt<WT>;
     using SmemT = Smem<NG>;
@@ -631,37 +744,79 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     int8_t *chunk_sum = planes + tps * plane_bytes<WT>(p.n_in, p.rows);
     uint8_t *stages = reinterpret_cast<uint8_t *>(chunk_sum) + tps * chunk_sum_bytes<WT>(p.n_in, p.rows);
 
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_warps = min(kConsumerWarps, p.units * tps);   // consumer warps that ever hold a unit
     const int sub_warps = STACK ? p.units : n_warps;         // warps that share one 16-row tile
-    // Programmatic dependent launch: the next kernel in the stream may start its prologue (and, being
-    // this same kernel, its weight prefetch) as soon as every CTA here has passed this point and an
-    // SM has room; it still waits for this grid to complete before touching activations or outputs.
+    // Programmatic dependent launch: the next kernel in the stream may become resident beside this one
+    // (a CTA takes half an SM) as soon as every CTA here has passed this point; it prefetches weights
+    // and waits for this grid to complete before touching activations or outputs.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // A device-side table is the output of the kernel before this one: every role waits for that grid.
-    if (p.dev_table) asm volatile("griddepcontrol.wait;" ::: "memory");
-    const TableView tv = table_view(p);
-    if (tid == 0) {
-        for (int s = 0; s < p.n_stages; s++) {
-            mbar_init(smem_u32(&sm->full[s]), 1);
-            mbar_init(smem_u32(&sm->empty[s]), kConsumerWarps);
-        }
-        for (int s = 0; s < red_slots(NG); s++) {
-            mbar_init(smem_u32(&sm->red_full[s]), n_warps);
-            mbar_init(smem_u32(&sm->red_empty[s]), 1);
-        }
-        sm->gave_up = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    __syncthreads();
     volatile int *gave_up = &sm->gave_up;
 
-    if (tid >= kConsumerThreads + 32) {
+    if (warp == 0) {
+        // ===== producer warp: weights only, so it can run ahead of everything else =====
+        if (lane == 0) {
+            for (int s = 0; s < p.n_stages; s++) {
+                mbar_init(smem_u32(&sm->full[s]), 1);
+                mbar_init(smem_u32(&sm->empty[s]), kConsumerWarps);
+            }
+            for (int s = 0; s < red_slots(NG); s++) {
+                mbar_init(smem_u32(&sm->red_full[s]), n_warps);
+                mbar_init(smem_u32(&sm->red_empty[s]), 1);
+            }
+            sm->gave_up = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __threadfence_block();
+        }
+        __syncwarp();
+        // the other warps wait here for the barriers (they arrive as they start); this warp does not wait
+        asm volatile("bar.arrive 1, %0;" ::"r"(kThreads) : "memory");
+        // A device-side table is the output of the kernel before this one: wait for that grid.
+        if (p.dev_table) asm volatile("griddepcontrol.wait;" ::: "memory");
+        const TableView tv = table_view(p);
+        walk(p, tv, tps, [](int) {}, [&](const StageInfo &s) {
+            const int slot = s.slot;
+            const uint32_t full = smem_u32(&sm->full[slot]), empty = smem_u32(&sm->empty[slot]);
+            wait_phase(empty, s.phase ^ 1, gave_up, p.status);
+            uint8_t *dst = stages + (size_t)slot * p.stage_bytes;
+            const uint8_t *src = tv.mat[s.mat].w + (size_t)s.row0 * p.row_bytes;
+            if (p.use_tma) {
+                // the box is clipped where the matrix ends (rows past n_out, units past the row) and
+                // still signals its full size
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(full, (uint32_t)p.box_bytes);
+                    tma_box(smem_u32(dst), &p.wmap[s.mat], s.row0, s.unit0, full);
+                }
+            } else if (!p.whole_tiles) {
+                const uint32_t bytes = (uint32_t)s.n_units * F::unit_bytes;
+                if (lane == 0) mbar_arrive_expect_tx(full, bytes * s.n_rows);
+                __syncwarp();
+                for (int r = lane; r < s.n_rows; r += 32)
+                    bulk_g2s(smem_u32(dst + r * p.row_stride),
+                             src + (size_t)r * p.row_bytes + (size_t)s.unit0 * F::unit_bytes, bytes, full);
+            } else if (lane == 0) {
+                // rows are not 16-byte multiples: one copy of the whole tile, rounded down to 16 bytes,
+                // and the (< 16 byte, 4-byte granular) tail with plain loads before the arrive
+                const uint32_t total = (uint32_t)s.n_rows * p.row_bytes;
+                const uint32_t bulk = total & ~15u;
+                for (uint32_t o = bulk; o < total; o += 4)
+                    *reinterpret_cast<uint32_t *>(dst + o) = *reinterpret_cast<const uint32_t *>(src + o);
+                mbar_arrive_expect_tx(full, bulk);
+                if (bulk) bulk_g2s(smem_u32(dst), src, bulk, full);
+            }
+            __syncwarp();
+        });
+        return;
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(kThreads) : "memory");
+    if (p.dev_table) asm volatile("griddepcontrol.wait;" ::: "memory");
+    const TableView tv = table_view(p);
+
+    if (warp == kEpilogueWarp) {
         // ===== epilogue warp =====
-        // Output (row, activation row) of a tile is the sum, over the consumer warps in warp order and
-        // their four lanes t = 0..3 of row group g, of the share each lane left in `red`.
-        const int lane = tid - kConsumerThreads - 32;
+        // Output (row, activation row) of a tile is the sum, over the consumer warps in warp order, of the
+        // share each warp left in `red` (already added up over the four lanes of a row group).
         constexpr int kSlots = red_slots(NG);
         float gate_reg[NG];   // gate tile kept for the silu fold (stacked tiles keep theirs in shared memory)
         int tile_it = 0;
@@ -676,16 +831,14 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
 #pragma unroll
                 for (int i = 0; i < NG; i++) {
                     const int idx = lane + 32 * i, row = idx & (kTileRows - 1), r = idx >> 4;   // r = 2*i + (lane >> 4)
-                    const float *src = reinterpret_cast<const float *>(&sm->red[slot][sub * sub_warps][i][4 * (row & 7)]) +
+                    const float *src = reinterpret_cast<const float *>(&sm->red[slot][sub * sub_warps][i][row & 7]) +
                                        2 * (row >> 3) + (r & 1);
+                    float part[kConsumerWarps];
+#pragma unroll
+                    for (int w = 0; w < kConsumerWarps; w++) part[w] = w < sub_warps ? src[(size_t)w * (NG * 8 * 4)] : 0.0f;
                     float v = 0.0f;
-                    for (int w = 0; w < sub_warps; w++) {
-                        const float *q = src + (size_t)w * (NG * 32 * 4);
-                        v += q[0];
-                        v += q[4];
-                        v += q[8];
-                        v += q[12];
-                    }
+#pragma unroll
+                    for (int w = 0; w < kConsumerWarps; w++) v += part[w];
                     const int srow = kTileRows * sub + row;   // row inside the stage
                     if (r < p.rows) {
                         if (p.step == 2 && s.which == 0) {
@@ -700,7 +853,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                                 const GemvMat &mat = tv.mat[p.step == 2 ? s.mat - 1 : s.mat];
                                 float *y = mat.y + (size_t)r * mat.n_out + s.row0 + srow;
                                 const float gt = STACK ? sm->gate[sub][i][lane] : gate_reg[i];
-                                if (p.step == 2) v = __fmul_rn(__fdiv_rn(gt, __fadd_rn(1.0f, expf(-gt))), v);
+                                if (p.step == 2) v = __fmul_rn(__fdiv_rn(gt, __fadd_rn(1.0f, exp_as_host(-gt))), v);
                                 *y = p.accumulate ? __fadd_rn(*y, v) : v;
                             }
                         }
@@ -713,17 +866,19 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         if (p.n_peers > 0) {
             // This CTA's stores are out. The CTA that reports last publishes the epoch to every peer and
             // then waits (bounded) until every peer has published the same epoch here, so that the end
-            // of this kernel is the end of the all-gather on this GPU.
+            // of this kernel is the end of the all-gather on this GPU. The count of CTAs that have
+            // reported lives behind this GPU's own flags (word n_peers + 1), one per exchange object.
             __threadfence_system();
             __syncwarp();
+            int *own = p.peer_flag[p.my_rank];
+            unsigned *done_counter = reinterpret_cast<unsigned *>(own + p.n_peers + 1);
             unsigned done = 0;
-            if (lane == 0) done = atomicAdd(p.done_counter, 1u);
+            if (lane == 0) done = atomicAdd(done_counter, 1u);
             done = __shfl_sync(0xffffffffu, done, 0);
             if (done == gridDim.x - 1) {
-                int *own = p.peer_flag[p.my_rank];
                 int epoch = p.epoch;
                 if (lane == 0) {
-                    *p.done_counter = 0;
+                    *done_counter = 0;
                     if (epoch == 0) {   // device-counted steps: the count lives behind this GPU's flags
                         epoch = own[p.n_peers] + 1;
                         own[p.n_peers] = epoch;
@@ -749,58 +904,33 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         return;
     }
 
-    if (tid >= kConsumerThreads) {
-        // ===== producer warp: weights only, so it can run ahead of everything else =====
-        const int lane = tid - kConsumerThreads;
-        walk(p, tv, tps, [](int) {}, [&](const StageInfo &s) {
-            const int slot = s.slot;
-            const uint32_t full = smem_u32(&sm->full[slot]), empty = smem_u32(&sm->empty[slot]);
-            wait_phase(empty, s.phase ^ 1, gave_up, p.status);
-            uint8_t *dst = stages + (size_t)slot * p.stage_bytes;
-            const uint8_t *src = tv.mat[s.mat].w + (size_t)s.row0 * p.row_bytes;
-            if (!p.whole_tiles) {
-                const uint32_t bytes = (uint32_t)s.n_units * F::unit_bytes;
-                if (lane == 0) mbar_arrive_expect_tx(full, bytes * s.n_rows);
-                __syncwarp();
-                for (int r = lane; r < (STACK ? s.n_rows : min(s.n_rows, 32)); r += 32)
-                    bulk_g2s(smem_u32(dst + r * p.row_stride),
-                             src + (size_t)r * p.row_bytes + (size_t)s.unit0 * F::unit_bytes, bytes, full);
-            } else if (lane == 0) {
-                // rows are not 16-byte multiples: one copy of the whole tile, rounded down to 16 bytes,
-                // and the (< 16 byte, 4-byte granular) tail with plain loads before the arrive
-                const uint32_t total = (uint32_t)s.n_rows * p.row_bytes;
-                const uint32_t bulk = total & ~15u;
-                for (uint32_t o = bulk; o < total; o += 4)
-                    *reinterpret_cast<uint32_t *>(dst + o) = *reinterpret_cast<const uint32_t *>(src + o);
-                mbar_arrive_expect_tx(full, bulk);
-                if (bulk) bulk_g2s(smem_u32(dst), src, bulk, full);
-            }
-            __syncwarp();
-        });
-        return;
-    }
-
     // ===== consumer warps =====
-    const int wid = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int wid = warp - 1, g = lane >> 2, t = lane & 3;
     const float *prepared = nullptr;
     const int8_t *bp[NG], *sp[NG];
     float xs[2 * NG];   // this warp's scale of each activation row
     Accum<NG> acc;
+    AccumSingle acs;
     accum_zero(acc);
+    acs.f[0] = acs.f[1] = acs.m[0] = acs.m[1] = acs.m[2] = acs.m[3] = 0.0f;
     int tile_it = 0;
-    // With stacked tiles warp w holds unit w % units of sub-tile w / units of every stage; otherwise unit
-    // w of every 16-unit chunk of the one tile in the stage.
+    // With stacked tiles warp w holds unit w % units of sub-tile w / units of every stage; otherwise units
+    // w, w + 8, ... of the stage (a stage holds at most 8 units unless it is one whole tile).
     const int my_sub = STACK ? wid / p.units : 0;
     const int my_unit = STACK ? wid - my_sub * p.units : wid;
     const bool stacked_idle = STACK && my_sub >= tps;
-    const uint32_t lane_off = (uint32_t)my_unit * F::unit_bytes + (uint32_t)(kTileRows * my_sub + g) * p.row_stride;
+    const uint32_t lane_off = (uint32_t)(kTileRows * my_sub + g) * p.row_stride;
     if (!stacked_idle) {
         planes += my_sub * plane_bytes<WT>(p.n_in, p.rows);
         chunk_sum += my_sub * chunk_sum_bytes<WT>(p.n_in, p.rows);
     }
+    // single-row form: column g = limb g/2 of the low (g even) or high (g odd) chunk of a group
+    const int8_t *bq = planes + (g < 6 ? (g >> 1) * plane_stride(p.n_in) + 32 * (g & 1) : 0);
+    const int8_t *sq = chunk_sum + (g & 3) * (p.n_in >> 5);
+    BFrag held[2];
 
     // The same walk as walk() above, written flat: per stage a consumer warp only needs the ring
-    // slot and its K unit, not which matrix or rows the tile belongs to.
+    // slot and its K units, not which matrix or rows the tile belongs to.
     const int cta = (int)blockIdx.x;
     const int g0 = cta * tv.gran_q + min(cta, tv.gran_r);
     const int g1 = g0 + tv.gran_q + (cta < tv.gran_r ? 1 : 0);
@@ -822,29 +952,46 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
 #pragma unroll
             for (int r = 0; r < 2 * NG; r++)
                 // (stacked tiles: every sub-tile prepares its own copy)
-                xs[r] = r < p.rows ? prepare_x_row<WT>(prepared + (size_t)r * p.n_in, p, planes + (size_t)(r * 3) * p.n_in,
+                xs[r] = r < p.rows ? prepare_x_row<WT>(prepared + (size_t)r * p.n_in, p,
+                                                       planes + (size_t)(r * 3) * plane_stride(p.n_in),
                                                        chunk_sum + (size_t)(r * 4) * (p.n_in >> 5),
                                                        stacked_idle ? kConsumerWarps : my_unit, lane)
                                    : 0.0f;
             __syncwarp();
-            lane_planes<NG>(planes, chunk_sum, p.n_in, p.rows, g, bp, sp);
+            if (!SINGLE) lane_planes<NG>(planes, chunk_sum, p.n_in, p.rows, g, bp, sp);
+            if (SINGLE == 2 && !stacked_idle) {
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int u = my_unit + j * kConsumerWarps;
+                    if (u < p.units) held[j] = load_bfrag(bq + u * F::unit_values, sq + ((u * F::unit_values) >> 5), t);
+                }
+            }
         }
         const int stage_rows = kTileRows * tps;
         const int n_tiles = ((r1 - r0 + stage_rows - 1) / stage_rows) * p.step;
         for (int tile = 0; tile < n_tiles; tile++) {
-            for (int ck = 0; ck < n_chunks; ck++) {
+            // one stage of the tile: `bf` are the warp's held B fragments for it (SINGLE == 2), else unused
+            auto stage = [&](const int ck, const BFrag &bf) {
                 wait_phase(full0 + 8 * slot, phase, gave_up, p.status);
-                const int unit = ck * kConsumerWarps + my_unit;
-                if (unit < p.units && !stacked_idle) {
-                    const uint8_t *rowA = stages + (size_t)slot * p.stage_bytes + lane_off, *rowB = rowA + (size_t)8 * p.row_stride;
-                    const int kbase = unit * F::unit_values;
-                    if (WT == KRK_CUDA_Q4_K) {
-                        unit_q4_k<NG>(rowA, rowB, kbase, bp, sp, t, acc);
-                    } else if (WT == KRK_CUDA_Q8_0) {
-                        unit_q8_0<NG>(rowA, rowB, kbase, bp, t, acc);
-                    } else {
-                        if (unit & 1) unit_q6_k<NG, true>(rowA, rowB, kbase, bp, t, acc);
-                        else unit_q6_k<NG, false>(rowA, rowB, kbase, bp, t, acc);
+                const int stage_units = p.whole_tiles ? p.units : min(kConsumerWarps, p.units - ck * kConsumerWarps);
+                if (!stacked_idle) {
+                    const uint8_t *tile0 = stages + (size_t)slot * p.stage_bytes + lane_off;
+                    for (int su = my_unit; su < stage_units; su += kConsumerWarps) {
+                        const uint8_t *rowA = tile0 + (size_t)su * p.unit_stride, *rowB = rowA + (size_t)8 * p.row_stride;
+                        const int unit = ck * kConsumerWarps + su;
+                        const int kbase = unit * F::unit_values;
+                        if (SINGLE == 2) {
+                            unit_q4_k_single(rowA, rowB, bf, t, acs);
+                        } else if (SINGLE == 1) {
+                            unit_q4_k_single(rowA, rowB, load_bfrag(bq + kbase, sq + (kbase >> 5), t), t, acs);
+                        } else if (WT == KRK_CUDA_Q4_K) {
+                            unit_q4_k<NG>(rowA, rowB, kbase, bp, sp, t, acc);
+                        } else if (WT == KRK_CUDA_Q8_0) {
+                            unit_q8_0<NG>(rowA, rowB, kbase, bp, t, acc);
+                        } else {
+                            if (unit & 1) unit_q6_k<NG, true>(rowA, rowB, kbase, bp, t, acc);
+                            else unit_q6_k<NG, false>(rowA, rowB, kbase, bp, t, acc);
+                        }
                     }
                 }
                 __syncwarp();
@@ -853,43 +1000,73 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                     slot = 0;
                     phase ^= 1;
                 }
+            };
+            if (SINGLE == 2) {   // at most two stages per tile, each with its own registers
+                stage(0, held[0]);
+                if (n_chunks > 1) stage(1, held[1]);
+            } else {
+                for (int ck = 0; ck < n_chunks; ck++) stage(ck, held[0]);
             }
             {
-             // ---- end of the tile: each lane leaves its weighted share of the four outputs it touches ----
-             // Column c of a group carries limb c%3 (weights 65536, 256, 1) of activation row c/3; this lane
-             // holds columns 2t and 2t+1, so its accumulators enter the even activation row with (we0, we1)
-             // and the odd one with (wo0, wo1). The Q4_K min term is already a per-lane partial sum.
+             // ---- end of the tile: the four lanes of a row group add their weighted shares, lane t = 0 leaves them ----
              constexpr int kSlots = red_slots(NG);
              const int rslot = tile_it % kSlots;
              const uint32_t rphase = (tile_it / kSlots) & 1;
              tile_it++;
              if (wid >= n_warps) continue;
-             wait_phase(smem_u32(&sm->red_empty[rslot]), rphase ^ 1, gave_up, p.status);
-             const float we0 = t == 0 ? 65536.0f : (t == 1 ? 1.0f : 0.0f), we1 = t == 0 ? 256.0f : 0.0f;
-             const float wo0 = t == 2 ? 256.0f : 0.0f, wo1 = t == 1 ? 65536.0f : (t == 2 ? 1.0f : 0.0f);
              // min columns: limb c%4 (weights 2^24, 2^16, 2^8, 1) of activation row c/4
              const float me0 = t == 0 ? 16777216.0f : (t == 1 ? 256.0f : 0.0f), me1 = t == 0 ? 65536.0f : (t == 1 ? 1.0f : 0.0f);
              const float mo0 = t == 2 ? 16777216.0f : (t == 3 ? 256.0f : 0.0f), mo1 = t == 2 ? 65536.0f : (t == 3 ? 1.0f : 0.0f);
+             float4 o[NG];
+             if (SINGLE) {
+                 // lane t holds limb t (weights 65536, 256, 1) of rows g and g+8, times 16
+                 const float wl = t == 0 ? 4096.0f : (t == 1 ? 16.0f : (t == 2 ? 0.0625f : 0.0f));
+                 o[0].x = (wl * acs.f[0] - fmaf(me0, acs.m[0], me1 * acs.m[1])) * xs[0];
+                 o[0].z = (wl * acs.f[1] - fmaf(me0, acs.m[2], me1 * acs.m[3])) * xs[0];
+                 o[0].y = o[0].w = 0.0f;
+                 acs.f[0] = acs.f[1] = acs.m[0] = acs.m[1] = acs.m[2] = acs.m[3] = 0.0f;
+             } else {
+                 // Column c of a group carries limb c%3 (weights 65536, 256, 1) of activation row c/3; this lane
+                 // holds columns 2t and 2t+1, so its accumulators enter the even activation row with (we0, we1)
+                 // and the odd one with (wo0, wo1). The Q4_K min term is already a per-lane partial sum.
+                 const float we0 = t == 0 ? 65536.0f : (t == 1 ? 1.0f : 0.0f), we1 = t == 0 ? 256.0f : 0.0f;
+                 const float wo0 = t == 2 ? 256.0f : 0.0f, wo1 = t == 1 ? 65536.0f : (t == 2 ? 1.0f : 0.0f);
+#pragma unroll
+                 for (int mg = 0; mg < NG; mg++) {
+                     o[mg].x = fmaf(we0, acc.f[mg][0], we1 * acc.f[mg][1]);   // row g,   even activation row
+                     o[mg].y = fmaf(wo0, acc.f[mg][0], wo1 * acc.f[mg][1]);   // row g,   odd
+                     o[mg].z = fmaf(we0, acc.f[mg][2], we1 * acc.f[mg][3]);   // row g+8, even
+                     o[mg].w = fmaf(wo0, acc.f[mg][2], wo1 * acc.f[mg][3]);   // row g+8, odd
+                     if (WT == KRK_CUDA_Q4_K) {
+                         o[mg].x -= fmaf(me0, acc.m[mg][0], me1 * acc.m[mg][1]);
+                         o[mg].y -= fmaf(mo0, acc.m[mg][0], mo1 * acc.m[mg][1]);
+                         o[mg].z -= fmaf(me0, acc.m[mg][2], me1 * acc.m[mg][3]);
+                         o[mg].w -= fmaf(mo0, acc.m[mg][2], mo1 * acc.m[mg][3]);
+                     }
+                     o[mg].x *= xs[2 * mg];
+                     o[mg].y *= xs[2 * mg + 1];
+                     o[mg].z *= xs[2 * mg];
+                     o[mg].w *= xs[2 * mg + 1];
+                 }
+                 accum_zero(acc);
+             }
 #pragma unroll
              for (int mg = 0; mg < NG; mg++) {
-                 float4 o;
-                 o.x = fmaf(we0, acc.f[mg][0], we1 * acc.f[mg][1]);   // row g,   even activation row
-                 o.y = fmaf(wo0, acc.f[mg][0], wo1 * acc.f[mg][1]);   // row g,   odd
-                 o.z = fmaf(we0, acc.f[mg][2], we1 * acc.f[mg][3]);   // row g+8, even
-                 o.w = fmaf(wo0, acc.f[mg][2], wo1 * acc.f[mg][3]);   // row g+8, odd
-                 if (WT == KRK_CUDA_Q4_K) {
-                     o.x -= fmaf(me0, acc.m[mg][0], me1 * acc.m[mg][1]);
-                     o.y -= fmaf(mo0, acc.m[mg][0], mo1 * acc.m[mg][1]);
-                     o.z -= fmaf(me0, acc.m[mg][2], me1 * acc.m[mg][3]);
-                     o.w -= fmaf(mo0, acc.m[mg][2], mo1 * acc.m[mg][3]);
+#pragma unroll
+                 for (int d = 1; d <= 2; d <<= 1) {   // (t0 + t1) + (t2 + t3): a fixed order
+                     o[mg].x += __shfl_xor_sync(0xFFFFFFFFu, o[mg].x, d);
+                     o[mg].z += __shfl_xor_sync(0xFFFFFFFFu, o[mg].z, d);
+                     if (!SINGLE) {
+                         o[mg].y += __shfl_xor_sync(0xFFFFFFFFu, o[mg].y, d);
+                         o[mg].w += __shfl_xor_sync(0xFFFFFFFFu, o[mg].w, d);
+                     }
                  }
-                 o.x *= xs[2 * mg];
-                 o.y *= xs[2 * mg + 1];
-                 o.z *= xs[2 * mg];
-                 o.w *= xs[2 * mg + 1];
-                 sm->red[rslot][wid][mg][lane] = o;
              }
-             accum_zero(acc);
+             wait_phase(smem_u32(&sm->red_empty[rslot]), rphase ^ 1, gave_up, p.status);
+             if (t == 0) {
+#pragma unroll
+                 for (int mg = 0; mg < NG; mg++) sm->red[rslot][wid][mg][g] = o[mg];
+             }
              __syncwarp();
              if (lane == 0) mbar_arrive(smem_u32(&sm->red_full[rslot]));
             }
@@ -897,14 +1074,16 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     }
 }
 
-template <int WT, int NG, bool STACK>
+template <int WT, int NG, bool STACK, int SINGLE>
 int launch_one(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
     static bool configured[64] = {};   // per instantiation and device: the opt-in is sticky
-    auto kernel = gemv_stream_kernel<WT, NG, STACK>;
+    auto kernel = gemv_stream_kernel<WT, NG, STACK, SINGLE>;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemWhole);
+        // all of the SM's configurable memory as shared memory, so that two CTAs fit
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         if (e != cudaSuccess) {
             note_cuda_error(e);
             return KRK_CUDA_ELAUNCH;
@@ -934,7 +1113,7 @@ int launch_one(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
 // Fills the fields that depend only on the format, the width and the activation row count.
 // Returns false when the streaming kernel does not address the shape.
 template <int WT>
-bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t *smem_out) {
+bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t *smem_out, bool want_tma = false) {
     using F = Fmt<WT>;
     if (n_in % 256 != 0 || n_in > (1 << 20) || rows < 1 || rows > KRK_CUDA_MAX_ROWS) return false;
     p.n_in = (int)n_in;
@@ -949,18 +1128,28 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
     p.n_peers = 0;
     p.my_rank = p.epoch = 0;
     p.peer_row_stride = p.peer_offset = 0;
-    p.done_counter = nullptr;
     if (WT == KRK_CUDA_Q6_K && (n_in % 2048) != 0) {
         // 210-byte blocks: rows are 16-byte multiples only for K % 2048 == 0. Otherwise whole 16-row
         // tiles are copied contiguously (needs 4-byte-multiple rows and the tile in one stage).
-        if ((p.row_bytes & 3) != 0 || p.units > kConsumerWarps) return false;
+        if ((p.row_bytes & 3) != 0 || p.units > 2 * kConsumerWarps) return false;
         p.whole_tiles = 1;
         p.gran = 8;
     }
     const int ku_max = p.whole_tiles ? p.units : (p.units < kConsumerWarps ? p.units : kConsumerWarps);
     p.tps = kConsumerWarps / p.units;   // 0 when a tile has more units than there are consumer warps
     p.tps = p.tps < 1 ? 1 : (p.tps > kMaxStack ? kMaxStack : p.tps);
-    if (p.whole_tiles) {
+    p.use_tma = 0;
+    p.box_bytes = 0;
+    p.unit_stride = F::unit_bytes;
+    if (want_tma && F::tma && !p.whole_tiles) {
+        // a stage is one tensor copy: [units of the stage][rows of the stage][unit_bytes]. The 144-byte
+        // pitch of a Q4_K unit puts the eight rows of a fragment load 16 bytes apart in the banks.
+        p.use_tma = 1;
+        p.row_stride = F::unit_bytes;
+        p.unit_stride = kTileRows * p.tps * F::unit_bytes;
+        p.box_bytes = ku_max * p.unit_stride;
+        p.stage_bytes = align_up(p.box_bytes, 128);
+    } else if (p.whole_tiles) {
         p.row_stride = p.row_bytes;
         p.stage_bytes = align_up(kTileRows * p.tps * p.row_bytes, 128);
     } else {
@@ -970,16 +1159,12 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
     }
     const int smem_struct = rows <= 2 ? (int)sizeof(Smem<1>) : rows <= 4 ? (int)sizeof(Smem<2>) : (int)sizeof(Smem<4>);
     const int fixed = align_up(smem_struct, 128) + p.tps * (plane_bytes<WT>(p.n_in, rows) + chunk_sum_bytes<WT>(p.n_in, rows));
-    // Depth of the ring: KRK_CUDA_GEMV_STAGE_KB of staged weights per SM (default 96), at least 3 stages.
-    static const int stage_kb = [] {
-        const char *e = std::getenv("KRK_CUDA_GEMV_STAGE_KB");
-        const int v = e ? std::atoi(e) : 0;
-        return v > 0 ? v : 96;
-    }();
-    const int max_fit = (kSmemLimit - fixed) / p.stage_bytes;
-    int want = (stage_kb * 1024 + p.stage_bytes - 1) / p.stage_bytes;
-    want = want < 3 ? 3 : (want > kMaxStages ? kMaxStages : want);
-    p.n_stages = want < max_fit ? want : max_fit;
+    // Depth of the ring: as many stages as fit beside the prepared activation in half an SM, at most
+    // kMaxStages. Wide activations (large K) leave too little of a half, and the forms for more than two
+    // activation rows are compiled for one CTA per SM (more registers): those take the whole SM.
+    int max_fit = rows <= 2 ? (kSmemLimit - fixed) / p.stage_bytes : 0;
+    if (max_fit < 3) max_fit = (kSmemWhole - fixed) / p.stage_bytes;
+    p.n_stages = max_fit < kMaxStages ? max_fit : kMaxStages;
     if (p.n_stages < 2) return false;
     *smem_out = (size_t)fixed + (size_t)p.n_stages * p.stage_bytes;
     return true;
@@ -987,21 +1172,115 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
 
 template <int WT>
 int launch_rows(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
+    constexpr bool kQ4K = WT == KRK_CUDA_Q4_K;
     if (p.tps > 1) {
-        if (p.rows <= 2) return launch_one<WT, 1, true>(p, grid, smem, st);
-        if (p.rows <= 4) return launch_one<WT, 2, true>(p, grid, smem, st);
-        return launch_one<WT, 4, true>(p, grid, smem, st);
+        if (kQ4K && p.rows == 1) return launch_one<WT, 1, true, kQ4K ? 2 : 0>(p, grid, smem, st);
+        if (p.rows <= 2) return launch_one<WT, 1, true, 0>(p, grid, smem, st);
+        if (p.rows <= 4) return launch_one<WT, 2, true, 0>(p, grid, smem, st);
+        return launch_one<WT, 4, true, 0>(p, grid, smem, st);
     }
-    if (p.rows <= 2) return launch_one<WT, 1, false>(p, grid, smem, st);
-    if (p.rows <= 4) return launch_one<WT, 2, false>(p, grid, smem, st);
-    return launch_one<WT, 4, false>(p, grid, smem, st);
+    if (kQ4K && p.rows == 1 && !p.whole_tiles && p.units <= 2 * kConsumerWarps) return launch_one<WT, 1, false, kQ4K ? 2 : 0>(p, grid, smem, st);
+    if (kQ4K && p.rows == 1) return launch_one<WT, 1, false, kQ4K ? 1 : 0>(p, grid, smem, st);
+    if (p.rows <= 2) return launch_one<WT, 1, false, 0>(p, grid, smem, st);
+    if (p.rows <= 4) return launch_one<WT, 2, false, 0>(p, grid, smem, st);
+    return launch_one<WT, 4, false, 0>(p, grid, smem, st);
+}
+
+// CTAs of one launch per SM. 1 (default): the other half of the SM is left to the next launch in the
+// stream, which sets itself up and prefetches while this one streams. 2 (KRK_CUDA_GEMV_CTAS_PER_SM=2):
+// both halves work on this launch.
+int ctas_per_sm(size_t smem) {
+    static const int want = [] {
+        const char *e = std::getenv("KRK_CUDA_GEMV_CTAS_PER_SM");
+        const int v = e ? std::atoi(e) : 0;
+        return v == 2 ? 2 : 1;
+    }();
+    return smem <= (size_t)kSmemLimit ? want : 1;
+}
+
+// Tensor maps are encoded on the host (a driver call of a microsecond or two) and kept per (matrix, box):
+// weights stay where they were uploaded, so a decode loop encodes each matrix once.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+struct MapKey {
+    const void *w;
+    int64_t n_out;
+    int row_bytes, unit_bytes, box_rows, box_units;
+    bool operator==(const MapKey &o) const {
+        return w == o.w && n_out == o.n_out && row_bytes == o.row_bytes && unit_bytes == o.unit_bytes &&
+               box_rows == o.box_rows && box_units == o.box_units;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey &k) const {
+        size_t h = reinterpret_cast<size_t>(k.w) * 0x9E3779B97F4A7C15ull;
+        h ^= (size_t)k.n_out * 0xC2B2AE3D27D4EB4Full + (size_t)k.row_bytes * 31 + (size_t)k.box_rows * 7 + (size_t)k.box_units;
+        return h;
+    }
+};
+bool weight_map(CUtensorMap *out, const uint8_t *w, int64_t n_out, int row_bytes, int unit_bytes, int box_rows, int box_units) {
+    static EncodeTiledFn encode = [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            ptr = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(ptr);
+    }();
+    if (!encode) return false;
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{w, n_out, row_bytes, unit_bytes, box_rows, box_units};
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return true;
+    }
+    const cuuint64_t dims[3] = {(cuuint64_t)unit_bytes, (cuuint64_t)n_out, (cuuint64_t)(row_bytes / unit_bytes)};
+    const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, (cuuint64_t)unit_bytes};
+    const cuuint32_t box[3] = {(cuuint32_t)unit_bytes, (cuuint32_t)box_rows, (cuuint32_t)box_units};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    CUtensorMap m;
+    if (encode(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t *>(w), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    if (cache.size() > 65536) cache.clear();   // bounded: a host that keeps re-uploading weights starts over
+    cache.emplace(key, m);
+    *out = m;
+    return true;
+}
+
+// Fills p.wmap for the first n matrices of p.mat; on failure the launch falls back to row copies.
+template <int WT>
+bool encode_maps(StreamParams &p, int n) {
+    using F = Fmt<WT>;
+    const int ku_max = p.units < kConsumerWarps ? p.units : kConsumerWarps;
+    for (int m = 0; m < n; m++) {
+        if (p.mat[m].n_out <= 0) continue;
+        if ((reinterpret_cast<uintptr_t>(p.mat[m].w) & 15) != 0) return false;
+        if (!weight_map(&p.wmap[m], p.mat[m].w, p.mat[m].n_out, p.row_bytes, F::unit_bytes, kTileRows * p.tps, ku_max)) return false;
+    }
+    return true;
 }
 
 template <int WT>
 int launch_fmt(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accumulate, int silu_pair, cudaStream_t st) {
     StreamParams p;
     size_t smem = 0;
-    if (!setup_format<WT>(p, n_in, rows, silu_pair, &smem)) return 0;
+    static const bool no_tma = std::getenv("KRK_CUDA_GEMV_NO_TMA") != nullptr;
+    bool tma = Fmt<WT>::tma && !no_tma;
+    if (tma) {
+        // try the tensor-copy layout first; if a map cannot be encoded, set up again for row copies
+        if (!setup_format<WT>(p, n_in, rows, silu_pair, &smem, true)) return 0;
+        if (p.use_tma) {
+            for (int m = 0; m < n_mat; m++) p.mat[m] = mats[m];
+            if (!encode_maps<WT>(p, n_mat)) tma = false;
+        }
+    }
+    if (!tma && !setup_format<WT>(p, n_in, rows, silu_pair, &smem)) return 0;
     p.accumulate = accumulate;
     p.n_entries = 0;
     int total = 0;
@@ -1017,7 +1296,7 @@ int launch_fmt(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accum
     if (total == 0) return 1;
     p.status = device_status_word();
     if (!p.status) return KRK_CUDA_EDEVICE;
-    const int sms = sm_count();
+    const int sms = sm_count() * ctas_per_sm(smem);
     const int grid = total < sms ? total : sms;
     p.gran_q = total / grid;
     p.gran_r = total % grid;
@@ -1054,15 +1333,6 @@ int launch_peers_fmt(const GemvMat &mat, int64_t n_in, int rows, const PeerScatt
     p.total_gran = total;
     p.status = device_status_word();
     if (!p.status) return KRK_CUDA_EDEVICE;
-    static unsigned *counter_of[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) return KRK_CUDA_EDEVICE;
-    if (!counter_of[dev]) {
-        if (cudaMalloc(&counter_of[dev], sizeof(unsigned)) != cudaSuccess) return KRK_CUDA_EDEVICE;
-        cudaMemset(counter_of[dev], 0, sizeof(unsigned));
-    }
-    p.done_counter = counter_of[dev];
     p.n_peers = ps.n_peers;
     for (int q = 0; q < ps.n_peers; q++) {
         p.peer_y[q] = ps.y[q];

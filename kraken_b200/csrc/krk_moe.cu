@@ -24,7 +24,7 @@ __device__ __forceinline__ void route_token(int32_t *__restrict__ ids, float *__
     for (int e = lane; e < n_expert; e += 32) mx = fmaxf(mx, lg[e]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-    for (int e = lane; e < n_expert; e += 32) prob[e] = expf(__fsub_rn(lg[e], mx));
+    for (int e = lane; e < n_expert; e += 32) prob[e] = exp_as_host(__fsub_rn(lg[e], mx));
     __syncwarp();
     float sum = 0.0f;
     if (lane == 0)
@@ -78,6 +78,117 @@ route_kernel(int32_t *__restrict__ ids, float *__restrict__ wts, const float *__
     route_token(ids + t * k, wts + t * k, logits + t * n_expert, n_expert, k, prob, wsel, threadIdx.x);
 }
 
+// The router in the three steps Backend exposes (include/krk/backend.hpp:934-986): probabilities,
+// selection, expert-major plan. Same arithmetic as route_token, split where the interface splits it.
+__global__ void __launch_bounds__(32)
+router_softmax_kernel(float *__restrict__ probs, const float *__restrict__ logits, int n_expert) {
+    const float *lg = logits + (int64_t)blockIdx.x * n_expert;
+    float *pr = probs + (int64_t)blockIdx.x * n_expert;
+    const int lane = threadIdx.x;
+    float mx = -INFINITY;
+    for (int e = lane; e < n_expert; e += 32) mx = fmaxf(mx, lg[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    for (int e = lane; e < n_expert; e += 32) pr[e] = exp_as_host(__fsub_rn(lg[e], mx));
+    __syncwarp();
+    float sum = 0.0f;
+    if (lane == 0)
+        for (int e = 0; e < n_expert; e++) sum = __fadd_rn(sum, pr[e]);   // in expert order, as the host adds them
+    sum = __shfl_sync(0xFFFFFFFFu, sum, 0);
+    const float inv = sum > 0.0f ? __fdiv_rn(1.0f, sum) : 0.0f;
+    for (int e = lane; e < n_expert; e += 32) pr[e] = __fmul_rn(pr[e], inv);
+}
+
+// k picks of the largest probability per row (strict '>': a tie keeps the lower id), weights = the picked
+// probabilities, divided by their slot-order sum when `normalize`, times `scale`.
+__global__ void __launch_bounds__(32)
+router_topk_kernel(const float *__restrict__ probs, int n_expert, int k, int32_t *__restrict__ ids, float *__restrict__ wts,
+                   int normalize, float scale) {
+    __shared__ float prob[kMaxExperts];
+    __shared__ float wsel[kMaxK];
+    const float *pr = probs + (int64_t)blockIdx.x * n_expert;
+    const int lane = threadIdx.x;
+    for (int e = lane; e < n_expert; e += 32) prob[e] = pr[e];
+    __syncwarp();
+    for (int s = 0; s < k; s++) {
+        float bp = -1.0f;
+        int be = 0x7FFFFFFF;
+        for (int e = lane; e < n_expert; e += 32) {
+            const float pe = prob[e];
+            if (pe > bp) {
+                bp = pe;
+                be = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float op = __shfl_xor_sync(0xFFFFFFFFu, bp, o);
+            const int oe = __shfl_xor_sync(0xFFFFFFFFu, be, o);
+            if (op > bp || (op == bp && oe < be)) {
+                bp = op;
+                be = oe;
+            }
+        }
+        if (lane == 0) {
+            const bool ok = be < n_expert && bp >= 0.0f;
+            ids[(int64_t)blockIdx.x * k + s] = ok ? be : -1;
+            wsel[s] = ok ? bp : 0.0f;
+            if (ok) prob[be] = -2.0f;
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        float kinv = 1.0f;
+        if (normalize) {
+            float ksum = 0.0f;
+            for (int s = 0; s < k; s++) ksum = __fadd_rn(ksum, wsel[s]);
+            kinv = ksum > 0.0f ? __fdiv_rn(1.0f, ksum) : 0.0f;
+        }
+        for (int s = 0; s < k; s++) {
+            float w = normalize ? __fmul_rn(wsel[s], kinv) : wsel[s];
+            if (scale != 1.0f) w = __fmul_rn(w, scale);
+            wts[(int64_t)blockIdx.x * k + s] = w;
+        }
+    }
+}
+
+// The expert-major plan of a layer from the selected ids: off[n_expert + 1] prefix offsets, rows[n * k] the
+// token of each entry and wt[n * k] its weight, entries of one expert in (token, slot) order: the order of the
+// host's plan (src/engine.cpp:12215-12248; device twin src/hip/kernels/router.hpp:252-289). Thread e walks
+// the pairs in order for expert e, so the order is prescribed, not left to scheduling. One block.
+__global__ void __launch_bounds__(1024)
+moe_plan_build_kernel(const int32_t *__restrict__ ids, int n_rows, int k, int n_expert, int32_t *__restrict__ off,
+                      int32_t *__restrict__ rows, float *__restrict__ wt, const float *__restrict__ wts) {
+    __shared__ int count[kMaxExperts + 1];
+    const int nk = n_rows * k;
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+        int c = 0;
+        for (int i = 0; i < nk; i++) c += ids[i] == e;
+        count[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < n_expert; e++) {
+            const int c = count[e];
+            count[e] = run;
+            off[e] = run;
+            run += c;
+        }
+        off[n_expert] = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+        int at = count[e];
+        for (int i = 0; i < nk; i++)
+            if (ids[i] == e) {
+                rows[at] = i / k;
+                wt[at] = wts ? wts[i] : 0.0f;
+                at++;
+            }
+    }
+}
+
 struct MoeParams {
     const uint8_t *gate, *up, *down;
     const float *x;        // [n_tok][n_embd]
@@ -117,7 +228,7 @@ moe_gate_up_kernel(const __grid_constant__ MoeParams p) {
     sg = warp_sum(sg);
     su = warp_sum(su);
     if (lane == 0)
-        p.h[(int64_t)pick * p.n_ff + row] = __fmul_rn(__fdiv_rn(sg, __fadd_rn(1.0f, expf(-sg))), su);
+        p.h[(int64_t)pick * p.n_ff + row] = __fmul_rn(__fdiv_rn(sg, __fadd_rn(1.0f, exp_as_host(-sg))), su);
 }
 
 // d[pick][row] = Wdown_e[row] . h[pick]
@@ -247,6 +358,32 @@ int launch_route(int32_t *ids, float *wts, const float *logits, int64_t n_tok, i
         return KRK_CUDA_EARG;
     if (n_tok == 0) return KRK_CUDA_OK;
     route_kernel<<<(unsigned)n_tok, 32, 0, st>>>(ids, wts, logits, n_expert, k);
+    note_launch();
+    return check_launch();
+}
+
+int launch_router_softmax(float *probs, const float *logits, int64_t n_rows, int n_expert, cudaStream_t st) {
+    if (n_expert <= 0 || n_expert > kMaxExperts) return KRK_CUDA_EARG;
+    if (n_rows == 0) return KRK_CUDA_OK;
+    router_softmax_kernel<<<(unsigned)n_rows, 32, 0, st>>>(probs, logits, n_expert);
+    note_launch();
+    return check_launch();
+}
+
+int launch_router_topk(const float *probs, int64_t n_rows, int n_expert, int k, int32_t *ids, float *wts, int normalize,
+                       float scale, cudaStream_t st) {
+    if (n_expert <= 0 || n_expert > kMaxExperts || k <= 0 || k > kMaxK || k > n_expert) return KRK_CUDA_EARG;
+    if (n_rows == 0) return KRK_CUDA_OK;
+    router_topk_kernel<<<(unsigned)n_rows, 32, 0, st>>>(probs, n_expert, k, ids, wts, normalize, scale);
+    note_launch();
+    return check_launch();
+}
+
+int launch_moe_plan_build(const int32_t *ids, int64_t n_rows, int k, int n_expert, int32_t *off, int32_t *rows, float *wt,
+                          const float *wts, cudaStream_t st) {
+    if (n_expert <= 0 || n_expert > kMaxExperts || k <= 0 || n_rows < 0 || n_rows * k > (1 << 24)) return KRK_CUDA_EARG;
+    moe_plan_build_kernel<<<1, n_expert < 1024 ? ((n_expert + 31) / 32) * 32 : 1024, 0, st>>>(ids, (int)n_rows, k, n_expert, off, rows,
+                                                                                              wt, wts);
     note_launch();
     return check_launch();
 }

@@ -22,15 +22,17 @@ constexpr long long kPeerWaitCycles = 4000000000LL;   // ~2 s at boost clock, th
 
 struct PeerGather {
     float *gather[KRK_CUDA_MAX_PEERS];   // each GPU's buffer: [2][n_peers][slot_stride] floats
-    int *flag[KRK_CUDA_MAX_PEERS];       // each GPU's flags: [n_peers] epochs + [1] step count
+    int *flag[KRK_CUDA_MAX_PEERS];       // each GPU's flags: [n_peers] epochs + [1] step count + [1] count of CTAs done
     int n_peers, my_rank;
     long long slot_stride;
 };
 
 __global__ void __launch_bounds__(256)
-allgather_sum_kernel(PeerGather pg, const float4 *__restrict__ part, float4 *__restrict__ out, long long n4,
-                     unsigned *done_counter, int *status) {
+allgather_sum_kernel(PeerGather pg, const float4 *__restrict__ part, float4 *__restrict__ out, long long n4, int *status) {
     int *own = pg.flag[pg.my_rank];
+    // CTAs that have stored their share: one word per exchange object, behind its step count, so that two
+    // exchanges on one GPU (other streams, other layers) never mix their counts
+    unsigned *done_counter = reinterpret_cast<unsigned *>(own + pg.n_peers + 1);
     // every CTA reads the count before it reports below; the last reporter is the only writer
     const int epoch = *reinterpret_cast<volatile int *>(own + pg.n_peers) + 1;
     const size_t half = (size_t)(epoch & 1) * pg.n_peers * pg.slot_stride;
@@ -86,14 +88,6 @@ int launch_allgather_sum(float *const gather[], int *const flag[], int n_peers, 
     if (n == 0) return KRK_CUDA_OK;
     int *status = device_status_word();
     if (!status) return KRK_CUDA_EDEVICE;
-    static unsigned *counter_of[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) return KRK_CUDA_EDEVICE;
-    if (!counter_of[dev]) {
-        if (cudaMalloc(&counter_of[dev], sizeof(unsigned)) != cudaSuccess) return KRK_CUDA_EDEVICE;
-        cudaMemset(counter_of[dev], 0, sizeof(unsigned));
-    }
     PeerGather pg;
     for (int q = 0; q < n_peers; q++) {
         pg.gather[q] = gather[q];
@@ -108,7 +102,7 @@ int launch_allgather_sum(float *const gather[], int *const flag[], int n_peers, 
     const int64_t want = (n4 + 255) / 256;
     const int grid = (int)(want < (int64_t)sm_count() ? want : (int64_t)sm_count());
     allgather_sum_kernel<<<grid, 256, 0, st>>>(pg, reinterpret_cast<const float4 *>(part), reinterpret_cast<float4 *>(out), n4,
-                                               counter_of[dev], status);
+                                               status);
     note_launch();
     return check_launch();
 }

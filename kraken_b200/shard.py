@@ -137,7 +137,7 @@ class PeerSum:
         self.capi = capi
         world = dist.get_world_size(group)
         self.slot = (n_max + 3) // 4 * 4
-        self.bufs = _PeerBuffers(capi, [2 * world * self.slot * 4, 4 * (world + 1)], group)
+        self.bufs = _PeerBuffers(capi, [2 * world * self.slot * 4, 4 * (world + 2)], group)
         self.rank = self.bufs.rank
         self._out = None
 
@@ -172,10 +172,10 @@ class PeerHead:
         self.begin, self.count = row_range(n_out, self.world, self.rank, align)
         # two logits buffers and one flag word per peer (+ the device-side step count), in memory the
         # other processes map
-        out_bytes, flag_bytes = rows * n_out * 4, 4 * (self.world + 1)
+        out_bytes, flag_bytes = rows * n_out * 4, 4 * (self.world + 2)
         self._bufs = _PeerBuffers(capi, [out_bytes, out_bytes, flag_bytes], group)
         self.out = [self._bufs.own[b].tensor((rows, n_out), torch.float32) for b in range(2)]
-        self.flags = self._bufs.own[2].tensor((self.world + 1,), torch.int32)
+        self.flags = self._bufs.own[2].tensor((self.world + 2,), torch.int32)
         self.peer_out = [self._bufs.ptrs[0], self._bufs.ptrs[1]]
         self.peer_flags = self._bufs.ptrs[2]
         self.epoch = 0

@@ -25,7 +25,14 @@ _i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
 def build(with_ref: bool = True) -> None:
     """Compile the restatement and, if the reference tree is mounted, oracle/_ref."""
     targets = ["all"] + (["ref"] if with_ref else [])
-    subprocess.run(["make", "-C", _HERE] + targets, check=True, stdout=subprocess.DEVNULL)
+    env = dict(os.environ)
+    if "KRK_REF" not in env:
+        # a Kraken tree checked out beside this repository as `reference`; elsewhere set KRK_REF (without
+        # either, `make ref` keeps whatever prebuilt oracle/_ref travelled with the tree)
+        cand = os.path.join(os.path.dirname(os.path.dirname(_HERE.rstrip(os.sep))), "reference")
+        if os.path.isdir(os.path.join(cand, "src")):
+            env["KRK_REF"] = cand
+    subprocess.run(["make", "-C", _HERE] + targets, check=True, stdout=subprocess.DEVNULL, env=env)
 
 
 def _c(a, dtype):

@@ -14,7 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def declared_symbols():
     text = open(os.path.join(ROOT, "include", "krk_cuda.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(krk_cuda_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(krk_(?:cuda|gguf)_\w+)\s*\(", text)))
 
 
 def test_every_declared_symbol_is_exported_and_bound():

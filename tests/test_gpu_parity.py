@@ -426,3 +426,28 @@ def test_decode_layer_matmuls_through_backend(cuda, oracle):
     for p in list(d.values()) + [d_q, d_k, d_v, d_h, d_u]:
         be.release(p)
     be.close()
+
+
+@pytest.mark.parametrize("wt,n_in", [(synth.Q8_0, 96), (synth.Q8_0, 4128), (synth.Q4_0, 160), (synth.Q5_0, 96)])
+@pytest.mark.parametrize("rows", [9, 40])
+def test_backend_gemm_fallback_rung_k_not_multiple_of_256(cuda, oracle, wt, n_in, rows):
+    """More than eight activation rows with a K that is whole 32-value blocks but not a multiple of 256 (legal
+    for the 32-value formats): Backend::gemm_k_ok says yes (include/krk/backend.hpp:862-869), so gemm() must
+    compute it (the place of the reference's fallback GEMM, src/hip/kernels/gemm.hpp:1013-1134), not abort."""
+    be = cuda.Backend(0)
+    n_out = 77
+    assert be.gemm_k_ok(wt, n_in)
+    w = synth.weights(wt, n_out, n_in, SEED + 21, stream=wt)
+    x = synth.activations(rows, n_in, SEED + 21)
+    d_w, d_x, d_y = be.alloc(w.nbytes), be.alloc(x.nbytes), be.alloc(rows * n_out * 4)
+    be.upload(d_w, w.ctypes.data, w.nbytes)
+    be.upload(d_x, x.ctypes.data, x.nbytes)
+    be.gemm(d_y, d_x, d_w, wt, n_out, n_in, rows)
+    y = np.empty((rows, n_out), np.float32)
+    be.download(y.ctypes.data, d_y, y.nbytes)
+    ref = oracle.gemm(x, w, wt, n_out, n_in, rows=rows, threads=4)
+    ok, worst = bound_ok(y, ref, oracle.dequant_rows(w, wt, n_out, n_in), x, GEMV_TOL)
+    assert ok, worst
+    for p in (d_w, d_x, d_y):
+        be.release(p)
+    be.close()
