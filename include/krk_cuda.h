@@ -37,6 +37,12 @@ extern "C" {
 #define KRK_CUDA_Q5_0 6
 #define KRK_CUDA_Q5_1 7
 #define KRK_CUDA_Q5_K 13
+/* and the low-bit formats of Q2_K / Q3_K_M / IQ4_NL files (src/quant.cpp:398-424, 514-553, 566-575): bit-exact
+ * decode, shape-agnostic GEMV, embedding gather; IQ4_NL also on the prefill GEMM, Q2_K / Q3_K prefill through
+ * the row-batch rung */
+#define KRK_CUDA_Q2_K 10
+#define KRK_CUDA_Q3_K 11
+#define KRK_CUDA_IQ4_NL 20
 
 /* Activation types accepted by krk_cuda_gemm. */
 #define KRK_CUDA_X_F32 0
@@ -63,7 +69,7 @@ const char *krk_cuda_strerror(int rc);
 /* Text of the last CUDA runtime error seen by this library on this thread ("" if none). */
 const char *krk_cuda_last_cuda_error(void);
 
-/* 1 if `wt` is one of the formats above (Q8_0, Q4_0, Q4_K, Q6_K, Q5_0, Q5_1, Q5_K). Replaces
+/* 1 if `wt` is one of the formats above (Q8_0, Q4_0, Q4_K, Q6_K, Q5_0, Q5_1, Q5_K, Q2_K, Q3_K, IQ4_NL). Replaces
  * krk::dtype_supported for this path
  * (include/krk/quant.hpp:180-186). */
 int krk_cuda_dtype_ok(int wt);

@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libkrk_cuda.so")
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
 Q5_0, Q5_1, Q5_K = 6, 7, 13
+Q2_K, Q3_K, IQ4_NL = 10, 11, 20
 X_F32, X_F16 = 0, 1
 MAX_GROUP, MAX_ROWS = 16, 8
 

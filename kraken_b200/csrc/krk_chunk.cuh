@@ -71,6 +71,9 @@ __device__ __forceinline__ void decode_chunk<KRK_CUDA_Q6_K>(const uint8_t *row, 
 KRK_CHUNK_BY_ELEMENT(KRK_CUDA_Q5_0)
 KRK_CHUNK_BY_ELEMENT(KRK_CUDA_Q5_1)
 KRK_CHUNK_BY_ELEMENT(KRK_CUDA_Q5_K)
+KRK_CHUNK_BY_ELEMENT(KRK_CUDA_Q2_K)
+KRK_CHUNK_BY_ELEMENT(KRK_CUDA_Q3_K)
+KRK_CHUNK_BY_ELEMENT(KRK_CUDA_IQ4_NL)
 #undef KRK_CHUNK_BY_ELEMENT
 
 // Dot of chunk c of a weight row with the matching 32 activations (x 16-byte aligned).

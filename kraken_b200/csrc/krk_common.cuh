@@ -36,13 +36,14 @@ __device__ __forceinline__ float exp_as_host(float x) { return (float)exp((doubl
 // ---- geometry (src/quant.cpp:1805-1900) ----------------------------------------------
 
 __host__ __device__ constexpr int block_size(int wt) {
-    return (wt == KRK_CUDA_Q8_0 || wt == KRK_CUDA_Q4_0 || wt == KRK_CUDA_Q5_0 || wt == KRK_CUDA_Q5_1) ? 32
-           : (wt == KRK_CUDA_Q4_K || wt == KRK_CUDA_Q6_K || wt == KRK_CUDA_Q5_K) ? 256 : 0;
+    return (wt == KRK_CUDA_Q8_0 || wt == KRK_CUDA_Q4_0 || wt == KRK_CUDA_Q5_0 || wt == KRK_CUDA_Q5_1 || wt == KRK_CUDA_IQ4_NL) ? 32
+           : (wt == KRK_CUDA_Q4_K || wt == KRK_CUDA_Q6_K || wt == KRK_CUDA_Q5_K || wt == KRK_CUDA_Q2_K || wt == KRK_CUDA_Q3_K) ? 256 : 0;
 }
 __host__ __device__ constexpr int block_bytes(int wt) {
     return wt == KRK_CUDA_Q8_0 ? 34 : wt == KRK_CUDA_Q4_0 ? 18 : wt == KRK_CUDA_Q4_K ? 144
            : wt == KRK_CUDA_Q6_K ? 210 : wt == KRK_CUDA_Q5_0 ? 22 : wt == KRK_CUDA_Q5_1 ? 24
-           : wt == KRK_CUDA_Q5_K ? 176 : 0;
+           : wt == KRK_CUDA_Q5_K ? 176 : wt == KRK_CUDA_Q2_K ? 84 : wt == KRK_CUDA_Q3_K ? 110
+           : wt == KRK_CUDA_IQ4_NL ? 18 : 0;
 }
 __host__ __device__ inline size_t row_bytes(int wt, int64_t n_in) {
     const int bs = block_size(wt);
@@ -152,6 +153,44 @@ __device__ __forceinline__ float decode_value<KRK_CUDA_Q5_K>(const uint8_t *row,
     return __fsub_rn(__fmul_rn(dl, (float)q), ml);
 }
 
+// src/quant.cpp:398-424: 16 scale bytes (scale low nibble, min high nibble), 64 bytes of 2-bit quants, d, dmin
+template <>
+__device__ __forceinline__ float decode_value<KRK_CUDA_Q2_K>(const uint8_t *row, int64_t k) {
+    const uint8_t *b = row + (k >> 8) * 84;
+    const int e = (int)(k & 255), g = e >> 7, r = e & 127, j = r >> 5, l = r & 31;
+    const uint8_t sc = b[8 * g + 2 * j + (l >> 4)];
+    const int q = (b[16 + 32 * g + l] >> (2 * j)) & 3;
+    const float dl = __fmul_rn(half_bits_to_float(b + 80), (float)(sc & 0xF));
+    const float ml = __fmul_rn(half_bits_to_float(b + 82), (float)(sc >> 4));
+    return __fsub_rn(__fmul_rn(dl, (float)q), ml);
+}
+
+// src/quant.cpp:514-553: 32 mask bytes, 64 bytes of 2-bit quants, sixteen 6-bit scales in 12 bytes, d
+template <>
+__device__ __forceinline__ float decode_value<KRK_CUDA_Q3_K>(const uint8_t *row, int64_t k) {
+    const uint8_t *b = row + (k >> 8) * 110;
+    const int e = (int)(k & 255), nn = e >> 7, r = e & 127, j = r >> 5, l = r & 31;
+    const int is = 8 * nn + 2 * j + (l >> 4);
+    const uint8_t *sr = b + 96;
+    const int lo = is < 8 ? (sr[is] & 0xF) : (sr[is - 8] >> 4);
+    const int hi = (sr[8 + (is & 3)] >> (2 * (is >> 2))) & 3;
+    const int scale = (lo | (hi << 4)) - 32;
+    const int q = (int)((b[32 + 32 * nn + l] >> (2 * j)) & 3) - ((b[l] >> (4 * nn + j)) & 1 ? 0 : 4);
+    return __fmul_rn(__fmul_rn(half_bits_to_float(b + 108), (float)scale), (float)q);
+}
+
+// src/quant.cpp:88-91, 566-575: d and 16 bytes of indices into the format's non-linear grid
+template <>
+__device__ __forceinline__ float decode_value<KRK_CUDA_IQ4_NL>(const uint8_t *row, int64_t k) {
+    // the sixteen grid values, packed four to a word (signed bytes)
+    constexpr uint32_t grid[4] = {0xBFAD9881u, 0xF6EADDCFu, 0x26190D01u, 0x71594535u};
+    const uint8_t *b = row + (k >> 5) * 18;
+    const int j = (int)(k & 31);
+    const int idx = j < 16 ? (b[2 + j] & 0xF) : (b[2 + j - 16] >> 4);
+    const int v = (int)(int8_t)((grid[idx >> 2] >> (8 * (idx & 3))) & 0xFF);
+    return __fmul_rn(half_bits_to_float(b), (float)v);
+}
+
 // Runs the statement(s) with `WT` bound to the compile-time weight type matching `wt`
 // (kernels are specialised per format; there is no runtime type switch on the device).
 #define KRK_DISPATCH_WT(wt, ...)                                                        \
@@ -163,8 +202,27 @@ __device__ __forceinline__ float decode_value<KRK_CUDA_Q5_K>(const uint8_t *row,
     case KRK_CUDA_Q5_0: { constexpr int WT = KRK_CUDA_Q5_0; __VA_ARGS__; } break;       \
     case KRK_CUDA_Q5_1: { constexpr int WT = KRK_CUDA_Q5_1; __VA_ARGS__; } break;       \
     case KRK_CUDA_Q5_K: { constexpr int WT = KRK_CUDA_Q5_K; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q2_K: { constexpr int WT = KRK_CUDA_Q2_K; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q3_K: { constexpr int WT = KRK_CUDA_Q3_K; __VA_ARGS__; } break;       \
+    case KRK_CUDA_IQ4_NL: { constexpr int WT = KRK_CUDA_IQ4_NL; __VA_ARGS__; } break;   \
     default: break;                                                                     \
     }
+
+// The formats the tensor-core GEMM stages: every one whose 256-value segment is a whole number of 8-byte
+// granules (Q2_K's 84 and Q3_K's 110 bytes are not: those take the row-batch rung).
+#define KRK_DISPATCH_WT_GEMM(wt, ...)                                                   \
+    switch (wt) {                                                                       \
+    case KRK_CUDA_Q8_0: { constexpr int WT = KRK_CUDA_Q8_0; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q4_0: { constexpr int WT = KRK_CUDA_Q4_0; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q4_K: { constexpr int WT = KRK_CUDA_Q4_K; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q6_K: { constexpr int WT = KRK_CUDA_Q6_K; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q5_0: { constexpr int WT = KRK_CUDA_Q5_0; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q5_1: { constexpr int WT = KRK_CUDA_Q5_1; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q5_K: { constexpr int WT = KRK_CUDA_Q5_K; __VA_ARGS__; } break;       \
+    case KRK_CUDA_IQ4_NL: { constexpr int WT = KRK_CUDA_IQ4_NL; __VA_ARGS__; } break;   \
+    default: break;                                                                     \
+    }
+__host__ __device__ constexpr bool gemm_tc_takes(int wt) { return wt != KRK_CUDA_Q2_K && wt != KRK_CUDA_Q3_K; }
 
 // ---- kernel-family entry points (one .cu file each) -------------------------------------
 

@@ -78,7 +78,7 @@ extern "C" {
 const char *krk_cuda_strerror(int rc) {
     switch (rc) {
     case KRK_CUDA_OK: return "ok";
-    case KRK_CUDA_EDTYPE: return "unsupported weight type (want Q8_0, Q4_0, Q4_K, Q6_K, Q5_0, Q5_1 or Q5_K)";
+    case KRK_CUDA_EDTYPE: return "unsupported weight type (want Q8_0, Q4_0, Q4_K, Q6_K, Q5_0, Q5_1, Q5_K, Q2_K, Q3_K or IQ4_NL)";
     case KRK_CUDA_ESHAPE: return "shape not addressable (n_in must be a positive whole number of blocks; sizes non-negative; rows in range)";
     case KRK_CUDA_ENULL: return "null pointer";
     case KRK_CUDA_EALIGN: return "misaligned pointer (weights and x 16 bytes, y 4 bytes)";
@@ -172,9 +172,10 @@ int krk_cuda_gemm(void *y_f32, const void *x, int x_dtype, const void *w, int wt
     if (x_dtype != KRK_CUDA_X_F32 && x_dtype != KRK_CUDA_X_F16) return KRK_CUDA_EARG;
     const int rc = check_matmul_args(y_f32, x, w, wt, n_out, n_in, rows);
     if (rc != KRK_CUDA_OK) return rc;
-    if (n_in % 256 != 0) {
+    if (n_in % 256 != 0 || !gemm_tc_takes(wt)) {
         // The fallback rung (the place of gemm_simt_kernel, src/hip/kernels/gemm.hpp:1013-1134): 32-value
-        // block formats whose K is a whole number of blocks but not of 256. Correct, not fast: the
+        // block formats whose K is a whole number of blocks but not of 256, and the formats whose blocks the
+        // tensor-core kernel does not stage (Q2_K, Q3_K). Correct, not fast: the
         // shape-agnostic GEMV over batches of KRK_CUDA_MAX_ROWS activation rows. f32 activations only.
         if (x_dtype != KRK_CUDA_X_F32) return KRK_CUDA_ESHAPE;
         if (n_out == 0 || rows == 0) return KRK_CUDA_OK;

@@ -1083,7 +1083,7 @@ int launch_gemm_tc(float *y, const void *x, int x_dtype, const uint8_t *w, int w
     if (cr != CUDA_SUCCESS) return KRK_CUDA_ELAUNCH;
 
     int rc = KRK_CUDA_EDTYPE;
-    KRK_DISPATCH_WT(wt, rc = launch_wt<WT>(p, map, g.grid, st));
+    KRK_DISPATCH_WT_GEMM(wt, rc = launch_wt<WT>(p, map, g.grid, st));
     return rc;
 }
 
@@ -1106,7 +1106,7 @@ using namespace krk_cuda;
 
 extern "C" int krk_cuda_gemm_f32_static(void *y_f32, const void *x_f32, const void *w, int wt, int64_t n_out, int64_t n_in,
                                         int64_t rows, void *stream) {
-    if (!krk_cuda_dtype_ok(wt)) return KRK_CUDA_EDTYPE;
+    if (!krk_cuda_dtype_ok(wt) || !gemm_tc_takes(wt)) return KRK_CUDA_EDTYPE;
     if (n_out < 0 || rows < 0 || !krk_cuda_gemm_k_ok(wt, n_in) || n_in % 256 != 0) return KRK_CUDA_ESHAPE;
     if (rows > (1 << 24) || n_out > (1 << 30) || n_in > (1 << 24)) return KRK_CUDA_ESHAPE;
     if (n_out == 0 || rows == 0) return KRK_CUDA_OK;
@@ -1188,7 +1188,7 @@ extern "C" int krk_cuda_gemm_f32_static(void *y_f32, const void *x_f32, const vo
     const int tiles = p.n_tiles_n * p.n_tiles_m;
     const int grid = tiles < sms ? tiles : sms;
     rc = KRK_CUDA_EDTYPE;
-    KRK_DISPATCH_WT(wt, rc = launch_wt<WT>(p, map, grid, st));
+    KRK_DISPATCH_WT_GEMM(wt, rc = launch_wt<WT>(p, map, grid, st));
     return rc;
 }
 

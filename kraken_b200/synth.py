@@ -22,13 +22,15 @@ import numpy as np
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
 Q5_0, Q5_1, Q5_K = 6, 7, 13          # the further formats of mixed files (shape-agnostic kernels only)
+Q2_K, Q3_K, IQ4_NL = 10, 11, 20
 FORMATS = (Q8_0, Q4_0, Q4_K, Q6_K)
-MORE_FORMATS = (Q5_0, Q5_1, Q5_K)
-NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K", Q5_0: "Q5_0", Q5_1: "Q5_1", Q5_K: "Q5_K"}
-BLOCK_SIZE = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256, Q5_0: 32, Q5_1: 32, Q5_K: 256}
-BLOCK_BYTES = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210, Q5_0: 22, Q5_1: 24, Q5_K: 176}
+MORE_FORMATS = (Q5_0, Q5_1, Q5_K, Q2_K, Q3_K, IQ4_NL)
+NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K", Q5_0: "Q5_0", Q5_1: "Q5_1", Q5_K: "Q5_K",
+         Q2_K: "Q2_K", Q3_K: "Q3_K", IQ4_NL: "IQ4_NL"}
+BLOCK_SIZE = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256, Q5_0: 32, Q5_1: 32, Q5_K: 256, Q2_K: 256, Q3_K: 256, IQ4_NL: 32}
+BLOCK_BYTES = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210, Q5_0: 22, Q5_1: 24, Q5_K: 176, Q2_K: 84, Q3_K: 110, IQ4_NL: 18}
 # 64-bit words of randomness drawn per block
-_WORDS = {Q4_0: 3, Q8_0: 9, Q4_K: 19, Q6_K: 27, Q5_0: 4, Q5_1: 4, Q5_K: 23}
+_WORDS = {Q4_0: 3, Q8_0: 9, Q4_K: 19, Q6_K: 27, Q5_0: 4, Q5_1: 4, Q5_K: 23, Q2_K: 11, Q3_K: 15, IQ4_NL: 3}
 
 _GOLDEN = np.uint64(0x9E3779B97F4A7C15)
 _M1 = np.uint64(0xBF58476D1CE4E5B9)
@@ -149,6 +151,16 @@ def weights(wt: int, n_rows: int, n_in: int, seed: int, stream: int = 0, row_beg
             six = by[..., 160:176] & 63
             blocks[..., 4:16] = pack_scales_k4(six[..., 0:8], six[..., 8:16])
         blocks[..., 16:176] = by[..., 0:160]
+    elif wt == Q2_K:      # 16 scale/min bytes, 64 bytes of 2-bit quants, d, dmin: every payload byte uniform
+        blocks[..., 0:80] = by[..., 0:80]
+        _put_u16(blocks, 80, _f16_bits(1e-3, 1e-2, u_lo))
+        _put_u16(blocks, 82, _f16_bits(0.0, 5e-3, u_hi))
+    elif wt == Q3_K:      # 32 mask bytes, 64 bytes of 2-bit quants, 12 packed 6-bit scale bytes, d
+        blocks[..., 0:108] = by[..., 0:108]
+        _put_u16(blocks, 108, _f16_bits(1e-3, 1e-2, u_lo))
+    elif wt == IQ4_NL:    # d and 16 bytes of grid indices
+        _put_u16(blocks, 0, _f16_bits(1e-4, 2e-3, u_lo))
+        blocks[..., 2:18] = by[..., 0:16]
     else:
         raise ValueError(f"unsupported weight type {wt}")
     return blocks.reshape(n_rows, nblk * BLOCK_BYTES[wt])

@@ -24,7 +24,10 @@ int krk_oracle_block_size(int wt) {
     case KRK_ORACLE_Q4_0:
     case KRK_ORACLE_Q5_0:
     case KRK_ORACLE_Q5_1:
+    case KRK_ORACLE_IQ4_NL:
     case KRK_ORACLE_Q8_0: return 32;
+    case KRK_ORACLE_Q2_K:
+    case KRK_ORACLE_Q3_K:
     case KRK_ORACLE_Q4_K:
     case KRK_ORACLE_Q5_K:
     case KRK_ORACLE_Q6_K: return 256;
@@ -41,6 +44,9 @@ int krk_oracle_block_bytes(int wt) {
     case KRK_ORACLE_Q5_0: return 22;
     case KRK_ORACLE_Q5_1: return 24;
     case KRK_ORACLE_Q5_K: return 176;
+    case KRK_ORACLE_Q2_K: return 84;
+    case KRK_ORACLE_Q3_K: return 110;
+    case KRK_ORACLE_IQ4_NL: return 18;
     default: return 0;
     }
 }
@@ -195,6 +201,63 @@ static void block_q5_k(const uint8_t *b, float *y) {
     }
 }
 
+/* src/quant.cpp:398-424: 84 bytes = 16 scale bytes (scale in the low nibble, min in the high one), 64 bytes of
+ * 2-bit quants, f16 d, f16 dmin. Two 128-value halves; in a half, bit pair j of the 32 quant bytes gives 32
+ * values, the first 16 and the last 16 with a scale byte each: y = (d * sc) * q - dmin * m. */
+static void block_q2_k(const uint8_t *b, float *y) {
+    const float d = half_at(b + 80), dmin = half_at(b + 82);
+    int is = 0;
+    for (int g = 0; g < 2; g++) {
+        const uint8_t *q = b + 16 + 32 * g;
+        for (int j = 0; j < 4; j++) {
+            for (int h = 0; h < 2; h++) {
+                const uint8_t sc = b[is++];
+                const float dl = d * (float)(sc & 0xF), ml = dmin * (float)(sc >> 4);
+                for (int l = 0; l < 16; l++) y[l + 16 * h] = dl * (float)((q[l + 16 * h] >> (2 * j)) & 3) - ml;
+            }
+            y += 32;
+        }
+    }
+}
+
+/* src/quant.cpp:514-553: 110 bytes = 32 bytes of high-bit masks, 64 bytes of 2-bit quants, 12 bytes holding
+ * sixteen 6-bit scales (low 4 bits in the first 8 bytes' nibbles, high 2 bits in the last 4 bytes), f16 d.
+ * q = 2 low bits, minus 4 when the mask bit is clear; y = (d * (scale - 32)) * q. */
+static void block_q3_k(const uint8_t *b, float *y) {
+    const float d_all = half_at(b + 108);
+    const uint8_t *hm = b, *q = b + 32, *sr = b + 96;
+    int scales[16];
+    for (int j = 0; j < 16; j++) {
+        const int lo = j < 8 ? (sr[j] & 0xF) : (sr[j - 8] >> 4);
+        const int hi = (sr[8 + (j & 3)] >> (2 * (j >> 2))) & 3;
+        scales[j] = (lo | (hi << 4)) - 32;
+    }
+    int is = 0;
+    uint8_t m = 1;
+    for (int nn = 0; nn < 2; nn++, q += 32) {
+        for (int j = 0; j < 4; j++, m = (uint8_t)(m << 1)) {
+            for (int h = 0; h < 2; h++) {
+                const float dl = d_all * (float)scales[is++];
+                for (int l = 0; l < 16; l++) {
+                    const int v = (int)((q[l + 16 * h] >> (2 * j)) & 3) - ((hm[l + 16 * h] & m) ? 0 : 4);
+                    *y++ = dl * (float)v;
+                }
+            }
+        }
+    }
+}
+
+/* src/quant.cpp:88-91, 566-575: f16 d and 16 bytes of nibbles indexing the format's 16-entry non-linear grid;
+ * low nibbles are values 0..15, high nibbles 16..31. */
+static const int8_t k_iq4nl_grid[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+static void block_iq4_nl(const uint8_t *b, float *y) {
+    const float d = half_at(b);
+    for (int k = 0; k < 16; k++) {
+        y[k] = d * (float)k_iq4nl_grid[b[2 + k] & 0xF];
+        y[k + 16] = d * (float)k_iq4nl_grid[b[2 + k] >> 4];
+    }
+}
+
 /* src/quant.cpp:1553-1599 */
 static void decode_block(int wt, const uint8_t *b, float *y) {
     switch (wt) {
@@ -205,6 +268,9 @@ static void decode_block(int wt, const uint8_t *b, float *y) {
     case KRK_ORACLE_Q5_0: block_q5_0(b, y); break;
     case KRK_ORACLE_Q5_1: block_q5_1(b, y); break;
     case KRK_ORACLE_Q5_K: block_q5_k(b, y); break;
+    case KRK_ORACLE_Q2_K: block_q2_k(b, y); break;
+    case KRK_ORACLE_Q3_K: block_q3_k(b, y); break;
+    case KRK_ORACLE_IQ4_NL: block_iq4_nl(b, y); break;
     default: break;
     }
 }

@@ -30,6 +30,9 @@ enum {
     KRK_ORACLE_Q8_0 = 8,
     KRK_ORACLE_Q4_K = 12,
     KRK_ORACLE_Q6_K = 14,
+    KRK_ORACLE_Q2_K = 10,
+    KRK_ORACLE_Q3_K = 11,
+    KRK_ORACLE_IQ4_NL = 20,
     KRK_ORACLE_Q5_0 = 6,
     KRK_ORACLE_Q5_1 = 7,
     KRK_ORACLE_Q5_K = 13
