@@ -210,6 +210,8 @@ def check_step(torch, layers, base, grouped):
     for li in sorted({0, len(layers) - 1}):
         for mi, (w_np, _, n_out, n_in) in enumerate(base):
             _, x, y, _, _ = layers[li][mi]
+            if grouped and mi == 2:
+                x = layers[li][1][1]          # gate and up leave in one launch on the gate's activation row
             x_np = x.cpu().numpy().reshape(1, -1)
             ref = orc.gemm(x_np, w_np, WT, n_out, n_in, threads=os.cpu_count() or 1)[0]
             wd = orc.dequant_rows(w_np, WT, n_out, n_in).astype(np.float64)
@@ -527,7 +529,23 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
     ms_full = reduce_max(timed(torch, head_call, 60, barrier, variants=n_rep))
     ms_local = reduce_max(timed(torch, head_local, 60, barrier, variants=n_rep))
     ms_full_host = reduce_max(timed(torch, head_call, 60, barrier))
-    ms_peer = ms_peer_host = None
+    ms_peer = ms_peer_host = ms_c_nccl = ms_c_gather = None
+    if world > 1 and count * world == n_out:
+        # the same through the C ABI: GEMV into its slot of a persistent row + in-place ncclAllGather
+        # (krk_cuda_shard_allgather), and the collective alone, so that the limiter is a number
+        c_head = shard.NcclHead(n_out, n_in, synth.Q6_K, ws[0], align=8)
+
+        def c_head_call(i):
+            c_head.w_local = ws[i % n_rep]
+            return c_head.forward(x)
+        ms_c_nccl = reduce_max(timed(torch, c_head_call, 60, barrier, variants=n_rep))
+        ms_c_gather = reduce_max(timed(torch, lambda i: c_head.gather_only(), 60, barrier, variants=1))
+        c_head.w_local = state["w"] = ws[0]
+        row_c = c_head.forward(x).clone()
+        row_t = head.forward(x).clone()
+        torch.cuda.synchronize()
+        parity["head_c_nccl"] = bool(torch.equal(row_c, row_t))
+        c_head.close()
     if world > 1:
         # the fused form: the GEMV's epilogue stores into every GPU's logits row and its last CTA waits
         # (bounded) for the peers' slices. An even number of captured steps keeps the two output buffers
@@ -555,6 +573,8 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
     out["head_q6_k_128256x4096"] = {
         "ms_per_token": round(ms_full, 5), "ms_gemv_only": round(ms_local, 5), "ms_per_token_host_launched": round(ms_full_host, 5),
         "launch": "CUDA graph replay (GEMV + NCCL all-gather)",
+        "ms_per_token_c_abi_nccl_in_place": None if ms_c_nccl is None else round(ms_c_nccl, 5),
+        "ms_nccl_all_gather_alone": None if ms_c_gather is None else round(ms_c_gather, 5),
         "ms_per_token_peer_store_fused": None if ms_peer is None else round(ms_peer, 5),
         "ms_per_token_peer_store_fused_host_launched": None if ms_peer_host is None else round(ms_peer_host, 5),
         "weight_gbps_peer_store_fused": None if ms_peer is None else round(n_out * synth.row_bytes(synth.Q6_K, n_in) / (ms_peer * 1e-3) / 1e9, 1),

@@ -188,8 +188,13 @@ struct krk_cuda_expert_bank {
  * ascending expert id, of wts * Wdown_e . (silu(Wgate_e x_t) * (Wup_e x_t)); picks held
  * elsewhere contribute nothing (a shard's partial sum). Replaces the per-expert loop /
  * moe_decode_batch / Backend::moe_dispatch (src/engine.cpp:12353-, 10896-11060;
- * include/krk/backend.hpp:1001-1009). ids/wts come from krk_cuda_route. n_tok in 1..8.
- * workspace: krk_cuda_moe_workspace_bytes() bytes of device memory. */
+ * include/krk/backend.hpp:1001-1009). ids/wts come from krk_cuda_route.
+ * n_tok 1..8 (decode): the streaming GEMV over device-side matrix tables, ids never leave the device.
+ * n_tok > 8 (prefill): expert-major, the reference's grouped form (src/engine.cpp:12353-12690; device twin
+ * src/hip/kernels/moe_table.hpp:463-534): the plan is built on the device, its per-expert row counts are read
+ * back once (this call synchronises the stream once), then per expert gather_rows -> gate / up / down as
+ * tensor-core GEMMs (GEMVs for up to 8 rows) -> silu_mul -> scatter_axpy_rows in ascending expert id.
+ * workspace: krk_cuda_moe_workspace_bytes() bytes of device memory, 256-byte aligned. */
 size_t krk_cuda_moe_workspace_bytes(const struct krk_cuda_expert_bank *bank, int k, int64_t n_tok);
 int krk_cuda_moe_ffn(void *y_f32, const void *x_f32, const void *ids_i32, const void *wts_f32,
                      const struct krk_cuda_expert_bank *bank, int k, int64_t n_tok,

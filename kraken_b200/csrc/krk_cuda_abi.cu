@@ -260,11 +260,11 @@ int krk_cuda_moe_ffn(void *y_f32, const void *x_f32, const void *ids_i32, const 
     const int rc = check_bank(bank);
     if (rc != KRK_CUDA_OK) return rc;
     if (k <= 0 || k > 32) return KRK_CUDA_EARG;
-    if (n_tok < 0 || n_tok > KRK_CUDA_MAX_ROWS) return KRK_CUDA_ESHAPE;
+    if (n_tok < 0 || n_tok * k > (1 << 22)) return KRK_CUDA_ESHAPE;
     if (n_tok == 0) return KRK_CUDA_OK;
     if (!y_f32 || !x_f32 || !ids_i32 || !wts_f32) return KRK_CUDA_ENULL;
     if (!aligned(x_f32, 16) || !aligned(y_f32, 4)) return KRK_CUDA_EALIGN;
-    if (!workspace || ws_bytes < moe_workspace_bytes(bank, k, n_tok) || !aligned(workspace, 16))
+    if (!workspace || ws_bytes < moe_workspace_bytes(bank, k, n_tok) || !aligned(workspace, n_tok > KRK_CUDA_MAX_ROWS ? 128 : 16))
         return KRK_CUDA_EWORKSPACE;
     if (!device_state()) return KRK_CUDA_EDEVICE;
     return launch_moe_ffn_generic(static_cast<float *>(y_f32), static_cast<const float *>(x_f32),
@@ -279,11 +279,11 @@ int krk_cuda_moe_ffn_routed(void *y_f32, const void *x_f32, const void *router_l
     const int rc = check_bank(bank);
     if (rc != KRK_CUDA_OK) return rc;
     if (k <= 0 || k > 32 || n_expert <= 0 || n_expert > 1024 || k > n_expert) return KRK_CUDA_EARG;
-    if (n_tok < 0 || n_tok > KRK_CUDA_MAX_ROWS) return KRK_CUDA_ESHAPE;
+    if (n_tok < 0 || n_tok * k > (1 << 22)) return KRK_CUDA_ESHAPE;
     if (n_tok == 0) return KRK_CUDA_OK;
     if (!y_f32 || !x_f32 || !router_logits_f32 || !ids_i32 || !wts_f32) return KRK_CUDA_ENULL;
     if (!aligned(x_f32, 16) || !aligned(y_f32, 4)) return KRK_CUDA_EALIGN;
-    if (!workspace || ws_bytes < moe_workspace_bytes(bank, k, n_tok) || !aligned(workspace, 16))
+    if (!workspace || ws_bytes < moe_workspace_bytes(bank, k, n_tok) || !aligned(workspace, n_tok > KRK_CUDA_MAX_ROWS ? 128 : 16))
         return KRK_CUDA_EWORKSPACE;
     if (!device_state()) return KRK_CUDA_EDEVICE;
     return launch_moe_ffn_generic(static_cast<float *>(y_f32), static_cast<const float *>(x_f32),

@@ -875,8 +875,13 @@ gemm_tc_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
 }
 
 __global__ void __launch_bounds__(256) f32_to_f16_kernel(__half *__restrict__ out, const float *__restrict__ in, int64_t n) {
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
-        out[i] = __float2half_rn(in[i]);
+    // A finite activation beyond the f16 range saturates to +-65504 instead of becoming an infinity (which the
+    // f32 accumulation would turn into NaN on the first cancellation): the rule of the reference's f16
+    // activation stores (src/hip/krk_hip.hpp:141-202). Infinities and NaNs pass through unchanged.
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = in[i];
+        out[i] = __float2half_rn(fabsf(v) <= 3.4028234e38f ? fminf(fmaxf(v, -65504.0f), 65504.0f) : v);
+    }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,

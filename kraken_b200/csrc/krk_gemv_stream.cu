@@ -62,10 +62,13 @@ constexpr float kFixedOne = 8323072.0f;           // 127 * 65536: |X| <= this ke
 constexpr long long kWaitCycles = 4000000000LL;   // ~2 s at boost clock, then give up
 
 template <int WT> struct Fmt;
-// tma: a unit is a whole number of 16-byte granules, so a stage can arrive as one tiled tensor copy
-template <> struct Fmt<KRK_CUDA_Q4_K> { static constexpr int unit_values = 256, unit_bytes = 144, stride_mod = 32; static constexpr bool tma = true; };
-template <> struct Fmt<KRK_CUDA_Q6_K> { static constexpr int unit_values = 256, unit_bytes = 210, stride_mod = 16; static constexpr bool tma = false; };
-template <> struct Fmt<KRK_CUDA_Q8_0> { static constexpr int unit_values = 128, unit_bytes = 136, stride_mod = 16; static constexpr bool tma = false; };
+// tma: how a stage can arrive as ONE tiled tensor copy. 1: a unit is a whole number of 16-byte granules (Q4_K's
+// 144 bytes): box {unit bytes, rows, units}, laid out [unit][row][unit bytes]. 2: eight units of a row are (Q6_K:
+// 8 x 210 = 1680 bytes, as 210 64-bit elements): box {8 units, rows}, laid out [row][8 units], which is the
+// layout of the per-row copies with a 1680-byte pitch. 0: per-row bulk copies only.
+template <> struct Fmt<KRK_CUDA_Q4_K> { static constexpr int unit_values = 256, unit_bytes = 144, stride_mod = 32, tma = 1; };
+template <> struct Fmt<KRK_CUDA_Q6_K> { static constexpr int unit_values = 256, unit_bytes = 210, stride_mod = 16, tma = 2; };
+template <> struct Fmt<KRK_CUDA_Q8_0> { static constexpr int unit_values = 128, unit_bytes = 136, stride_mod = 16, tma = 0; };
 
 struct StreamParams {
     GemvMat mat[KRK_CUDA_MAX_GROUP];
@@ -84,8 +87,11 @@ struct StreamParams {
                           // sub-tile w / units)
     int row_stride;       // bytes between rows inside a stage
     int unit_stride;      // bytes between the K units of one row group inside a stage
-    int use_tma;          // 1: a stage arrives as one tiled tensor copy, laid out [unit][row][unit_bytes]
+    int use_tma;          // 1: a stage arrives as one tiled tensor copy, laid out [unit][row][unit_bytes]; 2: [row][units]
+    int tma_unit_div;     // the copy's third coordinate is the stage's first unit / this
     int box_bytes;        // bytes one tensor copy signals (the whole box, also where the matrix clips it)
+    int tune;             // experiment bits: 1 = weights are not prefetched before the dependency wait; 2 = the dependent
+                          // launch is released after this grid's own dependency wait instead of at its start
     int stage_bytes;
     int n_stages;
     int total_gran;
@@ -750,7 +756,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     // Programmatic dependent launch: the next kernel in the stream may become resident beside this one
     // (a CTA takes half an SM) as soon as every CTA here has passed this point; it prefetches weights
     // and waits for this grid to complete before touching activations or outputs.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!(p.tune & 2)) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     volatile int *gave_up = &sm->gave_up;
 
     if (warp == 0) {
@@ -773,7 +779,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         // the other warps wait here for the barriers (they arrive as they start); this warp does not wait
         asm volatile("bar.arrive 1, %0;" ::"r"(kThreads) : "memory");
         // A device-side table is the output of the kernel before this one: wait for that grid.
-        if (p.dev_table) asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (p.dev_table || (p.tune & 1)) asm volatile("griddepcontrol.wait;" ::: "memory");
         const TableView tv = table_view(p);
         walk(p, tv, tps, [](int) {}, [&](const StageInfo &s) {
             const int slot = s.slot;
@@ -786,7 +792,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                 // still signals its full size
                 if (lane == 0) {
                     mbar_arrive_expect_tx(full, (uint32_t)p.box_bytes);
-                    tma_box(smem_u32(dst), &p.wmap[s.mat], s.row0, s.unit0, full);
+                    tma_box(smem_u32(dst), &p.wmap[s.mat], s.row0, s.unit0 / p.tma_unit_div, full);
                 }
             } else if (!p.whole_tiles) {
                 const uint32_t bytes = (uint32_t)s.n_units * F::unit_bytes;
@@ -947,7 +953,10 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         if (tv.mat[m].x != prepared) {
             // x may be the output of the kernel before this one (and y its input): wait for that grid to
             // complete. Weights are never written by a kernel in flight, so the producer warp does not wait.
-            if (prepared == nullptr) asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (prepared == nullptr) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                if (p.tune & 2) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+            }
             prepared = tv.mat[m].x;
 #pragma unroll
             for (int r = 0; r < 2 * NG; r++)
@@ -1140,14 +1149,28 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
     p.tps = p.tps < 1 ? 1 : (p.tps > kMaxStack ? kMaxStack : p.tps);
     p.use_tma = 0;
     p.box_bytes = 0;
+    static const int tune = [] {
+        const char *e = std::getenv("KRK_CUDA_GEMV_TUNE");
+        return e ? std::atoi(e) : 0;
+    }();
+    p.tune = tune;
     p.unit_stride = F::unit_bytes;
-    if (want_tma && F::tma && !p.whole_tiles) {
+    p.tma_unit_div = 1;
+    if (want_tma && F::tma == 1 && !p.whole_tiles) {
         // a stage is one tensor copy: [units of the stage][rows of the stage][unit_bytes]. The 144-byte
         // pitch of a Q4_K unit puts the eight rows of a fragment load 16 bytes apart in the banks.
         p.use_tma = 1;
         p.row_stride = F::unit_bytes;
         p.unit_stride = kTileRows * p.tps * F::unit_bytes;
         p.box_bytes = ku_max * p.unit_stride;
+        p.stage_bytes = align_up(p.box_bytes, 128);
+    } else if (want_tma && F::tma == 2 && !p.whole_tiles && ku_max == kConsumerWarps && p.units % kConsumerWarps == 0) {
+        // a stage is one tensor copy of eight units of each row: [row][8 units], pitch 8 * unit_bytes (1680 for
+        // Q6_K: the rows of a fragment load again lie 16 bytes apart in the banks)
+        p.use_tma = 2;
+        p.tma_unit_div = kConsumerWarps;
+        p.row_stride = ku_max * F::unit_bytes;
+        p.box_bytes = kTileRows * p.tps * p.row_stride;
         p.stage_bytes = align_up(p.box_bytes, 128);
     } else if (p.whole_tiles) {
         p.row_stride = p.row_bytes;
@@ -1219,7 +1242,8 @@ struct MapKeyHash {
         return h;
     }
 };
-bool weight_map(CUtensorMap *out, const uint8_t *w, int64_t n_out, int row_bytes, int unit_bytes, int box_rows, int box_units) {
+bool weight_map(CUtensorMap *out, const uint8_t *w, int64_t n_out, int row_bytes, int unit_bytes, int box_rows, int box_units,
+                int mode) {
     static EncodeTiledFn encode = [] {
         void *ptr = nullptr;
         cudaDriverEntryPointQueryResult q;
@@ -1231,19 +1255,24 @@ bool weight_map(CUtensorMap *out, const uint8_t *w, int64_t n_out, int row_bytes
     if (!encode) return false;
     static std::mutex mu;
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    const MapKey key{w, n_out, row_bytes, unit_bytes, box_rows, box_units};
+    const MapKey key{w, n_out, row_bytes, unit_bytes, box_rows, mode == 2 ? -box_units : box_units};
     std::lock_guard<std::mutex> lk(mu);
     auto it = cache.find(key);
     if (it != cache.end()) {
         *out = it->second;
         return true;
     }
-    const cuuint64_t dims[3] = {(cuuint64_t)unit_bytes, (cuuint64_t)n_out, (cuuint64_t)(row_bytes / unit_bytes)};
-    const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, (cuuint64_t)unit_bytes};
-    const cuuint32_t box[3] = {(cuuint32_t)unit_bytes, (cuuint32_t)box_rows, (cuuint32_t)box_units};
+    // mode 1: {unit bytes, rows, units of a row} in bytes; mode 2: {box_units units as 64-bit elements, rows, groups of
+    // box_units units of a row}
+    const int inner_bytes = mode == 2 ? box_units * unit_bytes : unit_bytes;
+    if (mode == 2 && (inner_bytes % 16 != 0 || inner_bytes / 8 > 256 || row_bytes % inner_bytes != 0)) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)(mode == 2 ? inner_bytes / 8 : inner_bytes), (cuuint64_t)n_out,
+                                (cuuint64_t)(row_bytes / inner_bytes)};
+    const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, (cuuint64_t)inner_bytes};
+    const cuuint32_t box[3] = {(cuuint32_t)dims[0], (cuuint32_t)box_rows, (cuuint32_t)(mode == 2 ? 1 : box_units)};
     const cuuint32_t elem[3] = {1, 1, 1};
     CUtensorMap m;
-    if (encode(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t *>(w), dims, strides, box, elem,
+    if (encode(&m, mode == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT64 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t *>(w), dims, strides, box, elem,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
@@ -1261,26 +1290,32 @@ bool encode_maps(StreamParams &p, int n) {
     for (int m = 0; m < n; m++) {
         if (p.mat[m].n_out <= 0) continue;
         if ((reinterpret_cast<uintptr_t>(p.mat[m].w) & 15) != 0) return false;
-        if (!weight_map(&p.wmap[m], p.mat[m].w, p.mat[m].n_out, p.row_bytes, F::unit_bytes, kTileRows * p.tps, ku_max)) return false;
+        if (!weight_map(&p.wmap[m], p.mat[m].w, p.mat[m].n_out, p.row_bytes, F::unit_bytes, kTileRows * p.tps, ku_max, p.use_tma)) return false;
     }
     return true;
+}
+
+// setup_format with the tensor-copy layout where the format and the matrices allow it (the maps are encoded here),
+// else with per-row copies. False when the streaming kernel does not address the shape.
+template <int WT>
+bool setup_launch(StreamParams &p, const GemvMat *mats, int n_mat, int64_t n_in, int rows, int silu_pair, size_t *smem) {
+    static const bool no_tma = std::getenv("KRK_CUDA_GEMV_NO_TMA") != nullptr;
+    bool tma = Fmt<WT>::tma != 0 && !no_tma;
+    if (tma) {
+        if (!setup_format<WT>(p, n_in, rows, silu_pair, smem, true)) return false;
+        if (p.use_tma) {
+            for (int m = 0; m < n_mat; m++) p.mat[m] = mats[m];
+            if (!encode_maps<WT>(p, n_mat)) tma = false;   // a map cannot be encoded: set up again for row copies
+        }
+    }
+    return tma || setup_format<WT>(p, n_in, rows, silu_pair, smem);
 }
 
 template <int WT>
 int launch_fmt(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accumulate, int silu_pair, cudaStream_t st) {
     StreamParams p;
     size_t smem = 0;
-    static const bool no_tma = std::getenv("KRK_CUDA_GEMV_NO_TMA") != nullptr;
-    bool tma = Fmt<WT>::tma && !no_tma;
-    if (tma) {
-        // try the tensor-copy layout first; if a map cannot be encoded, set up again for row copies
-        if (!setup_format<WT>(p, n_in, rows, silu_pair, &smem, true)) return 0;
-        if (p.use_tma) {
-            for (int m = 0; m < n_mat; m++) p.mat[m] = mats[m];
-            if (!encode_maps<WT>(p, n_mat)) tma = false;
-        }
-    }
-    if (!tma && !setup_format<WT>(p, n_in, rows, silu_pair, &smem)) return 0;
+    if (!setup_launch<WT>(p, mats, n_mat, n_in, rows, silu_pair, &smem)) return 0;
     p.accumulate = accumulate;
     p.n_entries = 0;
     int total = 0;
@@ -1323,8 +1358,8 @@ template <int WT>
 int launch_peers_fmt(const GemvMat &mat, int64_t n_in, int rows, const PeerScatter &ps, cudaStream_t st) {
     StreamParams p;
     size_t smem = 0;
-    if (!setup_format<WT>(p, n_in, rows, 0, &smem)) return 0;
     if (mat.n_out > (1 << 30) || mat.n_out <= 0) return 0;
+    if (!setup_launch<WT>(p, &mat, 1, n_in, rows, 0, &smem)) return 0;
     p.mat[0] = mat;
     p.n_entries = 1;
     p.gran_begin[0] = 0;
@@ -1343,7 +1378,7 @@ int launch_peers_fmt(const GemvMat &mat, int64_t n_in, int rows, const PeerScatt
     p.wait_peers = ps.wait_peers;
     p.peer_row_stride = ps.row_stride;
     p.peer_offset = ps.offset;
-    const int sms = sm_count();
+    const int sms = sm_count() * ctas_per_sm(smem);
     const int grid = total < sms ? total : sms;
     p.gran_q = total / grid;
     p.gran_r = total % grid;

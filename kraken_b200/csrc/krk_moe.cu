@@ -393,9 +393,104 @@ static size_t moe_float_bytes(const krk_cuda_expert_bank *bank, int k, int64_t n
     return (b + 255) & ~(size_t)255;
 }
 
+// ---- more than eight tokens: expert-major, the tokens of an expert as one matrix (the reference's grouped form,
+// src/engine.cpp:12353-12690: gather the expert's rows, gate / up as a GEMM each, silu_mul, down, scatter-add).
+struct GroupedLayout {
+    size_t off, rows, wt, xg, g, u, dg, gemm, total;
+    size_t gemm_bytes;
+};
+static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
+// rung for a [m x n_in] . W^T product by row count: streaming / shape-agnostic GEMV up to 8 rows, tensor cores above
+static size_t grouped_gemm_bytes(const krk_cuda_expert_bank *bank, int64_t n_tok) {
+    size_t a = 0, b = 0;
+    if (bank->n_embd % 256 == 0 && gemm_tc_takes(bank->wt_gate_up)) a = gemm_workspace_bytes(KRK_CUDA_X_F32, bank->n_ff, bank->n_embd, n_tok);
+    if (bank->n_ff % 256 == 0 && gemm_tc_takes(bank->wt_down)) b = gemm_workspace_bytes(KRK_CUDA_X_F32, bank->n_embd, bank->n_ff, n_tok);
+    return up256(a > b ? a : b);
+}
+static GroupedLayout grouped_layout(const krk_cuda_expert_bank *bank, int k, int64_t n_tok) {
+    GroupedLayout L;
+    const size_t picks = (size_t)(n_tok * k);
+    size_t at = 0;
+    L.off = at; at += up256(sizeof(int32_t) * (kMaxExperts + 1));
+    L.rows = at; at += up256(sizeof(int32_t) * picks);
+    L.wt = at; at += up256(sizeof(float) * picks);
+    L.xg = at; at += up256(sizeof(float) * (size_t)n_tok * bank->n_embd);
+    L.g = at; at += up256(sizeof(float) * (size_t)n_tok * bank->n_ff);
+    L.u = at; at += up256(sizeof(float) * (size_t)n_tok * bank->n_ff);
+    L.dg = at; at += up256(sizeof(float) * (size_t)n_tok * bank->n_embd);
+    L.gemm = at;
+    L.gemm_bytes = grouped_gemm_bytes(bank, n_tok);
+    at += L.gemm_bytes;
+    L.total = at;
+    return L;
+}
+
 size_t moe_workspace_bytes(const krk_cuda_expert_bank *bank, int k, int64_t n_tok) {
+    if (n_tok > KRK_CUDA_MAX_ROWS) return grouped_layout(bank, k, n_tok).total;
     // per-pick h and d rows, then the two matrix tables of the streaming path
     return moe_float_bytes(bank, k, n_tok) + 2 * ((sizeof(StreamTable) + 255) & ~(size_t)255);
+}
+
+static int grouped_matmul(float *y, const float *x, const uint8_t *w, int wt, int64_t n_out, int64_t n_in, int64_t m, void *ws,
+                          cudaStream_t st) {
+    if (m > KRK_CUDA_MAX_ROWS && n_in % 256 == 0 && gemm_tc_takes(wt))
+        return launch_gemm_tc(y, x, KRK_CUDA_X_F32, w, wt, n_out, n_in, m, ws, st);
+    for (int64_t r0 = 0; r0 < m; r0 += KRK_CUDA_MAX_ROWS) {
+        const int64_t nr = m - r0 < KRK_CUDA_MAX_ROWS ? m - r0 : KRK_CUDA_MAX_ROWS;
+        GemvMat mat;
+        mat.w = w;
+        mat.x = x + r0 * n_in;
+        mat.y = y + r0 * n_out;
+        mat.n_out = n_out;
+        mat.wt = wt;
+        int rc = launch_gemv_stream(&mat, 1, n_in, (int)nr, 0, 0, st);
+        if (rc < 0) return rc;
+        if (rc == 0) rc = launch_gemv_generic(&mat, 1, n_in, (int)nr, 0, 0, st);
+        if (rc != KRK_CUDA_OK && rc != 1) return rc;
+    }
+    return KRK_CUDA_OK;
+}
+
+// y[n_tok][n_embd] = sum over the picks this bank holds, experts in ascending id, of w * down(silu(gate x) * up x).
+// One device-to-host copy of the plan's offsets (a stream synchronisation) tells the host how many rows each
+// expert has, as the reference's host plan does.
+static int launch_moe_ffn_grouped(float *y, const float *x, const int32_t *ids, const float *wts, const krk_cuda_expert_bank *bank,
+                                  int k, int64_t n_tok, void *workspace, cudaStream_t st) {
+    const int n_expert = bank->expert_base + bank->n_local;   // ids at or above this are held elsewhere
+    if (n_expert > kMaxExperts) return KRK_CUDA_EARG;
+    const GroupedLayout L = grouped_layout(bank, k, n_tok);
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    int32_t *off = reinterpret_cast<int32_t *>(ws + L.off), *rows = reinterpret_cast<int32_t *>(ws + L.rows);
+    float *wt = reinterpret_cast<float *>(ws + L.wt), *xg = reinterpret_cast<float *>(ws + L.xg);
+    float *g = reinterpret_cast<float *>(ws + L.g), *u = reinterpret_cast<float *>(ws + L.u), *dg = reinterpret_cast<float *>(ws + L.dg);
+    int rc = launch_moe_plan_build(ids, n_tok, k, n_expert, off, rows, wt, wts, st);
+    if (rc != KRK_CUDA_OK) return rc;
+    static thread_local int32_t h_off[kMaxExperts + 1];
+    cudaError_t e = cudaMemcpyAsync(h_off, off, sizeof(int32_t) * (size_t)(n_expert + 1), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(y, 0, sizeof(float) * (size_t)n_tok * bank->n_embd, st);
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        return KRK_CUDA_ELAUNCH;
+    }
+    const size_t rb_gu = row_bytes(bank->wt_gate_up, bank->n_embd), rb_dn = row_bytes(bank->wt_down, bank->n_ff);
+    for (int ex = bank->expert_base; ex < n_expert; ex++) {
+        const int64_t m = h_off[ex + 1] - h_off[ex];
+        if (m <= 0) continue;
+        const int local = ex - bank->expert_base;
+        const int32_t *er = rows + h_off[ex];
+        const float *ew = wt + h_off[ex];
+        const uint8_t *wg = static_cast<const uint8_t *>(bank->gate) + (size_t)local * bank->n_ff * rb_gu;
+        const uint8_t *wu = static_cast<const uint8_t *>(bank->up) + (size_t)local * bank->n_ff * rb_gu;
+        const uint8_t *wd = static_cast<const uint8_t *>(bank->down) + (size_t)local * bank->n_embd * rb_dn;
+        if ((rc = launch_gather_rows(xg, x, er, m, bank->n_embd, st)) != KRK_CUDA_OK) return rc;
+        if ((rc = grouped_matmul(g, xg, wg, bank->wt_gate_up, bank->n_ff, bank->n_embd, m, ws + L.gemm, st)) != KRK_CUDA_OK) return rc;
+        if ((rc = grouped_matmul(u, xg, wu, bank->wt_gate_up, bank->n_ff, bank->n_embd, m, ws + L.gemm, st)) != KRK_CUDA_OK) return rc;
+        if ((rc = launch_silu_mul(g, g, u, m * bank->n_ff, st)) != KRK_CUDA_OK) return rc;
+        if ((rc = grouped_matmul(dg, g, wd, bank->wt_down, bank->n_embd, bank->n_ff, m, ws + L.gemm, st)) != KRK_CUDA_OK) return rc;
+        if ((rc = launch_scatter_axpy_rows(y, dg, er, ew, m, bank->n_embd, st)) != KRK_CUDA_OK) return rc;
+    }
+    return KRK_CUDA_OK;
 }
 
 int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const float *wts,
@@ -404,6 +499,13 @@ int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const f
     // `logits` set: route first (ids / wts are outputs). The streaming path folds the routing into its plan
     // kernel; every other path runs the routing kernel on its own.
     bool routed = logits == nullptr;
+    if (n_tok > KRK_CUDA_MAX_ROWS) {
+        if (!routed) {
+            const int rc = launch_route(const_cast<int32_t *>(ids), const_cast<float *>(wts), logits, n_tok, n_expert, k, st);
+            if (rc != KRK_CUDA_OK) return rc;
+        }
+        return launch_moe_ffn_grouped(y, x, ids, wts, bank, k, n_tok, workspace, st);
+    }
     MoeParams p;
     p.gate = static_cast<const uint8_t *>(bank->gate);
     p.up = static_cast<const uint8_t *>(bank->up);

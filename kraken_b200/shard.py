@@ -87,6 +87,44 @@ class ShardedHead:
         return torch.cat([self._gather[r, :, :c] for r, (_, c) in enumerate(self.ranges)], dim=1)
 
 
+class NcclHead:
+    """The NCCL form of the sharded head through the C ABI (krk_cuda_shard_allgather over ncclAllGather): the GEMV
+    writes this rank's slice straight into its slot of a persistent full-row buffer and the all-gather runs in
+    place on it, so a step is one kernel and one collective with no staging copy; both replay from a CUDA
+    graph. Needs slices of equal length (n_out a multiple of world * align) and one activation row. The
+    communicator is the library's own (krk_cuda_nccl_comm_init); its id travels through the process group."""
+
+    def __init__(self, n_out: int, n_in: int, wt: int, w_local, group=None, align: int = 8):
+        import torch
+        import torch.distributed as dist
+        from . import capi
+        self.capi = capi
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.begin, self.count = row_range(n_out, self.world, self.rank, align)
+        if self.count * self.world != n_out:
+            raise ValueError("NcclHead needs equal slices")
+        self.n_out, self.n_in, self.wt, self.w_local = n_out, n_in, wt, w_local
+        ids = [capi.NcclComm.unique_id() if self.rank == 0 else None]
+        dist.broadcast_object_list(ids, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        self.comm = capi.NcclComm(self.world, self.rank, ids[0])
+        self.full = torch.zeros((1, n_out), dtype=torch.float32, device=w_local.device)
+        self.slot = self.full[:, self.begin:self.begin + self.count]
+
+    def forward(self, x):
+        slot = self.full.view(-1)[self.begin:self.begin + self.count]
+        self.capi.gemv(x, self.w_local, self.wt, self.count, self.n_in, out=slot.view(1, -1))
+        self.comm.allgather(self.full, slot)
+        return self.full
+
+    def gather_only(self):
+        slot = self.full.view(-1)[self.begin:self.begin + self.count]
+        self.comm.allgather(self.full, slot)
+        return self.full
+
+    def close(self):
+        self.comm.close()
+
+
 class _PeerBuffers:
     """A set of device buffers per GPU that every process of the group has mapped: ``own[i]`` is this
     GPU's i-th buffer (capi.PeerBuffer), ``ptrs[i][q]`` its address on GPU q as seen from this process.

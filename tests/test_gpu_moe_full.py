@@ -128,3 +128,69 @@ def test_router_near_ties_match_the_host(cuda, oracle):
     good = np.ones(n_rows, dtype=bool)
     good[bad] = False
     assert np.allclose(wts.cpu().numpy()[good], wts_ref[good], rtol=2e-6, atol=1e-9)
+
+
+@pytest.mark.parametrize("n_tok,n_exp,k", [(40, 16, 4), (9, 8, 2), (300, 16, 8)])
+def test_moe_more_than_eight_tokens_expert_major(cuda, oracle, n_tok, n_exp, k):
+    """Prefill batches: the expert-major grouped path (gather the tokens of an expert, gate / up / down on the
+    tensor cores, scatter-add in ascending expert id) against the checker's per-expert loop. The GEMMs round the
+    activations to f16 (the prefill bar is 2e-3 of ||w_row|| * ||x_row|| per product), so the end-to-end bar is a
+    relative L2 of 3e-3; experts with at most eight tokens run the decode GEMV."""
+    n_embd, n_ff = 1024, 512
+    seed = SEED + 900 + n_tok
+    gate = [synth.weights(synth.Q4_K, n_ff, n_embd, seed, stream=1000 + e) for e in range(n_exp)]
+    up = [synth.weights(synth.Q4_K, n_ff, n_embd, seed, stream=2000 + e) for e in range(n_exp)]
+    down = [synth.weights(synth.Q6_K, n_embd, n_ff, seed, stream=3000 + e) for e in range(n_exp)]
+    # activations of a size that keeps silu(gate) * up inside the f16 range the GEMM stages its input in (the
+    # synthetic weights are far larger than a trained model's)
+    x = synth.activations(n_tok, n_embd, seed) * np.float32(0.125)
+    logits = synth.activations(n_tok, n_exp, seed, stream=7)
+    ids_ref, wts_ref = oracle.route(logits, k)
+    y_ref = oracle.moe_ffn(x, ids_ref, wts_ref, gate, up, down, synth.Q4_K, synth.Q6_K, n_embd, n_ff, threads=8)
+    bank = cuda.make_bank(dev(np.stack(gate)), dev(np.stack(up)), dev(np.stack(down)), synth.Q4_K, synth.Q6_K, n_exp, 0,
+                          n_embd, n_ff)
+    y, ids, wts = cuda.moe_ffn_routed(dev(x), dev(logits), k, bank)
+    assert cuda.device_status() == 0
+    assert np.array_equal(ids.cpu().numpy(), ids_ref)
+    rel = np.linalg.norm(y.cpu().numpy() - y_ref) / np.linalg.norm(y_ref)
+    assert rel < 3e-3, f"relative L2 error {rel:.2e}"
+    # a shard (the upper half of the experts) gives the checker's partial sum over those experts
+    lo = n_exp // 2
+    part_bank = cuda.make_bank(dev(np.stack(gate[lo:])), dev(np.stack(up[lo:])), dev(np.stack(down[lo:])), synth.Q4_K,
+                               synth.Q6_K, n_exp - lo, lo, n_embd, n_ff)
+    part = cuda.moe_ffn(dev(x), ids, wts, part_bank).cpu().numpy()
+    sel = lambda mats: [m if e >= lo else None for e, m in enumerate(mats)]
+    part_ref = oracle.moe_ffn(x, ids_ref, wts_ref, sel(gate), sel(up), sel(down), synth.Q4_K, synth.Q6_K, n_embd, n_ff, threads=8)
+    assert np.linalg.norm(part - part_ref) / np.linalg.norm(part_ref) < 3e-3
+
+
+def test_router_steps_and_plan_match_the_host(cuda, oracle):
+    """router_softmax -> router_topk -> moe_plan_build, the three steps of the Backend interface: ids and weights
+    are the one-call router's (hence the host's), the plan is the host's expert-major plan (tokens ascending, then
+    slots ascending, within each expert)."""
+    n_tok, n_exp, k = 37, 128, 8
+    logits = synth.activations(n_tok, n_exp, SEED + 41, stream=7)
+    ld = dev(logits)
+    probs = cuda.router_softmax(ld)
+    ids, wts = cuda.router_topk(probs, k)
+    ids1, wts1 = cuda.route(ld, k)
+    import torch
+    assert torch.equal(ids, ids1) and torch.equal(wts, wts1)
+    ids_ref, wts_ref = oracle.route(logits, k)
+    assert np.array_equal(ids.cpu().numpy(), ids_ref)
+    p = probs.cpu().numpy()
+    assert np.allclose(p.sum(axis=1), 1.0, atol=1e-5)
+    _, raw = cuda.router_topk(probs, k, normalize=False, scale=2.0)
+    picked = np.take_along_axis(p, ids_ref.astype(np.int64), axis=1)
+    assert np.array_equal(raw.cpu().numpy(), (picked * np.float32(2.0)).astype(np.float32))
+    off, rows, wt = (t.cpu().numpy() for t in cuda.moe_plan_build(ids, wts, n_exp))
+    want_off, want_rows, want_wt = [0], [], []
+    w_np = wts.cpu().numpy()
+    for e in range(n_exp):
+        for t in range(n_tok):
+            for s in range(k):
+                if ids_ref[t, s] == e:
+                    want_rows.append(t)
+                    want_wt.append(w_np[t, s])
+        want_off.append(len(want_rows))
+    assert off.tolist() == want_off and rows.tolist() == want_rows and wt.tolist() == want_wt

@@ -75,6 +75,24 @@ def _worker(rank, world, port, ret):
             assert rel < 1e-5, rel
         peer_sum.close()
         dist.barrier()
+        # ---- the C-side exchange: krk_cuda_shard_allgather over a communicator made by the library's own wrappers ----
+        ids = [capi.NcclComm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        comm = capi.NcclComm(world, rank, ids[0])
+        even = (n_out // world) // 8 * 8                      # equal slices for the plain all-gather
+        x = torch.from_numpy(synth.activations(1, n_in, seed + 90)).cuda()
+        mine = capi.gemv(x, w_full[rank * even:(rank + 1) * even].contiguous(), wt, even, n_in)
+        full = torch.zeros((world, even), dtype=torch.float32, device="cuda")
+        comm.allgather(full, mine)
+        torch.cuda.synchronize()
+        want = capi.gemv(x, w_full[:world * even].contiguous(), wt, world * even, n_in)
+        assert torch.equal(full.view(1, -1), want), "C-side NCCL all-gather of the slices differs from the unsharded row"
+        full[rank].copy_(mine[0] * 2)                          # in place: the slice already sits in its slot
+        comm.allgather(full, full[rank])
+        torch.cuda.synchronize()
+        assert torch.equal(full.view(1, -1), want * 2)
+        comm.close()
+        dist.barrier()
         ret[rank] = "ok"
     finally:
         dist.destroy_process_group()
