@@ -1164,6 +1164,7 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
         p.unit_stride = kTileRows * p.tps * F::unit_bytes;
         p.box_bytes = ku_max * p.unit_stride;
         p.stage_bytes = align_up(p.box_bytes, 128);
+        p.gran = kTileRows * p.tps;   // a copy brings whole tiles: CTAs split the rows at tile boundaries, so no row is fetched twice
     } else if (want_tma && F::tma == 2 && !p.whole_tiles && ku_max == kConsumerWarps && p.units % kConsumerWarps == 0) {
         // a stage is one tensor copy of eight units of each row: [row][8 units], pitch 8 * unit_bytes (1680 for
         // Q6_K: the rows of a fragment load again lie 16 bytes apart in the banks)
@@ -1172,6 +1173,7 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
         p.row_stride = ku_max * F::unit_bytes;
         p.box_bytes = kTileRows * p.tps * p.row_stride;
         p.stage_bytes = align_up(p.box_bytes, 128);
+        p.gran = kTileRows * p.tps;
     } else if (p.whole_tiles) {
         p.row_stride = p.row_bytes;
         p.stage_bytes = align_up(kTileRows * p.tps * p.row_bytes, 128);
@@ -1244,6 +1246,14 @@ struct MapKeyHash {
         return h;
     }
 };
+CUtensorMapL2promotion l2_promotion() {
+    static const int v = [] {
+        const char *e = std::getenv("KRK_CUDA_GEMV_L2PROMO");
+        return e ? std::atoi(e) : 3;
+    }();
+    return v == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : v == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+           : v == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+}
 bool weight_map(CUtensorMap *out, const uint8_t *w, int64_t n_out, int row_bytes, int unit_bytes, int box_rows, int box_units,
                 int mode) {
     static EncodeTiledFn encode = [] {
@@ -1275,7 +1285,7 @@ bool weight_map(CUtensorMap *out, const uint8_t *w, int64_t n_out, int row_bytes
     const cuuint32_t elem[3] = {1, 1, 1};
     CUtensorMap m;
     if (encode(&m, mode == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT64 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t *>(w), dims, strides, box, elem,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, l2_promotion(),
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     if (cache.size() > 65536) cache.clear();   // bounded: a host that keeps re-uploading weights starts over
