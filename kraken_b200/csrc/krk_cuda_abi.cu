@@ -15,7 +15,7 @@ std::atomic<int64_t> g_family[4];
 
 struct DeviceState {
     int *status = nullptr;
-    int sms = 0;
+    std::atomic<int> sms{0};   // published last (release): a thread that sees it set also sees `status`
 };
 constexpr int kMaxDevices = 64;
 DeviceState g_dev[kMaxDevices];
@@ -25,16 +25,16 @@ DeviceState *device_state() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
     DeviceState &s = g_dev[dev];
-    if (s.sms == 0) {
+    if (s.sms.load(std::memory_order_acquire) == 0) {
         std::lock_guard<std::mutex> lk(g_dev_mu);
-        if (s.sms == 0) {
+        if (s.sms.load(std::memory_order_relaxed) == 0) {
             int sms = 0;
             if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
             int *p = nullptr;
             if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
             cudaMemset(p, 0, sizeof(int));
             s.status = p;
-            s.sms = sms;
+            s.sms.store(sms, std::memory_order_release);
         }
     }
     return &s;
@@ -55,7 +55,7 @@ int *device_status_word() {
 }
 int sm_count() {
     DeviceState *s = device_state();
-    return s ? s->sms : 1;
+    return s ? s->sms.load(std::memory_order_relaxed) : 1;
 }
 
 static inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }

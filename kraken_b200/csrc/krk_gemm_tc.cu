@@ -496,12 +496,11 @@ struct Raw<KRK_CUDA_Q8_0> {
 // ---- the kernel ------------------------------------------------------------------------------------
 
 // ---- work items ---------------------------------------------------------------------------------------
-// Tiles are dealt to the persistent CTAs in whole waves; the tiles left over after the last whole wave
-// (all of them when there are fewer tiles than CTAs) would keep only some SMs busy, so their K range is
-// cut into equal pieces over ALL CTAs instead (in units of four K steps = one super-block). A tile that
-// is cut this way has its pieces written to a scratch slot each; the CTA that finishes a tile's last
-// piece (a counter tells it so, nobody waits for anybody) adds the pieces in K order and writes Y, so
-// the result is the same on every run.
+// Tiles are dealt to the persistent CTAs in whole waves. With split_tail set (off by default) the tiles left
+// over after the last whole wave, which would keep only some SMs busy, have their K range cut into equal
+// pieces over ALL CTAs instead (in units of four K steps = one super-block). The pieces of a cut tile meet in
+// Y itself: piece 0 stores, piece k waits (bounded) until the tile's count says that pieces 0..k-1 are in Y and
+// then adds with a TMA reduction, so the additions happen in K order and the result is the same on every run.
 struct Item {
     int tile;      // tile index
     int k0, nk;    // K steps [k0, k0 + nk)
