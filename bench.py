@@ -682,7 +682,10 @@ def decode_extra(torch, capi, gen, barrier):
     cases = [("config1_q8_0_4096x4096", synth.Q8_0, 4096, 4096, device_weights_q8_0),
              ("steady_q8_0_65536x4096", synth.Q8_0, 65536, 4096, device_weights_q8_0),
              ("steady_q4_k_131072x4096", synth.Q4_K, 131072, 4096, device_weights),
-             ("steady_q6_k_128256x4096", synth.Q6_K, 128256, 4096, device_weights_q6k)]
+             ("steady_q6_k_128256x4096", synth.Q6_K, 128256, 4096, device_weights_q6k),
+             ("steady_q4_0_131072x4096", synth.Q4_0, 131072, 4096, device_weights_q4_0),
+             # a format without a streaming arm: the warp-per-row kernel, so that its gap is on record
+             ("warp_per_row_q5_k_65536x4096", synth.Q5_K, 65536, 4096, device_weights_q5_k)]
     out = {}
     for name, wt, n_out, n_in, make in cases:
         wbytes = n_out * synth.row_bytes(wt, n_in)

@@ -69,6 +69,8 @@ template <int WT> struct Fmt;
 template <> struct Fmt<KRK_CUDA_Q4_K> { static constexpr int unit_values = 256, unit_bytes = 144, stride_mod = 32, tma = 1; };
 template <> struct Fmt<KRK_CUDA_Q6_K> { static constexpr int unit_values = 256, unit_bytes = 210, stride_mod = 16, tma = 2; };
 template <> struct Fmt<KRK_CUDA_Q8_0> { static constexpr int unit_values = 128, unit_bytes = 136, stride_mod = 16, tma = 0; };
+// Q4_0: eight 18-byte blocks are 144 bytes, the size of a Q4_K unit, so the stages are laid out the same way.
+template <> struct Fmt<KRK_CUDA_Q4_0> { static constexpr int unit_values = 256, unit_bytes = 144, stride_mod = 16, tma = 1; };
 
 struct StreamParams {
     GemvMat mat[KRK_CUDA_MAX_GROUP];
@@ -163,6 +165,11 @@ __device__ __forceinline__ void mma_s8_k16_biased(float (&c)[4], uint32_t a0, ui
 #pragma unroll
     for (int i = 0; i < 4; i++) c[i] = __int_as_float(r[i]) - kMagic;
 }
+__device__ __forceinline__ void mma_u8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
 __device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
     asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
@@ -222,7 +229,7 @@ template <int WT>
 __host__ __device__ inline int plane_bytes(int n_in, int rows) { return align_up(rows * 3 * plane_stride(n_in), 128); }
 template <int WT>
 __host__ __device__ inline int chunk_sum_bytes(int n_in, int rows) {   // [row][4 limbs][n_in / 32] s8
-    return WT == KRK_CUDA_Q4_K ? align_up(rows * (n_in / 32) * 4, 128) : 0;
+    return (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q4_0) ? align_up(rows * (n_in / 32) * 4, 128) : 0;   // Q4_0: [row][n_in / 32] f32
 }
 
 // ---- the walk over this CTA's stages: identical in the producer and in the consumers -------------
@@ -356,11 +363,38 @@ __device__ __forceinline__ void quantize_slice(const float (&f)[Fmt<WT>::unit_va
             *reinterpret_cast<uint16_t *>(p1 + base + kb) = (uint16_t)(w1 >> 16);
             *reinterpret_cast<uint16_t *>(p2 + base + ka) = (uint16_t)(w2 & 0xFFFF);
             *reinterpret_cast<uint16_t *>(p2 + base + kb) = (uint16_t)(w2 >> 16);
+        } else if (WT == KRK_CUDA_Q4_0) {
+            // A block's 16 quant bytes hold value j in their low and value 16 + j in their high nibbles, so the
+            // limbs of a block lie as [16 of the low half][16 of the high half], each in the order the lanes take
+            // the quant bytes: as they are in odd blocks; [0,1,14,15, 2..13] in even blocks, whose quants start
+            // 2 bytes off a word boundary (pairs stay together, as for Q8_0).
+            const int e = i & 15, base = (i & ~31) + (i & 16);
+            if (((i >> 5) & 1) == 0) {
+                const int e2 = e + 2;
+                const int ka = e < 2 ? e : (e >= 14 ? e - 12 : e + 2);
+                const int kb = e2 < 2 ? e2 : (e2 >= 14 ? e2 - 12 : e2 + 2);
+                *reinterpret_cast<uint16_t *>(p0 + base + ka) = (uint16_t)(w0 & 0xFFFF);
+                *reinterpret_cast<uint16_t *>(p0 + base + kb) = (uint16_t)(w0 >> 16);
+                *reinterpret_cast<uint16_t *>(p1 + base + ka) = (uint16_t)(w1 & 0xFFFF);
+                *reinterpret_cast<uint16_t *>(p1 + base + kb) = (uint16_t)(w1 >> 16);
+                *reinterpret_cast<uint16_t *>(p2 + base + ka) = (uint16_t)(w2 & 0xFFFF);
+                *reinterpret_cast<uint16_t *>(p2 + base + kb) = (uint16_t)(w2 >> 16);
+            } else {
+                *reinterpret_cast<uint32_t *>(p0 + base + e) = w0;
+                *reinterpret_cast<uint32_t *>(p1 + base + e) = w1;
+                *reinterpret_cast<uint32_t *>(p2 + base + e) = w2;
+            }
         } else {
             *reinterpret_cast<uint32_t *>(p0 + i) = w0;
             *reinterpret_cast<uint32_t *>(p1 + i) = w1;
             *reinterpret_cast<uint32_t *>(p2 + i) = w2;
         }
+    }
+    if (WT == KRK_CUDA_Q4_0) {
+        // the sum of X over each 32-value block, as a float: the -8 of every quant leaves -8 * d * sum per block
+        total += __shfl_xor_sync(0xFFFFFFFFu, total, 1);
+        total += __shfl_xor_sync(0xFFFFFFFFu, total, 2);
+        if ((lane & 3) == 0) reinterpret_cast<float *>(sums)[k0 >> 5] = (float)total;   // |sum| < 2^28
     }
     if (WT == KRK_CUDA_Q4_K) {
         // a 32-value chunk is held by 4 consecutive lanes; |sum| <= 32 * 127 * 2^16 < 2^28
@@ -601,6 +635,47 @@ __device__ __forceinline__ void unit_q4_k_single(const uint8_t *rowA, const uint
     acc.m[3] = fmaf(nB, cm[3], acc.m[3]);
 }
 
+// Eight Q4_0 blocks (src/quant.cpp:331-339), one activation row. A block is a 2-byte scale d and 16 bytes whose
+// low nibbles are quants 0..15 and whose high nibbles are quants 16..31; the value is d * (q - 8). Per block two
+// k16 MMAs over the same 16 bytes, L = (bytes & 0x0F) and R = raw bytes, against columns [limb j over the low
+// half, limb j over the high half]: low half = L[even column], high half = (R[odd] - L[odd]) / 16. Lane t keeps
+// limb t of rows g and g+8 (times 16); lane t = 3, whose columns carry no limb, keeps d * (sum of X over the
+// block) instead, which enters the result with weight -8. Blocks at an even index have their quants 2 bytes off
+// a word boundary: lane t = 0 glues the half words at the two ends (the limbs are laid out to match).
+__device__ __forceinline__ void unit_q4_0(const uint8_t *rowA, const uint8_t *rowB, const int8_t *bq, const float *fs, int t,
+                                          AccumSingle &acc) {
+#pragma unroll
+    for (int b = 0; b < 8; b++) {
+        uint32_t qa, qb;
+        float dA, dB;
+        if ((b & 1) == 0) {
+            const uint32_t *wa = reinterpret_cast<const uint32_t *>(rowA + 18 * b);
+            const uint32_t *wb = reinterpret_cast<const uint32_t *>(rowB + 18 * b);
+            const uint32_t a_first = wa[0], b_first = wb[0];
+            qa = t == 0 ? __byte_perm(a_first, wa[4], 0x5432) : wa[t];
+            qb = t == 0 ? __byte_perm(b_first, wb[4], 0x5432) : wb[t];
+            dA = half_lo(a_first);
+            dB = half_lo(b_first);
+        } else {
+            qa = reinterpret_cast<const uint32_t *>(rowA + 18 * b + 2)[t];
+            qb = reinterpret_cast<const uint32_t *>(rowB + 18 * b + 2)[t];
+            dA = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(rowA + 18 * b)));
+            dB = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(rowB + 18 * b)));
+        }
+        const uint32_t bw = *reinterpret_cast<const uint32_t *>(bq + 32 * b + 4 * t);
+        int cl[4], cr[4];
+        mma_u8_k16(cl, qa & 0x0F0F0F0Fu, qb & 0x0F0F0F0Fu, bw);
+        mma_u8_k16(cr, qa, qb, bw);
+        // |16 lo + hr - hl| < 2^21: 16 x (16 * 15 + 255 + 15) x 128, so the bits of 1.5 * 2^23 turn it into a float
+        const int vA = 16 * cl[0] + cr[1] - cl[1], vB = 16 * cl[2] + cr[3] - cl[3];
+        const float sum = fs[b];
+        const float fa = t == 3 ? sum : __int_as_float(vA + 0x4B400000) - kMagic;
+        const float fb = t == 3 ? sum : __int_as_float(vB + 0x4B400000) - kMagic;
+        acc.f[0] = fmaf(dA, fa, acc.f[0]);
+        acc.f[1] = fmaf(dB, fb, acc.f[1]);
+    }
+}
+
 // Four Q8_0 blocks. A block is a 2-byte scale then 32 quants, so blocks at an even index have
 // their quants 2 bytes off a word boundary: their lanes read the aligned words and lane t = 0
 // glues the two half words at the ends into one (the activation limbs are permuted to match).
@@ -738,7 +813,8 @@ __global__ void __launch_bounds__(kThreads, NG == 1 ? 2 : 1)
 gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     // STACK: several 16-row tiles per stage (p.tps of them); compiled apart so that the usual one-tile
     // form carries none of its index arithmetic.
-    static_assert(!SINGLE || (WT == KRK_CUDA_Q4_K && NG == 1), "the single-row form is Q4_K only");
+    static_assert(!SINGLE || ((WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q4_0) && NG == 1), "the single-row forms are Q4_K and Q4_0");
+    static_assert(WT != KRK_CUDA_Q4_0 || SINGLE == 1, "Q4_0 has the single-row form only");
     const int tps = STACK ? p.tps : 1;
     using F = Fmt<WT>;
     using SmemT = Smem<NG>;
@@ -931,7 +1007,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         chunk_sum += my_sub * chunk_sum_bytes<WT>(p.n_in, p.rows);
     }
     // single-row form: column g = limb g/2 of the low (g even) or high (g odd) chunk of a group
-    const int8_t *bq = planes + (g < 6 ? (g >> 1) * plane_stride(p.n_in) + 32 * (g & 1) : 0);
+    const int8_t *bq = planes + (g < 6 ? (g >> 1) * plane_stride(p.n_in) + (WT == KRK_CUDA_Q4_0 ? 16 : 32) * (g & 1) : 0);
     const int8_t *sq = chunk_sum + (g & 3) * (p.n_in >> 5);
     BFrag held[2];
 
@@ -989,7 +1065,9 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                         const uint8_t *rowA = tile0 + (size_t)su * p.unit_stride, *rowB = rowA + (size_t)8 * p.row_stride;
                         const int unit = ck * kConsumerWarps + su;
                         const int kbase = unit * F::unit_values;
-                        if (SINGLE == 2) {
+                        if (WT == KRK_CUDA_Q4_0) {
+                            unit_q4_0(rowA, rowB, bq + kbase, reinterpret_cast<const float *>(chunk_sum) + (kbase >> 5), t, acs);
+                        } else if (SINGLE == 2) {
                             unit_q4_k_single(rowA, rowB, bf, t, acs);
                         } else if (SINGLE == 1) {
                             unit_q4_k_single(rowA, rowB, load_bfrag(bq + kbase, sq + (kbase >> 5), t), t, acs);
@@ -1029,7 +1107,8 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
              float4 o[NG];
              if (SINGLE) {
                  // lane t holds limb t (weights 65536, 256, 1) of rows g and g+8, times 16
-                 const float wl = t == 0 ? 4096.0f : (t == 1 ? 16.0f : (t == 2 ? 0.0625f : 0.0f));
+                 // (Q4_0: lane t = 3 holds d * sum of X per block, the -8 of every quant)
+                 const float wl = t == 0 ? 4096.0f : (t == 1 ? 16.0f : (t == 2 ? 0.0625f : (WT == KRK_CUDA_Q4_0 ? -8.0f : 0.0f)));
                  o[0].x = (wl * acs.f[0] - fmaf(me0, acs.m[0], me1 * acs.m[1])) * xs[0];
                  o[0].z = (wl * acs.f[1] - fmaf(me0, acs.m[2], me1 * acs.m[3])) * xs[0];
                  o[0].y = o[0].w = 0.0f;
@@ -1125,6 +1204,7 @@ template <int WT>
 bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t *smem_out, bool want_tma = false) {
     using F = Fmt<WT>;
     if (n_in % 256 != 0 || n_in > (1 << 20) || rows < 1 || rows > KRK_CUDA_MAX_ROWS) return false;
+    if (WT == KRK_CUDA_Q4_0 && rows != 1) return false;   // its unit carries one activation row: 2..8 rows take the warp-per-row kernel
     p.n_in = (int)n_in;
     p.units = (int)(n_in / F::unit_values);
     p.row_bytes = (int)row_bytes(WT, n_in);
@@ -1198,17 +1278,22 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
 template <int WT>
 int launch_rows(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
     constexpr bool kQ4K = WT == KRK_CUDA_Q4_K;
-    if (p.tps > 1) {
-        if (kQ4K && p.rows == 1) return launch_one<WT, 1, true, kQ4K ? 2 : 0>(p, grid, smem, st);
-        if (p.rows <= 2) return launch_one<WT, 1, true, 0>(p, grid, smem, st);
-        if (p.rows <= 4) return launch_one<WT, 2, true, 0>(p, grid, smem, st);
-        return launch_one<WT, 4, true, 0>(p, grid, smem, st);
+    if constexpr (WT == KRK_CUDA_Q4_0) {   // one activation row only (setup_format refuses the others)
+        if (p.tps > 1) return launch_one<WT, 1, true, 1>(p, grid, smem, st);
+        return launch_one<WT, 1, false, 1>(p, grid, smem, st);
+    } else {
+        if (p.tps > 1) {
+            if (kQ4K && p.rows == 1) return launch_one<WT, 1, true, kQ4K ? 2 : 0>(p, grid, smem, st);
+            if (p.rows <= 2) return launch_one<WT, 1, true, 0>(p, grid, smem, st);
+            if (p.rows <= 4) return launch_one<WT, 2, true, 0>(p, grid, smem, st);
+            return launch_one<WT, 4, true, 0>(p, grid, smem, st);
+        }
+        if (kQ4K && p.rows == 1 && !p.whole_tiles && p.units <= 2 * kConsumerWarps) return launch_one<WT, 1, false, kQ4K ? 2 : 0>(p, grid, smem, st);
+        if (kQ4K && p.rows == 1) return launch_one<WT, 1, false, kQ4K ? 1 : 0>(p, grid, smem, st);
+        if (p.rows <= 2) return launch_one<WT, 1, false, 0>(p, grid, smem, st);
+        if (p.rows <= 4) return launch_one<WT, 2, false, 0>(p, grid, smem, st);
+        return launch_one<WT, 4, false, 0>(p, grid, smem, st);
     }
-    if (kQ4K && p.rows == 1 && !p.whole_tiles && p.units <= 2 * kConsumerWarps) return launch_one<WT, 1, false, kQ4K ? 2 : 0>(p, grid, smem, st);
-    if (kQ4K && p.rows == 1) return launch_one<WT, 1, false, kQ4K ? 1 : 0>(p, grid, smem, st);
-    if (p.rows <= 2) return launch_one<WT, 1, false, 0>(p, grid, smem, st);
-    if (p.rows <= 4) return launch_one<WT, 2, false, 0>(p, grid, smem, st);
-    return launch_one<WT, 4, false, 0>(p, grid, smem, st);
 }
 
 // CTAs of one launch per SM. 2 (default): both halves of an SM work on this launch (16 consumer warps per SM:
@@ -1434,7 +1519,8 @@ int launch_gemv_stream(const GemvMat *mats, int n_mat, int64_t n_in, int rows, i
     case KRK_CUDA_Q4_K: return launch_fmt<KRK_CUDA_Q4_K>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q6_K: return launch_fmt<KRK_CUDA_Q6_K>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q8_0: return launch_fmt<KRK_CUDA_Q8_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
-    default: return 0;   // Q4_0 takes the shape-agnostic kernel
+    case KRK_CUDA_Q4_0: return launch_fmt<KRK_CUDA_Q4_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
+    default: return 0;   // the other formats take the shape-agnostic kernel
     }
 }
 
@@ -1443,6 +1529,7 @@ int launch_gemv_stream_table(const StreamTable *table, int wt, int64_t n_in, int
     case KRK_CUDA_Q4_K: return launch_table_fmt<KRK_CUDA_Q4_K>(table, n_in, silu_pair, st);
     case KRK_CUDA_Q6_K: return launch_table_fmt<KRK_CUDA_Q6_K>(table, n_in, silu_pair, st);
     case KRK_CUDA_Q8_0: return launch_table_fmt<KRK_CUDA_Q8_0>(table, n_in, silu_pair, st);
+    case KRK_CUDA_Q4_0: return launch_table_fmt<KRK_CUDA_Q4_0>(table, n_in, silu_pair, st);
     default: return 0;
     }
 }
@@ -1452,6 +1539,7 @@ int launch_gemv_stream_peers(const GemvMat &mat, int64_t n_in, int rows, const P
     case KRK_CUDA_Q4_K: return launch_peers_fmt<KRK_CUDA_Q4_K>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q6_K: return launch_peers_fmt<KRK_CUDA_Q6_K>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q8_0: return launch_peers_fmt<KRK_CUDA_Q8_0>(mat, n_in, rows, ps, st);
+    case KRK_CUDA_Q4_0: return launch_peers_fmt<KRK_CUDA_Q4_0>(mat, n_in, rows, ps, st);
     default: return 0;
     }
 }
@@ -1469,6 +1557,7 @@ int stream_gran(int wt, int64_t n_in) {
     case KRK_CUDA_Q4_K: return gran_fmt<KRK_CUDA_Q4_K>(n_in);
     case KRK_CUDA_Q6_K: return gran_fmt<KRK_CUDA_Q6_K>(n_in);
     case KRK_CUDA_Q8_0: return gran_fmt<KRK_CUDA_Q8_0>(n_in);
+    case KRK_CUDA_Q4_0: return gran_fmt<KRK_CUDA_Q4_0>(n_in);
     default: return 0;
     }
 }

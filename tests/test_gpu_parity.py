@@ -150,9 +150,14 @@ def test_config4_q6_k_head_slice_and_linearity(cuda, oracle):
 
 
 def test_path_selection(cuda, oracle):
-    """Which kernel serves which shape: Q4_0 and K not a multiple of 256 take the shape-agnostic
-    kernel; Q6_K rows that are not 16-byte multiples (K = 1536) still stream, as whole tiles."""
-    run_gemv(cuda, oracle, synth.Q4_0, 64, 1024, 1, SEED + 30, expect_stream=False)
+    """Which kernel serves which shape: K not a multiple of 256, Q4_0 at more than one activation row and the
+    formats without a streaming arm take the shape-agnostic kernel; Q6_K rows that are not 16-byte multiples
+    (K = 1536) still stream, as whole tiles; Q4_0 streams at one activation row (stacked tiles at K = 1024)."""
+    run_gemv(cuda, oracle, synth.Q4_0, 64, 1024, 1, SEED + 30, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q4_0, 4099, 4096, 1, SEED + 37, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q4_0, 1001, 11008, 1, SEED + 38, random_payload=True, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q4_0, 64, 1024, 2, SEED + 39, expect_stream=False)
+    run_gemv(cuda, oracle, synth.Q5_K, 64, 1024, 1, SEED + 40, expect_stream=False)
     run_gemv(cuda, oracle, synth.Q8_0, 64, 96, 1, SEED + 31, expect_stream=False)
     run_gemv(cuda, oracle, synth.Q6_K, 4096, 1536, 1, SEED + 32, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q6_K, 1001, 1536, 8, SEED + 33, expect_stream=True)
@@ -169,6 +174,11 @@ def test_gemv_nonfinite_activation_gives_nan(cuda):
     x[100] = 0.0
     assert torch.isfinite(cuda.gemv(x, w, synth.Q4_K, 32, 512)).all()
     assert (cuda.gemv(torch.zeros(512, device="cuda"), w, synth.Q4_K, 32, 512) == 0).all()
+    w0 = dev(synth.weights(synth.Q4_0, 32, 512, SEED + 36))
+    x[100] = float("nan")
+    assert torch.isnan(cuda.gemv(x, w0, synth.Q4_0, 32, 512)).all()
+    x[100] = 0.0
+    assert torch.isfinite(cuda.gemv(x, w0, synth.Q4_0, 32, 512)).all()
 
 
 def test_gemv_empty_and_refusals(cuda):
