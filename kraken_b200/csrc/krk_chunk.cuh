@@ -62,19 +62,107 @@ __device__ __forceinline__ void decode_chunk<KRK_CUDA_Q6_K>(const uint8_t *row, 
     }
 }
 
-// The 5-bit formats decode element by element (they ride the shape-agnostic kernels only).
-#define KRK_CHUNK_BY_ELEMENT(WT_)                                                                                        \
-    template <>                                                                                                          \
-    __device__ __forceinline__ void decode_chunk<WT_>(const uint8_t *row, int64_t c, float (&v)[32]) {                    \
-        _Pragma("unroll") for (int k = 0; k < 32; k++) v[k] = decode_value<WT_>(row, c * 32 + k);                          \
+// The formats below follow decode_value<WT> operation for operation (so the values are the same bits) with
+// everything that is common to a chunk taken out of the loop over its 32 values.
+
+// src/quant.cpp:351-364
+template <>
+__device__ __forceinline__ void decode_chunk<KRK_CUDA_Q5_0>(const uint8_t *row, int64_t c, float (&v)[32]) {
+    const uint8_t *b = row + c * 22;
+    const float d = half_bits_to_float(b);
+    const uint32_t qh = (uint32_t)b[2] | ((uint32_t)b[3] << 8) | ((uint32_t)b[4] << 16) | ((uint32_t)b[5] << 24);
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        const uint8_t q = b[6 + j];
+        v[j] = __fmul_rn(d, (float)(((q & 0xF) | (int)(((qh >> j) & 1u) << 4)) - 16));
+        v[j + 16] = __fmul_rn(d, (float)(((q >> 4) | (int)(((qh >> (j + 16)) & 1u) << 4)) - 16));
     }
-KRK_CHUNK_BY_ELEMENT(KRK_CUDA_Q5_0)
-KRK_CHUNK_BY_ELEMENT(KRK_CUDA_Q5_1)
-KRK_CHUNK_BY_ELEMENT(KRK_CUDA_Q5_K)
-KRK_CHUNK_BY_ELEMENT(KRK_CUDA_Q2_K)
-KRK_CHUNK_BY_ELEMENT(KRK_CUDA_Q3_K)
-KRK_CHUNK_BY_ELEMENT(KRK_CUDA_IQ4_NL)
-#undef KRK_CHUNK_BY_ELEMENT
+}
+
+// src/quant.cpp:366-379
+template <>
+__device__ __forceinline__ void decode_chunk<KRK_CUDA_Q5_1>(const uint8_t *row, int64_t c, float (&v)[32]) {
+    const uint8_t *b = row + c * 24;
+    const float d = half_bits_to_float(b), m = half_bits_to_float(b + 2);
+    const uint32_t qh = (uint32_t)b[4] | ((uint32_t)b[5] << 8) | ((uint32_t)b[6] << 16) | ((uint32_t)b[7] << 24);
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        const uint8_t q = b[8 + j];
+        v[j] = __fadd_rn(__fmul_rn(d, (float)((q & 0xF) | (int)(((qh >> j) & 1u) << 4))), m);
+        v[j + 16] = __fadd_rn(__fmul_rn(d, (float)((q >> 4) | (int)(((qh >> (j + 16)) & 1u) << 4))), m);
+    }
+}
+
+// src/quant.cpp:462-489
+template <>
+__device__ __forceinline__ void decode_chunk<KRK_CUDA_Q5_K>(const uint8_t *row, int64_t c, float (&v)[32]) {
+    const uint8_t *b = row + (c >> 3) * 176;
+    const int cc = (int)(c & 7);
+    int sc, mn;
+    scale_min_k4(cc, b + 4, sc, mn);
+    const float dl = __fmul_rn(half_bits_to_float(b), (float)sc);
+    const float ml = __fmul_rn(half_bits_to_float(b + 2), (float)mn);
+    const uint8_t *q = b + 48 + 32 * (cc >> 1), *qh = b + 16;
+    const int shift = (cc & 1) * 4;
+#pragma unroll
+    for (int l = 0; l < 32; l++) {
+        const int quant = ((q[l] >> shift) & 0xF) + (((qh[l] >> cc) & 1) ? 16 : 0);
+        v[l] = __fsub_rn(__fmul_rn(dl, (float)quant), ml);
+    }
+}
+
+// src/quant.cpp:398-424
+template <>
+__device__ __forceinline__ void decode_chunk<KRK_CUDA_Q2_K>(const uint8_t *row, int64_t c, float (&v)[32]) {
+    const uint8_t *b = row + (c >> 3) * 84;
+    const int cc = (int)(c & 7), g = cc >> 2, j = cc & 3;
+    const float d = half_bits_to_float(b + 80), dmin = half_bits_to_float(b + 82);
+    const uint8_t s0 = b[8 * g + 2 * j], s1 = b[8 * g + 2 * j + 1];
+    const float dl0 = __fmul_rn(d, (float)(s0 & 0xF)), ml0 = __fmul_rn(dmin, (float)(s0 >> 4));
+    const float dl1 = __fmul_rn(d, (float)(s1 & 0xF)), ml1 = __fmul_rn(dmin, (float)(s1 >> 4));
+    const uint8_t *q = b + 16 + 32 * g;
+#pragma unroll
+    for (int l = 0; l < 32; l++) {
+        const int quant = (q[l] >> (2 * j)) & 3;
+        v[l] = __fsub_rn(__fmul_rn(l < 16 ? dl0 : dl1, (float)quant), l < 16 ? ml0 : ml1);
+    }
+}
+
+// src/quant.cpp:514-553
+template <>
+__device__ __forceinline__ void decode_chunk<KRK_CUDA_Q3_K>(const uint8_t *row, int64_t c, float (&v)[32]) {
+    const uint8_t *b = row + (c >> 3) * 110;
+    const int cc = (int)(c & 7), nn = cc >> 2, j = cc & 3;
+    const uint8_t *sr = b + 96;
+    float dl[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int is = 8 * nn + 2 * j + h;
+        const int lo = is < 8 ? (sr[is] & 0xF) : (sr[is - 8] >> 4);
+        const int hi = (sr[8 + (is & 3)] >> (2 * (is >> 2))) & 3;
+        dl[h] = __fmul_rn(half_bits_to_float(b + 108), (float)((lo | (hi << 4)) - 32));
+    }
+    const uint8_t *q = b + 32 + 32 * nn;
+#pragma unroll
+    for (int l = 0; l < 32; l++) {
+        const int quant = (int)((q[l] >> (2 * j)) & 3) - ((b[l] >> (4 * nn + j)) & 1 ? 0 : 4);
+        v[l] = __fmul_rn(l < 16 ? dl[0] : dl[1], (float)quant);
+    }
+}
+
+// src/quant.cpp:88-91, 566-575
+template <>
+__device__ __forceinline__ void decode_chunk<KRK_CUDA_IQ4_NL>(const uint8_t *row, int64_t c, float (&v)[32]) {
+    constexpr uint32_t grid[4] = {0xBFAD9881u, 0xF6EADDCFu, 0x26190D01u, 0x71594535u};
+    const uint8_t *b = row + c * 18;
+    const float d = half_bits_to_float(b);
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        const int lo = b[2 + j] & 0xF, hi = b[2 + j] >> 4;
+        v[j] = __fmul_rn(d, (float)(int)(int8_t)((grid[lo >> 2] >> (8 * (lo & 3))) & 0xFF));
+        v[j + 16] = __fmul_rn(d, (float)(int)(int8_t)((grid[hi >> 2] >> (8 * (hi & 3))) & 0xFF));
+    }
+}
 
 // Dot of chunk c of a weight row with the matching 32 activations (x 16-byte aligned).
 template <int WT>

@@ -1,5 +1,5 @@
-// Shape-agnostic decode GEMV: one warp per output row, lanes stride over 32-value chunks,
-// f32 accumulation, shuffle reduction. It takes every legal shape (any n_in that is a
+// Shape-agnostic decode GEMV: one warp per output row, lanes stride over 32-value chunks staged in shared
+// memory, f32 accumulation, shuffle reduction. It takes every legal shape (any n_in that is a
 // whole number of blocks, any alignment the format allows) and is the path for shapes the
 // streaming kernel does not address and for Q4_0. Same contract as gemv_kernel /
 // gemv_m_kernel of the reference (src/hip/kernels/gemm.hpp:76-167) with f32 activations.
@@ -20,42 +20,73 @@ struct GenericParams {
     int64_t n_in;
 };
 
+// A K segment of 1024 values is staged in shared memory before it is decoded: the activations of every row once
+// per block (chunk c at a pitch of 33 floats, so that the 32 lanes of a warp, one chunk each, read different
+// banks), and each warp's own weight-row bytes with 16-byte loads from the 16-byte boundary before them. The
+// per-value decode then reads shared memory instead of issuing byte loads to global memory. Which lane takes
+// which chunk, and the order of the additions, are those of the plain warp-per-row walk.
+constexpr int kSegValues = 1024, kSegChunks = kSegValues / 32, kXPitch = 33;
+constexpr int kSegBytesMax = kSegValues / 32 * 34;   // Q8_0 is the widest format per value
+
 template <int WT, int ROWS>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 gemv_generic_kernel(const __grid_constant__ GenericParams p) {
+    __shared__ float xs[ROWS][kSegChunks * kXPitch];
+    __shared__ __align__(16) uint8_t wbuf[kWarpsPerBlock][kSegBytesMax + 32];
     int m = 0;
     while (m + 1 < p.n_mat && (int)blockIdx.x >= p.block_begin[m + 1]) m++;
     const GemvMat &mat = p.mat[m];
-    const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)(blockIdx.x - p.block_begin[m]) * kWarpsPerBlock + (threadIdx.x >> 5);
-    if (row >= mat.n_out) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t row = (int64_t)(blockIdx.x - p.block_begin[m]) * kWarpsPerBlock + warp;
+    const bool live = row < mat.n_out;
     const int64_t n_chunks = p.n_in >> 5;
-    const uint8_t *wrow = mat.w + (size_t)row * row_bytes(WT, p.n_in);
+    const size_t rb = row_bytes(WT, p.n_in);
+    const uint8_t *wrow = mat.w + (size_t)(live ? row : 0) * rb;
+    const uint8_t *w_end = mat.w + (size_t)mat.n_out * rb;
+    constexpr int kChunksPerBlock = block_size(WT) / 32;
 
     float acc[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; r++) acc[r] = 0.0f;
 
-    for (int64_t c = lane; c < n_chunks; c += 32) {
-        float v[32];
-        decode_chunk<WT>(wrow, c, v);
-#pragma unroll
+    for (int64_t c0 = 0; c0 < n_chunks; c0 += kSegChunks) {
+        const int seg_chunks = (int)min((int64_t)kSegChunks, n_chunks - c0);
+        __syncthreads();   // everybody is done with the segment before
         for (int r = 0; r < ROWS; r++) {
-            if (r < p.rows) {
-                const float4 *xv = reinterpret_cast<const float4 *>(mat.x + (int64_t)r * p.n_in + c * 32);
-                float s = 0.0f;
-#pragma unroll
-                for (int k = 0; k < 8; k++) {
-                    const float4 t = xv[k];
-                    s = fmaf(v[4 * k + 0], t.x, s);
-                    s = fmaf(v[4 * k + 1], t.y, s);
-                    s = fmaf(v[4 * k + 2], t.z, s);
-                    s = fmaf(v[4 * k + 3], t.w, s);
+            if (r >= p.rows) break;
+            const float *xr = mat.x + (int64_t)r * p.n_in + c0 * 32;
+            for (int i = threadIdx.x; i < seg_chunks * 32; i += kWarpsPerBlock * 32) xs[r][(i >> 5) * kXPitch + (i & 31)] = xr[i];
+        }
+        const uint8_t *src = wrow + (size_t)(c0 / kChunksPerBlock) * block_bytes(WT);
+        const int lead = (int)(reinterpret_cast<uintptr_t>(src) & 15);
+        if (live) {
+            const int total = lead + seg_chunks / kChunksPerBlock * block_bytes(WT);
+            const uint8_t *base = src - lead;   // not before the matrix: its base is 16-byte aligned
+            for (int i = lane * 16; i < total; i += 32 * 16) {
+                if (base + i + 16 <= w_end) {
+                    *reinterpret_cast<uint4 *>(&wbuf[warp][i]) = *reinterpret_cast<const uint4 *>(base + i);
+                } else {
+                    for (int j = 0; j < 16 && base + i + j < w_end; j++) wbuf[warp][i + j] = base[i + j];
                 }
-                acc[r] += s;
+            }
+        }
+        __syncthreads();
+        if (live && lane < seg_chunks) {
+            float v[32];
+            decode_chunk<WT>(&wbuf[warp][lead], lane, v);
+#pragma unroll
+            for (int r = 0; r < ROWS; r++) {
+                if (r < p.rows) {
+                    const float *xv = &xs[r][lane * kXPitch];
+                    float s = 0.0f;
+#pragma unroll
+                    for (int k = 0; k < 32; k++) s = fmaf(v[k], xv[k], s);
+                    acc[r] += s;
+                }
             }
         }
     }
+    if (!live) return;
 #pragma unroll
     for (int r = 0; r < ROWS; r++) {
         float s = acc[r];
