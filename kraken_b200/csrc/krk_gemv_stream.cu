@@ -676,6 +676,48 @@ __device__ __forceinline__ void unit_q4_0(const uint8_t *rowA, const uint8_t *ro
     }
 }
 
+// The same eight blocks for 2..8 activation rows: the quants are centred first ((q + 0x78) ^ 0x80 is q - 8 as a
+// signed byte, no carry since q <= 15), low and high nibbles go to one k16 MMA each per column group, and the
+// columns carry the limbs of two activation rows as in the other general forms.
+template <int NG>
+__device__ __forceinline__ void unit_q4_0_rows(const uint8_t *rowA, const uint8_t *rowB, int kbase, const int8_t *const (&bp)[NG],
+                                               int t, Accum<NG> &acc) {
+#pragma unroll
+    for (int b = 0; b < 8; b++) {
+        uint32_t qa, qb;
+        float dA, dB;
+        if ((b & 1) == 0) {
+            const uint32_t *wa = reinterpret_cast<const uint32_t *>(rowA + 18 * b);
+            const uint32_t *wb = reinterpret_cast<const uint32_t *>(rowB + 18 * b);
+            const uint32_t a_first = wa[0], b_first = wb[0];
+            qa = t == 0 ? __byte_perm(a_first, wa[4], 0x5432) : wa[t];
+            qb = t == 0 ? __byte_perm(b_first, wb[4], 0x5432) : wb[t];
+            dA = half_lo(a_first);
+            dB = half_lo(b_first);
+        } else {
+            qa = reinterpret_cast<const uint32_t *>(rowA + 18 * b + 2)[t];
+            qb = reinterpret_cast<const uint32_t *>(rowB + 18 * b + 2)[t];
+            dA = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(rowA + 18 * b)));
+            dB = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(rowB + 18 * b)));
+        }
+        const uint32_t la = ((qa & 0x0F0F0F0Fu) + 0x78787878u) ^ 0x80808080u, lb = ((qb & 0x0F0F0F0Fu) + 0x78787878u) ^ 0x80808080u;
+        const uint32_t ha = (((qa >> 4) & 0x0F0F0F0Fu) + 0x78787878u) ^ 0x80808080u;
+        const uint32_t hb = (((qb >> 4) & 0x0F0F0F0Fu) + 0x78787878u) ^ 0x80808080u;
+#pragma unroll
+        for (int mg = 0; mg < NG; mg++) {
+            const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 4 * t);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 16 + 4 * t);
+            int cl[4], ch[4];
+            mma_s8_k16(cl, la, lb, b0);
+            mma_s8_k16(ch, ha, hb, b1);
+            acc.f[mg][0] = fmaf(dA, (float)(cl[0] + ch[0]), acc.f[mg][0]);
+            acc.f[mg][1] = fmaf(dA, (float)(cl[1] + ch[1]), acc.f[mg][1]);
+            acc.f[mg][2] = fmaf(dB, (float)(cl[2] + ch[2]), acc.f[mg][2]);
+            acc.f[mg][3] = fmaf(dB, (float)(cl[3] + ch[3]), acc.f[mg][3]);
+        }
+    }
+}
+
 // Four Q8_0 blocks. A block is a 2-byte scale then 32 quants, so blocks at an even index have
 // their quants 2 bytes off a word boundary: their lanes read the aligned words and lane t = 0
 // glues the two half words at the ends into one (the activation limbs are permuted to match).
@@ -814,7 +856,6 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     // STACK: several 16-row tiles per stage (p.tps of them); compiled apart so that the usual one-tile
     // form carries none of its index arithmetic.
     static_assert(!SINGLE || ((WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q4_0) && NG == 1), "the single-row forms are Q4_K and Q4_0");
-    static_assert(WT != KRK_CUDA_Q4_0 || SINGLE == 1, "Q4_0 has the single-row form only");
     const int tps = STACK ? p.tps : 1;
     using F = Fmt<WT>;
     using SmemT = Smem<NG>;
@@ -1065,7 +1106,9 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                         const uint8_t *rowA = tile0 + (size_t)su * p.unit_stride, *rowB = rowA + (size_t)8 * p.row_stride;
                         const int unit = ck * kConsumerWarps + su;
                         const int kbase = unit * F::unit_values;
-                        if (WT == KRK_CUDA_Q4_0) {
+                        if (WT == KRK_CUDA_Q4_0 && !SINGLE) {
+                            unit_q4_0_rows<NG>(rowA, rowB, kbase, bp, t, acc);
+                        } else if (WT == KRK_CUDA_Q4_0) {
                             unit_q4_0(rowA, rowB, bq + kbase, reinterpret_cast<const float *>(chunk_sum) + (kbase >> 5), t, acs);
                         } else if (SINGLE == 2) {
                             unit_q4_k_single(rowA, rowB, bf, t, acs);
@@ -1204,7 +1247,6 @@ template <int WT>
 bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t *smem_out, bool want_tma = false) {
     using F = Fmt<WT>;
     if (n_in % 256 != 0 || n_in > (1 << 20) || rows < 1 || rows > KRK_CUDA_MAX_ROWS) return false;
-    if (WT == KRK_CUDA_Q4_0 && rows != 1) return false;   // its unit carries one activation row: 2..8 rows take the warp-per-row kernel
     p.n_in = (int)n_in;
     p.units = (int)(n_in / F::unit_values);
     p.row_bytes = (int)row_bytes(WT, n_in);
@@ -1278,9 +1320,11 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
 template <int WT>
 int launch_rows(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
     constexpr bool kQ4K = WT == KRK_CUDA_Q4_K;
-    if constexpr (WT == KRK_CUDA_Q4_0) {   // one activation row only (setup_format refuses the others)
-        if (p.tps > 1) return launch_one<WT, 1, true, 1>(p, grid, smem, st);
-        return launch_one<WT, 1, false, 1>(p, grid, smem, st);
+    if constexpr (WT == KRK_CUDA_Q4_0) {
+        if (p.rows == 1) return p.tps > 1 ? launch_one<WT, 1, true, 1>(p, grid, smem, st) : launch_one<WT, 1, false, 1>(p, grid, smem, st);
+        if (p.rows <= 2) return p.tps > 1 ? launch_one<WT, 1, true, 0>(p, grid, smem, st) : launch_one<WT, 1, false, 0>(p, grid, smem, st);
+        if (p.rows <= 4) return p.tps > 1 ? launch_one<WT, 2, true, 0>(p, grid, smem, st) : launch_one<WT, 2, false, 0>(p, grid, smem, st);
+        return p.tps > 1 ? launch_one<WT, 4, true, 0>(p, grid, smem, st) : launch_one<WT, 4, false, 0>(p, grid, smem, st);
     } else {
         if (p.tps > 1) {
             if (kQ4K && p.rows == 1) return launch_one<WT, 1, true, kQ4K ? 2 : 0>(p, grid, smem, st);
