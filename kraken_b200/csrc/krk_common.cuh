@@ -272,12 +272,22 @@ int launch_flag_wait(const int *flags, int n, int epoch, cudaStream_t st);
 int launch_allgather_sum(float *const gather[], int *const flag[], int n_peers, int my_rank, int64_t slot_stride,
                          const float *part, float *out, int64_t n, cudaStream_t st);
 
-// Rows per granule the streaming kernel splits matrices of this type and width by (1 or 8), or 0 when
-// it does not address the shape (then the shape-agnostic kernels serve it).
-int stream_gran(int wt, int64_t n_in);
+// The stacked banks the matrices of a table lie in (entry matrix j of a pair lies in bank j; single matrices in
+// bank 0), `rows` weight rows each: with them a table launch stages weights with tensor copies out of one map per
+// bank instead of one copy per row.
+struct StreamBanks {
+    const uint8_t *base[2];
+    int64_t rows;
+};
+// Rows per granule the streaming kernel splits matrices of this type and width by (1, 8, or a whole tile when the
+// launch will use the banks' tensor maps), or 0 when it does not address the shape (then the shape-agnostic kernels
+// serve it).
+int stream_gran(int wt, int64_t n_in, bool banks = false);
 // The streaming kernel over a device-side table (one activation row per matrix; all matrices of type
-// wt and width n_in). Returns 1 when launched, 0 when the shape is not addressed, < 0 on error.
-int launch_gemv_stream_table(const StreamTable *table, int wt, int64_t n_in, int silu_pair, cudaStream_t st);
+// wt and width n_in; built with the granule of stream_gran(wt, n_in, banks != nullptr)). Returns 1 when launched, 0
+// when the shape is not addressed, < 0 on error.
+int launch_gemv_stream_table(const StreamTable *table, int wt, int64_t n_in, int silu_pair, const StreamBanks *banks,
+                             cudaStream_t st);
 
 int launch_silu_mul(float *out, const float *gate, const float *up, int64_t n, cudaStream_t st);
 int launch_gather_rows(float *dst, const float *src, const int32_t *rows, int64_t n_rows, int64_t n, cudaStream_t st);

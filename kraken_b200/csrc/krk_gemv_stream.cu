@@ -99,6 +99,10 @@ struct StreamParams {
     int total_gran;
     int gran_q, gran_r;   // total_gran = grid * gran_q + gran_r
     const StreamTable *dev_table;   // when set, matrices and granule prefix come from device memory
+    // Table launches with tensor copies: every matrix of the table lies inside one of two stacked banks (the gate
+    // and the up bank of an expert set), each described by ONE tensor map (wmap[0], wmap[1]) over all of its
+    // rows; a matrix is then a row offset into its bank.
+    const uint8_t *bank_base[2];
     // Fused all-gather (single-matrix launches of a row shard): y goes to slot `peer_offset` of the full
     // output row in every peer's memory (this GPU's own buffer included), then the peers are told.
     float *peer_y[KRK_CUDA_MAX_PEERS];
@@ -909,7 +913,14 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                 // still signals its full size
                 if (lane == 0) {
                     mbar_arrive_expect_tx(full, (uint32_t)p.box_bytes);
-                    tma_box(smem_u32(dst), &p.wmap[s.mat], s.row0, s.unit0 / p.tma_unit_div, full);
+                    if (p.dev_table) {
+                        // (a 64-bit division per stage, by the one lane that issues a copy per stage)
+                        const int bank = s.mat % p.step;
+                        const int row_off = (int)((size_t)(tv.mat[s.mat].w - p.bank_base[bank]) / (size_t)p.row_bytes);
+                        tma_box(smem_u32(dst), &p.wmap[bank], row_off + s.row0, s.unit0 / p.tma_unit_div, full);
+                    } else {
+                        tma_box(smem_u32(dst), &p.wmap[s.mat], s.row0, s.unit0 / p.tma_unit_div, full);
+                    }
                 }
             } else if (!p.whole_tiles) {
                 const uint32_t bytes = (uint32_t)s.n_units * F::unit_bytes;
@@ -1481,10 +1492,34 @@ int launch_fmt(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accum
 }
 
 template <int WT>
-int launch_table_fmt(const StreamTable *table, int64_t n_in, int silu_pair, cudaStream_t st) {
+int gran_fmt(int64_t n_in, bool banks) {
     StreamParams p;
     size_t smem = 0;
-    if (!setup_format<WT>(p, n_in, 1, silu_pair, &smem)) return 0;
+    static const bool no_tma = std::getenv("KRK_CUDA_GEMV_NO_TMA") != nullptr;
+    if (banks && Fmt<WT>::tma == 1 && !no_tma && setup_format<WT>(p, n_in, 1, 0, &smem, true) && p.use_tma == 1) return p.gran;
+    return setup_format<WT>(p, n_in, 1, 0, &smem) ? p.gran : 0;
+}
+
+template <int WT>
+int launch_table_fmt(const StreamTable *table, int64_t n_in, int silu_pair, const StreamBanks *banks, cudaStream_t st) {
+    StreamParams p;
+    size_t smem = 0;
+    // With the banks known, a stage arrives as one tensor copy out of the bank's map (the table must then have been
+    // built with the granule of stream_gran(..., true): rows split at tile boundaries).
+    static const bool no_tma = std::getenv("KRK_CUDA_GEMV_NO_TMA") != nullptr;
+    bool tma = false;
+    if (banks && Fmt<WT>::tma == 1 && !no_tma && setup_format<WT>(p, n_in, 1, silu_pair, &smem, true) && p.use_tma == 1) {
+        tma = true;
+        const int ku_max = p.units < kConsumerWarps ? p.units : kConsumerWarps;
+        for (int b = 0; b < p.step && tma; b++) {
+            p.bank_base[b] = banks->base[b];
+            tma = banks->base[b] && (reinterpret_cast<uintptr_t>(banks->base[b]) & 15) == 0 && banks->rows > 0 &&
+                  weight_map(&p.wmap[b], banks->base[b], banks->rows, p.row_bytes, Fmt<WT>::unit_bytes, kTileRows * p.tps, ku_max, 1);
+        }
+    }
+    if (!tma && !setup_format<WT>(p, n_in, 1, silu_pair, &smem)) return 0;
+    // the table was built with this granule whichever way the stages arrive (row copies take any granule)
+    if (banks) p.gran = gran_fmt<WT>(n_in, true);
     p.n_entries = 0;
     p.total_gran = 0;
     p.gran_q = p.gran_r = 0;
@@ -1544,13 +1579,6 @@ __global__ void __launch_bounds__(32) flag_wait_kernel(const int *flags, int n, 
     __threadfence_system();
 }
 
-template <int WT>
-int gran_fmt(int64_t n_in) {
-    StreamParams p;
-    size_t smem = 0;
-    return setup_format<WT>(p, n_in, 1, 0, &smem) ? p.gran : 0;
-}
-
 } // namespace
 
 int launch_gemv_stream(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accumulate, int silu_pair,
@@ -1568,12 +1596,13 @@ int launch_gemv_stream(const GemvMat *mats, int n_mat, int64_t n_in, int rows, i
     }
 }
 
-int launch_gemv_stream_table(const StreamTable *table, int wt, int64_t n_in, int silu_pair, cudaStream_t st) {
+int launch_gemv_stream_table(const StreamTable *table, int wt, int64_t n_in, int silu_pair, const StreamBanks *banks,
+                             cudaStream_t st) {
     switch (wt) {
-    case KRK_CUDA_Q4_K: return launch_table_fmt<KRK_CUDA_Q4_K>(table, n_in, silu_pair, st);
-    case KRK_CUDA_Q6_K: return launch_table_fmt<KRK_CUDA_Q6_K>(table, n_in, silu_pair, st);
-    case KRK_CUDA_Q8_0: return launch_table_fmt<KRK_CUDA_Q8_0>(table, n_in, silu_pair, st);
-    case KRK_CUDA_Q4_0: return launch_table_fmt<KRK_CUDA_Q4_0>(table, n_in, silu_pair, st);
+    case KRK_CUDA_Q4_K: return launch_table_fmt<KRK_CUDA_Q4_K>(table, n_in, silu_pair, banks, st);
+    case KRK_CUDA_Q6_K: return launch_table_fmt<KRK_CUDA_Q6_K>(table, n_in, silu_pair, banks, st);
+    case KRK_CUDA_Q8_0: return launch_table_fmt<KRK_CUDA_Q8_0>(table, n_in, silu_pair, banks, st);
+    case KRK_CUDA_Q4_0: return launch_table_fmt<KRK_CUDA_Q4_0>(table, n_in, silu_pair, banks, st);
     default: return 0;
     }
 }
@@ -1596,12 +1625,12 @@ int launch_flag_wait(const int *flags, int n, int epoch, cudaStream_t st) {
     return check_launch();
 }
 
-int stream_gran(int wt, int64_t n_in) {
+int stream_gran(int wt, int64_t n_in, bool banks) {
     switch (wt) {
-    case KRK_CUDA_Q4_K: return gran_fmt<KRK_CUDA_Q4_K>(n_in);
-    case KRK_CUDA_Q6_K: return gran_fmt<KRK_CUDA_Q6_K>(n_in);
-    case KRK_CUDA_Q8_0: return gran_fmt<KRK_CUDA_Q8_0>(n_in);
-    case KRK_CUDA_Q4_0: return gran_fmt<KRK_CUDA_Q4_0>(n_in);
+    case KRK_CUDA_Q4_K: return gran_fmt<KRK_CUDA_Q4_K>(n_in, banks);
+    case KRK_CUDA_Q6_K: return gran_fmt<KRK_CUDA_Q6_K>(n_in, banks);
+    case KRK_CUDA_Q8_0: return gran_fmt<KRK_CUDA_Q8_0>(n_in, banks);
+    case KRK_CUDA_Q4_0: return gran_fmt<KRK_CUDA_Q4_0>(n_in, banks);
     default: return 0;
     }
 }

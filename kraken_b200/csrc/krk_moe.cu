@@ -524,7 +524,12 @@ int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const f
     p.n_tok = (int)n_tok;
     const int picks = (int)(n_tok * k);
     // Streaming path: the same kernel as the dense decode GEMV, fed from device-side tables.
-    const int gran_gu = stream_gran(bank->wt_gate_up, bank->n_embd), gran_dn = stream_gran(bank->wt_down, bank->n_ff);
+    // gate and up experts are rows of two stacked banks: their table launch stages weights out of one tensor map each
+    StreamBanks gu_banks;
+    gu_banks.base[0] = p.gate;
+    gu_banks.base[1] = p.up;
+    gu_banks.rows = (int64_t)bank->n_local * bank->n_ff;
+    const int gran_gu = stream_gran(bank->wt_gate_up, bank->n_embd, true), gran_dn = stream_gran(bank->wt_down, bank->n_ff);
     if (gran_gu > 0 && gran_dn > 0 && picks <= kStreamTableEntries) {
         const bool fuse_route = !routed && n_expert <= kPlanRouteExperts && n_tok * 32 <= kPlanThreads;
         if (!routed && !fuse_route) {
@@ -542,9 +547,9 @@ int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const f
         note_launch();
         int rc = check_launch();
         if (rc != KRK_CUDA_OK) return rc;
-        rc = launch_gemv_stream_table(ta, bank->wt_gate_up, bank->n_embd, 1, st);
+        rc = launch_gemv_stream_table(ta, bank->wt_gate_up, bank->n_embd, 1, &gu_banks, st);
         if (rc < 0) return rc;
-        rc = launch_gemv_stream_table(tb, bank->wt_down, bank->n_ff, 0, st);
+        rc = launch_gemv_stream_table(tb, bank->wt_down, bank->n_ff, 0, nullptr, st);
         if (rc < 0) return rc;
         dim3 grid((unsigned)((bank->n_embd + 255) / 256), (unsigned)n_tok);
         moe_combine_kernel<<<grid, 256, 0, st>>>(p);
