@@ -257,6 +257,10 @@ moe_combine_kernel(const __grid_constant__ MoeParams p) {
     __shared__ int s_pick[kMaxK];
     __shared__ float s_w[kMaxK];
     __shared__ int s_n;
+    // programmatic dependent launch: this grid may start while the one before it drains (it reads nothing before
+    // that grid is complete), and lets the one after it start the same way
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int t = blockIdx.y;
     if (threadIdx.x < 32) {
         // lane s looks at slot s of this token: its place among the slots held here, by expert id
@@ -303,6 +307,8 @@ moe_plan_kernel(const __grid_constant__ MoeParams p, StreamTable *gate_up, Strea
     __shared__ int key[kStreamTableEntries];
     __shared__ float prob[KRK_CUDA_MAX_ROWS][kPlanRouteExperts];
     __shared__ float wsel[KRK_CUDA_MAX_ROWS][kMaxK];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // (see moe_combine_kernel)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (logits) {
         const int t = threadIdx.x >> 5;
         if (t < p.n_tok)
@@ -348,6 +354,22 @@ moe_plan_kernel(const __grid_constant__ MoeParams p, StreamTable *gate_up, Strea
         gate_up->total_gran = n * gu;
         down->total_gran = n * dn;
     }
+}
+
+// A launch that may overlap the tail of the kernel before it in the stream (the kernel waits for that grid itself).
+template <class... KArgs, class... Args>
+cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 } // namespace
@@ -540,11 +562,16 @@ int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const f
         uint8_t *tables = static_cast<uint8_t *>(workspace) + moe_float_bytes(bank, k, n_tok);
         StreamTable *ta = reinterpret_cast<StreamTable *>(tables);
         StreamTable *tb = reinterpret_cast<StreamTable *>(tables + ((sizeof(StreamTable) + 255) & ~(size_t)255));
-        moe_plan_kernel<<<1, kPlanThreads, 0, st>>>(p, ta, tb, bank->wt_gate_up, bank->wt_down,
-                                                     row_bytes(bank->wt_gate_up, bank->n_embd),
-                                                     row_bytes(bank->wt_down, bank->n_ff), gran_gu, gran_dn,
-                                                     fuse_route ? logits : nullptr, n_expert);
+        cudaError_t le = launch_overlapped(moe_plan_kernel, dim3(1), dim3(kPlanThreads), st, p, ta, tb, bank->wt_gate_up,
+                                           bank->wt_down, row_bytes(bank->wt_gate_up, bank->n_embd),
+                                           row_bytes(bank->wt_down, bank->n_ff), gran_gu, gran_dn,
+                                           fuse_route ? logits : (const float *)nullptr, n_expert);
         note_launch();
+        if (le != cudaSuccess) {
+            note_cuda_error(le);
+            (void)cudaGetLastError();
+            return KRK_CUDA_ELAUNCH;
+        }
         int rc = check_launch();
         if (rc != KRK_CUDA_OK) return rc;
         rc = launch_gemv_stream_table(ta, bank->wt_gate_up, bank->n_embd, 1, &gu_banks, st);
@@ -552,8 +579,13 @@ int launch_moe_ffn_generic(float *y, const float *x, const int32_t *ids, const f
         rc = launch_gemv_stream_table(tb, bank->wt_down, bank->n_ff, 0, nullptr, st);
         if (rc < 0) return rc;
         dim3 grid((unsigned)((bank->n_embd + 255) / 256), (unsigned)n_tok);
-        moe_combine_kernel<<<grid, 256, 0, st>>>(p);
+        le = launch_overlapped(moe_combine_kernel, grid, dim3(256), st, p);
         note_launch();
+        if (le != cudaSuccess) {
+            note_cuda_error(le);
+            (void)cudaGetLastError();
+            return KRK_CUDA_ELAUNCH;
+        }
         return check_launch();
     }
     if (!routed) {
