@@ -529,7 +529,7 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
     ms_full = reduce_max(timed(torch, head_call, 60, barrier, variants=n_rep))
     ms_local = reduce_max(timed(torch, head_local, 60, barrier, variants=n_rep))
     ms_full_host = reduce_max(timed(torch, head_call, 60, barrier))
-    ms_peer = ms_peer_host = ms_c_nccl = ms_c_gather = None
+    ms_peer = ms_peer_host = ms_peer_chain = ms_c_nccl = ms_c_gather = None
     if world > 1 and count * world == n_out:
         # the same through the C ABI: GEMV into its slot of a persistent row + in-place ncclAllGather
         # (krk_cuda_shard_allgather), and the collective alone, so that the limiter is a number
@@ -557,6 +557,10 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
             return peer.forward(x)
         ms_peer = reduce_max(timed(torch, peer_call, 60, barrier, variants=n_rep if n_rep % 2 == 0 else 2 * n_rep))
         ms_peer_host = reduce_max(timed(torch, peer_call, 60, barrier))
+        # the same steps captured back to back into ONE graph: consecutive launches then overlap their boundaries
+        # (programmatic dependent launch), which separate one-kernel graphs cannot do across graph launches
+        nv = n_rep if n_rep % 2 == 0 else 2 * n_rep
+        ms_peer_chain = reduce_max(timed(torch, peer_call, 6 * nv, barrier, variants=nv, chain=True))
         torch.cuda.synchronize()
         if capi.device_status() != 0:
             raise RuntimeError("a bounded wait of the fused all-gather gave up")
@@ -577,6 +581,7 @@ def sharded_extra(torch, dist, capi, gen, rank, world, barrier, reduce_max):
         "ms_nccl_all_gather_alone": None if ms_c_gather is None else round(ms_c_gather, 5),
         "ms_per_token_peer_store_fused": None if ms_peer is None else round(ms_peer, 5),
         "ms_per_token_peer_store_fused_host_launched": None if ms_peer_host is None else round(ms_peer_host, 5),
+        "ms_per_token_peer_store_fused_one_graph": None if ms_peer_chain is None else round(ms_peer_chain, 5),
         "weight_gbps_peer_store_fused": None if ms_peer is None else round(n_out * synth.row_bytes(synth.Q6_K, n_in) / (ms_peer * 1e-3) / 1e9, 1),
         "weight_gbps_all_gpus": round(wbytes / (ms_full * 1e-3) / 1e9, 1),
         "weight_gbps_gemv_only": round(wbytes / (ms_local * 1e-3) / 1e9, 1),
