@@ -69,6 +69,8 @@ template <int WT> struct Fmt;
 template <> struct Fmt<KRK_CUDA_Q4_K> { static constexpr int unit_values = 256, unit_bytes = 144, stride_mod = 32, tma = 1; };
 template <> struct Fmt<KRK_CUDA_Q6_K> { static constexpr int unit_values = 256, unit_bytes = 210, stride_mod = 16, tma = 2; };
 template <> struct Fmt<KRK_CUDA_Q8_0> { static constexpr int unit_values = 128, unit_bytes = 136, stride_mod = 16, tma = 0; };
+// Q5_K: Q4_K's header and nibbles with 32 bytes of fifth bits between them (src/quant.cpp:462-489).
+template <> struct Fmt<KRK_CUDA_Q5_K> { static constexpr int unit_values = 256, unit_bytes = 176, stride_mod = 32, tma = 1; };
 // Q4_0: eight 18-byte blocks are 144 bytes, the size of a Q4_K unit, so the stages are laid out the same way.
 template <> struct Fmt<KRK_CUDA_Q4_0> { static constexpr int unit_values = 256, unit_bytes = 144, stride_mod = 16, tma = 1; };
 
@@ -233,7 +235,7 @@ template <int WT>
 __host__ __device__ inline int plane_bytes(int n_in, int rows) { return align_up(rows * 3 * plane_stride(n_in), 128); }
 template <int WT>
 __host__ __device__ inline int chunk_sum_bytes(int n_in, int rows) {   // [row][4 limbs][n_in / 32] s8
-    return (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q4_0) ? align_up(rows * (n_in / 32) * 4, 128) : 0;   // Q4_0: [row][n_in / 32] f32
+    return (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q5_K || WT == KRK_CUDA_Q4_0) ? align_up(rows * (n_in / 32) * 4, 128) : 0;   // Q4_0: [row][n_in / 32] f32
 }
 
 // ---- the walk over this CTA's stages: identical in the producer and in the consumers -------------
@@ -400,7 +402,7 @@ __device__ __forceinline__ void quantize_slice(const float (&f)[Fmt<WT>::unit_va
         total += __shfl_xor_sync(0xFFFFFFFFu, total, 2);
         if ((lane & 3) == 0) reinterpret_cast<float *>(sums)[k0 >> 5] = (float)total;   // |sum| < 2^28
     }
-    if (WT == KRK_CUDA_Q4_K) {
+    if (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q5_K) {
         // a 32-value chunk is held by 4 consecutive lanes; |sum| <= 32 * 127 * 2^16 < 2^28
         total += __shfl_xor_sync(0xFFFFFFFFu, total, 1);
         total += __shfl_xor_sync(0xFFFFFFFFu, total, 2);
@@ -513,11 +515,19 @@ __device__ __forceinline__ void lane_planes(const int8_t *planes, const int8_t *
     }
 }
 
-template <int NG>
+// FIFTH: the Q5_K super-block: 32 bytes after the header whose bit c is the fifth quant bit of chunk c's value at the
+// same position; the nibbles follow them.
+template <int NG, bool FIFTH>
 __device__ __forceinline__ void unit_q4_k(const uint8_t *rowA, const uint8_t *rowB, int kbase, const int8_t *const (&bp)[NG],
                                           const int8_t *const (&sp)[NG], int t, Accum<NG> &acc) {
+    constexpr int kQs = FIFTH ? 48 : 16;
     const uint4 hA = *reinterpret_cast<const uint4 *>(rowA);
     const uint4 hB = *reinterpret_cast<const uint4 *>(rowB);
+    uint2 fa = make_uint2(0u, 0u), fb = make_uint2(0u, 0u);
+    if (FIFTH) {
+        fa = *reinterpret_cast<const uint2 *>(rowA + 16 + 8 * t);
+        fb = *reinterpret_cast<const uint2 *>(rowB + 16 + 8 * t);
+    }
     // 6-bit scales and mins of the 8 chunks, four per word (src/quant.cpp:427-435 done bytewise)
     const uint32_t scA[2] = {hA.y & 0x3F3F3F3Fu, (hA.w & 0x0F0F0F0Fu) | ((hA.y >> 2) & 0x30303030u)};
     const uint32_t scB[2] = {hB.y & 0x3F3F3F3Fu, (hB.w & 0x0F0F0F0Fu) | ((hB.y >> 2) & 0x30303030u)};
@@ -530,13 +540,19 @@ __device__ __forceinline__ void unit_q4_k(const uint8_t *rowA, const uint8_t *ro
         for (int j = 0; j < 4; j++) I[mg][j] = 0;
 #pragma unroll
     for (int p = 0; p < 4; p++) {
-        const uint2 qa = *reinterpret_cast<const uint2 *>(rowA + 16 + 32 * p + 8 * t);
-        const uint2 qb = *reinterpret_cast<const uint2 *>(rowB + 16 + 32 * p + 8 * t);
+        const uint2 qa = *reinterpret_cast<const uint2 *>(rowA + kQs + 32 * p + 8 * t);
+        const uint2 qb = *reinterpret_cast<const uint2 *>(rowB + kQs + 32 * p + 8 * t);
 #pragma unroll
         for (int nib = 0; nib < 2; nib++) {
             const int c = 2 * p + nib;
-            const uint32_t a0 = (qa.x >> (4 * nib)) & 0x0F0F0F0Fu, a1 = (qb.x >> (4 * nib)) & 0x0F0F0F0Fu;
-            const uint32_t a2 = (qa.y >> (4 * nib)) & 0x0F0F0F0Fu, a3 = (qb.y >> (4 * nib)) & 0x0F0F0F0Fu;
+            uint32_t a0 = (qa.x >> (4 * nib)) & 0x0F0F0F0Fu, a1 = (qb.x >> (4 * nib)) & 0x0F0F0F0Fu;
+            uint32_t a2 = (qa.y >> (4 * nib)) & 0x0F0F0F0Fu, a3 = (qb.y >> (4 * nib)) & 0x0F0F0F0Fu;
+            if (FIFTH) {   // bit c of the mask bytes becomes bit 4 of the quants (0..31: still positive as s8)
+                a0 |= (c < 4 ? fa.x << (4 - c) : fa.x >> (c - 4)) & 0x10101010u;
+                a1 |= (c < 4 ? fb.x << (4 - c) : fb.x >> (c - 4)) & 0x10101010u;
+                a2 |= (c < 4 ? fa.y << (4 - c) : fa.y >> (c - 4)) & 0x10101010u;
+                a3 |= (c < 4 ? fb.y << (4 - c) : fb.y >> (c - 4)) & 0x10101010u;
+            }
             const int sa = (scA[c >> 2] >> (8 * (c & 3))) & 0xFF, sb = (scB[c >> 2] >> (8 * (c & 3))) & 0xFF;
 #pragma unroll
             for (int mg = 0; mg < NG; mg++) {
@@ -1125,8 +1141,8 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                             unit_q4_k_single(rowA, rowB, bf, t, acs);
                         } else if (SINGLE == 1) {
                             unit_q4_k_single(rowA, rowB, load_bfrag(bq + kbase, sq + (kbase >> 5), t), t, acs);
-                        } else if (WT == KRK_CUDA_Q4_K) {
-                            unit_q4_k<NG>(rowA, rowB, kbase, bp, sp, t, acc);
+                        } else if (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q5_K) {
+                            unit_q4_k<NG, WT == KRK_CUDA_Q5_K>(rowA, rowB, kbase, bp, sp, t, acc);
                         } else if (WT == KRK_CUDA_Q8_0) {
                             unit_q8_0<NG>(rowA, rowB, kbase, bp, t, acc);
                         } else {
@@ -1179,7 +1195,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                      o[mg].y = fmaf(wo0, acc.f[mg][0], wo1 * acc.f[mg][1]);   // row g,   odd
                      o[mg].z = fmaf(we0, acc.f[mg][2], we1 * acc.f[mg][3]);   // row g+8, even
                      o[mg].w = fmaf(wo0, acc.f[mg][2], wo1 * acc.f[mg][3]);   // row g+8, odd
-                     if (WT == KRK_CUDA_Q4_K) {
+                     if (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q5_K) {
                          o[mg].x -= fmaf(me0, acc.m[mg][0], me1 * acc.m[mg][1]);
                          o[mg].y -= fmaf(mo0, acc.m[mg][0], mo1 * acc.m[mg][1]);
                          o[mg].z -= fmaf(me0, acc.m[mg][2], me1 * acc.m[mg][3]);
@@ -1592,6 +1608,7 @@ int launch_gemv_stream(const GemvMat *mats, int n_mat, int64_t n_in, int rows, i
     case KRK_CUDA_Q6_K: return launch_fmt<KRK_CUDA_Q6_K>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q8_0: return launch_fmt<KRK_CUDA_Q8_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q4_0: return launch_fmt<KRK_CUDA_Q4_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
+    case KRK_CUDA_Q5_K: return launch_fmt<KRK_CUDA_Q5_K>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     default: return 0;   // the other formats take the shape-agnostic kernel
     }
 }
@@ -1603,6 +1620,7 @@ int launch_gemv_stream_table(const StreamTable *table, int wt, int64_t n_in, int
     case KRK_CUDA_Q6_K: return launch_table_fmt<KRK_CUDA_Q6_K>(table, n_in, silu_pair, banks, st);
     case KRK_CUDA_Q8_0: return launch_table_fmt<KRK_CUDA_Q8_0>(table, n_in, silu_pair, banks, st);
     case KRK_CUDA_Q4_0: return launch_table_fmt<KRK_CUDA_Q4_0>(table, n_in, silu_pair, banks, st);
+    case KRK_CUDA_Q5_K: return launch_table_fmt<KRK_CUDA_Q5_K>(table, n_in, silu_pair, banks, st);
     default: return 0;
     }
 }
@@ -1613,6 +1631,7 @@ int launch_gemv_stream_peers(const GemvMat &mat, int64_t n_in, int rows, const P
     case KRK_CUDA_Q6_K: return launch_peers_fmt<KRK_CUDA_Q6_K>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q8_0: return launch_peers_fmt<KRK_CUDA_Q8_0>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q4_0: return launch_peers_fmt<KRK_CUDA_Q4_0>(mat, n_in, rows, ps, st);
+    case KRK_CUDA_Q5_K: return launch_peers_fmt<KRK_CUDA_Q5_K>(mat, n_in, rows, ps, st);
     default: return 0;
     }
 }
@@ -1631,6 +1650,7 @@ int stream_gran(int wt, int64_t n_in, bool banks) {
     case KRK_CUDA_Q6_K: return gran_fmt<KRK_CUDA_Q6_K>(n_in, banks);
     case KRK_CUDA_Q8_0: return gran_fmt<KRK_CUDA_Q8_0>(n_in, banks);
     case KRK_CUDA_Q4_0: return gran_fmt<KRK_CUDA_Q4_0>(n_in, banks);
+    case KRK_CUDA_Q5_K: return gran_fmt<KRK_CUDA_Q5_K>(n_in, banks);
     default: return 0;
     }
 }

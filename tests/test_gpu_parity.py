@@ -152,13 +152,17 @@ def test_config4_q6_k_head_slice_and_linearity(cuda, oracle):
 def test_path_selection(cuda, oracle):
     """Which kernel serves which shape: K not a multiple of 256 and the formats without a streaming arm take the
     shape-agnostic kernel; Q6_K rows that are not 16-byte multiples
-    (K = 1536) still stream, as whole tiles; Q4_0 streams (stacked tiles at K = 1024)."""
+    (K = 1536) still stream, as whole tiles; Q4_0 and Q5_K stream (stacked tiles at K = 1024)."""
     run_gemv(cuda, oracle, synth.Q4_0, 64, 1024, 1, SEED + 30, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q4_0, 4099, 4096, 1, SEED + 37, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q4_0, 1001, 11008, 1, SEED + 38, random_payload=True, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q4_0, 64, 1024, 2, SEED + 39, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q4_0, 333, 4096, 7, SEED + 41, random_payload=True, expect_stream=True)
-    run_gemv(cuda, oracle, synth.Q5_K, 64, 1024, 1, SEED + 40, expect_stream=False)
+    run_gemv(cuda, oracle, synth.Q5_K, 64, 1024, 1, SEED + 40, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q5_K, 1001, 4096, 1, SEED + 42, random_payload=True, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q5_K, 333, 4096, 8, SEED + 43, random_payload=True, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q5_K, 77, 11008, 2, SEED + 45, random_payload=True, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q5_0, 64, 1024, 1, SEED + 44, expect_stream=False)
     run_gemv(cuda, oracle, synth.Q8_0, 64, 96, 1, SEED + 31, expect_stream=False)
     run_gemv(cuda, oracle, synth.Q6_K, 4096, 1536, 1, SEED + 32, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q6_K, 1001, 1536, 8, SEED + 33, expect_stream=True)
