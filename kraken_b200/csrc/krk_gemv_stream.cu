@@ -58,7 +58,8 @@ constexpr int kMaxStages = 8;
 constexpr int kSmemLimit = 113 * 1024;           // two CTAs per SM (228 KB, 1 KB reserved per CTA)
 constexpr int kSmemWhole = 227 * 1024;
 constexpr int kPlanePad = 32;                     // bytes between limb planes beyond n_in: spreads the B-fragment loads over the banks
-constexpr float kFixedOne = 8323072.0f;           // 127 * 65536: |X| <= this keeps every limb in s8
+constexpr float kFixedOne = 4194303.0f;           // 2^22 - 1: every limb stays in s8 and X = rint(x / s) is one FMA against
+                                                  // the bits of 1.5 * 2^23 (no conversion instruction)
 constexpr long long kWaitCycles = 4000000000LL;   // ~2 s at boost clock, then give up
 
 template <int WT> struct Fmt;
@@ -348,7 +349,7 @@ __device__ __forceinline__ void quantize_slice(const float (&f)[Fmt<WT>::unit_va
         uint32_t z[4];   // byte 0: limb 2 (weight 1), byte 1: limb 1 (256), byte 2: limb 0 (65536)
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const int X = __float2int_rn(f[j4 + j] * inv);
+            const int X = __float_as_int(fmaf(f[j4 + j], inv, kMagic)) - 0x4B400000;   // |x * inv| < 2^22
             total += X;
             z[j] = limbs3(X);
         }
@@ -417,9 +418,11 @@ __device__ __forceinline__ void quantize_slice(const float (&f)[Fmt<WT>::unit_va
     }
 }
 
+// (the running maximum is kept on the bit patterns of |x|: they order like the values, and anything above the
+// largest finite pattern is an infinity or a NaN)
 template <int WT>
 __device__ __forceinline__ void load_slice(const float *__restrict__ x, int k0, float (&f)[Fmt<WT>::unit_values / 32],
-                                           float &mx, int &bad) {
+                                           uint32_t &mxb) {
     constexpr int PER = Fmt<WT>::unit_values / 32;
 #pragma unroll
     for (int j = 0; j < PER; j += 4) {
@@ -427,11 +430,7 @@ __device__ __forceinline__ void load_slice(const float *__restrict__ x, int k0, 
         f[j] = v.x; f[j + 1] = v.y; f[j + 2] = v.z; f[j + 3] = v.w;
     }
 #pragma unroll
-    for (int j = 0; j < PER; j++) {
-        const float a = fabsf(f[j]);
-        mx = fmaxf(mx, a);
-        bad |= !(a <= FLT_MAX);
-    }
+    for (int j = 0; j < PER; j++) mxb = max(mxb, __float_as_uint(f[j]) & 0x7FFFFFFFu);
 }
 
 // All slices this warp will read of one activation row; returns the row's scale for this warp.
@@ -443,22 +442,20 @@ __device__ __forceinline__ float prepare_x_row(const float *__restrict__ xr, con
     // the first two slices stay in registers between the max and the quantisation (K <= 4096 for
     // 256-value units); any further ones are read twice
     float held[kHeld][PER];
-    float mx = 0.0f;
-    int bad = 0;
+    uint32_t mxb = 0u;
 #pragma unroll
     for (int j = 0; j < kHeld; j++) {
         const int u = wid + j * kConsumerWarps;
-        if (u < p.units) load_slice<WT>(xr, u * UV + lane * PER, held[j], mx, bad);
+        if (u < p.units) load_slice<WT>(xr, u * UV + lane * PER, held[j], mxb);
     }
     for (int u = wid + kHeld * kConsumerWarps; u < p.units; u += kConsumerWarps) {
         float f[PER];
-        load_slice<WT>(xr, u * UV + lane * PER, f, mx, bad);
+        load_slice<WT>(xr, u * UV + lane * PER, f, mxb);
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-        bad |= __shfl_xor_sync(0xFFFFFFFFu, bad, o);
-    }
+    for (int o = 16; o > 0; o >>= 1) mxb = max(mxb, __shfl_xor_sync(0xFFFFFFFFu, mxb, o));
+    const bool bad = mxb > 0x7F7FFFFFu;
+    const float mx = __uint_as_float(mxb);
     const float inv = (mx > 0.0f && !bad) ? __fdiv_rn(kFixedOne, mx) : 0.0f;
 #pragma unroll
     for (int j = 0; j < kHeld; j++) {
@@ -468,9 +465,8 @@ __device__ __forceinline__ float prepare_x_row(const float *__restrict__ xr, con
     }
     for (int u = wid + kHeld * kConsumerWarps; u < p.units; u += kConsumerWarps) {
         float f[PER];
-        float m2 = 0.0f;
-        int b2 = 0;
-        load_slice<WT>(xr, u * UV + lane * PER, f, m2, b2);
+        uint32_t m2 = 0u;
+        load_slice<WT>(xr, u * UV + lane * PER, f, m2);
         quantize_slice<WT>(f, inv, u * UV + lane * PER, p0, p0 + ps, p0 + 2 * ps, sums, n_chunks, lane);
     }
     return bad ? __int_as_float(0x7FC00000) : __fdiv_rn(mx, kFixedOne);
