@@ -54,7 +54,8 @@ __host__ __device__ constexpr int red_slots(int ng) { return ng == 1 ? 4 : ng ==
 constexpr int kMaxRedSlots = 4;
 constexpr int kMaxStack = 4;      // 16-row tiles per stage at most
 constexpr int kTileRows = 16;                     // the M of the MMA
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 4;                    // measured: four stages in flight per CTA stream a large Q4_K matrix at 0.89 of the
+                                                  // copy bandwidth, five (all that fit) at 0.86, three at 0.86
 constexpr int kSmemLimit = 113 * 1024;           // two CTAs per SM (228 KB, 1 KB reserved per CTA)
 constexpr int kSmemWhole = 227 * 1024;
 constexpr int kPlanePad = 32;                     // bytes between limb planes beyond n_in: spreads the B-fragment loads over the banks
