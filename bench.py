@@ -403,7 +403,7 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(per_step_ms, 5), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "s8 quants x 24-bit fixed-point activations, f32 scales",
+            "scaling": "weak", "vs_baseline": None, "dtype": "s8 quants x 23-bit fixed-point activations, f32 scales",
             "data": "synthetic",
             "config": workload_config(args.layers, world),
             "run": {"launch": "host launches" if args.no_graph else "CUDA graph replay of the step's launches",

@@ -20,8 +20,8 @@
 //    tensor cores as EXACT integer arithmetic: the quants are fed as s8 fragments straight from
 //    the packed bytes (one AND per four nibbles) to mma.sync m16n8k32 / m16n8k16 (s8 x s8 -> s32),
 //    16 output rows at a time, and the activation is held as three signed 8-bit limbs of a
-//    24-bit fixed-point number (x ~ s * (l0*65536 + l1*256 + l2)), one limb per MMA column.
-//    The products and sums are exact; the only rounding is the 24-bit quantisation of x
+//    23-bit fixed-point number (x ~ s * (l0*65536 + l1*256 + l2), |X| < 2^22), one limb per MMA column.
+//    The products and sums are exact; the only rounding is the 23-bit quantisation of x
 //    (relative to max|x|, i.e. f32-mantissa sized) and the final f32 scale arithmetic, so the
 //    result sits well inside the 1e-4 * ||w_row|| * ||x|| bound. Sub-block scales are applied
 //    to the s32 partial sums in integer arithmetic, block scales in f32.
