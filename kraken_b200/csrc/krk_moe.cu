@@ -13,6 +13,20 @@ namespace {
 constexpr int kMaxExperts = 1024;
 constexpr int kMaxK = 32;
 
+// The sum of v[0..n) in index order (the order the host adds them in), by a whole warp: each lane fetches one value
+// of every 32 and the running sum takes them lane by lane through shuffles, so the chain is 4-cycle additions
+// instead of one shared-memory round trip per term. Every lane returns the sum.
+__device__ __forceinline__ float ordered_sum(const float *v, int n, int lane) {
+    float sum = 0.0f;
+    for (int base = 0; base < n; base += 32) {
+        const float mine = base + lane < n ? v[base + lane] : 0.0f;
+        const int m = min(32, n - base);
+#pragma unroll 8
+        for (int i = 0; i < m; i++) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, mine, i));
+    }
+    return sum;
+}
+
 // One warp per token. Softmax as the reference computes it: subtract the maximum, sum the
 // exponentials in expert order, multiply by the reciprocal (src/engine.cpp:11704-11713);
 // then k picks of the largest probability, strict '>' so equal probabilities keep the lower
@@ -26,10 +40,7 @@ __device__ __forceinline__ void route_token(int32_t *__restrict__ ids, float *__
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
     for (int e = lane; e < n_expert; e += 32) prob[e] = exp_as_host(__fsub_rn(lg[e], mx));
     __syncwarp();
-    float sum = 0.0f;
-    if (lane == 0)
-        for (int e = 0; e < n_expert; e++) sum = __fadd_rn(sum, prob[e]);
-    sum = __shfl_sync(0xFFFFFFFFu, sum, 0);
+    const float sum = ordered_sum(prob, n_expert, lane);
     const float inv = sum > 0.0f ? __fdiv_rn(1.0f, sum) : 0.0f;
     for (int e = lane; e < n_expert; e += 32) prob[e] = __fmul_rn(prob[e], inv);
     __syncwarp();
@@ -91,10 +102,7 @@ router_softmax_kernel(float *__restrict__ probs, const float *__restrict__ logit
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
     for (int e = lane; e < n_expert; e += 32) pr[e] = exp_as_host(__fsub_rn(lg[e], mx));
     __syncwarp();
-    float sum = 0.0f;
-    if (lane == 0)
-        for (int e = 0; e < n_expert; e++) sum = __fadd_rn(sum, pr[e]);   // in expert order, as the host adds them
-    sum = __shfl_sync(0xFFFFFFFFu, sum, 0);
+    const float sum = ordered_sum(pr, n_expert, lane);   // in expert order, as the host adds them
     const float inv = sum > 0.0f ? __fdiv_rn(1.0f, sum) : 0.0f;
     for (int e = lane; e < n_expert; e += 32) pr[e] = __fmul_rn(pr[e], inv);
 }
@@ -288,8 +296,16 @@ moe_combine_kernel(const __grid_constant__ MoeParams p) {
     const int n = s_n;
     for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < p.n_embd;
          j += (int64_t)gridDim.x * blockDim.x) {
+        // the loads of a batch of eight go out together; the additions keep their order
         float acc = 0.0f;
-        for (int i = 0; i < n; i++) acc = __fadd_rn(acc, __fmul_rn(s_w[i], p.d[(int64_t)s_pick[i] * p.n_embd + j]));
+        for (int i0 = 0; i0 < n; i0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = i0 + i < n ? p.d[(int64_t)s_pick[i0 + i] * p.n_embd + j] : 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                if (i0 + i < n) acc = __fadd_rn(acc, __fmul_rn(s_w[i0 + i], v[i]));
+        }
         p.y[(int64_t)t * p.n_embd + j] = acc;
     }
 }
