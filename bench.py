@@ -800,7 +800,7 @@ def prefill_extra(torch, capi, gen):
 # ncu dram__bytes_read.sum + dram__bytes_write.sum of the streaming kernel over the launches of one layer (a one-layer
 # run of this file under ncu); the bench line divides it by the launches per layer. Re-measure when the kernel changes.
 TRAFFIC_BYTES_PER_LAYER = None                # four launches: not captured for the current kernel
-TRAFFIC_BYTES_PER_LAYER_GROUPED = 91349504    # three launches: 11,611,648 + 53,227,008 (gate and up) + 26,510,848
+TRAFFIC_BYTES_PER_LAYER_GROUPED = 91480064    # three launches, read + write: 11,609,344 + 53,361,664 (gate and up) + 26,509,056
 
 
 # ---- CPU arms ---------------------------------------------------------------------------------------
