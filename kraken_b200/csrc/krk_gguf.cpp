@@ -140,7 +140,11 @@ bool parse(File &f, std::string &err) {
     f.version = c.get<uint32_t>();
     if (f.version != 2 && f.version != 3) { err = "unsupported GGUF version " + std::to_string(f.version); return false; }
     const uint64_t n_tensors = c.get<uint64_t>(), n_kv = c.get<uint64_t>();
-    if (!c.ok || n_tensors > (1u << 24) || n_kv > (1u << 24)) { err = "truncated or implausible header"; return false; }
+    // (a tensor entry takes at least 24 bytes of the file and a key/value at least 13: no count can exceed that)
+    if (!c.ok || n_tensors > (1u << 24) || n_kv > (1u << 24) || n_tensors > f.size / 24 || n_kv > f.size / 13) {
+        err = "truncated or implausible header";
+        return false;
+    }
     uint64_t alignment = 32;
     for (uint64_t k = 0; k < n_kv; k++) {
         std::string key = c.str();
@@ -167,7 +171,10 @@ bool parse(File &f, std::string &err) {
         if (key == "general.alignment" && v.type != kString && v.type != kArray && v.u > 0) alignment = v.u;
         f.kvs.emplace_back(std::move(key), std::move(v));
     }
-    if (alignment == 0 || (alignment & (alignment - 1)) != 0) { err = "general.alignment is not a power of two"; return false; }
+    if (alignment == 0 || (alignment & (alignment - 1)) != 0 || alignment > (1u << 20)) {
+        err = "general.alignment is not a power of two up to 1 MiB";
+        return false;
+    }
     f.tensors.resize((size_t)n_tensors);
     for (Tensor &t : f.tensors) {
         t.name = c.str();
@@ -185,9 +192,12 @@ bool parse(File &f, std::string &err) {
     for (Tensor &t : f.tensors) {
         if (t.offset % alignment != 0) { err = "tensor " + t.name + ": offset not aligned"; return false; }
         const size_t rb = type_row_bytes(t.type_id, t.ne[0]);
-        uint64_t rows = 1;
-        for (int d = 1; d < 4; d++) rows *= t.ne[d];
-        t.n_bytes = rb ? rb * (size_t)rows : 0;
+        uint64_t rows = 1, total = 0;
+        bool overflow = false;
+        for (int d = 1; d < 4; d++) overflow |= __builtin_mul_overflow(rows, t.ne[d], &rows);
+        overflow |= __builtin_mul_overflow((uint64_t)rb, rows, &total);
+        if (overflow) { err = "tensor " + t.name + ": implausible shape"; return false; }
+        t.n_bytes = (size_t)total;
         if (t.offset > f.size - f.data_off || t.n_bytes > f.size - f.data_off - t.offset) {
             err = "tensor " + t.name + ": data runs past the end of the file";
             return false;

@@ -96,6 +96,18 @@ def test_reader_refuses_malformed_files(tmp_path):
             capi.Gguf(p)
     with pytest.raises(ValueError):
         capi.Gguf(str(tmp_path / "absent.gguf"))
+    # headers that ask for more than the file can hold: a tensor count beyond the file's size, a shape whose byte
+    # count wraps around 64 bits, an alignment of 2^40
+    p = str(tmp_path / "bad.gguf")
+    open(p, "wb").write(raw[:8] + struct.pack("<Q", 1 << 23) + raw[16:])
+    with pytest.raises(ValueError):
+        capi.Gguf(p)
+    write_gguf(p, [], [("w", [32, 1 << 40, 1 << 40], synth.Q8_0, b"\0" * 68)])
+    with pytest.raises(ValueError):
+        capi.Gguf(p)
+    write_gguf(p, [("general.alignment", 10, 1 << 40)], [("w", [32, 2], synth.Q8_0, b"\0" * 68)], alignment=32)
+    with pytest.raises(ValueError):
+        capi.Gguf(p)
 
 
 def reference_file(name):
