@@ -385,6 +385,12 @@ int krk_cuda_backend_gemm_accumulate(void *be, void *dst, const void *x, const v
 int krk_cuda_backend_gemm_group(void *be, void *const out[], const void *x, const void *const w[], int wt,
                                 const int64_t n_out[], int64_t n_in, int n_mat, int64_t rows, int silu,
                                 int *silu_fused);
+/* The same with the two optional arrays of Backend::gemm_group (backend.hpp:1040-1056): wts[m] the weight type of
+ * matrix m (NULL: all of type wt) and xs[m] its activation (NULL: all read x), e.g. the routed experts' down
+ * projections, which read a different silu row each. Both are HOST arrays. */
+int krk_cuda_backend_gemm_group_ex(void *be, void *const out[], const void *x, const void *const w[], int wt,
+                                   const int64_t n_out[], int64_t n_in, int n_mat, int64_t rows, int silu,
+                                   int *silu_fused, const int wts[], const void *const xs[]);
 
 /* ---- the on-disk format either side of the path: a GGUF v2 / v3 tensor reader ----
  * Replaces krk::Gguf for this path (include/krk/gguf.hpp; src/gguf.cpp): one file, mapped read-only; header,

@@ -62,11 +62,15 @@ public:
     bool gemm_group(void *const out[], const void *x, const void *const w[], DType wt, const i64 n_out[], i64 n_in,
                     int n_mat, i64 rows, bool silu = false, bool *silu_fused = nullptr, bool row_parallel_only = false,
                     const DType *wts = nullptr, const void *const xs[] = nullptr) override {
-        if (wts || xs)   // per-matrix types / activations: the base class's loop over gemm() (or bind krk_cuda_gemv_group)
-            return Backend::gemm_group(out, x, w, wt, n_out, n_in, n_mat, rows, silu, silu_fused, row_parallel_only, wts, xs);
+        (void)row_parallel_only;   // every matrix is one row-parallel pass on this backend
         int fused = 0;
-        const bool ran = krk_cuda_backend_gemm_group(impl_, out, x, w, static_cast<int>(wt), n_out, n_in, n_mat, rows,
-                                                     silu ? 1 : 0, &fused) != 0;
+        int types[64];
+        if (wts && n_mat > 64)
+            return Backend::gemm_group(out, x, w, wt, n_out, n_in, n_mat, rows, silu, silu_fused, row_parallel_only, wts, xs);
+        if (wts)
+            for (int m = 0; m < n_mat; m++) types[m] = static_cast<int>(wts[m]);
+        const bool ran = krk_cuda_backend_gemm_group_ex(impl_, out, x, w, static_cast<int>(wt), n_out, n_in, n_mat, rows,
+                                                        silu ? 1 : 0, &fused, wts ? types : nullptr, xs) != 0;
         if (silu_fused) *silu_fused = fused != 0;
         return ran;
     }

@@ -134,6 +134,8 @@ SIGNATURES = {
     "krk_cuda_backend_gemm_accumulate": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _i64, _i64]),
     "krk_cuda_backend_gemm_group": (_int, [_vp, C.POINTER(_vp), _vp, C.POINTER(_vp), _int, C.POINTER(_i64),
                                            _i64, _int, _i64, _int, C.POINTER(_int)]),
+    "krk_cuda_backend_gemm_group_ex": (_int, [_vp, C.POINTER(_vp), _vp, C.POINTER(_vp), _int, C.POINTER(_i64),
+                                              _i64, _int, _i64, _int, C.POINTER(_int), C.POINTER(_int), C.POINTER(_vp)]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():
@@ -559,11 +561,19 @@ class Backend:
     def gemm_accumulate(self, dst: int, x: int, w: int, wt: int, n_out: int, n_in: int, rows: int) -> bool:
         return bool(lib.krk_cuda_backend_gemm_accumulate(self.h, dst, x, w, wt, n_out, n_in, rows))
 
-    def gemm_group(self, outs, x: int, ws, wt: int, n_outs, n_in: int, rows: int = 1, silu: bool = False):
+    def gemm_group(self, outs, x: int, ws, wt: int, n_outs, n_in: int, rows: int = 1, silu: bool = False,
+                   wts=None, xs=None):
+        """Backend::gemm_group; wts / xs are its optional per-matrix weight types and activations."""
         n = len(ws)
         fused = _int(0)
-        ran = lib.krk_cuda_backend_gemm_group(self.h, (_vp * n)(*outs), x, (_vp * n)(*ws), wt, (_i64 * n)(*n_outs),
-                                              n_in, n, rows, int(silu), C.byref(fused))
+        if wts is None and xs is None:
+            ran = lib.krk_cuda_backend_gemm_group(self.h, (_vp * n)(*outs), x, (_vp * n)(*ws), wt, (_i64 * n)(*n_outs),
+                                                  n_in, n, rows, int(silu), C.byref(fused))
+        else:
+            ran = lib.krk_cuda_backend_gemm_group_ex(self.h, (_vp * n)(*outs), x, (_vp * n)(*ws), wt, (_i64 * n)(*n_outs),
+                                                     n_in, n, rows, int(silu), C.byref(fused),
+                                                     (_int * n)(*wts) if wts is not None else None,
+                                                     (_vp * n)(*xs) if xs is not None else None)
         return bool(ran), bool(fused.value)
 
 

@@ -342,4 +342,23 @@ int krk_cuda_backend_gemm_group(void *be, void *const out[], const void *x, cons
     return ran ? 1 : 0;
 }
 
+int krk_cuda_backend_gemm_group_ex(void *be, void *const out[], const void *x, const void *const w[], int wt,
+                                   const int64_t n_out[], int64_t n_in, int n_mat, int64_t rows, int silu,
+                                   int *silu_fused, const int wts[], const void *const xs[]) {
+    bool fused = false;
+    DType types[KRK_CUDA_MAX_GROUP];
+    if (wts && n_mat > KRK_CUDA_MAX_GROUP) {   // larger groups than one launch takes: the per-matrix loop
+        auto *b = static_cast<CudaBackend *>(be);
+        for (int m = 0; m < n_mat; m++) b->gemm(out[m], xs ? xs[m] : x, w[m], static_cast<DType>(wts[m]), n_out[m], n_in, rows);
+        if (silu_fused) *silu_fused = 0;
+        return 0;
+    }
+    if (wts)
+        for (int m = 0; m < n_mat; m++) types[m] = static_cast<DType>(wts[m]);
+    const bool ran = static_cast<CudaBackend *>(be)->gemm_group(out, x, w, static_cast<DType>(wt), n_out, n_in, n_mat, rows,
+                                                                silu != 0, &fused, false, wts ? types : nullptr, xs);
+    if (silu_fused) *silu_fused = fused ? 1 : 0;
+    return ran ? 1 : 0;
+}
+
 } // extern "C"

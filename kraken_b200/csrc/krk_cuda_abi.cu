@@ -156,9 +156,20 @@ int krk_cuda_gemv_group(void *const host_y[], const void *const host_x[], const 
     }
     if (!device_state()) return KRK_CUDA_EDEVICE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int rc = launch_gemv_stream(mats, n_mat, n_in, 1, 0, fuse_silu_pair, st);
-    if (rc != 0) return rc < 0 ? rc : KRK_CUDA_OK;
-    return launch_gemv_generic(mats, n_mat, n_in, 1, 0, fuse_silu_pair, st);
+    // One launch per run of equal weight types (a pair of the silu fold never straddles two runs: its types are
+    // equal), each on the streaming kernel where it addresses the shape.
+    for (int first = 0; first < n_mat;) {
+        int last = first + 1;
+        while (last < n_mat && mats[last].wt == mats[first].wt) last++;
+        int rc = launch_gemv_stream(mats + first, last - first, n_in, 1, 0, fuse_silu_pair, st);
+        if (rc < 0) return rc;
+        if (rc == 0) {
+            rc = launch_gemv_generic(mats + first, last - first, n_in, 1, 0, fuse_silu_pair, st);
+            if (rc != KRK_CUDA_OK) return rc;
+        }
+        first = last;
+    }
+    return KRK_CUDA_OK;
 }
 
 size_t krk_cuda_gemm_workspace_bytes(int x_dtype, int64_t n_out, int64_t n_in, int64_t rows) {

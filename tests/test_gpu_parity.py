@@ -443,6 +443,39 @@ def test_decode_layer_matmuls_through_backend(cuda, oracle):
     be.close()
 
 
+def test_backend_gemm_group_with_per_matrix_types_and_activations(cuda, oracle):
+    """Backend::gemm_group's optional arrays (include/krk/backend.hpp:1040-1056): `wts` (q/k/v of a mixed file in
+    ONE group: Q4_K, Q4_K, Q6_K) and `xs` (the routed experts' down projections, each reading its own row)."""
+    be = cuda.Backend(0)
+    n_in, seed = 1024, SEED + 50
+    shapes = [(512, synth.Q4_K), (256, synth.Q4_K), (256, synth.Q6_K), (128, synth.Q8_0)]
+    ws = [synth.weights(wt, n, n_in, seed, stream=10 + i) for i, (n, wt) in enumerate(shapes)]
+    xs = [synth.activations(1, n_in, seed, stream=20 + i) for i in range(len(shapes))]
+
+    def up(a):
+        p = be.alloc(a.nbytes)
+        be.upload(p, a.ctypes.data, a.nbytes)
+        return p
+
+    d_w, d_x = [up(w) for w in ws], [up(x) for x in xs]
+    d_y = [be.alloc(4 * n) for n, _ in shapes]
+    for use_xs in (False, True):
+        ran, fused = be.gemm_group(d_y, d_x[0], d_w, synth.Q4_K, [n for n, _ in shapes], n_in, rows=1,
+                                   wts=[wt for _, wt in shapes], xs=d_x if use_xs else None)
+        assert ran and not fused
+        for i, (n, wt) in enumerate(shapes):
+            got = np.empty(n, np.float32)
+            be.download(got.ctypes.data, d_y[i], got.nbytes)
+            x = xs[i] if use_xs else xs[0]
+            ref = oracle.gemm(x, ws[i], wt, n, n_in, rows=1, threads=4)
+            ok, worst = bound_ok(got[None, :], ref, oracle.dequant_rows(ws[i], wt, n, n_in), x, GEMV_TOL)
+            assert ok, (i, use_xs, worst)
+    assert cuda.device_status() == 0
+    for p in d_w + d_x + d_y:
+        be.release(p)
+    be.close()
+
+
 @pytest.mark.parametrize("wt,n_in", [(synth.Q8_0, 96), (synth.Q8_0, 4128), (synth.Q4_0, 160), (synth.Q5_0, 96)])
 @pytest.mark.parametrize("rows", [9, 40])
 def test_backend_gemm_fallback_rung_k_not_multiple_of_256(cuda, oracle, wt, n_in, rows):
