@@ -256,11 +256,11 @@ def test_route_ids_exact(cuda, oracle):
     assert np.allclose(wts.cpu().numpy(), wts_ref, rtol=2e-6, atol=1e-9)
 
 
-def moe_case(cuda, oracle, n_embd, n_ff, n_exp, k, n_tok, seed, local=None):
+def moe_case(cuda, oracle, n_embd, n_ff, n_exp, k, n_tok, seed, local=None, wt_gu=synth.Q4_K, wt_dn=synth.Q6_K):
     import torch
-    gate = [synth.weights(synth.Q4_K, n_ff, n_embd, seed, stream=1000 + e) for e in range(n_exp)]
-    up = [synth.weights(synth.Q4_K, n_ff, n_embd, seed, stream=2000 + e) for e in range(n_exp)]
-    down = [synth.weights(synth.Q6_K, n_embd, n_ff, seed, stream=3000 + e) for e in range(n_exp)]
+    gate = [synth.weights(wt_gu, n_ff, n_embd, seed, stream=1000 + e) for e in range(n_exp)]
+    up = [synth.weights(wt_gu, n_ff, n_embd, seed, stream=2000 + e) for e in range(n_exp)]
+    down = [synth.weights(wt_dn, n_embd, n_ff, seed, stream=3000 + e) for e in range(n_exp)]
     x = synth.activations(n_tok, n_embd, seed)
     logits = synth.activations(n_tok, n_exp, seed, stream=7)
     ids_ref, wts_ref = oracle.route(logits, k)
@@ -268,10 +268,10 @@ def moe_case(cuda, oracle, n_embd, n_ff, n_exp, k, n_tok, seed, local=None):
     assert np.array_equal(ids.cpu().numpy(), ids_ref)
     lo, hi = local if local else (0, n_exp)
     sel = lambda mats: [m if lo <= e < hi else None for e, m in enumerate(mats)]
-    y_ref = oracle.moe_ffn(x, ids_ref, wts_ref, sel(gate), sel(up), sel(down), synth.Q4_K, synth.Q6_K, n_embd, n_ff,
+    y_ref = oracle.moe_ffn(x, ids_ref, wts_ref, sel(gate), sel(up), sel(down), wt_gu, wt_dn, n_embd, n_ff,
                            threads=8)
     bank = cuda.make_bank(dev(np.stack(gate[lo:hi])), dev(np.stack(up[lo:hi])), dev(np.stack(down[lo:hi])),
-                          synth.Q4_K, synth.Q6_K, hi - lo, lo, n_embd, n_ff)
+                          wt_gu, wt_dn, hi - lo, lo, n_embd, n_ff)
     keep = (bank,)
     y = cuda.moe_ffn(dev(x), ids, wts, bank).cpu().numpy()
     assert cuda.device_status() == 0
@@ -299,6 +299,15 @@ def test_moe_routed_equals_route_then_ffn(cuda):
         assert cuda.device_status() == 0
         assert torch.equal(ids, ids2) and torch.equal(wts, wts2)
         assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("wt_gu,wt_dn", [(synth.Q4_0, synth.Q8_0), (synth.Q5_K, synth.Q4_K), (synth.Q8_0, synth.Q5_K),
+                                          (synth.Q6_K, synth.Q4_0), (synth.Q5_0, synth.Q5_1)])
+def test_moe_other_expert_formats(cuda, oracle, wt_gu, wt_dn):
+    """Expert banks in the other formats: the device-table launches of every streaming arm (Q4_0, Q5_K, Q8_0, Q6_K
+    with 16-byte-multiple rows, Q4_K down) and the warp-per-row kernels (Q5_0 / Q5_1), whole bank and a shard."""
+    moe_case(cuda, oracle, 2048, 1024, 8, 2, 3, SEED + 13, wt_gu=wt_gu, wt_dn=wt_dn)
+    moe_case(cuda, oracle, 2048, 1024, 8, 4, 1, SEED + 14, local=(4, 8), wt_gu=wt_gu, wt_dn=wt_dn)
 
 
 def test_moe_small(cuda, oracle):
