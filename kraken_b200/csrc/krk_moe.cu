@@ -27,29 +27,49 @@ __device__ __forceinline__ float ordered_sum(const float *v, int n, int lane) {
     return sum;
 }
 
-// One warp per token. Softmax as the reference computes it: subtract the maximum, sum the
-// exponentials in expert order, multiply by the reciprocal (src/engine.cpp:11704-11713);
-// then k picks of the largest probability, strict '>' so equal probabilities keep the lower
-// id (:11857-11886); then the picked weights are divided by their slot-order sum
-// (:11913-11918).
-__device__ __forceinline__ void route_token(int32_t *__restrict__ ids, float *__restrict__ wts, const float *__restrict__ lg,
-                                            int n_expert, int k, float *prob, float *wsel, int lane) {
-    float mx = -INFINITY;
-    for (int e = lane; e < n_expert; e += 32) mx = fmaxf(mx, lg[e]);
+// The k largest of prob[0..n) in slot order by one warp: strict '>' so equal values keep the lower index
+// (src/engine.cpp:11857-11886). Lane s (s < k) returns slot s's index (-1: none left) and value; `sum` is the sum of
+// the picked values in slot order. Up to 128 entries live in registers (four per lane) and a round is two warp
+// reductions: the maximum over the bit patterns of the (non-negative) values, then the lowest index among the lanes
+// that hold it. More entries take rounds over shared memory (prob is then modified: -2 marks a taken entry).
+__device__ __forceinline__ void topk_warp(float *prob, int n, int k, int lane, int &my_id, float &my_w, float &sum) {
+    my_id = -1;
+    my_w = 0.0f;
+    sum = 0.0f;
+    if (n <= 128) {
+        float v[4];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-    for (int e = lane; e < n_expert; e += 32) prob[e] = exp_as_host(__fsub_rn(lg[e], mx));
-    __syncwarp();
-    const float sum = ordered_sum(prob, n_expert, lane);
-    const float inv = sum > 0.0f ? __fdiv_rn(1.0f, sum) : 0.0f;
-    for (int e = lane; e < n_expert; e += 32) prob[e] = __fmul_rn(prob[e], inv);
-    __syncwarp();
-
+        for (int j = 0; j < 4; j++) v[j] = lane + 32 * j < n ? prob[lane + 32 * j] : -2.0f;
+        for (int s = 0; s < k; s++) {
+            float bp = -1.0f;
+            int be = 0x7FFFFFFF;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (v[j] > bp) {
+                    bp = v[j];
+                    be = lane + 32 * j;
+                }
+            const unsigned key = bp >= 0.0f ? __float_as_uint(bp) + 1u : 0u;   // bit patterns of values >= 0 order like the values
+            const unsigned top = __reduce_max_sync(0xFFFFFFFFu, key);
+            const unsigned win = __reduce_min_sync(0xFFFFFFFFu, (key == top && top != 0u) ? (unsigned)be : 0x7FFFFFFFu);
+            const bool ok = top != 0u;
+            const float w = ok ? __uint_as_float(top - 1u) : 0.0f;
+            sum = __fadd_rn(sum, w);
+            if (lane == s) {
+                my_id = ok ? (int)win : -1;
+                my_w = w;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (ok && lane + 32 * j == (int)win) v[j] = -2.0f;
+        }
+        return;
+    }
     for (int s = 0; s < k; s++) {
         float bp = -1.0f;
         int be = 0x7FFFFFFF;
-        for (int e = lane; e < n_expert; e += 32) {
-            const float pe = prob[e];   // a taken expert is marked with -2
+        for (int e = lane; e < n; e += 32) {
+            const float pe = prob[e];
             if (pe > bp) {
                 bp = pe;
                 be = e;
@@ -64,19 +84,44 @@ __device__ __forceinline__ void route_token(int32_t *__restrict__ ids, float *__
                 be = oe;
             }
         }
-        if (lane == 0) {
-            const bool ok = be < n_expert && bp >= 0.0f;
-            ids[s] = ok ? be : -1;
-            wsel[s] = ok ? bp : 0.0f;
-            if (ok) prob[be] = -2.0f;
+        const bool ok = be < n && bp >= 0.0f;
+        const float w = ok ? bp : 0.0f;
+        sum = __fadd_rn(sum, w);
+        if (lane == s) {
+            my_id = ok ? be : -1;
+            my_w = w;
         }
+        if (ok && lane == 0) prob[be] = -2.0f;
         __syncwarp();
     }
-    if (lane == 0) {
-        float ksum = 0.0f;
-        for (int s = 0; s < k; s++) ksum = __fadd_rn(ksum, wsel[s]);
-        const float kinv = ksum > 0.0f ? __fdiv_rn(1.0f, ksum) : 0.0f;
-        for (int s = 0; s < k; s++) wts[s] = __fmul_rn(wsel[s], kinv);
+}
+
+// One warp per token. Softmax as the reference computes it: subtract the maximum, sum the
+// exponentials in expert order, multiply by the reciprocal (src/engine.cpp:11704-11713);
+// then k picks of the largest probability, strict '>' so equal probabilities keep the lower
+// id (:11857-11886); then the picked weights are divided by their slot-order sum
+// (:11913-11918).
+__device__ __forceinline__ void route_token(int32_t *__restrict__ ids, float *__restrict__ wts, const float *__restrict__ lg,
+                                            int n_expert, int k, float *prob, int *sid, int lane) {
+    float mx = -INFINITY;
+    for (int e = lane; e < n_expert; e += 32) mx = fmaxf(mx, lg[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    for (int e = lane; e < n_expert; e += 32) prob[e] = exp_as_host(__fsub_rn(lg[e], mx));
+    __syncwarp();
+    const float sum = ordered_sum(prob, n_expert, lane);
+    const float inv = sum > 0.0f ? __fdiv_rn(1.0f, sum) : 0.0f;
+    for (int e = lane; e < n_expert; e += 32) prob[e] = __fmul_rn(prob[e], inv);
+    __syncwarp();
+
+    int my_id;
+    float my_w, ksum;
+    topk_warp(prob, n_expert, k, lane, my_id, my_w, ksum);
+    const float kinv = ksum > 0.0f ? __fdiv_rn(1.0f, ksum) : 0.0f;
+    if (lane < k) {
+        ids[lane] = my_id;
+        wts[lane] = __fmul_rn(my_w, kinv);
+        if (sid) sid[lane] = my_id;
     }
 }
 
@@ -84,9 +129,8 @@ __global__ void __launch_bounds__(32)
 route_kernel(int32_t *__restrict__ ids, float *__restrict__ wts, const float *__restrict__ logits,
              int n_expert, int k) {
     __shared__ float prob[kMaxExperts];
-    __shared__ float wsel[kMaxK];
     const int64_t t = blockIdx.x;
-    route_token(ids + t * k, wts + t * k, logits + t * n_expert, n_expert, k, prob, wsel, threadIdx.x);
+    route_token(ids + t * k, wts + t * k, logits + t * n_expert, n_expert, k, prob, nullptr, threadIdx.x);
 }
 
 // The router in the three steps Backend exposes (include/krk/backend.hpp:934-986): probabilities,
@@ -113,50 +157,19 @@ __global__ void __launch_bounds__(32)
 router_topk_kernel(const float *__restrict__ probs, int n_expert, int k, int32_t *__restrict__ ids, float *__restrict__ wts,
                    int normalize, float scale) {
     __shared__ float prob[kMaxExperts];
-    __shared__ float wsel[kMaxK];
     const float *pr = probs + (int64_t)blockIdx.x * n_expert;
     const int lane = threadIdx.x;
     for (int e = lane; e < n_expert; e += 32) prob[e] = pr[e];
     __syncwarp();
-    for (int s = 0; s < k; s++) {
-        float bp = -1.0f;
-        int be = 0x7FFFFFFF;
-        for (int e = lane; e < n_expert; e += 32) {
-            const float pe = prob[e];
-            if (pe > bp) {
-                bp = pe;
-                be = e;
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float op = __shfl_xor_sync(0xFFFFFFFFu, bp, o);
-            const int oe = __shfl_xor_sync(0xFFFFFFFFu, be, o);
-            if (op > bp || (op == bp && oe < be)) {
-                bp = op;
-                be = oe;
-            }
-        }
-        if (lane == 0) {
-            const bool ok = be < n_expert && bp >= 0.0f;
-            ids[(int64_t)blockIdx.x * k + s] = ok ? be : -1;
-            wsel[s] = ok ? bp : 0.0f;
-            if (ok) prob[be] = -2.0f;
-        }
-        __syncwarp();
-    }
-    if (lane == 0) {
-        float kinv = 1.0f;
-        if (normalize) {
-            float ksum = 0.0f;
-            for (int s = 0; s < k; s++) ksum = __fadd_rn(ksum, wsel[s]);
-            kinv = ksum > 0.0f ? __fdiv_rn(1.0f, ksum) : 0.0f;
-        }
-        for (int s = 0; s < k; s++) {
-            float w = normalize ? __fmul_rn(wsel[s], kinv) : wsel[s];
-            if (scale != 1.0f) w = __fmul_rn(w, scale);
-            wts[(int64_t)blockIdx.x * k + s] = w;
-        }
+    int my_id;
+    float my_w, ksum;
+    topk_warp(prob, n_expert, k, lane, my_id, my_w, ksum);
+    const float kinv = normalize ? (ksum > 0.0f ? __fdiv_rn(1.0f, ksum) : 0.0f) : 1.0f;
+    if (lane < k) {
+        float w = normalize ? __fmul_rn(my_w, kinv) : my_w;
+        if (scale != 1.0f) w = __fmul_rn(w, scale);
+        ids[(int64_t)blockIdx.x * k + lane] = my_id;
+        wts[(int64_t)blockIdx.x * k + lane] = w;
     }
 }
 
@@ -322,19 +335,24 @@ moe_plan_kernel(const __grid_constant__ MoeParams p, StreamTable *gate_up, Strea
                 size_t rb_gate_up, size_t rb_down, int gran_gate_up, int gran_down, const float *logits, int n_expert) {
     __shared__ int key[kStreamTableEntries];
     __shared__ float prob[KRK_CUDA_MAX_ROWS][kPlanRouteExperts];
-    __shared__ float wsel[KRK_CUDA_MAX_ROWS][kMaxK];
+    __shared__ int sid[KRK_CUDA_MAX_ROWS][kMaxK];   // the ids the fused routing picked, for the plan below
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // (see moe_combine_kernel)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (logits) {
         const int t = threadIdx.x >> 5;
         if (t < p.n_tok)
             route_token(const_cast<int32_t *>(p.ids) + t * p.k, const_cast<float *>(p.wts) + t * p.k,
-                        logits + (int64_t)t * n_expert, n_expert, p.k, prob[t], wsel[t], threadIdx.x & 31);
+                        logits + (int64_t)t * n_expert, n_expert, p.k, prob[t], sid[t], threadIdx.x & 31);
         __syncthreads();   // the ids written above are read below by other threads of this block
     }
     const int n_pick = p.n_tok * p.k, pick = threadIdx.x;
     int e = -1;
-    if (pick < n_pick) e = local_expert(p, pick);
+    if (pick < n_pick) {
+        // (with the routing fused the ids come out of shared memory, not back from global memory)
+        const int id = logits ? sid[pick / p.k][pick % p.k] : p.ids[pick];
+        const int le = id - p.expert_base;
+        e = (le >= 0 && le < p.n_local) ? le : -1;
+    }
     if (pick < kStreamTableEntries) key[pick] = e >= 0 ? e * kStreamTableEntries + pick : 0x7FFFFFFF;
     __syncthreads();
     if (e >= 0) {
