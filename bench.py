@@ -786,7 +786,8 @@ def prefill_extra(torch, capi, gen):
     other = {}
     del ws
     for name, wt, make in (("q6_k", synth.Q6_K, device_weights_q6k), ("q8_0", synth.Q8_0, device_weights_q8_0),
-                           ("q4_0", synth.Q4_0, device_weights_q4_0), ("q5_k", synth.Q5_K, device_weights_q5_k)):
+                           ("q4_0", synth.Q4_0, device_weights_q4_0), ("q5_k", synth.Q5_K, device_weights_q5_k),
+                           ("q5_0", synth.Q5_0, device_weights_q5_0)):
         wf = [make(torch, n_out, n_in, gen) for _ in range(3)]
         rows = 512
         x = torch.randn((rows, n_in), device="cuda", generator=gen).to(torch.float16)

@@ -61,9 +61,13 @@ constexpr int kRawBytes = kTileN * 144;
 __host__ __device__ constexpr bool row_phased(int wt) { return wt == KRK_CUDA_Q6_K; }
 constexpr int kPhases = 8;
 __host__ __device__ constexpr bool tma_staged(int wt) {
-    return wt == KRK_CUDA_Q4_K || wt == KRK_CUDA_Q4_0 || wt == KRK_CUDA_Q5_K || wt == KRK_CUDA_Q8_0 || row_phased(wt);
+    return wt == KRK_CUDA_Q4_K || wt == KRK_CUDA_Q4_0 || wt == KRK_CUDA_Q5_K || wt == KRK_CUDA_Q8_0 || wt == KRK_CUDA_Q5_0 ||
+           wt == KRK_CUDA_Q5_1 || row_phased(wt);
 }
-__host__ __device__ constexpr int raw_seg(int wt) { return wt == KRK_CUDA_Q5_K ? 176 : wt == KRK_CUDA_Q6_K ? 224 : 144; }
+// (Q5_0: eight 22-byte blocks = 176 bytes; Q5_1: eight 24-byte blocks = 192)
+__host__ __device__ constexpr int raw_seg(int wt) {
+    return (wt == KRK_CUDA_Q5_K || wt == KRK_CUDA_Q5_0) ? 176 : wt == KRK_CUDA_Q5_1 ? 192 : wt == KRK_CUDA_Q6_K ? 224 : 144;
+}
 // Which staged row and which weight row of the tile the decode thread of TMEM lane t works on. Phased formats:
 // a warp's 32 lanes take the rows 32w .. 32w + 31 of the tile (so the read-out writes 32 different banks) in
 // an order whose neighbouring lanes read staged rows on different banks.
@@ -72,9 +76,9 @@ __host__ __device__ constexpr int tile_slot(int wt, int t) { return row_phased(w
 struct WMaps {
     CUtensorMap m[kPhases];   // m[0] alone for the formats staged as one box
 };
-__host__ __device__ constexpr int raw_stages(int wt) { return (wt == KRK_CUDA_Q5_K || wt == KRK_CUDA_Q6_K) ? 2 : 3; }
+__host__ __device__ constexpr int raw_stages(int wt) { return raw_seg(wt) > 144 ? 2 : 3; }
 constexpr int kRawArea = 2 * kTileN * 224;
-static_assert(2 * kTileN * 176 <= kRawArea && kRawStages * kRawBytes <= kRawArea, "every format's stages fit the raw area");
+static_assert(2 * kTileN * 192 <= kRawArea && kRawStages * kRawBytes <= kRawArea, "every format's stages fit the raw area");
 constexpr int kDecodeThreads = 256, kEpilogueThreads = 128;   // two decode threads per weight row
 constexpr int kThreads = kDecodeThreads + kEpilogueThreads + 96;
 constexpr int kTmemCols = 512, kTmemA = 256;
@@ -450,6 +454,84 @@ struct Raw<KRK_CUDA_Q5_K> {
             const uint32_t v01 = __byte_perm(t, 0x64646464u, 0x5140), v23 = __byte_perm(t, 0x64646464u, 0x7362);
             out[2 * i] = h2_bits(__hfma2(__hsub2(bits_h2(v01), k1024), dl, ml));
             out[2 * i + 1] = h2_bits(__hfma2(__hsub2(bits_h2(v23), k1024), dl, ml));
+        }
+    }
+};
+
+// Four bits (a nibble's worth of fifth quant bits) spread to bit 4 of four bytes: bit m of b goes to bit 8m + 4.
+__device__ __forceinline__ uint32_t spread_fifth(uint32_t b) { return (((b & 0xFu) * 0x00204081u) & 0x01010101u) << 4; }
+
+// Q5_0: eight 22-byte blocks per 256 values (src/quant.cpp:351-364): f16 d, 32 fifth bits, 16 bytes whose low nibbles
+// are quants 0..15 and whose high nibbles are quants 16..31; value = d * (q - 16). K step p covers blocks 2p (thread
+// half 0: the block starts on a word of the 176 bytes) and 2p + 1 (half 1: half a word later, so its bit word and its
+// quant bytes are whole words).
+template <>
+struct Raw<KRK_CUDA_Q5_0> {
+    static constexpr int kSteps = 4;
+    uint32_t w[44];
+    __device__ __forceinline__ void load_block(const uint8_t *block, int, int) {
+        const uint4 *b = reinterpret_cast<const uint4 *>(block);
+#pragma unroll
+        for (int i = 0; i < 11; i++) {
+            const uint4 v = b[i];
+            w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
+        }
+    }
+    __device__ __forceinline__ void convert(int p, int half, int, uint32_t (&out)[16]) const {
+        // (both candidates with constant indices, then a select: a branch on `half` would index w[] dynamically)
+        const int W = 11 * p;
+        uint32_t q[4];
+        const uint32_t dbits = half ? (w[W + 5] >> 16) : (w[W] & 0xFFFFu);
+        const uint32_t qh = half ? w[W + 6] : __funnelshift_r(w[W], w[W + 1], 16);
+#pragma unroll
+        for (int i = 0; i < 4; i++) q[i] = half ? w[W + 7 + i] : __funnelshift_r(w[W + 1 + i], w[W + 2 + i], 16);
+        const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)dbits));
+        const __half2 bias = __float2half2_rn(1040.0f);   // 0x6400 | q is the half 1024 + q; the quant is q - 16
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t lo = (q[i] & 0x0F0F0F0Fu) | spread_fifth(qh >> (4 * i));
+            const uint32_t hi = ((q[i] >> 4) & 0x0F0F0F0Fu) | spread_fifth(qh >> (16 + 4 * i));
+            out[2 * i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(lo, 0x64646464u, 0x5140)), bias), d2));
+            out[2 * i + 1] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(lo, 0x64646464u, 0x7362)), bias), d2));
+            out[8 + 2 * i] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(hi, 0x64646464u, 0x5140)), bias), d2));
+            out[8 + 2 * i + 1] = h2_bits(__hmul2(__hsub2(bits_h2(__byte_perm(hi, 0x64646464u, 0x7362)), bias), d2));
+        }
+    }
+};
+
+// Q5_1: eight 24-byte blocks per 256 values (src/quant.cpp:366-379): f16 d, f16 m, 32 fifth bits, 16 quant bytes;
+// value = d * q + m, q unsigned. Every field of every block is word aligned.
+template <>
+struct Raw<KRK_CUDA_Q5_1> {
+    static constexpr int kSteps = 4;
+    uint32_t w[48];
+    __device__ __forceinline__ void load_block(const uint8_t *block, int, int) {
+        const uint4 *b = reinterpret_cast<const uint4 *>(block);
+#pragma unroll
+        for (int i = 0; i < 12; i++) {
+            const uint4 v = b[i];
+            w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
+        }
+    }
+    __device__ __forceinline__ void convert(int p, int half, int, uint32_t (&out)[16]) const {
+        // (the block's six words picked with constant indices and a select: `half` in the index would put w[] in
+        // local memory)
+        uint32_t b[6];
+#pragma unroll
+        for (int i = 0; i < 6; i++) b[i] = half ? w[12 * p + 6 + i] : w[12 * p + i];
+        const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)(b[0] & 0xFFFFu)));
+        const __half2 m2 = __half2half2(__ushort_as_half((unsigned short)(b[0] >> 16)));
+        const uint32_t qh = b[1];
+        const __half2 k1024 = __float2half2_rn(1024.0f);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t qw = b[2 + i];
+            const uint32_t lo = (qw & 0x0F0F0F0Fu) | spread_fifth(qh >> (4 * i));
+            const uint32_t hi = ((qw >> 4) & 0x0F0F0F0Fu) | spread_fifth(qh >> (16 + 4 * i));
+            out[2 * i] = h2_bits(__hfma2(__hsub2(bits_h2(__byte_perm(lo, 0x64646464u, 0x5140)), k1024), d2, m2));
+            out[2 * i + 1] = h2_bits(__hfma2(__hsub2(bits_h2(__byte_perm(lo, 0x64646464u, 0x7362)), k1024), d2, m2));
+            out[8 + 2 * i] = h2_bits(__hfma2(__hsub2(bits_h2(__byte_perm(hi, 0x64646464u, 0x5140)), k1024), d2, m2));
+            out[8 + 2 * i + 1] = h2_bits(__hfma2(__hsub2(bits_h2(__byte_perm(hi, 0x64646464u, 0x7362)), k1024), d2, m2));
         }
     }
 };
