@@ -220,9 +220,12 @@ __device__ __forceinline__ float decode_value<KRK_CUDA_IQ4_NL>(const uint8_t *ro
     case KRK_CUDA_Q5_1: { constexpr int WT = KRK_CUDA_Q5_1; __VA_ARGS__; } break;       \
     case KRK_CUDA_Q5_K: { constexpr int WT = KRK_CUDA_Q5_K; __VA_ARGS__; } break;       \
     case KRK_CUDA_IQ4_NL: { constexpr int WT = KRK_CUDA_IQ4_NL; __VA_ARGS__; } break;   \
+    case KRK_CUDA_Q2_K: { constexpr int WT = KRK_CUDA_Q2_K; __VA_ARGS__; } break;       \
+    case KRK_CUDA_Q3_K: { constexpr int WT = KRK_CUDA_Q3_K; __VA_ARGS__; } break;       \
     default: break;                                                                     \
     }
-__host__ __device__ constexpr bool gemm_tc_takes(int wt) { return wt != KRK_CUDA_Q2_K && wt != KRK_CUDA_Q3_K; }
+// (every format this library decodes has a tensor-core prefill arm; the row-batch rung remains for K % 256 != 0)
+__host__ __device__ constexpr bool gemm_tc_takes(int wt) { return block_size(wt) != 0; }
 
 // ---- kernel-family entry points (one .cu file each) -------------------------------------
 

@@ -185,8 +185,7 @@ int krk_cuda_gemm(void *y_f32, const void *x, int x_dtype, const void *w, int wt
     if (rc != KRK_CUDA_OK) return rc;
     if (n_in % 256 != 0 || !gemm_tc_takes(wt)) {
         // The fallback rung (the place of gemm_simt_kernel, src/hip/kernels/gemm.hpp:1013-1134): 32-value
-        // block formats whose K is a whole number of blocks but not of 256, and the formats whose blocks the
-        // tensor-core kernel does not stage (Q2_K, Q3_K). Correct, not fast: the
+        // block formats whose K is a whole number of blocks but not of 256. Correct, not fast: the
         // shape-agnostic GEMV over batches of KRK_CUDA_MAX_ROWS activation rows. f32 activations only.
         if (x_dtype != KRK_CUDA_X_F32) return KRK_CUDA_ESHAPE;
         if (n_out == 0 || rows == 0) return KRK_CUDA_OK;

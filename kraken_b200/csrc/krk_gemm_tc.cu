@@ -231,16 +231,18 @@ __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cas
 __device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
 
 template <int WT>
-struct Raw {   // formats without a packed decoder (Q5_0, Q5_1): raw bytes staged in shared memory, decoded element by element
+struct Raw {   // formats without a packed decoder (IQ4_NL, Q2_K, Q3_K): raw bytes staged in shared memory, decoded element by element
     static constexpr int kSteps = 4;                                                       // K steps per stage
     static constexpr int kRowSeg = kSteps * kBK / block_size(WT) * block_bytes(WT);       // bytes of one row per stage
     static constexpr int kStageBytes = kTileN * kRowSeg;
-    // Staging granule: with K a multiple of 256 the rows and the segments start 8-byte aligned.
-    static_assert(kRowSeg % 8 == 0, "8-byte staging granules");
-    static constexpr int kUnits = kStageBytes / 8;
+    // Staging granule: with K a multiple of 256 the rows and the segments start on a multiple of it (144-byte
+    // segments: 8 bytes; Q2_K's 84: 4; Q3_K's 110: 2).
+    static constexpr int kGran = kRowSeg % 8 == 0 ? 8 : kRowSeg % 4 == 0 ? 4 : 2;
+    static constexpr int kUnits = kStageBytes / kGran;
     static constexpr int kPer = (kUnits + kDecodeThreads - 1) / kDecodeThreads;            // loads per thread
+    static constexpr int kWords = kGran == 8 ? 2 : 1;
     static_assert(kStageBytes <= kRawStages * kRawBytes / 2, "two stages must fit the raw staging area");
-    uint32_t pre[2 * kPer];   // this thread's share of the NEXT stage, on its way from global memory
+    uint32_t pre[kWords * kPer];   // this thread's share of the NEXT stage, on its way from global memory
     const uint8_t *stage;     // the stage being decoded, [128 rows][kRowSeg]
     // Loads of stage `ks` (K steps ks .. ks + kSteps of weight rows n0 ..): neighbouring threads take
     // neighbouring granules of a row. Rows past n_out read as zero blocks.
@@ -249,19 +251,30 @@ struct Raw {   // formats without a packed decoder (Q5_0, Q5_1): raw bytes stage
 #pragma unroll
         for (int j = 0; j < kPer; j++) {
             const int i = tid + j * kDecodeThreads;
-            const int rr = i / (kRowSeg / 8), col = i - rr * (kRowSeg / 8);
+            const int rr = i / (kRowSeg / kGran), col = i - rr * (kRowSeg / kGran);
             const bool ok = i < kUnits && n0 + rr < n_out;
-            uint2 v = make_uint2(0u, 0u);
-            if (ok) v = __ldg(reinterpret_cast<const uint2 *>(w + (size_t)(n0 + rr) * row_bytes + seg) + col);
-            pre[2 * j] = v.x;
-            pre[2 * j + 1] = v.y;
+            const uint8_t *src = w + (size_t)(n0 + rr) * row_bytes + seg + (size_t)col * kGran;
+            if constexpr (kGran == 8) {
+                uint2 v = make_uint2(0u, 0u);
+                if (ok) v = __ldg(reinterpret_cast<const uint2 *>(src));
+                pre[2 * j] = v.x;
+                pre[2 * j + 1] = v.y;
+            } else if constexpr (kGran == 4) {
+                pre[j] = ok ? __ldg(reinterpret_cast<const uint32_t *>(src)) : 0u;
+            } else {
+                pre[j] = ok ? (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(src)) : 0u;
+            }
         }
     }
     __device__ __forceinline__ void stash(uint8_t *dst, int tid) {
 #pragma unroll
         for (int j = 0; j < kPer; j++) {
             const int i = tid + j * kDecodeThreads;
-            if (i < kUnits) reinterpret_cast<uint2 *>(dst)[i] = make_uint2(pre[2 * j], pre[2 * j + 1]);
+            if (i < kUnits) {
+                if constexpr (kGran == 8) reinterpret_cast<uint2 *>(dst)[i] = make_uint2(pre[2 * j], pre[2 * j + 1]);
+                else if constexpr (kGran == 4) reinterpret_cast<uint32_t *>(dst)[i] = pre[j];
+                else reinterpret_cast<unsigned short *>(dst)[i] = (unsigned short)pre[j];
+            }
         }
         stage = dst;
     }

@@ -92,10 +92,10 @@ def test_device_decode_gemv_gemm_embed(cuda, oracle, wt):
         y = cuda.gemv(dev(x), dev(w), wt, n_out, n_in).cpu().numpy()
         ok, worst = bound_ok(y, oracle.gemm(x, w, wt, n_out, n_in, rows=rows, threads=8), w_deq, x, 1e-4)
         assert ok, worst
-    rows = 40                                                      # the tensor-core path (Q2_K / Q3_K: the row-batch rung, f32 x)
+    rows = 40                                                      # the tensor-core path
     x16 = synth.activations(rows, n_in, SEED + 40).astype(np.float16)
     xf = x16.astype(np.float32)
-    y = cuda.gemm(dev(xf if wt in (synth.Q2_K, synth.Q3_K) else x16), dev(w), wt, n_out, n_in).cpu().numpy()
+    y = cuda.gemm(dev(x16), dev(w), wt, n_out, n_in).cpu().numpy()
     ok, worst = bound_ok(y, oracle.gemm(xf, w, wt, n_out, n_in, rows=rows, threads=8), w_deq, xf, 2e-3)
     assert ok, worst
     toks = np.array([0, 514, 515, -2, 77], np.int32)
