@@ -867,8 +867,15 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
 
 // SINGLE: 0 the general form; 1 Q4_K with one activation row (unit_q4_k_single); 2 the same with the B
 // fragments of the warp's (at most two) K units held in registers, for rows of at most 16 units.
+// Two CTAs per SM (96 registers per thread) or one (up to 192). One or two activation rows always fit in 96.
+// Three or four rows (two column groups) of Q8_0 also do, and two half-SM CTAs are then 1.1-1.5x faster than one
+// at every size. Q4_0 fits too but gains only on very tall matrices (+14 % at 131072 rows, -3 to -9 % at layer
+// sizes); the K-quant forms spill at 96 registers and are faster alone on an SM at layer sizes.
+template <int WT, int NG>
+constexpr bool kTwoPerSm = NG == 1 || (NG == 2 && WT == KRK_CUDA_Q8_0);
+
 template <int WT, int NG, bool STACK, int SINGLE>
-__global__ void __launch_bounds__(kThreads, NG == 1 ? 2 : 1)
+__global__ void __launch_bounds__(kThreads, kTwoPerSm<WT, NG> ? 2 : 1)
 gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     // STACK: several 16-row tiles per stage (p.tps of them); compiled apart so that the usual one-tile
     // form carries none of its index arithmetic.
@@ -1331,9 +1338,10 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
     const int smem_struct = rows <= 2 ? (int)sizeof(Smem<1>) : rows <= 4 ? (int)sizeof(Smem<2>) : (int)sizeof(Smem<4>);
     const int fixed = align_up(smem_struct, 128) + p.tps * (plane_bytes<WT>(p.n_in, rows) + chunk_sum_bytes<WT>(p.n_in, rows));
     // Depth of the ring: as many stages as fit beside the prepared activation in half an SM, at most
-    // kMaxStages. Wide activations (large K) leave too little of a half, and the forms for more than two
-    // activation rows are compiled for one CTA per SM (more registers): those take the whole SM.
-    int max_fit = rows <= 2 ? (kSmemLimit - fixed) / p.stage_bytes : 0;
+    // kMaxStages. Wide activations (large K) leave too little of a half, and the forms compiled for one CTA
+    // per SM (more registers; see kTwoPerSm) take the whole SM.
+    const bool halves = rows <= 2 || (rows <= 4 && kTwoPerSm<WT, 2>);
+    int max_fit = halves ? (kSmemLimit - fixed) / p.stage_bytes : 0;
     if (max_fit < 3) max_fit = (kSmemWhole - fixed) / p.stage_bytes;
     p.n_stages = max_fit < kMaxStages ? max_fit : kMaxStages;
     if (p.n_stages < 2) return false;
@@ -1369,13 +1377,17 @@ int launch_rows(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
 // (KRK_CUDA_GEMV_CTAS_PER_SM=1): the other half is left to the next launch in the stream, which becomes
 // resident early, sets itself up and fills its ring while this one streams; measured on the layer-sized
 // matrices of a decode step the slower streaming of eight warps costs more than the overlap saves.
-int ctas_per_sm(size_t smem) {
+// The forms compiled for one CTA per SM (kTwoPerSm) get one whatever their shared memory: a grid of two per
+// SM would run as two waves and prepare the activation twice.
+template <int WT>
+int ctas_per_sm(size_t smem, int rows) {
     static const int want = [] {
         const char *e = std::getenv("KRK_CUDA_GEMV_CTAS_PER_SM");
         const int v = e ? std::atoi(e) : 0;
         return v == 1 ? 1 : 2;
     }();
-    return smem <= (size_t)kSmemLimit ? want : 1;
+    const bool halves = rows <= 2 || (rows <= 4 && kTwoPerSm<WT, 2>);
+    return halves && smem <= (size_t)kSmemLimit ? want : 1;
 }
 
 // Tensor maps are encoded on the host (a driver call of a microsecond or two) and kept per (matrix, box):
@@ -1496,7 +1508,7 @@ int launch_fmt(const GemvMat *mats, int n_mat, int64_t n_in, int rows, int accum
     if (total == 0) return 1;
     p.status = device_status_word();
     if (!p.status) return KRK_CUDA_EDEVICE;
-    const int sms = sm_count() * ctas_per_sm(smem);
+    const int sms = sm_count() * ctas_per_sm<WT>(smem, p.rows);
     const int grid = total < sms ? total : sms;
     p.gran_q = total / grid;
     p.gran_r = total % grid;
@@ -1539,7 +1551,7 @@ int launch_table_fmt(const StreamTable *table, int64_t n_in, int silu_pair, cons
     p.dev_table = table;
     p.status = device_status_word();
     if (!p.status) return KRK_CUDA_EDEVICE;
-    const int rc = launch_rows<WT>(p, sm_count() * ctas_per_sm(smem), smem, st);
+    const int rc = launch_rows<WT>(p, sm_count() * ctas_per_sm<WT>(smem, p.rows), smem, st);
     return rc == KRK_CUDA_OK ? 1 : rc;
 }
 
@@ -1567,7 +1579,7 @@ int launch_peers_fmt(const GemvMat &mat, int64_t n_in, int rows, const PeerScatt
     p.wait_peers = ps.wait_peers;
     p.peer_row_stride = ps.row_stride;
     p.peer_offset = ps.offset;
-    const int sms = sm_count() * ctas_per_sm(smem);
+    const int sms = sm_count() * ctas_per_sm<WT>(smem, p.rows);
     const int grid = total < sms ? total : sms;
     p.gran_q = total / grid;
     p.gran_r = total % grid;
