@@ -791,8 +791,11 @@ __device__ __forceinline__ uint32_t ld_q6(const uint8_t *blk, int off) {
     return *reinterpret_cast<const uint32_t *>(blk + off);
 }
 
-// q - 32 for four packed 6-bit values: add 0x60 (no carry: q <= 63), flip the sign bit.
-__device__ __forceinline__ uint32_t center_q6(uint32_t q) { return (q + 0x60606060u) ^ 0x80808080u; }
+// The A operand is 4 * (q - 32) as a signed byte: the low four quant bits at bits 2-5, the high two at bits 6-7
+// with the top one flipped (q - 32 is q with bit 5 flipped, read as a 6-bit two's complement; at the top of the
+// byte it needs no sign extension). The flip is done once per word of high bits, before the fields are split.
+// Four integer instructions per four quants against six for assembling q and then centring it; the factor 4
+// leaves with the block scale.
 
 template <int NG, bool ODD>
 __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *blkB, int kbase, const int8_t *const (&bp)[NG],
@@ -812,8 +815,8 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
         }
 #pragma unroll
         for (int i = 0; i < 2; i++) {
-            qhA[i] = ld_q6<ODD>(blkA, 128 + 32 * h + 16 * i + 4 * t);
-            qhB[i] = ld_q6<ODD>(blkB, 128 + 32 * h + 16 * i + 4 * t);
+            qhA[i] = ld_q6<ODD>(blkA, 128 + 32 * h + 16 * i + 4 * t) ^ 0xAAAAAAAAu;
+            qhB[i] = ld_q6<ODD>(blkB, 128 + 32 * h + 16 * i + 4 * t) ^ 0xAAAAAAAAu;
             scA[i] = ld_q6<ODD>(blkA, 192 + 8 * h + 4 * i);
             scB[i] = ld_q6<ODD>(blkB, 192 + 8 * h + 4 * i);
         }
@@ -824,12 +827,12 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
         for (int G = 0; G < 8; G++) {
             const int quad = G >> 1, s = G & 1;
             const uint32_t la = qlA[2 * (quad & 1) + s], lb = qlB[2 * (quad & 1) + s];
-            const uint32_t lowA = (quad & 2) ? (la >> 4) & 0x0F0F0F0Fu : la & 0x0F0F0F0Fu;
-            const uint32_t lowB = (quad & 2) ? (lb >> 4) & 0x0F0F0F0Fu : lb & 0x0F0F0F0Fu;
-            const uint32_t hiA = quad == 0 ? (qhA[s] << 4) : quad == 1 ? (qhA[s] << 2) : quad == 2 ? qhA[s] : (qhA[s] >> 2);
-            const uint32_t hiB = quad == 0 ? (qhB[s] << 4) : quad == 1 ? (qhB[s] << 2) : quad == 2 ? qhB[s] : (qhB[s] >> 2);
-            const uint32_t a0 = center_q6(lowA | (hiA & 0x30303030u));
-            const uint32_t a1 = center_q6(lowB | (hiB & 0x30303030u));
+            const uint32_t lowA = (quad & 2) ? (la >> 2) : (la << 2);
+            const uint32_t lowB = (quad & 2) ? (lb >> 2) : (lb << 2);
+            const uint32_t hiA = quad == 3 ? qhA[s] : (qhA[s] << (6 - 2 * quad));
+            const uint32_t hiB = quad == 3 ? qhB[s] : (qhB[s] << (6 - 2 * quad));
+            const uint32_t a0 = (lowA & 0x3C3C3C3Cu) | (hiA & 0xC0C0C0C0u);
+            const uint32_t a1 = (lowB & 0x3C3C3C3Cu) | (hiB & 0xC0C0C0C0u);
             const int sa = sext_byte(scA[G >> 2], G & 3), sb = sext_byte(scB[G >> 2], G & 3);
 #pragma unroll
             for (int mg = 0; mg < NG; mg++) {
@@ -843,8 +846,8 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
             }
         }
     }
-    const float dA = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blkA + 208)));
-    const float dB = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blkB + 208)));
+    const float dA = 0.25f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blkA + 208)));
+    const float dB = 0.25f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blkB + 208)));
 #pragma unroll
     for (int mg = 0; mg < NG; mg++) {
         acc.f[mg][0] = fmaf(dA, (float)I[mg][0], acc.f[mg][0]);
