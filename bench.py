@@ -687,6 +687,17 @@ def device_weights_q5_0(torch, n_out: int, n_in: int, gen):
     return w.view(n_out, nblk * 22)
 
 
+def device_weights_q5_1(torch, n_out: int, n_in: int, gen):
+    """Q5_1 blocks made on the device: nibbles and fifth bits uniform, d in [1e-3, 2e-2], m in [-0.1, 0.1] as f16."""
+    nblk = n_in // 32
+    w = torch.randint(0, 256, (n_out, nblk, 24), dtype=torch.uint8, device="cuda", generator=gen)
+    d = (1e-3 + 1.9e-2 * torch.rand((n_out, nblk), device="cuda", generator=gen)).to(torch.float16)
+    m = (0.2 * torch.rand((n_out, nblk), device="cuda", generator=gen) - 0.1).to(torch.float16)
+    w[..., 0:2] = d.view(torch.uint8).view(n_out, nblk, 2)
+    w[..., 2:4] = m.view(torch.uint8).view(n_out, nblk, 2)
+    return w.view(n_out, nblk * 24)
+
+
 def device_weights_q5_k(torch, n_out: int, n_in: int, gen):
     """Q5_K blocks made on the device: payload bytes uniform (5-bit quants and packed 6-bit scale/min uniform),
     d in [5e-4, 5e-3], dmin in [0, 5e-3] as f16."""
@@ -711,8 +722,11 @@ def decode_extra(torch, capi, gen, barrier):
              ("steady_q6_k_128256x4096", synth.Q6_K, 128256, 4096, device_weights_q6k),
              ("steady_q4_0_131072x4096", synth.Q4_0, 131072, 4096, device_weights_q4_0),
              ("steady_q5_k_65536x4096", synth.Q5_K, 65536, 4096, device_weights_q5_k),
+             ("steady_q5_0_65536x4096", synth.Q5_0, 65536, 4096, device_weights_q5_0),
+             ("steady_q5_1_65536x4096", synth.Q5_1, 65536, 4096, device_weights_q5_1),
              # a format without a streaming arm: the warp-per-row kernel, so that its gap is on record
-             ("warp_per_row_q5_0_65536x4096", synth.Q5_0, 65536, 4096, device_weights_q5_0)]
+             # (IQ4_NL blocks have the layout of Q4_0 blocks)
+             ("warp_per_row_iq4_nl_65536x4096", synth.IQ4_NL, 65536, 4096, device_weights_q4_0)]
     out = {}
     for name, wt, n_out, n_in, make in cases:
         wbytes = n_out * synth.row_bytes(wt, n_in)

@@ -75,6 +75,11 @@ template <> struct Fmt<KRK_CUDA_Q8_0> { static constexpr int unit_values = 128, 
 template <> struct Fmt<KRK_CUDA_Q5_K> { static constexpr int unit_values = 256, unit_bytes = 176, stride_mod = 32, tma = 1; };
 // Q4_0: eight 18-byte blocks are 144 bytes, the size of a Q4_K unit, so the stages are laid out the same way.
 template <> struct Fmt<KRK_CUDA_Q4_0> { static constexpr int unit_values = 256, unit_bytes = 144, stride_mod = 16, tma = 1; };
+// Q5_0: eight 22-byte blocks are 176 bytes, the size of a Q5_K unit (rows of a fragment load 44 words apart: no
+// bank is met twice). Q5_1: eight 24-byte blocks are 192 bytes, a pitch that would put rows g and g + 2 on the
+// same banks, so its stages arrive as per-row copies with a padded pitch.
+template <> struct Fmt<KRK_CUDA_Q5_0> { static constexpr int unit_values = 256, unit_bytes = 176, stride_mod = 16, tma = 1; };
+template <> struct Fmt<KRK_CUDA_Q5_1> { static constexpr int unit_values = 256, unit_bytes = 192, stride_mod = 16, tma = 0; };
 
 struct StreamParams {
     GemvMat mat[KRK_CUDA_MAX_GROUP];
@@ -179,6 +184,11 @@ __device__ __forceinline__ void mma_s8_k16_chain(int (&c)[4], uint32_t a0, uint3
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
         : "r"(a0), "r"(a1), "r"(b0));
 }
+__device__ __forceinline__ void mma_u8_k16_chain(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0));
+}
 __device__ __forceinline__ void mma_u8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
     asm("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
@@ -243,7 +253,8 @@ template <int WT>
 __host__ __device__ inline int plane_bytes(int n_in, int rows) { return align_up(rows * 3 * plane_stride(n_in), 128); }
 template <int WT>
 __host__ __device__ inline int chunk_sum_bytes(int n_in, int rows) {   // [row][4 limbs][n_in / 32] s8
-    return (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q5_K || WT == KRK_CUDA_Q4_0) ? align_up(rows * (n_in / 32) * 4, 128) : 0;   // Q4_0: [row][n_in / 32] f32
+    return (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q5_K || WT == KRK_CUDA_Q4_0 || WT == KRK_CUDA_Q5_1)
+               ? align_up(rows * (n_in / 32) * 4, 128) : 0;   // Q4_0, Q5_1: [row][n_in / 32] f32
 }
 
 // ---- the walk over this CTA's stages: identical in the producer and in the consumers -------------
@@ -377,6 +388,18 @@ __device__ __forceinline__ void quantize_slice(const float (&f)[Fmt<WT>::unit_va
             *reinterpret_cast<uint16_t *>(p1 + base + kb) = (uint16_t)(w1 >> 16);
             *reinterpret_cast<uint16_t *>(p2 + base + ka) = (uint16_t)(w2 & 0xFFFF);
             *reinterpret_cast<uint16_t *>(p2 + base + kb) = (uint16_t)(w2 >> 16);
+        } else if (WT == KRK_CUDA_Q5_0 && ((i >> 5) & 1) == 0) {
+            // As Q4_0, [16 of the low half][16 of the high half], but the quants of an even block start 6 bytes
+            // into it: its lanes take them rotated by two, [14,15, 0..13], so that lane t holds values 4t-2..4t+1
+            // of a half and their fifth bits are four neighbours of the rotated mask.
+            const int e = i & 15, base = (i & ~31) + (i & 16);
+            const int ka = (e + 2) & 15, kb = (e + 4) & 15;
+            *reinterpret_cast<uint16_t *>(p0 + base + ka) = (uint16_t)(w0 & 0xFFFF);
+            *reinterpret_cast<uint16_t *>(p0 + base + kb) = (uint16_t)(w0 >> 16);
+            *reinterpret_cast<uint16_t *>(p1 + base + ka) = (uint16_t)(w1 & 0xFFFF);
+            *reinterpret_cast<uint16_t *>(p1 + base + kb) = (uint16_t)(w1 >> 16);
+            *reinterpret_cast<uint16_t *>(p2 + base + ka) = (uint16_t)(w2 & 0xFFFF);
+            *reinterpret_cast<uint16_t *>(p2 + base + kb) = (uint16_t)(w2 >> 16);
         } else if (WT == KRK_CUDA_Q4_0) {
             // A block's 16 quant bytes hold value j in their low and value 16 + j in their high nibbles, so the
             // limbs of a block lie as [16 of the low half][16 of the high half], each in the order the lanes take
@@ -404,8 +427,9 @@ __device__ __forceinline__ void quantize_slice(const float (&f)[Fmt<WT>::unit_va
             *reinterpret_cast<uint32_t *>(p2 + i) = w2;
         }
     }
-    if (WT == KRK_CUDA_Q4_0) {
+    if (WT == KRK_CUDA_Q4_0 || WT == KRK_CUDA_Q5_1) {
         // the sum of X over each 32-value block, as a float: the -8 of every quant leaves -8 * d * sum per block
+        // (Q5_1: the block's offset m enters as m * sum)
         total += __shfl_xor_sync(0xFFFFFFFFu, total, 1);
         total += __shfl_xor_sync(0xFFFFFFFFu, total, 2);
         if ((lane & 3) == 0) reinterpret_cast<float *>(sums)[k0 >> 5] = (float)total;   // |sum| < 2^28
@@ -746,6 +770,97 @@ __device__ __forceinline__ void unit_q4_0_rows(const uint8_t *rowA, const uint8_
     }
 }
 
+// Bits 0..3 of n to bit 7 of bytes 0..3: bit i times 2^(7j + 7) lands at 8k + 7 only for i = j = k, and no two
+// products share a position, so nothing carries.
+__device__ __forceinline__ uint32_t spread_top(uint32_t n) { return (n * 0x10204080u) & 0x80808080u; }
+
+// Eight Q5_0 blocks (src/quant.cpp:352-364): a 2-byte scale d, a 32-bit mask of fifth bits, 16 bytes whose low
+// nibbles are quants 0..15 and whose high nibbles are quants 16..31; the value is d * (q - 16). The A operand is
+// 8 * (q - 16) as a signed byte: the nibble at bits 3-6 and the inverted fifth bit at bit 7 (q - 16 is q with
+// bit 4 flipped, read as a 5-bit two's complement); the 8 leaves with d. Two k16 MMAs per block and column
+// group, chained on one accumulator preset to the bits of 1.5 * 2^23 (|sum| <= 32 * 128 * 128 = 2^19). Blocks at
+// an even index have mask and quants 2 bytes off a word boundary: the mask is glued from two words, lane t takes
+// quant bytes 4t-2..4t+1 (lane 0: 14, 15, 0, 1) and the mask is rotated to match.
+template <int NG>
+__device__ __forceinline__ void unit_q5_0(const uint8_t *rowA, const uint8_t *rowB, int kbase, const int8_t *const (&bp)[NG],
+                                          int t, Accum<NG> &acc) {
+#pragma unroll
+    for (int b = 0; b < 8; b++) {
+        uint32_t qa, qb, ma, mb;
+        float dA, dB;
+        if ((b & 1) == 0) {
+            const uint32_t *wa = reinterpret_cast<const uint32_t *>(rowA + 22 * b);
+            const uint32_t *wb = reinterpret_cast<const uint32_t *>(rowB + 22 * b);
+            const uint32_t a0 = wa[0], a1 = wa[1], b0 = wb[0], b1 = wb[1];
+            qa = t == 0 ? __byte_perm(a1, wa[5], 0x3254) : wa[t + 1];
+            qb = t == 0 ? __byte_perm(b1, wb[5], 0x3254) : wb[t + 1];
+            const uint32_t ha = ~__byte_perm(a0, a1, 0x5432), hb = ~__byte_perm(b0, b1, 0x5432);
+            ma = ((ha << 2) & 0xFFFCFFFCu) | ((ha >> 14) & 0x00030003u);   // both 16-bit halves rotated left by 2
+            mb = ((hb << 2) & 0xFFFCFFFCu) | ((hb >> 14) & 0x00030003u);
+            dA = half_lo(a0);
+            dB = half_lo(b0);
+        } else {
+            qa = reinterpret_cast<const uint32_t *>(rowA + 22 * b + 6)[t];
+            qb = reinterpret_cast<const uint32_t *>(rowB + 22 * b + 6)[t];
+            ma = ~*reinterpret_cast<const uint32_t *>(rowA + 22 * b + 2);
+            mb = ~*reinterpret_cast<const uint32_t *>(rowB + 22 * b + 2);
+            dA = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(rowA + 22 * b)));
+            dB = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(rowB + 22 * b)));
+        }
+        const uint32_t la = ((qa << 3) & 0x78787878u) | spread_top((ma >> (4 * t)) & 0xFu);
+        const uint32_t lb = ((qb << 3) & 0x78787878u) | spread_top((mb >> (4 * t)) & 0xFu);
+        const uint32_t ha = ((qa >> 1) & 0x78787878u) | spread_top((ma >> (16 + 4 * t)) & 0xFu);
+        const uint32_t hb = ((qb >> 1) & 0x78787878u) | spread_top((mb >> (16 + 4 * t)) & 0xFu);
+        dA *= 0.125f;
+        dB *= 0.125f;
+#pragma unroll
+        for (int mg = 0; mg < NG; mg++) {
+            const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 4 * t);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 16 + 4 * t);
+            int c[4] = {0x4B400000, 0x4B400000, 0x4B400000, 0x4B400000};
+            mma_s8_k16_chain(c, la, lb, b0);
+            mma_s8_k16_chain(c, ha, hb, b1);
+            acc.f[mg][0] = fmaf(dA, __int_as_float(c[0]) - kMagic, acc.f[mg][0]);
+            acc.f[mg][1] = fmaf(dA, __int_as_float(c[1]) - kMagic, acc.f[mg][1]);
+            acc.f[mg][2] = fmaf(dB, __int_as_float(c[2]) - kMagic, acc.f[mg][2]);
+            acc.f[mg][3] = fmaf(dB, __int_as_float(c[3]) - kMagic, acc.f[mg][3]);
+        }
+    }
+}
+
+// Eight Q5_1 blocks (src/quant.cpp:366-379): scale d, offset m, the mask, the nibbles, all on word boundaries;
+// the value is d * q + m with q = 0..31. The A operand is 8 * q as an unsigned byte; the offset enters as
+// m * (sum of X over the block), which the activation pass leaves per block as a float: the lanes whose columns
+// carry the limb of weight 1 (column 2 of the even, column 5 of the odd activation row of a group) add it.
+template <int NG>
+__device__ __forceinline__ void unit_q5_1(const uint8_t *rowA, const uint8_t *rowB, int kbase, const int8_t *const (&bp)[NG],
+                                          const float *const (&fe)[NG], const float *const (&fo)[NG], int t, Accum<NG> &acc) {
+#pragma unroll
+    for (int b = 0; b < 8; b++) {
+        const uint32_t *wa = reinterpret_cast<const uint32_t *>(rowA + 24 * b);
+        const uint32_t *wb = reinterpret_cast<const uint32_t *>(rowB + 24 * b);
+        const uint32_t a0 = wa[0], b0w = wb[0], ma = wa[1], mb = wb[1], qa = wa[2 + t], qb = wb[2 + t];
+        const float dA = 0.125f * half_lo(a0), dB = 0.125f * half_lo(b0w), oA = half_hi(a0), oB = half_hi(b0w);
+        const uint32_t la = ((qa << 3) & 0x78787878u) | spread_top((ma >> (4 * t)) & 0xFu);
+        const uint32_t lb = ((qb << 3) & 0x78787878u) | spread_top((mb >> (4 * t)) & 0xFu);
+        const uint32_t ha = ((qa >> 1) & 0x78787878u) | spread_top((ma >> (16 + 4 * t)) & 0xFu);
+        const uint32_t hb = ((qb >> 1) & 0x78787878u) | spread_top((mb >> (16 + 4 * t)) & 0xFu);
+#pragma unroll
+        for (int mg = 0; mg < NG; mg++) {
+            const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 4 * t);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 16 + 4 * t);
+            int c[4] = {0x4B400000, 0x4B400000, 0x4B400000, 0x4B400000};   // |sum| <= 32 * 248 * 128 < 2^20
+            mma_u8_k16_chain(c, la, lb, b0);
+            mma_u8_k16_chain(c, ha, hb, b1);
+            const float se = t == 1 ? fe[mg][(kbase >> 5) + b] : 0.0f, so = t == 2 ? fo[mg][(kbase >> 5) + b] : 0.0f;
+            acc.f[mg][0] = fmaf(dA, __int_as_float(c[0]) - kMagic, fmaf(oA, se, acc.f[mg][0]));
+            acc.f[mg][1] = fmaf(dA, __int_as_float(c[1]) - kMagic, fmaf(oA, so, acc.f[mg][1]));
+            acc.f[mg][2] = fmaf(dB, __int_as_float(c[2]) - kMagic, fmaf(oB, se, acc.f[mg][2]));
+            acc.f[mg][3] = fmaf(dB, __int_as_float(c[3]) - kMagic, fmaf(oB, so, acc.f[mg][3]));
+        }
+    }
+}
+
 // Four Q8_0 blocks. A block is a 2-byte scale then 32 quants, so blocks at an even index have
 // their quants 2 bytes off a word boundary: their lanes read the aligned words and lane t = 0
 // glues the two half words at the ends into one (the activation limbs are permuted to match).
@@ -1076,6 +1191,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     const int wid = warp - 1, g = lane >> 2, t = lane & 3;
     const float *prepared = nullptr;
     const int8_t *bp[NG], *sp[NG];
+    const float *fe[NG], *fo[NG];
     float xs[2 * NG];   // this warp's scale of each activation row
     Accum<NG> acc;
     AccumSingle acs;
@@ -1130,6 +1246,13 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                                    : 0.0f;
             __syncwarp();
             if (!SINGLE) lane_planes<NG>(planes, chunk_sum, p.n_in, p.rows, g, bp, sp);
+            if (WT == KRK_CUDA_Q5_1) {
+#pragma unroll
+                for (int mg = 0; mg < NG; mg++) {   // per-block sums of the group's even and odd activation rows
+                    fe[mg] = reinterpret_cast<const float *>(chunk_sum) + (size_t)min(2 * mg, p.rows - 1) * (p.n_in >> 5);
+                    fo[mg] = reinterpret_cast<const float *>(chunk_sum) + (size_t)min(2 * mg + 1, p.rows - 1) * (p.n_in >> 5);
+                }
+            }
             if (SINGLE == 2 && !stacked_idle) {
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
@@ -1163,6 +1286,10 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                             unit_q4_k<NG, WT == KRK_CUDA_Q5_K>(rowA, rowB, kbase, bp, sp, t, acc);
                         } else if (WT == KRK_CUDA_Q8_0) {
                             unit_q8_0<NG>(rowA, rowB, kbase, bp, t, acc);
+                        } else if (WT == KRK_CUDA_Q5_0) {
+                            unit_q5_0<NG>(rowA, rowB, kbase, bp, t, acc);
+                        } else if (WT == KRK_CUDA_Q5_1) {
+                            unit_q5_1<NG>(rowA, rowB, kbase, bp, fe, fo, t, acc);
                         } else {
                             if (unit & 1) unit_q6_k<NG, true>(rowA, rowB, kbase, bp, t, acc);
                             else unit_q6_k<NG, false>(rowA, rowB, kbase, bp, t, acc);
@@ -1632,6 +1759,8 @@ int launch_gemv_stream(const GemvMat *mats, int n_mat, int64_t n_in, int rows, i
     case KRK_CUDA_Q8_0: return launch_fmt<KRK_CUDA_Q8_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q4_0: return launch_fmt<KRK_CUDA_Q4_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q5_K: return launch_fmt<KRK_CUDA_Q5_K>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
+    case KRK_CUDA_Q5_0: return launch_fmt<KRK_CUDA_Q5_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
+    case KRK_CUDA_Q5_1: return launch_fmt<KRK_CUDA_Q5_1>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     default: return 0;   // the other formats take the shape-agnostic kernel
     }
 }
@@ -1644,6 +1773,8 @@ int launch_gemv_stream_table(const StreamTable *table, int wt, int64_t n_in, int
     case KRK_CUDA_Q8_0: return launch_table_fmt<KRK_CUDA_Q8_0>(table, n_in, silu_pair, banks, st);
     case KRK_CUDA_Q4_0: return launch_table_fmt<KRK_CUDA_Q4_0>(table, n_in, silu_pair, banks, st);
     case KRK_CUDA_Q5_K: return launch_table_fmt<KRK_CUDA_Q5_K>(table, n_in, silu_pair, banks, st);
+    case KRK_CUDA_Q5_0: return launch_table_fmt<KRK_CUDA_Q5_0>(table, n_in, silu_pair, banks, st);
+    case KRK_CUDA_Q5_1: return launch_table_fmt<KRK_CUDA_Q5_1>(table, n_in, silu_pair, banks, st);
     default: return 0;
     }
 }
@@ -1655,6 +1786,8 @@ int launch_gemv_stream_peers(const GemvMat &mat, int64_t n_in, int rows, const P
     case KRK_CUDA_Q8_0: return launch_peers_fmt<KRK_CUDA_Q8_0>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q4_0: return launch_peers_fmt<KRK_CUDA_Q4_0>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q5_K: return launch_peers_fmt<KRK_CUDA_Q5_K>(mat, n_in, rows, ps, st);
+    case KRK_CUDA_Q5_0: return launch_peers_fmt<KRK_CUDA_Q5_0>(mat, n_in, rows, ps, st);
+    case KRK_CUDA_Q5_1: return launch_peers_fmt<KRK_CUDA_Q5_1>(mat, n_in, rows, ps, st);
     default: return 0;
     }
 }
@@ -1674,6 +1807,8 @@ int stream_gran(int wt, int64_t n_in, bool banks) {
     case KRK_CUDA_Q8_0: return gran_fmt<KRK_CUDA_Q8_0>(n_in, banks);
     case KRK_CUDA_Q4_0: return gran_fmt<KRK_CUDA_Q4_0>(n_in, banks);
     case KRK_CUDA_Q5_K: return gran_fmt<KRK_CUDA_Q5_K>(n_in, banks);
+    case KRK_CUDA_Q5_0: return gran_fmt<KRK_CUDA_Q5_0>(n_in, banks);
+    case KRK_CUDA_Q5_1: return gran_fmt<KRK_CUDA_Q5_1>(n_in, banks);
     default: return 0;
     }
 }

@@ -21,7 +21,7 @@ from __future__ import annotations
 import numpy as np
 
 Q4_0, Q8_0, Q4_K, Q6_K = 2, 8, 12, 14
-Q5_0, Q5_1, Q5_K = 6, 7, 13          # the further formats of mixed files (shape-agnostic kernels only)
+Q5_0, Q5_1, Q5_K = 6, 7, 13          # the further formats of mixed files
 Q2_K, Q3_K, IQ4_NL = 10, 11, 20
 FORMATS = (Q8_0, Q4_0, Q4_K, Q6_K)
 MORE_FORMATS = (Q5_0, Q5_1, Q5_K, Q2_K, Q3_K, IQ4_NL)
