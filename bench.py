@@ -698,6 +698,16 @@ def device_weights_q5_1(torch, n_out: int, n_in: int, gen):
     return w.view(n_out, nblk * 24)
 
 
+def device_weights_q2_k(torch, n_out: int, n_in: int, gen):
+    """Q2_K blocks made on the device: 16 scale/min bytes and 64 quant bytes uniform, d and dmin in [1e-3, 1e-2] as
+    f16 at the end of the 84-byte block."""
+    nblk = n_in // 256
+    w = torch.randint(0, 256, (n_out, nblk, 84), dtype=torch.uint8, device="cuda", generator=gen)
+    d = (1e-3 + 9e-3 * torch.rand((n_out, nblk, 2), device="cuda", generator=gen)).to(torch.float16)
+    w[..., 80:84] = d.view(torch.uint8).view(n_out, nblk, 4)
+    return w.view(n_out, nblk * 84)
+
+
 def device_weights_q5_k(torch, n_out: int, n_in: int, gen):
     """Q5_K blocks made on the device: payload bytes uniform (5-bit quants and packed 6-bit scale/min uniform),
     d in [5e-4, 5e-3], dmin in [0, 5e-3] as f16."""
@@ -724,9 +734,10 @@ def decode_extra(torch, capi, gen, barrier):
              ("steady_q5_k_65536x4096", synth.Q5_K, 65536, 4096, device_weights_q5_k),
              ("steady_q5_0_65536x4096", synth.Q5_0, 65536, 4096, device_weights_q5_0),
              ("steady_q5_1_65536x4096", synth.Q5_1, 65536, 4096, device_weights_q5_1),
-             # a format without a streaming arm: the warp-per-row kernel, so that its gap is on record
              # (IQ4_NL blocks have the layout of Q4_0 blocks)
-             ("warp_per_row_iq4_nl_65536x4096", synth.IQ4_NL, 65536, 4096, device_weights_q4_0)]
+             ("steady_iq4_nl_131072x4096", synth.IQ4_NL, 131072, 4096, device_weights_q4_0),
+             # a format without a streaming arm: the warp-per-row kernel, so that its gap is on record
+             ("warp_per_row_q2_k_65536x4096", synth.Q2_K, 65536, 4096, device_weights_q2_k)]
     out = {}
     for name, wt, n_out, n_in, make in cases:
         wbytes = n_out * synth.row_bytes(wt, n_in)

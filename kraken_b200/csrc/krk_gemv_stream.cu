@@ -79,6 +79,8 @@ template <> struct Fmt<KRK_CUDA_Q4_0> { static constexpr int unit_values = 256, 
 // bank is met twice). Q5_1: eight 24-byte blocks are 192 bytes, a pitch that would put rows g and g + 2 on the
 // same banks, so its stages arrive as per-row copies with a padded pitch.
 template <> struct Fmt<KRK_CUDA_Q5_0> { static constexpr int unit_values = 256, unit_bytes = 176, stride_mod = 16, tma = 1; };
+// IQ4_NL: Q4_0's block with grid indices in place of quants.
+template <> struct Fmt<KRK_CUDA_IQ4_NL> { static constexpr int unit_values = 256, unit_bytes = 144, stride_mod = 16, tma = 1; };
 template <> struct Fmt<KRK_CUDA_Q5_1> { static constexpr int unit_values = 256, unit_bytes = 192, stride_mod = 16, tma = 0; };
 
 struct StreamParams {
@@ -400,7 +402,7 @@ __device__ __forceinline__ void quantize_slice(const float (&f)[Fmt<WT>::unit_va
             *reinterpret_cast<uint16_t *>(p1 + base + kb) = (uint16_t)(w1 >> 16);
             *reinterpret_cast<uint16_t *>(p2 + base + ka) = (uint16_t)(w2 & 0xFFFF);
             *reinterpret_cast<uint16_t *>(p2 + base + kb) = (uint16_t)(w2 >> 16);
-        } else if (WT == KRK_CUDA_Q4_0) {
+        } else if (WT == KRK_CUDA_Q4_0 || WT == KRK_CUDA_IQ4_NL) {
             // A block's 16 quant bytes hold value j in their low and value 16 + j in their high nibbles, so the
             // limbs of a block lie as [16 of the low half][16 of the high half], each in the order the lanes take
             // the quant bytes: as they are in odd blocks; [0,1,14,15, 2..13] in even blocks, whose quants start
@@ -760,6 +762,67 @@ __device__ __forceinline__ void unit_q4_0_rows(const uint8_t *rowA, const uint8_
             const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 4 * t);
             const uint32_t b1 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 16 + 4 * t);
             int c[4] = {0x4B400000, 0x4B400000, 0x4B400000, 0x4B400000};
+            mma_s8_k16_chain(c, la, lb, b0);
+            mma_s8_k16_chain(c, ha, hb, b1);
+            acc.f[mg][0] = fmaf(dA, __int_as_float(c[0]) - kMagic, acc.f[mg][0]);
+            acc.f[mg][1] = fmaf(dA, __int_as_float(c[1]) - kMagic, acc.f[mg][1]);
+            acc.f[mg][2] = fmaf(dB, __int_as_float(c[2]) - kMagic, acc.f[mg][2]);
+            acc.f[mg][3] = fmaf(dB, __int_as_float(c[3]) - kMagic, acc.f[mg][3]);
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+
+// Eight IQ4_NL blocks (src/quant.cpp:88-91, 566-575): Q4_0's layout, but a nibble is an index into a grid of 16
+// signed bytes. The grid lies in four words; a byte permute looks four indices up in two of them at a time (the
+// low three bits of each nibble of the selector), once in the lower and once in the upper half of the grid, and
+// the index's top bit picks between the two through a mask made by another permute in its sign-replicating mode.
+// Nibbles 0..3 of a quant word are [low 0, high 0, low 1, high 1], so two last permutes regroup the results into
+// the four low-nibble and the four high-nibble values. 13 integer instructions per eight values. The limbs lie
+// as for Q4_0.
+template <int NG>
+__device__ __forceinline__ void unit_iq4_nl(const uint8_t *rowA, const uint8_t *rowB, int kbase, const int8_t *const (&bp)[NG],
+                                            int t, Accum<NG> &acc) {
+    constexpr uint32_t kG0 = 0xBFAD9881u, kG1 = 0xF6EADDCFu, kG2 = 0x26190D01u, kG3 = 0x71594535u;
+    auto grid = [&](uint32_t q, uint32_t &lo4, uint32_t &hi4) {
+        const uint32_t s = q & 0x77777777u, s2 = s >> 16, y = q << 4;
+        const uint32_t m01 = prmt(y, q, 0xD9C8u), m23 = prmt(y, q, 0xFBEAu);   // 0xFF where the index is 8..15
+        const uint32_t r01 = (prmt(kG0, kG1, s) & ~m01) | (prmt(kG2, kG3, s) & m01);
+        const uint32_t r23 = (prmt(kG0, kG1, s2) & ~m23) | (prmt(kG2, kG3, s2) & m23);
+        lo4 = prmt(r01, r23, 0x6420u);
+        hi4 = prmt(r01, r23, 0x7531u);
+    };
+#pragma unroll
+    for (int b = 0; b < 8; b++) {
+        uint32_t qa, qb;
+        float dA, dB;
+        if ((b & 1) == 0) {
+            const uint32_t *wa = reinterpret_cast<const uint32_t *>(rowA + 18 * b);
+            const uint32_t *wb = reinterpret_cast<const uint32_t *>(rowB + 18 * b);
+            const uint32_t a_first = wa[0], b_first = wb[0];
+            qa = t == 0 ? __byte_perm(a_first, wa[4], 0x5432) : wa[t];
+            qb = t == 0 ? __byte_perm(b_first, wb[4], 0x5432) : wb[t];
+            dA = half_lo(a_first);
+            dB = half_lo(b_first);
+        } else {
+            qa = reinterpret_cast<const uint32_t *>(rowA + 18 * b + 2)[t];
+            qb = reinterpret_cast<const uint32_t *>(rowB + 18 * b + 2)[t];
+            dA = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(rowA + 18 * b)));
+            dB = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(rowB + 18 * b)));
+        }
+        uint32_t la, ha, lb, hb;
+        grid(qa, la, ha);
+        grid(qb, lb, hb);
+#pragma unroll
+        for (int mg = 0; mg < NG; mg++) {
+            const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 4 * t);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 16 + 4 * t);
+            int c[4] = {0x4B400000, 0x4B400000, 0x4B400000, 0x4B400000};   // |sum| <= 32 * 127 * 128 < 2^19
             mma_s8_k16_chain(c, la, lb, b0);
             mma_s8_k16_chain(c, ha, hb, b1);
             acc.f[mg][0] = fmaf(dA, __int_as_float(c[0]) - kMagic, acc.f[mg][0]);
@@ -1288,6 +1351,8 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                             unit_q8_0<NG>(rowA, rowB, kbase, bp, t, acc);
                         } else if (WT == KRK_CUDA_Q5_0) {
                             unit_q5_0<NG>(rowA, rowB, kbase, bp, t, acc);
+                        } else if (WT == KRK_CUDA_IQ4_NL) {
+                            unit_iq4_nl<NG>(rowA, rowB, kbase, bp, t, acc);
                         } else if (WT == KRK_CUDA_Q5_1) {
                             unit_q5_1<NG>(rowA, rowB, kbase, bp, fe, fo, t, acc);
                         } else {
@@ -1759,6 +1824,7 @@ int launch_gemv_stream(const GemvMat *mats, int n_mat, int64_t n_in, int rows, i
     case KRK_CUDA_Q8_0: return launch_fmt<KRK_CUDA_Q8_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q4_0: return launch_fmt<KRK_CUDA_Q4_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q5_K: return launch_fmt<KRK_CUDA_Q5_K>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
+    case KRK_CUDA_IQ4_NL: return launch_fmt<KRK_CUDA_IQ4_NL>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q5_0: return launch_fmt<KRK_CUDA_Q5_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q5_1: return launch_fmt<KRK_CUDA_Q5_1>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     default: return 0;   // the other formats take the shape-agnostic kernel
@@ -1773,6 +1839,7 @@ int launch_gemv_stream_table(const StreamTable *table, int wt, int64_t n_in, int
     case KRK_CUDA_Q8_0: return launch_table_fmt<KRK_CUDA_Q8_0>(table, n_in, silu_pair, banks, st);
     case KRK_CUDA_Q4_0: return launch_table_fmt<KRK_CUDA_Q4_0>(table, n_in, silu_pair, banks, st);
     case KRK_CUDA_Q5_K: return launch_table_fmt<KRK_CUDA_Q5_K>(table, n_in, silu_pair, banks, st);
+    case KRK_CUDA_IQ4_NL: return launch_table_fmt<KRK_CUDA_IQ4_NL>(table, n_in, silu_pair, banks, st);
     case KRK_CUDA_Q5_0: return launch_table_fmt<KRK_CUDA_Q5_0>(table, n_in, silu_pair, banks, st);
     case KRK_CUDA_Q5_1: return launch_table_fmt<KRK_CUDA_Q5_1>(table, n_in, silu_pair, banks, st);
     default: return 0;
@@ -1786,6 +1853,7 @@ int launch_gemv_stream_peers(const GemvMat &mat, int64_t n_in, int rows, const P
     case KRK_CUDA_Q8_0: return launch_peers_fmt<KRK_CUDA_Q8_0>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q4_0: return launch_peers_fmt<KRK_CUDA_Q4_0>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q5_K: return launch_peers_fmt<KRK_CUDA_Q5_K>(mat, n_in, rows, ps, st);
+    case KRK_CUDA_IQ4_NL: return launch_peers_fmt<KRK_CUDA_IQ4_NL>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q5_0: return launch_peers_fmt<KRK_CUDA_Q5_0>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q5_1: return launch_peers_fmt<KRK_CUDA_Q5_1>(mat, n_in, rows, ps, st);
     default: return 0;
@@ -1807,6 +1875,7 @@ int stream_gran(int wt, int64_t n_in, bool banks) {
     case KRK_CUDA_Q8_0: return gran_fmt<KRK_CUDA_Q8_0>(n_in, banks);
     case KRK_CUDA_Q4_0: return gran_fmt<KRK_CUDA_Q4_0>(n_in, banks);
     case KRK_CUDA_Q5_K: return gran_fmt<KRK_CUDA_Q5_K>(n_in, banks);
+    case KRK_CUDA_IQ4_NL: return gran_fmt<KRK_CUDA_IQ4_NL>(n_in, banks);
     case KRK_CUDA_Q5_0: return gran_fmt<KRK_CUDA_Q5_0>(n_in, banks);
     case KRK_CUDA_Q5_1: return gran_fmt<KRK_CUDA_Q5_1>(n_in, banks);
     default: return 0;
