@@ -95,6 +95,9 @@ struct StreamParams {
     int row_bytes;
     int gran;             // rows per granule: 1, or 8 when rows are not 16-byte multiples
     int whole_tiles;      // 1: a stage is one contiguous copy of whole rows (unaligned row size)
+    int ragged;           // 1: rows are not 16-byte multiples and too long for whole tiles: every row of a stage is
+                          // copied from the 16-byte boundary below its first byte, and its bytes sit that far
+                          // (0..15 bytes, a multiple of 2) into the row's slot
     int tps;              // 16-row tiles stacked in one stage (> 1 when a row has so few K units that one
                           // tile would leave most consumer warps idle: warp w takes unit w % units of
                           // sub-tile w / units)
@@ -970,9 +973,16 @@ __device__ __forceinline__ void unit_q8_0(const uint8_t *rowA, const uint8_t *ro
 
 // 32-bit load at a 4-byte-multiple offset of a Q6_K block that itself starts 0 or 2 bytes off
 // a word boundary (blocks are 210 bytes, so odd blocks of a row are misaligned).
-template <bool ODD>
+// MODE 0: the block starts on a word boundary; 1: 2 bytes off; 2: either, found from the address (ragged rows:
+// the two rows of a lane may differ).
+template <int MODE>
 __device__ __forceinline__ uint32_t ld_q6(const uint8_t *blk, int off) {
-    if (ODD) {
+    if (MODE == 2) {
+        const uintptr_t a = reinterpret_cast<uintptr_t>(blk + off);
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+        return __funnelshift_r(w[0], w[1], (uint32_t)(a & 2) * 8u);
+    }
+    if (MODE == 1) {
         const uint32_t lo = *reinterpret_cast<const uint32_t *>(blk + off - 2);
         const uint32_t hi = *reinterpret_cast<const uint32_t *>(blk + off + 2);
         return __byte_perm(lo, hi, 0x5432);
@@ -986,7 +996,7 @@ __device__ __forceinline__ uint32_t ld_q6(const uint8_t *blk, int off) {
 // Four integer instructions per four quants against six for assembling q and then centring it; the factor 4
 // leaves with the block scale.
 
-template <int NG, bool ODD>
+template <int NG, int ODD>
 __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *blkB, int kbase, const int8_t *const (&bp)[NG],
                                           int t, Accum<NG> &acc) {
     int I[NG][4];
@@ -1133,6 +1143,23 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                     } else {
                         tma_box(smem_u32(dst), &p.wmap[s.mat], s.row0, s.unit0 / p.tma_unit_div, full);
                     }
+                }
+            } else if (p.ragged) {
+                // a stage starts a multiple of 8 units (1680 bytes) into its rows, so a row lies equally far off
+                // a 16-byte boundary in every stage
+                const uint32_t bytes = (uint32_t)s.n_units * F::unit_bytes;
+                uint32_t total = 0;
+                for (int r = lane; r < s.n_rows; r += 32) {
+                    const uint32_t a = (uint32_t)(reinterpret_cast<uintptr_t>(src + (size_t)r * p.row_bytes) & 15);
+                    total += (a + bytes + 15u) & ~15u;
+                }
+                total = __reduce_add_sync(0xFFFFFFFFu, total);
+                if (lane == 0) mbar_arrive_expect_tx(full, total);
+                __syncwarp();
+                for (int r = lane; r < s.n_rows; r += 32) {
+                    const uint8_t *row = src + (size_t)r * p.row_bytes + (size_t)s.unit0 * F::unit_bytes;
+                    const uint32_t a = (uint32_t)(reinterpret_cast<uintptr_t>(row) & 15);
+                    bulk_g2s(smem_u32(dst + r * p.row_stride), row - a, (a + bytes + 15u) & ~15u, full);
                 }
             } else if (!p.whole_tiles) {
                 const uint32_t bytes = (uint32_t)s.n_units * F::unit_bytes;
@@ -1327,6 +1354,14 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         const int stage_rows = kTileRows * tps;
         const int n_tiles = ((r1 - r0 + stage_rows - 1) / stage_rows) * p.step;
         for (int tile = 0; tile < n_tiles; tile++) {
+            // ragged rows: how far this lane's two rows sit into their slots of a stage
+            uint32_t ragA = 0, ragB = 0;
+            if (WT == KRK_CUDA_Q6_K && p.ragged) {
+                const int row = r0 + (tile / p.step) * stage_rows + kTileRows * my_sub + g;
+                const uintptr_t base = reinterpret_cast<uintptr_t>(tv.mat[m + tile % p.step].w);
+                ragA = (uint32_t)((base + (size_t)row * p.row_bytes) & 15);
+                ragB = (uint32_t)((base + (size_t)(row + 8) * p.row_bytes) & 15);
+            }
             // one stage of the tile: `bf` are the warp's held B fragments for it (SINGLE == 2), else unused
             auto stage = [&](const int ck, const BFrag &bf) {
                 wait_phase(full0 + 8 * slot, phase, gave_up, p.status);
@@ -1334,7 +1369,8 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                 if (!stacked_idle) {
                     const uint8_t *tile0 = stages + (size_t)slot * p.stage_bytes + lane_off;
                     for (int su = my_unit; su < stage_units; su += kConsumerWarps) {
-                        const uint8_t *rowA = tile0 + (size_t)su * p.unit_stride, *rowB = rowA + (size_t)8 * p.row_stride;
+                        const uint8_t *rowA = tile0 + (size_t)su * p.unit_stride + ragA;
+                        const uint8_t *rowB = tile0 + (size_t)su * p.unit_stride + (size_t)8 * p.row_stride + ragB;
                         const int unit = ck * kConsumerWarps + su;
                         const int kbase = unit * F::unit_values;
                         if (WT == KRK_CUDA_Q4_0 && !SINGLE) {
@@ -1356,8 +1392,9 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                         } else if (WT == KRK_CUDA_Q5_1) {
                             unit_q5_1<NG>(rowA, rowB, kbase, bp, fe, fo, t, acc);
                         } else {
-                            if (unit & 1) unit_q6_k<NG, true>(rowA, rowB, kbase, bp, t, acc);
-                            else unit_q6_k<NG, false>(rowA, rowB, kbase, bp, t, acc);
+                            if (p.ragged) unit_q6_k<NG, 2>(rowA, rowB, kbase, bp, t, acc);
+                            else if (unit & 1) unit_q6_k<NG, 1>(rowA, rowB, kbase, bp, t, acc);
+                            else unit_q6_k<NG, 0>(rowA, rowB, kbase, bp, t, acc);
                         }
                     }
                 }
@@ -1491,6 +1528,7 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
     p.accumulate = 0;
     p.step = silu_pair ? 2 : 1;
     p.whole_tiles = 0;
+    p.ragged = 0;
     p.gran = 1;
     p.dev_table = nullptr;
     p.n_peers = 0;
@@ -1498,10 +1536,14 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
     p.peer_row_stride = p.peer_offset = 0;
     if (WT == KRK_CUDA_Q6_K && (n_in % 2048) != 0) {
         // 210-byte blocks: rows are 16-byte multiples only for K % 2048 == 0. Otherwise whole 16-row
-        // tiles are copied contiguously (needs 4-byte-multiple rows and the tile in one stage).
-        if ((p.row_bytes & 3) != 0 || p.units > 2 * kConsumerWarps) return false;
-        p.whole_tiles = 1;
-        p.gran = 8;
+        // tiles are copied contiguously (needs 4-byte-multiple rows and the tile in one stage), or, for longer
+        // or odd rows (K = 11008: 9030 bytes), row by row from the 16-byte boundary below each row.
+        if ((p.row_bytes & 3) == 0 && p.units <= 2 * kConsumerWarps) {
+            p.whole_tiles = 1;
+            p.gran = 8;
+        } else {
+            p.ragged = 1;
+        }
     }
     const int ku_max = p.whole_tiles ? p.units : (p.units < kConsumerWarps ? p.units : kConsumerWarps);
     p.tps = kConsumerWarps / p.units;   // 0 when a tile has more units than there are consumer warps
@@ -1537,7 +1579,9 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
         p.row_stride = p.row_bytes;
         p.stage_bytes = align_up(kTileRows * p.tps * p.row_bytes, 128);
     } else {
-        const int raw = ku_max * F::unit_bytes;
+        // (ragged rows: up to 15 bytes before and 15 after the row's own, and a word of slack for the loads that
+        // glue a value from two words)
+        const int raw = ku_max * F::unit_bytes + (p.ragged ? 48 : 0);
         p.row_stride = raw + ((F::stride_mod - raw % 128) + 128) % 128;
         p.stage_bytes = align_up(kTileRows * p.tps * p.row_stride, 128);
     }

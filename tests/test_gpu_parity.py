@@ -175,6 +175,18 @@ def test_path_selection(cuda, oracle):
     run_gemv(cuda, oracle, synth.Q6_K, 4096, 1536, 1, SEED + 32, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q6_K, 1001, 1536, 8, SEED + 33, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q4_K, 1536, 4096, 8, SEED + 34, expect_stream=True)
+    # Q6_K rows that are neither 16-byte multiples nor short enough for whole tiles: copied row by row from the
+    # 16-byte boundary below (K = 11008: 9030-byte rows, 2-byte aligned; K = 5120: 4200 bytes; K = 768: stacked tiles)
+    run_gemv(cuda, oracle, synth.Q6_K, 4099, 11008, 1, SEED + 60, random_payload=True, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q6_K, 333, 11008, 2, SEED + 61, random_payload=True, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q6_K, 77, 11008, 4, SEED + 62, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q6_K, 77, 5120, 8, SEED + 69, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q6_K, 1001, 5120, 1, SEED + 63, random_payload=True, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q6_K, 100, 5120, 4, SEED + 64, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q6_K, 257, 768, 1, SEED + 65, random_payload=True, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q6_K, 40, 768, 3, SEED + 66, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q6_K, 5, 13824, 1, SEED + 67, expect_stream=True)
+    run_gemv(cuda, oracle, synth.Q6_K, 64, 11008, 1, SEED + 68, accumulate=True, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q8_0, 5, 256, 3, SEED + 35, expect_stream=True)
 
 
@@ -254,6 +266,30 @@ def test_gemv_group_own_x_mixed_types(cuda, oracle):
         ref = oracle.gemm(x, w, wt, w.shape[0], n_in)
         ok, worst = bound_ok(y.cpu().numpy()[None], ref, oracle.dequant_rows(w, wt, w.shape[0], n_in), x, GEMV_TOL)
         assert ok, (wt, worst)
+
+
+def test_gemv_group_ragged_q6k_rows(cuda, oracle):
+    """Groups and the gate/up fold over Q6_K rows that are copied from the 16-byte boundary below each row
+    (K = 5120 and K = 11008): matrices of one launch start at different offsets into their slots."""
+    seed = SEED + 70
+    for n_in, n_outs in ((5120, (333, 333, 48)), (11008, (100, 100, 17))):
+        x = synth.activations(1, n_in, seed)
+        ws = [synth.weights(synth.Q6_K, n, n_in, seed, stream=400 + i, random_payload=(i == 2)) for i, n in enumerate(n_outs)]
+        dx = dev(x)
+        before = cuda.family_count(cuda.FAMILY_GEMV_STREAM)
+        outs = cuda.gemv_group([dx] * 3, [dev(w) for w in ws], [synth.Q6_K] * 3, list(n_outs), n_in)
+        assert cuda.family_count(cuda.FAMILY_GEMV_STREAM) == before + 1
+        for w, y in zip(ws, outs):
+            ref = oracle.gemm(x, w, synth.Q6_K, w.shape[0], n_in)
+            ok, worst = bound_ok(y.cpu().numpy()[None], ref, oracle.dequant_rows(w, synth.Q6_K, w.shape[0], n_in), x, GEMV_TOL)
+            assert ok, (n_in, worst)
+        outs = cuda.gemv_group([dx] * 2, [dev(ws[0]), dev(ws[1])], [synth.Q6_K] * 2, list(n_outs[:2]), n_in, fuse_silu_pair=True)
+        g = oracle.gemm(x, ws[0], synth.Q6_K, n_outs[0], n_in)
+        u = oracle.gemm(x, ws[1], synth.Q6_K, n_outs[1], n_in)
+        want = oracle.silu_mul(g, u)[0]
+        got = outs[0].cpu().numpy()
+        assert np.abs(got - want).max() <= 2e-4 * np.abs(want).max() + 1e-6
+        assert cuda.device_status() == 0
 
 
 # ---- MoE --------------------------------------------------------------------------------------
