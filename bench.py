@@ -708,6 +708,16 @@ def device_weights_q2_k(torch, n_out: int, n_in: int, gen):
     return w.view(n_out, nblk * 84)
 
 
+def device_weights_q3_k(torch, n_out: int, n_in: int, gen):
+    """Q3_K blocks made on the device: mask, quant and packed scale bytes uniform, d in [1e-3, 1e-2] as f16 at the
+    end of the 110-byte block."""
+    nblk = n_in // 256
+    w = torch.randint(0, 256, (n_out, nblk, 110), dtype=torch.uint8, device="cuda", generator=gen)
+    d = (1e-3 + 9e-3 * torch.rand((n_out, nblk), device="cuda", generator=gen)).to(torch.float16)
+    w[..., 108:110] = d.view(torch.uint8).view(n_out, nblk, 2)
+    return w.view(n_out, nblk * 110)
+
+
 def device_weights_q5_k(torch, n_out: int, n_in: int, gen):
     """Q5_K blocks made on the device: payload bytes uniform (5-bit quants and packed 6-bit scale/min uniform),
     d in [5e-4, 5e-3], dmin in [0, 5e-3] as f16."""
@@ -736,8 +746,10 @@ def decode_extra(torch, capi, gen, barrier):
              ("steady_q5_1_65536x4096", synth.Q5_1, 65536, 4096, device_weights_q5_1),
              # (IQ4_NL blocks have the layout of Q4_0 blocks)
              ("steady_iq4_nl_131072x4096", synth.IQ4_NL, 131072, 4096, device_weights_q4_0),
-             # a format without a streaming arm: the warp-per-row kernel, so that its gap is on record
-             ("warp_per_row_q2_k_65536x4096", synth.Q2_K, 65536, 4096, device_weights_q2_k)]
+             ("steady_q2_k_131072x4096", synth.Q2_K, 131072, 4096, device_weights_q2_k),
+             ("steady_q3_k_131072x4096", synth.Q3_K, 131072, 4096, device_weights_q3_k),
+             # K not a multiple of 256: the warp-per-row kernel, so that its gap is on record
+             ("warp_per_row_q8_0_65536x4064", synth.Q8_0, 65536, 4064, device_weights_q8_0)]
     out = {}
     for name, wt, n_out, n_in, make in cases:
         wbytes = n_out * synth.row_bytes(wt, n_in)

@@ -33,7 +33,7 @@ extern "C" {
 #define KRK_CUDA_Q4_K 12
 #define KRK_CUDA_Q6_K 14
 /* further GGUF formats a Q4_K_M / Q5_K_M file mixes in: decoded bit-exactly and served by the prefill GEMM and,
- * for decode, by the streaming GEMV (Q5_K, Q5_0, Q5_1, IQ4_NL) or the shape-agnostic GEMV (Q2_K, Q3_K) */
+ * for decode, by the streaming GEMV (the shape-agnostic GEMV when K is not a multiple of 256) */
 #define KRK_CUDA_Q5_0 6
 #define KRK_CUDA_Q5_1 7
 #define KRK_CUDA_Q5_K 13

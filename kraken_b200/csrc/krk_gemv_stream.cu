@@ -1,5 +1,5 @@
-// Streaming decode GEMV for sm_100a: Q4_K, Q6_K and Q8_0 weights, 1..8 activation rows, up to
-// 16 matrices per launch.
+// Streaming decode GEMV for sm_100a: weights in any of the ten block formats (Q4_K, Q6_K, Q8_0, Q4_0, Q5_K, Q5_0,
+// Q5_1, IQ4_NL, Q2_K, Q3_K), K a multiple of 256, 1..8 activation rows, up to 16 matrices per launch.
 //
 // Design (B200-first, not the reference's one-warp-per-row walk of src/hip/kernels/gemm.hpp:76):
 //
@@ -79,6 +79,9 @@ template <> struct Fmt<KRK_CUDA_Q4_0> { static constexpr int unit_values = 256, 
 // bank is met twice). Q5_1: eight 24-byte blocks are 192 bytes, a pitch that would put rows g and g + 2 on the
 // same banks, so its stages arrive as per-row copies with a padded pitch.
 template <> struct Fmt<KRK_CUDA_Q5_0> { static constexpr int unit_values = 256, unit_bytes = 176, stride_mod = 16, tma = 1; };
+// Q2_K (84 bytes) and Q3_K (110 bytes): per-row copies; rows that are not 16-byte multiples go the ragged way.
+template <> struct Fmt<KRK_CUDA_Q2_K> { static constexpr int unit_values = 256, unit_bytes = 84, stride_mod = 16, tma = 0; };
+template <> struct Fmt<KRK_CUDA_Q3_K> { static constexpr int unit_values = 256, unit_bytes = 110, stride_mod = 16, tma = 0; };
 // IQ4_NL: Q4_0's block with grid indices in place of quants.
 template <> struct Fmt<KRK_CUDA_IQ4_NL> { static constexpr int unit_values = 256, unit_bytes = 144, stride_mod = 16, tma = 1; };
 template <> struct Fmt<KRK_CUDA_Q5_1> { static constexpr int unit_values = 256, unit_bytes = 192, stride_mod = 16, tma = 0; };
@@ -256,10 +259,14 @@ __host__ __device__ constexpr int align_up(int v, int a) { return (v + a - 1) / 
 __host__ __device__ inline int plane_stride(int n_in) { return n_in + kPlanePad; }
 template <int WT>
 __host__ __device__ inline int plane_bytes(int n_in, int rows) { return align_up(rows * 3 * plane_stride(n_in), 128); }
+// Sums of the quantised activation over the stretch of K that shares one minimum or offset: 32 values (2^5) for
+// Q4_K, Q5_K, Q4_0 and Q5_1, 16 for Q2_K.
 template <int WT>
-__host__ __device__ inline int chunk_sum_bytes(int n_in, int rows) {   // [row][4 limbs][n_in / 32] s8
-    return (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q5_K || WT == KRK_CUDA_Q4_0 || WT == KRK_CUDA_Q5_1)
-               ? align_up(rows * (n_in / 32) * 4, 128) : 0;   // Q4_0, Q5_1: [row][n_in / 32] f32
+constexpr int kSumShift = WT == KRK_CUDA_Q2_K ? 4 : 5;
+template <int WT>
+__host__ __device__ inline int chunk_sum_bytes(int n_in, int rows) {   // [row][4 limbs][n_in >> kSumShift] s8
+    return (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q5_K || WT == KRK_CUDA_Q4_0 || WT == KRK_CUDA_Q5_1 || WT == KRK_CUDA_Q2_K)
+               ? align_up(rows * (n_in >> kSumShift<WT>) * 4, 128) : 0;   // Q4_0, Q5_1: [row][n_in / 32] f32
 }
 
 // ---- the walk over this CTA's stages: identical in the producer and in the consumers -------------
@@ -439,12 +446,13 @@ __device__ __forceinline__ void quantize_slice(const float (&f)[Fmt<WT>::unit_va
         total += __shfl_xor_sync(0xFFFFFFFFu, total, 2);
         if ((lane & 3) == 0) reinterpret_cast<float *>(sums)[k0 >> 5] = (float)total;   // |sum| < 2^28
     }
-    if (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q5_K) {
-        // a 32-value chunk is held by 4 consecutive lanes; |sum| <= 32 * 127 * 2^16 < 2^28
+    if (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q5_K || WT == KRK_CUDA_Q2_K) {
+        // a 32-value chunk is held by 4 consecutive lanes (Q2_K: a 16-value group by 2); |sum| <= 32 * 2^22
+        constexpr int kLanes = WT == KRK_CUDA_Q2_K ? 2 : 4;
         total += __shfl_xor_sync(0xFFFFFFFFu, total, 1);
-        total += __shfl_xor_sync(0xFFFFFFFFu, total, 2);
-        if ((lane & 3) == 0) {
-            const int c = k0 >> 5;
+        if (kLanes == 4) total += __shfl_xor_sync(0xFFFFFFFFu, total, 2);
+        if ((lane & (kLanes - 1)) == 0) {
+            const int c = k0 >> kSumShift<WT>;
             const uint32_t z = limbs4(total);   // byte 0: limb 3 (weight 1) ... byte 3: limb 0 (2^24)
             sums[c] = (int8_t)(z >> 24);
             sums[n_chunks + c] = (int8_t)(z >> 16);
@@ -474,7 +482,7 @@ template <int WT>
 __device__ __forceinline__ float prepare_x_row(const float *__restrict__ xr, const StreamParams &p, int8_t *p0, int8_t *sums,
                                                int wid, int lane) {
     constexpr int UV = Fmt<WT>::unit_values, PER = UV / 32, kHeld = 2;
-    const int n_chunks = p.n_in >> 5, ps = plane_stride(p.n_in);
+    const int n_chunks = p.n_in >> kSumShift<WT>, ps = plane_stride(p.n_in);
     // the first two slices stay in registers between the max and the quantisation (K <= 4096 for
     // 256-value units); any further ones are read twice
     float held[kHeld][PER];
@@ -535,7 +543,7 @@ __device__ __forceinline__ void accum_zero(Accum<NG> &a) {
 // carries no limb (columns 6, 7, or an activation row past `rows`) reads some valid plane: its
 // accumulator columns are never looked at, so what it multiplies does not matter.
 template <int NG>
-__device__ __forceinline__ void lane_planes(const int8_t *planes, const int8_t *chunk_sum, int n_in, int rows, int g,
+__device__ __forceinline__ void lane_planes(const int8_t *planes, const int8_t *chunk_sum, int n_in, int n_sums, int rows, int g,
                                             const int8_t *(&bp)[NG], const int8_t *(&sp)[NG]) {
 #pragma unroll
     for (int mg = 0; mg < NG; mg++) {
@@ -543,7 +551,7 @@ __device__ __forceinline__ void lane_planes(const int8_t *planes, const int8_t *
         bp[mg] = planes + (size_t)(r * 3 + g % 3) * plane_stride(n_in);
         // chunk sums: column c = limb c%4 of activation row c/4 of the group
         const int rs = min(2 * mg + g / 4, rows - 1);
-        sp[mg] = chunk_sum + (size_t)(rs * 4 + g % 4) * (n_in >> 5);
+        sp[mg] = chunk_sum + (size_t)(rs * 4 + g % 4) * n_sums;
     }
 }
 
@@ -1056,6 +1064,133 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
     }
 }
 
+// A Q2_K super-block (src/quant.cpp:398-424): 16 bytes of (scale | min << 4), 64 bytes of 2-bit quants, d, dmin;
+// value = d * scale * q - dmin * min per group of 16. Blocks are 84 bytes, so every word load is aligned. Group
+// G = 8n + 2j + s takes bits 2j, 2j+1 of quant bytes 32n + 16s ..+15: one shift and one AND per four quants, one
+// k16 MMA per group. The minimums go through one more MMA per super-block, the 16 of them against the group
+// sums of X (acc.m, as for Q4_K).
+template <int NG>
+__device__ __forceinline__ void unit_q2_k(const uint8_t *blkA, const uint8_t *blkB, int kbase, const int8_t *const (&bp)[NG],
+                                          const int8_t *const (&sp)[NG], int t, Accum<NG> &acc) {
+    const uint32_t *wa = reinterpret_cast<const uint32_t *>(blkA), *wb = reinterpret_cast<const uint32_t *>(blkB);
+    uint32_t scA[4], scB[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        scA[k] = wa[k];
+        scB[k] = wb[k];
+    }
+    int I[NG][4];
+#pragma unroll
+    for (int mg = 0; mg < NG; mg++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) I[mg][j] = 0;
+#pragma unroll
+    for (int n = 0; n < 2; n++) {
+        const uint32_t qA[2] = {wa[4 + 8 * n + t], wa[8 + 8 * n + t]}, qB[2] = {wb[4 + 8 * n + t], wb[8 + 8 * n + t]};
+#pragma unroll
+        for (int js = 0; js < 8; js++) {
+            const int j = js >> 1, s = js & 1, G = 8 * n + js;
+            const uint32_t a0 = (qA[s] >> (2 * j)) & 0x03030303u, a1 = (qB[s] >> (2 * j)) & 0x03030303u;
+            const int sa = (scA[G >> 2] >> (8 * (G & 3))) & 0xF, sb = (scB[G >> 2] >> (8 * (G & 3))) & 0xF;
+#pragma unroll
+            for (int mg = 0; mg < NG; mg++) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 16 * G + 4 * t);
+                int cc[4];
+                mma_s8_k16(cc, a0, a1, b0);
+                I[mg][0] += sa * cc[0];
+                I[mg][1] += sa * cc[1];
+                I[mg][2] += sb * cc[2];
+                I[mg][3] += sb * cc[3];
+            }
+        }
+    }
+    const uint32_t hA = wa[20], hB = wb[20];
+    const float dA = half_lo(hA), dB = half_lo(hB), nA = half_hi(hA), nB = half_hi(hB);
+    const uint32_t m0 = (wa[t] >> 4) & 0x0F0F0F0Fu, m1 = (wb[t] >> 4) & 0x0F0F0F0Fu;   // k slot j = group j: lane t brings 4t..4t+3
+#pragma unroll
+    for (int mg = 0; mg < NG; mg++) {
+        acc.f[mg][0] = fmaf(dA, (float)I[mg][0], acc.f[mg][0]);
+        acc.f[mg][1] = fmaf(dA, (float)I[mg][1], acc.f[mg][1]);
+        acc.f[mg][2] = fmaf(dB, (float)I[mg][2], acc.f[mg][2]);
+        acc.f[mg][3] = fmaf(dB, (float)I[mg][3], acc.f[mg][3]);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(sp[mg] + (kbase >> 4) + 4 * t);
+        int cc[4];
+        mma_s8_k16(cc, m0, m1, b0);
+        acc.m[mg][0] = fmaf(nA, (float)cc[0], acc.m[mg][0]);
+        acc.m[mg][1] = fmaf(nA, (float)cc[1], acc.m[mg][1]);
+        acc.m[mg][2] = fmaf(nB, (float)cc[2], acc.m[mg][2]);
+        acc.m[mg][3] = fmaf(nB, (float)cc[3], acc.m[mg][3]);
+    }
+}
+
+// A Q3_K super-block (src/quant.cpp:514-553): 32 mask bytes, 64 bytes of 2-bit quants, sixteen 6-bit scales in 12
+// bytes, d; value = d * (scale - 32) * (q2 - (mask bit ? 0 : 4)). The A operand is 32 * (q3 - 4) with q3 = q2 + 4 *
+// mask bit: q2 at bits 5-6 and the inverted mask bit at bit 7 (a 3-bit two's complement at the top of the byte),
+// two shifts, an AND and an AND-OR per four quants; the 32 leaves with d. Blocks are 110 bytes: every other one is
+// 2 bytes off a word boundary (MODE as for Q6_K).
+template <int NG, int MODE>
+__device__ __forceinline__ void unit_q3_k(const uint8_t *blkA, const uint8_t *blkB, int kbase, const int8_t *const (&bp)[NG],
+                                          int t, Accum<NG> &acc) {
+    uint32_t SA[4], SB[4];
+    {
+        const uint32_t a0 = ld_q6<MODE>(blkA, 96), a1 = ld_q6<MODE>(blkA, 100), a2 = ld_q6<MODE>(blkA, 104);
+        const uint32_t b0 = ld_q6<MODE>(blkB, 96), b1 = ld_q6<MODE>(blkB, 100), b2 = ld_q6<MODE>(blkB, 104);
+        // scale i: low four bits in the nibbles of bytes 0..7, high two in byte 8 + i % 4 at bits 2 * (i / 4)
+        SA[0] = (a0 & 0x0F0F0F0Fu) | ((a2 << 4) & 0x30303030u);
+        SA[1] = (a1 & 0x0F0F0F0Fu) | ((a2 << 2) & 0x30303030u);
+        SA[2] = ((a0 >> 4) & 0x0F0F0F0Fu) | (a2 & 0x30303030u);
+        SA[3] = ((a1 >> 4) & 0x0F0F0F0Fu) | ((a2 >> 2) & 0x30303030u);
+        SB[0] = (b0 & 0x0F0F0F0Fu) | ((b2 << 4) & 0x30303030u);
+        SB[1] = (b1 & 0x0F0F0F0Fu) | ((b2 << 2) & 0x30303030u);
+        SB[2] = ((b0 >> 4) & 0x0F0F0F0Fu) | (b2 & 0x30303030u);
+        SB[3] = ((b1 >> 4) & 0x0F0F0F0Fu) | ((b2 >> 2) & 0x30303030u);
+#pragma unroll
+        for (int k = 0; k < 4; k++) {   // scale - 32 as signed bytes: add 0x60 (no carry: scale <= 63), flip the sign bit
+            SA[k] = (SA[k] + 0x60606060u) ^ 0x80808080u;
+            SB[k] = (SB[k] + 0x60606060u) ^ 0x80808080u;
+        }
+    }
+    const uint32_t hmA[2] = {~ld_q6<MODE>(blkA, 4 * t), ~ld_q6<MODE>(blkA, 16 + 4 * t)};
+    const uint32_t hmB[2] = {~ld_q6<MODE>(blkB, 4 * t), ~ld_q6<MODE>(blkB, 16 + 4 * t)};
+    int I[NG][4];
+#pragma unroll
+    for (int mg = 0; mg < NG; mg++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) I[mg][j] = 0;
+#pragma unroll
+    for (int n = 0; n < 2; n++) {
+        const uint32_t qA[2] = {ld_q6<MODE>(blkA, 32 + 32 * n + 4 * t), ld_q6<MODE>(blkA, 48 + 32 * n + 4 * t)};
+        const uint32_t qB[2] = {ld_q6<MODE>(blkB, 32 + 32 * n + 4 * t), ld_q6<MODE>(blkB, 48 + 32 * n + 4 * t)};
+#pragma unroll
+        for (int js = 0; js < 8; js++) {
+            const int j = js >> 1, s = js & 1, G = 8 * n + js, hb = 4 * n + j;
+            const uint32_t qa = j < 3 ? (qA[s] << (5 - 2 * j)) : (qA[s] >> 1), qb = j < 3 ? (qB[s] << (5 - 2 * j)) : (qB[s] >> 1);
+            const uint32_t a0 = (qa & 0x60606060u) | ((hmA[s] << (7 - hb)) & 0x80808080u);
+            const uint32_t a1 = (qb & 0x60606060u) | ((hmB[s] << (7 - hb)) & 0x80808080u);
+            const int sa = sext_byte(SA[G >> 2], G & 3), sb = sext_byte(SB[G >> 2], G & 3);
+#pragma unroll
+            for (int mg = 0; mg < NG; mg++) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 16 * G + 4 * t);
+                int cc[4];
+                mma_s8_k16(cc, a0, a1, b0);
+                I[mg][0] += sa * cc[0];
+                I[mg][1] += sa * cc[1];
+                I[mg][2] += sb * cc[2];
+                I[mg][3] += sb * cc[3];
+            }
+        }
+    }
+    const float dA = 0.03125f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blkA + 108)));
+    const float dB = 0.03125f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blkB + 108)));
+#pragma unroll
+    for (int mg = 0; mg < NG; mg++) {
+        acc.f[mg][0] = fmaf(dA, (float)I[mg][0], acc.f[mg][0]);
+        acc.f[mg][1] = fmaf(dA, (float)I[mg][1], acc.f[mg][1]);
+        acc.f[mg][2] = fmaf(dB, (float)I[mg][2], acc.f[mg][2]);
+        acc.f[mg][3] = fmaf(dB, (float)I[mg][3], acc.f[mg][3]);
+    }
+}
+
 // ---- the kernel ------------------------------------------------------------------------------------------
 // Three roles, connected only by mbarriers, so no warp ever waits at a CTA-wide barrier while
 // weights are streaming:
@@ -1076,7 +1211,9 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
 template <int WT, int NG>
 constexpr bool kTwoPerSm = NG == 1 || (NG == 2 && WT == KRK_CUDA_Q8_0);
 
-template <int WT, int NG, bool STACK, int SINGLE>
+// RAG: the form for ragged rows of Q6_K and Q3_K, whose units find each word's alignment from its address; compiled
+// apart so that the usual form does not carry a third copy of the unit.
+template <int WT, int NG, bool STACK, int SINGLE, bool RAG = false>
 __global__ void __launch_bounds__(kThreads, kTwoPerSm<WT, NG> ? 2 : 1)
 gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     // STACK: several 16-row tiles per stage (p.tps of them); compiled apart so that the usual one-tile
@@ -1144,8 +1281,8 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                         tma_box(smem_u32(dst), &p.wmap[s.mat], s.row0, s.unit0 / p.tma_unit_div, full);
                     }
                 }
-            } else if (p.ragged) {
-                // a stage starts a multiple of 8 units (1680 bytes) into its rows, so a row lies equally far off
+            } else if ((WT == KRK_CUDA_Q6_K || WT == KRK_CUDA_Q2_K || WT == KRK_CUDA_Q3_K) && p.ragged) {
+                // a stage starts a multiple of 8 units (a multiple of 16 bytes in all three formats) into its rows, so a row lies equally far off
                 // a 16-byte boundary in every stage
                 const uint32_t bytes = (uint32_t)s.n_units * F::unit_bytes;
                 uint32_t total = 0;
@@ -1331,11 +1468,11 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                 // (stacked tiles: every sub-tile prepares its own copy)
                 xs[r] = r < p.rows ? prepare_x_row<WT>(prepared + (size_t)r * p.n_in, p,
                                                        planes + (size_t)(r * 3) * plane_stride(p.n_in),
-                                                       chunk_sum + (size_t)(r * 4) * (p.n_in >> 5),
+                                                       chunk_sum + (size_t)(r * 4) * (p.n_in >> kSumShift<WT>),
                                                        stacked_idle ? kConsumerWarps : my_unit, lane)
                                    : 0.0f;
             __syncwarp();
-            if (!SINGLE) lane_planes<NG>(planes, chunk_sum, p.n_in, p.rows, g, bp, sp);
+            if (!SINGLE) lane_planes<NG>(planes, chunk_sum, p.n_in, p.n_in >> kSumShift<WT>, p.rows, g, bp, sp);
             if (WT == KRK_CUDA_Q5_1) {
 #pragma unroll
                 for (int mg = 0; mg < NG; mg++) {   // per-block sums of the group's even and odd activation rows
@@ -1356,7 +1493,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         for (int tile = 0; tile < n_tiles; tile++) {
             // ragged rows: how far this lane's two rows sit into their slots of a stage
             uint32_t ragA = 0, ragB = 0;
-            if (WT == KRK_CUDA_Q6_K && p.ragged) {
+            if (RAG || (WT == KRK_CUDA_Q2_K && p.ragged)) {
                 const int row = r0 + (tile / p.step) * stage_rows + kTileRows * my_sub + g;
                 const uintptr_t base = reinterpret_cast<uintptr_t>(tv.mat[m + tile % p.step].w);
                 ragA = (uint32_t)((base + (size_t)row * p.row_bytes) & 15);
@@ -1389,10 +1526,16 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                             unit_q5_0<NG>(rowA, rowB, kbase, bp, t, acc);
                         } else if (WT == KRK_CUDA_IQ4_NL) {
                             unit_iq4_nl<NG>(rowA, rowB, kbase, bp, t, acc);
+                        } else if (WT == KRK_CUDA_Q2_K) {
+                            unit_q2_k<NG>(rowA, rowB, kbase, bp, sp, t, acc);
+                        } else if (WT == KRK_CUDA_Q3_K) {
+                            if (RAG) unit_q3_k<NG, 2>(rowA, rowB, kbase, bp, t, acc);
+                            else if (unit & 1) unit_q3_k<NG, 1>(rowA, rowB, kbase, bp, t, acc);
+                            else unit_q3_k<NG, 0>(rowA, rowB, kbase, bp, t, acc);
                         } else if (WT == KRK_CUDA_Q5_1) {
                             unit_q5_1<NG>(rowA, rowB, kbase, bp, fe, fo, t, acc);
                         } else {
-                            if (p.ragged) unit_q6_k<NG, 2>(rowA, rowB, kbase, bp, t, acc);
+                            if (RAG) unit_q6_k<NG, 2>(rowA, rowB, kbase, bp, t, acc);
                             else if (unit & 1) unit_q6_k<NG, 1>(rowA, rowB, kbase, bp, t, acc);
                             else unit_q6_k<NG, 0>(rowA, rowB, kbase, bp, t, acc);
                         }
@@ -1442,7 +1585,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                      o[mg].y = fmaf(wo0, acc.f[mg][0], wo1 * acc.f[mg][1]);   // row g,   odd
                      o[mg].z = fmaf(we0, acc.f[mg][2], we1 * acc.f[mg][3]);   // row g+8, even
                      o[mg].w = fmaf(wo0, acc.f[mg][2], wo1 * acc.f[mg][3]);   // row g+8, odd
-                     if (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q5_K) {
+                     if (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q5_K || WT == KRK_CUDA_Q2_K) {
                          o[mg].x -= fmaf(me0, acc.m[mg][0], me1 * acc.m[mg][1]);
                          o[mg].y -= fmaf(mo0, acc.m[mg][0], mo1 * acc.m[mg][1]);
                          o[mg].z -= fmaf(me0, acc.m[mg][2], me1 * acc.m[mg][3]);
@@ -1479,10 +1622,10 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     }
 }
 
-template <int WT, int NG, bool STACK, int SINGLE>
+template <int WT, int NG, bool STACK, int SINGLE, bool RAG = false>
 int launch_one(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
     static bool configured[64] = {};   // per instantiation and device: the opt-in is sticky
-    auto kernel = gemv_stream_kernel<WT, NG, STACK, SINGLE>;
+    auto kernel = gemv_stream_kernel<WT, NG, STACK, SINGLE, RAG>;
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
@@ -1545,6 +1688,8 @@ bool setup_format(StreamParams &p, int64_t n_in, int rows, int silu_pair, size_t
             p.ragged = 1;
         }
     }
+    // Q2_K rows are 16-byte multiples for K % 1024 == 0, Q3_K rows for K % 2048 == 0
+    if ((WT == KRK_CUDA_Q2_K || WT == KRK_CUDA_Q3_K) && (p.row_bytes & 15) != 0) p.ragged = 1;
     const int ku_max = p.whole_tiles ? p.units : (p.units < kConsumerWarps ? p.units : kConsumerWarps);
     p.tps = kConsumerWarps / p.units;   // 0 when a tile has more units than there are consumer warps
     p.tps = p.tps < 1 ? 1 : (p.tps > kMaxStack ? kMaxStack : p.tps);
@@ -1608,6 +1753,18 @@ int launch_rows(const StreamParams &p, int grid, size_t smem, cudaStream_t st) {
         if (p.rows <= 4) return p.tps > 1 ? launch_one<WT, 2, true, 0>(p, grid, smem, st) : launch_one<WT, 2, false, 0>(p, grid, smem, st);
         return p.tps > 1 ? launch_one<WT, 4, true, 0>(p, grid, smem, st) : launch_one<WT, 4, false, 0>(p, grid, smem, st);
     } else {
+        if constexpr (WT == KRK_CUDA_Q6_K || WT == KRK_CUDA_Q3_K) {
+            if (p.ragged) {
+                if (p.tps > 1) {
+                    if (p.rows <= 2) return launch_one<WT, 1, true, 0, true>(p, grid, smem, st);
+                    if (p.rows <= 4) return launch_one<WT, 2, true, 0, true>(p, grid, smem, st);
+                    return launch_one<WT, 4, true, 0, true>(p, grid, smem, st);
+                }
+                if (p.rows <= 2) return launch_one<WT, 1, false, 0, true>(p, grid, smem, st);
+                if (p.rows <= 4) return launch_one<WT, 2, false, 0, true>(p, grid, smem, st);
+                return launch_one<WT, 4, false, 0, true>(p, grid, smem, st);
+            }
+        }
         if (p.tps > 1) {
             if (kQ4K && p.rows == 1) return launch_one<WT, 1, true, kQ4K ? 2 : 0>(p, grid, smem, st);
             if (p.rows <= 2) return launch_one<WT, 1, true, 0>(p, grid, smem, st);
@@ -1868,6 +2025,8 @@ int launch_gemv_stream(const GemvMat *mats, int n_mat, int64_t n_in, int rows, i
     case KRK_CUDA_Q8_0: return launch_fmt<KRK_CUDA_Q8_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q4_0: return launch_fmt<KRK_CUDA_Q4_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q5_K: return launch_fmt<KRK_CUDA_Q5_K>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
+    case KRK_CUDA_Q2_K: return launch_fmt<KRK_CUDA_Q2_K>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
+    case KRK_CUDA_Q3_K: return launch_fmt<KRK_CUDA_Q3_K>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_IQ4_NL: return launch_fmt<KRK_CUDA_IQ4_NL>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q5_0: return launch_fmt<KRK_CUDA_Q5_0>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
     case KRK_CUDA_Q5_1: return launch_fmt<KRK_CUDA_Q5_1>(mats, n_mat, n_in, rows, accumulate, silu_pair, st);
@@ -1883,6 +2042,8 @@ int launch_gemv_stream_table(const StreamTable *table, int wt, int64_t n_in, int
     case KRK_CUDA_Q8_0: return launch_table_fmt<KRK_CUDA_Q8_0>(table, n_in, silu_pair, banks, st);
     case KRK_CUDA_Q4_0: return launch_table_fmt<KRK_CUDA_Q4_0>(table, n_in, silu_pair, banks, st);
     case KRK_CUDA_Q5_K: return launch_table_fmt<KRK_CUDA_Q5_K>(table, n_in, silu_pair, banks, st);
+    case KRK_CUDA_Q2_K: return launch_table_fmt<KRK_CUDA_Q2_K>(table, n_in, silu_pair, banks, st);
+    case KRK_CUDA_Q3_K: return launch_table_fmt<KRK_CUDA_Q3_K>(table, n_in, silu_pair, banks, st);
     case KRK_CUDA_IQ4_NL: return launch_table_fmt<KRK_CUDA_IQ4_NL>(table, n_in, silu_pair, banks, st);
     case KRK_CUDA_Q5_0: return launch_table_fmt<KRK_CUDA_Q5_0>(table, n_in, silu_pair, banks, st);
     case KRK_CUDA_Q5_1: return launch_table_fmt<KRK_CUDA_Q5_1>(table, n_in, silu_pair, banks, st);
@@ -1897,6 +2058,8 @@ int launch_gemv_stream_peers(const GemvMat &mat, int64_t n_in, int rows, const P
     case KRK_CUDA_Q8_0: return launch_peers_fmt<KRK_CUDA_Q8_0>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q4_0: return launch_peers_fmt<KRK_CUDA_Q4_0>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q5_K: return launch_peers_fmt<KRK_CUDA_Q5_K>(mat, n_in, rows, ps, st);
+    case KRK_CUDA_Q2_K: return launch_peers_fmt<KRK_CUDA_Q2_K>(mat, n_in, rows, ps, st);
+    case KRK_CUDA_Q3_K: return launch_peers_fmt<KRK_CUDA_Q3_K>(mat, n_in, rows, ps, st);
     case KRK_CUDA_IQ4_NL: return launch_peers_fmt<KRK_CUDA_IQ4_NL>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q5_0: return launch_peers_fmt<KRK_CUDA_Q5_0>(mat, n_in, rows, ps, st);
     case KRK_CUDA_Q5_1: return launch_peers_fmt<KRK_CUDA_Q5_1>(mat, n_in, rows, ps, st);
@@ -1919,6 +2082,8 @@ int stream_gran(int wt, int64_t n_in, bool banks) {
     case KRK_CUDA_Q8_0: return gran_fmt<KRK_CUDA_Q8_0>(n_in, banks);
     case KRK_CUDA_Q4_0: return gran_fmt<KRK_CUDA_Q4_0>(n_in, banks);
     case KRK_CUDA_Q5_K: return gran_fmt<KRK_CUDA_Q5_K>(n_in, banks);
+    case KRK_CUDA_Q2_K: return gran_fmt<KRK_CUDA_Q2_K>(n_in, banks);
+    case KRK_CUDA_Q3_K: return gran_fmt<KRK_CUDA_Q3_K>(n_in, banks);
     case KRK_CUDA_IQ4_NL: return gran_fmt<KRK_CUDA_IQ4_NL>(n_in, banks);
     case KRK_CUDA_Q5_0: return gran_fmt<KRK_CUDA_Q5_0>(n_in, banks);
     case KRK_CUDA_Q5_1: return gran_fmt<KRK_CUDA_Q5_1>(n_in, banks);

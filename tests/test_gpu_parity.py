@@ -152,7 +152,7 @@ def test_config4_q6_k_head_slice_and_linearity(cuda, oracle):
 def test_path_selection(cuda, oracle):
     """Which kernel serves which shape: K not a multiple of 256 and the formats without a streaming arm take the
     shape-agnostic kernel; Q6_K rows that are not 16-byte multiples
-    (K = 1536) still stream, as whole tiles; Q4_0, Q5_K, Q5_0, Q5_1 and IQ4_NL stream (stacked tiles at K = 1024); Q2_K and Q3_K do not."""
+    (K = 1536) still stream, as whole tiles; every block format streams when K is a multiple of 256 (stacked tiles at K <= 1024)."""
     run_gemv(cuda, oracle, synth.Q4_0, 64, 1024, 1, SEED + 30, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q4_0, 4099, 4096, 1, SEED + 37, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q4_0, 1001, 11008, 1, SEED + 38, random_payload=True, expect_stream=True)
@@ -162,15 +162,19 @@ def test_path_selection(cuda, oracle):
     run_gemv(cuda, oracle, synth.Q5_K, 1001, 4096, 1, SEED + 42, random_payload=True, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q5_K, 333, 4096, 8, SEED + 43, random_payload=True, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q5_K, 77, 11008, 2, SEED + 45, random_payload=True, expect_stream=True)
-    for k, wt in enumerate((synth.Q5_0, synth.Q5_1, synth.IQ4_NL)):
+    for k, wt in enumerate((synth.Q5_0, synth.Q5_1, synth.IQ4_NL, synth.Q2_K, synth.Q3_K)):
         run_gemv(cuda, oracle, wt, 64, 1024, 1, SEED + 44 + 100 * k, expect_stream=True)
         run_gemv(cuda, oracle, wt, 4099, 4096, 1, SEED + 46 + 100 * k, random_payload=True, expect_stream=True)
         run_gemv(cuda, oracle, wt, 1001, 11008, 2, SEED + 47 + 100 * k, random_payload=True, expect_stream=True)
         run_gemv(cuda, oracle, wt, 333, 4096, 3, SEED + 48 + 100 * k, random_payload=True, expect_stream=True)
         run_gemv(cuda, oracle, wt, 77, 2048, 8, SEED + 49 + 100 * k, random_payload=True, expect_stream=True)
         run_gemv(cuda, oracle, wt, 50, 256, 1, SEED + 50 + 100 * k, expect_stream=True)
-    run_gemv(cuda, oracle, synth.Q2_K, 64, 1024, 1, SEED + 51, expect_stream=False)
-    run_gemv(cuda, oracle, synth.Q3_K, 64, 1024, 2, SEED + 52, expect_stream=False)
+    # Q2_K / Q3_K rows are 16-byte multiples only for K % 1024 / K % 2048 == 0: both kinds of row, odd unit counts
+    for k, wt in enumerate((synth.Q2_K, synth.Q3_K)):
+        run_gemv(cuda, oracle, wt, 300, 768, 2, SEED + 51 + 100 * k, random_payload=True, expect_stream=True)
+        run_gemv(cuda, oracle, wt, 129, 5120, 1, SEED + 52 + 100 * k, random_payload=True, expect_stream=True)
+        run_gemv(cuda, oracle, wt, 64, 8192, 4, SEED + 53 + 100 * k, expect_stream=True)
+        run_gemv(cuda, oracle, wt, 40, 1280, 1, SEED + 54 + 100 * k, accumulate=True, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q8_0, 64, 96, 1, SEED + 31, expect_stream=False)
     run_gemv(cuda, oracle, synth.Q6_K, 4096, 1536, 1, SEED + 32, expect_stream=True)
     run_gemv(cuda, oracle, synth.Q6_K, 1001, 1536, 8, SEED + 33, expect_stream=True)
@@ -204,7 +208,7 @@ def test_gemv_nonfinite_activation_gives_nan(cuda):
     assert torch.isnan(cuda.gemv(x, w0, synth.Q4_0, 32, 512)).all()
     x[100] = 0.0
     assert torch.isfinite(cuda.gemv(x, w0, synth.Q4_0, 32, 512)).all()
-    for wt in (synth.Q5_0, synth.Q5_1, synth.IQ4_NL, synth.Q5_K, synth.Q6_K, synth.Q8_0):
+    for wt in (synth.Q5_0, synth.Q5_1, synth.IQ4_NL, synth.Q2_K, synth.Q3_K, synth.Q5_K, synth.Q6_K, synth.Q8_0):
         w5 = dev(synth.weights(wt, 32, 512, SEED + 36))
         x[77] = float("-inf")
         assert torch.isnan(cuda.gemv(x, w5, wt, 32, 512)).all()
