@@ -38,7 +38,7 @@ extern "C" {
 #define KRK_CUDA_Q5_1 7
 #define KRK_CUDA_Q5_K 13
 /* and the low-bit formats of Q2_K / Q3_K_M / IQ4_NL files (src/quant.cpp:398-424, 514-553, 566-575): bit-exact
- * decode, shape-agnostic GEMV, embedding gather, prefill GEMM (raw blocks staged by the decode warps, decoded
+ * decode, streaming GEMV, embedding gather, prefill GEMM (raw blocks staged by the decode warps, decoded
  * element by element) */
 #define KRK_CUDA_Q2_K 10
 #define KRK_CUDA_Q3_K 11

@@ -1,7 +1,8 @@
 // Shape-agnostic decode GEMV: one warp per output row, lanes stride over 32-value chunks staged in shared
 // memory, f32 accumulation, shuffle reduction. It takes every legal shape (any n_in that is a
 // whole number of blocks, any alignment the format allows) and is the path for shapes the
-// streaming kernel does not address and for Q4_0. Same contract as gemv_kernel /
+// streaming kernel does not address (K not a multiple of 256, activations too wide for shared
+// memory). Same contract as gemv_kernel /
 // gemv_m_kernel of the reference (src/hip/kernels/gemm.hpp:76-167) with f32 activations.
 #include "krk_chunk.cuh"
 

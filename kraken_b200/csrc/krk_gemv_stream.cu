@@ -1418,7 +1418,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     const int wid = warp - 1, g = lane >> 2, t = lane & 3;
     const float *prepared = nullptr;
     const int8_t *bp[NG], *sp[NG];
-    const float *fe[NG], *fo[NG];
+    const float *fe[NG], *fo[NG];   // Q5_1: per-block sums of the even / odd activation row of each column group
     float xs[2 * NG];   // this warp's scale of each activation row
     Accum<NG> acc;
     AccumSingle acs;
