@@ -6,7 +6,9 @@
  * Conventions (they mirror krk::Backend, include/krk/backend.hpp:337):
  *  - every data pointer is a DEVICE pointer unless the parameter is named host_*;
  *  - weights are the unmodified GGUF bytes, row-major [n_out][krk_cuda_row_bytes()],
- *    16-byte aligned at the base, resident and not written while a call is in flight;
+ *    16-byte aligned at the base, resident and not written while a call is in flight; a kernel may read the
+ *    whole 16-byte granule that holds a matrix's last byte (rows whose size is not a multiple of 16 bytes are
+ *    fetched in aligned 16-byte pieces), which device allocations always cover;
  *  - activations and outputs are f32 (the CPU backend's activation type,
  *    src/backend_cpu.cpp:584), except the f16 X of the prefill entry;
  *  - `stream` is a cudaStream_t passed as void* (NULL = the default stream, which is
