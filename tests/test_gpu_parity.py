@@ -150,7 +150,7 @@ def test_config4_q6_k_head_slice_and_linearity(cuda, oracle):
 
 
 def test_path_selection(cuda, oracle):
-    """Which kernel serves which shape: K not a multiple of 256 and the formats without a streaming arm take the
+    """Which kernel serves which shape: K not a multiple of 256 takes the
     shape-agnostic kernel; Q6_K rows that are not 16-byte multiples
     (K = 1536) still stream, as whole tiles; every block format streams when K is a multiple of 256 (stacked tiles at K <= 1024)."""
     run_gemv(cuda, oracle, synth.Q4_0, 64, 1024, 1, SEED + 30, expect_stream=True)
@@ -356,12 +356,16 @@ def test_moe_routed_equals_route_then_ffn(cuda):
 
 
 @pytest.mark.parametrize("wt_gu,wt_dn", [(synth.Q4_0, synth.Q8_0), (synth.Q5_K, synth.Q4_K), (synth.Q8_0, synth.Q5_K),
-                                          (synth.Q6_K, synth.Q4_0), (synth.Q5_0, synth.Q5_1)])
+                                          (synth.Q6_K, synth.Q4_0), (synth.Q5_0, synth.Q5_1), (synth.Q5_1, synth.IQ4_NL),
+                                          (synth.IQ4_NL, synth.Q2_K), (synth.Q2_K, synth.Q3_K), (synth.Q3_K, synth.Q6_K)])
 def test_moe_other_expert_formats(cuda, oracle, wt_gu, wt_dn):
-    """Expert banks in the other formats: the device-table launches of every streaming arm (Q4_0, Q5_K, Q8_0, Q6_K
-    with 16-byte-multiple rows, Q4_K down) and the warp-per-row kernels (Q5_0 / Q5_1), whole bank and a shard."""
+    """Expert banks in the other formats: the device-table launches of every streaming arm, whole bank and a shard.
+    Hidden 2048 gives Q6_K / Q3_K rows of 16-byte multiples, expert width 1024 gives Q2_K such rows; the second
+    shape (hidden 1280, width 768) makes the rows of all three ragged."""
     moe_case(cuda, oracle, 2048, 1024, 8, 2, 3, SEED + 13, wt_gu=wt_gu, wt_dn=wt_dn)
     moe_case(cuda, oracle, 2048, 1024, 8, 4, 1, SEED + 14, local=(4, 8), wt_gu=wt_gu, wt_dn=wt_dn)
+    if wt_gu in (synth.Q6_K, synth.Q2_K, synth.Q3_K) or wt_dn in (synth.Q6_K, synth.Q2_K, synth.Q3_K):
+        moe_case(cuda, oracle, 1280, 768, 8, 2, 2, SEED + 15, wt_gu=wt_gu, wt_dn=wt_dn)
 
 
 def test_moe_small(cuda, oracle):
