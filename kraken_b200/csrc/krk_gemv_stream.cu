@@ -521,6 +521,13 @@ __device__ __forceinline__ float prepare_x_row(const float *__restrict__ xr, con
 // A fragments of rows g and g+8, column g of the B fragment (limb g%3 of activation row g/3 of
 // the column group), and accumulator columns 2t, 2t+1.
 
+// Column groups that go through the MMAs. One or two groups carry two activation rows each in columns 0..5. The
+// form for five to eight rows has four groups of outputs but multiplies only three: rows 0..5 sit in columns 0..5
+// of groups 0..2 and rows 6 and 7 in the spare columns 6 and 7, limb mg of the row in group mg, so that 24 columns
+// carry 8 rows x 3 limbs with none to spare.
+template <int NG>
+constexpr int kMmaGroups = NG == 4 ? 3 : NG;
+
 template <int NG>
 struct Accum {
     float f[NG][4];   // [group][(row g | g+8) x (col 2t | 2t+1)], already times the block scale d
@@ -547,8 +554,13 @@ __device__ __forceinline__ void lane_planes(const int8_t *planes, const int8_t *
                                             const int8_t *(&bp)[NG], const int8_t *(&sp)[NG]) {
 #pragma unroll
     for (int mg = 0; mg < NG; mg++) {
-        const int r = min(2 * mg + (g % 6) / 3, rows - 1);
-        bp[mg] = planes + (size_t)(r * 3 + g % 3) * plane_stride(n_in);
+        int r = 2 * mg + (g % 6) / 3, limb = g % 3;
+        if (NG == 4 && g >= 6) {   // the spare columns: limb mg of activation row 6 or 7 (group 3 multiplies nothing)
+            r = g;
+            limb = mg % 3;
+        }
+        r = min(r, rows - 1);
+        bp[mg] = planes + (size_t)(r * 3 + limb) * plane_stride(n_in);
         // chunk sums: column c = limb c%4 of activation row c/4 of the group
         const int rs = min(2 * mg + g / 4, rows - 1);
         sp[mg] = chunk_sum + (size_t)(rs * 4 + g % 4) * n_sums;
@@ -575,7 +587,7 @@ __device__ __forceinline__ void unit_q4_k(const uint8_t *rowA, const uint8_t *ro
     const uint32_t mnB[2] = {hB.z & 0x3F3F3F3Fu, ((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u)};
     int I[NG][4];
 #pragma unroll
-    for (int mg = 0; mg < NG; mg++)
+    for (int mg = 0; mg < kMmaGroups<NG>; mg++)
 #pragma unroll
         for (int j = 0; j < 4; j++) I[mg][j] = 0;
 #pragma unroll
@@ -595,7 +607,7 @@ __device__ __forceinline__ void unit_q4_k(const uint8_t *rowA, const uint8_t *ro
             }
             const int sa = (scA[c >> 2] >> (8 * (c & 3))) & 0xFF, sb = (scB[c >> 2] >> (8 * (c & 3))) & 0xFF;
 #pragma unroll
-            for (int mg = 0; mg < NG; mg++) {
+            for (int mg = 0; mg < kMmaGroups<NG>; mg++) {
                 const uint2 b = *reinterpret_cast<const uint2 *>(bp[mg] + kbase + 32 * c + 8 * t);
                 int cc[4];
                 mma_s8_k32(cc, a0, a1, a2, a3, b.x, b.y);
@@ -608,7 +620,7 @@ __device__ __forceinline__ void unit_q4_k(const uint8_t *rowA, const uint8_t *ro
     }
     const float dA = half_lo(hA.x), dB = half_lo(hB.x);
 #pragma unroll
-    for (int mg = 0; mg < NG; mg++) {
+    for (int mg = 0; mg < kMmaGroups<NG>; mg++) {
         acc.f[mg][0] = fmaf(dA, (float)I[mg][0], acc.f[mg][0]);
         acc.f[mg][1] = fmaf(dA, (float)I[mg][1], acc.f[mg][1]);
         acc.f[mg][2] = fmaf(dB, (float)I[mg][2], acc.f[mg][2]);
@@ -769,7 +781,7 @@ __device__ __forceinline__ void unit_q4_0_rows(const uint8_t *rowA, const uint8_
         dA *= 0.0625f;
         dB *= 0.0625f;
 #pragma unroll
-        for (int mg = 0; mg < NG; mg++) {
+        for (int mg = 0; mg < kMmaGroups<NG>; mg++) {
             const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 4 * t);
             const uint32_t b1 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 16 + 4 * t);
             int c[4] = {0x4B400000, 0x4B400000, 0x4B400000, 0x4B400000};
@@ -830,7 +842,7 @@ __device__ __forceinline__ void unit_iq4_nl(const uint8_t *rowA, const uint8_t *
         grid(qa, la, ha);
         grid(qb, lb, hb);
 #pragma unroll
-        for (int mg = 0; mg < NG; mg++) {
+        for (int mg = 0; mg < kMmaGroups<NG>; mg++) {
             const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 4 * t);
             const uint32_t b1 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 16 + 4 * t);
             int c[4] = {0x4B400000, 0x4B400000, 0x4B400000, 0x4B400000};   // |sum| <= 32 * 127 * 128 < 2^19
@@ -888,7 +900,7 @@ __device__ __forceinline__ void unit_q5_0(const uint8_t *rowA, const uint8_t *ro
         dA *= 0.125f;
         dB *= 0.125f;
 #pragma unroll
-        for (int mg = 0; mg < NG; mg++) {
+        for (int mg = 0; mg < kMmaGroups<NG>; mg++) {
             const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 4 * t);
             const uint32_t b1 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 16 + 4 * t);
             int c[4] = {0x4B400000, 0x4B400000, 0x4B400000, 0x4B400000};
@@ -920,13 +932,16 @@ __device__ __forceinline__ void unit_q5_1(const uint8_t *rowA, const uint8_t *ro
         const uint32_t ha = ((qa >> 1) & 0x78787878u) | spread_top((ma >> (16 + 4 * t)) & 0xFu);
         const uint32_t hb = ((qb >> 1) & 0x78787878u) | spread_top((mb >> (16 + 4 * t)) & 0xFu);
 #pragma unroll
-        for (int mg = 0; mg < NG; mg++) {
+        for (int mg = 0; mg < kMmaGroups<NG>; mg++) {
             const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 4 * t);
             const uint32_t b1 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 16 + 4 * t);
             int c[4] = {0x4B400000, 0x4B400000, 0x4B400000, 0x4B400000};   // |sum| <= 32 * 248 * 128 < 2^20
             mma_u8_k16_chain(c, la, lb, b0);
             mma_u8_k16_chain(c, ha, hb, b1);
-            const float se = t == 1 ? fe[mg][(kbase >> 5) + b] : 0.0f, so = t == 2 ? fo[mg][(kbase >> 5) + b] : 0.0f;
+            // (five to eight rows: the weight-1 limbs of rows 6 and 7 are columns 6 and 7 of group 2, in lane t = 3)
+            const bool spare = NG == 4 && mg == 2 && t == 3;
+            const float se = t == 1 ? fe[mg][(kbase >> 5) + b] : (spare ? fe[NG - 1][(kbase >> 5) + b] : 0.0f);
+            const float so = t == 2 ? fo[mg][(kbase >> 5) + b] : (spare ? fo[NG - 1][(kbase >> 5) + b] : 0.0f);
             acc.f[mg][0] = fmaf(dA, __int_as_float(c[0]) - kMagic, fmaf(oA, se, acc.f[mg][0]));
             acc.f[mg][1] = fmaf(dA, __int_as_float(c[1]) - kMagic, fmaf(oA, so, acc.f[mg][1]));
             acc.f[mg][2] = fmaf(dB, __int_as_float(c[2]) - kMagic, fmaf(oB, se, acc.f[mg][2]));
@@ -966,7 +981,7 @@ __device__ __forceinline__ void unit_q8_0(const uint8_t *rowA, const uint8_t *ro
             dB = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(rowB + 34 * b)));
         }
 #pragma unroll
-        for (int mg = 0; mg < NG; mg++) {
+        for (int mg = 0; mg < kMmaGroups<NG>; mg++) {
             const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 4 * t);
             const uint32_t b1 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 32 * b + 16 + 4 * t);
             int cc[4];   // (presetting the accumulator to 1.5 * 2^23 to save the int-to-float step is 0.3-3 % slower here)
@@ -1009,7 +1024,7 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
                                           int t, Accum<NG> &acc) {
     int I[NG][4];
 #pragma unroll
-    for (int mg = 0; mg < NG; mg++)
+    for (int mg = 0; mg < kMmaGroups<NG>; mg++)
 #pragma unroll
         for (int j = 0; j < 4; j++) I[mg][j] = 0;
 #pragma unroll
@@ -1042,7 +1057,7 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
             const uint32_t a1 = (lowB & 0x3C3C3C3Cu) | (hiB & 0xC0C0C0C0u);
             const int sa = sext_byte(scA[G >> 2], G & 3), sb = sext_byte(scB[G >> 2], G & 3);
 #pragma unroll
-            for (int mg = 0; mg < NG; mg++) {
+            for (int mg = 0; mg < kMmaGroups<NG>; mg++) {
                 const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 128 * h + 16 * G + 4 * t);
                 int cc[4];
                 mma_s8_k16(cc, a0, a1, b0);
@@ -1056,7 +1071,7 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
     const float dA = 0.25f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blkA + 208)));
     const float dB = 0.25f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blkB + 208)));
 #pragma unroll
-    for (int mg = 0; mg < NG; mg++) {
+    for (int mg = 0; mg < kMmaGroups<NG>; mg++) {
         acc.f[mg][0] = fmaf(dA, (float)I[mg][0], acc.f[mg][0]);
         acc.f[mg][1] = fmaf(dA, (float)I[mg][1], acc.f[mg][1]);
         acc.f[mg][2] = fmaf(dB, (float)I[mg][2], acc.f[mg][2]);
@@ -1081,7 +1096,7 @@ __device__ __forceinline__ void unit_q2_k(const uint8_t *blkA, const uint8_t *bl
     }
     int I[NG][4];
 #pragma unroll
-    for (int mg = 0; mg < NG; mg++)
+    for (int mg = 0; mg < kMmaGroups<NG>; mg++)
 #pragma unroll
         for (int j = 0; j < 4; j++) I[mg][j] = 0;
 #pragma unroll
@@ -1093,7 +1108,7 @@ __device__ __forceinline__ void unit_q2_k(const uint8_t *blkA, const uint8_t *bl
             const uint32_t a0 = (qA[s] >> (2 * j)) & 0x03030303u, a1 = (qB[s] >> (2 * j)) & 0x03030303u;
             const int sa = (scA[G >> 2] >> (8 * (G & 3))) & 0xF, sb = (scB[G >> 2] >> (8 * (G & 3))) & 0xF;
 #pragma unroll
-            for (int mg = 0; mg < NG; mg++) {
+            for (int mg = 0; mg < kMmaGroups<NG>; mg++) {
                 const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 16 * G + 4 * t);
                 int cc[4];
                 mma_s8_k16(cc, a0, a1, b0);
@@ -1108,11 +1123,14 @@ __device__ __forceinline__ void unit_q2_k(const uint8_t *blkA, const uint8_t *bl
     const float dA = half_lo(hA), dB = half_lo(hB), nA = half_hi(hA), nB = half_hi(hB);
     const uint32_t m0 = (wa[t] >> 4) & 0x0F0F0F0Fu, m1 = (wb[t] >> 4) & 0x0F0F0F0Fu;   // k slot j = group j: lane t brings 4t..4t+3
 #pragma unroll
-    for (int mg = 0; mg < NG; mg++) {
+    for (int mg = 0; mg < kMmaGroups<NG>; mg++) {
         acc.f[mg][0] = fmaf(dA, (float)I[mg][0], acc.f[mg][0]);
         acc.f[mg][1] = fmaf(dA, (float)I[mg][1], acc.f[mg][1]);
         acc.f[mg][2] = fmaf(dB, (float)I[mg][2], acc.f[mg][2]);
         acc.f[mg][3] = fmaf(dB, (float)I[mg][3], acc.f[mg][3]);
+    }
+#pragma unroll
+    for (int mg = 0; mg < NG; mg++) {
         const uint32_t b0 = *reinterpret_cast<const uint32_t *>(sp[mg] + (kbase >> 4) + 4 * t);
         int cc[4];
         mma_s8_k16(cc, m0, m1, b0);
@@ -1154,7 +1172,7 @@ __device__ __forceinline__ void unit_q3_k(const uint8_t *blkA, const uint8_t *bl
     const uint32_t hmB[2] = {~ld_q6<MODE>(blkB, 4 * t), ~ld_q6<MODE>(blkB, 16 + 4 * t)};
     int I[NG][4];
 #pragma unroll
-    for (int mg = 0; mg < NG; mg++)
+    for (int mg = 0; mg < kMmaGroups<NG>; mg++)
 #pragma unroll
         for (int j = 0; j < 4; j++) I[mg][j] = 0;
 #pragma unroll
@@ -1169,7 +1187,7 @@ __device__ __forceinline__ void unit_q3_k(const uint8_t *blkA, const uint8_t *bl
             const uint32_t a1 = (qb & 0x60606060u) | ((hmB[s] << (7 - hb)) & 0x80808080u);
             const int sa = sext_byte(SA[G >> 2], G & 3), sb = sext_byte(SB[G >> 2], G & 3);
 #pragma unroll
-            for (int mg = 0; mg < NG; mg++) {
+            for (int mg = 0; mg < kMmaGroups<NG>; mg++) {
                 const uint32_t b0 = *reinterpret_cast<const uint32_t *>(bp[mg] + kbase + 16 * G + 4 * t);
                 int cc[4];
                 mma_s8_k16(cc, a0, a1, b0);
@@ -1183,7 +1201,7 @@ __device__ __forceinline__ void unit_q3_k(const uint8_t *blkA, const uint8_t *bl
     const float dA = 0.03125f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blkA + 108)));
     const float dB = 0.03125f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blkB + 108)));
 #pragma unroll
-    for (int mg = 0; mg < NG; mg++) {
+    for (int mg = 0; mg < kMmaGroups<NG>; mg++) {
         acc.f[mg][0] = fmaf(dA, (float)I[mg][0], acc.f[mg][0]);
         acc.f[mg][1] = fmaf(dA, (float)I[mg][1], acc.f[mg][1]);
         acc.f[mg][2] = fmaf(dB, (float)I[mg][2], acc.f[mg][2]);
@@ -1581,10 +1599,19 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                  const float wo0 = t == 2 ? 256.0f : 0.0f, wo1 = t == 1 ? 65536.0f : (t == 2 ? 1.0f : 0.0f);
 #pragma unroll
                  for (int mg = 0; mg < NG; mg++) {
-                     o[mg].x = fmaf(we0, acc.f[mg][0], we1 * acc.f[mg][1]);   // row g,   even activation row
-                     o[mg].y = fmaf(wo0, acc.f[mg][0], wo1 * acc.f[mg][1]);   // row g,   odd
-                     o[mg].z = fmaf(we0, acc.f[mg][2], we1 * acc.f[mg][3]);   // row g+8, even
-                     o[mg].w = fmaf(wo0, acc.f[mg][2], wo1 * acc.f[mg][3]);   // row g+8, odd
+                     if (NG == 4 && mg == 3) {
+                         // activation rows 6 and 7 rode in columns 6 and 7 (lane t = 3) of groups 0..2, limb mg in group mg
+                         const float w0 = t == 3 ? 65536.0f : 0.0f, w1 = t == 3 ? 256.0f : 0.0f, w2 = t == 3 ? 1.0f : 0.0f;
+                         o[mg].x = fmaf(w0, acc.f[0][0], fmaf(w1, acc.f[1][0], w2 * acc.f[2][0]));
+                         o[mg].y = fmaf(w0, acc.f[0][1], fmaf(w1, acc.f[1][1], w2 * acc.f[2][1]));
+                         o[mg].z = fmaf(w0, acc.f[0][2], fmaf(w1, acc.f[1][2], w2 * acc.f[2][2]));
+                         o[mg].w = fmaf(w0, acc.f[0][3], fmaf(w1, acc.f[1][3], w2 * acc.f[2][3]));
+                     } else {
+                         o[mg].x = fmaf(we0, acc.f[mg][0], we1 * acc.f[mg][1]);   // row g,   even activation row
+                         o[mg].y = fmaf(wo0, acc.f[mg][0], wo1 * acc.f[mg][1]);   // row g,   odd
+                         o[mg].z = fmaf(we0, acc.f[mg][2], we1 * acc.f[mg][3]);   // row g+8, even
+                         o[mg].w = fmaf(wo0, acc.f[mg][2], wo1 * acc.f[mg][3]);   // row g+8, odd
+                     }
                      if (WT == KRK_CUDA_Q4_K || WT == KRK_CUDA_Q5_K || WT == KRK_CUDA_Q2_K) {
                          o[mg].x -= fmaf(me0, acc.m[mg][0], me1 * acc.m[mg][1]);
                          o[mg].y -= fmaf(mo0, acc.m[mg][0], mo1 * acc.m[mg][1]);
