@@ -207,6 +207,15 @@ __device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
         : "r"(a0), "r"(a1), "r"(b0), "r"(0));
 }
+// x << log2(M), issued as a multiply-add: the units below are bound by the integer ALU pipe (shifts, logic ops,
+// byte permutes) while the multiply-add pipe idles, so the left shifts of the operand assembly go there. The
+// compiler turns a plain `x * M` back into a shift.
+template <uint32_t M>
+__device__ __forceinline__ uint32_t shl_mad(uint32_t x) {
+    uint32_t r;
+    asm("mad.lo.u32 %0, %1, %2, 0;" : "=r"(r) : "r"(x), "n"(M));
+    return r;
+}
 __device__ __forceinline__ int sext_byte(uint32_t w, int i) {
     int r;
     asm("bfe.s32 %0, %1, %2, 8;" : "=r"(r) : "r"(w), "r"(8 * i));
@@ -1049,10 +1058,10 @@ __device__ __forceinline__ void unit_q6_k(const uint8_t *blkA, const uint8_t *bl
         for (int G = 0; G < 8; G++) {
             const int quad = G >> 1, s = G & 1;
             const uint32_t la = qlA[2 * (quad & 1) + s], lb = qlB[2 * (quad & 1) + s];
-            const uint32_t lowA = (quad & 2) ? (la >> 2) : (la << 2);
-            const uint32_t lowB = (quad & 2) ? (lb >> 2) : (lb << 2);
-            const uint32_t hiA = quad == 3 ? qhA[s] : (qhA[s] << (6 - 2 * quad));
-            const uint32_t hiB = quad == 3 ? qhB[s] : (qhB[s] << (6 - 2 * quad));
+            const uint32_t lowA = (quad & 2) ? (la >> 2) : shl_mad<4u>(la);
+            const uint32_t lowB = (quad & 2) ? (lb >> 2) : shl_mad<4u>(lb);
+            const uint32_t hiA = quad == 0 ? shl_mad<64u>(qhA[s]) : quad == 1 ? shl_mad<16u>(qhA[s]) : quad == 2 ? shl_mad<4u>(qhA[s]) : qhA[s];
+            const uint32_t hiB = quad == 0 ? shl_mad<64u>(qhB[s]) : quad == 1 ? shl_mad<16u>(qhB[s]) : quad == 2 ? shl_mad<4u>(qhB[s]) : qhB[s];
             const uint32_t a0 = (lowA & 0x3C3C3C3Cu) | (hiA & 0xC0C0C0C0u);
             const uint32_t a1 = (lowB & 0x3C3C3C3Cu) | (hiB & 0xC0C0C0C0u);
             const int sa = sext_byte(scA[G >> 2], G & 3), sb = sext_byte(scB[G >> 2], G & 3);
