@@ -216,6 +216,15 @@ __device__ __forceinline__ uint32_t shl_mad(uint32_t x) {
     asm("mad.lo.u32 %0, %1, %2, 0;" : "=r"(r) : "r"(x), "n"(M));
     return r;
 }
+__device__ __forceinline__ uint32_t shl_mad_n(uint32_t x, int k) {   // k is a constant once the caller's loops are unrolled
+    switch (k) {
+    case 1: return shl_mad<2u>(x);
+    case 2: return shl_mad<4u>(x);
+    case 3: return shl_mad<8u>(x);
+    case 4: return shl_mad<16u>(x);
+    default: return x << k;
+    }
+}
 __device__ __forceinline__ int sext_byte(uint32_t w, int i) {
     int r;
     asm("bfe.s32 %0, %1, %2, 8;" : "=r"(r) : "r"(w), "r"(8 * i));
@@ -609,10 +618,10 @@ __device__ __forceinline__ void unit_q4_k(const uint8_t *rowA, const uint8_t *ro
             uint32_t a0 = (qa.x >> (4 * nib)) & 0x0F0F0F0Fu, a1 = (qb.x >> (4 * nib)) & 0x0F0F0F0Fu;
             uint32_t a2 = (qa.y >> (4 * nib)) & 0x0F0F0F0Fu, a3 = (qb.y >> (4 * nib)) & 0x0F0F0F0Fu;
             if (FIFTH) {   // bit c of the mask bytes becomes bit 4 of the quants (0..31: still positive as s8)
-                a0 |= (c < 4 ? fa.x << (4 - c) : fa.x >> (c - 4)) & 0x10101010u;
-                a1 |= (c < 4 ? fb.x << (4 - c) : fb.x >> (c - 4)) & 0x10101010u;
-                a2 |= (c < 4 ? fa.y << (4 - c) : fa.y >> (c - 4)) & 0x10101010u;
-                a3 |= (c < 4 ? fb.y << (4 - c) : fb.y >> (c - 4)) & 0x10101010u;
+                a0 |= (c < 4 ? shl_mad_n(fa.x, 4 - c) : fa.x >> (c - 4)) & 0x10101010u;
+                a1 |= (c < 4 ? shl_mad_n(fb.x, 4 - c) : fb.x >> (c - 4)) & 0x10101010u;
+                a2 |= (c < 4 ? shl_mad_n(fa.y, 4 - c) : fa.y >> (c - 4)) & 0x10101010u;
+                a3 |= (c < 4 ? shl_mad_n(fb.y, 4 - c) : fb.y >> (c - 4)) & 0x10101010u;
             }
             const int sa = (scA[c >> 2] >> (8 * (c & 3))) & 0xFF, sb = (scB[c >> 2] >> (8 * (c & 3))) & 0xFF;
 #pragma unroll
